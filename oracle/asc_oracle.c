@@ -1,0 +1,489 @@
+/*
+ * CPU oracle for the Ascend C high-level operator hot path (TEST INFRASTRUCTURE, not product).
+ *
+ * This file restates, in plain C, the arithmetic that the reference's adv_api Matmul / SoftMax /
+ * AscendQuant / AscendDequant perform.  The reference executes that arithmetic inside the closed
+ * CANN CPU twin (tikicpulib: mad, mad_mx, copy_matrix_cc_to_gm, vector ops), which is not part of
+ * the reference tree, so every function below follows the reference call site, its documentation
+ * and its own golden-data scripts, cited per function (paths relative to the reference project).
+ *
+ * Parity pin: the fixpipe epilogues are pinned against the reference's algorithm scripts
+ * (fixpipe_l0c2gm/scripts/gen_data_{s322s8,f322s8,s322f16}.py), the casts against the worked
+ * examples of precision_conversion.md, and the GEMM / softmax / quant / dequant bodies against
+ * the example generators' numpy recipes; the fixtures live in tests/golden.  The reference's own
+ * kernel unit tests assert only all-zero outputs, so there are no stored result vectors to pin to.
+ *
+ * Only tests, the smoke check and the benchmark's cpu_baseline / reference arm may link this file.
+ * Build: gcc -O3 -march=x86-64-v3 -ffp-contract=off -fopenmp -shared -fPIC.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORC_API __attribute__((visibility("default")))
+
+/* dtype codes shared with include/ascb200.h */
+enum { ORC_F32 = 0, ORC_F16 = 1, ORC_BF16 = 2, ORC_S8 = 3, ORC_S32 = 4 };
+
+/* ---------------------------------------------------------------------------------------------
+ * Scalar conversions.  CAST_RINT = round to nearest, ties to even
+ * (docs/zh/api/SIMD-API/basic_api/data_structures/precision_conversion.md:19-23).
+ * ------------------------------------------------------------------------------------------- */
+static inline uint32_t f2u(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+static inline float u2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+
+ORC_API float orc_f16_to_f32(uint16_t h)
+{
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1Fu;
+    uint32_t man = h & 0x3FFu;
+    if (exp == 0) {
+        if (man == 0) return u2f(sign);
+        float v = (float)man * 5.9604644775390625e-08f; /* 2^-24 */
+        return sign ? -v : v;
+    }
+    if (exp == 31) return u2f(sign | 0x7F800000u | (man << 13));
+    return u2f(sign | ((exp + 112u) << 23) | (man << 13));
+}
+
+/* fp32 -> fp16, RINT.  sat != 0 clamps overflow to +-65504 (the reference's RndR SatS vector cast,
+ * impl/adv_api/detail/quantization/quant/ascend_quant_3510_impl.h:96); sat == 0 gives IEEE inf. */
+static inline uint16_t f32_to_f16(float f, int sat)
+{
+    uint32_t u = f2u(f);
+    uint16_t sign = (uint16_t)((u >> 16) & 0x8000u);
+    uint32_t a = u & 0x7FFFFFFFu;
+    if (a > 0x7F800000u) return (uint16_t)(sign | 0x7E00u);          /* NaN */
+    if (a >= 0x477FF000u) {                                          /* rounds to >= 65520 */
+        if (a == 0x7F800000u && !sat) return (uint16_t)(sign | 0x7C00u);
+        return (uint16_t)(sign | (sat ? 0x7BFFu : 0x7C00u));
+    }
+    if (a < 0x33000001u) return sign;                                /* |f| <= 2^-25 -> 0 */
+    int32_t e = (int32_t)(a >> 23) - 127;
+    uint32_t m = (a & 0x7FFFFFu) | 0x800000u;
+    int shift;
+    uint32_t base;
+    if (e < -14) { shift = 13 + (-14 - e); base = 0; }               /* subnormal half */
+    else { shift = 13; base = (uint32_t)(e + 15) << 10; m &= 0x7FFFFFu; }
+    uint32_t q = m >> shift;
+    uint32_t rem = m & ((1u << shift) - 1u);
+    uint32_t half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (q & 1u))) q++;
+    return (uint16_t)(sign | (base + q));                            /* carry into exponent is right */
+}
+ORC_API uint16_t orc_f32_to_f16(float f) { return f32_to_f16(f, 0); }
+ORC_API uint16_t orc_f32_to_f16_sat(float f) { return f32_to_f16(f, 1); }
+
+ORC_API float orc_bf16_to_f32(uint16_t b) { return u2f((uint32_t)b << 16); }
+ORC_API uint16_t orc_f32_to_bf16(float f)
+{
+    uint32_t u = f2u(f);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40u);
+    uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7FFFu + lsb;
+    return (uint16_t)(u >> 16);
+}
+
+/* float -> int8, RINT with saturation (precision_conversion.md:379-382). NaN -> 0. */
+static inline int8_t f32_to_s8_rint_sat(float f)
+{
+    if (f != f) return 0;
+    if (f >= 127.0f) return 127;
+    if (f <= -128.0f) return -128;
+    return (int8_t)nearbyintf(f);
+}
+ORC_API int8_t orc_f32_to_s8(float f) { return f32_to_s8_rint_sat(f); }
+
+/* fp4 e2m1 nibble -> value {0,.5,1,1.5,2,3,4,6} with sign; e8m0 byte -> 2^(b-127)
+ * (docs/zh/api/SIMD-API/basic_api/cube_compute_ISASI/mmad_compute/MmadMx.md:71-75). */
+static const float k_e2m1[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+ORC_API float orc_e2m1_to_f32(uint8_t nib)
+{
+    float v = k_e2m1[nib & 7u];
+    return (nib & 8u) ? -v : v;
+}
+ORC_API float orc_e8m0_to_f32(uint8_t b)
+{
+    if (b == 255) return NAN;
+    if (b == 0) return u2f(0x00400000u); /* 2^-127 */
+    return u2f((uint32_t)b << 23);
+}
+
+/* The (1,8,10) scale that fixpipe reads from bits [31:13] of the 64-bit quant parameter
+ * (examples/01_simd_cpp_api/03_basic_api/03_matrix_compute/fixpipe_l0c2gm/scripts/gen_data_s322s8.py:35-58;
+ *  equivalently float(bits & 0xFFFFE000), 04_advanced_api/00_matmul/matmul_quant/scripts/gen_data.py:37-40). */
+ORC_API float orc_quant_alpha(uint64_t q) { return u2f((uint32_t)(q & 0xFFFFE000u)); }
+static inline int quant_offset9(uint64_t q)
+{
+    /* gen_data_s322s8.py:46 reads the 9 bits as an unsigned value; the documentation calls the
+     * field a signed 9-bit offset.  Interpret two's complement: the scripts only use offset 0. */
+    int o = (int)((q >> 37) & 0x1FFu);
+    return (o & 0x100) ? o - 512 : o;
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * GEMM bodies.  Accumulation follows the adv_api scheduler: one output block accumulates K in
+ * sequential baseK chunks, the first chunk initialises (bias first when enabled)
+ * (impl/adv_api/detail/matmul/scheduler/base/scheduler_norm.h:193-296,
+ *  impl/adv_api/detail/matmul/scheduler/bias/bias_scheduler_v220.h:85-135).
+ * Inside a chunk the summation order of the cube unit is not documented; we sum k ascending.
+ * ------------------------------------------------------------------------------------------- */
+
+/* C[M,N] fp32 = A*B (+bias).  A is [M,K] (lda) or, transA, [K,M]; B is [K,N] (ldb) or, transB, [N,K].
+ * Elements are fp16 (is_bf16 == 0) or bf16.  Mmad.md:186-237 (fp16/bf16 in, fp32 accumulate). */
+ORC_API void orc_gemm_f16(const uint16_t* A, const uint16_t* B, const float* bias, float* C, int M, int N, int K,
+                          int lda, int ldb, int transA, int transB, int is_bf16, int baseK)
+{
+    if (baseK <= 0) baseK = K;
+    float* Af = (float*)malloc((size_t)M * K * sizeof(float));
+    float* Bt = (float*)malloc((size_t)N * K * sizeof(float)); /* [N,K] */
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int k = 0; k < K; ++k) {
+            uint16_t v = transA ? A[(size_t)k * lda + m] : A[(size_t)m * lda + k];
+            Af[(size_t)m * K + k] = is_bf16 ? orc_bf16_to_f32(v) : orc_f16_to_f32(v);
+        }
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int k = 0; k < K; ++k) {
+            uint16_t v = transB ? B[(size_t)n * ldb + k] : B[(size_t)k * ldb + n];
+            Bt[(size_t)n * K + k] = is_bf16 ? orc_bf16_to_f32(v) : orc_f16_to_f32(v);
+        }
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m) {
+        const float* a = Af + (size_t)m * K;
+        for (int n = 0; n < N; ++n) {
+            const float* b = Bt + (size_t)n * K;
+            float acc = bias ? bias[n] : 0.0f;
+            for (int k0 = 0; k0 < K; k0 += baseK) {
+                int k1 = k0 + baseK < K ? k0 + baseK : K;
+                float part = 0.0f;
+                for (int k = k0; k < k1; ++k) part += a[k] * b[k];
+                acc += part;
+            }
+            C[(size_t)m * N + n] = acc;
+        }
+    }
+    free(Af);
+    free(Bt);
+}
+
+/* int8 x int8 -> int32 (+ int32 bias), exact.  Mmad.md:186-237 (s8 in, s32 accumulate). */
+ORC_API void orc_gemm_i8(const int8_t* A, const int8_t* B, const int32_t* bias, int32_t* C, int M, int N, int K,
+                         int lda, int ldb, int transA, int transB)
+{
+    int8_t* Ar = (int8_t*)A;
+    int8_t* Bt = (int8_t*)B;
+    if (transA) {
+        Ar = (int8_t*)malloc((size_t)M * K);
+        for (int m = 0; m < M; ++m)
+            for (int k = 0; k < K; ++k) Ar[(size_t)m * K + k] = A[(size_t)k * lda + m];
+        lda = K;
+    }
+    if (!transB) {
+        Bt = (int8_t*)malloc((size_t)N * K);
+#pragma omp parallel for schedule(static)
+        for (int n = 0; n < N; ++n)
+            for (int k = 0; k < K; ++k) Bt[(size_t)n * K + k] = B[(size_t)k * ldb + n];
+        ldb = K;
+    }
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m) {
+        const int8_t* a = Ar + (size_t)m * lda;
+        for (int n = 0; n < N; ++n) {
+            const int8_t* b = Bt + (size_t)n * ldb;
+            int32_t acc = bias ? bias[n] : 0;
+            for (int k = 0; k < K; ++k) acc += (int32_t)a[k] * (int32_t)b[k];
+            C[(size_t)m * N + n] = acc;
+        }
+    }
+    if (transA) free(Ar);
+    if (!transB) free(Bt);
+}
+
+/* MX matmul, fp4 e2m1 operands, one e8m0 scale per 32 K elements, fp32 accumulate
+ * (MmadMx.md:71-75,160-171).  Both operands K-major: A [M,K/2] bytes, B [N,K/2] bytes, low nibble
+ * = even k (05_best_practices/01_matrix_compute/matmul_mxfp4_high_performance/scripts/gen_data.py:25-36);
+ * sA [M,K/32], sB [N,K/32].  Every product (value x value x 2^e) is exact in fp32; the sum is taken
+ * in double per baseK chunk and rounded to fp32 once per chunk, the chunks added in fp32 - the
+ * reference golden sums in float64 (gen_data.py:51-59). */
+ORC_API void orc_gemm_mxf4(const uint8_t* A, const uint8_t* sA, const uint8_t* B, const uint8_t* sB, const float* bias,
+                           float* C, int M, int N, int K, int baseK)
+{
+    if (baseK <= 0) baseK = K;
+    const int K2 = K / 2, KS = K / 32;
+    float* Af = (float*)malloc((size_t)M * K * sizeof(float));
+    float* Bf = (float*)malloc((size_t)N * K * sizeof(float));
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int k = 0; k < K; ++k) {
+            uint8_t byte = A[(size_t)m * K2 + k / 2];
+            Af[(size_t)m * K + k] = orc_e2m1_to_f32((k & 1) ? (byte >> 4) : (byte & 15)) * orc_e8m0_to_f32(sA[(size_t)m * KS + k / 32]);
+        }
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int k = 0; k < K; ++k) {
+            uint8_t byte = B[(size_t)n * K2 + k / 2];
+            Bf[(size_t)n * K + k] = orc_e2m1_to_f32((k & 1) ? (byte >> 4) : (byte & 15)) * orc_e8m0_to_f32(sB[(size_t)n * KS + k / 32]);
+        }
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m) {
+        const float* a = Af + (size_t)m * K;
+        for (int n = 0; n < N; ++n) {
+            const float* b = Bf + (size_t)n * K;
+            float acc = bias ? bias[n] : 0.0f;
+            for (int k0 = 0; k0 < K; k0 += baseK) {
+                int k1 = k0 + baseK < K ? k0 + baseK : K;
+                double part = 0.0;
+                for (int k = k0; k < k1; ++k) part += (double)a[k] * (double)b[k];
+                acc += (float)part;
+            }
+            C[(size_t)m * N + n] = acc;
+        }
+    }
+    free(Af);
+    free(Bf);
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * Fixpipe epilogues (L0C -> GM).
+ * ------------------------------------------------------------------------------------------- */
+
+/* Plain cast of fp32 accumulators: F322F16 / F322BF16 are RINT
+ * (docs/zh/api/SIMD-API/basic_api/cube_compute_ISASI/fixpipe/accompanying_quantization.md:5). */
+ORC_API void orc_cast_f32(const float* acc, void* out, int dtype, size_t n, int relu)
+{
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; ++i) {
+        float v = acc[i];
+        if (relu && v < 0.0f) v = 0.0f;
+        if (dtype == ORC_F32) ((float*)out)[i] = v;
+        else if (dtype == ORC_F16) ((uint16_t*)out)[i] = f32_to_f16(v, 1);
+        else ((uint16_t*)out)[i] = orc_f32_to_bf16(v);
+    }
+}
+
+static inline float clipf(float v, float lo, float hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+/* REQ8 / VREQ8: int32 -> int8.  gen_data_s322s8.py:69-89:
+ *   f = float(x) * alpha (relu_alpha when x < 0); q = rint(clip(f,-256,255)) + offset9; out = rint(clip(q,-128,127)).
+ * q points at one parameter (per_channel == 0) or N of them.  relu_mode: 0 none (relu_alpha = alpha), 1 relu (0). */
+ORC_API void orc_fixpipe_req8(const int32_t* acc, int8_t* out, int M, int N, const uint64_t* q, int per_channel, int relu)
+{
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            uint64_t p = q[per_channel ? n : 0];
+            float f = (float)acc[(size_t)m * N + n];
+            f = (f >= 0.0f || !relu) ? f * orc_quant_alpha(p) : 0.0f;
+            float t = nearbyintf(clipf(f, -256.0f, 255.0f)) + (float)quant_offset9(p);
+            out[(size_t)m * N + n] = (int8_t)nearbyintf(clipf(t, -128.0f, 127.0f));
+        }
+}
+
+/* QF322B8_PRE / VQF322B8_PRE: fp32 -> int8, same arithmetic on an fp32 accumulator (gen_data_f322s8.py:66-85). */
+ORC_API void orc_fixpipe_qf322b8(const float* acc, int8_t* out, int M, int N, const uint64_t* q, int per_channel, int relu)
+{
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            uint64_t p = q[per_channel ? n : 0];
+            float f = acc[(size_t)m * N + n];
+            f = (f >= 0.0f || !relu) ? f * orc_quant_alpha(p) : 0.0f;
+            float t = nearbyintf(clipf(f, -256.0f, 255.0f)) + (float)quant_offset9(p);
+            out[(size_t)m * N + n] = (f != f) ? 0 : (int8_t)nearbyintf(clipf(t, -128.0f, 127.0f));
+        }
+}
+
+/* DEQF16 / VDEQF16: int32 -> half = half_sat(float(x) * alpha) (gen_data_s322f16.py:66-83). */
+ORC_API void orc_fixpipe_deqf16(const int32_t* acc, uint16_t* out, int M, int N, const uint64_t* q, int per_channel, int relu)
+{
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            uint64_t p = q[per_channel ? n : 0];
+            float f = (float)acc[(size_t)m * N + n];
+            f = (f >= 0.0f || !relu) ? f * orc_quant_alpha(p) : 0.0f;
+            out[(size_t)m * N + n] = f32_to_f16(f, 1);
+        }
+}
+
+/* QS322BF16_PRE / VQS322BF16_PRE (950 only): int32 -> bf16 = bf16_rint(float(x) * alpha)
+ * (impl/adv_api/detail/matmul/stage/copy_cube_out/quant/quant_processor_fixpipe.h:211-235). */
+ORC_API void orc_fixpipe_qs322bf16(const int32_t* acc, uint16_t* out, int M, int N, const uint64_t* q, int per_channel, int relu)
+{
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            uint64_t p = q[per_channel ? n : 0];
+            float f = (float)acc[(size_t)m * N + n];
+            f = (f >= 0.0f || !relu) ? f * orc_quant_alpha(p) : 0.0f;
+            out[(size_t)m * N + n] = orc_f32_to_bf16(f);
+        }
+}
+
+/* Per-channel x per-token dequant that the grouped example applies after the int8 matmul:
+ * AscendDequant (float(acc) * scale[n]) then Mul by perTokenScale[m], then Cast RINT
+ * (examples/01_simd_cpp_api/05_best_practices/03_fusion_compute/quant_group_matmul_high_performance/
+ *  quant_group_matmul_custom.asc:433,439,450).  act: 0 identity, 1 FasterGelu x*e^(.851(x-|x|))/(1+e^(-1.702|x|))
+ *  (scripts/gen_data.py:19-23). */
+ORC_API void orc_dequant_tok_ch(const int32_t* acc, void* out, int dtype, int M, int N, const float* tok, const float* ch, int act)
+{
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            float v = (float)acc[(size_t)m * N + n] * ch[n];
+            if (tok) v = v * tok[m];
+            if (act == 1) {
+                float ax = fabsf(v);
+                v = v * expf(0.851f * (v - ax)) / (1.0f + expf(-1.702f * ax));
+            }
+            size_t i = (size_t)m * N + n;
+            if (dtype == ORC_F32) ((float*)out)[i] = v;
+            else if (dtype == ORC_F16) ((uint16_t*)out)[i] = f32_to_f16(v, 1);
+            else ((uint16_t*)out)[i] = orc_f32_to_bf16(v);
+        }
+}
+
+/* Grouped int8 matmul: rows of x are split into consecutive groups by counts[g] (counts, not a
+ * cumulative sum; groups with count <= 0 are skipped, quant_group_matmul_custom.asc:263-264);
+ * group g multiplies by W[g] ([N,K] when transB else [K,N]) and scale ch[g*N + n]. */
+ORC_API void orc_grouped_i8(const int8_t* x, const int8_t* W, const int64_t* counts, int G, const float* tok, const float* ch,
+                            void* out, int dtype, int K, int N, int transB, int act)
+{
+    int64_t row = 0;
+    for (int g = 0; g < G; ++g) {
+        int64_t mg = counts[g];
+        if (mg <= 0) continue;
+        int32_t* acc = (int32_t*)malloc((size_t)mg * N * sizeof(int32_t));
+        orc_gemm_i8(x + (size_t)row * K, W + (size_t)g * N * K, NULL, acc, (int)mg, N, K, K, transB ? K : N, 0, transB);
+        size_t esz = dtype == ORC_F32 ? 4 : 2;
+        orc_dequant_tok_ch(acc, (char*)out + (size_t)row * N * esz, dtype, (int)mg, N, tok ? tok + row : NULL, ch + (size_t)g * N, act);
+        free(acc);
+        row += mg;
+    }
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * SoftMax: per row x32 = float(x); max; e = exp(x32 - max); sum; y = e / sum; cast RINT
+ * (impl/adv_api/detail/activation/softmax/membase/common/softmax_impl/softmax_generic_nd_impl.h:92-121,
+ *  impl/adv_api/detail/common/common.h:27-28; formula docs SoftMax.md, golden
+ *  examples/01_simd_cpp_api/04_advanced_api/01_activation/softmax/scripts/gen_data.py:23-37).
+ * max/sum are written once per row (brc == 0) or broadcast over one 32-byte block (brc == 1:
+ * 8 floats for fp32 statistics; include/adv_api/activation/softmax.h:92-109).
+ * The reduction order of the vector unit is not documented; we sum k ascending in fp32.
+ * ------------------------------------------------------------------------------------------- */
+ORC_API void orc_softmax(const void* x, void* y, float* max_out, float* sum_out, int M, int K, int dtype, int brc)
+{
+    const int rep = brc ? 8 : 1;
+#pragma omp parallel
+    {
+        float* row = (float*)malloc((size_t)K * sizeof(float));
+#pragma omp for schedule(static)
+        for (int m = 0; m < M; ++m) {
+            float mx = -INFINITY;
+            for (int k = 0; k < K; ++k) {
+                float v = dtype == ORC_F16 ? orc_f16_to_f32(((const uint16_t*)x)[(size_t)m * K + k]) : ((const float*)x)[(size_t)m * K + k];
+                row[k] = v;
+                if (v > mx) mx = v;
+            }
+            float s = 0.0f;
+            for (int k = 0; k < K; ++k) {
+                row[k] = expf(row[k] - mx);
+                s += row[k];
+            }
+            for (int k = 0; k < K; ++k) {
+                float v = row[k] / s;
+                if (dtype == ORC_F16) ((uint16_t*)y)[(size_t)m * K + k] = f32_to_f16(v, 1);
+                else ((float*)y)[(size_t)m * K + k] = v;
+            }
+            for (int r = 0; r < rep; ++r) {
+                max_out[(size_t)m * rep + r] = mx;
+                sum_out[(size_t)m * rep + r] = s;
+            }
+        }
+        free(row);
+    }
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * AscendQuant -> int8.  All arithmetic in fp16: src (and fp32 scale/offset) cast to half RINT with
+ * saturation, Mul in half, Add in half, half -> int8 RINT with saturation
+ * (impl/adv_api/detail/quantization/quant/ascend_quant_3510_impl.h:34-66 per tensor,
+ *  :275-322 per channel half, :335-378 per channel fp32; default round mode CAST_RINT,
+ *  include/adv_api/quantization/ascend_quant_utils.h:64,70).
+ * ------------------------------------------------------------------------------------------- */
+static inline uint16_t half_mul(uint16_t a, uint16_t b) { return f32_to_f16(orc_f16_to_f32(a) * orc_f16_to_f32(b), 0); }
+static inline uint16_t half_add(uint16_t a, uint16_t b) { return f32_to_f16(orc_f16_to_f32(a) + orc_f16_to_f32(b), 0); }
+static inline uint16_t load_as_half(const void* p, size_t i, int dtype)
+{
+    if (dtype == ORC_F16) return ((const uint16_t*)p)[i];
+    if (dtype == ORC_BF16) return f32_to_f16(orc_bf16_to_f32(((const uint16_t*)p)[i]), 1);
+    return f32_to_f16(((const float*)p)[i], 1);
+}
+
+ORC_API void orc_quant_per_tensor(const void* src, int8_t* dst, size_t n, int dtype, float scale, float offset)
+{
+    const uint16_t hs = f32_to_f16(scale, 0), ho = f32_to_f16(offset, 0); /* static_cast<half>(scale) */
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; ++i) {
+        uint16_t v = half_add(half_mul(load_as_half(src, i, dtype), hs), ho);
+        dst[i] = f32_to_s8_rint_sat(orc_f16_to_f32(v));
+    }
+}
+
+/* scale has scale_count entries of the source dtype; offset is a tensor of the same kind
+ * (offset_is_tensor) or one scalar of the source dtype passed in offset_scalar. */
+ORC_API void orc_quant_per_channel(const void* src, int8_t* dst, int rows, int scale_count, int dtype, const void* scale,
+                                   const void* offset_tensor, float offset_scalar)
+{
+    uint16_t hos = dtype == ORC_F32 ? f32_to_f16(offset_scalar, 1)
+                 : dtype == ORC_BF16 ? f32_to_f16(orc_bf16_to_f32(orc_f32_to_bf16(offset_scalar)), 1)
+                                     : f32_to_f16(offset_scalar, 0);
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < scale_count; ++c) {
+            size_t i = (size_t)r * scale_count + c;
+            uint16_t hs = load_as_half(scale, c, dtype);
+            uint16_t ho = offset_tensor ? load_as_half(offset_tensor, c, dtype) : hos;
+            uint16_t v = half_add(half_mul(load_as_half(src, i, dtype), hs), ho);
+            dst[i] = f32_to_s8_rint_sat(orc_f16_to_f32(v));
+        }
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * AscendDequant: dst[i,j] = dstT(float(src[i,j]) * float(scale[j])) for j < cal_count; src rows
+ * have n int32 each; dst rows have n_dst elements (n rounded up to a 32-byte multiple)
+ * (impl/adv_api/detail/quantization/dequant/ascend_dequant_common_impl.h:261-365;
+ *  golden examples/01_simd_cpp_api/04_advanced_api/03_quantization/dequant/scripts/gen_data.py:19-34).
+ * scale_dtype: ORC_F32, ORC_BF16, or -1 for a single fp32 scalar in *scale.
+ * ------------------------------------------------------------------------------------------- */
+ORC_API void orc_dequant(const int32_t* src, void* dst, int m, int n, int cal_count, int n_dst, int dst_dtype, const void* scale,
+                         int scale_dtype)
+{
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < m; ++i)
+        for (int j = 0; j < cal_count; ++j) {
+            float s = scale_dtype == -1 ? ((const float*)scale)[0]
+                    : scale_dtype == ORC_BF16 ? orc_bf16_to_f32(((const uint16_t*)scale)[j])
+                                              : ((const float*)scale)[j];
+            float v = (float)src[(size_t)i * n + j] * s;
+            size_t o = (size_t)i * n_dst + j;
+            if (dst_dtype == ORC_F32) ((float*)dst)[o] = v;
+            else if (dst_dtype == ORC_F16) ((uint16_t*)dst)[o] = f32_to_f16(v, 1);
+            else ((uint16_t*)dst)[o] = orc_f32_to_bf16(v);
+        }
+}
+
+ORC_API int orc_num_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}

@@ -1,0 +1,189 @@
+"""ctypes binding of the CPU oracle (oracle/asc_oracle.c).  Test infrastructure only.
+
+The shared object is built by oracle/build.py (gcc, OpenMP).  Nothing in the product package may
+import this module; it exists for tests, the smoke check and the benchmark's CPU baseline.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+F32, F16, BF16, S8, S32 = 0, 1, 2, 3, 4
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            from build import build_oracle  # noqa: WPS433  (sibling file)
+            build_oracle()
+        _lib = C.CDLL(path)
+        _lib.orc_f16_to_f32.restype = C.c_float
+        _lib.orc_f16_to_f32.argtypes = [C.c_uint16]
+        _lib.orc_f32_to_f16.restype = C.c_uint16
+        _lib.orc_f32_to_f16.argtypes = [C.c_float]
+        _lib.orc_f32_to_f16_sat.restype = C.c_uint16
+        _lib.orc_f32_to_f16_sat.argtypes = [C.c_float]
+        _lib.orc_f32_to_bf16.restype = C.c_uint16
+        _lib.orc_f32_to_bf16.argtypes = [C.c_float]
+        _lib.orc_f32_to_s8.restype = C.c_int8
+        _lib.orc_f32_to_s8.argtypes = [C.c_float]
+        _lib.orc_quant_alpha.restype = C.c_float
+        _lib.orc_quant_alpha.argtypes = [C.c_uint64]
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt=None):
+    if a is None:
+        return None
+    return np.ascontiguousarray(a if dt is None else a.astype(dt, copy=False))
+
+
+_OUT = {F32: np.float32, F16: np.uint16, BF16: np.uint16}
+
+
+def gemm_f16(a, b, bias=None, trans_a=False, trans_b=False, is_bf16=False, base_k=0):
+    """a, b: uint16 bit patterns. a [M,K] ([K,M] if trans_a); b [K,N] ([N,K] if trans_b). Returns fp32 [M,N]."""
+    a, b, bias = _c(a, np.uint16), _c(b, np.uint16), _c(bias, np.float32)
+    M, K = (a.shape[1], a.shape[0]) if trans_a else a.shape
+    N = b.shape[0] if trans_b else b.shape[1]
+    c = np.empty((M, N), np.float32)
+    lib().orc_gemm_f16(_p(a), _p(b), _p(bias), _p(c), M, N, K, a.shape[1], b.shape[1], int(trans_a), int(trans_b),
+                       int(is_bf16), int(base_k))
+    return c
+
+
+def gemm_i8(a, b, bias=None, trans_a=False, trans_b=False):
+    a, b, bias = _c(a, np.int8), _c(b, np.int8), _c(bias, np.int32)
+    M, K = (a.shape[1], a.shape[0]) if trans_a else a.shape
+    N = b.shape[0] if trans_b else b.shape[1]
+    c = np.empty((M, N), np.int32)
+    lib().orc_gemm_i8(_p(a), _p(b), _p(bias), _p(c), M, N, K, a.shape[1], b.shape[1], int(trans_a), int(trans_b))
+    return c
+
+
+def gemm_mxf4(a, sa, b, sb, bias=None, base_k=0):
+    """a [M,K/2], b [N,K/2] packed e2m1 bytes; sa [M,K/32], sb [N,K/32] e8m0 bytes. Returns fp32 [M,N]."""
+    a, sa, b, sb, bias = _c(a, np.uint8), _c(sa, np.uint8), _c(b, np.uint8), _c(sb, np.uint8), _c(bias, np.float32)
+    M, N, K = a.shape[0], b.shape[0], a.shape[1] * 2
+    c = np.empty((M, N), np.float32)
+    lib().orc_gemm_mxf4(_p(a), _p(sa), _p(b), _p(sb), _p(bias), _p(c), M, N, K, int(base_k))
+    return c
+
+
+def cast_f32(acc, dtype, relu=False):
+    acc = _c(acc, np.float32)
+    out = np.empty(acc.shape, _OUT[dtype])
+    lib().orc_cast_f32(_p(acc), _p(out), dtype, C.c_size_t(acc.size), int(relu))
+    return out
+
+
+def _fix(fn, acc, acc_dt, out_dt, q, relu):
+    acc = _c(acc, acc_dt)
+    q = _c(np.atleast_1d(q), np.uint64)
+    M, N = acc.shape
+    out = np.empty((M, N), out_dt)
+    getattr(lib(), fn)(_p(acc), _p(out), M, N, _p(q), int(q.size > 1), int(relu))
+    return out
+
+
+def fixpipe_req8(acc, q, relu=False):
+    return _fix("orc_fixpipe_req8", acc, np.int32, np.int8, q, relu)
+
+
+def fixpipe_qf322b8(acc, q, relu=False):
+    return _fix("orc_fixpipe_qf322b8", acc, np.float32, np.int8, q, relu)
+
+
+def fixpipe_deqf16(acc, q, relu=False):
+    return _fix("orc_fixpipe_deqf16", acc, np.int32, np.uint16, q, relu)
+
+
+def fixpipe_qs322bf16(acc, q, relu=False):
+    return _fix("orc_fixpipe_qs322bf16", acc, np.int32, np.uint16, q, relu)
+
+
+def dequant_tok_ch(acc, tok, ch, dtype=BF16, act=0):
+    acc, tok, ch = _c(acc, np.int32), _c(tok, np.float32), _c(ch, np.float32)
+    M, N = acc.shape
+    out = np.empty((M, N), _OUT[dtype])
+    lib().orc_dequant_tok_ch(_p(acc), _p(out), dtype, M, N, _p(tok), _p(ch), int(act))
+    return out
+
+
+def grouped_i8(x, w, counts, tok, ch, dtype=BF16, trans_b=True, act=0):
+    """x [sumM,K] int8; w [G,N,K] (trans_b) or [G,K,N]; counts int64 [G]; tok [sumM]; ch [G,N]."""
+    x, w, counts, tok, ch = _c(x, np.int8), _c(w, np.int8), _c(counts, np.int64), _c(tok, np.float32), _c(ch, np.float32)
+    G = w.shape[0]
+    K = x.shape[1]
+    N = w.shape[1] if trans_b else w.shape[2]
+    out = np.zeros((x.shape[0], N), _OUT[dtype])
+    lib().orc_grouped_i8(_p(x), _p(w), _p(counts), G, _p(tok), _p(ch), _p(out), dtype, K, N, int(trans_b), int(act))
+    return out
+
+
+def softmax(x, dtype=F16, brc=False):
+    """x: uint16 half bits (dtype F16) or float32 [M,K]. Returns (y, max, sum)."""
+    x = _c(x, np.uint16 if dtype == F16 else np.float32)
+    M, K = x.shape
+    y = np.empty_like(x)
+    rep = 8 if brc else 1
+    mx = np.empty((M, rep), np.float32)
+    sm = np.empty((M, rep), np.float32)
+    lib().orc_softmax(_p(x), _p(y), _p(mx), _p(sm), M, K, dtype, int(brc))
+    return (y, mx, sm) if brc else (y, mx[:, 0], sm[:, 0])
+
+
+def _src(x, dtype):
+    return _c(x, np.float32 if dtype == F32 else np.uint16)
+
+
+def quant_per_tensor(src, dtype, scale, offset):
+    src = _src(src, dtype)
+    dst = np.empty(src.shape, np.int8)
+    lib().orc_quant_per_tensor(_p(src), _p(dst), C.c_size_t(src.size), dtype, C.c_float(scale), C.c_float(offset))
+    return dst
+
+
+def quant_per_channel(src, dtype, scale, offset):
+    """scale: [K] of the source dtype; offset: same-shaped array or a python float."""
+    src, scale = _src(src, dtype), _src(scale, dtype)
+    rows, K = src.shape
+    dst = np.empty(src.shape, np.int8)
+    off_t = None if np.isscalar(offset) else _src(offset, dtype)
+    lib().orc_quant_per_channel(_p(src), _p(dst), rows, K, dtype, _p(scale), _p(off_t),
+                                C.c_float(offset if off_t is None else 0.0))
+    return dst
+
+
+def dequant(src, scale, dst_dtype=F32, scale_dtype=F32, cal_count=None, n_dst=None):
+    src = _c(src, np.int32)
+    m, n = src.shape
+    cal_count = n if cal_count is None else cal_count
+    n_dst = n if n_dst is None else n_dst
+    if np.isscalar(scale):
+        sc, sdt = np.array([scale], np.float32), -1
+    else:
+        sc, sdt = _src(scale, scale_dtype), scale_dtype
+    dst = np.zeros((m, n_dst), _OUT[dst_dtype])
+    lib().orc_dequant(_p(src), _p(dst), m, n, cal_count, n_dst, dst_dtype, _p(sc), sdt)
+    return dst
+
+
+def num_threads():
+    return int(lib().orc_num_threads())
+
+
+def f16_bits_to_f32(bits):
+    return np.asarray(bits, np.uint16).view(np.float16).astype(np.float32)
+
+
+def bf16_bits_to_f32(bits):
+    return (np.asarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)

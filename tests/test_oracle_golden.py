@@ -1,0 +1,134 @@
+"""Pins the CPU oracle against fixtures produced by the reference's own Python generators
+(tests/golden/make_golden.py).  Runs without a GPU."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle as orc
+
+
+def load(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name))
+
+
+def test_casts(golden_dir):
+    g = load(golden_dir, "casts.npz")
+    L = orc.lib()
+    assert [L.orc_f32_to_f16_sat(float(v)) for v in g["f32_to_f16_in"]] == g["f32_to_f16_out"].tolist()
+    assert [L.orc_f32_to_s8(float(v)) for v in g["f32_to_s8_in"]] == g["f32_to_s8_out"].tolist()
+    assert [L.orc_f32_to_bf16(float(v)) for v in g["f32_to_bf16_in"]] == g["f32_to_bf16_out"].tolist()
+
+
+def test_f16_roundtrip_all_bit_patterns():
+    L = orc.lib()
+    bits = np.arange(0, 0x10000, dtype=np.uint32).astype(np.uint16)
+    ref = bits.view(np.float16).astype(np.float32)
+    for b in list(range(0, 0x10000, 97)) + [0x0001, 0x03FF, 0x0400, 0x7BFF, 0x7C00, 0xFC00, 0x8000]:
+        v = L.orc_f16_to_f32(b)
+        assert np.float32(v).tobytes() == ref[b].tobytes() or (np.isnan(v) and np.isnan(ref[b]))
+        if not np.isnan(ref[b]):
+            assert L.orc_f32_to_f16(float(ref[b])) == b
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(4000).astype(np.float32) * s for s in (1e-7, 1e-4, 1.0, 300.0, 7e4)])
+    got = np.array([L.orc_f32_to_f16(float(v)) for v in x], np.uint16)
+    with np.errstate(over="ignore"):
+        assert (got == x.astype(np.float16).view(np.uint16)).all()
+
+
+@pytest.mark.parametrize("relu", [0, 1])
+def test_fixpipe_req8_and_qf322b8_match_reference_scripts(golden_dir, relu):
+    g = load(golden_dir, "fixpipe.npz")
+    assert (orc.fixpipe_req8(g["acc_i"], g["q"], relu) == g[f"req8_relu{relu}"]).all()
+    assert (orc.fixpipe_qf322b8(g["acc_f"], g["q"], relu) == g[f"qf322b8_relu{relu}"]).all()
+    # scalar (per-tensor) parameter = every channel carrying the same value
+    q0 = g["q"][5]
+    ref = orc.fixpipe_req8(g["acc_i"], np.full(g["q"].shape, q0, np.uint64), relu)
+    assert (orc.fixpipe_req8(g["acc_i"], q0, relu) == ref).all()
+
+
+def test_fixpipe_deqf16_matches_reference_script(golden_dir):
+    g = load(golden_dir, "fixpipe.npz")
+    assert (orc.fixpipe_deqf16(g["acc_d"], g["qd"]) == g["deqf16"].view(np.uint16)).all()
+
+
+def test_matmul_fp16_recipe(golden_dir):
+    g = load(golden_dir, "matmul_fp16.npz")
+    c = orc.gemm_f16(g["a"].view(np.uint16), g["b"].view(np.uint16), g["bias"])
+    # the reference's own acceptance rule: rtol = atol = 1e-3 (matmul/scripts/verify_result.py:19-47)
+    assert np.isclose(c, g["golden"], rtol=1e-3, atol=1e-3).all()
+    # K chunking (baseK) only reorders fp32 additions
+    c64 = orc.gemm_f16(g["a"].view(np.uint16), g["b"].view(np.uint16), g["bias"], base_k=64)
+    assert np.isclose(c64, g["golden"], rtol=1e-3, atol=1e-3).all()
+    # transposed operand layouts give the same numbers
+    ct = orc.gemm_f16(np.ascontiguousarray(g["a"].T).view(np.uint16), np.ascontiguousarray(g["b"].T).view(np.uint16),
+                      g["bias"], trans_a=True, trans_b=True)
+    assert (ct == c).all()
+
+
+def test_matmul_quant_recipe(golden_dir):
+    g = load(golden_dir, "matmul_quant.npz")
+    acc = orc.gemm_i8(g["a"], g["b"], g["bias"])
+    assert (acc == g["a"].astype(np.int32) @ g["b"].astype(np.int32) + g["bias"]).all()
+    out = orc.fixpipe_deqf16(acc, g["q"]).view(np.float16).astype(np.float32)
+    # the example golden multiplies in fp16 after casting the int32 sum to fp16 (matmul_quant/scripts/gen_data.py:27-44),
+    # fixpipe multiplies in fp32 and rounds once: equal within half precision
+    assert np.isclose(out, g["golden"].astype(np.float32), rtol=2e-3, atol=1e-3).all()
+
+
+def test_softmax_recipe(golden_dir):
+    g = load(golden_dir, "softmax.npz")
+    y, mx, sm = orc.softmax(g["x16"].view(np.uint16), orc.F16)
+    yf = y.view(np.float16).astype(np.float32)
+    assert np.allclose(yf, g["y16"], rtol=1e-3, atol=1e-7)
+    assert (mx == g["max16"][:, 0]).all()
+    assert np.allclose(sm, g["sum16"][:, 0], rtol=1e-5)
+    y32, mx32, sm32 = orc.softmax(g["x32"], orc.F32, brc=True)
+    assert mx32.shape == (32, 8) and (mx32 == mx32[:, :1]).all()
+    assert np.allclose(y32, g["y32"], rtol=1e-5, atol=1e-9)
+    assert (mx32[:, 0] == g["max32"][:, 0]).all()
+
+
+def test_quant_recipe(golden_dir):
+    g = load(golden_dir, "quant.npz")
+    # dav-2201 variant: half source; round(src*2+0.9) evaluated by numpy in half precision
+    q16 = orc.quant_per_tensor(g["src_f16"].astype(np.float16).view(np.uint16), orc.F16, 2.0, 0.9)
+    assert (q16 == g["golden_f16"]).all()
+    # dav-3510 variant: fp32 source, numpy golden computed in fp32 while the operator rounds the
+    # source, scale and offset to half first (ascend_quant_3510_impl.h:83-100): differ by at most 1 step
+    q32 = orc.quant_per_tensor(g["src_f32"], orc.F32, 2.0, 0.9)
+    d = np.abs(q32.astype(np.int32) - g["golden_f32"].astype(np.int32))
+    assert d.max() <= 1 and (d != 0).mean() < 0.02
+    # per-channel with a constant scale tensor reproduces per-tensor
+    src = g["src_f16"].astype(np.float16).reshape(32, 32)
+    qc = orc.quant_per_channel(src.view(np.uint16), orc.F16, np.full(32, 2.0, np.float16).view(np.uint16), 0.9)
+    assert (qc.reshape(-1) == q16).all()
+
+
+def test_dequant_recipe(golden_dir):
+    g = load(golden_dir, "dequant.npz")
+    out = orc.dequant(g["src"], g["scale"])
+    assert (out == g["golden"]).all()
+
+
+def test_grouped_recipe(golden_dir):
+    g = load(golden_dir, "grouped.npz")
+    w_t = np.ascontiguousarray(g["w"].transpose(0, 2, 1))
+    for trans_b, w in ((True, w_t), (False, g["w"])):
+        lin = orc.grouped_i8(g["x"], w, g["counts"], g["tok"], g["scale"], orc.F32, trans_b=trans_b)
+        # reference golden multiplies scale*tok first, then the product (gen_data.py:52); the kernel
+        # order is (acc*scale)*tok (quant_group_matmul_custom.asc:433,439): equal to fp32 rounding
+        assert np.allclose(lin, g["golden_linear"], rtol=1e-6, atol=1e-9)
+    gelu = orc.grouped_i8(g["x"], w_t, g["counts"], g["tok"], g["scale"], orc.F16, act=1).view(np.float16)
+    ok = np.isclose(gelu.astype(np.float32), g["golden_gelu"].astype(np.float32), rtol=1e-3, atol=1e-3)
+    assert (~ok).mean() <= 1e-4  # quant_group_matmul_high_performance/scripts/verify_result.py:19-41
+
+
+def test_mxfp4_recipe(golden_dir):
+    g = load(golden_dir, "mxfp4.npz")
+    c = orc.gemm_mxf4(g["a"], g["sa"], g["b"], g["sb"])
+    assert np.allclose(c, g["golden_f64"], rtol=1e-6, atol=1e-6)
+    bf = orc.cast_f32(c, orc.BF16)
+    assert (bf != g["golden_bf16_bits"]).mean() < 1e-3  # float64 golden rounded straight to bf16
+    c64 = orc.gemm_mxf4(g["a"], g["sa"], g["b"], g["sb"], base_k=64)
+    assert np.abs(c64 - c).max() <= 1e-6 * np.abs(c).max()  # chunking only reorders fp32 additions
