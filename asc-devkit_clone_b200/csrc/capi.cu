@@ -1,0 +1,191 @@
+// Library state, error reporting and the memory / stream shims of the C ABI.
+#include <mutex>
+
+#include "common.cuh"
+
+namespace ascb200 {
+
+static DeviceState g_states[16];
+static std::mutex g_mu;
+static thread_local int t_last_cuda = 0;
+
+int cuda_fail(cudaError_t e)
+{
+    t_last_cuda = static_cast<int>(e);
+    (void)cudaGetLastError();
+    return ASCB200_ECUDA;
+}
+
+DeviceState* current_state()
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+    DeviceState* st = &g_states[dev];
+    return st->ready ? st : nullptr;
+}
+
+int ensure_scratch(DeviceState* st, size_t bytes, cudaStream_t stream)
+{
+    if (bytes <= st->scratch_bytes) return ASCB200_OK;
+    // Work queued on other streams may still read the old block: wait for the device first.
+    ASCB200_CUDA(cudaDeviceSynchronize());
+    (void)stream;
+    if (st->scratch_dev) ASCB200_CUDA(cudaFree(st->scratch_dev));
+    st->scratch_dev = nullptr;
+    st->scratch_bytes = 0;
+    size_t want = bytes + (bytes >> 2);
+    ASCB200_CUDA(cudaMalloc(&st->scratch_dev, want));
+    st->scratch_bytes = want;
+    return ASCB200_OK;
+}
+
+}  // namespace ascb200
+
+using namespace ascb200;
+
+extern "C" {
+
+int ascb200_init(int device)
+{
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+        (void)cudaGetLastError();
+        return ASCB200_ENODEV;
+    }
+    if (device < 0 || device >= count || device >= 16) return ASCB200_EINVAL;
+    ASCB200_CUDA(cudaSetDevice(device));
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceState* st = &g_states[device];
+    if (st->ready) return ASCB200_OK;
+    cudaDeviceProp prop;
+    ASCB200_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return ASCB200_ENODEV;
+    st->device = device;
+    st->sm_count = prop.multiProcessorCount;
+    ASCB200_CUDA(cudaMalloc(&st->status_dev, 256));
+    ASCB200_CUDA(cudaMemset(st->status_dev, 0, 256));
+    st->ready = true;
+    return ASCB200_OK;
+}
+
+const char* ascb200_strerror(int code)
+{
+    switch (code) {
+        case ASCB200_OK: return "ok";
+        case ASCB200_EINVAL: return "invalid argument";
+        case ASCB200_EALIGN: return "pointer or leading dimension not aligned as required";
+        case ASCB200_EUNSUPPORTED: return "combination not supported";
+        case ASCB200_ENODEV: return "no initialised sm_100 CUDA device (call ascb200_init)";
+        case ASCB200_ECUDA: return "CUDA call failed";
+        case ASCB200_ETIMEOUT: return "device-side wait expired";
+        case ASCB200_ETOOBIG: return "extent beyond supported limit";
+        default: return "unknown error";
+    }
+}
+
+int ascb200_last_cuda_error(void) { return t_last_cuda; }
+
+int ascb200_sm_count(void)
+{
+    DeviceState* st = current_state();
+    return st ? st->sm_count : ASCB200_ENODEV;
+}
+
+int ascb200_device_status(void* stream, uint32_t* status_host)
+{
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    uint32_t v = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    ASCB200_CUDA(cudaMemcpyAsync(&v, st->status_dev, sizeof(v), cudaMemcpyDeviceToHost, s));
+    ASCB200_CUDA(cudaStreamSynchronize(s));
+    if (status_host) *status_host = v;
+    if (v != 0) {
+        ASCB200_CUDA(cudaMemsetAsync(st->status_dev, 0, sizeof(v), s));
+        return ASCB200_ETIMEOUT;
+    }
+    return ASCB200_OK;
+}
+
+int ascb200_malloc(void** p, size_t bytes)
+{
+    if (!p) return ASCB200_EINVAL;
+    ASCB200_CUDA(cudaMalloc(p, bytes ? bytes : 1));
+    return ASCB200_OK;
+}
+int ascb200_free(void* p)
+{
+    ASCB200_CUDA(cudaFree(p));
+    return ASCB200_OK;
+}
+int ascb200_malloc_host(void** p, size_t bytes)
+{
+    if (!p) return ASCB200_EINVAL;
+    ASCB200_CUDA(cudaMallocHost(p, bytes ? bytes : 1));
+    return ASCB200_OK;
+}
+int ascb200_free_host(void* p)
+{
+    ASCB200_CUDA(cudaFreeHost(p));
+    return ASCB200_OK;
+}
+int ascb200_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream)
+{
+    ASCB200_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+    return ASCB200_OK;
+}
+int ascb200_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream)
+{
+    ASCB200_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+    return ASCB200_OK;
+}
+int ascb200_memset(void* dst, int value, size_t bytes, void* stream)
+{
+    ASCB200_CUDA(cudaMemsetAsync(dst, value, bytes, static_cast<cudaStream_t>(stream)));
+    return ASCB200_OK;
+}
+int ascb200_stream_create(void** stream)
+{
+    if (!stream) return ASCB200_EINVAL;
+    cudaStream_t s;
+    ASCB200_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *stream = s;
+    return ASCB200_OK;
+}
+int ascb200_stream_destroy(void* stream)
+{
+    ASCB200_CUDA(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
+    return ASCB200_OK;
+}
+int ascb200_stream_sync(void* stream)
+{
+    ASCB200_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    return ASCB200_OK;
+}
+int ascb200_event_create(void** event)
+{
+    if (!event) return ASCB200_EINVAL;
+    cudaEvent_t e;
+    ASCB200_CUDA(cudaEventCreate(&e));
+    *event = e;
+    return ASCB200_OK;
+}
+int ascb200_event_destroy(void* event)
+{
+    ASCB200_CUDA(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+    return ASCB200_OK;
+}
+int ascb200_event_record(void* event, void* stream)
+{
+    ASCB200_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)));
+    return ASCB200_OK;
+}
+int ascb200_event_elapsed_ms(void* start, void* stop, float* ms)
+{
+    if (!ms) return ASCB200_EINVAL;
+    ASCB200_CUDA(cudaEventSynchronize(static_cast<cudaEvent_t>(stop)));
+    ASCB200_CUDA(cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(stop)));
+    return ASCB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,58 @@
+// Shared host/device helpers of the ascb200 library (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ascb200.h"
+
+namespace ascb200 {
+
+// Per-device state created by ascb200_init.
+struct DeviceState {
+    bool ready = false;
+    int device = -1;
+    int sm_count = 0;
+    uint32_t* status_dev = nullptr;  // bit 0: bounded wait expired inside a GEMM kernel
+    void* scratch_dev = nullptr;     // grows on demand (scale re-tiling, padded operands)
+    size_t scratch_bytes = 0;
+};
+
+DeviceState* current_state();           // nullptr (and ASCB200_ENODEV recorded) when init has not run
+int ensure_scratch(DeviceState* st, size_t bytes, cudaStream_t stream);
+int cuda_fail(cudaError_t e);           // records e, returns ASCB200_ECUDA
+#define ASCB200_CUDA(call)                                   \
+    do {                                                     \
+        cudaError_t e__ = (call);                            \
+        if (e__ != cudaSuccess) return ::ascb200::cuda_fail(e__); \
+    } while (0)
+
+static inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+#ifdef __CUDACC__
+// ---- numeric conversions: one definition per rounding rule of the reference -----------------
+// fp32 -> fp16, round to nearest even, overflow saturates to +-65504 (CAST_RINT with saturation).
+__device__ __forceinline__ __half f32_to_f16_sat(float f)
+{
+    unsigned short b = __half_as_ushort(__float2half_rn(f));
+    if ((b & 0x7FFFu) == 0x7C00u) b = (b & 0x8000u) | 0x7BFFu;  // +-inf -> +-65504, NaN untouched
+    return __ushort_as_half(b);
+}
+__device__ __forceinline__ __nv_bfloat16 f32_to_bf16(float f) { return __float2bfloat16_rn(f); }
+// fp32 -> int8, round to nearest even, saturating; NaN -> 0.
+__device__ __forceinline__ int f32_to_s8(float f)
+{
+    int i = __float2int_rn(f);  // saturates to int32, NaN -> 0
+    return max(-128, min(127, i));
+}
+// The (1,8,10) scale in bits [31:13] of a fixpipe quant parameter.
+__device__ __forceinline__ float quant_alpha(uint64_t q) { return __uint_as_float(static_cast<uint32_t>(q) & 0xFFFFE000u); }
+__device__ __forceinline__ float quant_offset(uint64_t q)
+{
+    int o = static_cast<int>((q >> 37) & 0x1FFu);
+    return static_cast<float>((o & 0x100) ? o - 512 : o);
+}
+#endif
+
+}  // namespace ascb200

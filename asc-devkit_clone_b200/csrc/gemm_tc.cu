@@ -1,0 +1,730 @@
+// Tensor-core GEMM for sm_100a: the contraction behind Matmul::IterateAll and the grouped quantized
+// matmul.  One persistent, warp-specialised kernel template:
+//
+//   warp 0    TMA producer: global -> shared memory tiles (128-byte swizzle), NUM_STAGES deep ring
+//   warp 1    MMA issuer: one thread issues tcgen05.mma (kind::f16 / kind::i8 / kind::mxf4.block_scale),
+//             accumulators live in TMEM
+//   warp 2    TMEM allocation / release
+//   warps 4-7 epilogue: tcgen05.ld TMEM -> registers, fused fixpipe stage (bias, cast, dequant,
+//             requant, per-token x per-channel scaling), vector stores to global memory
+//
+// A CTA computes 128 x BLOCK_N output tiles; with two accumulator stages in TMEM the epilogue of
+// tile i overlaps the main loop of tile i+1.  Tiles are visited M-fastest so that concurrently
+// running CTAs share B columns in L2.  No load uses cluster multicast.
+#include <algorithm>
+#include <mutex>
+
+#include "tc_common.cuh"
+
+namespace ascb200 {
+namespace {
+
+using namespace tc;
+
+constexpr int BLOCK_M = 128;
+constexpr int ROW_BYTES = 128;          // one swizzle row: 64 x 16-bit, 128 x 8-bit, 256 x 4-bit along the contiguous axis
+constexpr int A_TILE_BYTES = BLOCK_M * ROW_BYTES;
+constexpr int NUM_THREADS = 256;
+constexpr int MAX_GROUPS = 1024;
+constexpr int SF_CHUNK_BYTES = 512;     // scale factors of 128 rows x 4 K-blocks (of 32 elements)
+
+enum : int { OUT_F32 = ASCB200_F32, OUT_F16 = ASCB200_F16, OUT_BF16 = ASCB200_BF16, OUT_S8 = ASCB200_S8, OUT_S32 = ASCB200_S32 };
+
+struct EpiParams {
+    void* c;
+    void* c2;
+    long long ldc, ldc2;
+    int c_dtype, c2_dtype;
+    int mode;
+    int relu, act;
+    int vec_c, vec_c2;       // rows of c / c2 are 16-byte aligned at every 32-column boundary
+    const void* bias;        // float (fp32 accumulators) or int32 (int32 accumulators)
+    const float* tok;
+    const float* ch;
+    const unsigned long long* quant;
+    unsigned long long quant_scalar;
+};
+
+struct GemmParams {
+    int m, n, k;
+    int num_k_blocks;
+    int a_mn, b_mn;          // operand is MN-major (contiguous along M / N) instead of K-major
+    int groups;              // > 0: grouped mode
+    const long long* group_counts;
+    const uint8_t* sfa;      // MXFP4: re-tiled scale factors (see retile_scales_kernel)
+    const uint8_t* sfb;
+    int sf_kc;               // 512-byte chunks per 128-row block in sfa / sfb
+    uint32_t idesc;
+    uint32_t* status;
+    EpiParams epi;
+};
+
+template <int KIND, int BLOCK_N>
+struct Cfg {
+    static constexpr int B_TILE_BYTES = BLOCK_N * ROW_BYTES;
+    static constexpr int SF_BYTES = KIND == KIND_MXF4 ? (2 + 2 * (BLOCK_N / 128)) * SF_CHUNK_BYTES : 0;
+    static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + SF_BYTES;
+    static constexpr int NUM_STAGES = std::min(8, (220 * 1024) / STAGE_BYTES);
+    static constexpr int ACC_STAGES = (KIND == KIND_MXF4 && BLOCK_N == 256) ? 1 : 2;
+    static constexpr int ACC_COLS = ACC_STAGES * BLOCK_N;
+    static constexpr int SF_COLS_PER_STAGE = 32;  // 8 for A + up to 16 for B, padded
+    static constexpr int SF_COL0 = ACC_COLS;
+    static constexpr int TMEM_NEED = ACC_COLS + (KIND == KIND_MXF4 ? NUM_STAGES * SF_COLS_PER_STAGE : 0);
+    static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
+    static_assert(TMEM_NEED <= 512, "TMEM budget");
+    // bytes of one K step of the instruction (32 in every kind) -> elements along K per tile row
+    static constexpr int BLOCK_K = KIND == KIND_F16 ? 64 : KIND == KIND_I8 ? 128 : 256;
+    static constexpr int UMMA_K = BLOCK_K / 4;
+    static constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ +
+                                      2 * (MAX_GROUPS + 1) * static_cast<int>(sizeof(int));
+};
+
+struct TileInfo {
+    int row0, row_end, n0, group;
+};
+
+// Grouped mode: prefix sums of rows and of tiles per group, built once per CTA by warp 0.
+__device__ void build_group_tables(const long long* counts, int groups, int num_n, int* row_start, int* tile_start)
+{
+    const int lane = threadIdx.x & 31;
+    int rows_carry = 0, tiles_carry = 0;
+    for (int base = 0; base < groups; base += 32) {
+        const int g = base + lane;
+        long long c = g < groups ? counts[g] : 0;
+        int rows = c > 0 ? static_cast<int>(c) : 0;
+        int tiles = ((rows + BLOCK_M - 1) / BLOCK_M) * num_n;
+        int rs = rows, ts = tiles;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int r2 = __shfl_up_sync(0xFFFFFFFFu, rs, o);
+            int t2 = __shfl_up_sync(0xFFFFFFFFu, ts, o);
+            if (lane >= o) {
+                rs += r2;
+                ts += t2;
+            }
+        }
+        if (g < groups) {
+            row_start[g + 1] = rows_carry + rs;
+            tile_start[g + 1] = tiles_carry + ts;
+        }
+        rows_carry += __shfl_sync(0xFFFFFFFFu, rs, 31);
+        tiles_carry += __shfl_sync(0xFFFFFFFFu, ts, 31);
+    }
+    if (lane == 0) {
+        row_start[0] = 0;
+        tile_start[0] = 0;
+    }
+}
+
+template <int BLOCK_N>
+__device__ __forceinline__ bool locate_tile(const GemmParams& p, int tile, int num_m, int total_tiles, const int* row_start,
+                                            const int* tile_start, int& cursor, TileInfo& t)
+{
+    if (tile >= total_tiles) return false;
+    if (p.groups > 0) {
+        while (tile >= tile_start[cursor + 1]) ++cursor;
+        const int local = tile - tile_start[cursor];
+        const int rows = row_start[cursor + 1] - row_start[cursor];
+        const int m_tiles = (rows + BLOCK_M - 1) / BLOCK_M;
+        t.group = cursor;
+        t.row0 = row_start[cursor] + (local % m_tiles) * BLOCK_M;
+        t.row_end = row_start[cursor + 1];
+        t.n0 = (local / m_tiles) * BLOCK_N;
+    } else {
+        t.group = 0;
+        t.row0 = (tile % num_m) * BLOCK_M;
+        t.row_end = p.m;
+        t.n0 = (tile / num_m) * BLOCK_N;
+    }
+    return true;
+}
+
+// ---- epilogue helpers -------------------------------------------------------------------------
+__device__ __forceinline__ float faster_gelu(float x)
+{
+    const float ax = fabsf(x);
+    return x * __expf(0.851f * (x - ax)) / (1.0f + __expf(-1.702f * ax));
+}
+
+template <typename T4>
+__device__ __forceinline__ void st_v4(void* p, T4 v) { *reinterpret_cast<T4*>(p) = v; }
+
+// Stores 32 consecutive outputs of one row.  f: values for F32/F16/BF16; qi: values for S8/S32.
+__device__ __forceinline__ void store32(void* base, long long ld, int dtype, int vec, int row, int col0, int ncols, const float* f,
+                                        const int* qi)
+{
+    const size_t off = static_cast<size_t>(row) * static_cast<size_t>(ld) + col0;
+    if (dtype == OUT_F32 || dtype == OUT_S32) {
+        uint32_t* out = static_cast<uint32_t*>(base) + off;
+        if (vec && ncols == 32) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint4 v;
+                if (dtype == OUT_F32) v = make_uint4(__float_as_uint(f[4 * j]), __float_as_uint(f[4 * j + 1]), __float_as_uint(f[4 * j + 2]), __float_as_uint(f[4 * j + 3]));
+                else v = make_uint4(qi[4 * j], qi[4 * j + 1], qi[4 * j + 2], qi[4 * j + 3]);
+                st_v4(out + 4 * j, v);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncols) out[j] = dtype == OUT_F32 ? __float_as_uint(f[j]) : static_cast<uint32_t>(qi[j]);
+        }
+    } else if (dtype == OUT_F16 || dtype == OUT_BF16) {
+        uint16_t h[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            h[j] = dtype == OUT_F16 ? __half_as_ushort(f32_to_f16_sat(f[j])) : __bfloat16_as_ushort(f32_to_bf16(f[j]));
+        uint16_t* out = static_cast<uint16_t*>(base) + off;
+        if (vec && ncols == 32) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                v.x = h[8 * j] | (static_cast<uint32_t>(h[8 * j + 1]) << 16);
+                v.y = h[8 * j + 2] | (static_cast<uint32_t>(h[8 * j + 3]) << 16);
+                v.z = h[8 * j + 4] | (static_cast<uint32_t>(h[8 * j + 5]) << 16);
+                v.w = h[8 * j + 6] | (static_cast<uint32_t>(h[8 * j + 7]) << 16);
+                st_v4(out + 8 * j, v);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncols) out[j] = h[j];
+        }
+    } else {  // OUT_S8
+        int8_t* out = static_cast<int8_t*>(base) + off;
+        if (vec && ncols == 32) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    w[q] = (qi[16 * j + 4 * q] & 0xFF) | ((qi[16 * j + 4 * q + 1] & 0xFF) << 8) | ((qi[16 * j + 4 * q + 2] & 0xFF) << 16) |
+                           (static_cast<uint32_t>(qi[16 * j + 4 * q + 3] & 0xFF) << 24);
+                st_v4(out + 16 * j, make_uint4(w[0], w[1], w[2], w[3]));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncols) out[j] = static_cast<int8_t>(qi[j]);
+        }
+    }
+}
+
+// Applies the fixpipe stage to 32 accumulators r[] of output row `row`, columns col0 .. col0+ncols.
+// chan0: index of column col0 in the per-channel arrays (bias, ch scale, quant parameters).
+template <bool ACC_INT>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const EpiParams& e, int row, int col0, int ncols, size_t chan0,
+                                               size_t ch_off, float tok)
+{
+    float f[32];
+    int qi[32];
+    if constexpr (ACC_INT) {
+        const int* bias = static_cast<const int*>(e.bias);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            int a = static_cast<int>(r[j]);
+            if (bias && j < ncols) a += bias[chan0 + j];
+            qi[j] = a;
+            f[j] = static_cast<float>(a);
+        }
+    } else {
+        const float* bias = static_cast<const float*>(e.bias);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            float a = __uint_as_float(r[j]);
+            if (bias && j < ncols) a = __fadd_rn(a, bias[chan0 + j]);
+            f[j] = a;
+        }
+        if (e.c2) store32(e.c2, e.ldc2, e.c2_dtype, e.vec_c2, row, col0, ncols, f, qi);
+    }
+    if (e.mode == ASCB200_EPI_CAST) {
+        if (e.relu) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                f[j] = fmaxf(f[j], 0.0f);
+                qi[j] = max(qi[j], 0);
+            }
+        }
+    } else if (e.mode == ASCB200_EPI_FIXPIPE_QUANT) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const unsigned long long q = (e.quant && j < ncols) ? e.quant[chan0 + j] : e.quant_scalar;
+            float v = (f[j] >= 0.0f || !e.relu) ? __fmul_rn(f[j], quant_alpha(q)) : 0.0f;
+            if (e.c_dtype == OUT_S8) {
+                // REQ8 / QF322B8_PRE: clip to 9 bits, round, add the offset, clip to int8
+                float t = rintf(fminf(fmaxf(v, -256.0f), 255.0f)) + quant_offset(q);
+                qi[j] = (v != v) ? 0 : static_cast<int>(rintf(fminf(fmaxf(t, -128.0f), 127.0f)));
+            }
+            f[j] = v;
+        }
+    } else {  // ASCB200_EPI_DEQUANT_TOKEN_CHANNEL
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float s = j < ncols ? e.ch[ch_off + j] : 0.0f;
+            float v = __fmul_rn(__fmul_rn(f[j], s), tok);
+            if (e.act == 1) v = faster_gelu(v);
+            f[j] = v;
+        }
+    }
+    store32(e.c, e.ldc, e.c_dtype, e.vec_c, row, col0, ncols, f, qi);
+}
+
+// ---- the kernel --------------------------------------------------------------------------------
+template <int KIND, int BLOCK_N>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p)
+{
+    using C = Cfg<KIND, BLOCK_N>;
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzled tiles need 1024-byte aligned bases
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* tiles = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::NUM_STAGES * C::STAGE_BYTES);
+    uint64_t* full_bar = bars;                         // [NUM_STAGES]
+    uint64_t* empty_bar = bars + C::NUM_STAGES;        // [NUM_STAGES]
+    uint64_t* acc_full_bar = bars + 2 * C::NUM_STAGES; // [2]
+    uint64_t* acc_empty_bar = acc_full_bar + 2;        // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+    volatile uint32_t* abort_word = tmem_slot + 1;
+    int* row_start = reinterpret_cast<int*>(smem + C::NUM_STAGES * C::STAGE_BYTES + 256);
+    int* tile_start = row_start + (MAX_GROUPS + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_n = (p.n + BLOCK_N - 1) / BLOCK_N;
+    const int num_m = (p.m + BLOCK_M - 1) / BLOCK_M;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::NUM_STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&acc_full_bar[s]), 1);
+            mbar_init(smem_u32(&acc_empty_bar[s]), 4);
+        }
+        *abort_word = 0u;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 0 && p.groups > 0) build_group_tables(p.group_counts, p.groups, num_n, row_start, tile_start);
+    if (warp == 2) {
+        tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = p.groups > 0 ? tile_start[p.groups] : num_m * num_n;
+
+    if (warp == 0) {
+        // ===== TMA producer =====
+        int stage = 0, cursor = 0;
+        uint32_t phase = 0;
+        TileInfo t;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && locate_tile<BLOCK_N>(p, tile, num_m, total_tiles, row_start, tile_start, cursor, t); tile += gridDim.x) {
+            for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_word, p.status);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t bar = smem_u32(&full_bar[stage]);
+                    const uint32_t sa = smem_u32(tiles + stage * C::STAGE_BYTES);
+                    const uint32_t sb = sa + A_TILE_BYTES;
+                    mbar_expect_tx(bar, C::STAGE_BYTES);
+                    const int k0 = kb * C::BLOCK_K;
+                    // x coordinates are counted in tensor-map elements (bytes for int8 and packed fp4)
+                    const int kx = KIND == KIND_MXF4 ? k0 / 2 : k0;
+                    if (!p.a_mn) {
+                        tma_load_2d(sa, &tmap_a, kx, t.row0, bar);
+                    } else {
+                        constexpr int MN_PER_BOX = KIND == KIND_F16 ? 64 : 128;
+                        constexpr int BOX_BYTES = C::BLOCK_K * ROW_BYTES;
+#pragma unroll
+                        for (int j = 0; j < BLOCK_M / MN_PER_BOX; ++j) tma_load_2d(sa + j * BOX_BYTES, &tmap_a, t.row0 + j * MN_PER_BOX, k0, bar);
+                    }
+                    if (!p.b_mn) {
+                        tma_load_3d(sb, &tmap_b, kx, t.n0, t.group, bar);
+                    } else {
+                        constexpr int MN_PER_BOX = KIND == KIND_F16 ? 64 : 128;
+                        constexpr int BOX_BYTES = C::BLOCK_K * ROW_BYTES;
+#pragma unroll
+                        for (int j = 0; j < BLOCK_N / MN_PER_BOX; ++j) tma_load_3d(sb + j * BOX_BYTES, &tmap_b, t.n0 + j * MN_PER_BOX, k0, t.group, bar);
+                    }
+                    if constexpr (KIND == KIND_MXF4) {
+                        const uint32_t ssf = sb + C::B_TILE_BYTES;
+                        const size_t kc = static_cast<size_t>(kb) * 2;
+                        bulk_load(ssf, p.sfa + (static_cast<size_t>(t.row0 / 128) * p.sf_kc + kc) * SF_CHUNK_BYTES, 2 * SF_CHUNK_BYTES, bar);
+#pragma unroll
+                        for (int rb = 0; rb < BLOCK_N / 128; ++rb)
+                            bulk_load(ssf + (1 + rb) * 2 * SF_CHUNK_BYTES,
+                                      p.sfb + (static_cast<size_t>(t.n0 / 128 + rb) * p.sf_kc + kc) * SF_CHUNK_BYTES, 2 * SF_CHUNK_BYTES, bar);
+                    }
+                }
+                __syncwarp();
+                if (++stage == C::NUM_STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer =====
+        int stage = 0, cursor = 0, acc_iter = 0;
+        uint32_t phase = 0;
+        TileInfo t;
+        bool ok = true;
+        // K-major: rows of 128 bytes, 8-row groups 1024 bytes apart.  MN-major: one TMA box per
+        // 128 bytes of M/N, BLOCK_K k-rows of 128 bytes each, boxes BLOCK_K*128 bytes apart.
+        const uint64_t a_hi = p.a_mn ? smem_desc_sw128(C::BLOCK_K * ROW_BYTES, 1024) : smem_desc_sw128(16, 1024);
+        const uint64_t b_hi = p.b_mn ? smem_desc_sw128(C::BLOCK_K * ROW_BYTES, 1024) : smem_desc_sw128(16, 1024);
+        const uint32_t a_kstep = p.a_mn ? C::UMMA_K * ROW_BYTES : 32;
+        const uint32_t b_kstep = p.b_mn ? C::UMMA_K * ROW_BYTES : 32;
+        constexpr uint64_t sf_hi = smem_desc_noswizzle(16, 128);
+        for (int tile = blockIdx.x; ok && locate_tile<BLOCK_N>(p, tile, num_m, total_tiles, row_start, tile_start, cursor, t); tile += gridDim.x, ++acc_iter) {
+            const int acc_stage = acc_iter % C::ACC_STAGES;
+            const uint32_t acc_phase = (acc_iter / C::ACC_STAGES) & 1u;
+            ok = mbar_wait(smem_u32(&acc_empty_bar[acc_stage]), acc_phase ^ 1u, abort_word, p.status);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
+            for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_word, p.status);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t sa = smem_u32(tiles + stage * C::STAGE_BYTES);
+                    const uint32_t sb = sa + A_TILE_BYTES;
+                    if constexpr (KIND == KIND_MXF4) {
+                        const uint32_t ssf = sb + C::B_TILE_BYTES;
+                        const uint32_t sf_t = tmem_base + C::SF_COL0 + stage * C::SF_COLS_PER_STAGE;
+                        // chunk order in shared memory: A kc0, A kc1, then per 128-column block of B: kc0, kc1
+                        tmem_cp_32x128b_warpx4(sf_t + 0, desc_at(sf_hi, ssf));
+                        tmem_cp_32x128b_warpx4(sf_t + 4, desc_at(sf_hi, ssf + SF_CHUNK_BYTES));
+#pragma unroll
+                        for (int rb = 0; rb < BLOCK_N / 128; ++rb) {
+                            // TMEM columns of B scales: [8 + kc*8 + rb*4]
+                            tmem_cp_32x128b_warpx4(sf_t + 8 + 0 * 8 + rb * 4, desc_at(sf_hi, ssf + (2 + rb * 2) * SF_CHUNK_BYTES));
+                            tmem_cp_32x128b_warpx4(sf_t + 8 + 1 * 8 + rb * 4, desc_at(sf_hi, ssf + (3 + rb * 2) * SF_CHUNK_BYTES));
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t sf_id = (j & 1) * 2u;
+                            const uint32_t idesc = p.idesc | (sf_id << 4) | (sf_id << 29);
+                            mma_mxf4(d_tmem, desc_at(a_hi, sa + j * 32), desc_at(b_hi, sb + j * 32), idesc, sf_t + (j >> 1) * 4,
+                                     sf_t + 8 + (j >> 1) * 8, (kb | j) != 0 ? 1u : 0u);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            mma_ss<KIND>(d_tmem, desc_at(a_hi, sa + j * a_kstep), desc_at(b_hi, sb + j * b_kstep), p.idesc,
+                                         (kb | j) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&empty_bar[stage]));          // stage reusable once these MMAs have read it
+                    if (kb == p.num_k_blocks - 1) tc_commit(smem_u32(&acc_full_bar[acc_stage]));
+                }
+                __syncwarp();
+                if (++stage == C::NUM_STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ===== epilogue =====
+        const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31
+        int cursor = 0, acc_iter = 0;
+        TileInfo t;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && locate_tile<BLOCK_N>(p, tile, num_m, total_tiles, row_start, tile_start, cursor, t); tile += gridDim.x, ++acc_iter) {
+            const int acc_stage = acc_iter % C::ACC_STAGES;
+            const uint32_t acc_phase = (acc_iter / C::ACC_STAGES) & 1u;
+            ok = mbar_wait(smem_u32(&acc_full_bar[acc_stage]), acc_phase, abort_word, p.status);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = t.row0 + quad * 32 + lane;
+            const bool row_ok = row < t.row_end;
+            const float tok = (row_ok && p.epi.tok) ? p.epi.tok[row] : 1.0f;
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc_stage * BLOCK_N;
+#pragma unroll 1
+            for (int c = 0; c < BLOCK_N / 32; ++c) {
+                const int col0 = t.n0 + c * 32;
+                if (col0 >= p.n) break;  // uniform across the CTA
+                uint32_t r[32];
+                tmem_ld_32x32(t_addr + c * 32, r);
+                tmem_ld_wait();
+                if (row_ok) {
+                    const int ncols = min(32, p.n - col0);
+                    epilogue_chunk<KIND == KIND_I8>(r, p.epi, row, col0, ncols, static_cast<size_t>(col0),
+                                                    static_cast<size_t>(t.group) * p.n + col0, tok);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[acc_stage]));
+        }
+    }
+
+    // ===== teardown =====
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_word) {
+        // give copies that may still be in flight time to land before the CTA's shared memory is released
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// Re-tiles MX scale factors [rows, ks] (row-major bytes) into 512-byte chunks: chunk (rb, kc) holds
+// the scales of rows rb*128 .. +127 and K-blocks kc*4 .. +3 at byte (r%32)*16 + (r/32)*4 + (ks%4),
+// the order tcgen05.cp (32x128b, warpx4) expects.  Missing rows / K-blocks are filled with 127 (1.0).
+__global__ void retile_scales_kernel(const uint8_t* __restrict__ src, uint32_t* __restrict__ dst, int rows, int ks, int row_blocks, int kc_count)
+{
+    const size_t total = static_cast<size_t>(row_blocks) * kc_count * 128;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int pos = static_cast<int>(i % 128);
+        const size_t chunk = i / 128;
+        const int kc = static_cast<int>(chunk % kc_count);
+        const int rb = static_cast<int>(chunk / kc_count);
+        const int r = rb * 128 + (pos & 3) * 32 + (pos >> 2);
+        uint32_t w = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int k = kc * 4 + b;
+            const uint32_t v = (r < rows && k < ks) ? src[static_cast<size_t>(r) * ks + k] : 127u;
+            w |= v << (8 * b);
+        }
+        dst[i] = w;
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(f);
+        else
+            (void)cudaGetLastError();
+    });
+    return fn;
+}
+
+// rank-3 map over [d2][d1][d0] (d0 contiguous), box {b0, b1, 1}, 128-byte swizzle, zero fill out of bounds.
+int make_map(CUtensorMap* map, CUtensorMapDataType dt, int esz, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_elems,
+             uint64_t stride2_elems, uint32_t b0, uint32_t b1)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return ASCB200_ECUDA;
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {stride1_elems * esz, stride2_elems * esz};
+    cuuint32_t box[3] = {b0, b1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (!aligned_to(base, 16) || strides[0] % 16 != 0 || strides[1] % 16 != 0) return ASCB200_EALIGN;
+    CUresult r = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? ASCB200_OK : ASCB200_ECUDA;
+}
+
+template <int KIND, int BLOCK_N>
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream)
+{
+    using C = Cfg<KIND, BLOCK_N>;
+    static bool configured[16] = {};
+    int dev = 0;
+    ASCB200_CUDA(cudaGetDevice(&dev));
+    if (!configured[dev & 15]) {
+        ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        configured[dev & 15] = true;
+    }
+    gemm_tc_kernel<KIND, BLOCK_N><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
+    ASCB200_CUDA(cudaGetLastError());
+    return ASCB200_OK;
+}
+
+int elem_bits(int kind) { return kind == ASCB200_KIND_MXFP4 ? 4 : kind == ASCB200_KIND_S8 ? 8 : 16; }
+int out_bytes(int dt) { return dt == OUT_S8 ? 1 : (dt == OUT_F16 || dt == OUT_BF16) ? 2 : 4; }
+
+int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups, cudaStream_t stream)
+{
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    if (!d) return ASCB200_EINVAL;
+    if (d->m < 0 || d->n < 0 || d->k < 0) return ASCB200_EINVAL;
+    if (d->m == 0 || d->n == 0) return ASCB200_OK;
+    if (!d->a_dev || !d->b_dev || !d->c_dev || d->k == 0) return ASCB200_EINVAL;
+    for (int i = 0; i < 4; ++i)
+        if (d->reserved[i] != 0) return ASCB200_EINVAL;
+    const int kind = d->kind;
+    if (kind < ASCB200_KIND_F16 || kind > ASCB200_KIND_MXFP4) return ASCB200_EINVAL;
+    const bool acc_int = kind == ASCB200_KIND_S8;
+    const bool grouped = groups > 0;
+    if (grouped && (groups > MAX_GROUPS)) return ASCB200_ETOOBIG;
+    if (grouped && (!group_counts || kind != ASCB200_KIND_S8 || d->epilogue != ASCB200_EPI_DEQUANT_TOKEN_CHANNEL || d->trans_a)) return ASCB200_EUNSUPPORTED;
+
+    // ---- epilogue validation ----
+    EpiParams e = {};
+    e.c = d->c_dev;
+    e.ldc = d->ldc ? d->ldc : d->n;
+    e.c_dtype = d->c_dtype;
+    e.mode = d->epilogue;
+    e.relu = d->relu;
+    e.act = d->act;
+    e.bias = d->bias_dev;
+    e.tok = d->tok_scale_dev;
+    e.ch = d->ch_scale_dev;
+    e.quant = reinterpret_cast<const unsigned long long*>(d->quant_dev);
+    e.quant_scalar = d->quant_scalar;
+    if (e.ldc < d->n) return ASCB200_EINVAL;
+    switch (d->epilogue) {
+        case ASCB200_EPI_CAST:
+            if (acc_int ? d->c_dtype != OUT_S32 : !(d->c_dtype == OUT_F32 || d->c_dtype == OUT_F16 || d->c_dtype == OUT_BF16)) return ASCB200_EUNSUPPORTED;
+            break;
+        case ASCB200_EPI_FIXPIPE_QUANT:
+            if (acc_int ? !(d->c_dtype == OUT_F16 || d->c_dtype == OUT_S8 || d->c_dtype == OUT_BF16)
+                        : !(d->c_dtype == OUT_S8 || d->c_dtype == OUT_F16 || d->c_dtype == OUT_BF16 || d->c_dtype == OUT_F32))
+                return ASCB200_EUNSUPPORTED;
+            break;
+        case ASCB200_EPI_DEQUANT_TOKEN_CHANNEL:
+            if (!acc_int || !d->ch_scale_dev) return ASCB200_EINVAL;
+            if (!(d->c_dtype == OUT_F32 || d->c_dtype == OUT_F16 || d->c_dtype == OUT_BF16)) return ASCB200_EUNSUPPORTED;
+            break;
+        default: return ASCB200_EINVAL;
+    }
+    if (d->act != 0 && !(d->act == 1 && d->epilogue == ASCB200_EPI_DEQUANT_TOKEN_CHANNEL)) return ASCB200_EUNSUPPORTED;
+    if (d->c2_dev) {
+        if (acc_int || !(d->c2_dtype == OUT_F32 || d->c2_dtype == OUT_F16 || d->c2_dtype == OUT_BF16)) return ASCB200_EUNSUPPORTED;
+        e.c2 = d->c2_dev;
+        e.ldc2 = d->ldc2 ? d->ldc2 : d->n;
+        e.c2_dtype = d->c2_dtype;
+        if (e.ldc2 < d->n) return ASCB200_EINVAL;
+        e.vec_c2 = aligned_to(e.c2, 16) && (e.ldc2 * out_bytes(e.c2_dtype)) % 16 == 0;
+    }
+    e.vec_c = aligned_to(e.c, 16) && (e.ldc * out_bytes(e.c_dtype)) % 16 == 0;
+
+    // ---- operands ----
+    const int bits = elem_bits(kind);
+    const int k = d->k, m = d->m, n = d->n;
+    if (kind == ASCB200_KIND_MXFP4) {
+        // K-major operands only; K a multiple of 64 like the reference's MmadMx
+        if (d->trans_a || !d->trans_b) return ASCB200_EUNSUPPORTED;
+        if (k % 64 != 0) return ASCB200_EINVAL;
+        if (!d->scale_a_dev || !d->scale_b_dev) return ASCB200_EINVAL;
+    }
+    const int64_t lda = d->lda ? d->lda : (d->trans_a ? m : k);
+    const int64_t ldb = d->ldb ? d->ldb : (d->trans_b ? k : n);
+    const int esz = bits == 16 ? 2 : 1;                // bytes per tensor-map element
+    const int epb = bits == 4 ? 2 : 1;                 // logical elements per tensor-map element
+    const CUtensorMapDataType dt = kind == ASCB200_KIND_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                 : kind == ASCB200_KIND_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                             : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const uint32_t row_elems = ROW_BYTES / esz;        // tensor-map elements per 128-byte row
+    const int block_k = bits == 16 ? 64 : bits == 8 ? 128 : 256;
+
+    int block_n = 256;
+    {
+        const long long num_m = grouped ? (m + BLOCK_M - 1) / BLOCK_M + groups : (m + BLOCK_M - 1) / BLOCK_M;
+        while (block_n > 64 && (n <= block_n / 2 || num_m * ((n + block_n - 1) / block_n) < st->sm_count)) block_n /= 2;
+        if (kind == ASCB200_KIND_MXFP4 && block_n < 128) block_n = 128;
+    }
+
+    CUtensorMap ta, tb;
+    int rc;
+    if (!d->trans_a) rc = make_map(&ta, dt, esz, d->a_dev, k / epb, m, 1, lda / epb, static_cast<uint64_t>(lda / epb) * m, row_elems, BLOCK_M);
+    else rc = make_map(&ta, dt, esz, d->a_dev, m, k, 1, lda, static_cast<uint64_t>(lda) * k, row_elems, block_k);
+    if (rc != ASCB200_OK) return rc;
+    const uint64_t g3 = grouped ? groups : 1;
+    if (d->trans_b) rc = make_map(&tb, dt, esz, d->b_dev, k / epb, n, g3, ldb / epb, static_cast<uint64_t>(ldb / epb) * n, row_elems, block_n);
+    else rc = make_map(&tb, dt, esz, d->b_dev, n, k, g3, ldb, static_cast<uint64_t>(ldb) * k, row_elems, block_k);
+    if (rc != ASCB200_OK) return rc;
+
+    GemmParams p = {};
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.num_k_blocks = (k + block_k - 1) / block_k;
+    p.a_mn = d->trans_a ? 1 : 0;
+    p.b_mn = d->trans_b ? 0 : 1;
+    p.groups = grouped ? groups : 0;
+    p.group_counts = reinterpret_cast<const long long*>(group_counts);
+    p.status = st->status_dev;
+    p.epi = e;
+
+    if (kind == ASCB200_KIND_MXFP4) {
+        // re-tile both scale tensors into scratch (layout documented at retile_scales_kernel)
+        const int ks = k / 32;
+        const int kc = 2 * p.num_k_blocks;
+        const int rba = (m + 127) / 128, rbb = (n + 255) / 256 * 2;
+        const size_t bytes_a = static_cast<size_t>(rba) * kc * SF_CHUNK_BYTES, bytes_b = static_cast<size_t>(rbb) * kc * SF_CHUNK_BYTES;
+        rc = ensure_scratch(st, bytes_a + bytes_b, stream);
+        if (rc != ASCB200_OK) return rc;
+        uint8_t* sfa = static_cast<uint8_t*>(st->scratch_dev);
+        uint8_t* sfb = sfa + bytes_a;
+        const int ga = static_cast<int>(std::min<size_t>((bytes_a / 4 + 255) / 256, 4096));
+        const int gb = static_cast<int>(std::min<size_t>((bytes_b / 4 + 255) / 256, 4096));
+        retile_scales_kernel<<<ga, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_a_dev), reinterpret_cast<uint32_t*>(sfa), m, ks, rba, kc);
+        retile_scales_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_b_dev), reinterpret_cast<uint32_t*>(sfb), n, ks, rbb, kc);
+        ASCB200_CUDA(cudaGetLastError());
+        p.sfa = sfa;
+        p.sfb = sfb;
+        p.sf_kc = kc;
+    }
+
+    const long long max_tiles = grouped ? (static_cast<long long>((m + BLOCK_M - 1) / BLOCK_M) + groups) * ((n + block_n - 1) / block_n)
+                                        : static_cast<long long>((m + BLOCK_M - 1) / BLOCK_M) * ((n + block_n - 1) / block_n);
+    const int grid = static_cast<int>(std::min<long long>(max_tiles, st->sm_count));
+
+    const uint32_t a_mn = p.a_mn, b_mn = p.b_mn;
+    switch (kind) {
+        case ASCB200_KIND_F16:
+        case ASCB200_KIND_BF16: {
+            const uint32_t fmt = kind == ASCB200_KIND_BF16 ? 1u : 0u;
+            p.idesc = make_idesc(1, fmt, fmt, a_mn, b_mn, BLOCK_M, block_n);
+            if (block_n == 256) return launch_gemm<KIND_F16, 256>(ta, tb, p, grid, stream);
+            if (block_n == 128) return launch_gemm<KIND_F16, 128>(ta, tb, p, grid, stream);
+            return launch_gemm<KIND_F16, 64>(ta, tb, p, grid, stream);
+        }
+        case ASCB200_KIND_S8:
+            p.idesc = make_idesc(2, 1, 1, a_mn, b_mn, BLOCK_M, block_n);
+            if (block_n == 256) return launch_gemm<KIND_I8, 256>(ta, tb, p, grid, stream);
+            if (block_n == 128) return launch_gemm<KIND_I8, 128>(ta, tb, p, grid, stream);
+            return launch_gemm<KIND_I8, 64>(ta, tb, p, grid, stream);
+        default:
+            p.idesc = make_idesc_mxf4(BLOCK_M, block_n);
+            if (block_n == 256) return launch_gemm<KIND_MXF4, 256>(ta, tb, p, grid, stream);
+            return launch_gemm<KIND_MXF4, 128>(ta, tb, p, grid, stream);
+    }
+}
+
+}  // namespace
+}  // namespace ascb200
+
+extern "C" {
+
+int ascb200_gemm(const ascb200_gemm_desc* desc, void* stream)
+{
+    return ascb200::run_gemm(desc, nullptr, 0, static_cast<cudaStream_t>(stream));
+}
+
+int ascb200_grouped_gemm(const ascb200_gemm_desc* desc, const int64_t* group_counts_dev, int32_t groups, void* stream)
+{
+    if (groups <= 0) return groups == 0 ? ASCB200_OK : ASCB200_EINVAL;
+    return ascb200::run_gemm(desc, group_counts_dev, groups, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

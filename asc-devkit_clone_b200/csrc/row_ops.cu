@@ -1,0 +1,439 @@
+// Memory-bound row operators: SoftMax, AscendQuant, AscendDequant and the fused SoftMax+AscendQuant.
+// Every kernel reads its input once with 128-bit loads, keeps the row in registers, reduces with
+// warp shuffles and writes each output once with vector stores.
+#include "common.cuh"
+
+namespace ascb200 {
+namespace {
+
+constexpr float kNegInf = -__builtin_huge_valf();
+
+__device__ __forceinline__ uint4 ldg_nc_v4(const void* p)
+{
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+
+// half(x) * half(scale) + half(offset) -> int8, every step rounded to half (no fused multiply-add).
+__device__ __forceinline__ int quant_half(__half x, __half s, __half o)
+{
+    __half v = __hadd_rn(__hmul_rn(x, s), o);
+    return f32_to_s8(__half2float(v));
+}
+__device__ __forceinline__ __half to_half_src(__half v) { return v; }
+__device__ __forceinline__ __half to_half_src(__nv_bfloat16 v) { return f32_to_f16_sat(__bfloat162float(v)); }
+__device__ __forceinline__ __half to_half_src(float v) { return f32_to_f16_sat(v); }
+
+template <int TPR>
+__device__ __forceinline__ float row_reduce_max(float v, float* red)
+{
+    v = warp_max(v);
+    if constexpr (TPR > 32) {
+        const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+        __syncthreads();
+        if (l == 0) red[w] = v;
+        __syncthreads();
+        v = (l < TPR / 32) ? red[l] : kNegInf;
+        v = warp_max(v);
+    }
+    return v;
+}
+template <int TPR>
+__device__ __forceinline__ float row_reduce_sum(float v, float* red)
+{
+    v = warp_sum(v);
+    if constexpr (TPR > 32) {
+        const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+        __syncthreads();
+        if (l == 0) red[w] = v;
+        __syncthreads();
+        v = (l < TPR / 32) ? red[l] : 0.0f;
+        v = warp_sum(v);
+    }
+    return v;
+}
+
+// One row per group of TPR threads (a warp, or the whole block).  Thread t of the group owns the
+// 16-byte chunks t, t+TPR, ... (NCHUNK of them).  T = __half (8 per chunk) or float (4 per chunk).
+template <typename T, int TPR, int NCHUNK, bool QUANT>
+__global__ void __launch_bounds__(TPR > 32 ? TPR : 256)
+softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __restrict__ sum_out, float* __restrict__ max_out,
+                    int8_t* __restrict__ q_out, const __half* __restrict__ q_scale, const __half* __restrict__ q_offset,
+                    __half q_offset_scalar, int m, int k, int stats_rep)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    __shared__ float red[32];
+    const int t = TPR > 32 ? threadIdx.x : (threadIdx.x & 31);
+    const int row = TPR > 32 ? blockIdx.x : blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= m) return;  // whole group leaves together
+    const int nchunks = k / VEC;
+    const T* srow = src + static_cast<size_t>(row) * k;
+
+    float v[NCHUNK * VEC];
+    uint4 raw[NCHUNK];
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+        const int c = t + i * TPR;
+        if (c < nchunks) raw[i] = ldg_nc_v4(srow + c * VEC);
+    }
+    float mx = kNegInf;
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+        const int c = t + i * TPR;
+        if (c < nchunks) {
+            if constexpr (sizeof(T) == 2) {
+                const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float2 f = __half22float2(h[j]);
+                    v[i * 8 + 2 * j] = f.x;
+                    v[i * 8 + 2 * j + 1] = f.y;
+                }
+            } else {
+                v[i * 4 + 0] = __uint_as_float(raw[i].x);
+                v[i * 4 + 1] = __uint_as_float(raw[i].y);
+                v[i * 4 + 2] = __uint_as_float(raw[i].z);
+                v[i * 4 + 3] = __uint_as_float(raw[i].w);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) v[i * VEC + j] = kNegInf;
+        }
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) mx = fmaxf(mx, v[i * VEC + j]);
+    }
+    mx = row_reduce_max<TPR>(mx, red);
+
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NCHUNK * VEC; ++i) {
+        v[i] = __expf(v[i] - mx);
+        s += v[i];
+    }
+    s = row_reduce_sum<TPR>(s, red);
+    const float inv = __frcp_rn(s);
+
+    T* drow = dst + static_cast<size_t>(row) * k;
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+        const int c = t + i * TPR;
+        if (c < nchunks) {
+            if constexpr (sizeof(T) == 2) {
+                uint4 o;
+                __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    h[j] = __halves2half2(f32_to_f16_sat(v[i * 8 + 2 * j] * inv), f32_to_f16_sat(v[i * 8 + 2 * j + 1] * inv));
+                *reinterpret_cast<uint4*>(drow + c * 8) = o;
+                if constexpr (QUANT) {
+                    const uint4 sc = *reinterpret_cast<const uint4*>(q_scale + c * 8);
+                    uint4 of;
+                    if (q_offset) of = *reinterpret_cast<const uint4*>(q_offset + c * 8);
+                    const __half* hs = reinterpret_cast<const __half*>(&sc);
+                    const __half* ho = reinterpret_cast<const __half*>(&of);
+                    const __half* hy = reinterpret_cast<const __half*>(&o);
+                    uint32_t pk[2] = {0u, 0u};
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int q = quant_half(hy[j], hs[j], q_offset ? ho[j] : q_offset_scalar);
+                        pk[j >> 2] |= static_cast<uint32_t>(q & 0xFF) << (8 * (j & 3));
+                    }
+                    *reinterpret_cast<uint2*>(q_out + static_cast<size_t>(row) * k + c * 8) = make_uint2(pk[0], pk[1]);
+                }
+            } else {
+                float4 o = make_float4(v[i * 4] * inv, v[i * 4 + 1] * inv, v[i * 4 + 2] * inv, v[i * 4 + 3] * inv);
+                *reinterpret_cast<float4*>(drow + c * 4) = o;
+            }
+        }
+    }
+    if (t < stats_rep) {
+        sum_out[static_cast<size_t>(row) * stats_rep + t] = s;
+        max_out[static_cast<size_t>(row) * stats_rep + t] = mx;
+    }
+}
+
+template <typename T, bool QUANT>
+int launch_softmax(const T* src, T* dst, float* sum, float* mx, int8_t* q, const __half* qs, const __half* qo, __half qos, int m,
+                   int k, int rep, cudaStream_t st)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    const int nchunks = k / VEC;
+#define ASCB200_SM_WARP(NC)                                                                                              \
+    softmax_rows_kernel<T, 32, NC, QUANT><<<(m + 7) / 8, 256, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep)
+#define ASCB200_SM_BLOCK(TPR, NC) softmax_rows_kernel<T, TPR, NC, QUANT><<<m, TPR, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep)
+    if (nchunks <= 32) ASCB200_SM_WARP(1);
+    else if (nchunks <= 64) ASCB200_SM_WARP(2);
+    else if (nchunks <= 128) ASCB200_SM_WARP(4);
+    else if (nchunks <= 256) ASCB200_SM_WARP(8);
+    else if (nchunks <= 1024) ASCB200_SM_BLOCK(256, 4);
+    else if (nchunks <= 2048) ASCB200_SM_BLOCK(256, 8);
+    else if (nchunks <= 8192) ASCB200_SM_BLOCK(1024, 8);
+    else return ASCB200_ETOOBIG;
+#undef ASCB200_SM_WARP
+#undef ASCB200_SM_BLOCK
+    ASCB200_CUDA(cudaGetLastError());
+    return ASCB200_OK;
+}
+
+// ---- AscendQuant ------------------------------------------------------------------------------
+// 8 elements per thread.  PER_CHANNEL: scale/offset indexed by (element index % scale_count).
+template <typename T, bool PER_CHANNEL>
+__global__ void __launch_bounds__(256)
+quant_vec8_kernel(const T* __restrict__ src, int8_t* __restrict__ dst, size_t n8, int scale_count, const T* __restrict__ scale,
+                  const T* __restrict__ offset, __half scale_h, __half offset_h)
+{
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        T x[8], s[8], o[8];
+        const size_t e = i * 8;
+        if constexpr (sizeof(T) == 2) {
+            *reinterpret_cast<uint4*>(x) = ldg_nc_v4(src + e);
+        } else {
+            *reinterpret_cast<uint4*>(x) = ldg_nc_v4(src + e);
+            *reinterpret_cast<uint4*>(x + 4) = ldg_nc_v4(src + e + 4);
+        }
+        if constexpr (PER_CHANNEL) {
+            const int c = static_cast<int>(e % static_cast<size_t>(scale_count));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[j] = scale[c + j];
+            if (offset) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = offset[c + j];
+            }
+        }
+        uint32_t pk[2] = {0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            __half hs = scale_h, ho = offset_h;
+            if constexpr (PER_CHANNEL) {
+                hs = to_half_src(s[j]);
+                if (offset) ho = to_half_src(o[j]);
+            }
+            const int q = quant_half(to_half_src(x[j]), hs, ho);
+            pk[j >> 2] |= static_cast<uint32_t>(q & 0xFF) << (8 * (j & 3));
+        }
+        *reinterpret_cast<uint2*>(dst + e) = make_uint2(pk[0], pk[1]);
+    }
+}
+// Scalar path for extents or pointers that do not allow the 8-wide path.
+template <typename T, bool PER_CHANNEL>
+__global__ void __launch_bounds__(256)
+quant_scalar_kernel(const T* __restrict__ src, int8_t* __restrict__ dst, size_t n, int scale_count, const T* __restrict__ scale,
+                    const T* __restrict__ offset, __half scale_h, __half offset_h)
+{
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        __half hs = scale_h, ho = offset_h;
+        if constexpr (PER_CHANNEL) {
+            const int c = static_cast<int>(i % static_cast<size_t>(scale_count));
+            hs = to_half_src(scale[c]);
+            if (offset) ho = to_half_src(offset[c]);
+        }
+        dst[i] = static_cast<int8_t>(quant_half(to_half_src(src[i]), hs, ho));
+    }
+}
+
+template <typename T>
+int launch_quant(const void* src, int8_t* dst, size_t n, int scale_count, const void* scale, const void* offset, __half scale_h,
+                 __half offset_h, int sms, cudaStream_t st)
+{
+    const bool per_channel = scale != nullptr;
+    const bool vec = (n % 8 == 0) && aligned_to(src, 16) && aligned_to(dst, 8) && (!per_channel || scale_count % 8 == 0);
+    const size_t work = vec ? n / 8 : n;
+    if (work == 0) return ASCB200_OK;
+    const int grid = static_cast<int>(std::min<size_t>((work + 255) / 256, static_cast<size_t>(sms) * 16));
+    const T* s = static_cast<const T*>(src);
+    const T* sc = static_cast<const T*>(scale);
+    const T* of = static_cast<const T*>(offset);
+    if (vec) {
+        if (per_channel) quant_vec8_kernel<T, true><<<grid, 256, 0, st>>>(s, dst, work, scale_count, sc, of, scale_h, offset_h);
+        else quant_vec8_kernel<T, false><<<grid, 256, 0, st>>>(s, dst, work, 1, nullptr, nullptr, scale_h, offset_h);
+    } else {
+        if (per_channel) quant_scalar_kernel<T, true><<<grid, 256, 0, st>>>(s, dst, work, scale_count, sc, of, scale_h, offset_h);
+        else quant_scalar_kernel<T, false><<<grid, 256, 0, st>>>(s, dst, work, 1, nullptr, nullptr, scale_h, offset_h);
+    }
+    ASCB200_CUDA(cudaGetLastError());
+    return ASCB200_OK;
+}
+
+// ---- AscendDequant ----------------------------------------------------------------------------
+template <typename D>
+__device__ __forceinline__ D dequant_cast(float v);
+template <>
+__device__ __forceinline__ float dequant_cast<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half dequant_cast<__half>(float v) { return f32_to_f16_sat(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 dequant_cast<__nv_bfloat16>(float v) { return f32_to_bf16(v); }
+
+// SCALE: 0 scalar, 1 fp32 tensor, 2 bf16 tensor.  VEC = 4 (vector path) or 1.
+template <typename D, int SCALE, int VEC>
+__global__ void __launch_bounds__(256)
+dequant_kernel(const int32_t* __restrict__ src, D* __restrict__ dst, int m, int n, int cal_count, int n_dst, const void* __restrict__ scale,
+               float scale_scalar)
+{
+    const int per_row = cal_count / VEC;
+    const size_t total = static_cast<size_t>(m) * per_row;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(i / per_row);
+        const int c = static_cast<int>(i % per_row) * VEC;
+        int32_t x[VEC];
+        D y[VEC];
+        if constexpr (VEC == 4) *reinterpret_cast<uint4*>(x) = ldg_nc_v4(src + static_cast<size_t>(r) * n + c);
+        else x[0] = src[static_cast<size_t>(r) * n + c];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            float s = scale_scalar;
+            if constexpr (SCALE == 1) s = static_cast<const float*>(scale)[c + j];
+            if constexpr (SCALE == 2) s = __bfloat162float(static_cast<const __nv_bfloat16*>(scale)[c + j]);
+            y[j] = dequant_cast<D>(__fmul_rn(static_cast<float>(x[j]), s));
+        }
+        D* out = dst + static_cast<size_t>(r) * n_dst + c;
+        if constexpr (VEC == 4 && sizeof(D) == 4) *reinterpret_cast<uint4*>(out) = *reinterpret_cast<uint4*>(y);
+        else if constexpr (VEC == 4) *reinterpret_cast<uint2*>(out) = *reinterpret_cast<uint2*>(y);
+        else out[0] = y[0];
+    }
+}
+
+template <typename D, int SCALE>
+int launch_dequant(const int32_t* src, void* dst, int m, int n, int cal, int n_dst, const void* scale, float ss, int sms, cudaStream_t st)
+{
+    const bool vec = n % 4 == 0 && cal % 4 == 0 && n_dst % 4 == 0 && aligned_to(src, 16) && aligned_to(dst, 16);
+    const size_t work = static_cast<size_t>(m) * (vec ? cal / 4 : cal);
+    if (work == 0) return ASCB200_OK;
+    const int grid = static_cast<int>(std::min<size_t>((work + 255) / 256, static_cast<size_t>(sms) * 16));
+    if (vec) dequant_kernel<D, SCALE, 4><<<grid, 256, 0, st>>>(src, static_cast<D*>(dst), m, n, cal, n_dst, scale, ss);
+    else dequant_kernel<D, SCALE, 1><<<grid, 256, 0, st>>>(src, static_cast<D*>(dst), m, n, cal, n_dst, scale, ss);
+    ASCB200_CUDA(cudaGetLastError());
+    return ASCB200_OK;
+}
+
+int check_softmax_args(const void* src, void* dst, float* sum, float* mx, int m, int k, int dtype)
+{
+    if (!src || !dst || !sum || !mx || m < 0 || k <= 0) return ASCB200_EINVAL;
+    if (dtype != ASCB200_F16 && dtype != ASCB200_F32) return ASCB200_EUNSUPPORTED;
+    const int esz = dtype == ASCB200_F16 ? 2 : 4;
+    if ((static_cast<size_t>(k) * esz) % 32 != 0) return ASCB200_EALIGN;  // the reference's last-axis rule
+    if (!aligned_to(src, 16) || !aligned_to(dst, 16)) return ASCB200_EALIGN;
+    return ASCB200_OK;
+}
+
+__half scalar_as_src_half(float v, int dtype)
+{
+    // The per-channel overload takes the scalar offset in the source type T; the operator then
+    // converts T to half exactly like the tensor elements.
+    if (dtype == ASCB200_F16) return __float2half_rn(v);
+    if (dtype == ASCB200_BF16) v = __bfloat162float(__float2bfloat16_rn(v));
+    unsigned short b = __half_as_ushort(__float2half_rn(v));
+    if ((b & 0x7FFFu) == 0x7C00u) b = (b & 0x8000u) | 0x7BFFu;
+    return __ushort_as_half(b);
+}
+
+}  // namespace
+}  // namespace ascb200
+
+using namespace ascb200;
+
+extern "C" {
+
+int ascb200_softmax(const void* src, void* dst, float* sum, float* mx, int32_t m, int32_t k, int32_t dtype, int32_t stats_brc,
+                    void* stream)
+{
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    int rc = check_softmax_args(src, dst, sum, mx, m, k, dtype);
+    if (rc != ASCB200_OK) return rc;
+    if (m == 0) return ASCB200_OK;
+    const int rep = stats_brc ? 8 : 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == ASCB200_F16)
+        return launch_softmax<__half, false>(static_cast<const __half*>(src), static_cast<__half*>(dst), sum, mx, nullptr, nullptr,
+                                             nullptr, __half(), m, k, rep, s);
+    return launch_softmax<float, false>(static_cast<const float*>(src), static_cast<float*>(dst), sum, mx, nullptr, nullptr, nullptr,
+                                        __half(), m, k, rep, s);
+}
+
+int ascb200_softmax_quant(const void* src, void* dst, float* sum, float* mx, int8_t* q, const void* scale, const void* offset_t,
+                          float offset, int32_t m, int32_t k, int32_t stats_brc, void* stream)
+{
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    int rc = check_softmax_args(src, dst, sum, mx, m, k, ASCB200_F16);
+    if (rc != ASCB200_OK) return rc;
+    if (!q || !scale) return ASCB200_EINVAL;
+    if (!aligned_to(q, 8) || !aligned_to(scale, 16) || (offset_t && !aligned_to(offset_t, 16))) return ASCB200_EALIGN;
+    if (m == 0) return ASCB200_OK;
+    return launch_softmax<__half, true>(static_cast<const __half*>(src), static_cast<__half*>(dst), sum, mx, q,
+                                        static_cast<const __half*>(scale), static_cast<const __half*>(offset_t),
+                                        __float2half_rn(offset), m, k, stats_brc ? 8 : 1, static_cast<cudaStream_t>(stream));
+}
+
+int ascb200_quant_per_tensor(const void* src, int8_t* dst, int64_t cal_count, int32_t dtype, float scale, float offset, void* stream)
+{
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    if (!src || !dst || cal_count < 0) return ASCB200_EINVAL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const __half hs = __float2half_rn(scale), ho = __float2half_rn(offset);  // static_cast<half>(scale)
+    const size_t n = static_cast<size_t>(cal_count);
+    switch (dtype) {
+        case ASCB200_F16: return launch_quant<__half>(src, dst, n, 1, nullptr, nullptr, hs, ho, st->sm_count, s);
+        case ASCB200_BF16: return launch_quant<__nv_bfloat16>(src, dst, n, 1, nullptr, nullptr, hs, ho, st->sm_count, s);
+        case ASCB200_F32: return launch_quant<float>(src, dst, n, 1, nullptr, nullptr, hs, ho, st->sm_count, s);
+        default: return ASCB200_EUNSUPPORTED;
+    }
+}
+
+int ascb200_quant_per_channel(const void* src, int8_t* dst, int32_t rows, int32_t scale_count, int32_t dtype, const void* scale,
+                              const void* offset_t, float offset, void* stream)
+{
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    if (!src || !dst || !scale || rows < 0 || scale_count <= 0) return ASCB200_EINVAL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t n = static_cast<size_t>(rows) * scale_count;
+    const __half ho = scalar_as_src_half(offset, dtype);
+    switch (dtype) {
+        case ASCB200_F16: return launch_quant<__half>(src, dst, n, scale_count, scale, offset_t, __half(), ho, st->sm_count, s);
+        case ASCB200_BF16: return launch_quant<__nv_bfloat16>(src, dst, n, scale_count, scale, offset_t, __half(), ho, st->sm_count, s);
+        case ASCB200_F32: return launch_quant<float>(src, dst, n, scale_count, scale, offset_t, __half(), ho, st->sm_count, s);
+        default: return ASCB200_EUNSUPPORTED;
+    }
+}
+
+int ascb200_dequant(const int32_t* src, void* dst, int32_t m, int32_t n, int32_t cal_count, int32_t n_dst, int32_t dst_dtype,
+                    const void* scale, int32_t scale_dtype, float scale_scalar, void* stream)
+{
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    if (!src || !dst || m < 0 || n <= 0 || cal_count < 0 || cal_count > n || n_dst < cal_count) return ASCB200_EINVAL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int sms = st->sm_count;
+#define ASCB200_DEQ(D)                                                                                                     \
+    do {                                                                                                                   \
+        if (!scale) return launch_dequant<D, 0>(src, dst, m, n, cal_count, n_dst, nullptr, scale_scalar, sms, s);          \
+        if (scale_dtype == ASCB200_F32) return launch_dequant<D, 1>(src, dst, m, n, cal_count, n_dst, scale, 0.f, sms, s);  \
+        if (scale_dtype == ASCB200_BF16) return launch_dequant<D, 2>(src, dst, m, n, cal_count, n_dst, scale, 0.f, sms, s); \
+        return ASCB200_EUNSUPPORTED;                                                                                       \
+    } while (0)
+    switch (dst_dtype) {
+        case ASCB200_F32: ASCB200_DEQ(float);
+        case ASCB200_F16: ASCB200_DEQ(__half);
+        case ASCB200_BF16: ASCB200_DEQ(__nv_bfloat16);
+        default: return ASCB200_EUNSUPPORTED;
+    }
+#undef ASCB200_DEQ
+}
+
+}  // extern "C"

@@ -1,0 +1,187 @@
+/*
+ * ascb200 - C ABI of the B200 (sm_100a) implementation of the Ascend C high-level operator hot
+ * path: adv_api Matmul (IterateAll + fixpipe quant/dequant epilogue), grouped quantized matmul,
+ * SoftMax, AscendQuant, AscendDequant.
+ *
+ * The reference is a header-only C++ template library instantiated inside the user's NPU kernel;
+ * it has no FFI of its own.  This header is the boundary a port binds instead: each entry point
+ * names the reference interface it replaces (paths relative to the reference project).  The C++
+ * mirror of the reference classes (AscendC::Matmul<>, AscendC::SoftMax, ...) in
+ * asc-devkit_clone_b200/hostapi calls only these functions.
+ *
+ * Conventions
+ *  - every pointer named *_dev is CUDA device memory owned by the caller; the library never frees it;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the default stream); calls are asynchronous;
+ *  - return value: 0 on success, a negative ASCB200_E* code otherwise; nothing throws, aborts or traps;
+ *  - there is no CPU fallback: without a usable sm_100 device every compute call returns ASCB200_ENODEV.
+ */
+#ifndef ASCB200_H
+#define ASCB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ASCB200_API __attribute__((visibility("default")))
+
+/* ---- error codes ------------------------------------------------------------------------- */
+enum {
+    ASCB200_OK = 0,
+    ASCB200_EINVAL = -1,      /* bad argument (null pointer, non-positive extent, unknown enum)   */
+    ASCB200_EALIGN = -2,      /* pointer or leading dimension violates an alignment rule          */
+    ASCB200_EUNSUPPORTED = -3,/* valid in the reference, not implemented here                     */
+    ASCB200_ENODEV = -4,      /* no CUDA device of compute capability 10.x                        */
+    ASCB200_ECUDA = -5,       /* a CUDA runtime / driver call failed (see ascb200_last_cuda_error) */
+    ASCB200_ETIMEOUT = -6,    /* a device-side bounded wait expired (reported by ascb200_device_status) */
+    ASCB200_ETOOBIG = -7      /* extent beyond a documented limit                                 */
+};
+
+/* ---- element types ----------------------------------------------------------------------- */
+enum {
+    ASCB200_F32 = 0,
+    ASCB200_F16 = 1,
+    ASCB200_BF16 = 2,
+    ASCB200_S8 = 3,
+    ASCB200_S32 = 4,
+    ASCB200_FP4_E2M1 = 5      /* two values per byte, even index in the low nibble */
+};
+
+/* ---- library / device ---------------------------------------------------------------------- */
+
+/* Selects `device`, checks it is sm_100, creates the per-device state (status word, scratch).
+ * Replaces the examples' aclInit/aclrtSetDevice
+ * (examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul/matmul.asc:212-217). */
+ASCB200_API int ascb200_init(int device);
+ASCB200_API const char* ascb200_strerror(int code);
+/* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
+ASCB200_API int ascb200_last_cuda_error(void);
+/* Copies the device status word to *status_host (synchronises `stream`). Bit 0: a bounded wait
+ * inside a GEMM kernel expired. Non-zero status makes the call return ASCB200_ETIMEOUT and clears it. */
+ASCB200_API int ascb200_device_status(void* stream, uint32_t* status_host);
+ASCB200_API int ascb200_sm_count(void);
+
+/* Memory and stream shims for aclrtMalloc / aclrtMallocHost / aclrtMemcpy(Async) /
+ * aclrtSynchronizeStream as used by the examples (matmul.asc:219-260). */
+ASCB200_API int ascb200_malloc(void** dev_ptr, size_t bytes);
+ASCB200_API int ascb200_free(void* dev_ptr);
+ASCB200_API int ascb200_malloc_host(void** host_ptr, size_t bytes);     /* pinned */
+ASCB200_API int ascb200_free_host(void* host_ptr);
+ASCB200_API int ascb200_memcpy_h2d(void* dst_dev, const void* src_host, size_t bytes, void* stream);
+ASCB200_API int ascb200_memcpy_d2h(void* dst_host, const void* src_dev, size_t bytes, void* stream);
+ASCB200_API int ascb200_memset(void* dst_dev, int value, size_t bytes, void* stream);
+ASCB200_API int ascb200_stream_create(void** stream);
+ASCB200_API int ascb200_stream_destroy(void* stream);
+ASCB200_API int ascb200_stream_sync(void* stream);
+/* Timing helpers (CUDA events on `stream`) so that C hosts can measure without the runtime API. */
+ASCB200_API int ascb200_event_create(void** event);
+ASCB200_API int ascb200_event_destroy(void* event);
+ASCB200_API int ascb200_event_record(void* event, void* stream);
+ASCB200_API int ascb200_event_elapsed_ms(void* start, void* stop, float* ms); /* synchronises on stop */
+
+/* ---- Matmul ---------------------------------------------------------------------------------- */
+
+/* Output stage applied to the accumulator tile, the job of Fixpipe in the reference
+ * (impl/adv_api/detail/matmul/stage/copy_cube_out/copy_cube_out_fixpipe.h:339-358). */
+enum {
+    /* cast only: fp32 acc -> F32 / F16 / BF16 (RINT, F322F16 / F322BF16); int32 acc -> S32 */
+    ASCB200_EPI_CAST = 0,
+    /* quantising fixpipe modes selected by (accumulator, c_dtype), parameter = `quant`:
+     *   int32 -> F16 (V)DEQF16, int32 -> S8 (V)REQ8, int32 -> BF16 (V)QS322BF16_PRE,
+     *   fp32 -> S8 (V)QF322B8_PRE, fp32 -> F16/BF16/F32 (V)QF322{F16,BF16,F32}_PRE
+     * (impl/adv_api/detail/matmul/stage/copy_cube_out/quant/quant_processor_fixpipe.h:89-116,209-236) */
+    ASCB200_EPI_FIXPIPE_QUANT = 1,
+    /* int32 acc -> (float(acc) * ch_scale[n]) * tok_scale[m] -> F32 / F16 / BF16: AscendDequant + Mul + Cast
+     * of the grouped example (quant_group_matmul_custom.asc:433-450); optional FasterGelu (act = 1) */
+    ASCB200_EPI_DEQUANT_TOKEN_CHANNEL = 2
+};
+
+enum { ASCB200_KIND_F16 = 0, ASCB200_KIND_BF16 = 1, ASCB200_KIND_S8 = 2, ASCB200_KIND_MXFP4 = 3 };
+
+typedef struct ascb200_gemm_desc {
+    int32_t kind;            /* ASCB200_KIND_*: operand type; accumulator is fp32 (F16/BF16/MXFP4) or int32 (S8) */
+    int32_t m, n, k;         /* C[m,n] = A[m,k] * B[k,n]; k counts elements (fp4 values for MXFP4) */
+    const void* a_dev;       /* trans_a == 0: [m,k] row-major (ND); trans_a == 1: [k,m] row-major */
+    const void* b_dev;       /* trans_b == 0: [k,n] row-major (ND); trans_b == 1: [n,k] row-major */
+    int64_t lda, ldb;        /* leading dimensions in elements (0 = packed) */
+    int32_t trans_a, trans_b;
+    const void* scale_a_dev; /* MXFP4: e8m0 bytes [m, k/32] row-major */
+    const void* scale_b_dev; /* MXFP4: e8m0 bytes [n, k/32] row-major */
+    const void* bias_dev;    /* NULL or [n]: fp32 for fp32 accumulators, int32 for int32 accumulators */
+    void* c_dev;             /* [m,n] row-major, leading dimension ldc (0 = n) */
+    int64_t ldc;
+    int32_t c_dtype;         /* ASCB200_F32 / F16 / BF16 / S8 / S32 */
+    void* c2_dev;            /* optional second output: the fp32 accumulator cast to c2_dtype (F16/BF16/F32) */
+    int64_t ldc2;
+    int32_t c2_dtype;
+    int32_t epilogue;        /* ASCB200_EPI_* */
+    const uint64_t* quant_dev; /* FIXPIPE_QUANT per channel: [n] parameters (SetQuantVector) or NULL */
+    uint64_t quant_scalar;   /* FIXPIPE_QUANT per tensor (SetQuantScalar), used when quant_dev == NULL */
+    const float* tok_scale_dev; /* DEQUANT_TOKEN_CHANNEL: [m] or NULL */
+    const float* ch_scale_dev;  /* DEQUANT_TOKEN_CHANNEL: [n] */
+    int32_t relu;            /* enableRelu of the fixpipe stage */
+    int32_t act;             /* 0 none, 1 FasterGelu (DEQUANT_TOKEN_CHANNEL only) */
+    int32_t reserved[4];     /* must be zero */
+} ascb200_gemm_desc;
+
+/* One whole Matmul: what Matmul<...>::IterateAll produces for the object state set by
+ * SetTensorA / SetTensorB / SetBias / SetQuantScalar / SetQuantVector
+ * (include/adv_api/matmul/matmul.h:79-399; impl/adv_api/detail/matmul/matmul_impl.h:119-139),
+ * MX variant with SetTensorScaleA/B (impl/adv_api/detail/matmul/mx_matmul_impl.h:136-173). */
+ASCB200_API int ascb200_gemm(const ascb200_gemm_desc* desc, void* stream);
+
+/* Grouped int8 matmul of the reference's QuantGroupMatmul example kernel
+ * (examples/01_simd_cpp_api/05_best_practices/03_fusion_compute/quant_group_matmul_high_performance/
+ *  quant_group_matmul_custom.asc:252-452): rows of A are split into `groups` consecutive groups by
+ * group_counts_dev[g] (int64 row counts, not a cumulative sum; counts <= 0 are skipped); group g
+ * uses B[g] ([n,k] when trans_b else [k,n]) and ch_scale_dev[g*n .. g*n+n).  `desc->m` is the row
+ * capacity of A / C (>= sum of counts); kind must be S8 and epilogue DEQUANT_TOKEN_CHANNEL. */
+ASCB200_API int ascb200_grouped_gemm(const ascb200_gemm_desc* desc, const int64_t* group_counts_dev, int32_t groups,
+                                     void* stream);
+
+/* ---- SoftMax ------------------------------------------------------------------------------------ */
+
+/* SoftMax<T>(dst, sum, max, src, tiling, shapeInfo) over the last axis of src[m,k]
+ * (include/adv_api/activation/softmax.h:92-109,229-247).  dtype F16 or F32; k*sizeof(T) must be a
+ * multiple of 32 bytes like in the reference (softmax_check_common.h:63-67).  sum/max are fp32:
+ * stats_brc != 0 writes [m, 32/sizeof(float)] with the value repeated over one 32-byte block (the
+ * reference default), stats_brc == 0 writes [m] (SoftmaxMode::SOFTMAX_OUTPUT_WITHOUT_BRC). */
+ASCB200_API int ascb200_softmax(const void* src_dev, void* dst_dev, float* sum_dev, float* max_dev, int32_t m, int32_t k,
+                                int32_t dtype, int32_t stats_brc, void* stream);
+
+/* ---- AscendQuant -------------------------------------------------------------------------------- */
+
+/* AscendQuant per tensor: dst = int8(rint_sat(half(src) * half(scale) + half(offset))), arithmetic in fp16
+ * (include/adv_api/quantization/ascend_quant.h; impl/.../quant/ascend_quant_3510_impl.h:34-120).
+ * src dtype F16 / BF16 / F32; cal_count elements. */
+ASCB200_API int ascb200_quant_per_tensor(const void* src_dev, int8_t* dst_dev, int64_t cal_count, int32_t dtype, float scale,
+                                         float offset, void* stream);
+/* AscendQuant per channel: src [rows, scale_count]; scale_dev (and offset_dev when not NULL) have
+ * scale_count entries of the source dtype; with offset_dev == NULL the scalar `offset` (converted
+ * to the source dtype) is used (impl/.../quant/ascend_quant_3510_impl.h:275-378,553-700). */
+ASCB200_API int ascb200_quant_per_channel(const void* src_dev, int8_t* dst_dev, int32_t rows, int32_t scale_count, int32_t dtype,
+                                          const void* scale_dev, const void* offset_dev, float offset, void* stream);
+
+/* SoftMax immediately followed by per-channel AscendQuant of its output, one pass over src:
+ * writes the fp16 SoftMax result, sum, max and the int8 tensor.  Equivalent to calling
+ * ascb200_softmax then ascb200_quant_per_channel (dtype F16). */
+ASCB200_API int ascb200_softmax_quant(const void* src_dev, void* dst_dev, float* sum_dev, float* max_dev, int8_t* q_dev,
+                                      const void* scale_dev, const void* offset_dev, float offset, int32_t m, int32_t k,
+                                      int32_t stats_brc, void* stream);
+
+/* ---- AscendDequant ------------------------------------------------------------------------------ */
+
+/* AscendDequant<dstT, scaleT>(dst, src, deqScale, DequantParams{m, n, calCount}):
+ * dst[i,j] = dstT(float(src[i,j]) * float(scale[j])), j < cal_count; src rows hold n int32, dst rows
+ * hold n_dst elements (the reference pads dst rows to 32 bytes)
+ * (include/adv_api/quantization/ascend_dequant.h; impl/.../dequant/ascend_dequant_common_impl.h:261-432).
+ * scale_dtype F32 or BF16 for a [cal_count] tensor; scale_dev == NULL selects the scalar overload. */
+ASCB200_API int ascb200_dequant(const int32_t* src_dev, void* dst_dev, int32_t m, int32_t n, int32_t cal_count, int32_t n_dst,
+                                int32_t dst_dtype, const void* scale_dev, int32_t scale_dtype, float scale_scalar, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ASCB200_H */

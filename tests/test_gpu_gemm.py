@@ -1,0 +1,219 @@
+"""GPU parity of the tensor-core Matmul path (fp16 / bf16 / int8 / MXFP4, grouped) against the CPU oracle."""
+import numpy as np
+import pytest
+
+import oracle as orc
+from gpu_util import NP_OUT, bf16_bits, dev, f16_bits, mx_quantize, out_to_f32, quant_params
+
+pytestmark = pytest.mark.gpu
+
+# north-star tolerance for floating-point GEMM outputs
+RTOL, ATOL = 1e-2, 1e-3
+
+
+def run_f16(m, n, k, trans_a=False, trans_b=False, bf16=False, bias=True, c_dtype=0, seed=0, relu=False):
+    ab = dev()
+    rng = np.random.default_rng(seed)
+    conv = bf16_bits if bf16 else f16_bits
+    a = conv(rng.uniform(-1, 1, (k, m) if trans_a else (m, k)).astype(np.float32))
+    b = conv(rng.uniform(-1, 1, (n, k) if trans_b else (k, n)).astype(np.float32))
+    bias_h = rng.uniform(-1, 1, n).astype(np.float32) if bias else None
+    d_c = ab.empty((m, n), NP_OUT[c_dtype])
+    d_c.fill(0xFF)
+    rc = ab.gemm(ab.KIND_BF16 if bf16 else ab.KIND_F16, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, c_dtype, trans_a=trans_a,
+                 trans_b=trans_b, bias=ab.to_dev(bias_h) if bias else None, relu=relu)
+    ab.check(rc, "gemm")
+    ab.sync()
+    got = out_to_f32(d_c.download(), c_dtype)
+    acc = orc.gemm_f16(a, b, bias_h, trans_a=trans_a, trans_b=trans_b, is_bf16=bf16, base_k=64)
+    ref = out_to_f32(orc.cast_f32(acc, c_dtype, relu=relu), c_dtype)
+    err = np.abs(got - ref)
+    assert np.isfinite(got).all(), f"non-finite outputs: {(~np.isfinite(got)).sum()}"
+    assert (err <= ATOL + RTOL * np.abs(ref)).all(), f"max err {err.max()} at {np.unravel_index(err.argmax(), err.shape)}"
+    # far tighter in practice: both sides accumulate in fp32
+    assert err.max() <= 1e-3 * max(1.0, np.abs(ref).max()) * (8 if c_dtype else 1)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 64, 256), (256, 512, 512), (200, 328, 264), (64, 504, 248), (8, 8, 8)])
+@pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, False), (True, True)])
+def test_gemm_f16_layouts(m, n, k, trans_a, trans_b):
+    run_f16(m, n, k, trans_a, trans_b, seed=m + n + k)
+
+
+def test_gemm_f16_baseline_config():
+    """A[512,512] fp16 ND, B[512,1024] fp16 ND, bias[1024] fp32, C fp32 (the reference Matmul example shape family)."""
+    run_f16(512, 1024, 512, False, False, bias=True, c_dtype=0, seed=0xA5C00000)
+
+
+@pytest.mark.parametrize("c_dtype", [0, 1, 2])
+def test_gemm_bf16_outputs(c_dtype):
+    run_f16(384, 640, 320, False, True, bf16=True, c_dtype=c_dtype, seed=5, relu=(c_dtype == 2))
+
+
+def test_gemm_f16_many_tiles_persistent():
+    run_f16(2048, 4352, 256, False, True, bias=False, c_dtype=2, seed=9)  # 16 x 17 tiles > SM count: several tiles per CTA
+
+
+def _i8_inputs(m, n, k, trans_a, trans_b, seed, lo=-127, hi=128):
+    rng = np.random.default_rng(seed)
+    a = rng.integers(lo, hi, (k, m) if trans_a else (m, k)).astype(np.int8)
+    b = rng.integers(lo, hi, (n, k) if trans_b else (k, n)).astype(np.int8)
+    return rng, a, b
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (128, 64, 512), (512, 1024, 1024), (144, 272, 400), (80, 48, 16)])
+@pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, True)])
+def test_gemm_i8_int32_exact(m, n, k, trans_a, trans_b):
+    ab = dev()
+    rng, a, b = _i8_inputs(m, n, k, trans_a, trans_b, m * 7 + n + k)
+    bias = rng.integers(-1000, 1000, n).astype(np.int32)
+    d_c = ab.empty((m, n), np.int32)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.S32, trans_a=trans_a, trans_b=trans_b,
+                     bias=ab.to_dev(bias)))
+    ab.sync()
+    ref = orc.gemm_i8(a, b, bias, trans_a=trans_a, trans_b=trans_b)
+    got = d_c.download()
+    assert (got == ref).all(), f"{(got != ref).sum()} of {ref.size} differ; first {np.argwhere(got != ref)[:5].tolist()}"
+
+
+@pytest.mark.parametrize("mode", ["req8", "req8_scalar_relu", "deqf16", "qs322bf16"])
+def test_gemm_i8_fixpipe_quant(mode):
+    ab = dev()
+    m, n, k = 256, 384, 256
+    rng, a, b = _i8_inputs(m, n, k, False, False, 21, -10, 10)
+    acc = orc.gemm_i8(a, b)
+    scales = rng.uniform(0.005, 0.05, n).astype(np.float32)
+    offsets = rng.integers(-20, 20, n)
+    q = quant_params(scales, offsets)
+    kw = dict(epilogue=ab.EPI_FIXPIPE_QUANT)
+    if mode == "req8":
+        c_dtype, ref = ab.S8, orc.fixpipe_req8(acc, q)
+        kw["quant"] = ab.to_dev(q)
+    elif mode == "req8_scalar_relu":
+        c_dtype, ref = ab.S8, orc.fixpipe_req8(acc, q[3], relu=True)
+        kw.update(quant_scalar=int(q[3]), relu=True)
+    elif mode == "deqf16":
+        c_dtype, ref = ab.F16, orc.fixpipe_deqf16(acc, q)
+        kw["quant"] = ab.to_dev(q)
+    else:
+        c_dtype, ref = ab.BF16, orc.fixpipe_qs322bf16(acc, q)
+        kw["quant"] = ab.to_dev(q)
+    d_c = ab.empty((m, n), NP_OUT[c_dtype])
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, c_dtype, **kw))
+    ab.sync()
+    assert (d_c.download() == ref).all()  # integer accumulators, one fp32 multiply, one rounding: bit exact
+
+
+@pytest.mark.parametrize("m,n,k,c_dtype", [(256, 512, 512, 2), (300, 200, 384, 1), (128, 1376, 1024, 2)])
+def test_gemm_a8w8_token_channel_dequant(m, n, k, c_dtype):
+    """The A8W8 baseline path: bf16((float(acc) * ch_scale[n]) * tok_scale[m]), B stored K-major."""
+    ab = dev()
+    rng, a, b = _i8_inputs(m, n, k, False, True, m + n)
+    tok = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+    ch = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    d_c = ab.empty((m, n), np.uint16)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, c_dtype, epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL,
+                     trans_b=True, tok=ab.to_dev(tok), ch=ab.to_dev(ch)))
+    ab.sync()
+    ref = orc.dequant_tok_ch(orc.gemm_i8(a, b, trans_b=True), tok, ch, c_dtype)
+    assert (d_c.download() == ref).all()
+
+
+@pytest.mark.parametrize("trans_b", [True, False])
+@pytest.mark.parametrize("counts", [[40, 0, 7, 300], [128, 128], [1, 1, 1, 1, 1, 500, 0, 0, 3]])
+def test_grouped_a8w8(counts, trans_b):
+    ab = dev()
+    counts = np.array(counts, np.int64)
+    G, k, n = len(counts), 384, 320
+    m = int(counts.sum())
+    rng = np.random.default_rng(G * 100 + m)
+    x = rng.integers(-127, 128, (m, k)).astype(np.int8)
+    w = rng.integers(-127, 128, (G, n, k) if trans_b else (G, k, n)).astype(np.int8)
+    tok = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+    ch = rng.uniform(1e-3, 1e-2, (G, n)).astype(np.float32)
+    d_c = ab.empty((m, n), np.uint16)
+    d_c.fill(0)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(x), ab.to_dev(w), d_c, ab.BF16, epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL,
+                     trans_b=trans_b, tok=ab.to_dev(tok), ch=ab.to_dev(ch), group_counts=ab.to_dev(counts), groups=G))
+    ab.sync()
+    ref = orc.grouped_i8(x, w, counts, tok, ch, orc.BF16, trans_b=trans_b)
+    assert (d_c.download() == ref).all()
+
+
+def test_grouped_matches_reference_recipe(golden_dir):
+    """The grouped example's own numpy recipe incl. FasterGelu and fp16 output (tests/golden/grouped.npz)."""
+    import os
+    ab = dev()
+    g = np.load(os.path.join(golden_dir, "grouped.npz"))
+    x, w, counts = g["x"], g["w"], g["counts"]
+    m, k = x.shape
+    G, _, n = w.shape
+    d_c = ab.empty((m, n), np.uint16)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(x), ab.to_dev(w), d_c, ab.F16, epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL,
+                     trans_b=False, tok=ab.to_dev(g["tok"]), ch=ab.to_dev(g["scale"]), group_counts=ab.to_dev(counts), groups=G, act=1))
+    ab.sync()
+    got = orc.f16_bits_to_f32(d_c.download())
+    ok = np.isclose(got, g["golden_gelu"].astype(np.float32), rtol=1e-3, atol=1e-3)
+    assert (~ok).mean() <= 1e-4  # the example's acceptance rule (verify_result.py:19-41)
+
+
+def _mx_case(m, n, k, seed):
+    rng = np.random.default_rng(seed)
+    a, sa = mx_quantize(rng.standard_normal((m, k)).astype(np.float32))
+    b, sb = mx_quantize(rng.standard_normal((n, k)).astype(np.float32))
+    return rng, a, sa, b, sb
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (128, 256, 512), (384, 512, 1024), (100, 200, 192), (256, 1024, 2048)])
+def test_gemm_mxfp4_fp32(m, n, k):
+    ab = dev()
+    rng, a, sa, b, sb = _mx_case(m, n, k, m + n + k)
+    d_c = ab.empty((m, n), np.float32)
+    ab.check(ab.gemm(ab.KIND_MXFP4, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.F32, trans_b=True, scale_a=ab.to_dev(sa),
+                     scale_b=ab.to_dev(sb)))
+    ab.sync()
+    got = d_c.download()
+    ref = orc.gemm_mxf4(a, sa, b, sb, base_k=256)
+    err = np.abs(got - ref)
+    print(f"mxfp4 {m}x{n}x{k}: max abs err {err.max():.3e}, max |ref| {np.abs(ref).max():.3e}, ratio {err.max() / np.abs(ref).max():.3e}")
+    assert (err <= ATOL + RTOL * np.abs(ref)).all(), f"max err {err.max()} ref {np.abs(ref).max()}"
+    assert err.max() <= 1e-3 * np.abs(ref).max()  # every product is exact in fp32; only the summation differs
+
+
+def test_gemm_mxfp4_requant_and_bf16():
+    """MXFP4 baseline epilogue: int8 via per-channel VQF322B8_PRE plus the bf16 cast of the same accumulators."""
+    ab = dev()
+    m, n, k = 256, 512, 1024
+    rng, a, sa, b, sb = _mx_case(m, n, k, 77)
+    ref_acc = orc.gemm_mxf4(a, sa, b, sb, base_k=256)
+    sigma = ref_acc.std()
+    scales = (rng.uniform(0.5, 2.0, n) * 40.0 / sigma).astype(np.float32)
+    q = quant_params(scales)
+    d_c, d_c2, d_acc = ab.empty((m, n), np.int8), ab.empty((m, n), np.uint16), ab.empty((m, n), np.float32)
+    args = (ab.KIND_MXFP4, m, n, k, ab.to_dev(a), ab.to_dev(b))
+    kw = dict(trans_b=True, scale_a=ab.to_dev(sa), scale_b=ab.to_dev(sb))
+    ab.check(ab.gemm(*args, d_c, ab.S8, epilogue=ab.EPI_FIXPIPE_QUANT, quant=ab.to_dev(q), c2=d_c2, c2_dtype=ab.BF16, **kw))
+    ab.check(ab.gemm(*args, d_acc, ab.F32, **kw))
+    ab.sync()
+    acc_gpu = d_acc.download()
+    # stage-wise: the epilogue applied to the accumulators the tensor cores produced is bit exact
+    assert (d_c.download() == orc.fixpipe_qf322b8(acc_gpu, q)).all()
+    assert (d_c2.download() == orc.cast_f32(acc_gpu, orc.BF16)).all()
+    # end to end against the all-oracle pipeline: int8 may differ by one step only at rounding boundaries
+    ref_q = orc.fixpipe_qf322b8(ref_acc, q)
+    diff = np.abs(d_c.download().astype(np.int32) - ref_q.astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 1e-3, f"int8 mismatches: {(diff != 0).sum()} of {diff.size}"
+    bf = orc.bf16_bits_to_f32(d_c2.download())
+    assert (np.abs(bf - ref_acc) <= ATOL + RTOL * np.abs(ref_acc)).all()
+
+
+def test_gemm_argument_errors():
+    ab = dev()
+    buf = ab.empty((256, 256), np.int8)
+    out = ab.empty((256, 256), np.float32)
+    assert ab.gemm(ab.KIND_S8, 128, 128, 128, buf, buf, out, ab.F32) == -3                # int32 accumulators cannot be cast to fp32 without a scale
+    assert ab.gemm(ab.KIND_S8, 128, 128, 100, buf, buf, out, ab.S32, trans_b=True) == -2  # K-major rows must be 16-byte multiples
+    assert ab.gemm(ab.KIND_F16, 128, 128, 128, None, buf, out, ab.F32) == -1
+    assert ab.gemm(ab.KIND_MXFP4, 128, 128, 96, buf, buf, out, ab.F32, trans_b=True, scale_a=buf, scale_b=buf) == -1  # K % 64
+    assert ab.gemm(ab.KIND_F16, 0, 128, 128, buf, buf, out, ab.F32) == 0                  # empty problem
+    assert ab.gemm(7, 128, 128, 128, buf, buf, out, ab.F32) == -1

@@ -1,0 +1,168 @@
+"""GPU parity of SoftMax / AscendQuant / AscendDequant against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+import oracle as orc
+from gpu_util import dev, f16_bits, bf16_bits
+
+pytestmark = pytest.mark.gpu
+
+HALF_STEP = 2.0 ** -24  # one subnormal half step
+
+
+def _softmax_case(m, k, dtype, brc, seed, sigma=3.0):
+    ab = dev()
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((m, k)).astype(np.float32) * sigma
+    xin = f16_bits(x) if dtype == ab.F16 else x
+    d_x = ab.to_dev(xin)
+    d_y = ab.empty((m, k), xin.dtype)
+    rep = 8 if brc else 1
+    d_sum, d_max = ab.empty((m, rep), np.float32), ab.empty((m, rep), np.float32)
+    ab.check(ab.softmax(d_x, d_y, d_sum, d_max, m, k, dtype, brc), "softmax")
+    ab.sync()
+    y, s, mx = d_y.download(), d_sum.download(), d_max.download()
+    ry, rmx, rs = orc.softmax(xin, dtype, brc=brc)
+    if not brc:
+        rmx, rs = rmx[:, None], rs[:, None]
+    assert (mx == rmx).all()
+    assert np.allclose(s, rs, rtol=1e-5, atol=0)
+    if dtype == ab.F16:
+        yf, rf = orc.f16_bits_to_f32(y), orc.f16_bits_to_f32(ry)
+        # north-star tolerance: 1e-3 relative; plus one subnormal half step where fp16 itself is coarser
+        assert (np.abs(yf - rf) <= 1e-3 * np.abs(rf) + HALF_STEP).all()
+        assert (y != ry).mean() < 0.02
+    else:
+        assert np.allclose(y, ry, rtol=1e-5, atol=1e-30)
+    return xin, y
+
+
+@pytest.mark.parametrize("m,k", [(1, 16), (7, 48), (33, 256), (64, 2048), (5, 4096), (3, 16384), (2, 65536), (4096, 2048)])
+def test_softmax_f16(m, k):
+    _softmax_case(m, k, 1, False, seed=m * 131 + k)
+
+
+@pytest.mark.parametrize("m,k", [(32, 32), (9, 8), (17, 1024), (6, 8192), (3, 32768)])
+def test_softmax_f32_brc(m, k):
+    _softmax_case(m, k, 0, True, seed=m * 17 + k)
+
+
+def test_softmax_reference_example_edge_rows():
+    """Row of FLT_MIN values (the reference example's first row) and a row with one dominant element."""
+    ab = dev()
+    x = np.random.default_rng(3).uniform(-1, 1, (32, 32)).astype(np.float32)
+    x[0, :] = np.finfo(np.float32).min
+    x[1, :] = -30.0
+    x[1, 5] = 30.0
+    d_x, d_y = ab.to_dev(x), ab.empty((32, 32), np.float32)
+    d_s, d_m = ab.empty((32, 8), np.float32), ab.empty((32, 8), np.float32)
+    ab.check(ab.softmax(d_x, d_y, d_s, d_m, 32, 32, ab.F32, True))
+    ab.sync()
+    ry, rm, rs = orc.softmax(x, orc.F32, brc=True)
+    assert np.allclose(d_y.download(), ry, rtol=1e-5, atol=1e-30)
+    assert (d_m.download() == rm).all()
+
+
+def test_softmax_argument_errors():
+    ab = dev()
+    d = ab.empty((4, 64), np.uint16)
+    s = ab.empty((4,), np.float32)
+    assert ab.softmax(d, d, s, s, 4, 24, ab.F16) == -2      # 48 bytes: not a 32-byte multiple
+    assert ab.softmax(None, d, s, s, 4, 64, ab.F16) == -1
+    assert ab.softmax(d, d, s, s, 4, 64, ab.S8) == -3
+    assert ab.softmax(d, d, s, s, 0, 64, ab.F16) == 0       # empty input
+
+
+@pytest.mark.parametrize("dtype", [1, 2, 0])
+@pytest.mark.parametrize("n", [32, 1024, 8 * 1000 + 32, 1 << 20])
+def test_quant_per_tensor(dtype, n):
+    ab = dev()
+    rng = np.random.default_rng(n + dtype)
+    x = rng.uniform(-4, 4, n).astype(np.float32)
+    x[:8] = [0.05, -0.05, 63.55, -64.45, 1e4, -1e4, 0.3, 0.8]
+    xin = f16_bits(x) if dtype == ab.F16 else bf16_bits(x) if dtype == ab.BF16 else x
+    d_x, d_q = ab.to_dev(xin), ab.empty((n,), np.int8)
+    ab.check(ab.quant_per_tensor(d_x, d_q, n, dtype, 2.0, 0.9))
+    ab.sync()
+    assert (d_q.download() == orc.quant_per_tensor(xin, dtype, 2.0, 0.9)).all()
+
+
+@pytest.mark.parametrize("dtype", [1, 2, 0])
+@pytest.mark.parametrize("rows,k,offset_tensor", [(4, 32, False), (37, 2048, True), (128, 96, True), (3, 40, False)])
+def test_quant_per_channel(dtype, rows, k, offset_tensor):
+    ab = dev()
+    rng = np.random.default_rng(rows * k + dtype)
+    x = rng.uniform(-1, 1, (rows, k)).astype(np.float32)
+    sc = rng.uniform(30, 250, k).astype(np.float32)
+    of = rng.uniform(-3, 3, k).astype(np.float32)
+    conv = (lambda a: f16_bits(a)) if dtype == ab.F16 else (lambda a: bf16_bits(a)) if dtype == ab.BF16 else (lambda a: a)
+    xin, scin, ofin = conv(x), conv(sc), conv(of)
+    d_x, d_s, d_o, d_q = ab.to_dev(xin), ab.to_dev(scin), ab.to_dev(ofin), ab.empty((rows, k), np.int8)
+    ab.check(ab.quant_per_channel(d_x, d_q, rows, k, dtype, d_s, d_o if offset_tensor else None, 0.25))
+    ab.sync()
+    ref = orc.quant_per_channel(xin, dtype, scin, ofin if offset_tensor else 0.25)
+    assert (d_q.download() == ref).all()
+
+
+@pytest.mark.parametrize("dst_dtype", [0, 1, 2])
+@pytest.mark.parametrize("m,n,cal,scale_kind", [(128, 32, 32, "f32"), (33, 256, 200, "bf16"), (5, 40, 40, "scalar"), (7, 24, 10, "f32")])
+def test_dequant(dst_dtype, m, n, cal, scale_kind):
+    ab = dev()
+    rng = np.random.default_rng(m * n + dst_dtype)
+    src = rng.integers(-100000, 100000, (m, n)).astype(np.int32)
+    scale = rng.uniform(-3, 3, cal).astype(np.float32)
+    esz = 4 if dst_dtype == ab.F32 else 2
+    n_dst = -(-n * esz // 32) * 32 // esz
+    d_src = ab.to_dev(src)
+    d_dst = ab.empty((m, n_dst), np.float32 if dst_dtype == ab.F32 else np.uint16)
+    d_dst.fill(0)
+    if scale_kind == "scalar":
+        ab.check(ab.dequant(d_src, d_dst, m, n, cal, n_dst, dst_dtype, None, ab.F32, 0.37))
+        ref = orc.dequant(src, 0.37, dst_dtype, cal_count=cal, n_dst=n_dst)
+    elif scale_kind == "bf16":
+        sb = bf16_bits(scale)
+        ab.check(ab.dequant(d_src, d_dst, m, n, cal, n_dst, dst_dtype, ab.to_dev(sb), ab.BF16, 0.0))
+        ref = orc.dequant(src, sb, dst_dtype, orc.BF16, cal_count=cal, n_dst=n_dst)
+    else:
+        ab.check(ab.dequant(d_src, d_dst, m, n, cal, n_dst, dst_dtype, ab.to_dev(scale), ab.F32, 0.0))
+        ref = orc.dequant(src, scale, dst_dtype, cal_count=cal, n_dst=n_dst)
+    ab.sync()
+    assert (d_dst.download() == ref).all()  # one fp32 multiply and one rounding: bit exact
+
+
+def test_softmax_quant_fused_full_size():
+    """BASELINE config: X[4096,2048] fp16 ~ N(0, 3^2), per-channel int8 quant of the SoftMax output.
+
+    Scales: u ~ U[0.5,2); AscendQuant multiplies by its scale, so the parity-bearing run uses the
+    reciprocal of the dequant scale u/127 (127/u); the literal scale u/127 is checked to give all zeros."""
+    ab = dev()
+    m, k = 4096, 2048
+    rng = np.random.default_rng(0xA5C00001)
+    x = f16_bits(rng.standard_normal((m, k)).astype(np.float32) * 3.0)
+    u = rng.uniform(0.5, 2.0, k).astype(np.float32)
+    d_x = ab.to_dev(x)
+    d_y, d_q = ab.empty((m, k), np.uint16), ab.empty((m, k), np.int8)
+    d_s, d_m = ab.empty((m,), np.float32), ab.empty((m,), np.float32)
+    for scale in (127.0 / u, u / 127.0):
+        sc = f16_bits(scale)
+        d_sc = ab.to_dev(sc)
+        ab.check(ab.softmax_quant(d_x, d_y, d_s, d_m, d_q, d_sc, None, 0.0, m, k))
+        ab.sync()
+        y, q = d_y.download(), d_q.download()
+        ry, rmx, rs = orc.softmax(x, orc.F16)
+        yf, rf = orc.f16_bits_to_f32(y), orc.f16_bits_to_f32(ry)
+        assert (np.abs(yf - rf) <= 1e-3 * np.abs(rf) + HALF_STEP).all()
+        assert (d_m.download() == rmx).all() and np.allclose(d_s.download(), rs, rtol=1e-5)
+        # stage-wise bit exactness: the int8 tensor is exactly AscendQuant of the fp16 tensor the kernel wrote
+        assert (q == orc.quant_per_channel(y, orc.F16, sc, 0.0)).all()
+        # and it agrees with the all-oracle pipeline except where the fp16 softmax value itself differs by one step
+        rq = orc.quant_per_channel(ry, orc.F16, sc, 0.0)
+        assert np.abs(q.astype(np.int32) - rq.astype(np.int32)).max() <= 1
+        assert ((q != rq) & (y == ry)).sum() == 0
+        # unfused pair gives the same bytes as the fused kernel
+        d_y2, d_q2 = ab.empty((m, k), np.uint16), ab.empty((m, k), np.int8)
+        ab.check(ab.softmax(d_x, d_y2, d_s, d_m, m, k, ab.F16))
+        ab.check(ab.quant_per_channel(d_y2, d_q2, m, k, ab.F16, d_sc, None, 0.0))
+        ab.sync()
+        assert (d_y2.download() == y).all() and (d_q2.download() == q).all()
+    assert (q == 0).all()  # literal scale: softmax <= 1 times <= 0.0158 rounds to zero everywhere
