@@ -338,12 +338,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     // x coordinates are counted in tensor-map elements (bytes for int8 and packed fp4)
                     const int kx = KIND == KIND_MXF4 ? k0 / 2 : k0;
                     if (!p.a_mn) {
-                        tma_load_2d(sa, &tmap_a, kx, t.row0, bar);
+                        tma_load_3d(sa, &tmap_a, kx, t.row0, 0, bar);  // every map is rank 3
                     } else {
                         constexpr int MN_PER_BOX = KIND == KIND_F16 ? 64 : 128;
                         constexpr int BOX_BYTES = C::BLOCK_K * ROW_BYTES;
 #pragma unroll
-                        for (int j = 0; j < BLOCK_M / MN_PER_BOX; ++j) tma_load_2d(sa + j * BOX_BYTES, &tmap_a, t.row0 + j * MN_PER_BOX, k0, bar);
+                        for (int j = 0; j < BLOCK_M / MN_PER_BOX; ++j) tma_load_3d(sa + j * BOX_BYTES, &tmap_a, t.row0 + j * MN_PER_BOX, k0, 0, bar);
                     }
                     if (!p.b_mn) {
                         tma_load_3d(sb, &tmap_b, kx, t.n0, t.group, bar);
@@ -641,6 +641,8 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         const long long num_m = grouped ? (m + BLOCK_M - 1) / BLOCK_M + groups : (m + BLOCK_M - 1) / BLOCK_M;
         while (block_n > 64 && (n <= block_n / 2 || num_m * ((n + block_n - 1) / block_n) < st->sm_count)) block_n /= 2;
         if (kind == ASCB200_KIND_MXFP4 && block_n < 128) block_n = 128;
+        // an N-contiguous 8-bit B tile is fetched in boxes of 128 columns (one 128-byte swizzle row)
+        if (kind == ASCB200_KIND_S8 && !d->trans_b && block_n < 128) block_n = 128;
     }
 
     CUtensorMap ta, tb;

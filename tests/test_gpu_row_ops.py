@@ -26,14 +26,15 @@ def _softmax_case(m, k, dtype, brc, seed, sigma=3.0):
     if not brc:
         rmx, rs = rmx[:, None], rs[:, None]
     assert (mx == rmx).all()
-    assert np.allclose(s, rs, rtol=1e-5, atol=0)
+    # the oracle adds k terms one after another in fp32; its own rounding error grows with k
+    assert np.allclose(s, rs, rtol=1e-5 if k <= 4096 else 1e-4, atol=0)
     if dtype == ab.F16:
         yf, rf = orc.f16_bits_to_f32(y), orc.f16_bits_to_f32(ry)
         # north-star tolerance: 1e-3 relative; plus one subnormal half step where fp16 itself is coarser
         assert (np.abs(yf - rf) <= 1e-3 * np.abs(rf) + HALF_STEP).all()
         assert (y != ry).mean() < 0.02
     else:
-        assert np.allclose(y, ry, rtol=1e-5, atol=1e-30)
+        assert np.allclose(y, ry, rtol=1e-5 if k <= 4096 else 1e-4, atol=1e-30)
     return xin, y
 
 
