@@ -1,0 +1,705 @@
+"""Benchmark of the ascb200 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload a8w8|grouped|mxfp4|softmax_quant|fp16] [--impl reference]
+
+One "step" is one pass of the hot path over one batch of seeded synthetic input.  The default
+workload is the A8W8 dense GEMM of the baseline (A[4096,4096] int8, B[11008,4096] int8 K-major,
+int32 accumulation, fused bf16(acc * ch_scale[n] * tok_scale[m]) epilogue), sharded by N-slab
+across ranks with no communication; `value` is the whole-job rate (all ranks' operations divided
+by the slowest rank's device time, CUDA events on the launching stream).
+
+Rank 0 prints ONE JSON line.  At N=1 it also carries, under "others", the same measurement for
+the other baseline configurations (grouped A8W8, MXFP4, SoftMax+AscendQuant, fp16 Matmul).
+
+`--impl reference` times the CPU restatement of the reference arithmetic (oracle/, OpenMP, all host
+threads) on a bounded row sample of the same workload; the reference's own CPU-debug executable
+needs the closed CANN CPU twin and cannot be built.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(ROOT, "asc-devkit_clone_b200"), os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks: NVML samples taken by a thread while the timed region runs
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                bits = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for b, name in self.REASONS.items():
+                    if bits & b:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.002)
+
+    def start(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------
+def dirichlet_counts(groups, total, seed):
+    """Deterministic Dirichlet(1) split of `total` rows: normalised Exp(1) draws, floor, remainder by largest fraction."""
+    e = np.random.default_rng(seed).exponential(1.0, groups)
+    w = e / e.sum() * total
+    c = np.floor(w).astype(np.int64)
+    rem = total - int(c.sum())
+    c[np.argsort(-(w - c))[:rem]] += 1
+    return c
+
+
+def lpt_partition(counts, parts):
+    """Greedy longest-processing-time assignment of groups to ranks by row count."""
+    load = [0] * parts
+    owner = [[] for _ in range(parts)]
+    for g in np.argsort(-counts, kind="stable"):
+        r = int(np.argmin(load))
+        owner[r].append(int(g))
+        load[r] += int(counts[g])
+    return [sorted(o) for o in owner]
+
+
+class Workload:
+    """Holds device buffers for `sets` rotating input/output sets and launches one step."""
+    name = metric = unit = dtype = ""
+    unit_scale = 1e12            # value = units / seconds / unit_scale (1e12: TOPS / TFLOPS, 1e9: GB/s)
+    bound = "tensor"
+    scaling = "strong"
+    kernels_per_step = 1
+    published = None  # (value, note) of a like-for-like number in BASELINE.md
+
+    def units_total(self):       # algorithmic operations (or bytes) of the whole job per step
+        raise NotImplementedError
+
+    def units_rank(self):        # of this rank per step (roofline of the dominant kernel)
+        raise NotImplementedError
+
+    def step(self, i):
+        raise NotImplementedError
+
+    def e2e_step(self, i):
+        raise NotImplementedError
+
+    def peak(self, peaks):
+        raise NotImplementedError
+
+
+class A8W8(Workload):
+    name = "a8w8_gemm_4096x4096x11008_dequant_bf16"
+    metric, unit, dtype = "quant-GEMM throughput (int8, fused per-token x per-channel dequant)", "TOPS", "s8"
+    M, K, N = 4096, 4096, 11008
+
+    def __init__(self, ab, rank, world, sets):
+        self.ab, self.rank, self.world = ab, rank, world
+        assert self.N % world == 0
+        self.n_loc = self.N // world
+        rng = np.random.default_rng(0xA5C00002)
+        self.a_h = rng.integers(-127, 128, (self.M, self.K)).astype(np.int8)
+        self.tok_h = rng.uniform(1e-3, 1e-2, self.M).astype(np.float32)
+        ch = rng.uniform(1e-3, 1e-2, self.N).astype(np.float32)
+        rng_b = np.random.default_rng(0xA5C00002 + 1000 + rank)   # each rank draws its own B slab
+        self.b_h = rng_b.integers(-127, 128, (self.n_loc, self.K)).astype(np.int8)
+        self.ch_h = ch[rank * self.n_loc:(rank + 1) * self.n_loc].copy()
+        self.sets = sets
+        self.a = [ab.to_dev(self.a_h) for _ in range(sets)]
+        self.b = [ab.to_dev(self.b_h) for _ in range(sets)]
+        self.c = [ab.empty((self.M, self.n_loc), np.uint16) for _ in range(sets)]
+        self.tok, self.ch = ab.to_dev(self.tok_h), ab.to_dev(self.ch_h)
+        self.config = {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "shard": f"N-slab x{world}",
+                       "cache": f"{sets} rotating buffer sets ({sets * self.bytes_rank() // 2**20} MiB > L2)"}
+        self.pin = None
+
+    def units_total(self):
+        return 2.0 * self.M * self.K * self.N
+
+    def units_rank(self):
+        return 2.0 * self.M * self.K * self.n_loc
+
+    def bytes_rank(self):
+        return self.M * self.K + self.n_loc * self.K + 2 * self.M * self.n_loc + 4 * (self.M + self.n_loc)
+
+    def peak(self, peaks):
+        return 2.0 * peaks["bf16_tflops"], "TOPS", "2 x measured bf16 cuBLAS burst (int8 runs at twice the bf16 rate)"
+
+    def step(self, i, stream=None):
+        ab, s = self.ab, i % self.sets
+        ab.check(ab.gemm(ab.KIND_S8, self.M, self.n_loc, self.K, self.a[s], self.b[s], self.c[s], ab.BF16,
+                         epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, trans_b=True, tok=self.tok, ch=self.ch, stream=stream))
+
+    def e2e_bytes(self):
+        return self.a_h.nbytes + self.b_h.nbytes + self.tok_h.nbytes + self.ch_h.nbytes, self.M * self.n_loc * 2
+
+    def e2e_setup(self):
+        self.pin = PinnedSet(self.ab, [self.a_h, self.b_h, self.tok_h, self.ch_h], self.M * self.n_loc * 2)
+
+    def e2e_step(self, i, stream):
+        ab, s = self.ab, i % self.sets
+        self.pin.h2d([self.a[s], self.b[s], self.tok, self.ch], stream)
+        self.step(i, stream)
+        self.pin.d2h(self.c[s], stream)
+
+    def cpu_sample(self, orc, rows):
+        t0 = time.perf_counter()
+        acc = orc.gemm_i8(self.a_h[:rows], self.b_h, trans_b=True)
+        orc.dequant_tok_ch(acc, self.tok_h[:rows], self.ch_h, orc.BF16)
+        return time.perf_counter() - t0, 2.0 * rows * self.K * self.n_loc, f"{rows} of {self.M} rows of A x all {self.n_loc} columns"
+
+    def verify(self, orc):
+        """Spot check of set 0 against the oracle: first 32 rows."""
+        got = self.c[0].download()[:32]
+        ref = orc.dequant_tok_ch(orc.gemm_i8(self.a_h[:32], self.b_h, trans_b=True), self.tok_h[:32], self.ch_h, orc.BF16)
+        return bool((got == ref).all())
+
+
+class Grouped(Workload):
+    name = "grouped_a8w8_64groups_M32768_K7168_N2048"
+    metric, unit, dtype = "grouped quant-GEMM throughput (int8, fused dequant)", "TOPS", "s8"
+    G, MTOT, K, N = 64, 32768, 7168, 2048
+
+    def __init__(self, ab, rank, world, sets):
+        self.ab, self.rank, self.world = ab, rank, world
+        counts = dirichlet_counts(self.G, self.MTOT, 0xA5C00003)
+        mine = lpt_partition(counts, world)[rank]
+        self.counts_h = counts[mine].astype(np.int64)
+        self.m_loc = int(self.counts_h.sum())
+        self.g_loc = len(mine)
+        rng = np.random.default_rng(0xA5C00003 + 1000 + rank)
+        self.x_h = rng.integers(-127, 128, (max(self.m_loc, 1), self.K)).astype(np.int8)
+        self.w_h = rng.integers(-127, 128, (self.g_loc, self.N, self.K), dtype=np.int8)
+        self.tok_h = rng.uniform(1e-3, 1e-2, max(self.m_loc, 1)).astype(np.float32)
+        self.ch_h = rng.uniform(1e-3, 1e-2, (self.g_loc, self.N)).astype(np.float32)
+        self.sets = sets
+        self.x = [ab.to_dev(self.x_h) for _ in range(sets)]
+        self.w = [ab.to_dev(self.w_h) for _ in range(1)]           # 0.94 GB of weights already exceed L2
+        self.c = [ab.empty((max(self.m_loc, 1), self.N), np.uint16) for _ in range(sets)]
+        self.tok, self.ch, self.counts = ab.to_dev(self.tok_h), ab.to_dev(self.ch_h), ab.to_dev(self.counts_h)
+        self.config = {"workload": self.name, "groups": self.G, "rows": self.MTOT, "K": self.K, "N": self.N,
+                       "shard": f"groups x{world} (greedy by rows)", "rows_this_rank": self.m_loc,
+                       "cache": "weights of one pass (0.94 GB / ranks) exceed L2"}
+
+    def units_total(self):
+        return 2.0 * self.MTOT * self.K * self.N
+
+    def units_rank(self):
+        return 2.0 * self.m_loc * self.K * self.N
+
+    def peak(self, peaks):
+        return 2.0 * peaks["bf16_tflops"], "TOPS", "2 x measured bf16 cuBLAS burst"
+
+    def step(self, i, stream=None):
+        ab, s = self.ab, i % self.sets
+        ab.check(ab.gemm(ab.KIND_S8, self.m_loc, self.N, self.K, self.x[s], self.w[0], self.c[s], ab.BF16,
+                         epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, trans_b=True, tok=self.tok, ch=self.ch, group_counts=self.counts,
+                         groups=self.g_loc, stream=stream))
+
+    def e2e_bytes(self):
+        return self.x_h.nbytes + self.w_h.nbytes + self.tok_h.nbytes + self.ch_h.nbytes + self.counts_h.nbytes, self.m_loc * self.N * 2
+
+    def e2e_setup(self):
+        self.pin = PinnedSet(self.ab, [self.x_h, self.w_h, self.tok_h, self.ch_h, self.counts_h], self.m_loc * self.N * 2)
+
+    def e2e_step(self, i, stream):
+        s = i % self.sets
+        self.pin.h2d([self.x[s], self.w[0], self.tok, self.ch, self.counts], stream)
+        self.step(i, stream)
+        self.pin.d2h(self.c[s], stream)
+
+    def cpu_sample(self, orc, rows):
+        # the first `rows` rows of every non-empty group
+        take = np.minimum(self.counts_h, rows)
+        starts = np.concatenate([[0], np.cumsum(self.counts_h)[:-1]])
+        idx = np.concatenate([np.arange(s, s + t) for s, t in zip(starts, take)])
+        x, tok = np.ascontiguousarray(self.x_h[idx]), self.tok_h[idx]
+        t0 = time.perf_counter()
+        orc.grouped_i8(x, self.w_h, take, tok, self.ch_h, orc.BF16, trans_b=True)
+        return time.perf_counter() - t0, 2.0 * int(take.sum()) * self.K * self.N, f"first {rows} rows of each of {self.g_loc} groups"
+
+    def verify(self, orc):
+        got = self.c[0].download()
+        take = np.minimum(self.counts_h, 2)
+        starts = np.concatenate([[0], np.cumsum(self.counts_h)[:-1]])
+        idx = np.concatenate([np.arange(s, s + t) for s, t in zip(starts, take)])
+        ref = orc.grouped_i8(np.ascontiguousarray(self.x_h[idx]), self.w_h, take, self.tok_h[idx], self.ch_h, orc.BF16, trans_b=True)
+        return bool((got[idx] == ref).all())
+
+
+class MXFP4(Workload):
+    name = "mxfp4_gemm_8192x8192x8192_requant_int8_bf16"
+    metric, unit, dtype = "quant-GEMM throughput (MXFP4 e2m1 x ue8m0, int8 requant + bf16 out)", "TFLOPS", "fp4_e2m1"
+    M = K = N = 8192
+    kernels_per_step = 3  # two scale re-tiling launches + the GEMM
+    published = (1614.0, "Ascend 950PR basic-API MXFP4 8192^3, bf16 out (BASELINE.md)")
+
+    def __init__(self, ab, rank, world, sets):
+        from gpu_util import mx_quantize, quant_params
+        self.ab, self.rank, self.world = ab, rank, world
+        self.n_loc = self.N // world
+        rng = np.random.default_rng(0xA5C00004)
+        self.a_h, self.sa_h = mx_quantize(rng.standard_normal((self.M, self.K), dtype=np.float32))
+        rng_b = np.random.default_rng(0xA5C00004 + 1000 + rank)
+        self.b_h, self.sb_h = mx_quantize(rng_b.standard_normal((self.n_loc, self.K), dtype=np.float32))
+        # accumulators ~ N(0, K * E[a^2] E[b^2]); quantised unit normals keep E[x^2] ~ 1 -> sigma ~ sqrt(K)
+        scales = (rng.uniform(0.5, 2.0, self.N) * 40.0 / np.sqrt(self.K)).astype(np.float32)
+        self.q_h = quant_params(scales[rank * self.n_loc:(rank + 1) * self.n_loc])
+        self.sets = sets
+        self.a = [ab.to_dev(self.a_h) for _ in range(sets)]
+        self.b = [ab.to_dev(self.b_h) for _ in range(sets)]
+        self.sa, self.sb, self.q = ab.to_dev(self.sa_h), ab.to_dev(self.sb_h), ab.to_dev(self.q_h)
+        self.c = [ab.empty((self.M, self.n_loc), np.int8) for _ in range(sets)]
+        self.c2 = [ab.empty((self.M, self.n_loc), np.uint16) for _ in range(sets)]
+        self.config = {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "shard": f"N-slab x{world}",
+                       "cache": f"{sets} rotating buffer sets"}
+
+    def units_total(self):
+        return 2.0 * self.M * self.K * self.N
+
+    def units_rank(self):
+        return 2.0 * self.M * self.K * self.n_loc
+
+    def peak(self, peaks):
+        return 4.0 * peaks["bf16_tflops"], "TFLOPS", "4 x measured bf16 cuBLAS burst (fp4 runs at four times the bf16 rate)"
+
+    def step(self, i, stream=None):
+        ab, s = self.ab, i % self.sets
+        ab.check(ab.gemm(ab.KIND_MXFP4, self.M, self.n_loc, self.K, self.a[s], self.b[s], self.c[s], ab.S8,
+                         epilogue=ab.EPI_FIXPIPE_QUANT, trans_b=True, scale_a=self.sa, scale_b=self.sb, quant=self.q,
+                         c2=self.c2[s], c2_dtype=ab.BF16, stream=stream))
+
+    def e2e_bytes(self):
+        return (self.a_h.nbytes + self.b_h.nbytes + self.sa_h.nbytes + self.sb_h.nbytes + self.q_h.nbytes,
+                self.M * self.n_loc * 3)
+
+    def e2e_setup(self):
+        self.pin = PinnedSet(self.ab, [self.a_h, self.b_h, self.sa_h, self.sb_h, self.q_h], self.M * self.n_loc * 3)
+
+    def e2e_step(self, i, stream):
+        s = i % self.sets
+        self.pin.h2d([self.a[s], self.b[s], self.sa, self.sb, self.q], stream)
+        self.step(i, stream)
+        self.pin.d2h(self.c[s], stream, 0)
+        self.pin.d2h(self.c2[s], stream, self.M * self.n_loc)
+
+    def cpu_sample(self, orc, rows):
+        t0 = time.perf_counter()
+        acc = orc.gemm_mxf4(self.a_h[:rows], self.sa_h[:rows], self.b_h, self.sb_h, base_k=256)
+        orc.fixpipe_qf322b8(acc, self.q_h)
+        orc.cast_f32(acc, orc.BF16)
+        return time.perf_counter() - t0, 2.0 * rows * self.K * self.n_loc, f"{rows} of {self.M} rows of A x all {self.n_loc} columns"
+
+    def verify(self, orc):
+        acc = orc.gemm_mxf4(self.a_h[:16], self.sa_h[:16], self.b_h, self.sb_h, base_k=256)
+        q = self.c[0].download()[:16]
+        bf = self.c2[0].download()[:16]
+        ref_q = orc.fixpipe_qf322b8(acc, self.q_h)
+        d = np.abs(q.astype(np.int32) - ref_q.astype(np.int32))
+        ok_bf = np.allclose(orc.bf16_bits_to_f32(bf), acc, rtol=1e-2, atol=1e-3)
+        return bool(d.max() <= 1 and (d != 0).mean() < 1e-3 and ok_bf)
+
+
+class SoftmaxQuant(Workload):
+    name = "softmax_ascendquant_4096x2048_fp16_int8"
+    metric, unit, dtype = "SoftMax + AscendQuant row-op bandwidth (fused single pass)", "GB/s", "f16"
+    bound = "hbm"
+    unit_scale = 1e9
+    scaling = "weak"  # rows are independent; every rank runs its own replica of the configuration
+    M, K = 4096, 2048
+
+    def __init__(self, ab, rank, world, sets):
+        from gpu_util import f16_bits
+        self.ab, self.rank, self.world = ab, rank, world
+        rng = np.random.default_rng(0xA5C00001 + rank)
+        self.x_h = f16_bits(rng.standard_normal((self.M, self.K), dtype=np.float32) * 3.0)
+        self.sc_h = f16_bits((127.0 / rng.uniform(0.5, 2.0, self.K)).astype(np.float32))
+        self.sets = sets = max(sets, 8)  # 42 MB per set: rotate 8 sets so no step finds its input in L2
+        self.x = [ab.to_dev(self.x_h) for _ in range(sets)]
+        self.y = [ab.empty((self.M, self.K), np.uint16) for _ in range(sets)]
+        self.q = [ab.empty((self.M, self.K), np.int8) for _ in range(sets)]
+        self.sm, self.mx = ab.empty((self.M,), np.float32), ab.empty((self.M,), np.float32)
+        self.sc = ab.to_dev(self.sc_h)
+        self.config = {"workload": self.name, "M": self.M, "K": self.K, "shard": f"replica per rank x{world}",
+                       "cache": f"{sets} rotating buffer sets ({sets * self.per_step_bytes() // 2**20} MiB > L2)"}
+
+    def per_step_bytes(self):
+        return self.M * self.K * (2 + 2 + 1) + 8 * self.M + 2 * self.K  # X in, Y + Q + sum + max out, scale in
+
+    def units_total(self):
+        return float(self.per_step_bytes()) * self.world
+
+    def units_rank(self):
+        return float(self.per_step_bytes())
+
+    def peak(self, peaks):
+        return peaks["hbm_gbs"], "GB/s", "measured STREAM-style copy"
+
+    def step(self, i, stream=None):
+        ab, s = self.ab, i % self.sets
+        ab.check(ab.softmax_quant(self.x[s], self.y[s], self.sm, self.mx, self.q[s], self.sc, None, 0.0, self.M, self.K, stream=stream))
+
+    def e2e_bytes(self):
+        return self.x_h.nbytes + self.sc_h.nbytes, self.M * self.K * 3 + 8 * self.M
+
+    def e2e_setup(self):
+        self.pin = PinnedSet(self.ab, [self.x_h, self.sc_h], self.M * self.K * 3 + 8 * self.M)
+
+    def e2e_step(self, i, stream):
+        s = i % self.sets
+        self.pin.h2d([self.x[s], self.sc], stream)
+        self.step(i, stream)
+        self.pin.d2h(self.y[s], stream, 0)
+        self.pin.d2h(self.q[s], stream, self.M * self.K * 2)
+        self.pin.d2h(self.sm, stream, self.M * self.K * 3)
+        self.pin.d2h(self.mx, stream, self.M * self.K * 3 + 4 * self.M)
+
+    def cpu_sample(self, orc, rows):
+        rows = min(rows * 16, self.M)
+        t0 = time.perf_counter()
+        y, _, _ = orc.softmax(self.x_h[:rows], orc.F16)
+        orc.quant_per_channel(y, orc.F16, self.sc_h, 0.0)
+        # the CPU path is the unfused pair, counted with the same algorithmic bytes as the fused kernel
+        return time.perf_counter() - t0, rows * self.K * 5.0, f"{rows} of {self.M} rows"
+
+    def verify(self, orc):
+        y, q = self.y[0].download()[:64], self.q[0].download()[:64]
+        ry, _, _ = orc.softmax(self.x_h[:64], orc.F16)
+        yf, rf = orc.f16_bits_to_f32(y), orc.f16_bits_to_f32(ry)
+        return bool((np.abs(yf - rf) <= 1e-3 * np.abs(rf) + 2.0 ** -24).all() and (q == orc.quant_per_channel(y, orc.F16, self.sc_h, 0.0)).all())
+
+
+class FP16(Workload):
+    name = "matmul_fp16_512x512x1024_bias_fp32"
+    metric, unit, dtype = "adv_api Matmul fp16 -> fp32 with bias", "TFLOPS", "f16"
+    scaling = "weak"  # too small to shard: replicas only
+    M, K, N = 512, 512, 1024
+
+    def __init__(self, ab, rank, world, sets):
+        from gpu_util import f16_bits
+        self.ab, self.rank, self.world = ab, rank, world
+        rng = np.random.default_rng(0xA5C00000)
+        self.a_h = f16_bits(rng.uniform(-1, 1, (self.M, self.K)).astype(np.float32))
+        self.b_h = f16_bits(rng.uniform(-1, 1, (self.K, self.N)).astype(np.float32))
+        self.bias_h = rng.uniform(-1, 1, self.N).astype(np.float32)
+        self.sets = sets = 48  # 3.7 MB per set: 48 sets = 176 MB > L2
+        self.a = [ab.to_dev(self.a_h) for _ in range(sets)]
+        self.b = [ab.to_dev(self.b_h) for _ in range(sets)]
+        self.c = [ab.empty((self.M, self.N), np.float32) for _ in range(sets)]
+        self.bias = ab.to_dev(self.bias_h)
+        self.config = {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "shard": f"replica per rank x{world}",
+                       "cache": f"{sets} rotating buffer sets (176 MiB > L2)", "note": "0.54 GFLOP: launch-latency bound"}
+
+    def units_total(self):
+        return 2.0 * self.M * self.K * self.N * self.world
+
+    def units_rank(self):
+        return 2.0 * self.M * self.K * self.N
+
+    def peak(self, peaks):
+        return peaks["bf16_tflops"], "TFLOPS", "measured bf16 cuBLAS burst"
+
+    def step(self, i, stream=None):
+        ab, s = self.ab, i % self.sets
+        ab.check(ab.gemm(ab.KIND_F16, self.M, self.N, self.K, self.a[s], self.b[s], self.c[s], ab.F32, bias=self.bias, stream=stream))
+
+    def e2e_bytes(self):
+        return self.a_h.nbytes + self.b_h.nbytes + self.bias_h.nbytes, self.M * self.N * 4
+
+    def e2e_setup(self):
+        self.pin = PinnedSet(self.ab, [self.a_h, self.b_h, self.bias_h], self.M * self.N * 4)
+
+    def e2e_step(self, i, stream):
+        s = i % self.sets
+        self.pin.h2d([self.a[s], self.b[s], self.bias], stream)
+        self.step(i, stream)
+        self.pin.d2h(self.c[s], stream)
+
+    def cpu_sample(self, orc, rows):
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 2.0:
+            orc.gemm_f16(self.a_h, self.b_h, self.bias_h, base_k=64)
+            reps += 1
+        return time.perf_counter() - t0, reps * 2.0 * self.M * self.K * self.N, f"whole problem x{reps}"
+
+    def verify(self, orc):
+        ref = orc.gemm_f16(self.a_h, self.b_h, self.bias_h, base_k=64)
+        return bool(np.allclose(self.c[0].download(), ref, rtol=1e-2, atol=1e-3))
+
+
+WORKLOADS = {"a8w8": A8W8, "grouped": Grouped, "mxfp4": MXFP4, "softmax_quant": SoftmaxQuant, "fp16": FP16}
+
+
+class PinnedSet:
+    """Pinned host copies of one step's inputs and a pinned landing buffer for its outputs."""
+
+    def __init__(self, ab, arrays, out_bytes):
+        import ctypes as C
+        self.ab, self.C = ab, C
+        self.src = []
+        for a in arrays:
+            p = C.c_void_p()
+            ab.check(ab.lib().ascb200_malloc_host(C.byref(p), max(a.nbytes, 1)))
+            C.memmove(p.value, a.ctypes.data, a.nbytes)
+            self.src.append((p.value, a.nbytes))
+        p = C.c_void_p()
+        ab.check(ab.lib().ascb200_malloc_host(C.byref(p), max(out_bytes, 1)))
+        self.out, self.out_bytes = p.value, out_bytes
+
+    def h2d(self, dev_bufs, stream):
+        for (p, n), d in zip(self.src, dev_bufs):
+            self.ab.check(self.ab.lib().ascb200_memcpy_h2d(d.ptr, p, n, stream))
+
+    def d2h(self, dev_buf, stream, offset=0):
+        n = min(dev_buf.nbytes, self.out_bytes - offset)
+        self.ab.check(self.ab.lib().ascb200_memcpy_d2h(self.out + offset, dev_buf.ptr, n, stream))
+
+
+# ------------------------------------------------------------------------------------------------
+# measurement
+# ------------------------------------------------------------------------------------------------
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+class Comm:
+    """torch.distributed (NCCL) used only for the barrier and the max over ranks of the measured time."""
+
+    def __init__(self, world, local_rank):
+        self.world = world
+        self.torch = None
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            self.torch, self.dist = torch, dist
+
+    def barrier(self):
+        if self.torch:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def max(self, v):
+        if not self.torch:
+            return v
+        t = self.torch.tensor([v], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def close(self):
+        if self.torch:
+            self.dist.destroy_process_group()
+
+
+def time_steps(ab, wl, comm, steps, warmup, stream, e2e=False):
+    fn = (lambda i: wl.e2e_step(i, stream)) if e2e else (lambda i: wl.step(i, stream))
+    for i in range(warmup):
+        fn(i)
+    ab.sync(stream)
+    comm.barrier()
+    timer = ab.Timer(stream)
+    timer.start()
+    for i in range(steps):
+        fn(warmup + i)
+    ms = timer.stop_ms()
+    ab.sync(stream)
+    comm.barrier()
+    return comm.max(ms)
+
+
+def cpu_baseline(wl, target_s):
+    import oracle as orc
+    rows = 2
+    t, units, what = wl.cpu_sample(orc, rows)
+    # grow the sample until it takes target_s (bounded), keeping the last measurement
+    while t < target_s / 3 and rows < 4096:
+        rows = min(4096, max(rows * 2, int(rows * target_s / max(t, 1e-3) * 0.7)))
+        t, units, what = wl.cpu_sample(orc, rows)
+        if "whole problem" in what:
+            break
+    return {"value": units / t / wl.unit_scale, "unit": wl.unit, "cores": orc.num_threads(), "kind": "port", "sample": what,
+            "seconds": round(t, 3)}
+
+
+def measure(ab, cls, comm, rank, world, args, peaks, with_cpu, clock_index):
+    stream_p = __import__("ctypes").c_void_p()
+    ab.check(ab.lib().ascb200_stream_create(__import__("ctypes").byref(stream_p)))
+    stream = stream_p.value
+    wl = cls(ab, rank, world, sets=2)
+    # untimed check that the configuration computes the right thing
+    wl.step(0, stream)
+    ab.sync(stream)
+    import oracle as orc
+    verified = wl.verify(orc)
+
+    sampler = ClockSampler(clock_index)
+    # keep the GPU busy for a moment so the clock samples describe the loaded state
+    t_end = time.time() + 0.3
+    sampler.start()
+    i = 0
+    while time.time() < t_end:
+        wl.step(i, stream)
+        i += 1
+        if i % 16 == 0:
+            ab.sync(stream)
+    ms = time_steps(ab, wl, comm, args.steps, max(args.warmup, 3), stream)
+    clocks = sampler.stop()
+
+    e2e_steps = max(3, min(args.steps, 20))
+    bi, bo = wl.e2e_bytes()
+    if args.kernel_only:
+        ms_e2e, with_cpu = float("nan"), False
+    else:
+        wl.e2e_setup()
+        ms_e2e = time_steps(ab, wl, comm, e2e_steps, 3, stream, e2e=True)
+
+    per_step_s = ms / 1e3 / args.steps
+    value = wl.units_total() / per_step_s / wl.unit_scale
+    achieved = wl.units_rank() / per_step_s / wl.unit_scale
+    peak, punit, pnote = wl.peak(peaks)
+    line = {
+        "metric": wl.metric, "value": round(value, 3), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 6), "higher_is_better": True, "scaling": wl.scaling,
+        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
+        "roofline": {"bound": wl.bound, "achieved": round(achieved, 3), "peak": round(peak, 1), "unit": punit,
+                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": f"{peaks['source']}: {pnote}"},
+        "e2e": {"value": round(wl.units_total() / (ms_e2e / 1e3 / e2e_steps) / wl.unit_scale, 4), "unit": wl.unit, "h2d_bytes_per_step": int(bi),
+                "d2h_bytes_per_step": int(bo), "steps": e2e_steps},
+        "gpu_launches": args.steps * wl.kernels_per_step, "clocks": clocks, "parity_spot_check": verified,
+    }
+    if wl.published:
+        line["vs_published_other_hw"] = {"ratio": round(value / wl.published[0], 3), "what": wl.published[1]}
+    if with_cpu:
+        line["cpu_baseline"] = cpu_baseline(wl, 10.0)
+    ab.lib().ascb200_stream_destroy(stream)
+    return line
+
+
+def run_reference_arm(args, rank, world):
+    """CPU restatement of the reference arithmetic, all host threads, bounded sample per step."""
+    if rank != 0:
+        return
+    import oracle as orc
+
+    class HostOnly:
+        """Stands in for the device binding: the reference arm allocates nothing on a GPU."""
+
+        @staticmethod
+        def to_dev(a):
+            return None
+
+        @staticmethod
+        def empty(shape, dtype):
+            return None
+
+    wl = WORKLOADS[args.workload](HostOnly, 0, 1, sets=1)
+    rows = 2
+    t, units, what = wl.cpu_sample(orc, rows)
+    while t < 0.7 and rows < 4096 and "whole problem" not in what:   # ~2 s per step
+        rows = min(4096, max(rows * 2, int(rows * 2.0 / max(t, 1e-3) * 0.7)))
+        t, units, what = wl.cpu_sample(orc, rows)
+    for _ in range(min(args.warmup, 1)):
+        wl.cpu_sample(orc, rows)
+    tot_t = tot_u = 0.0
+    for _ in range(args.steps):
+        t, units, what = wl.cpu_sample(orc, rows)
+        tot_t += t
+        tot_u += units
+    value = tot_u / tot_t / wl.unit_scale
+    line = {
+        "impl": "reference", "metric": wl.metric, "value": round(value, 6), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(tot_t / args.steps * 1e3, 3), "higher_is_better": True, "scaling": wl.scaling,
+        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
+        "cpu_baseline": {"value": round(value, 6), "unit": wl.unit, "cores": orc.num_threads(), "kind": "port", "sample": what + " per step"},
+        "e2e": {"value": round(value, 6), "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU restatement of the reference arithmetic (oracle/asc_oracle.c, OpenMP); the reference's CPU-debug build needs the closed CANN CPU twin",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="a8w8", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ascb200", choices=["ascb200", "reference"])
+    ap.add_argument("--no-others", action="store_true", help="skip the other baseline configurations at N=1")
+    ap.add_argument("--kernel-only", action="store_true", help="time the device-resident step only (no e2e, no CPU baseline): profiling runs")
+    args = ap.parse_args()
+    rank, local_rank, world = dist_env()
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import ascb200 as ab
+    comm = Comm(world, local_rank)
+    ab.init(local_rank)
+    peaks = measured_peaks()
+    line = measure(ab, WORKLOADS[args.workload], comm, rank, world, args, peaks, with_cpu=(world == 1 and rank == 0),
+                   clock_index=local_rank)
+    if world == 1 and not args.no_others and not args.kernel_only:
+        others = []
+        for name, cls in WORKLOADS.items():
+            if name == args.workload:
+                continue
+            sub = argparse.Namespace(**vars(args))
+            sub.steps = min(args.steps, 50)
+            o = measure(ab, cls, comm, rank, world, sub, peaks, with_cpu=True, clock_index=local_rank)
+            others.append({k: o[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "config", "roofline", "e2e", "cpu_baseline",
+                                             "clocks", "parity_spot_check", "gpu_launches") if k in o})
+        line["others"] = others
+    comm.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

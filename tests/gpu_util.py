@@ -44,27 +44,25 @@ def out_to_f32(bits, dtype):
 NP_OUT = {ab.F32: np.float32, ab.F16: np.uint16, ab.BF16: np.uint16, ab.S8: np.int8, ab.S32: np.int32}
 
 
-def mx_quantize(x):
+def mx_quantize(x, chunk=512):
     """fp32 [R,K] -> (packed e2m1 bytes [R,K/2], e8m0 scales [R,K/32]): per 32-element block
     e = floor(log2(amax)) - 2, scale byte = clamp(e+127, 0, 254), elements rounded to nearest
-    (ties to even) on the e2m1 grid with saturation at +-6; even index in the low nibble."""
+    (ties to the even code) on the e2m1 grid {0,.5,1,1.5,2,3,4,6} with saturation at +-6; even
+    index in the low nibble.  (An OCP-MX style quantiser; the reference generator only draws random
+    operands and scale bytes 127..129.)"""
     R, K = x.shape
-    blk = x.reshape(R, K // 32, 32).astype(np.float32)
-    amax = np.abs(blk).max(axis=2)
-    e = np.where(amax > 0, np.floor(np.log2(np.maximum(amax, 1e-38))) - 2, -127).astype(np.int32)
-    sb = np.clip(e + 127, 0, 254).astype(np.uint8)
-    scaled = blk / np.exp2(sb.astype(np.float32) - 127)[:, :, None]
-    grid = np.array([0, 0.5, 1, 1.5, 2, 3, 4, 6], np.float32)
-    mag = np.minimum(np.abs(scaled), 6.0)
-    # nearest grid point, ties to the even code
-    d = np.abs(mag[..., None] - grid)
-    idx = d.argmin(axis=-1)
-    lo = np.clip(idx - 1, 0, 7)
-    tie_lo = (np.abs(mag - grid[lo]) == np.abs(mag - grid[idx])) & (lo != idx)
-    idx = np.where(tie_lo & (idx % 2 == 1), lo, idx)
-    hi = np.clip(idx + 1, 0, 7)
-    tie_hi = (np.abs(mag - grid[hi]) == np.abs(mag - grid[idx])) & (hi != idx)
-    idx = np.where(tie_hi & (idx % 2 == 1), hi, idx)
-    code = (idx | ((scaled < 0) << 3)).astype(np.uint8).reshape(R, K)
-    packed = (code[:, 0::2] | (code[:, 1::2] << 4)).astype(np.uint8)
+    packed = np.empty((R, K // 2), np.uint8)
+    sb = np.empty((R, K // 32), np.uint8)
+    for r0 in range(0, R, chunk):
+        blk = x[r0:r0 + chunk].reshape(-1, K // 32, 32).astype(np.float32)
+        amax = np.abs(blk).max(axis=2)
+        e = np.where(amax > 0, np.floor(np.log2(np.maximum(amax, 1e-38))) - 2, -127).astype(np.int32)
+        s = np.clip(e + 127, 0, 254).astype(np.uint8)
+        scaled = blk / np.exp2(s.astype(np.float32) - 127)[:, :, None]
+        mag = np.abs(scaled)
+        # midpoints of the grid; a tie goes to the neighbour with the even code
+        idx = ((mag > 0.25).astype(np.uint8) + (mag >= 0.75) + (mag > 1.25) + (mag >= 1.75) + (mag > 2.5) + (mag >= 3.5) + (mag > 5.0))
+        code = (idx | ((scaled < 0).astype(np.uint8) << 3)).astype(np.uint8).reshape(-1, K)
+        packed[r0:r0 + chunk] = code[:, 0::2] | (code[:, 1::2] << 4)
+        sb[r0:r0 + chunk] = s
     return packed, sb
