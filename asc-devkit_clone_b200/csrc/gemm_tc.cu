@@ -5,8 +5,9 @@
 //   warp 1    MMA issuer: one thread issues tcgen05.mma (kind::f16 / kind::i8 / kind::mxf4.block_scale),
 //             accumulators live in TMEM
 //   warp 2    TMEM allocation / release
-//   warps 4-7 epilogue: tcgen05.ld TMEM -> registers, fused fixpipe stage (bias, cast, dequant,
-//             requant, per-token x per-channel scaling), vector stores to global memory
+//   warps 4-11 epilogue: tcgen05.ld TMEM -> registers, fused fixpipe stage (bias, cast, dequant,
+//             requant, per-token x per-channel scaling), vector stores to global memory; two warps
+//             per TMEM lane quadrant, each draining half of the tile's columns
 //
 // A CTA computes 128 x BLOCK_N output tiles; with two accumulator stages in TMEM the epilogue of
 // tile i overlaps the main loop of tile i+1.  Tiles are visited M-fastest so that concurrently
@@ -24,7 +25,8 @@ using namespace tc;
 constexpr int BLOCK_M = 128;
 constexpr int ROW_BYTES = 128;          // one swizzle row: 64 x 16-bit, 128 x 8-bit, 256 x 4-bit along the contiguous axis
 constexpr int A_TILE_BYTES = BLOCK_M * ROW_BYTES;
-constexpr int NUM_THREADS = 256;
+constexpr int NUM_THREADS = 384;        // 4 control warps + 8 epilogue warps
+constexpr int NUM_EPI_WARPS = 8;
 constexpr int MAX_GROUPS = 1024;
 constexpr int SF_CHUNK_BYTES = 512;     // scale factors of 128 rows x 4 K-blocks (of 32 elements)
 
@@ -43,6 +45,9 @@ struct EpiParams {
     const float* ch;
     const unsigned long long* quant;
     unsigned long long quant_scalar;
+#ifdef ASCB200_PROBE
+    int probe;
+#endif
 };
 
 struct GemmParams {
@@ -56,6 +61,9 @@ struct GemmParams {
     int sf_kc;               // 512-byte chunks per 128-row block in sfa / sfb
     uint32_t idesc;
     uint32_t* status;
+#ifdef ASCB200_PROBE
+    int probe;               // experiment switches: 1 skip TMA, 2 skip MMA, 4 skip epilogue math and stores
+#endif
     EpiParams epi;
 };
 
@@ -146,127 +154,211 @@ __device__ __forceinline__ float faster_gelu(float x)
     return x * __expf(0.851f * (x - ax)) / (1.0f + __expf(-1.702f * ax));
 }
 
-template <typename T4>
-__device__ __forceinline__ void st_v4(void* p, T4 v) { *reinterpret_cast<T4*>(p) = v; }
+__device__ __forceinline__ void st_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    *reinterpret_cast<uint4*>(p) = make_uint4(a, b, c, d);
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi)
+{
+    // round to nearest even; overflow saturates to +-65504 (NaN is kept)
+    lo = (lo != lo) ? lo : fminf(fmaxf(lo, -65504.0f), 65504.0f);
+    hi = (hi != hi) ? hi : fminf(fmaxf(hi, -65504.0f), 65504.0f);
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
 
-// Stores 32 consecutive outputs of one row.  f: values for F32/F16/BF16; qi: values for S8/S32.
-__device__ __forceinline__ void store32(void* base, long long ld, int dtype, int vec, int row, int col0, int ncols, const float* f,
-                                        const int* qi)
+// Stores 32 consecutive outputs of one row; DT is the element type of the destination.
+// f: values for F32/F16/BF16, qi: values for S8/S32.
+template <int DT>
+__device__ __forceinline__ void store_row32(void* base, long long ld, int vec, int row, int col0, int ncols, const float (&f)[32],
+                                            const int (&qi)[32])
 {
     const size_t off = static_cast<size_t>(row) * static_cast<size_t>(ld) + col0;
-    if (dtype == OUT_F32 || dtype == OUT_S32) {
+    if constexpr (DT == OUT_F32 || DT == OUT_S32) {
+        uint32_t w[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) w[j] = DT == OUT_F32 ? __float_as_uint(f[j]) : static_cast<uint32_t>(qi[j]);
         uint32_t* out = static_cast<uint32_t*>(base) + off;
         if (vec && ncols == 32) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                uint4 v;
-                if (dtype == OUT_F32) v = make_uint4(__float_as_uint(f[4 * j]), __float_as_uint(f[4 * j + 1]), __float_as_uint(f[4 * j + 2]), __float_as_uint(f[4 * j + 3]));
-                else v = make_uint4(qi[4 * j], qi[4 * j + 1], qi[4 * j + 2], qi[4 * j + 3]);
-                st_v4(out + 4 * j, v);
-            }
+            for (int j = 0; j < 8; ++j) st_v4(out + 4 * j, w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
         } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-                if (j < ncols) out[j] = dtype == OUT_F32 ? __float_as_uint(f[j]) : static_cast<uint32_t>(qi[j]);
+                if (j < ncols) out[j] = w[j];
         }
-    } else if (dtype == OUT_F16 || dtype == OUT_BF16) {
-        uint16_t h[32];
+    } else if constexpr (DT == OUT_F16 || DT == OUT_BF16) {
+        uint32_t w[16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-            h[j] = dtype == OUT_F16 ? __half_as_ushort(f32_to_f16_sat(f[j])) : __bfloat16_as_ushort(f32_to_bf16(f[j]));
+        for (int j = 0; j < 16; ++j) w[j] = DT == OUT_F16 ? pack_f16x2_sat(f[2 * j], f[2 * j + 1]) : pack_bf16x2(f[2 * j], f[2 * j + 1]);
         uint16_t* out = static_cast<uint16_t*>(base) + off;
         if (vec && ncols == 32) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint4 v;
-                v.x = h[8 * j] | (static_cast<uint32_t>(h[8 * j + 1]) << 16);
-                v.y = h[8 * j + 2] | (static_cast<uint32_t>(h[8 * j + 3]) << 16);
-                v.z = h[8 * j + 4] | (static_cast<uint32_t>(h[8 * j + 5]) << 16);
-                v.w = h[8 * j + 6] | (static_cast<uint32_t>(h[8 * j + 7]) << 16);
-                st_v4(out + 8 * j, v);
-            }
+            for (int j = 0; j < 4; ++j) st_v4(out + 8 * j, w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
         } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-                if (j < ncols) out[j] = h[j];
+                if (j < ncols) out[j] = static_cast<uint16_t>(w[j >> 1] >> (16 * (j & 1)));
         }
     } else {  // OUT_S8
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            w[j] = (qi[4 * j] & 0xFF) | ((qi[4 * j + 1] & 0xFF) << 8) | ((qi[4 * j + 2] & 0xFF) << 16) | (static_cast<uint32_t>(qi[4 * j + 3]) << 24);
         int8_t* out = static_cast<int8_t*>(base) + off;
         if (vec && ncols == 32) {
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                uint32_t w[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    w[q] = (qi[16 * j + 4 * q] & 0xFF) | ((qi[16 * j + 4 * q + 1] & 0xFF) << 8) | ((qi[16 * j + 4 * q + 2] & 0xFF) << 16) |
-                           (static_cast<uint32_t>(qi[16 * j + 4 * q + 3] & 0xFF) << 24);
-                st_v4(out + 16 * j, make_uint4(w[0], w[1], w[2], w[3]));
-            }
+            st_v4(out, w[0], w[1], w[2], w[3]);
+            st_v4(out + 16, w[4], w[5], w[6], w[7]);
         } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-                if (j < ncols) out[j] = static_cast<int8_t>(qi[j]);
+                if (j < ncols) out[j] = static_cast<int8_t>(w[j >> 2] >> (8 * (j & 3)));
         }
     }
 }
 
-// Applies the fixpipe stage to 32 accumulators r[] of output row `row`, columns col0 .. col0+ncols.
-// chan0: index of column col0 in the per-channel arrays (bias, ch scale, quant parameters).
-template <bool ACC_INT>
+// 32 per-channel fp32 parameters starting at p[0]: eight 128-bit loads when aligned.
+__device__ __forceinline__ void load_params32(const float* p, int ncols, float (&out)[32])
+{
+    if (ncols == 32 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(p) + j);
+            out[4 * j] = v.x;
+            out[4 * j + 1] = v.y;
+            out[4 * j + 2] = v.z;
+            out[4 * j + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) out[j] = j < ncols ? __ldg(p + j) : 0.0f;
+    }
+}
+
+// The fixpipe stage for 32 accumulators r[] of output row `row`, columns col0 .. col0+ncols.
+// MODE / DT are compile-time so that each combination is a short straight-line sequence.
+// chan0: index of column col0 in bias / quant; ch_off: index in the per-channel scale array.
+template <bool ACC_INT, int MODE, int DT>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const EpiParams& e, int row, int col0, int ncols, size_t chan0,
                                                size_t ch_off, float tok)
 {
     float f[32];
     int qi[32];
     if constexpr (ACC_INT) {
-        const int* bias = static_cast<const int*>(e.bias);
+        if (e.bias) {
+            const int* bias = static_cast<const int*>(e.bias) + chan0;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            int a = static_cast<int>(r[j]);
-            if (bias && j < ncols) a += bias[chan0 + j];
-            qi[j] = a;
-            f[j] = static_cast<float>(a);
+            for (int j = 0; j < 32; ++j) qi[j] = static_cast<int>(r[j]) + (j < ncols ? __ldg(bias + j) : 0);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) qi[j] = static_cast<int>(r[j]);
+        }
+        if constexpr (MODE != ASCB200_EPI_CAST) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = static_cast<float>(qi[j]);
         }
     } else {
-        const float* bias = static_cast<const float*>(e.bias);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            float a = __uint_as_float(r[j]);
-            if (bias && j < ncols) a = __fadd_rn(a, bias[chan0 + j]);
-            f[j] = a;
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+        if (e.bias) {
+            float b[32];
+            load_params32(static_cast<const float*>(e.bias) + chan0, ncols, b);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = __fadd_rn(f[j], b[j]);
         }
-        if (e.c2) store32(e.c2, e.ldc2, e.c2_dtype, e.vec_c2, row, col0, ncols, f, qi);
+        if (e.c2) {
+            if (e.c2_dtype == OUT_BF16) store_row32<OUT_BF16>(e.c2, e.ldc2, e.vec_c2, row, col0, ncols, f, qi);
+            else if (e.c2_dtype == OUT_F16) store_row32<OUT_F16>(e.c2, e.ldc2, e.vec_c2, row, col0, ncols, f, qi);
+            else store_row32<OUT_F32>(e.c2, e.ldc2, e.vec_c2, row, col0, ncols, f, qi);
+        }
     }
-    if (e.mode == ASCB200_EPI_CAST) {
+    if constexpr (MODE == ASCB200_EPI_CAST) {
         if (e.relu) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                f[j] = fmaxf(f[j], 0.0f);
-                qi[j] = max(qi[j], 0);
+                if constexpr (ACC_INT) qi[j] = max(qi[j], 0);
+                else f[j] = fmaxf(f[j], 0.0f);
             }
         }
-    } else if (e.mode == ASCB200_EPI_FIXPIPE_QUANT) {
+    } else if constexpr (MODE == ASCB200_EPI_FIXPIPE_QUANT) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-            const unsigned long long q = (e.quant && j < ncols) ? e.quant[chan0 + j] : e.quant_scalar;
-            float v = (f[j] >= 0.0f || !e.relu) ? __fmul_rn(f[j], quant_alpha(q)) : 0.0f;
-            if (e.c_dtype == OUT_S8) {
+            const unsigned long long q = (e.quant && j < ncols) ? __ldg(e.quant + chan0 + j) : e.quant_scalar;
+            const float v = (f[j] >= 0.0f || !e.relu) ? __fmul_rn(f[j], quant_alpha(q)) : 0.0f;
+            if constexpr (DT == OUT_S8) {
                 // REQ8 / QF322B8_PRE: clip to 9 bits, round, add the offset, clip to int8
-                float t = rintf(fminf(fmaxf(v, -256.0f), 255.0f)) + quant_offset(q);
-                qi[j] = (v != v) ? 0 : static_cast<int>(rintf(fminf(fmaxf(t, -128.0f), 127.0f)));
+                const float t = rintf(fminf(fmaxf(v, -256.0f), 255.0f)) + quant_offset(q);
+                qi[j] = (v != v) ? 0 : __float2int_rn(fminf(fmaxf(t, -128.0f), 127.0f));
             }
             f[j] = v;
         }
     } else {  // ASCB200_EPI_DEQUANT_TOKEN_CHANNEL
+        float s[32];
+        load_params32(e.ch + ch_off, ncols, s);
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-            const float s = j < ncols ? e.ch[ch_off + j] : 0.0f;
-            float v = __fmul_rn(__fmul_rn(f[j], s), tok);
+            float v = __fmul_rn(__fmul_rn(f[j], s[j]), tok);
             if (e.act == 1) v = faster_gelu(v);
             f[j] = v;
         }
     }
-    store32(e.c, e.ldc, e.c_dtype, e.vec_c, row, col0, ncols, f, qi);
+    store_row32<DT>(e.c, e.ldc, e.vec_c, row, col0, ncols, f, qi);
+}
+
+// Drains this warp's share of one accumulator tile: TMEM lanes of `quad`, chunks [chunk0, chunk1).
+template <bool ACC_INT, int MODE, int DT, int BLOCK_N>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInfo& t, uint32_t t_addr, int quad, int lane, int chunk0, int chunk1)
+{
+    const int row = t.row0 + quad * 32 + lane;
+    const bool row_ok = row < t.row_end;
+    const float tok = (MODE == ASCB200_EPI_DEQUANT_TOKEN_CHANNEL && row_ok && p.epi.tok) ? __ldg(p.epi.tok + row) : 1.0f;
+#pragma unroll 1
+    for (int c = chunk0; c < chunk1; ++c) {
+        const int col0 = t.n0 + c * 32;
+        if (col0 >= p.n) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+#ifdef ASCB200_PROBE
+        if (p.probe & 4) continue;
+#endif
+        if (row_ok)
+            epilogue_chunk<ACC_INT, MODE, DT>(r, p.epi, row, col0, min(32, p.n - col0), static_cast<size_t>(col0),
+                                              static_cast<size_t>(t.group) * p.n + col0, tok);
+    }
+}
+
+template <bool ACC_INT, int BLOCK_N>
+__device__ __forceinline__ void epilogue_dispatch(const GemmParams& p, const TileInfo& t, uint32_t t_addr, int quad, int lane, int chunk0, int chunk1)
+{
+#define ASCB200_EPI_CASE(MODE, DT)                                                                          \
+    if (p.epi.mode == MODE && p.epi.c_dtype == DT) {                                                          \
+        epilogue_tile<ACC_INT, MODE, DT, BLOCK_N>(p, t, t_addr, quad, lane, chunk0, chunk1);                  \
+        return;                                                                                               \
+    }
+    if constexpr (ACC_INT) {
+        ASCB200_EPI_CASE(ASCB200_EPI_DEQUANT_TOKEN_CHANNEL, OUT_BF16)
+        ASCB200_EPI_CASE(ASCB200_EPI_DEQUANT_TOKEN_CHANNEL, OUT_F16)
+        ASCB200_EPI_CASE(ASCB200_EPI_DEQUANT_TOKEN_CHANNEL, OUT_F32)
+        ASCB200_EPI_CASE(ASCB200_EPI_CAST, OUT_S32)
+        ASCB200_EPI_CASE(ASCB200_EPI_FIXPIPE_QUANT, OUT_S8)
+        ASCB200_EPI_CASE(ASCB200_EPI_FIXPIPE_QUANT, OUT_F16)
+        ASCB200_EPI_CASE(ASCB200_EPI_FIXPIPE_QUANT, OUT_BF16)
+    } else {
+        ASCB200_EPI_CASE(ASCB200_EPI_CAST, OUT_F32)
+        ASCB200_EPI_CASE(ASCB200_EPI_CAST, OUT_F16)
+        ASCB200_EPI_CASE(ASCB200_EPI_CAST, OUT_BF16)
+        ASCB200_EPI_CASE(ASCB200_EPI_FIXPIPE_QUANT, OUT_S8)
+        ASCB200_EPI_CASE(ASCB200_EPI_FIXPIPE_QUANT, OUT_F16)
+        ASCB200_EPI_CASE(ASCB200_EPI_FIXPIPE_QUANT, OUT_BF16)
+        ASCB200_EPI_CASE(ASCB200_EPI_FIXPIPE_QUANT, OUT_F32)
+    }
+#undef ASCB200_EPI_CASE
 }
 
 // ---- the kernel --------------------------------------------------------------------------------
@@ -301,7 +393,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&acc_full_bar[s]), 1);
-            mbar_init(smem_u32(&acc_empty_bar[s]), 4);
+            mbar_init(smem_u32(&acc_empty_bar[s]), NUM_EPI_WARPS);
         }
         *abort_word = 0u;
         fence_barrier_init();
@@ -329,6 +421,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                 ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_word, p.status);
                 if (!ok) break;
+#ifdef ASCB200_PROBE
+                if (p.probe & 1) {
+                    if (lane == 0) mbar_arrive(smem_u32(&full_bar[stage]));
+                } else
+#endif
                 if (lane == 0) {
                     const uint32_t bar = smem_u32(&full_bar[stage]);
                     const uint32_t sa = smem_u32(tiles + stage * C::STAGE_BYTES);
@@ -416,7 +513,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             mma_mxf4(d_tmem, desc_at(a_hi, sa + j * 32), desc_at(b_hi, sb + j * 32), idesc, sf_t + (j >> 1) * 4,
                                      sf_t + 8 + (j >> 1) * 8, (kb | j) != 0 ? 1u : 0u);
                         }
-                    } else {
+                    } else
+#ifdef ASCB200_PROBE
+                    if (!(p.probe & 2))
+#endif
+                    {
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
                             mma_ss<KIND>(d_tmem, desc_at(a_hi, sa + j * a_kstep), desc_at(b_hi, sb + j * b_kstep), p.idesc,
@@ -433,34 +534,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
         }
     } else if (warp >= 4) {
-        // ===== epilogue =====
-        const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31
+        // ===== epilogue: warps 4-7 drain the first half of the tile's columns, warps 8-11 the second =====
+        const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 are the ones this warp may read
+        const int half = (warp - 4) >> 2;
+        constexpr int CHUNKS = BLOCK_N / 32;
+        const int chunk0 = half * (CHUNKS / 2), chunk1 = chunk0 + CHUNKS / 2;
         int cursor = 0, acc_iter = 0;
         TileInfo t;
         bool ok = true;
         for (int tile = blockIdx.x; ok && locate_tile<BLOCK_N>(p, tile, num_m, total_tiles, row_start, tile_start, cursor, t); tile += gridDim.x, ++acc_iter) {
             const int acc_stage = acc_iter % C::ACC_STAGES;
             const uint32_t acc_phase = (acc_iter / C::ACC_STAGES) & 1u;
-            ok = mbar_wait(smem_u32(&acc_full_bar[acc_stage]), acc_phase, abort_word, p.status);
+            ok = mbar_wait_relaxed(smem_u32(&acc_full_bar[acc_stage]), acc_phase, abort_word, p.status);
             if (!ok) break;
             tc_fence_after();
-            const int row = t.row0 + quad * 32 + lane;
-            const bool row_ok = row < t.row_end;
-            const float tok = (row_ok && p.epi.tok) ? p.epi.tok[row] : 1.0f;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc_stage * BLOCK_N;
-#pragma unroll 1
-            for (int c = 0; c < BLOCK_N / 32; ++c) {
-                const int col0 = t.n0 + c * 32;
-                if (col0 >= p.n) break;  // uniform across the CTA
-                uint32_t r[32];
-                tmem_ld_32x32(t_addr + c * 32, r);
-                tmem_ld_wait();
-                if (row_ok) {
-                    const int ncols = min(32, p.n - col0);
-                    epilogue_chunk<KIND == KIND_I8>(r, p.epi, row, col0, ncols, static_cast<size_t>(col0),
-                                                    static_cast<size_t>(t.group) * p.n + col0, tok);
-                }
-            }
+            epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, t_addr, quad, lane, chunk0, chunk1);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[acc_stage]));
@@ -666,6 +755,10 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     p.group_counts = reinterpret_cast<const long long*>(group_counts);
     p.status = st->status_dev;
     p.epi = e;
+#ifdef ASCB200_PROBE
+    p.probe = getenv("ASCB200_PROBE") ? atoi(getenv("ASCB200_PROBE")) : 0;
+    p.epi.probe = p.probe;
+#endif
 
     if (kind == ASCB200_KIND_MXFP4) {
         // re-tile both scale tensors into scratch (layout documented at retile_scales_kernel)

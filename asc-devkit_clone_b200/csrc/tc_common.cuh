@@ -65,6 +65,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Same contract, for waits that are expected to last long (an epilogue warp waiting for a whole
+// main loop): backs off between polls so that it does not take issue slots from the warps that
+// feed the tensor cores.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile uint32_t* abort_smem, uint32_t* status)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    uint32_t it = 0;
+    while (true) {
+        __nanosleep(64);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++it & 63u) == 0u) {
+            if (*abort_smem) return false;
+            if (global_ns() - t0 > kWaitLimitNs) {
+                *abort_smem = 1u;
+                atomicOr(status, 1u);
+                return false;
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
