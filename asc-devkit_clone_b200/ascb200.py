@@ -21,6 +21,7 @@ EXPORTS = [
     "ascb200_malloc", "ascb200_free", "ascb200_malloc_host", "ascb200_free_host", "ascb200_memcpy_h2d", "ascb200_memcpy_d2h",
     "ascb200_memset", "ascb200_stream_create", "ascb200_stream_destroy", "ascb200_stream_sync", "ascb200_event_create",
     "ascb200_event_destroy", "ascb200_event_record", "ascb200_event_elapsed_ms", "ascb200_gemm", "ascb200_grouped_gemm",
+    "ascb200_gemm_mxfp4_noalloc",
     "ascb200_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
 ]
 
@@ -78,6 +79,7 @@ def lib():
         _lib.ascb200_device_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
         _lib.ascb200_gemm.argtypes = [C.POINTER(GemmDesc), C.c_void_p]
         _lib.ascb200_grouped_gemm.argtypes = [C.POINTER(GemmDesc), C.c_void_p, C.c_int32, C.c_void_p]
+        _lib.ascb200_gemm_mxfp4_noalloc.argtypes = [C.POINTER(GemmDesc), C.c_void_p]
         _lib.ascb200_softmax.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_void_p]
         _lib.ascb200_quant_per_tensor.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_float, C.c_void_p]
@@ -159,7 +161,7 @@ def _ptr(b):
 
 def gemm(kind, m, n, k, a, b, c, c_dtype, epilogue=EPI_CAST, trans_a=False, trans_b=False, lda=0, ldb=0, ldc=0, bias=None,
          scale_a=None, scale_b=None, c2=None, c2_dtype=0, ldc2=0, quant=None, quant_scalar=0, tok=None, ch=None, relu=False, act=0,
-         group_counts=None, groups=0, stream=None):
+         group_counts=None, groups=0, stream=None, noalloc=False):
     d = GemmDesc()
     d.kind, d.m, d.n, d.k = kind, m, n, k
     d.a_dev, d.b_dev, d.lda, d.ldb = _ptr(a), _ptr(b), lda, ldb
@@ -169,6 +171,8 @@ def gemm(kind, m, n, k, a, b, c, c_dtype, epilogue=EPI_CAST, trans_a=False, tran
     d.c2_dev, d.ldc2, d.c2_dtype = _ptr(c2), ldc2, c2_dtype
     d.epilogue, d.quant_dev, d.quant_scalar = epilogue, _ptr(quant), int(quant_scalar)
     d.tok_scale_dev, d.ch_scale_dev, d.relu, d.act = _ptr(tok), _ptr(ch), int(relu), act
+    if noalloc:
+        return lib().ascb200_gemm_mxfp4_noalloc(C.byref(d), stream)
     if groups:
         return lib().ascb200_grouped_gemm(C.byref(d), _ptr(group_counts), groups, stream)
     return lib().ascb200_gemm(C.byref(d), stream)

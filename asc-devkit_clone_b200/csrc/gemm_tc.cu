@@ -649,10 +649,19 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
 int elem_bits(int kind) { return kind == ASCB200_KIND_MXFP4 ? 4 : kind == ASCB200_KIND_S8 ? 8 : 16; }
 int out_bytes(int dt) { return dt == OUT_S8 ? 1 : (dt == OUT_F16 || dt == OUT_BF16) ? 2 : 4; }
 
-int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups, cudaStream_t stream)
+// Device resources of one call when they do not come from the per-device state of ascb200_init.
+struct FixedResources {
+    uint32_t* status_dev;
+    uint8_t* scale_scratch_dev;
+    size_t scale_scratch_bytes;
+    int sm_count;
+};
+
+int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups, cudaStream_t stream, const FixedResources* fixed = nullptr)
 {
-    DeviceState* st = current_state();
-    if (!st) return ASCB200_ENODEV;
+    DeviceState* st = fixed ? nullptr : current_state();
+    if (!fixed && !st) return ASCB200_ENODEV;
+    const int sm_count = fixed ? fixed->sm_count : st->sm_count;
     if (!d) return ASCB200_EINVAL;
     if (d->m < 0 || d->n < 0 || d->k < 0) return ASCB200_EINVAL;
     if (d->m == 0 || d->n == 0) return ASCB200_OK;
@@ -728,7 +737,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     int block_n = 256;
     {
         const long long num_m = grouped ? (m + BLOCK_M - 1) / BLOCK_M + groups : (m + BLOCK_M - 1) / BLOCK_M;
-        while (block_n > 64 && (n <= block_n / 2 || num_m * ((n + block_n - 1) / block_n) < st->sm_count)) block_n /= 2;
+        while (block_n > 64 && (n <= block_n / 2 || num_m * ((n + block_n - 1) / block_n) < sm_count)) block_n /= 2;
         if (kind == ASCB200_KIND_MXFP4 && block_n < 128) block_n = 128;
         // an N-contiguous 8-bit B tile is fetched in boxes of 128 columns (one 128-byte swizzle row)
         if (kind == ASCB200_KIND_S8 && !d->trans_b && block_n < 128) block_n = 128;
@@ -753,7 +762,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     p.b_mn = d->trans_b ? 0 : 1;
     p.groups = grouped ? groups : 0;
     p.group_counts = reinterpret_cast<const long long*>(group_counts);
-    p.status = st->status_dev;
+    p.status = fixed ? fixed->status_dev : st->status_dev;
     p.epi = e;
 #ifdef ASCB200_PROBE
     p.probe = getenv("ASCB200_PROBE") ? atoi(getenv("ASCB200_PROBE")) : 0;
@@ -766,9 +775,15 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         const int kc = 2 * p.num_k_blocks;
         const int rba = (m + 127) / 128, rbb = (n + 255) / 256 * 2;
         const size_t bytes_a = static_cast<size_t>(rba) * kc * SF_CHUNK_BYTES, bytes_b = static_cast<size_t>(rbb) * kc * SF_CHUNK_BYTES;
-        rc = ensure_scratch(st, bytes_a + bytes_b, stream);
-        if (rc != ASCB200_OK) return rc;
-        uint8_t* sfa = static_cast<uint8_t*>(st->scratch_dev);
+        uint8_t* sfa;
+        if (fixed) {
+            if (bytes_a + bytes_b > fixed->scale_scratch_bytes) return ASCB200_ETOOBIG;
+            sfa = fixed->scale_scratch_dev;
+        } else {
+            rc = ensure_scratch(st, bytes_a + bytes_b, stream);
+            if (rc != ASCB200_OK) return rc;
+            sfa = static_cast<uint8_t*>(st->scratch_dev);
+        }
         uint8_t* sfb = sfa + bytes_a;
         const int ga = static_cast<int>(std::min<size_t>((bytes_a / 4 + 255) / 256, 4096));
         const int gb = static_cast<int>(std::min<size_t>((bytes_b / 4 + 255) / 256, 4096));
@@ -782,7 +797,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
 
     const long long max_tiles = grouped ? (static_cast<long long>((m + BLOCK_M - 1) / BLOCK_M) + groups) * ((n + block_n - 1) / block_n)
                                         : static_cast<long long>((m + BLOCK_M - 1) / BLOCK_M) * ((n + block_n - 1) / block_n);
-    const int grid = static_cast<int>(std::min<long long>(max_tiles, st->sm_count));
+    const int grid = static_cast<int>(std::min<long long>(max_tiles, sm_count));
 
     const uint32_t a_mn = p.a_mn, b_mn = p.b_mn;
     switch (kind) {
@@ -806,10 +821,74 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     }
 }
 
+// ---- allocation-free MXFP4 variant ------------------------------------------------------------------
+// Scratch of ascb200_gemm_mxfp4_noalloc: 256 bytes for the status word of the bounded waits, then the
+// re-tiled scale factors.  The array lives in the library image: every GPU that loads the library
+// holds these bytes until the process exits.
+constexpr size_t NOALLOC_HEAD_BYTES = 256;
+constexpr size_t NOALLOC_SCALE_BYTES = ASCB200_NOALLOC_MAX_SCALE_BYTES;
+static __device__ __align__(256) uint8_t g_noalloc_scratch[NOALLOC_HEAD_BYTES + NOALLOC_SCALE_BYTES];
+
+struct NoAllocDevice {
+    bool ready = false;
+    uint8_t* base = nullptr;  // device address of g_noalloc_scratch on this device
+    int sm_count = 0;
+};
+NoAllocDevice g_noalloc_dev[16];
+std::mutex g_noalloc_mu;
+
+// Once per device, with that device current: resolve the device address of the array.  In host code
+// the symbol itself is only a stand-in and must never be handed to a kernel.
+int noalloc_setup(NoAllocDevice** out)
+{
+    int dev = -1;
+    ASCB200_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16) return ASCB200_EINVAL;
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    NoAllocDevice* nd = &g_noalloc_dev[dev];
+    if (!nd->ready) {
+        int major = 0, sms = 0;
+        ASCB200_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        if (major != 10) return ASCB200_ENODEV;
+        ASCB200_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        void* ptr = nullptr;
+        ASCB200_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        if (!ptr) return ASCB200_ECUDA;
+        nd->base = static_cast<uint8_t*>(ptr);
+        nd->sm_count = sms;
+        nd->ready = true;
+    }
+    *out = nd;
+    return ASCB200_OK;
+}
+
+int run_gemm_mxfp4_noalloc(const ascb200_gemm_desc* d, cudaStream_t stream)
+{
+    if (!d) return ASCB200_EINVAL;
+    if (d->kind != ASCB200_KIND_MXFP4) return ASCB200_EUNSUPPORTED;
+    NoAllocDevice* nd = nullptr;
+    int rc = noalloc_setup(&nd);
+    if (rc != ASCB200_OK) return rc;
+    FixedResources fixed;
+    fixed.status_dev = reinterpret_cast<uint32_t*>(nd->base);
+    fixed.scale_scratch_dev = nd->base + NOALLOC_HEAD_BYTES;
+    fixed.scale_scratch_bytes = NOALLOC_SCALE_BYTES;
+    fixed.sm_count = nd->sm_count;
+    // the array keeps whatever the previous call left: the status word must start at zero; the scale
+    // area needs no clearing because the re-tiling kernels rewrite every byte the GEMM reads
+    ASCB200_CUDA(cudaMemsetAsync(fixed.status_dev, 0, sizeof(uint32_t), stream));
+    return run_gemm(d, nullptr, 0, stream, &fixed);
+}
+
 }  // namespace
 }  // namespace ascb200
 
 extern "C" {
+
+int ascb200_gemm_mxfp4_noalloc(const ascb200_gemm_desc* desc, void* stream)
+{
+    return ascb200::run_gemm_mxfp4_noalloc(desc, static_cast<cudaStream_t>(stream));
+}
 
 int ascb200_gemm(const ascb200_gemm_desc* desc, void* stream)
 {

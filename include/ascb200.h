@@ -141,6 +141,34 @@ ASCB200_API int ascb200_gemm(const ascb200_gemm_desc* desc, void* stream);
 ASCB200_API int ascb200_grouped_gemm(const ascb200_gemm_desc* desc, const int64_t* group_counts_dev, int32_t groups,
                                      void* stream);
 
+/* MXFP4 Matmul for callers that must not allocate device memory.  (No counterpart in the reference:
+ * its operators run on buffers the user kernel already owns.)
+ *
+ * Who needs it: a host that has handed all of the GPU's memory to its own pool or arena before this
+ * library is touched (inference servers and training frameworks commonly do), or that runs inside a
+ * latency-critical loop where cudaMalloc's implicit device synchronisation is not acceptable.  For
+ * them ascb200_init (which allocates the status word) and ascb200_gemm (which grows a scratch block
+ * for the re-tiled MX scale factors on first use) are both off limits.
+ *
+ * This entry point needs neither: its status word and its scale scratch live in one array that is
+ * part of the library image (ASCB200_NOALLOC_MAX_SCALE_BYTES + 256 bytes on every GPU that loads the
+ * library, held until the process exits).  It calls no cudaMalloc / cudaFree and needs no ascb200_init;
+ * it works on the calling thread's current device.  Inputs and outputs are still the caller's.
+ *
+ *  - desc: exactly as for ascb200_gemm with kind == ASCB200_KIND_MXFP4 (other kinds: ASCB200_EUNSUPPORTED);
+ *  - limit: the re-tiled scales take (ceil(m/128) + 2*ceil(n/256)) * 2*ceil(k/256) * 512 bytes; if that
+ *    exceeds ASCB200_NOALLOC_MAX_SCALE_BYTES the call returns ASCB200_ETOOBIG and launches nothing
+ *    (m = n = k = 8192 just fits);
+ *  - the first call on each device looks up the array's device address; make that first call outside
+ *    any stream capture;
+ *  - all calls on one device share the array, which keeps the previous call's contents (the part that
+ *    must start at zero is cleared on the stream at the start of each call): two calls whose GPU work
+ *    may overlap - different streams, or different host threads - race on it; serialise them;
+ *  - an expired device-side wait is recorded in the array's first word, not in the word that
+ *    ascb200_device_status reads. */
+#define ASCB200_NOALLOC_MAX_SCALE_BYTES (4u << 20)
+ASCB200_API int ascb200_gemm_mxfp4_noalloc(const ascb200_gemm_desc* desc, void* stream);
+
 /* ---- SoftMax ------------------------------------------------------------------------------------ */
 
 /* SoftMax<T>(dst, sum, max, src, tiling, shapeInfo) over the last axis of src[m,k]
