@@ -21,7 +21,7 @@ EXPORTS = [
     "ascb200_malloc", "ascb200_free", "ascb200_malloc_host", "ascb200_free_host", "ascb200_memcpy_h2d", "ascb200_memcpy_d2h",
     "ascb200_memset", "ascb200_stream_create", "ascb200_stream_destroy", "ascb200_stream_sync", "ascb200_event_create",
     "ascb200_event_destroy", "ascb200_event_record", "ascb200_event_elapsed_ms", "ascb200_gemm", "ascb200_grouped_gemm",
-    "ascb200_gemm_mxfp4_noalloc",
+    "ascb200_gemm_mxfp4_noalloc", "ascb200_graph_begin", "ascb200_graph_end", "ascb200_graph_launch", "ascb200_graph_destroy",
     "ascb200_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
 ]
 
@@ -80,6 +80,10 @@ def lib():
         _lib.ascb200_gemm.argtypes = [C.POINTER(GemmDesc), C.c_void_p]
         _lib.ascb200_grouped_gemm.argtypes = [C.POINTER(GemmDesc), C.c_void_p, C.c_int32, C.c_void_p]
         _lib.ascb200_gemm_mxfp4_noalloc.argtypes = [C.POINTER(GemmDesc), C.c_void_p]
+        _lib.ascb200_graph_begin.argtypes = [C.c_void_p]
+        _lib.ascb200_graph_end.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+        _lib.ascb200_graph_launch.argtypes = [C.c_void_p, C.c_void_p]
+        _lib.ascb200_graph_destroy.argtypes = [C.c_void_p]
         _lib.ascb200_softmax.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_void_p]
         _lib.ascb200_quant_per_tensor.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_float, C.c_void_p]
@@ -198,6 +202,25 @@ def quant_per_channel(src, dst, rows, k, dtype, scale, offset_t=None, offset=0.0
 def dequant(src, dst, m, n, cal, n_dst, dst_dtype, scale=None, scale_dtype=F32, scale_scalar=0.0, stream=None):
     return lib().ascb200_dequant(_ptr(src), _ptr(dst), m, n, cal, n_dst, dst_dtype, _ptr(scale), scale_dtype, C.c_float(scale_scalar),
                                  stream)
+
+
+class Graph:
+    """Records what `fn()` issues on `stream` into a CUDA graph (through the C ABI) and replays it."""
+
+    def __init__(self, stream, fn):
+        self.stream = stream
+        check(lib().ascb200_graph_begin(stream), "graph begin")
+        try:
+            fn()
+        finally:
+            self.exec = C.c_void_p()
+            check(lib().ascb200_graph_end(stream, C.byref(self.exec)), "graph end")
+
+    def launch(self):
+        check(lib().ascb200_graph_launch(self.exec, self.stream), "graph launch")
+
+    def destroy(self):
+        lib().ascb200_graph_destroy(self.exec)
 
 
 class Timer:

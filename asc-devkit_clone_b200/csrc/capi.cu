@@ -188,4 +188,32 @@ int ascb200_event_elapsed_ms(void* start, void* stop, float* ms)
     return ASCB200_OK;
 }
 
+int ascb200_graph_begin(void* stream)
+{
+    ASCB200_CUDA(cudaStreamBeginCapture(static_cast<cudaStream_t>(stream), cudaStreamCaptureModeThreadLocal));
+    return ASCB200_OK;
+}
+int ascb200_graph_end(void* stream, void** graph_exec)
+{
+    if (!graph_exec) return ASCB200_EINVAL;
+    cudaGraph_t g = nullptr;
+    ASCB200_CUDA(cudaStreamEndCapture(static_cast<cudaStream_t>(stream), &g));
+    cudaGraphExec_t e = nullptr;
+    cudaError_t err = cudaGraphInstantiate(&e, g, 0);
+    (void)cudaGraphDestroy(g);
+    if (err != cudaSuccess) return cuda_fail(err);
+    *graph_exec = e;
+    return ASCB200_OK;
+}
+int ascb200_graph_launch(void* graph_exec, void* stream)
+{
+    ASCB200_CUDA(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph_exec), static_cast<cudaStream_t>(stream)));
+    return ASCB200_OK;
+}
+int ascb200_graph_destroy(void* graph_exec)
+{
+    ASCB200_CUDA(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec)));
+    return ASCB200_OK;
+}
+
 }  // extern "C"

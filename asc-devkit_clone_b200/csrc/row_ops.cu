@@ -14,6 +14,12 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void* p)
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
     return r;
 }
+__device__ __forceinline__ float exp2_approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float warp_max(float v)
 {
 #pragma unroll
@@ -27,15 +33,39 @@ __device__ __forceinline__ float warp_sum(float v)
     return v;
 }
 
-// half(x) * half(scale) + half(offset) -> int8, every step rounded to half (no fused multiply-add).
+// AscendQuant on two values at a time: half(x) * half(scale) + half(offset), each step rounded to
+// half (no fused multiply-add), then round-to-nearest-even to int8 with saturation, NaN -> 0.
+// The rounding uses the fp16 grid itself: after clamping to [-128, 127], adding 1536 lands in
+// [1024, 2048) where consecutive halves are 1 apart, so the sum is rint(v) + 1536 exactly and the
+// low byte of its bit pattern is the two's-complement int8.
+__device__ __forceinline__ uint32_t quant_half2_bits(__half2 x, __half2 s, __half2 o)
+{
+    __half2 v = __hadd2_rn(__hmul2_rn(x, s), o);
+    uint32_t bits = *reinterpret_cast<uint32_t*>(&v) & __heq2_mask(v, v);  // NaN lanes -> +0
+    v = *reinterpret_cast<__half2*>(&bits);
+    v = __hmax2(__hmin2(v, __float2half2_rn(127.0f)), __float2half2_rn(-128.0f));
+    v = __hadd2_rn(v, __float2half2_rn(1536.0f));
+    return *reinterpret_cast<uint32_t*>(&v);  // bytes 0 and 2 hold the two int8 results
+}
+// Packs the int8 results of two quant_half2_bits() words into the low / high halves of 4 bytes.
+__device__ __forceinline__ uint32_t pack_s8x4(uint32_t ab, uint32_t cd) { return __byte_perm(ab, cd, 0x6420); }
+
+__device__ __forceinline__ float clamp_half_range(float v) { return (v != v) ? v : fminf(fmaxf(v, -65504.0f), 65504.0f); }
+// Two source elements -> half2 the way the operator converts its input (RINT, saturating).
+__device__ __forceinline__ __half2 to_half2_src(__half a, __half b) { return __halves2half2(a, b); }
+__device__ __forceinline__ __half2 to_half2_src(__nv_bfloat16 a, __nv_bfloat16 b)
+{
+    return __floats2half2_rn(clamp_half_range(__bfloat162float(a)), clamp_half_range(__bfloat162float(b)));
+}
+__device__ __forceinline__ __half2 to_half2_src(float a, float b) { return __floats2half2_rn(clamp_half_range(a), clamp_half_range(b)); }
 __device__ __forceinline__ int quant_half(__half x, __half s, __half o)
 {
-    __half v = __hadd_rn(__hmul_rn(x, s), o);
-    return f32_to_s8(__half2float(v));
+    const uint32_t b = quant_half2_bits(__halves2half2(x, x), __halves2half2(s, s), __halves2half2(o, o));
+    return static_cast<int>(static_cast<int8_t>(b & 0xFFu));
 }
 __device__ __forceinline__ __half to_half_src(__half v) { return v; }
-__device__ __forceinline__ __half to_half_src(__nv_bfloat16 v) { return f32_to_f16_sat(__bfloat162float(v)); }
-__device__ __forceinline__ __half to_half_src(float v) { return f32_to_f16_sat(v); }
+__device__ __forceinline__ __half to_half_src(__nv_bfloat16 v) { return __float2half_rn(clamp_half_range(__bfloat162float(v))); }
+__device__ __forceinline__ __half to_half_src(float v) { return __float2half_rn(clamp_half_range(v)); }
 
 template <int TPR>
 __device__ __forceinline__ float row_reduce_max(float v, float* red)
@@ -69,7 +99,7 @@ __device__ __forceinline__ float row_reduce_sum(float v, float* red)
 // One row per group of TPR threads (a warp, or the whole block).  Thread t of the group owns the
 // 16-byte chunks t, t+TPR, ... (NCHUNK of them).  T = __half (8 per chunk) or float (4 per chunk).
 template <typename T, int TPR, int NCHUNK, bool QUANT>
-__global__ void __launch_bounds__(TPR > 32 ? TPR : 256)
+__global__ void __launch_bounds__(TPR > 32 ? TPR : 128)
 softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __restrict__ sum_out, float* __restrict__ max_out,
                     int8_t* __restrict__ q_out, const __half* __restrict__ q_scale, const __half* __restrict__ q_offset,
                     __half q_offset_scalar, int m, int k, int stats_rep)
@@ -120,7 +150,7 @@ softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __res
     float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < NCHUNK * VEC; ++i) {
-        v[i] = __expf(v[i] - mx);
+        v[i] = exp2_approx((v[i] - mx) * 1.4426950408889634f);  // exp(x - max); -inf padding gives 0
         s += v[i];
     }
     s = row_reduce_sum<TPR>(s, red);
@@ -132,26 +162,22 @@ softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __res
         const int c = t + i * TPR;
         if (c < nchunks) {
             if constexpr (sizeof(T) == 2) {
-                uint4 o;
+                uint4 o;  // softmax values lie in [0, 1]: the half cast cannot overflow
                 __half2* h = reinterpret_cast<__half2*>(&o);
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    h[j] = __halves2half2(f32_to_f16_sat(v[i * 8 + 2 * j] * inv), f32_to_f16_sat(v[i * 8 + 2 * j + 1] * inv));
+                for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(v[i * 8 + 2 * j] * inv, v[i * 8 + 2 * j + 1] * inv);
                 *reinterpret_cast<uint4*>(drow + c * 8) = o;
                 if constexpr (QUANT) {
-                    const uint4 sc = *reinterpret_cast<const uint4*>(q_scale + c * 8);
-                    uint4 of;
-                    if (q_offset) of = *reinterpret_cast<const uint4*>(q_offset + c * 8);
-                    const __half* hs = reinterpret_cast<const __half*>(&sc);
-                    const __half* ho = reinterpret_cast<const __half*>(&of);
-                    const __half* hy = reinterpret_cast<const __half*>(&o);
-                    uint32_t pk[2] = {0u, 0u};
+                    const uint4 sc = __ldg(reinterpret_cast<const uint4*>(q_scale + c * 8));
+                    uint4 of = make_uint4(0u, 0u, 0u, 0u);
+                    if (q_offset) of = __ldg(reinterpret_cast<const uint4*>(q_offset + c * 8));
+                    const __half2* hs = reinterpret_cast<const __half2*>(&sc);
+                    const __half2* ho = reinterpret_cast<const __half2*>(&of);
+                    const __half2 os = __half2half2(q_offset_scalar);
+                    uint32_t w[4];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int q = quant_half(hy[j], hs[j], q_offset ? ho[j] : q_offset_scalar);
-                        pk[j >> 2] |= static_cast<uint32_t>(q & 0xFF) << (8 * (j & 3));
-                    }
-                    *reinterpret_cast<uint2*>(q_out + static_cast<size_t>(row) * k + c * 8) = make_uint2(pk[0], pk[1]);
+                    for (int j = 0; j < 4; ++j) w[j] = quant_half2_bits(h[j], hs[j], q_offset ? ho[j] : os);
+                    *reinterpret_cast<uint2*>(q_out + static_cast<size_t>(row) * k + c * 8) = make_uint2(pack_s8x4(w[0], w[1]), pack_s8x4(w[2], w[3]));
                 }
             } else {
                 float4 o = make_float4(v[i * 4] * inv, v[i * 4 + 1] * inv, v[i * 4 + 2] * inv, v[i * 4 + 3] * inv);
@@ -172,7 +198,7 @@ int launch_softmax(const T* src, T* dst, float* sum, float* mx, int8_t* q, const
     constexpr int VEC = 16 / sizeof(T);
     const int nchunks = k / VEC;
 #define ASCB200_SM_WARP(NC)                                                                                              \
-    softmax_rows_kernel<T, 32, NC, QUANT><<<(m + 7) / 8, 256, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep)
+    softmax_rows_kernel<T, 32, NC, QUANT><<<(m + 3) / 4, 128, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep)
 #define ASCB200_SM_BLOCK(TPR, NC) softmax_rows_kernel<T, TPR, NC, QUANT><<<m, TPR, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep)
     if (nchunks <= 32) ASCB200_SM_WARP(1);
     else if (nchunks <= 64) ASCB200_SM_WARP(2);
@@ -213,17 +239,17 @@ quant_vec8_kernel(const T* __restrict__ src, int8_t* __restrict__ dst, size_t n8
                 for (int j = 0; j < 8; ++j) o[j] = offset[c + j];
             }
         }
-        uint32_t pk[2] = {0u, 0u};
+        uint32_t w[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            __half hs = scale_h, ho = offset_h;
+        for (int j = 0; j < 4; ++j) {
+            __half2 hs = __half2half2(scale_h), ho = __half2half2(offset_h);
             if constexpr (PER_CHANNEL) {
-                hs = to_half_src(s[j]);
-                if (offset) ho = to_half_src(o[j]);
+                hs = to_half2_src(s[2 * j], s[2 * j + 1]);
+                if (offset) ho = to_half2_src(o[2 * j], o[2 * j + 1]);
             }
-            const int q = quant_half(to_half_src(x[j]), hs, ho);
-            pk[j >> 2] |= static_cast<uint32_t>(q & 0xFF) << (8 * (j & 3));
+            w[j] = quant_half2_bits(to_half2_src(x[2 * j], x[2 * j + 1]), hs, ho);
         }
+        const uint32_t pk[2] = {pack_s8x4(w[0], w[1]), pack_s8x4(w[2], w[3])};
         *reinterpret_cast<uint2*>(dst + e) = make_uint2(pk[0], pk[1]);
     }
 }

@@ -352,14 +352,16 @@ class SoftmaxQuant(Workload):
     unit_scale = 1e9
     scaling = "weak"  # rows are independent; every rank runs its own replica of the configuration
     M, K = 4096, 2048
+    ROW_FACTOR = 1
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
+        self.M = self.M * self.ROW_FACTOR
         self.ab, self.rank, self.world = ab, rank, world
         rng = np.random.default_rng(0xA5C00001 + rank)
-        self.x_h = f16_bits(rng.standard_normal((self.M, self.K), dtype=np.float32) * 3.0)
+        self.x_h = np.tile(f16_bits(rng.standard_normal((4096, self.K), dtype=np.float32) * 3.0), (self.ROW_FACTOR, 1))
         self.sc_h = f16_bits((127.0 / rng.uniform(0.5, 2.0, self.K)).astype(np.float32))
-        self.sets = sets = max(sets, 8)  # 42 MB per set: rotate 8 sets so no step finds its input in L2
+        self.sets = sets = max(sets, 8) if self.ROW_FACTOR == 1 else 2  # 42 MB per set: rotate 8 sets so no step finds its input in L2
         self.x = [ab.to_dev(self.x_h) for _ in range(sets)]
         self.y = [ab.empty((self.M, self.K), np.uint16) for _ in range(sets)]
         self.q = [ab.empty((self.M, self.K), np.int8) for _ in range(sets)]
@@ -412,6 +414,13 @@ class SoftmaxQuant(Workload):
         ry, _, _ = orc.softmax(self.x_h[:64], orc.F16)
         yf, rf = orc.f16_bits_to_f32(y), orc.f16_bits_to_f32(ry)
         return bool((np.abs(yf - rf) <= 1e-3 * np.abs(rf) + 2.0 ** -24).all() and (q == orc.quant_per_channel(y, orc.F16, self.sc_h, 0.0)).all())
+
+
+class SoftmaxQuantLarge(SoftmaxQuant):
+    """Companion of the baseline row-op configuration with 64 x the rows (2.7 GB per pass): the 42 MB
+    baseline shape lasts only a few microseconds, so launch ramp-up and tail dominate its bandwidth figure."""
+    name = "softmax_ascendquant_262144x2048_fp16_int8"
+    ROW_FACTOR = 64
 
 
 class FP16(Workload):
@@ -473,7 +482,8 @@ class FP16(Workload):
         return bool(np.allclose(self.c[0].download(), ref, rtol=1e-2, atol=1e-3))
 
 
-WORKLOADS = {"a8w8": A8W8, "grouped": Grouped, "mxfp4": MXFP4, "softmax_quant": SoftmaxQuant, "fp16": FP16}
+WORKLOADS = {"a8w8": A8W8, "grouped": Grouped, "mxfp4": MXFP4, "softmax_quant": SoftmaxQuant, "softmax_quant_x64": SoftmaxQuantLarge,
+             "fp16": FP16}
 
 
 class PinnedSet:
@@ -539,18 +549,31 @@ class Comm:
 
 
 def time_steps(ab, wl, comm, steps, warmup, stream, e2e=False):
+    """Times exactly `steps` steps between a barrier + synchronize on both sides; returns the max over ranks (ms).
+    The device-resident measurement replays the steps from one CUDA graph, so that the host's launch
+    cost (a Python ctypes call per step) does not sit between kernels that last a few microseconds."""
     fn = (lambda i: wl.e2e_step(i, stream)) if e2e else (lambda i: wl.step(i, stream))
     for i in range(warmup):
         fn(i)
     ab.sync(stream)
+    graph = None
+    if not e2e:
+        graph = ab.Graph(stream, lambda: [fn(warmup + i) for i in range(steps)])
+        graph.launch()          # one untimed replay: graph upload
+        ab.sync(stream)
     comm.barrier()
     timer = ab.Timer(stream)
     timer.start()
-    for i in range(steps):
-        fn(warmup + i)
+    if graph:
+        graph.launch()
+    else:
+        for i in range(steps):
+            fn(warmup + i)
     ms = timer.stop_ms()
     ab.sync(stream)
     comm.barrier()
+    if graph:
+        graph.destroy()
     return comm.max(ms)
 
 

@@ -81,6 +81,15 @@ ASCB200_API int ascb200_event_destroy(void* event);
 ASCB200_API int ascb200_event_record(void* event, void* stream);
 ASCB200_API int ascb200_event_elapsed_ms(void* start, void* stop, float* ms); /* synchronises on stop */
 
+/* CUDA-graph shims: record the calls issued on `stream` between begin and end into one graph and
+ * replay it with a single launch.  For launch-bound sequences of small operators (the role the
+ * reference gives to a single kernel that calls several adv_api operators back to back).  A call
+ * that may allocate (the first MXFP4 ascb200_gemm of a larger size) must be made once before capture. */
+ASCB200_API int ascb200_graph_begin(void* stream);
+ASCB200_API int ascb200_graph_end(void* stream, void** graph_exec);
+ASCB200_API int ascb200_graph_launch(void* graph_exec, void* stream);
+ASCB200_API int ascb200_graph_destroy(void* graph_exec);
+
 /* ---- Matmul ---------------------------------------------------------------------------------- */
 
 /* Output stage applied to the accumulator tile, the job of Fixpipe in the reference
