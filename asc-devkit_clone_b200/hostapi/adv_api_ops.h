@@ -1,0 +1,211 @@
+// SoftMax, AscendQuant and AscendDequant with the reference's argument lists, forwarding to the C ABI.
+// Included by kernel_operator.h.  Tensors are device memory holding the whole operand; sharedTmpBuffer
+// arguments are accepted and ignored (the B200 kernels keep their working set in registers).
+#pragma once
+
+namespace AscendC {
+
+// include/adv_api/activation/softmax_utils.h:33-78
+enum class SoftmaxMode { SOFTMAX_NORMAL = 0, SOFTMAX_OUTPUT_WITHOUT_BRC = 1 };
+struct SoftmaxConfig {
+    constexpr SoftmaxConfig(bool isCheckTilingIn = true, uint32_t oriSrcMIn = 0, uint32_t oriSrcKIn = 0,
+                            SoftmaxMode modeIn = SoftmaxMode::SOFTMAX_NORMAL)
+        : isCheckTiling(isCheckTilingIn), oriSrcM(oriSrcMIn), oriSrcK(oriSrcKIn), mode(modeIn)
+    {}
+    bool isCheckTiling;
+    uint32_t oriSrcM, oriSrcK;
+    SoftmaxMode mode;
+};
+constexpr SoftmaxConfig SOFTMAX_DEFAULT_CFG = {true, 0, 0, SoftmaxMode::SOFTMAX_NORMAL};
+struct SoftMaxShapeInfo {
+    uint32_t srcM{0};
+    uint32_t srcK{0};
+    uint32_t oriSrcM{0};
+    uint32_t oriSrcK{0};
+};
+
+// SoftMax<T>(dst, sum, max, src, tiling, shapeInfo)  (include/adv_api/activation/softmax.h:92-109).
+// The shape comes from shapeInfo when given, else from the tiling, like the reference; sum / max are
+// [srcM, 8] fp32 (one 32-byte block per row) unless config.mode is SOFTMAX_OUTPUT_WITHOUT_BRC.
+template <typename T, bool isReuseSource = false, bool isBasicBlock = false, bool isDataFormatNZ = false,
+          const SoftmaxConfig& config = SOFTMAX_DEFAULT_CFG>
+inline void SoftMax(const LocalTensor<T>& dstTensor, const LocalTensor<float>& sumTensor, const LocalTensor<float>& maxTensor,
+                    const LocalTensor<T>& srcTensor, const SoftMaxTiling& tiling, const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    static_assert(!isDataFormatNZ, "NZ-format SoftMax is not part of the B200 path");
+    const uint32_t m = softmaxShapeInfo.srcM ? softmaxShapeInfo.srcM : tiling.srcM;
+    const uint32_t k = softmaxShapeInfo.srcK ? softmaxShapeInfo.srcK : tiling.srcK;
+    const int brc = config.mode == SoftmaxMode::SOFTMAX_OUTPUT_WITHOUT_BRC ? 0 : 1;
+    detail::Latch(ascb200_softmax(srcTensor.GetPhyAddr(), dstTensor.GetPhyAddr(), sumTensor.GetPhyAddr(), maxTensor.GetPhyAddr(),
+                                  static_cast<int32_t>(m), static_cast<int32_t>(k), detail::DTypeOf<T>::value, brc, detail::CurrentStream()),
+                  "SoftMax");
+}
+template <typename T, bool isReuseSource = false, bool isBasicBlock = false, bool isDataFormatNZ = false,
+          const SoftmaxConfig& config = SOFTMAX_DEFAULT_CFG>
+inline void SoftMax(const LocalTensor<T>& dstTensor, const LocalTensor<float>& sumTensor, const LocalTensor<float>& maxTensor,
+                    const LocalTensor<T>& srcTensor, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const SoftMaxTiling& tiling,
+                    const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    SoftMax<T, isReuseSource, isBasicBlock, isDataFormatNZ, config>(dstTensor, sumTensor, maxTensor, srcTensor, tiling, softmaxShapeInfo);
+}
+
+// include/adv_api/quantization/ascend_quant_utils.h:31-73
+struct AscendQuantConfig {
+    constexpr AscendQuantConfig(uint32_t calcCountIn, uint32_t offsetCountIn, uint32_t scaleCountIn, uint32_t workLocalSizeIn,
+                                bool hasOffsetIn = false, int32_t kDimIn = 1, RoundMode roundModeIn = RoundMode::CAST_RINT)
+        : calcCount(calcCountIn), offsetCount(offsetCountIn), scaleCount(scaleCountIn), workLocalSize(workLocalSizeIn),
+          hasOffset(hasOffsetIn), kDim(kDimIn), roundMode(roundModeIn)
+    {}
+    uint32_t calcCount, offsetCount, scaleCount, workLocalSize;
+    bool hasOffset;
+    int32_t kDim;
+    RoundMode roundMode;
+};
+constexpr AscendQuantConfig ASCEND_QUANT_DEFAULT_CFG = {0, 0, 0, 0, false, 1, RoundMode::CAST_RINT};
+
+namespace detail {
+template <typename T>
+inline void QuantPerTensor(const LocalTensor<int8_t>& dst, const LocalTensor<T>& src, float scale, float offset, uint64_t calCount)
+{
+    Latch(ascb200_quant_per_tensor(src.GetPhyAddr(), dst.GetPhyAddr(), static_cast<int64_t>(calCount), DTypeOf<T>::value, scale, offset,
+                                   CurrentStream()),
+          "AscendQuant");
+}
+template <typename T>
+inline void QuantPerChannel(const LocalTensor<int8_t>& dst, const LocalTensor<T>& src, const LocalTensor<T>& scale, const T* offsetTensor,
+                            float offsetScalar, uint64_t scaleCount, uint64_t calCount)
+{
+    if (scaleCount == 0 || calCount % scaleCount != 0) {
+        Latch(ASCB200_EINVAL, "AscendQuant (calCount must be a multiple of scaleCount)");
+        return;
+    }
+    Latch(ascb200_quant_per_channel(src.GetPhyAddr(), dst.GetPhyAddr(), static_cast<int32_t>(calCount / scaleCount),
+                                    static_cast<int32_t>(scaleCount), DTypeOf<T>::value, scale.GetPhyAddr(), offsetTensor, offsetScalar,
+                                    CurrentStream()),
+          "AscendQuant");
+}
+}  // namespace detail
+
+// per tensor (include/adv_api/quantization/ascend_quant.h:63-136)
+template <typename T, bool isReuseSource = false, const AscendQuantConfig& config = ASCEND_QUANT_DEFAULT_CFG>
+inline void AscendQuant(const LocalTensor<int8_t>& dst, const LocalTensor<T>& src, const float scale, const float offset, const uint32_t calCount)
+{
+    static_assert(config.roundMode == RoundMode::CAST_RINT, "only CAST_RINT is implemented");
+    detail::QuantPerTensor<T>(dst, src, scale, offset, calCount);
+}
+template <typename T, bool isReuseSource = false, const AscendQuantConfig& config = ASCEND_QUANT_DEFAULT_CFG>
+inline void AscendQuant(const LocalTensor<int8_t>& dst, const LocalTensor<T>& src, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/,
+                        const float scale, const float offset, const uint32_t calCount)
+{
+    detail::QuantPerTensor<T>(dst, src, scale, offset, calCount);
+}
+template <typename T, bool isReuseSource = false, const AscendQuantConfig& config = ASCEND_QUANT_DEFAULT_CFG>
+inline void AscendQuant(const LocalTensor<int8_t>& dst, const LocalTensor<T>& src, const float scale, const float offset)
+{
+    detail::QuantPerTensor<T>(dst, src, scale, offset, src.GetSize());
+}
+template <typename T, bool isReuseSource = false, const AscendQuantConfig& config = ASCEND_QUANT_DEFAULT_CFG>
+inline void AscendQuant(const LocalTensor<int8_t>& dst, const LocalTensor<T>& src, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/,
+                        const float scale, const float offset)
+{
+    detail::QuantPerTensor<T>(dst, src, scale, offset, src.GetSize());
+}
+// per channel, scalar offset (ascend_quant.h:159-236)
+template <typename T, bool isReuseSource = false, const AscendQuantConfig& config = ASCEND_QUANT_DEFAULT_CFG>
+inline void AscendQuant(const LocalTensor<int8_t>& dst, const LocalTensor<T>& src, const LocalTensor<T>& scaleTensor, const T offset,
+                        const uint32_t scaleCount, const uint32_t calCount)
+{
+    detail::QuantPerChannel<T>(dst, src, scaleTensor, nullptr, static_cast<float>(offset), scaleCount, calCount);
+}
+template <typename T, bool isReuseSource = false, const AscendQuantConfig& config = ASCEND_QUANT_DEFAULT_CFG>
+inline void AscendQuant(const LocalTensor<int8_t>& dst, const LocalTensor<T>& src, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/,
+                        const LocalTensor<T>& scaleTensor, const T offset, const uint32_t scaleCount, const uint32_t calCount)
+{
+    detail::QuantPerChannel<T>(dst, src, scaleTensor, nullptr, static_cast<float>(offset), scaleCount, calCount);
+}
+template <typename T, bool isReuseSource = false, const AscendQuantConfig& config = ASCEND_QUANT_DEFAULT_CFG>
+inline void AscendQuant(const LocalTensor<int8_t>& dst, const LocalTensor<T>& src, const LocalTensor<T>& scaleTensor, const T offset)
+{
+    detail::QuantPerChannel<T>(dst, src, scaleTensor, nullptr, static_cast<float>(offset), scaleTensor.GetSize(), src.GetSize());
+}
+// per channel, offset tensor (ascend_quant.h:261-342)
+template <typename T, bool isReuseSource = false, const AscendQuantConfig& config = ASCEND_QUANT_DEFAULT_CFG>
+inline void AscendQuant(const LocalTensor<int8_t>& dst, const LocalTensor<T>& src, const LocalTensor<T>& scaleTensor,
+                        const LocalTensor<T>& offsetTensor, const uint32_t scaleCount, const uint32_t offsetCount, const uint32_t calCount)
+{
+    if (offsetCount != scaleCount) {
+        detail::Latch(ASCB200_EINVAL, "AscendQuant (offsetCount must equal scaleCount)");
+        return;
+    }
+    detail::QuantPerChannel<T>(dst, src, scaleTensor, offsetTensor.GetPhyAddr(), 0.0f, scaleCount, calCount);
+}
+template <typename T, bool isReuseSource = false, const AscendQuantConfig& config = ASCEND_QUANT_DEFAULT_CFG>
+inline void AscendQuant(const LocalTensor<int8_t>& dst, const LocalTensor<T>& src, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/,
+                        const LocalTensor<T>& scaleTensor, const LocalTensor<T>& offsetTensor, const uint32_t scaleCount,
+                        const uint32_t offsetCount, const uint32_t calCount)
+{
+    AscendQuant<T, isReuseSource, config>(dst, src, scaleTensor, offsetTensor, scaleCount, offsetCount, calCount);
+}
+template <typename T, bool isReuseSource = false, const AscendQuantConfig& config = ASCEND_QUANT_DEFAULT_CFG>
+inline void AscendQuant(const LocalTensor<int8_t>& dst, const LocalTensor<T>& src, const LocalTensor<T>& scaleTensor,
+                        const LocalTensor<T>& offsetTensor)
+{
+    detail::QuantPerChannel<T>(dst, src, scaleTensor, offsetTensor.GetPhyAddr(), 0.0f, scaleTensor.GetSize(), src.GetSize());
+}
+
+// include/adv_api/quantization/ascend_dequant_utils.h:26-30
+struct DequantParams {
+    uint32_t m;         // rows of src
+    uint32_t n;         // int32 elements per src row (a multiple of 8: 32 bytes)
+    uint32_t calCount;  // leading elements of each row that are dequantised
+};
+
+namespace detail {
+template <typename dstT>
+inline uint32_t DequantDstRow(uint32_t n)
+{
+    const uint32_t perBlock = 32 / sizeof(dstT);  // dst rows are padded to a 32-byte multiple like in the reference
+    return (n + perBlock - 1) / perBlock * perBlock;
+}
+template <DeQuantMode mode>
+inline DequantParams DequantShape(DequantParams p)
+{
+    // {1, m*n, n} means {m, n, n} in single-row mode (include/adv_api/quantization/ascend_dequant.h, mode description)
+    if (mode == DeQuantMode::DEQUANT_WITH_SINGLE_ROW && p.m == 1 && p.calCount > 0 && p.n > p.calCount && p.n % p.calCount == 0)
+        return DequantParams{p.n / p.calCount, p.calCount, p.calCount};
+    return p;
+}
+}  // namespace detail
+
+// AscendDequant<dstT, scaleT, mode>(dst, src, deqScale, params)  (include/adv_api/quantization/ascend_dequant.h).
+// scaleT float or bfloat16_t for a tensor scale; a uint64_t tensor carries the fp32 scale in its low 32 bits
+// and is not supported here (convert once on the host).
+template <typename dstT, typename scaleT, DeQuantMode mode = DeQuantMode::DEQUANT_WITH_SINGLE_ROW>
+inline void AscendDequant(const LocalTensor<dstT>& dst, const LocalTensor<int32_t>& src, const LocalTensor<scaleT>& deqScale, DequantParams params)
+{
+    static_assert(sizeof(scaleT) != 8, "uint64_t deqScale tensors are not supported: pass the fp32 scales");
+    const DequantParams p = detail::DequantShape<mode>(params);
+    detail::Latch(ascb200_dequant(src.GetPhyAddr(), dst.GetPhyAddr(), static_cast<int32_t>(p.m), static_cast<int32_t>(p.n),
+                                  static_cast<int32_t>(p.calCount), static_cast<int32_t>(detail::DequantDstRow<dstT>(p.n)),
+                                  detail::DTypeOf<dstT>::value, deqScale.GetPhyAddr(), detail::DTypeOf<scaleT>::value, 0.0f,
+                                  detail::CurrentStream()),
+                  "AscendDequant");
+}
+template <typename dstT, typename scaleT, DeQuantMode mode = DeQuantMode::DEQUANT_WITH_SINGLE_ROW>
+inline void AscendDequant(const LocalTensor<dstT>& dst, const LocalTensor<int32_t>& src, const LocalTensor<scaleT>& deqScale,
+                          const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, DequantParams params)
+{
+    AscendDequant<dstT, scaleT, mode>(dst, src, deqScale, params);
+}
+// scalar scale overload
+template <typename dstT, typename scaleT, DeQuantMode mode = DeQuantMode::DEQUANT_WITH_SINGLE_ROW>
+inline void AscendDequant(const LocalTensor<dstT>& dst, const LocalTensor<int32_t>& src, const scaleT deqScale, DequantParams params)
+{
+    const DequantParams p = detail::DequantShape<mode>(params);
+    detail::Latch(ascb200_dequant(src.GetPhyAddr(), dst.GetPhyAddr(), static_cast<int32_t>(p.m), static_cast<int32_t>(p.n),
+                                  static_cast<int32_t>(p.calCount), static_cast<int32_t>(detail::DequantDstRow<dstT>(p.n)),
+                                  detail::DTypeOf<dstT>::value, nullptr, ASCB200_F32, static_cast<float>(deqScale), detail::CurrentStream()),
+                  "AscendDequant");
+}
+
+}  // namespace AscendC

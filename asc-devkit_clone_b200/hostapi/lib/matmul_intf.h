@@ -1,0 +1,237 @@
+// AscendC::Matmul for B200: the reference's operator object (include/adv_api/matmul/matmul.h:54-400,
+// include/adv_api/matmul/matmul_intf.h:46-67) kept on the host.  Set* methods record state; IterateAll
+// launches the tensor-core GEMM through ascb200_gemm.  Buffer-choreography settings of the Ascend
+// implementation (L1/L0 depths, double-buffer switches, iterate order) are accepted and have no effect
+// on results.
+#pragma once
+#include "../kernel_operator.h"
+
+namespace AscendC {
+
+// impl/adv_api/detail/matmul/utils/matmul_type_def.h:37-49
+template <TPosition POSITION, CubeFormat FORMAT, typename TYPE, bool ISTRANS = false>
+struct MatmulType {
+    constexpr static TPosition pos = POSITION;
+    constexpr static CubeFormat format = FORMAT;
+    using T = TYPE;
+    constexpr static bool isTrans = ISTRANS;
+};
+// impl/adv_api/detail/matmul/utils/matmul_type_def.h:114-130: operand type that carries an e8m0 scale tensor
+template <TPosition POSITION, TPosition SCALE_POSITION, CubeFormat FORMAT, typename TYPE, bool ISTRANS = false,
+          TPosition SRCPOS = TPosition::GM, CubeFormat SCALE_FORMAT = FORMAT, bool SCALE_ISTRANS = ISTRANS>
+struct MatmulTypeWithScale : public MatmulType<POSITION, FORMAT, TYPE, ISTRANS> {
+    constexpr static TPosition scalePosition = SCALE_POSITION;
+    constexpr static CubeFormat scaleFormat = SCALE_FORMAT;
+    constexpr static bool isScaleTrans = SCALE_ISTRANS;
+};
+
+// The fields of include/adv_api/matmul/matmul_config.h:143-207 that can change results; the presets keep their names.
+struct MatmulConfig {
+    bool enableRelu = false;       // fixpipe ReLU on the way out
+    bool enableSetBias = true;
+    bool isBiasBatch = true;
+    bool enableQuantVector = true;
+};
+constexpr MatmulConfig CFG_NORM = {};
+constexpr MatmulConfig CFG_MDL = {};
+constexpr MatmulConfig MM_CFG_BB = {};
+constexpr MatmulConfig CFG_IBSHARE_NORM = {};
+
+// impl/adv_api/detail/matmul/utils/matmul_call_back.h:26-39: only the all-default callback set is supported.
+template <void* DataCopyOut = nullptr, void* CopyA1 = nullptr, void* CopyB1 = nullptr>
+struct MatmulCallBackFunc {};
+struct MatmulPolicyDefault {};
+struct MatmulWithScalePolicy {};  // impl/adv_api/detail/matmul/policy/matmul_policy.h:66 (selects the MX scheduler)
+
+namespace detail {
+template <class T> struct KindOf;
+template <> struct KindOf<half> { static constexpr int value = ASCB200_KIND_F16; };
+template <> struct KindOf<bfloat16_t> { static constexpr int value = ASCB200_KIND_BF16; };
+template <> struct KindOf<int8_t> { static constexpr int value = ASCB200_KIND_S8; };
+template <> struct KindOf<fp4x2_e2m1_t> { static constexpr int value = ASCB200_KIND_MXFP4; };
+}  // namespace detail
+
+template <class A_TYPE, class B_TYPE, class C_TYPE, class BIAS_TYPE = C_TYPE, const MatmulConfig& MM_CFG = CFG_NORM,
+          class MM_CB = MatmulCallBackFunc<>, class POLICY = MatmulPolicyDefault>
+class Matmul {
+public:
+    using SrcAT = typename A_TYPE::T;
+    using SrcBT = typename B_TYPE::T;
+    using DstT = typename C_TYPE::T;
+    using BiasT = typename BIAS_TYPE::T;
+    static_assert(std::is_same<SrcAT, SrcBT>::value, "A and B must have the same element type");
+    static_assert(A_TYPE::format == CubeFormat::ND && B_TYPE::format == CubeFormat::ND && C_TYPE::format == CubeFormat::ND,
+                  "only ND (row-major) operands are implemented; use isTrans for the other orientation");
+    static constexpr bool isMx = std::is_same<SrcAT, fp4x2_e2m1_t>::value;
+    static constexpr int elemsPerStorage = isMx ? 2 : 1;  // GlobalTensor offsets count storage units (bytes for packed fp4)
+
+    void Init(const TCubeTiling* cubeTiling, TPipe* tpipe = nullptr)
+    {
+        tiling_ = *cubeTiling;
+        stream_ = tpipe ? tpipe->GetStream() : AscendC::detail::CurrentStream();
+        orgM_ = tiling_.M;
+        orgN_ = tiling_.N;
+        orgKa_ = tiling_.Ka;
+        orgKb_ = tiling_.Kb;
+        orgKc_ = 0;
+        singleM_ = tiling_.singleCoreM;
+        singleN_ = tiling_.singleCoreN;
+        singleK_ = tiling_.singleCoreK;
+        biasOn_ = false;
+        quantVec_ = nullptr;
+        quantScalar_ = 0;
+        quantSet_ = false;
+    }
+    void SetSubBlockIdx(uint8_t) {}
+    void SetOrgShape(int orgM, int orgN, int orgK) { SetOrgShape(orgM, orgN, orgK, orgK, 0); }
+    void SetOrgShape(int orgM, int orgN, int orgKa, int orgKb, int orgKc = 0)
+    {
+        orgM_ = orgM;
+        orgN_ = orgN;
+        orgKa_ = orgKa;
+        orgKb_ = orgKb;
+        orgKc_ = orgKc;
+    }
+    void SetSingleShape(int singleM, int singleN, int singleK)
+    {
+        singleM_ = singleM;
+        singleN_ = singleN;
+        singleK_ = singleK;
+    }
+    void SetTail(int tailM = -1, int tailN = -1, int tailK = -1)
+    {
+        if (tailM != -1) singleM_ = tailM;
+        if (tailN != -1) singleN_ = tailN;
+        if (tailK != -1) singleK_ = tailK;
+    }
+    void SetTensorA(const GlobalTensor<SrcAT>& gm, bool isTransposeA = false)
+    {
+        a_ = gm.GetPhyAddr();
+        transA_ = isTransposeA;
+    }
+    void SetTensorB(const GlobalTensor<SrcBT>& gm, bool isTransposeB = false)
+    {
+        b_ = gm.GetPhyAddr();
+        transB_ = isTransposeB;
+    }
+    void SetTensorScaleA(const GlobalTensor<fp8_e8m0_t>& gm, bool isTransposeScaleA = false)
+    {
+        scaleA_ = gm.GetPhyAddr();
+        transScaleA_ = isTransposeScaleA;
+    }
+    void SetTensorScaleB(const GlobalTensor<fp8_e8m0_t>& gm, bool isTransposeScaleB = true)
+    {
+        scaleB_ = gm.GetPhyAddr();
+        transScaleB_ = isTransposeScaleB;
+    }
+    void SetBias(const GlobalTensor<BiasT>& biasGlobal)
+    {
+        bias_ = biasGlobal.GetPhyAddr();
+        biasOn_ = true;
+    }
+    void DisableBias() { biasOn_ = false; }
+    void ClearBias() { biasOn_ = false; }
+    void SetQuantScalar(const uint64_t quantScalar)
+    {
+        quantScalar_ = quantScalar;
+        quantVec_ = nullptr;
+        quantSet_ = true;
+    }
+    void SetQuantVector(const GlobalTensor<uint64_t>& quantTensor)
+    {
+        quantVec_ = quantTensor.GetPhyAddr();
+        quantSet_ = true;
+    }
+
+    // The whole single-core block in one launch (impl/adv_api/detail/matmul/matmul_impl.h:119-139).
+    template <bool sync = true>
+    void IterateAll(const GlobalTensor<DstT>& gm, uint8_t enAtomic = 0, bool enSequentialWrite = false, bool waitIterateAll = false,
+                    bool fakeMsg = false)
+    {
+        (void)waitIterateAll;
+        (void)fakeMsg;
+        if (enAtomic != 0 || enSequentialWrite) {
+            AscendC::detail::Latch(ASCB200_EUNSUPPORTED, "Matmul::IterateAll (enAtomic / enSequentialWrite)");
+            return;
+        }
+        ascb200_gemm_desc d;
+        std::memset(&d, 0, sizeof(d));
+        d.kind = detail::KindOf<SrcAT>::value;
+        d.m = singleM_;
+        d.n = singleN_;
+        d.k = singleK_;
+        d.a_dev = a_;
+        d.b_dev = b_;
+        d.trans_a = transA_ ? 1 : 0;
+        d.trans_b = transB_ ? 1 : 0;
+        d.lda = transA_ ? orgM_ : orgKa_;
+        d.ldb = transB_ ? orgKb_ : orgN_;
+        d.scale_a_dev = scaleA_;
+        d.scale_b_dev = scaleB_;
+        d.bias_dev = (biasOn_ && MM_CFG.enableSetBias) ? bias_ : nullptr;
+        d.c_dev = gm.GetPhyAddr();
+        d.ldc = orgKc_ > 0 ? orgKc_ : orgN_;
+        d.c_dtype = AscendC::detail::DTypeOf<DstT>::value;
+        d.relu = MM_CFG.enableRelu ? 1 : 0;
+        if (quantSet_) {
+            d.epilogue = ASCB200_EPI_FIXPIPE_QUANT;
+            d.quant_dev = quantVec_;
+            d.quant_scalar = quantScalar_;
+        } else {
+            d.epilogue = ASCB200_EPI_CAST;
+        }
+        if (isMx && (transScaleA_ || !transScaleB_)) {
+            // scales must be [rows, K/32] with K contiguous for both operands
+            AscendC::detail::Latch(ASCB200_EUNSUPPORTED, "Matmul::IterateAll (scale tensor orientation)");
+            return;
+        }
+        AscendC::detail::Latch(ascb200_gemm(&d, stream_), "Matmul::IterateAll");
+        if (sync) done_ = true;
+    }
+
+    // Iterate / GetTensorC pair: the first Iterate() computes the whole block into the tensor that the
+    // following GetTensorC names; later Iterate() calls report completion.
+    template <bool sync = true>
+    bool Iterate(bool enPartialSum = false)
+    {
+        (void)enPartialSum;
+        if (iterPending_) {
+            iterPending_ = false;
+            return false;
+        }
+        iterPending_ = true;
+        return true;
+    }
+    template <bool sync = true>
+    void GetTensorC(const GlobalTensor<DstT>& gm, uint8_t enAtomic = 0, bool enSequentialWrite = false)
+    {
+        if (iterPending_) IterateAll<sync>(gm, enAtomic, enSequentialWrite);
+    }
+    void End() {}
+    void SetLocalWorkspace(const LocalTensor<uint8_t>&) {}
+    int GetLastError() const { return AscendC::GetLastError(); }
+
+private:
+    TCubeTiling tiling_{};
+    void* stream_ = nullptr;
+    const SrcAT* a_ = nullptr;
+    const SrcBT* b_ = nullptr;
+    const fp8_e8m0_t* scaleA_ = nullptr;
+    const fp8_e8m0_t* scaleB_ = nullptr;
+    const BiasT* bias_ = nullptr;
+    const uint64_t* quantVec_ = nullptr;
+    uint64_t quantScalar_ = 0;
+    bool transA_ = false, transB_ = false, transScaleA_ = false, transScaleB_ = true;
+    bool biasOn_ = false, quantSet_ = false, done_ = false, iterPending_ = false;
+    int orgM_ = 0, orgN_ = 0, orgKa_ = 0, orgKb_ = 0, orgKc_ = 0, singleM_ = 0, singleN_ = 0, singleK_ = 0;
+};
+
+}  // namespace AscendC
+
+// include/adv_api/matmul/matmul_intf.h:40-41 / impl/adv_api/detail/kfc/kfc_register_obj.h:142-162
+#define REGIST_MATMUL_OBJ(tpipe, workspace, obj, tiling) \
+    do {                                                 \
+        (void)(workspace);                               \
+        (obj).SetSubBlockIdx(0);                         \
+        (obj).Init((tiling), (tpipe));                   \
+    } while (0)

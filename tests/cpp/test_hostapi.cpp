@@ -1,0 +1,311 @@
+// Drives the C++ mirror of the reference operator API on a B200, following the call sequences of the
+// reference examples (Matmul: examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul/matmul.asc:95-184;
+// matmul_quant; SoftMax; AscendQuant; AscendDequant) and checks the results on the host.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <random>
+#include <vector>
+
+#include "lib/matmul_intf.h"
+#include "tiling/tiling_api.h"
+
+static int g_fail = 0;
+#define CHECK(cond, ...)                      \
+    do {                                      \
+        if (!(cond)) {                        \
+            std::printf("FAIL %s:%d: ", __FILE__, __LINE__); \
+            std::printf(__VA_ARGS__);         \
+            std::printf("\n");                \
+            ++g_fail;                         \
+        }                                     \
+    } while (0)
+
+template <class T>
+struct DevBuf {
+    T* p = nullptr;
+    size_t n = 0;
+    explicit DevBuf(size_t count) : n(count) { ascb200_malloc(reinterpret_cast<void**>(&p), count * sizeof(T)); }
+    explicit DevBuf(const std::vector<T>& h) : DevBuf(h.size()) { Upload(h); }
+    ~DevBuf() { ascb200_free(p); }
+    void Upload(const std::vector<T>& h)
+    {
+        ascb200_memcpy_h2d(p, h.data(), h.size() * sizeof(T), nullptr);
+        ascb200_stream_sync(nullptr);
+    }
+    std::vector<T> Download() const
+    {
+        std::vector<T> h(n);
+        ascb200_memcpy_d2h(h.data(), p, n * sizeof(T), nullptr);
+        ascb200_stream_sync(nullptr);
+        return h;
+    }
+};
+
+// The example's kernel class, as host code (matmul.asc:41-141): one "core" owns the whole problem.
+template <typename AType, typename BType, typename CType, typename BiasType>
+class MatmulKernel {
+public:
+    void Init(GM_ADDR a, GM_ADDR b, GM_ADDR bias, GM_ADDR c, const TCubeTiling& tiling)
+    {
+        this->tiling = tiling;
+        aGlobal.SetGlobalBuffer(reinterpret_cast<AType*>(a), tiling.M * tiling.Ka);
+        bGlobal.SetGlobalBuffer(reinterpret_cast<BType*>(b), tiling.Kb * tiling.N);
+        cGlobal.SetGlobalBuffer(reinterpret_cast<CType*>(c), tiling.M * tiling.N);
+        biasGlobal.SetGlobalBuffer(reinterpret_cast<BiasType*>(bias), tiling.N);
+        const int64_t blockIdx = AscendC::GetBlockIdx();
+        const auto mSingleBlocks = (tiling.M + tiling.singleCoreM - 1) / tiling.singleCoreM;
+        const auto mCoreIndx = blockIdx % mSingleBlocks, nCoreIndx = blockIdx / mSingleBlocks;
+        aGlobal = aGlobal[mCoreIndx * tiling.Ka * tiling.singleCoreM];
+        bGlobal = bGlobal[nCoreIndx * tiling.singleCoreN];
+        cGlobal = cGlobal[mCoreIndx * tiling.N * tiling.singleCoreM + nCoreIndx * tiling.singleCoreN];
+        biasGlobal = biasGlobal[nCoreIndx * tiling.singleCoreN];
+    }
+    void Process(AscendC::TPipe* pipe)
+    {
+        (void)pipe;
+        matmulObj.SetTensorA(aGlobal, false);
+        matmulObj.SetTensorB(bGlobal, false);
+        if (tiling.isBias) matmulObj.SetBias(biasGlobal);
+        matmulObj.IterateAll(cGlobal);
+        matmulObj.End();
+    }
+    AscendC::Matmul<AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, AType>, AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, BType>,
+                    AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, CType>, AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, BiasType>,
+                    AscendC::CFG_NORM>
+        matmulObj;
+
+private:
+    AscendC::GlobalTensor<AType> aGlobal;
+    AscendC::GlobalTensor<BType> bGlobal;
+    AscendC::GlobalTensor<CType> cGlobal;
+    AscendC::GlobalTensor<BiasType> biasGlobal;
+    TCubeTiling tiling;
+};
+
+static void TestMatmulFp16()
+{
+    const int M = 512, N = 1024, K = 512;  // the baseline fp16 configuration
+    std::mt19937 rng(0xA5C0);
+    std::uniform_real_distribution<float> u(-1.f, 1.f);
+    std::vector<half> a(M * K), b(K * N);
+    std::vector<float> bias(N);
+    for (auto& v : a) v = half(u(rng));
+    for (auto& v : b) v = half(u(rng));
+    for (auto& v : bias) v = u(rng);
+
+    // host tiling exactly as the example's GenerateTiling (matmul.asc:158-184)
+    auto* platform = platform_ascendc::PlatformAscendCManager::GetInstance();
+    optiling::TCubeTiling tilingData;
+    matmul_tiling::MultiCoreMatmulTiling tilingApi(*platform);
+    tilingApi.SetDim(1);
+    tilingApi.SetAType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_FLOAT16, false);
+    tilingApi.SetBType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_FLOAT16, false);
+    tilingApi.SetCType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_FLOAT);
+    tilingApi.SetBiasType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_FLOAT);
+    tilingApi.SetOrgShape(M, N, K);
+    tilingApi.SetShape(M, N, K);
+    tilingApi.EnableBias(true);
+    tilingApi.SetBufferSpace(-1, -1, -1);
+    CHECK(tilingApi.GetTiling(tilingData) == 0, "GetTiling");
+    std::vector<uint8_t> tilingBuf(tilingData.GetDataSize());
+    tilingData.SaveToBuffer(tilingBuf.data(), tilingBuf.size());
+
+    DevBuf<half> dA(a), dB(b);
+    DevBuf<float> dBias(bias), dC(static_cast<size_t>(M) * N);
+    {   // the example's kernel body (matmul.asc:144-156)
+        TCubeTiling tiling;
+        std::memcpy(&tiling, tilingBuf.data(), sizeof(tiling));
+        AscendC::TPipe pipe;
+        MatmulKernel<half, half, float, float> kernel;
+        REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), kernel.matmulObj, &tiling);
+        kernel.Init(reinterpret_cast<GM_ADDR>(dA.p), reinterpret_cast<GM_ADDR>(dB.p), reinterpret_cast<GM_ADDR>(dBias.p),
+                    reinterpret_cast<GM_ADDR>(dC.p), tiling);
+        kernel.Process(&pipe);
+    }
+    CHECK(AscendC::GetLastError() == 0, "operator error %d", AscendC::GetLastError());
+    const std::vector<float> c = dC.Download();
+    std::vector<float> af(a.begin(), a.end()), bf(b.begin(), b.end());
+    double worst = 0;
+    for (int m = 0; m < M; m += 7)
+        for (int n = 0; n < N; n += 5) {
+            float acc = bias[n];
+            for (int k = 0; k < K; ++k) acc += af[m * K + k] * bf[k * N + n];
+            const double err = std::fabs(c[static_cast<size_t>(m) * N + n] - acc);
+            worst = std::max(worst, err);
+            if (err > 1e-3 + 1e-2 * std::fabs(acc)) {
+                CHECK(false, "C[%d,%d] = %f, expected %f", m, n, c[static_cast<size_t>(m) * N + n], acc);
+                return;
+            }
+        }
+    std::printf("matmul fp16 512x512x1024+bias: max abs err %.3g\n", worst);
+}
+
+static void TestMatmulQuant()
+{
+    // matmul_quant example flow: int8 x int8 -> half through SetQuantVector (per-channel DEQF16) and SetQuantScalar
+    const int M = 256, N = 384, K = 256;
+    std::mt19937 rng(7);
+    std::uniform_int_distribution<int> ui(-10, 9);
+    std::uniform_real_distribution<float> us(0.1f, 2.0f);
+    std::vector<int8_t> a(M * K), b(K * N);
+    for (auto& v : a) v = static_cast<int8_t>(ui(rng));
+    for (auto& v : b) v = static_cast<int8_t>(ui(rng));
+    std::vector<uint64_t> q(N);
+    std::vector<float> alpha(N);
+    for (int n = 0; n < N; ++n) {
+        float s = us(rng);
+        uint32_t bits;
+        std::memcpy(&bits, &s, 4);
+        q[n] = bits;  // the unit keeps bits [31:13]
+        bits &= 0xFFFFE000u;
+        std::memcpy(&alpha[n], &bits, 4);
+    }
+    matmul_tiling::MatmulApiTiling api;
+    api.SetAType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_INT8);
+    api.SetBType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_INT8);
+    api.SetCType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_FLOAT16);
+    api.SetShape(M, N, K);
+    api.SetOrgShape(M, N, K);
+    api.SetDequantType(matmul_tiling::DequantType::TENSOR);
+    TCubeTiling tiling;
+    CHECK(api.GetTiling(tiling) == 0, "GetTiling");
+
+    DevBuf<int8_t> dA(a), dB(b);
+    DevBuf<uint64_t> dQ(q);
+    DevBuf<half> dC(static_cast<size_t>(M) * N);
+    AscendC::TPipe pipe;
+    using A = AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, int8_t>;
+    using C = AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, half>;
+    using B32 = AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, int32_t>;
+    AscendC::Matmul<A, A, C, B32> mm;
+    REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, &tiling);
+    AscendC::GlobalTensor<int8_t> ga, gb;
+    AscendC::GlobalTensor<uint64_t> gq;
+    AscendC::GlobalTensor<half> gc;
+    ga.SetGlobalBuffer(dA.p, a.size());
+    gb.SetGlobalBuffer(dB.p, b.size());
+    gq.SetGlobalBuffer(dQ.p, q.size());
+    gc.SetGlobalBuffer(dC.p, dC.n);
+    for (int pass = 0; pass < 2; ++pass) {
+        mm.SetTensorA(ga);
+        mm.SetTensorB(gb);
+        if (pass == 0) mm.SetQuantVector(gq);
+        else mm.SetQuantScalar(q[3]);
+        mm.IterateAll(gc);
+        mm.End();
+        ascb200_stream_sync(nullptr);
+        const std::vector<half> c = dC.Download();
+        int bad = 0;
+        for (int m = 0; m < M; m += 3)
+            for (int n = 0; n < N; ++n) {
+                int32_t acc = 0;
+                for (int k = 0; k < K; ++k) acc += static_cast<int32_t>(a[m * K + k]) * b[k * N + n];
+                const half expect(static_cast<float>(acc) * (pass == 0 ? alpha[n] : alpha[3]));
+                if (c[static_cast<size_t>(m) * N + n].bits != expect.bits) ++bad;
+            }
+        CHECK(bad == 0, "quant matmul pass %d: %d mismatches", pass, bad);
+    }
+    CHECK(AscendC::GetLastError() == 0, "operator error %d", AscendC::GetLastError());
+}
+
+static void TestSoftmaxQuantDequant()
+{
+    const uint32_t M = 64, K = 2048;
+    std::mt19937 rng(11);
+    std::normal_distribution<float> nd(0.f, 3.f);
+    std::vector<half> x(M * K);
+    for (auto& v : x) v = half(nd(rng));
+    DevBuf<half> dX(x), dY(M * K);
+    DevBuf<float> dSum(M * 8), dMax(M * 8);
+    ::SoftMaxTiling tiling;
+    ge::Shape shape(std::vector<int64_t>{M, K});
+    AscendC::SoftMaxTilingFunc(shape, sizeof(half), AscendC::GetSoftMaxMaxTmpSize(shape, sizeof(half), false), tiling);
+    AscendC::TPipe pipe;
+    AscendC::LocalTensor<half> src(dX.p, M * K), dst(dY.p, M * K);
+    AscendC::LocalTensor<float> sum(dSum.p, M * 8), mx(dMax.p, M * 8);
+    AscendC::SoftMaxShapeInfo info{M, K, M, K};
+    AscendC::SoftMax<half>(dst, sum, mx, src, tiling, info);
+    // per-channel AscendQuant of the result
+    std::vector<half> scale(K);
+    std::uniform_real_distribution<float> u(0.5f, 2.0f);
+    for (auto& s : scale) s = half(127.0f / u(rng));
+    DevBuf<half> dScale(scale);
+    DevBuf<int8_t> dQ(M * K);
+    AscendC::LocalTensor<half> scaleT(dScale.p, K);
+    AscendC::LocalTensor<int8_t> qT(dQ.p, M * K);
+    AscendC::AscendQuant<half>(qT, dst, scaleT, half(0.0f), K, M * K);
+    ascb200_stream_sync(nullptr);
+    CHECK(AscendC::GetLastError() == 0, "operator error %d", AscendC::GetLastError());
+    const auto y = dY.Download();
+    const auto s = dSum.Download();
+    const auto mxh = dMax.Download();
+    const auto q = dQ.Download();
+    int bad = 0, badq = 0;
+    for (uint32_t r = 0; r < M; ++r) {
+        float m = -INFINITY;
+        for (uint32_t k = 0; k < K; ++k) m = std::max(m, static_cast<float>(x[r * K + k]));
+        double tot = 0;
+        for (uint32_t k = 0; k < K; ++k) tot += std::exp(static_cast<double>(static_cast<float>(x[r * K + k]) - m));
+        if (mxh[r * 8] != m || mxh[r * 8 + 7] != m || std::fabs(s[r * 8] - tot) > 1e-5 * tot) ++bad;
+        for (uint32_t k = 0; k < K; ++k) {
+            const double ref = std::exp(static_cast<double>(static_cast<float>(x[r * K + k]) - m)) / tot;
+            const float got = y[r * K + k];
+            if (std::fabs(got - ref) > 1e-3 * ref + 6e-8) ++bad;
+            // AscendQuant in fp16: half(y * scale) then round to nearest even, saturating
+            const half prod(static_cast<float>(y[r * K + k]) * static_cast<float>(scale[k]));
+            const float pf = prod;
+            const int expect = static_cast<int>(std::max(-128.0f, std::min(127.0f, std::nearbyint(pf))));
+            if (q[r * K + k] != expect) ++badq;
+        }
+    }
+    CHECK(bad == 0, "softmax: %d bad values", bad);
+    CHECK(badq == 0, "AscendQuant: %d mismatches", badq);
+
+    // AscendDequant: int32 [m, n] x fp32 scale[n] -> fp32, the dequant example's shape
+    const uint32_t dm = 128, dn = 32;
+    std::vector<int32_t> src32(dm * dn);
+    std::vector<float> dscale(dn);
+    std::uniform_int_distribution<int> ui(-10, 9);
+    std::uniform_real_distribution<float> us(-100.f, 100.f);
+    for (auto& v : src32) v = ui(rng);
+    for (auto& v : dscale) v = us(rng);
+    DevBuf<int32_t> dSrc(src32);
+    DevBuf<float> dDs(dscale), dOut(dm * dn);
+    AscendC::LocalTensor<int32_t> srcT(dSrc.p, dm * dn);
+    AscendC::LocalTensor<float> scT(dDs.p, dn), outT(dOut.p, dm * dn);
+    AscendC::AscendDequant<float, float>(outT, srcT, scT, AscendC::DequantParams{dm, dn, dn});
+    ascb200_stream_sync(nullptr);
+    const auto out = dOut.Download();
+    int badd = 0;
+    for (uint32_t i = 0; i < dm * dn; ++i)
+        if (out[i] != static_cast<float>(src32[i]) * dscale[i % dn]) ++badd;
+    CHECK(badd == 0, "AscendDequant: %d mismatches", badd);
+}
+
+static void TestErrorLatch()
+{
+    AscendC::ClearLastError();
+    AscendC::LocalTensor<half> none;
+    AscendC::LocalTensor<float> nonef;
+    ::SoftMaxTiling tiling{};
+    tiling.srcM = 4;
+    tiling.srcK = 64;
+    AscendC::SoftMax<half>(none, nonef, nonef, none, tiling);  // null tensors: latched, no crash, no launch
+    CHECK(AscendC::GetLastError() == ASCB200_EINVAL, "expected EINVAL, got %d", AscendC::GetLastError());
+    AscendC::ClearLastError();
+}
+
+int main()
+{
+    if (ascb200_init(0) != 0) {
+        std::printf("no B200 available\n");
+        return 2;
+    }
+    TestMatmulFp16();
+    TestMatmulQuant();
+    TestSoftmaxQuantDequant();
+    TestErrorLatch();
+    std::printf(g_fail ? "%d checks failed\n" : "hostapi ok\n", g_fail);
+    return g_fail ? 1 : 0;
+}
