@@ -87,25 +87,7 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # workloads
 # ------------------------------------------------------------------------------------------------
-def dirichlet_counts(groups, total, seed):
-    """Deterministic Dirichlet(1) split of `total` rows: normalised Exp(1) draws, floor, remainder by largest fraction."""
-    e = np.random.default_rng(seed).exponential(1.0, groups)
-    w = e / e.sum() * total
-    c = np.floor(w).astype(np.int64)
-    rem = total - int(c.sum())
-    c[np.argsort(-(w - c))[:rem]] += 1
-    return c
-
-
-def lpt_partition(counts, parts):
-    """Greedy longest-processing-time assignment of groups to ranks by row count."""
-    load = [0] * parts
-    owner = [[] for _ in range(parts)]
-    for g in np.argsort(-counts, kind="stable"):
-        r = int(np.argmin(load))
-        owner[r].append(int(g))
-        load[r] += int(counts[g])
-    return [sorted(o) for o in owner]
+from sharding import dirichlet_counts, lpt_partition  # noqa: E402
 
 
 class Workload:
