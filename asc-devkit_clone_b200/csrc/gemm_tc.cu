@@ -70,12 +70,13 @@ struct GemmParams {
 template <int KIND, int BLOCK_N>
 struct Cfg {
     static constexpr int B_TILE_BYTES = BLOCK_N * ROW_BYTES;
-    static constexpr int SF_BYTES = KIND == KIND_MXF4 ? (2 + 2 * (BLOCK_N / 128)) * SF_CHUNK_BYTES : 0;
+    static constexpr int SF_B_BLOCKS = (BLOCK_N + 127) / 128;  // 128-row scale blocks that one B tile touches
+    static constexpr int SF_BYTES = KIND == KIND_MXF4 ? (2 + 2 * SF_B_BLOCKS) * SF_CHUNK_BYTES : 0;
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + SF_BYTES;
     static constexpr int NUM_STAGES = std::min(8, (220 * 1024) / STAGE_BYTES);
-    static constexpr int ACC_STAGES = (KIND == KIND_MXF4 && BLOCK_N == 256) ? 1 : 2;
+    static constexpr int ACC_STAGES = (KIND == KIND_MXF4 && BLOCK_N == 256) ? 1 : 2;  // 2 x 256 accumulator columns would leave no TMEM for scales
     static constexpr int ACC_COLS = ACC_STAGES * BLOCK_N;
-    static constexpr int SF_COLS_PER_STAGE = 32;  // 8 for A + up to 16 for B, padded
+    static constexpr int SF_COLS_PER_STAGE = 24;  // 8 for A + 16 for B
     static constexpr int SF_COL0 = ACC_COLS;
     static constexpr int TMEM_NEED = ACC_COLS + (KIND == KIND_MXF4 ? NUM_STAGES * SF_COLS_PER_STAGE : 0);
     static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
@@ -455,7 +456,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         const size_t kc = static_cast<size_t>(kb) * 2;
                         bulk_load(ssf, p.sfa + (static_cast<size_t>(t.row0 / 128) * p.sf_kc + kc) * SF_CHUNK_BYTES, 2 * SF_CHUNK_BYTES, bar);
 #pragma unroll
-                        for (int rb = 0; rb < BLOCK_N / 128; ++rb)
+                        for (int rb = 0; rb < C::SF_B_BLOCKS; ++rb)
                             bulk_load(ssf + (1 + rb) * 2 * SF_CHUNK_BYTES,
                                       p.sfb + (static_cast<size_t>(t.n0 / 128 + rb) * p.sf_kc + kc) * SF_CHUNK_BYTES, 2 * SF_CHUNK_BYTES, bar);
                     }
@@ -498,20 +499,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         const uint32_t ssf = sb + C::B_TILE_BYTES;
                         const uint32_t sf_t = tmem_base + C::SF_COL0 + stage * C::SF_COLS_PER_STAGE;
                         // chunk order in shared memory: A kc0, A kc1, then per 128-column block of B: kc0, kc1
+#ifdef ASCB200_PROBE
+                        if (!(p.probe & 64) || kb == 0)
+#endif
+                        {
                         tmem_cp_32x128b_warpx4(sf_t + 0, desc_at(sf_hi, ssf));
+#ifdef ASCB200_PROBE
+                        if (!(p.probe & 128))
+#endif
+                        {
                         tmem_cp_32x128b_warpx4(sf_t + 4, desc_at(sf_hi, ssf + SF_CHUNK_BYTES));
 #pragma unroll
-                        for (int rb = 0; rb < BLOCK_N / 128; ++rb) {
+                        for (int rb = 0; rb < C::SF_B_BLOCKS; ++rb) {
                             // TMEM columns of B scales: [8 + kc*8 + rb*4]
                             tmem_cp_32x128b_warpx4(sf_t + 8 + 0 * 8 + rb * 4, desc_at(sf_hi, ssf + (2 + rb * 2) * SF_CHUNK_BYTES));
                             tmem_cp_32x128b_warpx4(sf_t + 8 + 1 * 8 + rb * 4, desc_at(sf_hi, ssf + (3 + rb * 2) * SF_CHUNK_BYTES));
+                        }
+                        }
                         }
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const uint32_t sf_id = (j & 1) * 2u;
                             const uint32_t idesc = p.idesc | (sf_id << 4) | (sf_id << 29);
+                            // a 192-wide tile may start in the middle of a 128-row scale block: 32 rows per TMEM column
                             mma_mxf4(d_tmem, desc_at(a_hi, sa + j * 32), desc_at(b_hi, sb + j * 32), idesc, sf_t + (j >> 1) * 4,
-                                     sf_t + 8 + (j >> 1) * 8, (kb | j) != 0 ? 1u : 0u);
+                                     sf_t + 8 + (j >> 1) * 8 + (t.n0 % 128) / 32, (kb | j) != 0 ? 1u : 0u);
                         }
                     } else
 #ifdef ASCB200_PROBE
@@ -523,6 +535,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             mma_ss<KIND>(d_tmem, desc_at(a_hi, sa + j * a_kstep), desc_at(b_hi, sb + j * b_kstep), p.idesc,
                                          (kb | j) != 0 ? 1u : 0u);
                     }
+#ifdef ASCB200_PROBE
+                    if (p.probe & 256) mbar_arrive(smem_u32(&empty_bar[stage])); else
+#endif
                     tc_commit(smem_u32(&empty_bar[stage]));          // stage reusable once these MMAs have read it
                     if (kb == p.num_k_blocks - 1) tc_commit(smem_u32(&acc_full_bar[acc_stage]));
                 }
@@ -561,13 +576,211 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __syncthreads();
     if (*abort_word) {
         // give copies that may still be in flight time to land before the CTA's shared memory is released
-        const unsigned long long t0 = global_ns();
-        while (global_ns() - t0 < 200000ull) __nanosleep(1000);
+        const long long t0 = clock64();
+        while (clock64() - t0 < 400000ll) __nanosleep(1000);
         __syncthreads();
     }
     if (warp == 2) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---- the CTA-pair kernel -----------------------------------------------------------------------
+// Same roles and pipeline as gemm_tc_kernel, but two CTAs of a cluster share every MMA
+// (tcgen05.mma.cta_group::2): the pair computes a 256 x BLOCK_N tile, each CTA loads its own 128
+// rows of A and BLOCK_N/2 rows of B, so every SM reads a third less shared memory per instruction
+// and fetches half of B from L2.  The even CTA issues the MMAs; completion is signalled to both
+// CTAs with multicast commits; epilogue warps of both CTAs release the accumulator stage on the
+// leader's barrier.  Plain (non-grouped) problems only.
+template <int KIND, int BLOCK_N>
+struct Cfg2 {
+    static constexpr int B_TILE_BYTES = (BLOCK_N / 2) * ROW_BYTES;
+    static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+    static constexpr int NUM_STAGES = std::min(8, (216 * 1024) / STAGE_BYTES);
+    static constexpr int ACC_STAGES = 2;
+    static constexpr int TMEM_COLS = 512;
+    static_assert(ACC_STAGES * BLOCK_N <= 512, "TMEM budget");
+    static constexpr int BLOCK_K = KIND == KIND_F16 ? 64 : 128;
+    static constexpr int UMMA_K = BLOCK_K / 4;
+    static constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+template <int KIND, int BLOCK_N>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p)
+{
+    using C = Cfg2<KIND, BLOCK_N>;
+    constexpr int PAIR_M = 2 * BLOCK_M;
+    extern __shared__ uint8_t smem_raw[];
+    // both CTAs must use identical offsets: the dynamic shared memory window starts at the same offset in each
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* tiles = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::NUM_STAGES * C::STAGE_BYTES);
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + C::NUM_STAGES;
+    uint64_t* acc_full_bar = bars + 2 * C::NUM_STAGES;
+    uint64_t* acc_empty_bar = acc_full_bar + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+    volatile uint32_t* abort_word = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();   // 0 = leader
+    const int cluster_id = blockIdx.x >> 1;
+    const int num_clusters = gridDim.x >> 1;
+    const int num_n = (p.n + BLOCK_N - 1) / BLOCK_N;
+    const int num_m = (p.m + PAIR_M - 1) / PAIR_M;
+    const int total_tiles = num_m * num_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::NUM_STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&acc_full_bar[s]), 1);
+            mbar_init(smem_u32(&acc_empty_bar[s]), 2 * NUM_EPI_WARPS);  // epilogue warps of both CTAs
+        }
+        *abort_word = 0u;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 2) {
+        tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers exist before anything can arrive on them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ===== TMA producer (both CTAs) =====
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters) {
+            const int row0 = (tile % num_m) * PAIR_M + static_cast<int>(rank) * BLOCK_M;
+            const int n0 = (tile / num_m) * BLOCK_N + static_cast<int>(rank) * (BLOCK_N / 2);
+            for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_word, p.status);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t own_bar = smem_u32(&full_bar[stage]);
+                    const uint32_t bar = own_bar & kPeerBitMask;  // the leader's barrier counts both CTAs' bytes
+                    const uint32_t sa = smem_u32(tiles + stage * C::STAGE_BYTES);
+                    const uint32_t sb = sa + A_TILE_BYTES;
+                    if (rank == 0) mbar_expect_tx(own_bar, 2 * C::STAGE_BYTES);
+                    const int k0 = kb * C::BLOCK_K;
+                    constexpr int MN_PER_BOX = KIND == KIND_F16 ? 64 : 128;
+                    constexpr int BOX_BYTES = C::BLOCK_K * ROW_BYTES;
+                    if (!p.a_mn) {
+                        tma_load_3d_pair(sa, &tmap_a, k0, row0, 0, bar);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BLOCK_M / MN_PER_BOX; ++j) tma_load_3d_pair(sa + j * BOX_BYTES, &tmap_a, row0 + j * MN_PER_BOX, k0, 0, bar);
+                    }
+                    if (!p.b_mn) {
+                        tma_load_3d_pair(sb, &tmap_b, k0, n0, 0, bar);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < (BLOCK_N / 2) / MN_PER_BOX; ++j) tma_load_3d_pair(sb + j * BOX_BYTES, &tmap_b, n0 + j * MN_PER_BOX, k0, 0, bar);
+                    }
+                }
+                __syncwarp();
+                if (++stage == C::NUM_STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+        // drain: every stage's last release (a multicast commit from the leader) must have landed in
+        // this CTA's shared memory before the CTA may exit
+        for (int i = 0; ok && i < C::NUM_STAGES; ++i) {
+            ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_word, p.status);
+            if (++stage == C::NUM_STAGES) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+    } else if (warp == 1 && rank == 0) {
+        // ===== MMA issuer (leader CTA only) =====
+        int stage = 0, acc_iter = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const uint64_t a_hi = p.a_mn ? smem_desc_sw128(C::BLOCK_K * ROW_BYTES, 1024) : smem_desc_sw128(16, 1024);
+        const uint64_t b_hi = p.b_mn ? smem_desc_sw128(C::BLOCK_K * ROW_BYTES, 1024) : smem_desc_sw128(16, 1024);
+        const uint32_t a_kstep = p.a_mn ? C::UMMA_K * ROW_BYTES : 32;
+        const uint32_t b_kstep = p.b_mn ? C::UMMA_K * ROW_BYTES : 32;
+        for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters, ++acc_iter) {
+            const int acc_stage = acc_iter & 1;
+            const uint32_t acc_phase = (acc_iter >> 1) & 1u;
+            ok = mbar_wait(smem_u32(&acc_empty_bar[acc_stage]), acc_phase ^ 1u, abort_word, p.status);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
+            for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_word, p.status);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t sa = smem_u32(tiles + stage * C::STAGE_BYTES);
+                    const uint32_t sb = sa + A_TILE_BYTES;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        mma_ss_pair<KIND>(d_tmem, desc_at(a_hi, sa + j * a_kstep), desc_at(b_hi, sb + j * b_kstep), p.idesc, (kb | j) != 0 ? 1u : 0u);
+                    tc_commit_pair(smem_u32(&empty_bar[stage]));
+                    if (kb == p.num_k_blocks - 1) tc_commit_pair(smem_u32(&acc_full_bar[acc_stage]));
+                }
+                __syncwarp();
+                if (++stage == C::NUM_STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ===== epilogue (both CTAs, each for its own 128 rows) =====
+        const int quad = warp & 3;
+        const int half = (warp - 4) >> 2;
+        constexpr int CHUNKS = BLOCK_N / 32;
+        const int chunk0 = half * (CHUNKS / 2), chunk1 = chunk0 + CHUNKS / 2;
+        int acc_iter = 0;
+        bool ok = true;
+        for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters, ++acc_iter) {
+            const int acc_stage = acc_iter & 1;
+            const uint32_t acc_phase = (acc_iter >> 1) & 1u;
+            ok = mbar_wait_relaxed(smem_u32(&acc_full_bar[acc_stage]), acc_phase, abort_word, p.status);
+            if (!ok) break;
+            tc_fence_after();
+            TileInfo t;
+            t.group = 0;
+            t.row0 = (tile % num_m) * PAIR_M + static_cast<int>(rank) * BLOCK_M;
+            t.row_end = p.m;
+            t.n0 = (tile / num_m) * BLOCK_N;
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc_stage * BLOCK_N;
+            epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, t_addr, quad, lane, chunk0, chunk1);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(smem_u32(&acc_empty_bar[acc_stage]) & kPeerBitMask);
+        }
+    }
+
+    // ===== teardown =====
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_word) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 400000ll) __nanosleep(1000);
+        __syncthreads();
+    }
+    cluster_sync_all();  // neither CTA leaves while the other may still signal into its shared memory
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
     }
 }
 
@@ -642,6 +855,22 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
         configured[dev & 15] = true;
     }
     gemm_tc_kernel<KIND, BLOCK_N><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
+    ASCB200_CUDA(cudaGetLastError());
+    return ASCB200_OK;
+}
+
+template <int KIND, int BLOCK_N>
+int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int clusters, cudaStream_t stream)
+{
+    using C = Cfg2<KIND, BLOCK_N>;
+    static bool configured[16] = {};
+    int dev = 0;
+    ASCB200_CUDA(cudaGetDevice(&dev));
+    if (!configured[dev & 15]) {
+        ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        configured[dev & 15] = true;
+    }
+    gemm_tc_pair_kernel<KIND, BLOCK_N><<<2 * clusters, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
     ASCB200_CUDA(cudaGetLastError());
     return ASCB200_OK;
 }
@@ -739,9 +968,18 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         const long long num_m = grouped ? (m + BLOCK_M - 1) / BLOCK_M + groups : (m + BLOCK_M - 1) / BLOCK_M;
         while (block_n > 64 && (n <= block_n / 2 || num_m * ((n + block_n - 1) / block_n) < sm_count)) block_n /= 2;
         if (kind == ASCB200_KIND_MXFP4 && block_n < 128) block_n = 128;
+        // fp4 at 256 columns cannot double-buffer its accumulators (TMEM also holds the scales): 192 can
+        if (kind == ASCB200_KIND_MXFP4 && block_n == 256) block_n = 192;
         // an N-contiguous 8-bit B tile is fetched in boxes of 128 columns (one 128-byte swizzle row)
         if (kind == ASCB200_KIND_S8 && !d->trans_b && block_n < 128) block_n = 128;
     }
+
+    // CTA pairs (256 x 256 tiles) for plain fp16 / bf16 / int8 problems with enough tiles to fill every pair of SMs
+    const int pair_clusters = sm_count / 2;
+    const bool use_pair = !grouped && kind != ASCB200_KIND_MXFP4 && block_n == 256 &&
+                          static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((n + 255) / 256) >= pair_clusters &&
+                          !(getenv("ASCB200_NO_PAIR") && getenv("ASCB200_NO_PAIR")[0] == '1');
+    const int b_box_rows = use_pair ? block_n / 2 : block_n;
 
     CUtensorMap ta, tb;
     int rc;
@@ -749,7 +987,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     else rc = make_map(&ta, dt, esz, d->a_dev, m, k, 1, lda, static_cast<uint64_t>(lda) * k, row_elems, block_k);
     if (rc != ASCB200_OK) return rc;
     const uint64_t g3 = grouped ? groups : 1;
-    if (d->trans_b) rc = make_map(&tb, dt, esz, d->b_dev, k / epb, n, g3, ldb / epb, static_cast<uint64_t>(ldb / epb) * n, row_elems, block_n);
+    if (d->trans_b) rc = make_map(&tb, dt, esz, d->b_dev, k / epb, n, g3, ldb / epb, static_cast<uint64_t>(ldb / epb) * n, row_elems, b_box_rows);
     else rc = make_map(&tb, dt, esz, d->b_dev, n, k, g3, ldb, static_cast<uint64_t>(ldb) * k, row_elems, block_k);
     if (rc != ASCB200_OK) return rc;
 
@@ -773,7 +1011,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         // re-tile both scale tensors into scratch (layout documented at retile_scales_kernel)
         const int ks = k / 32;
         const int kc = 2 * p.num_k_blocks;
-        const int rba = (m + 127) / 128, rbb = (n + 255) / 256 * 2;
+        const int rba = (m + 127) / 128, rbb = (n + 127) / 128 + 2;  // B tiles may read up to two blocks past the last row
         const size_t bytes_a = static_cast<size_t>(rba) * kc * SF_CHUNK_BYTES, bytes_b = static_cast<size_t>(rbb) * kc * SF_CHUNK_BYTES;
         uint8_t* sfa;
         if (fixed) {
@@ -800,6 +1038,17 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     const int grid = static_cast<int>(std::min<long long>(max_tiles, sm_count));
 
     const uint32_t a_mn = p.a_mn, b_mn = p.b_mn;
+    if (use_pair) {
+        const long long pair_tiles = static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((n + 255) / 256);
+        const int clusters = static_cast<int>(std::min<long long>(pair_tiles, pair_clusters));
+        if (kind == ASCB200_KIND_S8) {
+            p.idesc = make_idesc(2, 1, 1, a_mn, b_mn, 2 * BLOCK_M, 256);
+            return launch_gemm_pair<KIND_I8, 256>(ta, tb, p, clusters, stream);
+        }
+        const uint32_t fmt = kind == ASCB200_KIND_BF16 ? 1u : 0u;
+        p.idesc = make_idesc(1, fmt, fmt, a_mn, b_mn, 2 * BLOCK_M, 256);
+        return launch_gemm_pair<KIND_F16, 256>(ta, tb, p, clusters, stream);
+    }
     switch (kind) {
         case ASCB200_KIND_F16:
         case ASCB200_KIND_BF16: {
@@ -817,6 +1066,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         default:
             p.idesc = make_idesc_mxf4(BLOCK_M, block_n);
             if (block_n == 256) return launch_gemm<KIND_MXF4, 256>(ta, tb, p, grid, stream);
+            if (block_n == 192) return launch_gemm<KIND_MXF4, 192>(ta, tb, p, grid, stream);
             return launch_gemm<KIND_MXF4, 128>(ta, tb, p, grid, stream);
     }
 }

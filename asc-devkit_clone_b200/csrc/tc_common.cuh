@@ -9,10 +9,13 @@ namespace ascb200 {
 namespace tc {
 
 // ---- bounded waits -------------------------------------------------------------------------
-// Every spin in these kernels gives up after kWaitLimitNs.  The first waiter that gives up sets
+// Every spin in these kernels gives up after a time limit.  The first waiter that gives up sets
 // the CTA-wide abort word in shared memory and bit 0 of the device status word; every later wait
 // returns at once, all roles leave their loops and the CTA frees its TMEM and exits normally.
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+// The limit is counted in SM clock cycles (clock64 is a cheap per-SM register; the global
+// nanosecond timer costs hundreds of cycles per read and must stay out of the polling path):
+// 4e9 cycles is about 2 s at the maximum SM clock and about 3.5 s at the lowest clock seen under load.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 
 __device__ __forceinline__ unsigned long long global_ns()
 {
@@ -46,22 +49,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+// Slow path shared by both wait flavours: called once every few hundred failed polls.
+__device__ __noinline__ bool mbar_wait_expired(long long t0, volatile uint32_t* abort_smem, uint32_t* status)
+{
+    if (*abort_smem) return true;
+    if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_smem = 1u;
+        atomicOr(status, 1u);
+        return true;
+    }
+    return false;
+}
 // Returns false when the wait was abandoned (abort already set, or the time limit ran out).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_smem, uint32_t* status)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
+    const long long t0 = clock64();
     uint32_t it = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++it & 63u) == 0u) {
-            if (*abort_smem) return false;
-            if (global_ns() - t0 > kWaitLimitNs) {
-                *abort_smem = 1u;
-                atomicOr(status, 1u);
-                return false;
-            }
-        }
+        if ((++it & 255u) == 0u && mbar_wait_expired(t0, abort_smem, status)) return false;
     }
 }
 
@@ -71,19 +78,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile uint32_t* abort_smem, uint32_t* status)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
+    const long long t0 = clock64();
     uint32_t it = 0;
     while (true) {
         __nanosleep(64);
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++it & 63u) == 0u) {
-            if (*abort_smem) return false;
-            if (global_ns() - t0 > kWaitLimitNs) {
-                *abort_smem = 1u;
-                atomicOr(status, 1u);
-                return false;
-            }
-        }
+        if ((++it & 255u) == 0u && mbar_wait_expired(t0, abort_smem, status)) return false;
     }
 }
 
@@ -136,7 +136,74 @@ __device__ __forceinline__ void tc_commit(uint32_t bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// ---- CTA pairs (cta_group::2) -------------------------------------------------------------------
+// Two CTAs of a cluster drive one 256-row MMA: each holds its 128 rows of A and half of B's rows in
+// its own shared memory, the even CTA (the leader) issues the instructions.  Shared-memory addresses
+// of the odd CTA carry bit 24 inside the cluster window; clearing it names the same offset in the leader.
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on a barrier that may live in the other CTA of the pair (address in the cluster window).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// Tile load issued by either CTA of a pair: data lands in the issuing CTA, the bytes are counted on
+// the leader's barrier.  No multicast: every CTA fetches exactly the rows it owns.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, int x, int y, int z, uint32_t leader_bar)
+{
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(leader_bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar)
+{
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask)
+                 : "memory");
+}
+
 enum : int { KIND_F16 = 0, KIND_I8 = 1, KIND_MXF4 = 2 };
+
+template <int KIND>
+__device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    if constexpr (KIND == KIND_F16) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
 
 template <int KIND>
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)

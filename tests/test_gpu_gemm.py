@@ -76,6 +76,40 @@ def test_gemm_i8_int32_exact(m, n, k, trans_a, trans_b):
     assert (got == ref).all(), f"{(got != ref).sum()} of {ref.size} differ; first {np.argwhere(got != ref)[:5].tolist()}"
 
 
+@pytest.mark.parametrize("m,n,k,trans_a,trans_b", [(2304, 2560, 256, False, True), (2304, 2560, 256, False, False), (2048, 2816, 384, True, True),
+                                                    (2200, 2568, 272, False, True)])
+def test_gemm_i8_cta_pair_exact(m, n, k, trans_a, trans_b):
+    """Shapes with at least one 256 x 256 tile per pair of SMs take the two-CTA kernel; ragged edges included."""
+    ab = dev()
+    rng, a, b = _i8_inputs(m, n, k, trans_a, trans_b, m + 3 * n + k)
+    bias = rng.integers(-1000, 1000, n).astype(np.int32)
+    d_c = ab.empty((m, n), np.int32)
+    d_c.fill(0x5A)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.S32, trans_a=trans_a, trans_b=trans_b, bias=ab.to_dev(bias)))
+    ab.sync()
+    ref = orc.gemm_i8(a, b, bias, trans_a=trans_a, trans_b=trans_b)
+    got = d_c.download()
+    assert (got == ref).all(), f"{(got != ref).sum()} of {ref.size} differ; first {np.argwhere(got != ref)[:5].tolist()}"
+
+
+@pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, False)])
+def test_gemm_f16_cta_pair(trans_a, trans_b):
+    run_f16(2304, 2560, 192, trans_a, trans_b, bias=True, c_dtype=0, seed=31)
+
+
+def test_gemm_a8w8_cta_pair_token_channel_dequant():
+    ab = dev()
+    m, n, k = 2100, 2576, 512
+    rng, a, b = _i8_inputs(m, n, k, False, True, 5)
+    tok = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+    ch = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    d_c = ab.empty((m, n), np.uint16)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.BF16, epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, trans_b=True,
+                     tok=ab.to_dev(tok), ch=ab.to_dev(ch)))
+    ab.sync()
+    assert (d_c.download() == orc.dequant_tok_ch(orc.gemm_i8(a, b, trans_b=True), tok, ch, orc.BF16)).all()
+
+
 @pytest.mark.parametrize("mode", ["req8", "req8_scalar_relu", "deqf16", "qs322bf16"])
 def test_gemm_i8_fixpipe_quant(mode):
     ab = dev()
@@ -164,7 +198,8 @@ def _mx_case(m, n, k, seed):
     return rng, a, sa, b, sb
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (128, 256, 512), (384, 512, 1024), (100, 200, 192), (256, 1024, 2048)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (128, 256, 512), (384, 512, 1024), (100, 200, 192), (256, 1024, 2048),
+                                   (2048, 2560, 512), (2000, 2600, 320)])  # the last two take the 192-column tile
 def test_gemm_mxfp4_fp32(m, n, k):
     ab = dev()
     rng, a, sa, b, sb = _mx_case(m, n, k, m + n + k)
