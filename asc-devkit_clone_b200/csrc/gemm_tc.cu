@@ -362,6 +362,98 @@ __device__ __forceinline__ void epilogue_dispatch(const GemmParams& p, const Til
 #undef ASCB200_EPI_CASE
 }
 
+// ---- MMA issue (one thread) -------------------------------------------------------------------
+// State of the issuing thread for the shared-memory ring: low descriptor words of the current
+// stage's A / B / scale tiles and the addresses of its barriers, advanced by one add per stage.
+template <int STAGE_BYTES, int NUM_STAGES, int B_OFFSET, int SF_OFFSET, int SF_COLS_PER_STAGE>
+struct IssueCursor {
+    uint32_t a_lo, b_lo, sf_lo, full_bar, empty_bar, sf_tmem;
+    uint32_t a_lo0, b_lo0, sf_lo0, full_bar0, empty_bar0, sf_tmem0;
+    int stage;
+    uint32_t phase;
+    __device__ __forceinline__ void init(uint32_t tiles_addr, uint32_t a_lbo_enc, uint32_t b_lbo_enc, uint32_t full0, uint32_t empty0, uint32_t sf_tmem_base)
+    {
+        a_lo0 = (a_lbo_enc << 16) | (tiles_addr >> 4);
+        b_lo0 = (b_lbo_enc << 16) | ((tiles_addr + B_OFFSET) >> 4);
+        sf_lo0 = (1u << 16) | ((tiles_addr + SF_OFFSET) >> 4);   // no-swizzle descriptor, leading offset 16 bytes
+        full_bar0 = full0;
+        empty_bar0 = empty0;
+        sf_tmem0 = sf_tmem_base;
+        rewind();
+        phase = 0;
+    }
+    __device__ __forceinline__ void rewind()
+    {
+        a_lo = a_lo0;
+        b_lo = b_lo0;
+        sf_lo = sf_lo0;
+        full_bar = full_bar0;
+        empty_bar = empty_bar0;
+        sf_tmem = sf_tmem0;
+        stage = 0;
+    }
+    __device__ __forceinline__ void advance()
+    {
+        if (++stage == NUM_STAGES) {
+            rewind();
+            phase ^= 1u;
+        } else {
+            a_lo += STAGE_BYTES >> 4;
+            b_lo += STAGE_BYTES >> 4;
+            sf_lo += STAGE_BYTES >> 4;
+            full_bar += 8;
+            empty_bar += 8;
+            sf_tmem += SF_COLS_PER_STAGE;
+        }
+    }
+};
+
+// Issues the tensor-core work of one K block (four MMAs, preceded by the scale-factor copies for
+// MXFP4) and the commit that releases the shared-memory stage.
+template <int KIND, bool PAIR, int SF_B_BLOCKS, class Cursor>
+__device__ __forceinline__ void issue_k_block(const Cursor& c, uint32_t d_tmem, uint32_t hi_word, uint32_t a_kstep16, uint32_t b_kstep16,
+                                              uint32_t idesc, uint32_t idesc_hi_sf, uint32_t sfb_col_offset, bool first)
+{
+    if constexpr (KIND == KIND_MXF4 && PAIR) {
+        // Scales arrive replicated (one 512-byte copy per 32-lane quadrant): per 128-row block and K block
+        // 4 KB = [kc0: 4 copies][kc1: 4 copies].  A 128x256b copy reads rows of two 16-byte halves that
+        // lie `leading offset` apart: A pairs (kc0, kc1) of its block (2048 apart) into TMEM columns 0-7;
+        // B pairs (block 0, block 1) of one kc (4096 apart) into columns 8-15 (kc0) and 16-23 (kc1).
+        static_assert(SF_B_BLOCKS == 2, "pair MXFP4 tile spans two 128-row scale blocks");
+        constexpr uint32_t sf_hi = (128u >> 4) | (1u << 14);
+        const uint32_t addr16 = c.sf_lo & 0xFFFFu;
+        sf_copy_128x256b_pair(c.sf_tmem + 0, ((2048u >> 4) << 16) | addr16, sf_hi);
+        sf_copy_128x256b_pair(c.sf_tmem + 8, ((4096u >> 4) << 16) | (addr16 + (4096u >> 4)), sf_hi);
+        sf_copy_128x256b_pair(c.sf_tmem + 16, ((4096u >> 4) << 16) | (addr16 + (4096u >> 4) + (2048u >> 4)), sf_hi);
+        const uint32_t sfb = c.sf_tmem + 8 + sfb_col_offset;
+        mma_issue_mxf4<PAIR>(d_tmem, c.a_lo, hi_word, c.b_lo, hi_word, idesc, c.sf_tmem, sfb, first ? 0u : 1u);
+        mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 2, hi_word, c.b_lo + 2, hi_word, idesc_hi_sf, c.sf_tmem, sfb, 1u);
+        mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 4, hi_word, c.b_lo + 4, hi_word, idesc, c.sf_tmem + 4, sfb + 8, 1u);
+        mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 6, hi_word, c.b_lo + 6, hi_word, idesc_hi_sf, c.sf_tmem + 4, sfb + 8, 1u);
+    } else if constexpr (KIND == KIND_MXF4) {
+        constexpr uint32_t sf_hi = (128u >> 4) | (1u << 14);  // stride 128 bytes between 8-row groups, descriptor version 1
+        // chunk order in shared memory: A kc0, A kc1, then per 128-row block of B: kc0, kc1 (512 bytes each)
+        sf_copy_issue<PAIR>(c.sf_tmem + 0, c.sf_lo, sf_hi);
+        sf_copy_issue<PAIR>(c.sf_tmem + 4, c.sf_lo + 32, sf_hi);
+#pragma unroll
+        for (int rb = 0; rb < SF_B_BLOCKS; ++rb) {
+            sf_copy_issue<PAIR>(c.sf_tmem + 8 + rb * 4, c.sf_lo + 64 + rb * 64, sf_hi);
+            sf_copy_issue<PAIR>(c.sf_tmem + 16 + rb * 4, c.sf_lo + 96 + rb * 64, sf_hi);
+        }
+        const uint32_t sfb = c.sf_tmem + 8 + sfb_col_offset;
+        mma_issue_mxf4<PAIR>(d_tmem, c.a_lo, hi_word, c.b_lo, hi_word, idesc, c.sf_tmem, sfb, first ? 0u : 1u);
+        mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 2, hi_word, c.b_lo + 2, hi_word, idesc_hi_sf, c.sf_tmem, sfb, 1u);
+        mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 4, hi_word, c.b_lo + 4, hi_word, idesc, c.sf_tmem + 4, sfb + 8, 1u);
+        mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 6, hi_word, c.b_lo + 6, hi_word, idesc_hi_sf, c.sf_tmem + 4, sfb + 8, 1u);
+    } else {
+        mma_issue<KIND, PAIR>(d_tmem, c.a_lo, hi_word, c.b_lo, hi_word, idesc, first ? 0u : 1u);
+        mma_issue<KIND, PAIR>(d_tmem, c.a_lo + a_kstep16, hi_word, c.b_lo + b_kstep16, hi_word, idesc, 1u);
+        mma_issue<KIND, PAIR>(d_tmem, c.a_lo + 2 * a_kstep16, hi_word, c.b_lo + 2 * b_kstep16, hi_word, idesc, 1u);
+        mma_issue<KIND, PAIR>(d_tmem, c.a_lo + 3 * a_kstep16, hi_word, c.b_lo + 3 * b_kstep16, hi_word, idesc, 1u);
+    }
+    commit_issue<PAIR>(c.empty_bar);
+}
+
 // ---- the kernel --------------------------------------------------------------------------------
 template <int KIND, int BLOCK_N>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -470,17 +562,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
     } else if (warp == 1) {
         // ===== MMA issuer =====
-        int stage = 0, cursor = 0, acc_iter = 0;
-        uint32_t phase = 0;
+        int cursor = 0, acc_iter = 0;
         TileInfo t;
         bool ok = true;
-        // K-major: rows of 128 bytes, 8-row groups 1024 bytes apart.  MN-major: one TMA box per
-        // 128 bytes of M/N, BLOCK_K k-rows of 128 bytes each, boxes BLOCK_K*128 bytes apart.
-        const uint64_t a_hi = p.a_mn ? smem_desc_sw128(C::BLOCK_K * ROW_BYTES, 1024) : smem_desc_sw128(16, 1024);
-        const uint64_t b_hi = p.b_mn ? smem_desc_sw128(C::BLOCK_K * ROW_BYTES, 1024) : smem_desc_sw128(16, 1024);
-        const uint32_t a_kstep = p.a_mn ? C::UMMA_K * ROW_BYTES : 32;
-        const uint32_t b_kstep = p.b_mn ? C::UMMA_K * ROW_BYTES : 32;
-        constexpr uint64_t sf_hi = smem_desc_noswizzle(16, 128);
+        // Shared-memory descriptors, 128-byte swizzle (high word: 1024 bytes between 8-row groups, version 1,
+        // layout type 2).  K-major operands: leading offset unused (16), one MMA advances 32 bytes.
+        // MN-major: one TMA box per 128 bytes of M/N, BLOCK_K k-rows each, boxes BLOCK_K*128 bytes apart,
+        // one MMA advances UMMA_K k-rows.
+        constexpr uint32_t hi_word = static_cast<uint32_t>(smem_desc_sw128(0, 1024) >> 32);
+        const uint32_t a_lbo = p.a_mn ? (C::BLOCK_K * ROW_BYTES) >> 4 : 1u, b_lbo = p.b_mn ? (C::BLOCK_K * ROW_BYTES) >> 4 : 1u;
+        const uint32_t a_k16 = (p.a_mn ? C::UMMA_K * ROW_BYTES : 32) >> 4, b_k16 = (p.b_mn ? C::UMMA_K * ROW_BYTES : 32) >> 4;
+        const uint32_t idesc_hi_sf = p.idesc | (2u << 4) | (2u << 29);  // MXFP4: scale bytes 2..3 of the TMEM column
+        IssueCursor<C::STAGE_BYTES, C::NUM_STAGES, A_TILE_BYTES, A_TILE_BYTES + C::B_TILE_BYTES, C::SF_COLS_PER_STAGE> cur;
+        cur.init(smem_u32(tiles), a_lbo, b_lbo, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]), tmem_base + C::SF_COL0);
         for (int tile = blockIdx.x; ok && locate_tile<BLOCK_N>(p, tile, num_m, total_tiles, row_start, tile_start, cursor, t); tile += gridDim.x, ++acc_iter) {
             const int acc_stage = acc_iter % C::ACC_STAGES;
             const uint32_t acc_phase = (acc_iter / C::ACC_STAGES) & 1u;
@@ -488,64 +582,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
-            for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_word, p.status);
+            const uint32_t acc_full = smem_u32(&acc_full_bar[acc_stage]);
+            const uint32_t sfb_off = static_cast<uint32_t>(t.n0 % 128) / 32;  // a 192-wide tile may start mid-way in a 128-row scale block
+            const int last = p.num_k_blocks - 1;
+            for (int kb = 0; kb <= last; ++kb) {
+                ok = mbar_wait(cur.full_bar, cur.phase, abort_word, p.status);
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t sa = smem_u32(tiles + stage * C::STAGE_BYTES);
-                    const uint32_t sb = sa + A_TILE_BYTES;
-                    if constexpr (KIND == KIND_MXF4) {
-                        const uint32_t ssf = sb + C::B_TILE_BYTES;
-                        const uint32_t sf_t = tmem_base + C::SF_COL0 + stage * C::SF_COLS_PER_STAGE;
-                        // chunk order in shared memory: A kc0, A kc1, then per 128-column block of B: kc0, kc1
-#ifdef ASCB200_PROBE
-                        if (!(p.probe & 64) || kb == 0)
-#endif
-                        {
-                        tmem_cp_32x128b_warpx4(sf_t + 0, desc_at(sf_hi, ssf));
-#ifdef ASCB200_PROBE
-                        if (!(p.probe & 128))
-#endif
-                        {
-                        tmem_cp_32x128b_warpx4(sf_t + 4, desc_at(sf_hi, ssf + SF_CHUNK_BYTES));
-#pragma unroll
-                        for (int rb = 0; rb < C::SF_B_BLOCKS; ++rb) {
-                            // TMEM columns of B scales: [8 + kc*8 + rb*4]
-                            tmem_cp_32x128b_warpx4(sf_t + 8 + 0 * 8 + rb * 4, desc_at(sf_hi, ssf + (2 + rb * 2) * SF_CHUNK_BYTES));
-                            tmem_cp_32x128b_warpx4(sf_t + 8 + 1 * 8 + rb * 4, desc_at(sf_hi, ssf + (3 + rb * 2) * SF_CHUNK_BYTES));
-                        }
-                        }
-                        }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint32_t sf_id = (j & 1) * 2u;
-                            const uint32_t idesc = p.idesc | (sf_id << 4) | (sf_id << 29);
-                            // a 192-wide tile may start in the middle of a 128-row scale block: 32 rows per TMEM column
-                            mma_mxf4(d_tmem, desc_at(a_hi, sa + j * 32), desc_at(b_hi, sb + j * 32), idesc, sf_t + (j >> 1) * 4,
-                                     sf_t + 8 + (j >> 1) * 8 + (t.n0 % 128) / 32, (kb | j) != 0 ? 1u : 0u);
-                        }
-                    } else
-#ifdef ASCB200_PROBE
-                    if (!(p.probe & 2))
-#endif
-                    {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            mma_ss<KIND>(d_tmem, desc_at(a_hi, sa + j * a_kstep), desc_at(b_hi, sb + j * b_kstep), p.idesc,
-                                         (kb | j) != 0 ? 1u : 0u);
-                    }
-#ifdef ASCB200_PROBE
-                    if (p.probe & 256) mbar_arrive(smem_u32(&empty_bar[stage])); else
-#endif
-                    tc_commit(smem_u32(&empty_bar[stage]));          // stage reusable once these MMAs have read it
-                    if (kb == p.num_k_blocks - 1) tc_commit(smem_u32(&acc_full_bar[acc_stage]));
+                    issue_k_block<KIND, false, C::SF_B_BLOCKS>(cur, d_tmem, hi_word, a_k16, b_k16, p.idesc, idesc_hi_sf, sfb_off, kb == 0);
+                    if (kb == last) tc_commit(acc_full);
                 }
                 __syncwarp();
-                if (++stage == C::NUM_STAGES) {
-                    stage = 0;
-                    phase ^= 1u;
-                }
+                cur.advance();
             }
         }
     } else if (warp >= 4) {
@@ -596,19 +645,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 template <int KIND, int BLOCK_N>
 struct Cfg2 {
     static constexpr int B_TILE_BYTES = (BLOCK_N / 2) * ROW_BYTES;
-    static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-    static constexpr int NUM_STAGES = std::min(8, (216 * 1024) / STAGE_BYTES);
+    static constexpr int SF_B_BLOCKS = (BLOCK_N + 127) / 128;   // every CTA needs the scales of all BLOCK_N columns
+    static constexpr int SF_REP_BYTES = 8 * SF_CHUNK_BYTES;   // scales of one 128-row block and K block, one copy per TMEM quadrant
+    static constexpr int SF_BYTES = KIND == KIND_MXF4 ? (1 + SF_B_BLOCKS) * SF_REP_BYTES : 0;
+    static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + SF_BYTES;
     static constexpr int ACC_STAGES = 2;
+    static constexpr int SF_COLS_PER_STAGE = 24;
+    static constexpr int SF_COL0 = ACC_STAGES * BLOCK_N;
+    static constexpr int MAX_SF_STAGES = KIND == KIND_MXF4 ? (512 - SF_COL0) / SF_COLS_PER_STAGE : 8;
+    static constexpr int NUM_STAGES = std::min(std::min(8, MAX_SF_STAGES), (216 * 1024) / STAGE_BYTES);
     static constexpr int TMEM_COLS = 512;
-    static_assert(ACC_STAGES * BLOCK_N <= 512, "TMEM budget");
-    static constexpr int BLOCK_K = KIND == KIND_F16 ? 64 : 128;
+    static_assert(ACC_STAGES * BLOCK_N + (KIND == KIND_MXF4 ? NUM_STAGES * SF_COLS_PER_STAGE : 0) <= 512, "TMEM budget");
+    static constexpr int BLOCK_K = KIND == KIND_F16 ? 64 : KIND == KIND_I8 ? 128 : 256;
     static constexpr int UMMA_K = BLOCK_K / 4;
     static constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + 1024 + 256;
 };
 
 template <int KIND, int BLOCK_N>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const GemmParams p)
 {
     using C = Cfg2<KIND, BLOCK_N>;
     constexpr int PAIR_M = 2 * BLOCK_M;
@@ -675,16 +731,27 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t sb = sa + A_TILE_BYTES;
                     if (rank == 0) mbar_expect_tx(own_bar, 2 * C::STAGE_BYTES);
                     const int k0 = kb * C::BLOCK_K;
+                    const int kx = KIND == KIND_MXF4 ? k0 / 2 : k0;  // packed fp4: two values per tensor-map element
                     constexpr int MN_PER_BOX = KIND == KIND_F16 ? 64 : 128;
                     constexpr int BOX_BYTES = C::BLOCK_K * ROW_BYTES;
+                    if constexpr (KIND == KIND_MXF4) {
+                        // replicated re-tiled scales as a [row, 128 x u32] tensor
+                        const uint32_t ssf = sb + C::B_TILE_BYTES;
+                        const int tile_n0 = n0 - static_cast<int>(rank) * (BLOCK_N / 2);
+                        // 8 rows of 512 bytes per (128-row block, K block): see retile_scales_rep4_kernel
+                        tma_load_2d_pair(ssf, &tmap_sfa, 0, ((row0 / 128) * p.num_k_blocks + kb) * 8, bar);
+#pragma unroll
+                        for (int rb = 0; rb < C::SF_B_BLOCKS; ++rb)
+                            tma_load_2d_pair(ssf + (1 + rb) * C::SF_REP_BYTES, &tmap_sfb, 0, ((tile_n0 / 128 + rb) * p.num_k_blocks + kb) * 8, bar);
+                    }
                     if (!p.a_mn) {
-                        tma_load_3d_pair(sa, &tmap_a, k0, row0, 0, bar);
+                        tma_load_3d_pair(sa, &tmap_a, kx, row0, 0, bar);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BLOCK_M / MN_PER_BOX; ++j) tma_load_3d_pair(sa + j * BOX_BYTES, &tmap_a, row0 + j * MN_PER_BOX, k0, 0, bar);
                     }
                     if (!p.b_mn) {
-                        tma_load_3d_pair(sb, &tmap_b, k0, n0, 0, bar);
+                        tma_load_3d_pair(sb, &tmap_b, kx, n0, 0, bar);
                     } else {
 #pragma unroll
                         for (int j = 0; j < (BLOCK_N / 2) / MN_PER_BOX; ++j) tma_load_3d_pair(sb + j * BOX_BYTES, &tmap_b, n0 + j * MN_PER_BOX, k0, 0, bar);
@@ -708,13 +775,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
     } else if (warp == 1 && rank == 0) {
         // ===== MMA issuer (leader CTA only) =====
-        int stage = 0, acc_iter = 0;
-        uint32_t phase = 0;
+        int acc_iter = 0;
         bool ok = true;
-        const uint64_t a_hi = p.a_mn ? smem_desc_sw128(C::BLOCK_K * ROW_BYTES, 1024) : smem_desc_sw128(16, 1024);
-        const uint64_t b_hi = p.b_mn ? smem_desc_sw128(C::BLOCK_K * ROW_BYTES, 1024) : smem_desc_sw128(16, 1024);
-        const uint32_t a_kstep = p.a_mn ? C::UMMA_K * ROW_BYTES : 32;
-        const uint32_t b_kstep = p.b_mn ? C::UMMA_K * ROW_BYTES : 32;
+        constexpr uint32_t hi_word = static_cast<uint32_t>(smem_desc_sw128(0, 1024) >> 32);
+        const uint32_t a_lbo = p.a_mn ? (C::BLOCK_K * ROW_BYTES) >> 4 : 1u, b_lbo = p.b_mn ? (C::BLOCK_K * ROW_BYTES) >> 4 : 1u;
+        const uint32_t a_k16 = (p.a_mn ? C::UMMA_K * ROW_BYTES : 32) >> 4, b_k16 = (p.b_mn ? C::UMMA_K * ROW_BYTES : 32) >> 4;
+        const uint32_t idesc_hi_sf = p.idesc | (2u << 4) | (2u << 29);
+        IssueCursor<C::STAGE_BYTES, C::NUM_STAGES, A_TILE_BYTES, A_TILE_BYTES + C::B_TILE_BYTES, C::SF_COLS_PER_STAGE> cur;
+        cur.init(smem_u32(tiles), a_lbo, b_lbo, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]), tmem_base + C::SF_COL0);
         for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters, ++acc_iter) {
             const int acc_stage = acc_iter & 1;
             const uint32_t acc_phase = (acc_iter >> 1) & 1u;
@@ -722,24 +790,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
-            for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_word, p.status);
+            const uint32_t acc_full = smem_u32(&acc_full_bar[acc_stage]);
+            const uint32_t sfb_off = static_cast<uint32_t>(((tile / num_m) * BLOCK_N) % 128) / 32;
+            const int last = p.num_k_blocks - 1;
+            for (int kb = 0; kb <= last; ++kb) {
+                ok = mbar_wait(cur.full_bar, cur.phase, abort_word, p.status);
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t sa = smem_u32(tiles + stage * C::STAGE_BYTES);
-                    const uint32_t sb = sa + A_TILE_BYTES;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        mma_ss_pair<KIND>(d_tmem, desc_at(a_hi, sa + j * a_kstep), desc_at(b_hi, sb + j * b_kstep), p.idesc, (kb | j) != 0 ? 1u : 0u);
-                    tc_commit_pair(smem_u32(&empty_bar[stage]));
-                    if (kb == p.num_k_blocks - 1) tc_commit_pair(smem_u32(&acc_full_bar[acc_stage]));
+                    issue_k_block<KIND, true, C::SF_B_BLOCKS>(cur, d_tmem, hi_word, a_k16, b_k16, p.idesc, idesc_hi_sf, sfb_off, kb == 0);
+                    if (kb == last) tc_commit_pair(acc_full);
                 }
                 __syncwarp();
-                if (++stage == C::NUM_STAGES) {
-                    stage = 0;
-                    phase ^= 1u;
-                }
+                cur.advance();
             }
         }
     } else if (warp >= 4) {
@@ -807,6 +870,32 @@ __global__ void retile_scales_kernel(const uint8_t* __restrict__ src, uint32_t* 
     }
 }
 
+// Pair-kernel variant: per 128-row block rb and K block kb (256 elements = 8 scales per row) it writes
+// 4 KB = [kc0: 4 identical 512-byte chunks][kc1: 4 identical chunks], chunk format as above, so that one
+// 128-lane tcgen05.cp can fill all four TMEM quadrants.
+__global__ void retile_scales_rep4_kernel(const uint8_t* __restrict__ src, uint32_t* __restrict__ dst, int rows, int ks, int row_blocks, int kb_count)
+{
+    const size_t total = static_cast<size_t>(row_blocks) * kb_count * 2 * 128;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int pos = static_cast<int>(i % 128);
+        const int kc = static_cast<int>((i / 128) % 2);
+        const size_t blk = i / 256;                       // rb * kb_count + kb
+        const int kb = static_cast<int>(blk % kb_count);
+        const int rb = static_cast<int>(blk / kb_count);
+        const int r = rb * 128 + (pos & 3) * 32 + (pos >> 2);
+        uint32_t w = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int kidx = (kb * 2 + kc) * 4 + b;
+            const uint32_t v = (r < rows && kidx < ks) ? src[static_cast<size_t>(r) * ks + kidx] : 127u;
+            w |= v << (8 * b);
+        }
+        uint32_t* out = dst + (blk * 8 + static_cast<size_t>(kc) * 4) * 128 + pos;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) out[q * 128] = w;
+    }
+}
+
 // ---- host side --------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -843,6 +932,20 @@ int make_map(CUtensorMap* map, CUtensorMapDataType dt, int esz, const void* base
     return r == CUDA_SUCCESS ? ASCB200_OK : ASCB200_ECUDA;
 }
 
+// rank-2 map over re-tiled scales: `chunks` rows of 128 x u32 (512 bytes), box = box_rows rows, no swizzle.
+int make_sf_map(CUtensorMap* map, const void* base, uint64_t chunks, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return ASCB200_ECUDA;
+    cuuint64_t dims[2] = {128, chunks};
+    cuuint64_t strides[1] = {SF_CHUNK_BYTES};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? ASCB200_OK : ASCB200_ECUDA;
+}
+
 template <int KIND, int BLOCK_N>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream)
 {
@@ -860,7 +963,8 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
 }
 
 template <int KIND, int BLOCK_N>
-int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int clusters, cudaStream_t stream)
+int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsfa, const CUtensorMap& tsfb, const GemmParams& p, int clusters,
+                     cudaStream_t stream)
 {
     using C = Cfg2<KIND, BLOCK_N>;
     static bool configured[16] = {};
@@ -870,7 +974,7 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPar
         ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured[dev & 15] = true;
     }
-    gemm_tc_pair_kernel<KIND, BLOCK_N><<<2 * clusters, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
+    gemm_tc_pair_kernel<KIND, BLOCK_N><<<2 * clusters, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, tsfa, tsfb, p);
     ASCB200_CUDA(cudaGetLastError());
     return ASCB200_OK;
 }
@@ -976,8 +1080,10 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
 
     // CTA pairs (256 x 256 tiles) for plain fp16 / bf16 / int8 problems with enough tiles to fill every pair of SMs
     const int pair_clusters = sm_count / 2;
-    const bool use_pair = !grouped && kind != ASCB200_KIND_MXFP4 && block_n == 256 &&
-                          static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((n + 255) / 256) >= pair_clusters &&
+    const int pair_n = kind == ASCB200_KIND_MXFP4 ? 192 : 256;
+    const long long pair_tiles = static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((n + pair_n - 1) / pair_n);
+    // (the allocation-free variant keeps the compact scale layout of the single-CTA kernel: its scratch is fixed)
+    const bool use_pair = !grouped && block_n == pair_n && pair_tiles >= pair_clusters && !(fixed && kind == ASCB200_KIND_MXFP4) &&
                           !(getenv("ASCB200_NO_PAIR") && getenv("ASCB200_NO_PAIR")[0] == '1');
     const int b_box_rows = use_pair ? block_n / 2 : block_n;
 
@@ -1012,7 +1118,8 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         const int ks = k / 32;
         const int kc = 2 * p.num_k_blocks;
         const int rba = (m + 127) / 128, rbb = (n + 127) / 128 + 2;  // B tiles may read up to two blocks past the last row
-        const size_t bytes_a = static_cast<size_t>(rba) * kc * SF_CHUNK_BYTES, bytes_b = static_cast<size_t>(rbb) * kc * SF_CHUNK_BYTES;
+        const size_t rep = use_pair ? 4 : 1;  // the pair kernel reads one copy per TMEM quadrant
+        const size_t bytes_a = static_cast<size_t>(rba) * kc * SF_CHUNK_BYTES * rep, bytes_b = static_cast<size_t>(rbb) * kc * SF_CHUNK_BYTES * rep;
         uint8_t* sfa;
         if (fixed) {
             if (bytes_a + bytes_b > fixed->scale_scratch_bytes) return ASCB200_ETOOBIG;
@@ -1025,8 +1132,13 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         uint8_t* sfb = sfa + bytes_a;
         const int ga = static_cast<int>(std::min<size_t>((bytes_a / 4 + 255) / 256, 4096));
         const int gb = static_cast<int>(std::min<size_t>((bytes_b / 4 + 255) / 256, 4096));
-        retile_scales_kernel<<<ga, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_a_dev), reinterpret_cast<uint32_t*>(sfa), m, ks, rba, kc);
-        retile_scales_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_b_dev), reinterpret_cast<uint32_t*>(sfb), n, ks, rbb, kc);
+        if (use_pair) {
+            retile_scales_rep4_kernel<<<ga, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_a_dev), reinterpret_cast<uint32_t*>(sfa), m, ks, rba, p.num_k_blocks);
+            retile_scales_rep4_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_b_dev), reinterpret_cast<uint32_t*>(sfb), n, ks, rbb, p.num_k_blocks);
+        } else {
+            retile_scales_kernel<<<ga, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_a_dev), reinterpret_cast<uint32_t*>(sfa), m, ks, rba, kc);
+            retile_scales_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_b_dev), reinterpret_cast<uint32_t*>(sfb), n, ks, rbb, kc);
+        }
         ASCB200_CUDA(cudaGetLastError());
         p.sfa = sfa;
         p.sfb = sfb;
@@ -1039,15 +1151,23 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
 
     const uint32_t a_mn = p.a_mn, b_mn = p.b_mn;
     if (use_pair) {
-        const long long pair_tiles = static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((n + 255) / 256);
         const int clusters = static_cast<int>(std::min<long long>(pair_tiles, pair_clusters));
+        if (kind == ASCB200_KIND_MXFP4) {
+            // the re-tiled scales as rank-2 tensors [chunk][128 x u32] for tile loads
+            CUtensorMap tsfa, tsfb;
+            rc = make_sf_map(&tsfa, p.sfa, static_cast<uint64_t>((m + 127) / 128) * p.num_k_blocks * 8, 8);
+            if (rc == ASCB200_OK) rc = make_sf_map(&tsfb, p.sfb, static_cast<uint64_t>((n + 127) / 128 + 2) * p.num_k_blocks * 8, 8);
+            if (rc != ASCB200_OK) return rc;
+            p.idesc = make_idesc_mxf4(2 * BLOCK_M, 192);
+            return launch_gemm_pair<KIND_MXF4, 192>(ta, tb, tsfa, tsfb, p, clusters, stream);
+        }
         if (kind == ASCB200_KIND_S8) {
             p.idesc = make_idesc(2, 1, 1, a_mn, b_mn, 2 * BLOCK_M, 256);
-            return launch_gemm_pair<KIND_I8, 256>(ta, tb, p, clusters, stream);
+            return launch_gemm_pair<KIND_I8, 256>(ta, tb, ta, tb, p, clusters, stream);
         }
         const uint32_t fmt = kind == ASCB200_KIND_BF16 ? 1u : 0u;
         p.idesc = make_idesc(1, fmt, fmt, a_mn, b_mn, 2 * BLOCK_M, 256);
-        return launch_gemm_pair<KIND_F16, 256>(ta, tb, p, clusters, stream);
+        return launch_gemm_pair<KIND_F16, 256>(ta, tb, ta, tb, p, clusters, stream);
     }
     switch (kind) {
         case ASCB200_KIND_F16:

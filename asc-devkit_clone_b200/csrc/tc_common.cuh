@@ -177,6 +177,27 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols
 {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, int x, int y, uint32_t leader_bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(leader_bar)
+                 : "memory");
+}
+// Pair forms of the block-scaled MMA and of the scale-factor copy: every CTA of the pair copies
+// from its own shared memory into its own TMEM.
+__device__ __forceinline__ void mma_mxf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
+                                              uint32_t sfb_tmem, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t sdesc)
+{
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
 // Arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far are done.
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar)
 {
@@ -253,6 +274,65 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- lean issue path ---------------------------------------------------------------------------
+// One thread feeds the tensor cores; every instruction it spends between two MMAs is time the
+// tensor pipe may sit idle.  These forms take descriptors as (low word, high word) pairs so that the
+// per-instruction work is one 32-bit add on the low word (start address in 16-byte units).
+template <int KIND, bool PAIR>
+__device__ __forceinline__ void mma_issue(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                          uint32_t accumulate)
+{
+#define ASCB200_MMA_ASM(GROUP, KINDSTR)                                                                       \
+    asm volatile(                                                                                             \
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"  \
+        "setp.ne.b32 p, %6, 0;\n\t"                                                                            \
+        "tcgen05.mma.cta_group::" GROUP ".kind::" KINDSTR " [%0], da, db, %5, p;\n\t}"                         \
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)                \
+        : "memory")
+    if constexpr (KIND == KIND_F16) {
+        if constexpr (PAIR) ASCB200_MMA_ASM("2", "f16");
+        else ASCB200_MMA_ASM("1", "f16");
+    } else {
+        if constexpr (PAIR) ASCB200_MMA_ASM("2", "i8");
+        else ASCB200_MMA_ASM("1", "i8");
+    }
+#undef ASCB200_MMA_ASM
+}
+template <bool PAIR>
+__device__ __forceinline__ void mma_issue_mxf4(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate)
+{
+#define ASCB200_MMA_ASM(GROUP)                                                                                \
+    asm volatile(                                                                                             \
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"  \
+        "setp.ne.b32 p, %8, 0;\n\t"                                                                            \
+        "tcgen05.mma.cta_group::" GROUP ".kind::mxf4.block_scale.scale_vec::2X [%0], da, db, %5, [%6], [%7], p;\n\t}" \
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate) \
+        : "memory")
+    if constexpr (PAIR) ASCB200_MMA_ASM("2");
+    else ASCB200_MMA_ASM("1");
+#undef ASCB200_MMA_ASM
+}
+template <bool PAIR>
+__device__ __forceinline__ void sf_copy_issue(uint32_t taddr, uint32_t s_lo, uint32_t s_hi)
+{
+    if constexpr (PAIR)
+        asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n\t}" ::"r"(taddr), "r"(s_lo), "r"(s_hi) : "memory");
+    else
+        asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n\t}" ::"r"(taddr), "r"(s_lo), "r"(s_hi) : "memory");
+}
+// 128 lanes x 32 bytes, no broadcast: the source already holds one copy per 32-lane quadrant.
+__device__ __forceinline__ void sf_copy_128x256b_pair(uint32_t taddr, uint32_t s_lo, uint32_t s_hi)
+{
+    asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::2.128x256b [%0], d;\n\t}" ::"r"(taddr), "r"(s_lo), "r"(s_hi) : "memory");
+}
+template <bool PAIR>
+__device__ __forceinline__ void commit_issue(uint32_t bar)
+{
+    if constexpr (PAIR) tc_commit_pair(bar);
+    else tc_commit(bar);
+}
 
 // ---- descriptors -----------------------------------------------------------------------------
 // Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.

@@ -186,10 +186,14 @@ class Grouped(Workload):
     name = "grouped_a8w8_64groups_M32768_K7168_N2048"
     metric, unit, dtype = "grouped quant-GEMM throughput (int8, fused dequant)", "TOPS", "s8"
     G, MTOT, K, N = 64, 32768, 7168, 2048
+    OUT, ACT = "BF16", 0
+
+    def counts(self):
+        return dirichlet_counts(self.G, self.MTOT, 0xA5C00003)
 
     def __init__(self, ab, rank, world, sets):
         self.ab, self.rank, self.world = ab, rank, world
-        counts = dirichlet_counts(self.G, self.MTOT, 0xA5C00003)
+        counts = self.counts()
         mine = lpt_partition(counts, world)[rank]
         self.counts_h = counts[mine].astype(np.int64)
         self.m_loc = int(self.counts_h.sum())
@@ -203,10 +207,10 @@ class Grouped(Workload):
         self.x = [ab.to_dev(self.x_h) for _ in range(sets)]
         self.w = [ab.to_dev(self.w_h) for _ in range(1)]           # 0.94 GB of weights already exceed L2
         self.c = [ab.empty((max(self.m_loc, 1), self.N), np.uint16) for _ in range(sets)]
-        self.tok, self.ch, self.counts = ab.to_dev(self.tok_h), ab.to_dev(self.ch_h), ab.to_dev(self.counts_h)
+        self.tok, self.ch, self.counts_d = ab.to_dev(self.tok_h), ab.to_dev(self.ch_h), ab.to_dev(self.counts_h)
         self.config = {"workload": self.name, "groups": self.G, "rows": self.MTOT, "K": self.K, "N": self.N,
                        "shard": f"groups x{world} (greedy by rows)", "rows_this_rank": self.m_loc,
-                       "cache": "weights of one pass (0.94 GB / ranks) exceed L2"}
+                       "cache": f"weights of one pass ({self.w_h.nbytes // 2**20} MiB on this rank)" + ("" if self.w_h.nbytes > L2_BYTES else ", may stay in L2")}
 
     def units_total(self):
         return 2.0 * self.MTOT * self.K * self.N
@@ -219,9 +223,9 @@ class Grouped(Workload):
 
     def step(self, i, stream=None):
         ab, s = self.ab, i % self.sets
-        ab.check(ab.gemm(ab.KIND_S8, self.m_loc, self.N, self.K, self.x[s], self.w[0], self.c[s], ab.BF16,
-                         epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, trans_b=True, tok=self.tok, ch=self.ch, group_counts=self.counts,
-                         groups=self.g_loc, stream=stream))
+        ab.check(ab.gemm(ab.KIND_S8, self.m_loc, self.N, self.K, self.x[s], self.w[0], self.c[s], getattr(ab, self.OUT),
+                         epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, trans_b=True, tok=self.tok, ch=self.ch, group_counts=self.counts_d,
+                         groups=self.g_loc, act=self.ACT, stream=stream))
 
     def e2e_bytes(self):
         return self.x_h.nbytes + self.w_h.nbytes + self.tok_h.nbytes + self.ch_h.nbytes + self.counts_h.nbytes, self.m_loc * self.N * 2
@@ -231,7 +235,7 @@ class Grouped(Workload):
 
     def e2e_step(self, i, stream):
         s = i % self.sets
-        self.pin.h2d([self.x[s], self.w[0], self.tok, self.ch, self.counts], stream)
+        self.pin.h2d([self.x[s], self.w[0], self.tok, self.ch, self.counts_d], stream)
         self.step(i, stream)
         self.pin.d2h(self.c[s], stream)
 
@@ -242,7 +246,7 @@ class Grouped(Workload):
         idx = np.concatenate([np.arange(s, s + t) for s, t in zip(starts, take)])
         x, tok = np.ascontiguousarray(self.x_h[idx]), self.tok_h[idx]
         t0 = time.perf_counter()
-        orc.grouped_i8(x, self.w_h, take, tok, self.ch_h, orc.BF16, trans_b=True)
+        orc.grouped_i8(x, self.w_h, take, tok, self.ch_h, getattr(orc, self.OUT), trans_b=True, act=self.ACT)
         return time.perf_counter() - t0, 2.0 * int(take.sum()) * self.K * self.N, f"first {rows} rows of each of {self.g_loc} groups"
 
     def verify(self, orc):
@@ -250,7 +254,10 @@ class Grouped(Workload):
         take = np.minimum(self.counts_h, 2)
         starts = np.concatenate([[0], np.cumsum(self.counts_h)[:-1]])
         idx = np.concatenate([np.arange(s, s + t) for s, t in zip(starts, take)])
-        ref = orc.grouped_i8(np.ascontiguousarray(self.x_h[idx]), self.w_h, take, self.tok_h[idx], self.ch_h, orc.BF16, trans_b=True)
+        ref = orc.grouped_i8(np.ascontiguousarray(self.x_h[idx]), self.w_h, take, self.tok_h[idx], self.ch_h, getattr(orc, self.OUT), trans_b=True,
+                             act=self.ACT)
+        if self.ACT:  # the activation uses fast exponentials: the example's own acceptance rule (rtol = atol = 1e-3)
+            return bool(np.isclose(orc.f16_bits_to_f32(got[idx]), orc.f16_bits_to_f32(ref), rtol=1e-3, atol=1e-3).mean() > 0.9999)
         return bool((got[idx] == ref).all())
 
 
@@ -464,8 +471,78 @@ class FP16(Workload):
         return bool(np.allclose(self.c[0].download(), ref, rtol=1e-2, atol=1e-3))
 
 
+class FP16Large(Workload):
+    """The reference's own published Matmul shape (fp16 8192^3, B stored transposed, fp16 out):
+    examples/01_simd_cpp_api/05_best_practices/01_matrix_compute/matmul_high_performance (scripts/gen_data.py:20-28)."""
+    name = "matmul_fp16_8192x8192x8192_fp16_out"
+    metric, unit, dtype = "adv_api Matmul fp16 -> fp16, 8192^3 (the reference's published shape)", "TFLOPS", "f16"
+    M = K = N = 8192
+    published = (427.0, "Ascend 950PR basic-API fp16 8192^3, 2572 us (BASELINE.md); Atlas A2 adv_api: 269")
+
+    def __init__(self, ab, rank, world, sets):
+        from gpu_util import f16_bits
+        self.ab, self.rank, self.world = ab, rank, world
+        self.n_loc = self.N // world
+        rng = np.random.default_rng(0xA5C00005)
+        self.a_h = f16_bits(rng.uniform(1, 10, (self.M, self.K)).astype(np.float32))      # the example draws U[1,10)
+        self.b_h = f16_bits(np.random.default_rng(0xA5C00005 + 1000 + rank).uniform(1, 10, (self.n_loc, self.K)).astype(np.float32))
+        self.sets = sets
+        self.a = [ab.to_dev(self.a_h) for _ in range(sets)]
+        self.b = [ab.to_dev(self.b_h) for _ in range(sets)]
+        self.c = [ab.empty((self.M, self.n_loc), np.uint16) for _ in range(sets)]
+        self.config = {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "shard": f"N-slab x{world}", "cache": f"{sets} rotating buffer sets"}
+
+    def units_total(self):
+        return 2.0 * self.M * self.K * self.N
+
+    def units_rank(self):
+        return 2.0 * self.M * self.K * self.n_loc
+
+    def peak(self, peaks):
+        return peaks["bf16_tflops"], "TFLOPS", "measured bf16 cuBLAS burst"
+
+    def step(self, i, stream=None):
+        ab, s = self.ab, i % self.sets
+        ab.check(ab.gemm(ab.KIND_F16, self.M, self.n_loc, self.K, self.a[s], self.b[s], self.c[s], ab.F16, trans_b=True, stream=stream))
+
+    def e2e_bytes(self):
+        return self.a_h.nbytes + self.b_h.nbytes, self.M * self.n_loc * 2
+
+    def e2e_setup(self):
+        self.pin = PinnedSet(self.ab, [self.a_h, self.b_h], self.M * self.n_loc * 2)
+
+    def e2e_step(self, i, stream):
+        s = i % self.sets
+        self.pin.h2d([self.a[s], self.b[s]], stream)
+        self.step(i, stream)
+        self.pin.d2h(self.c[s], stream)
+
+    def cpu_sample(self, orc, rows):
+        t0 = time.perf_counter()
+        acc = orc.gemm_f16(self.a_h[:rows], self.b_h, trans_b=True, base_k=64)
+        orc.cast_f32(acc, orc.F16)
+        return time.perf_counter() - t0, 2.0 * rows * self.K * self.n_loc, f"{rows} of {self.M} rows of A x all {self.n_loc} columns"
+
+    def verify(self, orc):
+        ref = orc.f16_bits_to_f32(orc.cast_f32(orc.gemm_f16(self.a_h[:8], self.b_h, trans_b=True, base_k=64), orc.F16))
+        return bool(np.allclose(orc.f16_bits_to_f32(self.c[0].download()[:8]), ref, rtol=1e-2, atol=1e-3))
+
+
+class GroupedRefShape(Grouped):
+    """The grouped example's own shape and epilogue: 8 groups x 1024 rows, K=1024, N=8192, FasterGelu, fp16 out
+    (quant_group_matmul_high_performance/scripts/gen_data.py:21-25); published 204.1 us on Ascend 950PR, 299.3 us on Atlas A2."""
+    name = "grouped_a8w8_8groups_M8192_K1024_N8192_gelu_fp16"
+    metric = "grouped quant-GEMM throughput (the reference example's shape, FasterGelu, fp16 out)"
+    G, MTOT, K, N = 8, 8192, 1024, 8192
+    published = (2.0 * 8192 * 1024 * 8192 / 204.129e-6 / 1e12, "Ascend 950PR, 204.129 us (BASELINE.md)")
+    OUT, ACT = "F16", 1
+
+    def counts(self):
+        return np.full(self.G, self.MTOT // self.G, np.int64)
+
+
 WORKLOADS = {"a8w8": A8W8, "grouped": Grouped, "mxfp4": MXFP4, "softmax_quant": SoftmaxQuant, "softmax_quant_x64": SoftmaxQuantLarge,
-             "fp16": FP16}
+             "fp16": FP16, "fp16_8192": FP16Large, "grouped_ref_shape": GroupedRefShape}
 
 
 class PinnedSet:
