@@ -20,7 +20,7 @@ EXPORTS = [
     "ascb200_init", "ascb200_strerror", "ascb200_last_cuda_error", "ascb200_device_status", "ascb200_sm_count",
     "ascb200_malloc", "ascb200_free", "ascb200_malloc_host", "ascb200_free_host", "ascb200_memcpy_h2d", "ascb200_memcpy_d2h",
     "ascb200_memset", "ascb200_stream_create", "ascb200_stream_destroy", "ascb200_stream_sync", "ascb200_event_create",
-    "ascb200_event_destroy", "ascb200_event_record", "ascb200_event_elapsed_ms", "ascb200_gemm", "ascb200_grouped_gemm",
+    "ascb200_event_destroy", "ascb200_event_record", "ascb200_stream_wait_event", "ascb200_event_elapsed_ms", "ascb200_gemm", "ascb200_grouped_gemm",
     "ascb200_gemm_mxfp4_noalloc", "ascb200_graph_begin", "ascb200_graph_end", "ascb200_graph_launch", "ascb200_graph_destroy",
     "ascb200_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
 ]
@@ -75,6 +75,7 @@ def lib():
         _lib.ascb200_event_create.argtypes = [C.POINTER(C.c_void_p)]
         _lib.ascb200_event_destroy.argtypes = [C.c_void_p]
         _lib.ascb200_event_record.argtypes = [C.c_void_p, C.c_void_p]
+        _lib.ascb200_stream_wait_event.argtypes = [C.c_void_p, C.c_void_p]
         _lib.ascb200_event_elapsed_ms.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]
         _lib.ascb200_device_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
         _lib.ascb200_gemm.argtypes = [C.POINTER(GemmDesc), C.c_void_p]

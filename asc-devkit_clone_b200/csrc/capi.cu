@@ -180,6 +180,11 @@ int ascb200_event_record(void* event, void* stream)
     ASCB200_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)));
     return ASCB200_OK;
 }
+int ascb200_stream_wait_event(void* stream, void* event)
+{
+    ASCB200_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(event), 0));
+    return ASCB200_OK;
+}
 int ascb200_event_elapsed_ms(void* start, void* stop, float* ms)
 {
     if (!ms) return ASCB200_EINVAL;

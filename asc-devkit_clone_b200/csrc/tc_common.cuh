@@ -49,6 +49,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe of the barrier phase.  try_wait may put the warp to sleep for a hardware-chosen
+// interval when the phase is not complete yet; the wake-up costs hundreds of cycles, which the
+// two warps that drive the pipeline cannot afford on every K block, so they poll with test_wait.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Slow path shared by both wait flavours: called once every few hundred failed polls.
 __device__ __noinline__ bool mbar_wait_expired(long long t0, volatile uint32_t* abort_smem, uint32_t* status)
 {
@@ -63,12 +78,12 @@ __device__ __noinline__ bool mbar_wait_expired(long long t0, volatile uint32_t* 
 // Returns false when the wait was abandoned (abort already set, or the time limit ran out).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_smem, uint32_t* status)
 {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t it = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++it & 255u) == 0u && mbar_wait_expired(t0, abort_smem, status)) return false;
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((++it & 1023u) == 0u && mbar_wait_expired(t0, abort_smem, status)) return false;
     }
 }
 
@@ -299,6 +314,9 @@ __device__ __forceinline__ void mma_issue(uint32_t d_tmem, uint32_t a_lo, uint32
     }
 #undef ASCB200_MMA_ASM
 }
+#ifndef ASCB200_MXF4_KIND
+#define ASCB200_MXF4_KIND "mxf4"
+#endif
 template <bool PAIR>
 __device__ __forceinline__ void mma_issue_mxf4(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
                                                uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate)
@@ -307,7 +325,7 @@ __device__ __forceinline__ void mma_issue_mxf4(uint32_t d_tmem, uint32_t a_lo, u
     asm volatile(                                                                                             \
         "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"  \
         "setp.ne.b32 p, %8, 0;\n\t"                                                                            \
-        "tcgen05.mma.cta_group::" GROUP ".kind::mxf4.block_scale.scale_vec::2X [%0], da, db, %5, [%6], [%7], p;\n\t}" \
+        "tcgen05.mma.cta_group::" GROUP ".kind::" ASCB200_MXF4_KIND ".block_scale.scale_vec::2X [%0], da, db, %5, [%6], [%7], p;\n\t}" \
         ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate) \
         : "memory")
     if constexpr (PAIR) ASCB200_MMA_ASM("2");

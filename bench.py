@@ -557,9 +557,12 @@ class PinnedSet:
             ab.check(ab.lib().ascb200_malloc_host(C.byref(p), max(a.nbytes, 1)))
             C.memmove(p.value, a.ctypes.data, a.nbytes)
             self.src.append((p.value, a.nbytes))
-        p = C.c_void_p()
-        ab.check(ab.lib().ascb200_malloc_host(C.byref(p), max(out_bytes, 1)))
-        self.out, self.out_bytes = p.value, out_bytes
+        self.outs = []
+        for _ in range(2):   # one landing buffer per in-flight step (two streams alternate)
+            p = C.c_void_p()
+            ab.check(ab.lib().ascb200_malloc_host(C.byref(p), max(out_bytes, 1)))
+            self.outs.append(p.value)
+        self.out, self.out_bytes, self.slot = self.outs[0], out_bytes, 0
 
     def h2d(self, dev_bufs, stream):
         for (p, n), d in zip(self.src, dev_bufs):
@@ -567,7 +570,7 @@ class PinnedSet:
 
     def d2h(self, dev_buf, stream, offset=0):
         n = min(dev_buf.nbytes, self.out_bytes - offset)
-        self.ab.check(self.ab.lib().ascb200_memcpy_d2h(self.out + offset, dev_buf.ptr, n, stream))
+        self.ab.check(self.ab.lib().ascb200_memcpy_d2h(self.outs[self.slot] + offset, dev_buf.ptr, n, stream))
 
 
 # ------------------------------------------------------------------------------------------------
@@ -602,19 +605,55 @@ class Comm:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t.item())
 
+    def allgather_ms(self, ab, dev_buf, nbytes, reps=5):
+        """Times all_gather_into_tensor of one rank's output slab (copied into a torch buffer once, outside the timing)."""
+        torch, dist = self.torch, self.dist
+        send = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        recv = torch.empty(nbytes * self.world, dtype=torch.uint8, device="cuda")
+        ab.sync()
+        host = dev_buf.download(shape=(nbytes,), dtype=np.uint8)
+        send.copy_(torch.from_numpy(host))
+        for _ in range(2):
+            dist.all_gather_into_tensor(recv, send)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        e0.record()
+        for _ in range(reps):
+            dist.all_gather_into_tensor(recv, send)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = self.max(e0.elapsed_time(e1) / reps)
+        ok = bool((recv[self.dist.get_rank() * nbytes:(self.dist.get_rank() + 1) * nbytes] == send).all().item())
+        return ms, ok
+
     def close(self):
         if self.torch:
             self.dist.destroy_process_group()
 
 
-def time_steps(ab, wl, comm, steps, warmup, stream, e2e=False):
+def time_steps(ab, wl, comm, steps, warmup, stream, e2e=False, stream2=None):
     """Times exactly `steps` steps between a barrier + synchronize on both sides; returns the max over ranks (ms).
     The device-resident measurement replays the steps from one CUDA graph, so that the host's launch
-    cost (a Python ctypes call per step) does not sit between kernels that last a few microseconds."""
-    fn = (lambda i: wl.e2e_step(i, stream)) if e2e else (lambda i: wl.step(i, stream))
+    cost (a Python ctypes call per step) does not sit between kernels that last a few microseconds.
+    The end-to-end measurement alternates two streams (and two buffer sets), so that the copy-out of one
+    step overlaps the copy-in of the next on the full-duplex host link; it is timed on the first stream,
+    which waits for the second before the closing event."""
+    import ctypes as C
+    streams = [stream, stream2 if (e2e and stream2) else stream]
+
+    def fn(i):
+        if e2e:
+            wl.pin.slot = i % 2
+            wl.e2e_step(i, streams[i % 2])
+        else:
+            wl.step(i, stream)
+
     for i in range(warmup):
         fn(i)
     ab.sync(stream)
+    if streams[1] is not stream:
+        ab.sync(streams[1])
     graph = None
     if not e2e:
         graph = ab.Graph(stream, lambda: [fn(warmup + i) for i in range(steps)])
@@ -626,10 +665,19 @@ def time_steps(ab, wl, comm, steps, warmup, stream, e2e=False):
     if graph:
         graph.launch()
     else:
+        if streams[1] is not stream:   # the second stream starts after the opening event
+            ab.check(ab.lib().ascb200_stream_wait_event(streams[1], timer.e0))
         for i in range(steps):
             fn(warmup + i)
+        if streams[1] is not stream:
+            ev = C.c_void_p()
+            ab.check(ab.lib().ascb200_event_create(C.byref(ev)))
+            ab.check(ab.lib().ascb200_event_record(ev, streams[1]))
+            ab.check(ab.lib().ascb200_stream_wait_event(stream, ev))
     ms = timer.stop_ms()
     ab.sync(stream)
+    if streams[1] is not stream:
+        ab.sync(streams[1])
     comm.barrier()
     if graph:
         graph.destroy()
@@ -680,7 +728,10 @@ def measure(ab, cls, comm, rank, world, args, peaks, with_cpu, clock_index):
         ms_e2e, with_cpu = float("nan"), False
     else:
         wl.e2e_setup()
-        ms_e2e = time_steps(ab, wl, comm, e2e_steps, 3, stream, e2e=True)
+        stream2_p = __import__("ctypes").c_void_p()
+        ab.check(ab.lib().ascb200_stream_create(__import__("ctypes").byref(stream2_p)))
+        ms_e2e = time_steps(ab, wl, comm, e2e_steps, 4, stream, e2e=True, stream2=stream2_p.value)
+        ab.lib().ascb200_stream_destroy(stream2_p.value)
 
     per_step_s = ms / 1e3 / args.steps
     value = wl.units_total() / per_step_s / wl.unit_scale
@@ -696,6 +747,11 @@ def measure(ab, cls, comm, rank, world, args, peaks, with_cpu, clock_index):
                 "d2h_bytes_per_step": int(bo), "steps": e2e_steps},
         "gpu_launches": args.steps * wl.kernels_per_step, "clocks": clocks, "parity_spot_check": verified,
     }
+    if getattr(args, "allgather", False) and world > 1 and hasattr(wl, "n_loc"):
+        slab_bytes = wl.c[0].nbytes
+        ms_ag, ok_ag = comm.allgather_ms(ab, wl.c[0], slab_bytes)
+        line["allgather"] = {"ms": round(ms_ag, 4), "bytes_per_rank": slab_bytes, "layout": "[rank][M][N/ranks]", "ok": ok_ag,
+                             "busbw_gbs": round(slab_bytes * (world - 1) / (ms_ag / 1e3) / 1e9, 1)}
     if wl.published:
         line["vs_published_other_hw"] = {"ratio": round(value / wl.published[0], 3), "what": wl.published[1]}
     if with_cpu:
@@ -754,6 +810,8 @@ def main():
     ap.add_argument("--workload", default="a8w8", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ascb200", choices=["ascb200", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the other baseline configurations at N=1")
+    ap.add_argument("--allgather", action="store_true",
+                    help="N>1, N-slab workloads: also time the NCCL all-gather that gives every rank all C slabs ([rank][M][N/ranks])")
     ap.add_argument("--kernel-only", action="store_true", help="time the device-resident step only (no e2e, no CPU baseline): profiling runs")
     args = ap.parse_args()
     rank, local_rank, world = dist_env()

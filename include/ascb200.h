@@ -79,6 +79,7 @@ ASCB200_API int ascb200_stream_sync(void* stream);
 ASCB200_API int ascb200_event_create(void** event);
 ASCB200_API int ascb200_event_destroy(void* event);
 ASCB200_API int ascb200_event_record(void* event, void* stream);
+ASCB200_API int ascb200_stream_wait_event(void* stream, void* event);          /* later work on stream waits for event */
 ASCB200_API int ascb200_event_elapsed_ms(void* start, void* stop, float* ms); /* synchronises on stop */
 
 /* CUDA-graph shims: record the calls issued on `stream` between begin and end into one graph and
