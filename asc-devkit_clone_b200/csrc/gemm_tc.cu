@@ -149,10 +149,13 @@ __device__ __forceinline__ bool locate_tile(const GemmParams& p, int tile, int n
 }
 
 // ---- epilogue helpers -------------------------------------------------------------------------
+// FasterGelu of the grouped example: x * e^(0.851 (x - |x|)) / (1 + e^(-1.702 |x|))
+// (quant_group_matmul_high_performance/scripts/gen_data.py:19-23), which is x / (1 + e^(-1.702 x)) written
+// so that no exponential overflows.  Evaluated in the short form with one ex2 and one fast division:
+// for x << 0 the exponential overflows to +inf and the quotient is -0, the limit of the long form.
 __device__ __forceinline__ float faster_gelu(float x)
 {
-    const float ax = fabsf(x);
-    return x * __expf(0.851f * (x - ax)) / (1.0f + __expf(-1.702f * ax));
+    return __fdividef(x, 1.0f + __expf(-1.702f * x));
 }
 
 __device__ __forceinline__ void st_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
@@ -1067,24 +1070,38 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     const uint32_t row_elems = ROW_BYTES / esz;        // tensor-map elements per 128-byte row
     const int block_k = bits == 16 ? 64 : bits == 8 ? 128 : 256;
 
-    int block_n = 256;
-    {
-        const long long num_m = grouped ? (m + BLOCK_M - 1) / BLOCK_M + groups : (m + BLOCK_M - 1) / BLOCK_M;
-        while (block_n > 64 && (n <= block_n / 2 || num_m * ((n + block_n - 1) / block_n) < sm_count)) block_n /= 2;
-        if (kind == ASCB200_KIND_MXFP4 && block_n < 128) block_n = 128;
-        // fp4 at 256 columns cannot double-buffer its accumulators (TMEM also holds the scales): 192 can
-        if (kind == ASCB200_KIND_MXFP4 && block_n == 256) block_n = 192;
-        // an N-contiguous 8-bit B tile is fetched in boxes of 128 columns (one 128-byte swizzle row)
-        if (kind == ASCB200_KIND_S8 && !d->trans_b && block_n < 128) block_n = 128;
-    }
-
-    // CTA pairs (256 x 256 tiles) for plain fp16 / bf16 / int8 problems with enough tiles to fill every pair of SMs
+    // Tile choice: estimated time = waves x tile work / efficiency of that tile shape (wider tiles read less shared
+    // memory and L2 per MAC; measured on 4096 x 4096 x 11008 int8: pair 256x256 1.0, single 128x256 0.88, 128x128 0.75,
+    // 128x64 0.5).  Small problems and thin N-slabs get narrower tiles so that the last wave is not mostly idle.
     const int pair_clusters = sm_count / 2;
-    const int pair_n = kind == ASCB200_KIND_MXFP4 ? 192 : 256;
-    const long long pair_tiles = static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((n + pair_n - 1) / pair_n);
-    // (the allocation-free variant keeps the compact scale layout of the single-CTA kernel: its scratch is fixed)
-    const bool use_pair = !grouped && block_n == pair_n && pair_tiles >= pair_clusters && !(fixed && kind == ASCB200_KIND_MXFP4) &&
-                          !(getenv("ASCB200_NO_PAIR") && getenv("ASCB200_NO_PAIR")[0] == '1');
+    const bool pair_allowed = !grouped && !(fixed && kind == ASCB200_KIND_MXFP4) && !(getenv("ASCB200_NO_PAIR") && getenv("ASCB200_NO_PAIR")[0] == '1');
+    const int wide = kind == ASCB200_KIND_MXFP4 ? 192 : 256;   // fp4 at 256 columns cannot double-buffer its accumulators in TMEM
+    int block_n = 64;
+    bool use_pair = false;
+    {
+        const long long m_tiles = grouped ? (m + BLOCK_M - 1) / BLOCK_M + groups : (m + BLOCK_M - 1) / BLOCK_M;
+        double best = -1.0;
+        struct Cand { int bn; bool pair; double eff; };
+        const Cand cands[] = {{wide, true, 1.0}, {wide, false, 0.88}, {128, false, 0.75}, {64, false, 0.5}};
+        for (const Cand& c : cands) {
+            if (c.pair && !pair_allowed) continue;
+            if (c.bn == 64 && kind == ASCB200_KIND_MXFP4) continue;                          // scale blocks span 128 rows
+            if (c.bn == 64 && kind == ASCB200_KIND_S8 && !d->trans_b) continue;              // N-contiguous int8 B comes in boxes of 128 columns
+            if (c.bn > 64 && n <= c.bn / 2 && c.bn != 128) continue;                         // do not pad N by more than 2x
+            const long long n_tiles = (n + c.bn - 1) / c.bn;
+            const long long tiles = c.pair ? static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * n_tiles : m_tiles * n_tiles;
+            const long long slots = c.pair ? pair_clusters : sm_count;
+            const long long waves = (tiles + slots - 1) / slots;
+            const double cost = static_cast<double>(waves) * (c.pair ? 2 : 1) * BLOCK_M * c.bn / c.eff / (c.pair ? 2 : 1);
+            if (best < 0 || cost < best) {
+                best = cost;
+                block_n = c.bn;
+                use_pair = c.pair;
+            }
+        }
+    }
+    const long long pair_tiles = static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((n + block_n - 1) / block_n);
+
     const int b_box_rows = use_pair ? block_n / 2 : block_n;
 
     CUtensorMap ta, tb;
