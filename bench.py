@@ -760,7 +760,7 @@ def measure(ab, cls, comm, rank, world, args, peaks, with_cpu, clock_index):
     return line
 
 
-def run_reference_arm(args, rank, world):
+def run_reference_arm(args, rank, world, out):
     """CPU restatement of the reference arithmetic, all host threads, bounded sample per step."""
     if rank != 0:
         return
@@ -799,10 +799,25 @@ def run_reference_arm(args, rank, world):
         "e2e": {"value": round(value, 6), "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "CPU restatement of the reference arithmetic (oracle/asc_oracle.c, OpenMP); the reference's CPU-debug build needs the closed CANN CPU twin",
     }
-    print(json.dumps(line), flush=True)
+    out.emit(json.dumps(line))
+
+
+class OneLineStdout:
+    """Everything that libraries print to stdout (NCCL's version banner, for one) is sent to stderr; the
+    JSON line is written to the real stdout at the end, so that stdout carries exactly one line."""
+
+    def __init__(self):
+        sys.stdout.flush()
+        self.real = os.dup(1)
+        os.dup2(2, 1)
+
+    def emit(self, text):
+        sys.stdout.flush()
+        os.write(self.real, (text + "\n").encode())
 
 
 def main():
+    out = OneLineStdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -816,7 +831,7 @@ def main():
     args = ap.parse_args()
     rank, local_rank, world = dist_env()
     if args.impl == "reference":
-        run_reference_arm(args, rank, world)
+        run_reference_arm(args, rank, world, out)
         return
 
     import ascb200 as ab
@@ -834,11 +849,11 @@ def main():
             sub.steps = min(args.steps, 50)
             o = measure(ab, cls, comm, rank, world, sub, peaks, with_cpu=True, clock_index=local_rank)
             others.append({k: o[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "config", "roofline", "e2e", "cpu_baseline",
-                                             "clocks", "parity_spot_check", "gpu_launches") if k in o})
+                                             "clocks", "parity_spot_check", "gpu_launches", "vs_published_other_hw") if k in o})
         line["others"] = others
     comm.close()
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        out.emit(json.dumps(line))
 
 
 if __name__ == "__main__":
