@@ -98,6 +98,9 @@ class Workload:
     scaling = "strong"
     kernels_per_step = 1
     published = None  # (value, note) of a like-for-like number in BASELINE.md
+    # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, per launch, from the ncu capture summarised in
+    # profiles/ (1 GPU, whole configuration); None where no capture exists
+    traffic_1gpu = None
 
     def units_total(self):       # algorithmic operations (or bytes) of the whole job per step
         raise NotImplementedError
@@ -119,6 +122,7 @@ class A8W8(Workload):
     name = "a8w8_gemm_4096x4096x11008_dequant_bf16"
     metric, unit, dtype = "quant-GEMM throughput (int8, fused per-token x per-channel dequant)", "TOPS", "s8"
     M, K, N = 4096, 4096, 11008
+    traffic_1gpu = 62.19e6 + 45.22e6   # profiles/gemm_tc_pair_kernel_int8_a8w8_4096x4096x11008.md
 
     def __init__(self, ab, rank, world, sets):
         self.ab, self.rank, self.world = ab, rank, world
@@ -187,6 +191,7 @@ class Grouped(Workload):
     metric, unit, dtype = "grouped quant-GEMM throughput (int8, fused dequant)", "TOPS", "s8"
     G, MTOT, K, N = 64, 32768, 7168, 2048
     OUT, ACT = "BF16", 0
+    traffic_1gpu = 1.2132e9 + 0.1228e9   # profiles/gemm_tc_kernel_int8_grouped_64groups_M32768_K7168_N2048.md
 
     def counts(self):
         return dirichlet_counts(self.G, self.MTOT, 0xA5C00003)
@@ -266,6 +271,7 @@ class MXFP4(Workload):
     metric, unit, dtype = "quant-GEMM throughput (MXFP4 e2m1 x ue8m0, int8 requant + bf16 out)", "TFLOPS", "fp4_e2m1"
     M = K = N = 8192
     kernels_per_step = 3  # two scale re-tiling launches + the GEMM
+    traffic_1gpu = 138.1e6 + 170.4e6    # profiles/gemm_tc_pair_kernel_mxfp4_8192x8192x8192.md
     published = (1614.0, "Ascend 950PR basic-API MXFP4 8192^3, bf16 out (BASELINE.md)")
 
     def __init__(self, ab, rank, world, sets):
@@ -342,6 +348,7 @@ class SoftmaxQuant(Workload):
     scaling = "weak"  # rows are independent; every rank runs its own replica of the configuration
     M, K = 4096, 2048
     ROW_FACTOR = 1
+    traffic_1gpu = 16.8e6               # profiles/softmax_rows_kernel_fused_quant_4096x2048.md (outputs still in L2 at kernel end)
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
@@ -410,6 +417,7 @@ class SoftmaxQuantLarge(SoftmaxQuant):
     baseline shape lasts only a few microseconds, so launch ramp-up and tail dominate its bandwidth figure."""
     name = "softmax_ascendquant_262144x2048_fp16_int8"
     ROW_FACTOR = 64
+    traffic_1gpu = 1.0738e9 + 1.5555e9  # profiles/softmax_rows_kernel_fused_quant_262144x2048.md
 
 
 class FP16(Workload):
@@ -534,6 +542,7 @@ class GroupedRefShape(Grouped):
     name = "grouped_a8w8_8groups_M8192_K1024_N8192_gelu_fp16"
     metric = "grouped quant-GEMM throughput (the reference example's shape, FasterGelu, fp16 out)"
     G, MTOT, K, N = 8, 8192, 1024, 8192
+    traffic_1gpu = None
     published = (2.0 * 8192 * 1024 * 8192 / 204.129e-6 / 1e12, "Ascend 950PR, 204.129 us (BASELINE.md)")
     OUT, ACT = "F16", 1
 
@@ -742,7 +751,9 @@ def measure(ab, cls, comm, rank, world, args, peaks, with_cpu, clock_index):
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 6), "higher_is_better": True, "scaling": wl.scaling,
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
         "roofline": {"bound": wl.bound, "achieved": round(achieved, 3), "peak": round(peak, 1), "unit": punit,
-                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": f"{peaks['source']}: {pnote}"},
+                     "frac": round(achieved / peak, 4), "traffic": (wl.traffic_1gpu if world == 1 else None),
+                     "algorithmic": wl.units_rank() if wl.bound == "hbm" else getattr(wl, "algorithmic_bytes", None),
+                     "peak_source": f"{peaks['source']}: {pnote}"},
         "e2e": {"value": round(wl.units_total() / (ms_e2e / 1e3 / e2e_steps) / wl.unit_scale, 4), "unit": wl.unit, "h2d_bytes_per_step": int(bi),
                 "d2h_bytes_per_step": int(bo), "steps": e2e_steps},
         "gpu_launches": args.steps * wl.kernels_per_step, "clocks": clocks, "parity_spot_check": verified,
