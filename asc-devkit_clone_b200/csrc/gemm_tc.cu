@@ -158,6 +158,24 @@ __device__ __forceinline__ float faster_gelu(float x)
     return __fdividef(x, 1.0f + __expf(-1.702f * x));
 }
 
+// fp32 -> int8 value, round to nearest even, saturating, NaN -> 0 (one conversion instruction).
+__device__ __forceinline__ int cvt_rni_sat_s8(float v)
+{
+    int r;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r;
+}
+// Two independent fp32 products in one instruction (round to nearest, no fusion with anything else).
+__device__ __forceinline__ float2 mul_f32x2(float2 a, float2 b)
+{
+    unsigned long long x, y, z;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(y) : "f"(b.x), "f"(b.y));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(z) : "l"(x), "l"(y));
+    float2 r;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(z));
+    return r;
+}
 __device__ __forceinline__ void st_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
     *reinterpret_cast<uint4*>(p) = make_uint4(a, b, c, d);
@@ -248,9 +266,11 @@ __device__ __forceinline__ void load_params32(const float* p, int ncols, float (
 // MODE / DT are compile-time so that each combination is a short straight-line sequence.
 // chan0: index of column col0 in bias / quant; ch_off: index in the per-channel scale array.
 template <bool ACC_INT, int MODE, int DT>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const EpiParams& e, int row, int col0, int ncols, size_t chan0,
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const EpiParams& e, int row, bool row_ok, int col0, int ncols, size_t chan0,
                                                size_t ch_off, float tok)
 {
+    // Runs on all 32 lanes (the quantising path exchanges per-column parameters with shuffles); lanes whose
+    // row lies outside the matrix compute on whatever their TMEM lane holds and store nothing.
     float f[32];
     int qi[32];
     if constexpr (ACC_INT) {
@@ -275,7 +295,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = __fadd_rn(f[j], b[j]);
         }
-        if (e.c2) {
+        if (e.c2 && row_ok) {
             if (e.c2_dtype == OUT_BF16) store_row32<OUT_BF16>(e.c2, e.ldc2, e.vec_c2, row, col0, ncols, f, qi);
             else if (e.c2_dtype == OUT_F16) store_row32<OUT_F16>(e.c2, e.ldc2, e.vec_c2, row, col0, ncols, f, qi);
             else store_row32<OUT_F32>(e.c2, e.ldc2, e.vec_c2, row, col0, ncols, f, qi);
@@ -290,19 +310,52 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
             }
         }
     } else if constexpr (MODE == ASCB200_EPI_FIXPIPE_QUANT) {
+        // Lane j decodes the parameter of column j once (scale = bits [31:13], 9-bit offset); every lane then
+        // fetches the 32 decoded values with shuffles instead of loading and decoding them itself.
+        const int lane = threadIdx.x & 31;
+        const unsigned long long q = (e.quant && lane < ncols) ? __ldg(e.quant + chan0 + lane) : e.quant_scalar;
+        const float my_alpha = quant_alpha(q), my_off = quant_offset(q);
+        const bool any_off = __any_sync(0xFFFFFFFFu, my_off != 0.0f);
+        if (DT == OUT_S8 && !any_off && !e.relu) {
+            // no offsets in this chunk: rint(clip(rint(clip(v, -256, 255)), -128, 127)) == rint-and-saturate of v; NaN -> 0
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const unsigned long long q = (e.quant && j < ncols) ? __ldg(e.quant + chan0 + j) : e.quant_scalar;
-            const float v = (f[j] >= 0.0f || !e.relu) ? __fmul_rn(f[j], quant_alpha(q)) : 0.0f;
-            if constexpr (DT == OUT_S8) {
-                // REQ8 / QF322B8_PRE: clip to 9 bits, round, add the offset, clip to int8
-                const float t = rintf(fminf(fmaxf(v, -256.0f), 255.0f)) + quant_offset(q);
-                qi[j] = (v != v) ? 0 : __float2int_rn(fminf(fmaxf(t, -128.0f), 127.0f));
+            for (int j = 0; j < 32; j += 2) {
+                const float2 v = mul_f32x2(make_float2(f[j], f[j + 1]),
+                                           make_float2(__shfl_sync(0xFFFFFFFFu, my_alpha, j), __shfl_sync(0xFFFFFFFFu, my_alpha, j + 1)));
+                qi[j] = cvt_rni_sat_s8(v.x);
+                qi[j + 1] = cvt_rni_sat_s8(v.y);
             }
-            f[j] = v;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float alpha = __shfl_sync(0xFFFFFFFFu, my_alpha, j);
+                const float v = (f[j] >= 0.0f || !e.relu) ? __fmul_rn(f[j], alpha) : 0.0f;
+                if constexpr (DT == OUT_S8) {
+                    // REQ8 / QF322B8_PRE: clip to 9 bits, round, add the offset, clip to int8
+                    const float t = rintf(fminf(fmaxf(v, -256.0f), 255.0f)) + __shfl_sync(0xFFFFFFFFu, my_off, j);
+                    qi[j] = (v != v) ? 0 : __float2int_rn(fminf(fmaxf(t, -128.0f), 127.0f));
+                }
+                f[j] = v;
+            }
         }
-    } else {  // ASCB200_EPI_DEQUANT_TOKEN_CHANNEL
+    } else if (e.act == 0) {  // ASCB200_EPI_DEQUANT_TOKEN_CHANNEL without activation: two packed multiplies per column pair
         float s[32];
+        load_params32(e.ch + ch_off, ncols, s);
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+            // (acc * ch[n]) * tok[m], each product rounded to nearest like the separate Mul steps of the reference
+            float2 v = mul_f32x2(mul_f32x2(make_float2(f[j], f[j + 1]), make_float2(s[j], s[j + 1])), make_float2(tok, tok));
+            f[j] = v.x;
+            f[j + 1] = v.y;
+        }
+    } else {  // ASCB200_EPI_DEQUANT_TOKEN_CHANNEL with FasterGelu
+        float s[32];
+#ifdef ASCB200_PROBE
+        if (e.probe & 16) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) s[j] = 1.5f;
+        } else
+#endif
         load_params32(e.ch + ch_off, ncols, s);
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -311,7 +364,15 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
             f[j] = v;
         }
     }
-    store_row32<DT>(e.c, e.ldc, e.vec_c, row, col0, ncols, f, qi);
+#ifdef ASCB200_PROBE
+    if (e.probe & 8) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc += f[j] + static_cast<float>(qi[j] & 1);
+        if (acc != 12345.678f) return;
+    }
+#endif
+    if (row_ok) store_row32<DT>(e.c, e.ldc, e.vec_c, row, col0, ncols, f, qi);
 }
 
 // Drains this warp's share of one accumulator tile: TMEM lanes of `quad`, chunks [chunk0, chunk1).
@@ -331,9 +392,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
 #ifdef ASCB200_PROBE
         if (p.probe & 4) continue;
 #endif
-        if (row_ok)
-            epilogue_chunk<ACC_INT, MODE, DT>(r, p.epi, row, col0, min(32, p.n - col0), static_cast<size_t>(col0),
-                                              static_cast<size_t>(t.group) * p.n + col0, tok);
+        epilogue_chunk<ACC_INT, MODE, DT>(r, p.epi, row, row_ok, col0, min(32, p.n - col0), static_cast<size_t>(col0),
+                                          static_cast<size_t>(t.group) * p.n + col0, tok);
     }
 }
 
