@@ -98,27 +98,28 @@ __device__ __forceinline__ float row_reduce_sum(float v, float* red)
 
 // One row per group of TPR threads (a warp, or the whole block).  Thread t of the group owns the
 // 16-byte chunks t, t+TPR, ... (NCHUNK of them).  T = __half (8 per chunk) or float (4 per chunk).
-template <typename T, int TPR, int NCHUNK, bool QUANT>
-__global__ void __launch_bounds__(TPR > 32 ? TPR : 128)
-softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __restrict__ sum_out, float* __restrict__ max_out,
-                    int8_t* __restrict__ q_out, const __half* __restrict__ q_scale, const __half* __restrict__ q_offset,
-                    __half q_offset_scalar, int m, int k, int stats_rep)
+// Warp rows (TPR == 32) are persistent: the grid is sized to the machine, every warp walks rows
+// row, row + #warps, ... and issues the loads of its next row before it works on the current one,
+// so that no wave of blocks ends with a mostly idle machine and HBM requests stay in flight.
+template <typename T, int TPR, int NCHUNK>
+__device__ __forceinline__ void softmax_load_row(const T* __restrict__ srow, int t, int nchunks, uint4 (&raw)[NCHUNK])
 {
     constexpr int VEC = 16 / sizeof(T);
-    __shared__ float red[32];
-    const int t = TPR > 32 ? threadIdx.x : (threadIdx.x & 31);
-    const int row = TPR > 32 ? blockIdx.x : blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= m) return;  // whole group leaves together
-    const int nchunks = k / VEC;
-    const T* srow = src + static_cast<size_t>(row) * k;
-
-    float v[NCHUNK * VEC];
-    uint4 raw[NCHUNK];
 #pragma unroll
     for (int i = 0; i < NCHUNK; ++i) {
         const int c = t + i * TPR;
         if (c < nchunks) raw[i] = ldg_nc_v4(srow + c * VEC);
     }
+}
+
+template <typename T, int TPR, int NCHUNK, bool QUANT>
+__device__ __forceinline__ void softmax_one_row(const uint4 (&raw)[NCHUNK], int row, int t, int nchunks, T* __restrict__ dst,
+                                                float* __restrict__ sum_out, float* __restrict__ max_out, int8_t* __restrict__ q_out,
+                                                const __half* __restrict__ q_scale, const __half* __restrict__ q_offset, __half q_offset_scalar,
+                                                int k, int stats_rep, float* red)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    float v[NCHUNK * VEC];
     float mx = kNegInf;
 #pragma unroll
     for (int i = 0; i < NCHUNK; ++i) {
@@ -191,15 +192,67 @@ softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __res
     }
 }
 
+constexpr int kSoftmaxWarpBlock = 224;  // 7 warps; two such blocks per SM
+
+// PERSIST (warp rows only): few rows per warp -> machine-sized grid with next-row prefetch; many rows ->
+// one row per warp and small blocks, where 20 resident warps per SM keep more requests in flight.
+template <typename T, int TPR, int NCHUNK, bool QUANT, bool PERSIST>
+__global__ void __launch_bounds__(TPR > 32 ? TPR : (PERSIST ? kSoftmaxWarpBlock : 128), TPR > 32 ? 1 : (PERSIST ? 2 : 5))
+softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __restrict__ sum_out, float* __restrict__ max_out,
+                    int8_t* __restrict__ q_out, const __half* __restrict__ q_scale, const __half* __restrict__ q_offset,
+                    __half q_offset_scalar, int m, int k, int stats_rep)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    __shared__ float red[32];
+    const int nchunks = k / VEC;
+    if constexpr (TPR > 32) {
+        const int row = blockIdx.x;
+        uint4 raw[NCHUNK];
+        softmax_load_row<T, TPR, NCHUNK>(src + static_cast<size_t>(row) * k, threadIdx.x, nchunks, raw);
+        softmax_one_row<T, TPR, NCHUNK, QUANT>(raw, row, threadIdx.x, nchunks, dst, sum_out, max_out, q_out, q_scale, q_offset, q_offset_scalar, k,
+                                               stats_rep, red);
+    } else {
+        const int t = threadIdx.x & 31;
+        const int warps_per_block = blockDim.x >> 5;
+        const int stride = gridDim.x * warps_per_block;
+        int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+        if (row >= m) return;  // whole warp leaves together
+        uint4 raw[NCHUNK];
+        softmax_load_row<T, TPR, NCHUNK>(src + static_cast<size_t>(row) * k, t, nchunks, raw);
+        if constexpr (!PERSIST) {
+            softmax_one_row<T, TPR, NCHUNK, QUANT>(raw, row, t, nchunks, dst, sum_out, max_out, q_out, q_scale, q_offset, q_offset_scalar, k,
+                                                   stats_rep, red);
+            return;
+        }
+        while (true) {
+            const int next = row + stride;
+            uint4 ahead[NCHUNK];
+            if (next < m) softmax_load_row<T, TPR, NCHUNK>(src + static_cast<size_t>(next) * k, t, nchunks, ahead);
+            softmax_one_row<T, TPR, NCHUNK, QUANT>(raw, row, t, nchunks, dst, sum_out, max_out, q_out, q_scale, q_offset, q_offset_scalar, k,
+                                                   stats_rep, red);
+            if (next >= m) break;
+#pragma unroll
+            for (int i = 0; i < NCHUNK; ++i) raw[i] = ahead[i];
+            row = next;
+        }
+    }
+}
+
 template <typename T, bool QUANT>
 int launch_softmax(const T* src, T* dst, float* sum, float* mx, int8_t* q, const __half* qs, const __half* qo, __half qos, int m,
-                   int k, int rep, cudaStream_t st)
+                   int k, int rep, int sms, cudaStream_t st)
 {
+    constexpr int wpb = kSoftmaxWarpBlock / 32;
+    const int warp_grid = std::min((m + wpb - 1) / wpb, 2 * sms);  // persistent: at most two blocks per SM
+    const bool persist = m <= 4 * 2 * sms * wpb;                    // up to four rows per warp
     constexpr int VEC = 16 / sizeof(T);
     const int nchunks = k / VEC;
 #define ASCB200_SM_WARP(NC)                                                                                              \
-    softmax_rows_kernel<T, 32, NC, QUANT><<<(m + 3) / 4, 128, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep)
-#define ASCB200_SM_BLOCK(TPR, NC) softmax_rows_kernel<T, TPR, NC, QUANT><<<m, TPR, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep)
+    do {                                                                                                                  \
+        if (persist) softmax_rows_kernel<T, 32, NC, QUANT, true><<<warp_grid, kSoftmaxWarpBlock, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep); \
+        else softmax_rows_kernel<T, 32, NC, QUANT, false><<<(m + 3) / 4, 128, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep);                \
+    } while (0)
+#define ASCB200_SM_BLOCK(TPR, NC) softmax_rows_kernel<T, TPR, NC, QUANT, false><<<m, TPR, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep)
     if (nchunks <= 32) ASCB200_SM_WARP(1);
     else if (nchunks <= 64) ASCB200_SM_WARP(2);
     else if (nchunks <= 128) ASCB200_SM_WARP(4);
@@ -385,9 +438,9 @@ int ascb200_softmax(const void* src, void* dst, float* sum, float* mx, int32_t m
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == ASCB200_F16)
         return launch_softmax<__half, false>(static_cast<const __half*>(src), static_cast<__half*>(dst), sum, mx, nullptr, nullptr,
-                                             nullptr, __half(), m, k, rep, s);
+                                             nullptr, __half(), m, k, rep, st->sm_count, s);
     return launch_softmax<float, false>(static_cast<const float*>(src), static_cast<float*>(dst), sum, mx, nullptr, nullptr, nullptr,
-                                        __half(), m, k, rep, s);
+                                        __half(), m, k, rep, st->sm_count, s);
 }
 
 int ascb200_softmax_quant(const void* src, void* dst, float* sum, float* mx, int8_t* q, const void* scale, const void* offset_t,
@@ -402,7 +455,7 @@ int ascb200_softmax_quant(const void* src, void* dst, float* sum, float* mx, int
     if (m == 0) return ASCB200_OK;
     return launch_softmax<__half, true>(static_cast<const __half*>(src), static_cast<__half*>(dst), sum, mx, q,
                                         static_cast<const __half*>(scale), static_cast<const __half*>(offset_t),
-                                        __float2half_rn(offset), m, k, stats_brc ? 8 : 1, static_cast<cudaStream_t>(stream));
+                                        __float2half_rn(offset), m, k, stats_brc ? 8 : 1, st->sm_count, static_cast<cudaStream_t>(stream));
 }
 
 int ascb200_quant_per_tensor(const void* src, int8_t* dst, int64_t cal_count, int32_t dtype, float scale, float offset, void* stream)
