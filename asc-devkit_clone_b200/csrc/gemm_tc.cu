@@ -471,11 +471,9 @@ struct IssueCursor {
     }
 };
 
-// Issues the tensor-core work of one K block (four MMAs, preceded by the scale-factor copies for
-// MXFP4) and the commit that releases the shared-memory stage.
+// Scale-factor copies of one K block (MXFP4 only): shared memory -> the stage's TMEM columns.
 template <int KIND, bool PAIR, int SF_B_BLOCKS, class Cursor>
-__device__ __forceinline__ void issue_k_block(const Cursor& c, uint32_t d_tmem, uint32_t hi_word, uint32_t a_kstep16, uint32_t b_kstep16,
-                                              uint32_t idesc, uint32_t idesc_hi_sf, uint32_t sfb_col_offset, bool first)
+__device__ __forceinline__ void issue_sf_copies(const Cursor& c)
 {
     if constexpr (KIND == KIND_MXF4 && PAIR) {
         // Scales arrive replicated (one 512-byte copy per 32-lane quadrant): per 128-row block and K block
@@ -488,11 +486,6 @@ __device__ __forceinline__ void issue_k_block(const Cursor& c, uint32_t d_tmem, 
         sf_copy_128x256b_pair(c.sf_tmem + 0, ((2048u >> 4) << 16) | addr16, sf_hi);
         sf_copy_128x256b_pair(c.sf_tmem + 8, ((4096u >> 4) << 16) | (addr16 + (4096u >> 4)), sf_hi);
         sf_copy_128x256b_pair(c.sf_tmem + 16, ((4096u >> 4) << 16) | (addr16 + (4096u >> 4) + (2048u >> 4)), sf_hi);
-        const uint32_t sfb = c.sf_tmem + 8 + sfb_col_offset;
-        mma_issue_mxf4<PAIR>(d_tmem, c.a_lo, hi_word, c.b_lo, hi_word, idesc, c.sf_tmem, sfb, first ? 0u : 1u);
-        mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 2, hi_word, c.b_lo + 2, hi_word, idesc_hi_sf, c.sf_tmem, sfb, 1u);
-        mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 4, hi_word, c.b_lo + 4, hi_word, idesc, c.sf_tmem + 4, sfb + 8, 1u);
-        mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 6, hi_word, c.b_lo + 6, hi_word, idesc_hi_sf, c.sf_tmem + 4, sfb + 8, 1u);
     } else if constexpr (KIND == KIND_MXF4) {
         constexpr uint32_t sf_hi = (128u >> 4) | (1u << 14);  // stride 128 bytes between 8-row groups, descriptor version 1
         // chunk order in shared memory: A kc0, A kc1, then per 128-row block of B: kc0, kc1 (512 bytes each)
@@ -503,6 +496,15 @@ __device__ __forceinline__ void issue_k_block(const Cursor& c, uint32_t d_tmem, 
             sf_copy_issue<PAIR>(c.sf_tmem + 8 + rb * 4, c.sf_lo + 64 + rb * 64, sf_hi);
             sf_copy_issue<PAIR>(c.sf_tmem + 16 + rb * 4, c.sf_lo + 96 + rb * 64, sf_hi);
         }
+    }
+}
+
+// The four MMAs of one K block and the commit that releases the shared-memory stage.
+template <int KIND, bool PAIR, class Cursor>
+__device__ __forceinline__ void issue_mmas(const Cursor& c, uint32_t d_tmem, uint32_t hi_word, uint32_t a_kstep16, uint32_t b_kstep16,
+                                           uint32_t idesc, uint32_t idesc_hi_sf, uint32_t sfb_col_offset, bool first)
+{
+    if constexpr (KIND == KIND_MXF4) {
         const uint32_t sfb = c.sf_tmem + 8 + sfb_col_offset;
         mma_issue_mxf4<PAIR>(d_tmem, c.a_lo, hi_word, c.b_lo, hi_word, idesc, c.sf_tmem, sfb, first ? 0u : 1u);
         mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 2, hi_word, c.b_lo + 2, hi_word, idesc_hi_sf, c.sf_tmem, sfb, 1u);
@@ -515,6 +517,16 @@ __device__ __forceinline__ void issue_k_block(const Cursor& c, uint32_t d_tmem, 
         mma_issue<KIND, PAIR>(d_tmem, c.a_lo + 3 * a_kstep16, hi_word, c.b_lo + 3 * b_kstep16, hi_word, idesc, 1u);
     }
     commit_issue<PAIR>(c.empty_bar);
+}
+
+// Issues the tensor-core work of one K block (four MMAs, preceded by the scale-factor copies for
+// MXFP4) and the commit that releases the shared-memory stage.
+template <int KIND, bool PAIR, int SF_B_BLOCKS, class Cursor>
+__device__ __forceinline__ void issue_k_block(const Cursor& c, uint32_t d_tmem, uint32_t hi_word, uint32_t a_kstep16, uint32_t b_kstep16,
+                                              uint32_t idesc, uint32_t idesc_hi_sf, uint32_t sfb_col_offset, bool first)
+{
+    issue_sf_copies<KIND, PAIR, SF_B_BLOCKS>(c);
+    issue_mmas<KIND, PAIR>(c, d_tmem, hi_word, a_kstep16, b_kstep16, idesc, idesc_hi_sf, sfb_col_offset, first);
 }
 
 // ---- the kernel --------------------------------------------------------------------------------
@@ -582,7 +594,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     if (lane == 0) mbar_arrive(smem_u32(&full_bar[stage]));
                 } else
 #endif
-                if (lane == 0) {
+                if (elect_one()) {
                     const uint32_t bar = smem_u32(&full_bar[stage]);
                     const uint32_t sa = smem_u32(tiles + stage * C::STAGE_BYTES);
                     const uint32_t sb = sa + A_TILE_BYTES;
@@ -652,7 +664,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 ok = mbar_wait(cur.full_bar, cur.phase, abort_word, p.status);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) {
+                if (elect_one()) {
                     issue_k_block<KIND, false, C::SF_B_BLOCKS>(cur, d_tmem, hi_word, a_k16, b_k16, p.idesc, idesc_hi_sf, sfb_off, kb == 0);
                     if (kb == last) tc_commit(acc_full);
                 }
@@ -705,6 +717,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // and fetches half of B from L2.  The even CTA issues the MMAs; completion is signalled to both
 // CTAs with multicast commits; epilogue warps of both CTAs release the accumulator stage on the
 // leader's barrier.  Plain (non-grouped) problems only.
+#ifdef ASCB200_PROBE
+__device__ unsigned long long g_probe_times[8];
+#endif
+
 template <int KIND, int BLOCK_N>
 struct Cfg2 {
     static constexpr int B_TILE_BYTES = (BLOCK_N / 2) * ROW_BYTES;
@@ -746,6 +762,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();   // 0 = leader
+#ifdef ASCB200_PROBE
+    const long long tk0 = clock64();
+    unsigned long long tg0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tg0));
+#endif
     const int cluster_id = blockIdx.x >> 1;
     const int num_clusters = gridDim.x >> 1;
     const int num_n = (p.n + BLOCK_N - 1) / BLOCK_N;
@@ -787,7 +808,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                 ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_word, p.status);
                 if (!ok) break;
-                if (lane == 0) {
+                if (elect_one()) {
                     const uint32_t own_bar = smem_u32(&full_bar[stage]);
                     const uint32_t bar = own_bar & kPeerBitMask;  // the leader's barrier counts both CTAs' bytes
                     const uint32_t sa = smem_u32(tiles + stage * C::STAGE_BYTES);
@@ -846,21 +867,86 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t idesc_hi_sf = p.idesc | (2u << 4) | (2u << 29);
         IssueCursor<C::STAGE_BYTES, C::NUM_STAGES, A_TILE_BYTES, A_TILE_BYTES + C::B_TILE_BYTES, C::SF_COLS_PER_STAGE> cur;
         cur.init(smem_u32(tiles), a_lbo, b_lbo, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]), tmem_base + C::SF_COL0);
+#ifdef ASCB200_PROBE
+        const long long tl0 = clock64();
+#endif
         for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters, ++acc_iter) {
             const int acc_stage = acc_iter & 1;
             const uint32_t acc_phase = (acc_iter >> 1) & 1u;
+#ifdef ASCB200_PROBE
+            const long long ta0 = clock64();
+#endif
             ok = mbar_wait(smem_u32(&acc_empty_bar[acc_stage]), acc_phase ^ 1u, abort_word, p.status);
             if (!ok) break;
             tc_fence_after();
+#ifdef ASCB200_PROBE
+            if (lane == 0 && cluster_id == 0) atomicAdd(&g_probe_times[4], static_cast<unsigned long long>(clock64() - ta0));
+#endif
             const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
             const uint32_t acc_full = smem_u32(&acc_full_bar[acc_stage]);
             const uint32_t sfb_off = static_cast<uint32_t>(((tile / num_m) * BLOCK_N) % 128) / 32;
             const int last = p.num_k_blocks - 1;
-            for (int kb = 0; kb <= last; ++kb) {
+            int kb = 0;
+            if constexpr (KIND == KIND_MXF4) {
+                // Every MMA waits until the scale copies queued before it have landed (a few hundred cycles),
+                // so the copies of two K blocks go out together and the wait is paid once per eight MMAs.
+                for (; kb < last; kb += 2) {
+                    auto nxt = cur;
+                    nxt.advance();
+#ifdef ASCB200_PROBE
+                    const long long t0 = clock64();
+#endif
+                    ok = mbar_wait(cur.full_bar, cur.phase, abort_word, p.status) && mbar_wait(nxt.full_bar, nxt.phase, abort_word, p.status);
+                    if (!ok) break;
+                    tc_fence_after();
+#ifdef ASCB200_PROBE
+                    const long long t1 = clock64();
+                    long long t2 = t1, t3 = t1;
+#endif
+                    if (elect_one()) {
+#ifdef ASCB200_PROBE
+                        if (!(p.probe & 32))
+#endif
+                        {
+                            issue_sf_copies<KIND, true, C::SF_B_BLOCKS>(cur);
+                            issue_sf_copies<KIND, true, C::SF_B_BLOCKS>(nxt);
+                        }
+#ifdef ASCB200_PROBE
+                        t2 = clock64();
+#endif
+#ifdef ASCB200_PROBE
+                        if (p.probe & 64) {
+                            commit_issue<true>(cur.empty_bar);
+                            commit_issue<true>(nxt.empty_bar);
+                        } else
+#endif
+                        {
+                            issue_mmas<KIND, true>(cur, d_tmem, hi_word, a_k16, b_k16, p.idesc, idesc_hi_sf, sfb_off, kb == 0);
+                            issue_mmas<KIND, true>(nxt, d_tmem, hi_word, a_k16, b_k16, p.idesc, idesc_hi_sf, sfb_off, false);
+                        }
+                        if (kb + 1 == last) tc_commit_pair(acc_full);
+#ifdef ASCB200_PROBE
+                        t3 = clock64();
+#endif
+                    }
+                    __syncwarp();
+#ifdef ASCB200_PROBE
+                    if (lane == 0 && cluster_id == 0) {
+                        atomicAdd(&g_probe_times[0], static_cast<unsigned long long>(t1 - t0));
+                        atomicAdd(&g_probe_times[1], static_cast<unsigned long long>(t2 - t1));
+                        atomicAdd(&g_probe_times[2], static_cast<unsigned long long>(t3 - t2));
+                        atomicAdd(&g_probe_times[3], 1ull);
+                    }
+#endif
+                    cur = nxt;
+                    cur.advance();
+                }
+            }
+            for (; ok && kb <= last; ++kb) {
                 ok = mbar_wait(cur.full_bar, cur.phase, abort_word, p.status);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) {
+                if (elect_one()) {
                     issue_k_block<KIND, true, C::SF_B_BLOCKS>(cur, d_tmem, hi_word, a_k16, b_k16, p.idesc, idesc_hi_sf, sfb_off, kb == 0);
                     if (kb == last) tc_commit_pair(acc_full);
                 }
@@ -868,6 +954,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 cur.advance();
             }
         }
+#ifdef ASCB200_PROBE
+        if (lane == 0 && cluster_id == 0) atomicAdd(&g_probe_times[5], static_cast<unsigned long long>(clock64() - tl0));
+#endif
     } else if (warp >= 4) {
         // ===== epilogue (both CTAs, each for its own 128 rows) =====
         const int quad = warp & 3;
@@ -908,6 +997,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tc_fence_after();
         tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
     }
+#ifdef ASCB200_PROBE
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        unsigned long long tg1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tg1));
+        atomicAdd(&g_probe_times[6], static_cast<unsigned long long>(clock64() - tk0));
+        atomicAdd(&g_probe_times[7], tg1 - tg0);
+    }
+#endif
 }
 
 // Re-tiles MX scale factors [rows, ks] (row-major bytes) into 512-byte chunks: chunk (rb, kc) holds
@@ -1349,3 +1446,15 @@ int ascb200_grouped_gemm(const ascb200_gemm_desc* desc, const int64_t* group_cou
 }
 
 }  // extern "C"
+
+#ifdef ASCB200_PROBE
+extern "C" __attribute__((visibility("default"))) int ascb200_probe_times(unsigned long long* out, int reset)
+{
+    if (out && cudaMemcpyFromSymbol(out, ascb200::g_probe_times, sizeof(ascb200::g_probe_times)) != cudaSuccess) return -5;
+    if (reset) {
+        unsigned long long z[8] = {};
+        if (cudaMemcpyToSymbol(ascb200::g_probe_times, z, sizeof(z)) != cudaSuccess) return -5;
+    }
+    return 0;
+}
+#endif

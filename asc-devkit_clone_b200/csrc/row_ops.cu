@@ -222,18 +222,18 @@ softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __res
         if constexpr (!PERSIST) {
             softmax_one_row<T, TPR, NCHUNK, QUANT>(raw, row, t, nchunks, dst, sum_out, max_out, q_out, q_scale, q_offset, q_offset_scalar, k,
                                                    stats_rep, red);
-            return;
-        }
-        while (true) {
-            const int next = row + stride;
-            uint4 ahead[NCHUNK];
-            if (next < m) softmax_load_row<T, TPR, NCHUNK>(src + static_cast<size_t>(next) * k, t, nchunks, ahead);
-            softmax_one_row<T, TPR, NCHUNK, QUANT>(raw, row, t, nchunks, dst, sum_out, max_out, q_out, q_scale, q_offset, q_offset_scalar, k,
-                                                   stats_rep, red);
-            if (next >= m) break;
+        } else {
+            while (true) {
+                const int next = row + stride;
+                uint4 ahead[NCHUNK];
+                if (next < m) softmax_load_row<T, TPR, NCHUNK>(src + static_cast<size_t>(next) * k, t, nchunks, ahead);
+                softmax_one_row<T, TPR, NCHUNK, QUANT>(raw, row, t, nchunks, dst, sum_out, max_out, q_out, q_scale, q_offset, q_offset_scalar,
+                                                       k, stats_rep, red);
+                if (next >= m) break;
 #pragma unroll
-            for (int i = 0; i < NCHUNK; ++i) raw[i] = ahead[i];
-            row = next;
+                for (int i = 0; i < NCHUNK; ++i) raw[i] = ahead[i];
+                row = next;
+            }
         }
     }
 }

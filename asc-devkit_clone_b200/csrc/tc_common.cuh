@@ -49,6 +49,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+// One lane of a converged warp (elect.sync).  Unlike a test of the lane index, the compiler knows
+// that the guarded code runs on a single thread and keeps its operands in uniform registers, which
+// the tcgen05 / TMA instructions take; this shortens the issue path of every such instruction.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred P1;\n"
+        "elect.sync _|P1, 0xFFFFFFFF;\n"
+        "selp.u32 %0, 1, 0, P1;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // Non-blocking probe of the barrier phase.  try_wait may put the warp to sleep for a hardware-chosen
 // interval when the phase is not complete yet; the wake-up costs hundreds of cycles, which the
 // two warps that drive the pipeline cannot afford on every K block, so they poll with test_wait.
