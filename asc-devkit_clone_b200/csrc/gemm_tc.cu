@@ -13,6 +13,7 @@
 // tile i overlaps the main loop of tile i+1.  Tiles are visited M-fastest so that concurrently
 // running CTAs share B columns in L2.  No load uses cluster multicast.
 #include <algorithm>
+#include <cstring>
 #include <mutex>
 
 #include "tc_common.cuh"
@@ -40,6 +41,7 @@ struct EpiParams {
     int mode;
     int relu, act;
     int vec_c, vec_c2;       // rows of c / c2 are 16-byte aligned at every 32-column boundary
+    int tma_c, tma_c2;       // c / c2 (1- or 2-byte elements) may be written with bulk tensor stores
     const void* bias;        // float (fp32 accumulators) or int32 (int32 accumulators)
     const float* tok;
     const float* ch;
@@ -73,7 +75,11 @@ struct Cfg {
     static constexpr int SF_B_BLOCKS = (BLOCK_N + 127) / 128;  // 128-row scale blocks that one B tile touches
     static constexpr int SF_BYTES = KIND == KIND_MXF4 ? (2 + 2 * SF_B_BLOCKS) * SF_CHUNK_BYTES : 0;
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + SF_BYTES;
-    static constexpr int NUM_STAGES = std::min(8, (220 * 1024) / STAGE_BYTES);
+    // output staging for bulk tensor stores: per epilogue warp 2 KB (2-byte chunk) + 1 KB (1-byte chunk)
+    static constexpr int EPI_BYTES_PER_WARP = (KIND == KIND_MXF4 && BLOCK_N == 256) ? 0 : 3072;
+    static constexpr int EPI_BYTES = NUM_EPI_WARPS * EPI_BYTES_PER_WARP;
+    static constexpr int FIXED_BYTES = 1024 /*alignment slack*/ + 256 /*barriers*/ + 2 * (MAX_GROUPS + 1) * static_cast<int>(sizeof(int)) + EPI_BYTES;
+    static constexpr int NUM_STAGES = std::min(8, (227 * 1024 - FIXED_BYTES) / STAGE_BYTES);
     static constexpr int ACC_STAGES = (KIND == KIND_MXF4 && BLOCK_N == 256) ? 1 : 2;  // 2 x 256 accumulator columns would leave no TMEM for scales
     static constexpr int ACC_COLS = ACC_STAGES * BLOCK_N;
     static constexpr int SF_COLS_PER_STAGE = 24;  // 8 for A + 16 for B
@@ -84,12 +90,27 @@ struct Cfg {
     // bytes of one K step of the instruction (32 in every kind) -> elements along K per tile row
     static constexpr int BLOCK_K = KIND == KIND_F16 ? 64 : KIND == KIND_I8 ? 128 : 256;
     static constexpr int UMMA_K = BLOCK_K / 4;
-    static constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ +
-                                      2 * (MAX_GROUPS + 1) * static_cast<int>(sizeof(int));
+    static constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + FIXED_BYTES;
 };
 
 struct TileInfo {
     int row0, row_end, n0, group;
+};
+
+// Tensor maps of the outputs (rank 2, box 32 x 32, swizzle = bytes of one box row).
+struct OutMaps {
+    CUtensorMap c, c2;
+};
+
+// Where one epilogue warp stages a 32 x 32 output chunk for a bulk tensor store.  A map pointer of
+// nullptr selects direct stores from registers (4-byte outputs, unaligned tensors, rows of a group
+// that end inside the warp's 32 rows).
+struct EpiStage {
+    const CUtensorMap* map_c;
+    const CUtensorMap* map_c2;
+    uint32_t smem_c, smem_c2;
+    int row_base;  // first output row of the warp
+    bool dual;     // both outputs staged: two bulk groups are in flight per chunk
 };
 
 // Grouped mode: prefix sums of rows and of tiles per group, built once per CTA by warp 0.
@@ -244,6 +265,45 @@ __device__ __forceinline__ void store_row32(void* base, long long ld, int vec, i
     }
 }
 
+// Same values as store_row32 for a 1- or 2-byte type, but through shared memory and one bulk tensor
+// store per warp: lane i writes row i of the 32 x 32 chunk (16-byte pieces XOR-swizzled like the tensor
+// map, so the writes do not collide on banks), lane 0 hands the chunk to the TMA unit, which writes
+// whole rows and clips at the edges of the matrix.  PENDING bulk groups of lane 0 may still be reading
+// other buffers; this buffer's previous group is older than those and has finished.
+template <int DT>
+__device__ __forceinline__ void stage_store32(const CUtensorMap* map, uint32_t smem, bool dual, int lane, int row_base, int col0,
+                                              const float (&f)[32], const int (&qi)[32])
+{
+    static_assert(DT == OUT_F16 || DT == OUT_BF16 || DT == OUT_S8, "staged stores carry 1- and 2-byte outputs");
+    if (lane == 0) {
+        if (dual) bulk_wait_group_read<1>();
+        else bulk_wait_group_read<0>();
+    }
+    __syncwarp();
+    if constexpr (DT == OUT_S8) {
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            w[j] = (qi[4 * j] & 0xFF) | ((qi[4 * j + 1] & 0xFF) << 8) | ((qi[4 * j + 2] & 0xFF) << 16) | (static_cast<uint32_t>(qi[4 * j + 3]) << 24);
+        const uint32_t row = smem + lane * 32, sw = (lane >> 2) & 1;  // 32-byte swizzle: piece ^= bit 2 of the row
+        st_shared_v4(row + ((0 ^ sw) << 4), w[0], w[1], w[2], w[3]);
+        st_shared_v4(row + ((1 ^ sw) << 4), w[4], w[5], w[6], w[7]);
+    } else {
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) w[j] = DT == OUT_F16 ? pack_f16x2_sat(f[2 * j], f[2 * j + 1]) : pack_bf16x2(f[2 * j], f[2 * j + 1]);
+        const uint32_t row = smem + lane * 64, sw = (lane >> 1) & 3;  // 64-byte swizzle: piece ^= bits 1-2 of the row
+#pragma unroll
+        for (int j = 0; j < 4; ++j) st_shared_v4(row + ((j ^ sw) << 4), w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        tma_store_2d(map, smem, col0, row_base);
+        bulk_commit_group();
+    }
+}
+
 // 32 per-channel fp32 parameters starting at p[0]: eight 128-bit loads when aligned.
 __device__ __forceinline__ void load_params32(const float* p, int ncols, float (&out)[32])
 {
@@ -266,8 +326,8 @@ __device__ __forceinline__ void load_params32(const float* p, int ncols, float (
 // MODE / DT are compile-time so that each combination is a short straight-line sequence.
 // chan0: index of column col0 in bias / quant; ch_off: index in the per-channel scale array.
 template <bool ACC_INT, int MODE, int DT>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const EpiParams& e, int row, bool row_ok, int col0, int ncols, size_t chan0,
-                                               size_t ch_off, float tok)
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const EpiParams& e, const EpiStage& st, int row, bool row_ok, int col0, int ncols,
+                                               size_t chan0, size_t ch_off, float tok)
 {
     // Runs on all 32 lanes (the quantising path exchanges per-column parameters with shuffles); lanes whose
     // row lies outside the matrix compute on whatever their TMEM lane holds and store nothing.
@@ -295,7 +355,11 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = __fadd_rn(f[j], b[j]);
         }
-        if (e.c2 && row_ok) {
+        if (st.map_c2) {
+            const int lane = threadIdx.x & 31;
+            if (e.c2_dtype == OUT_BF16) stage_store32<OUT_BF16>(st.map_c2, st.smem_c2, st.dual, lane, st.row_base, col0, f, qi);
+            else stage_store32<OUT_F16>(st.map_c2, st.smem_c2, st.dual, lane, st.row_base, col0, f, qi);
+        } else if (e.c2 && row_ok) {
             if (e.c2_dtype == OUT_BF16) store_row32<OUT_BF16>(e.c2, e.ldc2, e.vec_c2, row, col0, ncols, f, qi);
             else if (e.c2_dtype == OUT_F16) store_row32<OUT_F16>(e.c2, e.ldc2, e.vec_c2, row, col0, ncols, f, qi);
             else store_row32<OUT_F32>(e.c2, e.ldc2, e.vec_c2, row, col0, ncols, f, qi);
@@ -372,16 +436,36 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
         if (acc != 12345.678f) return;
     }
 #endif
+    if constexpr (DT == OUT_F16 || DT == OUT_BF16 || DT == OUT_S8) {
+        if (st.map_c) {
+            stage_store32<DT>(st.map_c, st.smem_c, st.dual, threadIdx.x & 31, st.row_base, col0, f, qi);
+            return;
+        }
+    }
     if (row_ok) store_row32<DT>(e.c, e.ldc, e.vec_c, row, col0, ncols, f, qi);
 }
 
 // Drains this warp's share of one accumulator tile: TMEM lanes of `quad`, chunks [chunk0, chunk1).
 template <bool ACC_INT, int MODE, int DT, int BLOCK_N>
-__device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInfo& t, uint32_t t_addr, int quad, int lane, int chunk0, int chunk1)
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInfo& t, const OutMaps& outs, uint32_t stage_smem, int stage_bytes,
+                                              uint32_t t_addr, int quad, int lane, int chunk0, int chunk1)
 {
     const int row = t.row0 + quad * 32 + lane;
     const bool row_ok = row < t.row_end;
     const float tok = (MODE == ASCB200_EPI_DEQUANT_TOKEN_CHANNEL && row_ok && p.epi.tok) ? __ldg(p.epi.tok + row) : 1.0f;
+    EpiStage st;
+    st.row_base = t.row0 + quad * 32;
+    // bulk stores clip at the matrix edge only: a group that ends inside this warp's rows is stored from registers
+    const bool rows_mine = p.groups == 0 || st.row_base + 32 <= t.row_end;
+    constexpr int C_BYTES = DT == OUT_S8 ? 1024 : 2048;
+    const bool stage_c = (DT == OUT_F16 || DT == OUT_BF16 || DT == OUT_S8) && p.epi.tma_c && rows_mine && C_BYTES <= stage_bytes;
+    const int c_used = stage_c ? C_BYTES : 0;
+    const bool stage_c2 = !ACC_INT && p.epi.c2 && p.epi.tma_c2 && rows_mine && c_used + 2048 <= stage_bytes;
+    st.map_c = stage_c ? &outs.c : nullptr;
+    st.map_c2 = stage_c2 ? &outs.c2 : nullptr;
+    st.smem_c = stage_smem;
+    st.smem_c2 = stage_smem + c_used;
+    st.dual = stage_c && stage_c2;
 #pragma unroll 1
     for (int c = chunk0; c < chunk1; ++c) {
         const int col0 = t.n0 + c * 32;
@@ -392,17 +476,18 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
 #ifdef ASCB200_PROBE
         if (p.probe & 4) continue;
 #endif
-        epilogue_chunk<ACC_INT, MODE, DT>(r, p.epi, row, row_ok, col0, min(32, p.n - col0), static_cast<size_t>(col0),
+        epilogue_chunk<ACC_INT, MODE, DT>(r, p.epi, st, row, row_ok, col0, min(32, p.n - col0), static_cast<size_t>(col0),
                                           static_cast<size_t>(t.group) * p.n + col0, tok);
     }
 }
 
 template <bool ACC_INT, int BLOCK_N>
-__device__ __forceinline__ void epilogue_dispatch(const GemmParams& p, const TileInfo& t, uint32_t t_addr, int quad, int lane, int chunk0, int chunk1)
+__device__ __forceinline__ void epilogue_dispatch(const GemmParams& p, const TileInfo& t, const OutMaps& outs, uint32_t stage_smem, int stage_bytes,
+                                                  uint32_t t_addr, int quad, int lane, int chunk0, int chunk1)
 {
 #define ASCB200_EPI_CASE(MODE, DT)                                                                          \
     if (p.epi.mode == MODE && p.epi.c_dtype == DT) {                                                          \
-        epilogue_tile<ACC_INT, MODE, DT, BLOCK_N>(p, t, t_addr, quad, lane, chunk0, chunk1);                  \
+        epilogue_tile<ACC_INT, MODE, DT, BLOCK_N>(p, t, outs, stage_smem, stage_bytes, t_addr, quad, lane, chunk0, chunk1); \
         return;                                                                                               \
     }
     if constexpr (ACC_INT) {
@@ -428,11 +513,11 @@ __device__ __forceinline__ void epilogue_dispatch(const GemmParams& p, const Til
 // ---- MMA issue (one thread) -------------------------------------------------------------------
 // State of the issuing thread for the shared-memory ring: low descriptor words of the current
 // stage's A / B / scale tiles and the addresses of its barriers, advanced by one add per stage.
-template <int STAGE_BYTES, int NUM_STAGES, int B_OFFSET, int SF_OFFSET, int SF_COLS_PER_STAGE>
+template <int STAGE_BYTES, int NUM_STAGES, int B_OFFSET, int SF_OFFSET, int SF_COLS_PER_STAGE, int SF_SLOTS = NUM_STAGES>
 struct IssueCursor {
     uint32_t a_lo, b_lo, sf_lo, full_bar, empty_bar, sf_tmem;
     uint32_t a_lo0, b_lo0, sf_lo0, full_bar0, empty_bar0, sf_tmem0;
-    int stage;
+    int stage, sf_slot;  // the TMEM columns of the scales rotate on their own (fewer slots than shared-memory stages fit TMEM)
     uint32_t phase;
     __device__ __forceinline__ void init(uint32_t tiles_addr, uint32_t a_lbo_enc, uint32_t b_lbo_enc, uint32_t full0, uint32_t empty0, uint32_t sf_tmem_base)
     {
@@ -443,6 +528,8 @@ struct IssueCursor {
         empty_bar0 = empty0;
         sf_tmem0 = sf_tmem_base;
         rewind();
+        sf_tmem = sf_tmem0;
+        sf_slot = 0;
         phase = 0;
     }
     __device__ __forceinline__ void rewind()
@@ -452,7 +539,6 @@ struct IssueCursor {
         sf_lo = sf_lo0;
         full_bar = full_bar0;
         empty_bar = empty_bar0;
-        sf_tmem = sf_tmem0;
         stage = 0;
     }
     __device__ __forceinline__ void advance()
@@ -466,6 +552,11 @@ struct IssueCursor {
             sf_lo += STAGE_BYTES >> 4;
             full_bar += 8;
             empty_bar += 8;
+        }
+        if (++sf_slot == SF_SLOTS) {
+            sf_slot = 0;
+            sf_tmem = sf_tmem0;
+        } else {
             sf_tmem += SF_COLS_PER_STAGE;
         }
     }
@@ -475,18 +566,9 @@ struct IssueCursor {
 template <int KIND, bool PAIR, int SF_B_BLOCKS, class Cursor>
 __device__ __forceinline__ void issue_sf_copies(const Cursor& c)
 {
-    if constexpr (KIND == KIND_MXF4 && PAIR) {
-        // Scales arrive replicated (one 512-byte copy per 32-lane quadrant): per 128-row block and K block
-        // 4 KB = [kc0: 4 copies][kc1: 4 copies].  A 128x256b copy reads rows of two 16-byte halves that
-        // lie `leading offset` apart: A pairs (kc0, kc1) of its block (2048 apart) into TMEM columns 0-7;
-        // B pairs (block 0, block 1) of one kc (4096 apart) into columns 8-15 (kc0) and 16-23 (kc1).
-        static_assert(SF_B_BLOCKS == 2, "pair MXFP4 tile spans two 128-row scale blocks");
-        constexpr uint32_t sf_hi = (128u >> 4) | (1u << 14);
-        const uint32_t addr16 = c.sf_lo & 0xFFFFu;
-        sf_copy_128x256b_pair(c.sf_tmem + 0, ((2048u >> 4) << 16) | addr16, sf_hi);
-        sf_copy_128x256b_pair(c.sf_tmem + 8, ((4096u >> 4) << 16) | (addr16 + (4096u >> 4)), sf_hi);
-        sf_copy_128x256b_pair(c.sf_tmem + 16, ((4096u >> 4) << 16) | (addr16 + (4096u >> 4) + (2048u >> 4)), sf_hi);
-    } else if constexpr (KIND == KIND_MXF4) {
+    if constexpr (KIND == KIND_MXF4) {
+        // Each copy broadcasts one 512-byte chunk (128 rows x 4 K-blocks of 32) to the four 32-lane quadrants of
+        // four TMEM columns; in a pair both CTAs copy from their own shared memory into their own TMEM.
         constexpr uint32_t sf_hi = (128u >> 4) | (1u << 14);  // stride 128 bytes between 8-row groups, descriptor version 1
         // chunk order in shared memory: A kc0, A kc1, then per 128-row block of B: kc0, kc1 (512 bytes each)
         sf_copy_issue<PAIR>(c.sf_tmem + 0, c.sf_lo, sf_hi);
@@ -532,21 +614,23 @@ __device__ __forceinline__ void issue_k_block(const Cursor& c, uint32_t d_tmem, 
 // ---- the kernel --------------------------------------------------------------------------------
 template <int KIND, int BLOCK_N>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ OutMaps outs,
+               const GemmParams p)
 {
     using C = Cfg<KIND, BLOCK_N>;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzled tiles need 1024-byte aligned bases
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* tiles = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::NUM_STAGES * C::STAGE_BYTES);
+    uint8_t* epi_stage = smem + C::NUM_STAGES * C::STAGE_BYTES;  // [NUM_EPI_WARPS][EPI_BYTES_PER_WARP], 1024-byte aligned
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + C::EPI_BYTES);
     uint64_t* full_bar = bars;                         // [NUM_STAGES]
     uint64_t* empty_bar = bars + C::NUM_STAGES;        // [NUM_STAGES]
     uint64_t* acc_full_bar = bars + 2 * C::NUM_STAGES; // [2]
     uint64_t* acc_empty_bar = acc_full_bar + 2;        // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
-    int* row_start = reinterpret_cast<int*>(smem + C::NUM_STAGES * C::STAGE_BYTES + 256);
+    int* row_start = reinterpret_cast<int*>(epi_stage + C::EPI_BYTES + 256);
     int* tile_start = row_start + (MAX_GROUPS + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -688,11 +772,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc_stage * BLOCK_N;
-            epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, t_addr, quad, lane, chunk0, chunk1);
+            epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, outs, smem_u32(epi_stage) + (warp - 4) * C::EPI_BYTES_PER_WARP, C::EPI_BYTES_PER_WARP, t_addr,
+                                                        quad, lane, chunk0, chunk1);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[acc_stage]));
         }
+        if (lane == 0) bulk_wait_group_read<0>();  // staged chunks have left shared memory before the CTA may exit
     }
 
     // ===== teardown =====
@@ -725,25 +811,29 @@ template <int KIND, int BLOCK_N>
 struct Cfg2 {
     static constexpr int B_TILE_BYTES = (BLOCK_N / 2) * ROW_BYTES;
     static constexpr int SF_B_BLOCKS = (BLOCK_N + 127) / 128;   // every CTA needs the scales of all BLOCK_N columns
-    static constexpr int SF_REP_BYTES = 8 * SF_CHUNK_BYTES;   // scales of one 128-row block and K block, one copy per TMEM quadrant
-    static constexpr int SF_BYTES = KIND == KIND_MXF4 ? (1 + SF_B_BLOCKS) * SF_REP_BYTES : 0;
+    static constexpr int SF_BLOCK_BYTES = 2 * SF_CHUNK_BYTES;   // scales of one 128-row block and K block (two chunks)
+    static constexpr int SF_BYTES = KIND == KIND_MXF4 ? (1 + SF_B_BLOCKS) * SF_BLOCK_BYTES : 0;
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + SF_BYTES;
     static constexpr int ACC_STAGES = 2;
     static constexpr int SF_COLS_PER_STAGE = 24;
     static constexpr int SF_COL0 = ACC_STAGES * BLOCK_N;
     static constexpr int MAX_SF_STAGES = KIND == KIND_MXF4 ? (512 - SF_COL0) / SF_COLS_PER_STAGE : 8;
-    static constexpr int NUM_STAGES = std::min(std::min(8, MAX_SF_STAGES), (216 * 1024) / STAGE_BYTES);
+    static constexpr int EPI_BYTES_PER_WARP = KIND == KIND_MXF4 ? 3072 : 4096;  // staged output chunks (see Cfg)
+    static constexpr int EPI_BYTES = NUM_EPI_WARPS * EPI_BYTES_PER_WARP;
+    static constexpr int NUM_STAGES = std::min(8, (227 * 1024 - 1024 - 256 - EPI_BYTES) / STAGE_BYTES);
+    static constexpr int SF_SLOTS = std::min(NUM_STAGES, MAX_SF_STAGES);  // scale-factor slots in TMEM
     static constexpr int TMEM_COLS = 512;
-    static_assert(ACC_STAGES * BLOCK_N + (KIND == KIND_MXF4 ? NUM_STAGES * SF_COLS_PER_STAGE : 0) <= 512, "TMEM budget");
+    static_assert(ACC_STAGES * BLOCK_N + (KIND == KIND_MXF4 ? SF_SLOTS * SF_COLS_PER_STAGE : 0) <= 512, "TMEM budget");
     static constexpr int BLOCK_K = KIND == KIND_F16 ? 64 : KIND == KIND_I8 ? 128 : 256;
     static constexpr int UMMA_K = BLOCK_K / 4;
-    static constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + 1024 + 256;
+    static constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
 };
 
 template <int KIND, int BLOCK_N>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const GemmParams p)
+                    const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const __grid_constant__ OutMaps outs,
+                    const GemmParams p)
 {
     using C = Cfg2<KIND, BLOCK_N>;
     constexpr int PAIR_M = 2 * BLOCK_M;
@@ -751,7 +841,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // both CTAs must use identical offsets: the dynamic shared memory window starts at the same offset in each
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* tiles = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::NUM_STAGES * C::STAGE_BYTES);
+    uint8_t* epi_stage = smem + C::NUM_STAGES * C::STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + C::EPI_BYTES);
     uint64_t* full_bar = bars;
     uint64_t* empty_bar = bars + C::NUM_STAGES;
     uint64_t* acc_full_bar = bars + 2 * C::NUM_STAGES;
@@ -819,14 +910,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     constexpr int MN_PER_BOX = KIND == KIND_F16 ? 64 : 128;
                     constexpr int BOX_BYTES = C::BLOCK_K * ROW_BYTES;
                     if constexpr (KIND == KIND_MXF4) {
-                        // replicated re-tiled scales as a [row, 128 x u32] tensor
+                        // re-tiled scales as a [chunk, 128 x u32] tensor: the two chunks of this K block per 128-row block
                         const uint32_t ssf = sb + C::B_TILE_BYTES;
                         const int tile_n0 = n0 - static_cast<int>(rank) * (BLOCK_N / 2);
-                        // 8 rows of 512 bytes per (128-row block, K block): see retile_scales_rep4_kernel
-                        tma_load_2d_pair(ssf, &tmap_sfa, 0, ((row0 / 128) * p.num_k_blocks + kb) * 8, bar);
+                        tma_load_2d_pair(ssf, &tmap_sfa, 0, (row0 / 128) * p.sf_kc + 2 * kb, bar);
 #pragma unroll
                         for (int rb = 0; rb < C::SF_B_BLOCKS; ++rb)
-                            tma_load_2d_pair(ssf + (1 + rb) * C::SF_REP_BYTES, &tmap_sfb, 0, ((tile_n0 / 128 + rb) * p.num_k_blocks + kb) * 8, bar);
+                            tma_load_2d_pair(ssf + (1 + rb) * C::SF_BLOCK_BYTES, &tmap_sfb, 0, (tile_n0 / 128 + rb) * p.sf_kc + 2 * kb, bar);
                     }
                     if (!p.a_mn) {
                         tma_load_3d_pair(sa, &tmap_a, kx, row0, 0, bar);
@@ -865,7 +955,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t a_lbo = p.a_mn ? (C::BLOCK_K * ROW_BYTES) >> 4 : 1u, b_lbo = p.b_mn ? (C::BLOCK_K * ROW_BYTES) >> 4 : 1u;
         const uint32_t a_k16 = (p.a_mn ? C::UMMA_K * ROW_BYTES : 32) >> 4, b_k16 = (p.b_mn ? C::UMMA_K * ROW_BYTES : 32) >> 4;
         const uint32_t idesc_hi_sf = p.idesc | (2u << 4) | (2u << 29);
-        IssueCursor<C::STAGE_BYTES, C::NUM_STAGES, A_TILE_BYTES, A_TILE_BYTES + C::B_TILE_BYTES, C::SF_COLS_PER_STAGE> cur;
+        IssueCursor<C::STAGE_BYTES, C::NUM_STAGES, A_TILE_BYTES, A_TILE_BYTES + C::B_TILE_BYTES, C::SF_COLS_PER_STAGE, C::SF_SLOTS> cur;
         cur.init(smem_u32(tiles), a_lbo, b_lbo, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]), tmem_base + C::SF_COL0);
 #ifdef ASCB200_PROBE
         const long long tl0 = clock64();
@@ -977,11 +1067,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             t.row_end = p.m;
             t.n0 = (tile / num_m) * BLOCK_N;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc_stage * BLOCK_N;
-            epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, t_addr, quad, lane, chunk0, chunk1);
+            epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, outs, smem_u32(epi_stage) + (warp - 4) * C::EPI_BYTES_PER_WARP, C::EPI_BYTES_PER_WARP, t_addr,
+                                                        quad, lane, chunk0, chunk1);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(smem_u32(&acc_empty_bar[acc_stage]) & kPeerBitMask);
         }
+        if (lane == 0) bulk_wait_group_read<0>();
     }
 
     // ===== teardown =====
@@ -1010,10 +1102,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // Re-tiles MX scale factors [rows, ks] (row-major bytes) into 512-byte chunks: chunk (rb, kc) holds
 // the scales of rows rb*128 .. +127 and K-blocks kc*4 .. +3 at byte (r%32)*16 + (r/32)*4 + (ks%4),
 // the order tcgen05.cp (32x128b, warpx4) expects.  Missing rows / K-blocks are filled with 127 (1.0).
-__global__ void retile_scales_kernel(const uint8_t* __restrict__ src, uint32_t* __restrict__ dst, int rows, int ks, int row_blocks, int kc_count)
+// One launch re-tiles both operands' scales: words [0, words_a) belong to A, the rest to B.
+__global__ void retile_scales_kernel(const uint8_t* __restrict__ src_a, uint32_t* __restrict__ dst_a, int rows_a, size_t words_a,
+                                     const uint8_t* __restrict__ src_b, uint32_t* __restrict__ dst_b, int rows_b, size_t words_b, int ks, int kc_count)
 {
-    const size_t total = static_cast<size_t>(row_blocks) * kc_count * 128;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < words_a + words_b; idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const bool is_a = idx < words_a;
+        const size_t i = is_a ? idx : idx - words_a;
+        const uint8_t* src = is_a ? src_a : src_b;
+        const int rows = is_a ? rows_a : rows_b;
         const int pos = static_cast<int>(i % 128);
         const size_t chunk = i / 128;
         const int kc = static_cast<int>(chunk % kc_count);
@@ -1026,33 +1123,7 @@ __global__ void retile_scales_kernel(const uint8_t* __restrict__ src, uint32_t* 
             const uint32_t v = (r < rows && k < ks) ? src[static_cast<size_t>(r) * ks + k] : 127u;
             w |= v << (8 * b);
         }
-        dst[i] = w;
-    }
-}
-
-// Pair-kernel variant: per 128-row block rb and K block kb (256 elements = 8 scales per row) it writes
-// 4 KB = [kc0: 4 identical 512-byte chunks][kc1: 4 identical chunks], chunk format as above, so that one
-// 128-lane tcgen05.cp can fill all four TMEM quadrants.
-__global__ void retile_scales_rep4_kernel(const uint8_t* __restrict__ src, uint32_t* __restrict__ dst, int rows, int ks, int row_blocks, int kb_count)
-{
-    const size_t total = static_cast<size_t>(row_blocks) * kb_count * 2 * 128;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const int pos = static_cast<int>(i % 128);
-        const int kc = static_cast<int>((i / 128) % 2);
-        const size_t blk = i / 256;                       // rb * kb_count + kb
-        const int kb = static_cast<int>(blk % kb_count);
-        const int rb = static_cast<int>(blk / kb_count);
-        const int r = rb * 128 + (pos & 3) * 32 + (pos >> 2);
-        uint32_t w = 0;
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const int kidx = (kb * 2 + kc) * 4 + b;
-            const uint32_t v = (r < rows && kidx < ks) ? src[static_cast<size_t>(r) * ks + kidx] : 127u;
-            w |= v << (8 * b);
-        }
-        uint32_t* out = dst + (blk * 8 + static_cast<size_t>(kc) * 4) * 128 + pos;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) out[q * 128] = w;
+        (is_a ? dst_a : dst_b)[i] = w;
     }
 }
 
@@ -1106,8 +1177,24 @@ int make_sf_map(CUtensorMap* map, const void* base, uint64_t chunks, uint32_t bo
     return r == CUDA_SUCCESS ? ASCB200_OK : ASCB200_ECUDA;
 }
 
+// rank-2 map over an output [rows][cols] of 1- or 2-byte elements, box 32 x 32, swizzle = bytes of one box row.
+// Returns false when the tensor cannot be described (alignment): the kernel then stores from registers.
+bool make_out_map(CUtensorMap* map, int esz, const void* base, uint64_t cols, uint64_t rows, uint64_t ld_elems)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || (esz != 1 && esz != 2) || !aligned_to(base, 16) || (ld_elems * esz) % 16 != 0 || cols == 0 || rows == 0) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld_elems * esz};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, esz == 1 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 template <int KIND, int BLOCK_N>
-int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream)
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& outs, const GemmParams& p, int grid, cudaStream_t stream)
 {
     using C = Cfg<KIND, BLOCK_N>;
     static bool configured[16] = {};
@@ -1117,14 +1204,14 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
         ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured[dev & 15] = true;
     }
-    gemm_tc_kernel<KIND, BLOCK_N><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
+    gemm_tc_kernel<KIND, BLOCK_N><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, outs, p);
     ASCB200_CUDA(cudaGetLastError());
     return ASCB200_OK;
 }
 
 template <int KIND, int BLOCK_N>
-int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsfa, const CUtensorMap& tsfb, const GemmParams& p, int clusters,
-                     cudaStream_t stream)
+int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsfa, const CUtensorMap& tsfb, const OutMaps& outs,
+                     const GemmParams& p, int clusters, cudaStream_t stream)
 {
     using C = Cfg2<KIND, BLOCK_N>;
     static bool configured[16] = {};
@@ -1134,7 +1221,7 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
         ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured[dev & 15] = true;
     }
-    gemm_tc_pair_kernel<KIND, BLOCK_N><<<2 * clusters, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, tsfa, tsfb, p);
+    gemm_tc_pair_kernel<KIND, BLOCK_N><<<2 * clusters, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, tsfa, tsfb, outs, p);
     ASCB200_CUDA(cudaGetLastError());
     return ASCB200_OK;
 }
@@ -1207,6 +1294,12 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         e.vec_c2 = aligned_to(e.c2, 16) && (e.ldc2 * out_bytes(e.c2_dtype)) % 16 == 0;
     }
     e.vec_c = aligned_to(e.c, 16) && (e.ldc * out_bytes(e.c_dtype)) % 16 == 0;
+    // 1- and 2-byte outputs leave through shared memory and bulk tensor stores when their layout allows a tensor map
+    OutMaps outs;
+    std::memset(&outs, 0, sizeof(outs));
+    const bool no_tma_store = getenv("ASCB200_NO_TMA_STORE") && getenv("ASCB200_NO_TMA_STORE")[0] == '1';
+    e.tma_c = !no_tma_store && make_out_map(&outs.c, out_bytes(e.c_dtype), e.c, d->n, d->m, e.ldc);
+    e.tma_c2 = !no_tma_store && e.c2 && make_out_map(&outs.c2, out_bytes(e.c2_dtype), e.c2, d->n, d->m, e.ldc2);
 
     // ---- operands ----
     const int bits = elem_bits(kind);
@@ -1292,8 +1385,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         const int ks = k / 32;
         const int kc = 2 * p.num_k_blocks;
         const int rba = (m + 127) / 128, rbb = (n + 127) / 128 + 2;  // B tiles may read up to two blocks past the last row
-        const size_t rep = use_pair ? 4 : 1;  // the pair kernel reads one copy per TMEM quadrant
-        const size_t bytes_a = static_cast<size_t>(rba) * kc * SF_CHUNK_BYTES * rep, bytes_b = static_cast<size_t>(rbb) * kc * SF_CHUNK_BYTES * rep;
+        const size_t bytes_a = static_cast<size_t>(rba) * kc * SF_CHUNK_BYTES, bytes_b = static_cast<size_t>(rbb) * kc * SF_CHUNK_BYTES;
         uint8_t* sfa;
         if (fixed) {
             if (bytes_a + bytes_b > fixed->scale_scratch_bytes) return ASCB200_ETOOBIG;
@@ -1304,15 +1396,9 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
             sfa = static_cast<uint8_t*>(st->scratch_dev);
         }
         uint8_t* sfb = sfa + bytes_a;
-        const int ga = static_cast<int>(std::min<size_t>((bytes_a / 4 + 255) / 256, 4096));
-        const int gb = static_cast<int>(std::min<size_t>((bytes_b / 4 + 255) / 256, 4096));
-        if (use_pair) {
-            retile_scales_rep4_kernel<<<ga, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_a_dev), reinterpret_cast<uint32_t*>(sfa), m, ks, rba, p.num_k_blocks);
-            retile_scales_rep4_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_b_dev), reinterpret_cast<uint32_t*>(sfb), n, ks, rbb, p.num_k_blocks);
-        } else {
-            retile_scales_kernel<<<ga, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_a_dev), reinterpret_cast<uint32_t*>(sfa), m, ks, rba, kc);
-            retile_scales_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_b_dev), reinterpret_cast<uint32_t*>(sfb), n, ks, rbb, kc);
-        }
+        const int grid_rt = static_cast<int>(std::min<size_t>(((bytes_a + bytes_b) / 4 + 255) / 256, 4096));
+        retile_scales_kernel<<<grid_rt, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_a_dev), reinterpret_cast<uint32_t*>(sfa), m, bytes_a / 4,
+                                                          static_cast<const uint8_t*>(d->scale_b_dev), reinterpret_cast<uint32_t*>(sfb), n, bytes_b / 4, ks, kc);
         ASCB200_CUDA(cudaGetLastError());
         p.sfa = sfa;
         p.sfb = sfb;
@@ -1329,39 +1415,39 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         if (kind == ASCB200_KIND_MXFP4) {
             // the re-tiled scales as rank-2 tensors [chunk][128 x u32] for tile loads
             CUtensorMap tsfa, tsfb;
-            rc = make_sf_map(&tsfa, p.sfa, static_cast<uint64_t>((m + 127) / 128) * p.num_k_blocks * 8, 8);
-            if (rc == ASCB200_OK) rc = make_sf_map(&tsfb, p.sfb, static_cast<uint64_t>((n + 127) / 128 + 2) * p.num_k_blocks * 8, 8);
+            rc = make_sf_map(&tsfa, p.sfa, static_cast<uint64_t>((m + 127) / 128) * p.sf_kc, 2);
+            if (rc == ASCB200_OK) rc = make_sf_map(&tsfb, p.sfb, static_cast<uint64_t>((n + 127) / 128 + 2) * p.sf_kc, 2);
             if (rc != ASCB200_OK) return rc;
             p.idesc = make_idesc_mxf4(2 * BLOCK_M, 192);
-            return launch_gemm_pair<KIND_MXF4, 192>(ta, tb, tsfa, tsfb, p, clusters, stream);
+            return launch_gemm_pair<KIND_MXF4, 192>(ta, tb, tsfa, tsfb, outs, p, clusters, stream);
         }
         if (kind == ASCB200_KIND_S8) {
             p.idesc = make_idesc(2, 1, 1, a_mn, b_mn, 2 * BLOCK_M, 256);
-            return launch_gemm_pair<KIND_I8, 256>(ta, tb, ta, tb, p, clusters, stream);
+            return launch_gemm_pair<KIND_I8, 256>(ta, tb, ta, tb, outs, p, clusters, stream);
         }
         const uint32_t fmt = kind == ASCB200_KIND_BF16 ? 1u : 0u;
         p.idesc = make_idesc(1, fmt, fmt, a_mn, b_mn, 2 * BLOCK_M, 256);
-        return launch_gemm_pair<KIND_F16, 256>(ta, tb, ta, tb, p, clusters, stream);
+        return launch_gemm_pair<KIND_F16, 256>(ta, tb, ta, tb, outs, p, clusters, stream);
     }
     switch (kind) {
         case ASCB200_KIND_F16:
         case ASCB200_KIND_BF16: {
             const uint32_t fmt = kind == ASCB200_KIND_BF16 ? 1u : 0u;
             p.idesc = make_idesc(1, fmt, fmt, a_mn, b_mn, BLOCK_M, block_n);
-            if (block_n == 256) return launch_gemm<KIND_F16, 256>(ta, tb, p, grid, stream);
-            if (block_n == 128) return launch_gemm<KIND_F16, 128>(ta, tb, p, grid, stream);
-            return launch_gemm<KIND_F16, 64>(ta, tb, p, grid, stream);
+            if (block_n == 256) return launch_gemm<KIND_F16, 256>(ta, tb, outs, p, grid, stream);
+            if (block_n == 128) return launch_gemm<KIND_F16, 128>(ta, tb, outs, p, grid, stream);
+            return launch_gemm<KIND_F16, 64>(ta, tb, outs, p, grid, stream);
         }
         case ASCB200_KIND_S8:
             p.idesc = make_idesc(2, 1, 1, a_mn, b_mn, BLOCK_M, block_n);
-            if (block_n == 256) return launch_gemm<KIND_I8, 256>(ta, tb, p, grid, stream);
-            if (block_n == 128) return launch_gemm<KIND_I8, 128>(ta, tb, p, grid, stream);
-            return launch_gemm<KIND_I8, 64>(ta, tb, p, grid, stream);
+            if (block_n == 256) return launch_gemm<KIND_I8, 256>(ta, tb, outs, p, grid, stream);
+            if (block_n == 128) return launch_gemm<KIND_I8, 128>(ta, tb, outs, p, grid, stream);
+            return launch_gemm<KIND_I8, 64>(ta, tb, outs, p, grid, stream);
         default:
             p.idesc = make_idesc_mxf4(BLOCK_M, block_n);
-            if (block_n == 256) return launch_gemm<KIND_MXF4, 256>(ta, tb, p, grid, stream);
-            if (block_n == 192) return launch_gemm<KIND_MXF4, 192>(ta, tb, p, grid, stream);
-            return launch_gemm<KIND_MXF4, 128>(ta, tb, p, grid, stream);
+            if (block_n == 256) return launch_gemm<KIND_MXF4, 256>(ta, tb, outs, p, grid, stream);
+            if (block_n == 192) return launch_gemm<KIND_MXF4, 192>(ta, tb, outs, p, grid, stream);
+            return launch_gemm<KIND_MXF4, 128>(ta, tb, outs, p, grid, stream);
     }
 }
 

@@ -49,6 +49,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+// ---- bulk tensor stores (shared -> global) -----------------------------------------------------
+// x * element size must be a multiple of 16 bytes; coordinates are never negative here.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 :: "l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns once all but the newest N bulk groups of this thread have finished reading shared memory.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(N) : "memory"); }
+// Makes this thread's shared-memory writes visible to the asynchronous (TMA) proxy.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" :: "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // One lane of a converged warp (elect.sync).  Unlike a test of the lane index, the compiler knows
 // that the guarded code runs on a single thread and keeps its operands in uniform registers, which
 // the tcgen05 / TMA instructions take; this shortens the issue path of every such instruction.
@@ -355,11 +373,6 @@ __device__ __forceinline__ void sf_copy_issue(uint32_t taddr, uint32_t s_lo, uin
         asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n\t}" ::"r"(taddr), "r"(s_lo), "r"(s_hi) : "memory");
     else
         asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n\t}" ::"r"(taddr), "r"(s_lo), "r"(s_hi) : "memory");
-}
-// 128 lanes x 32 bytes, no broadcast: the source already holds one copy per 32-lane quadrant.
-__device__ __forceinline__ void sf_copy_128x256b_pair(uint32_t taddr, uint32_t s_lo, uint32_t s_hi)
-{
-    asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::2.128x256b [%0], d;\n\t}" ::"r"(taddr), "r"(s_lo), "r"(s_hi) : "memory");
 }
 template <bool PAIR>
 __device__ __forceinline__ void commit_issue(uint32_t bar)
