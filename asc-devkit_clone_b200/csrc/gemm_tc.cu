@@ -1102,28 +1102,38 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // Re-tiles MX scale factors [rows, ks] (row-major bytes) into 512-byte chunks: chunk (rb, kc) holds
 // the scales of rows rb*128 .. +127 and K-blocks kc*4 .. +3 at byte (r%32)*16 + (r/32)*4 + (ks%4),
 // the order tcgen05.cp (32x128b, warpx4) expects.  Missing rows / K-blocks are filled with 127 (1.0).
-// One launch re-tiles both operands' scales: words [0, words_a) belong to A, the rest to B.
-__global__ void retile_scales_kernel(const uint8_t* __restrict__ src_a, uint32_t* __restrict__ dst_a, int rows_a, size_t words_a,
-                                     const uint8_t* __restrict__ src_b, uint32_t* __restrict__ dst_b, int rows_b, size_t words_b, int ks, int kc_count)
+// One launch covers both operands: blocks [0, rb_a * kc_tiles) re-tile A, the rest B.  A block moves
+// 128 rows x 32 chunks through shared memory so that rows are read and chunks written as whole lines.
+__global__ void __launch_bounds__(256)
+retile_scales_kernel(const uint8_t* __restrict__ src_a, uint32_t* __restrict__ dst_a, int rows_a, int rb_a, const uint8_t* __restrict__ src_b,
+                     uint32_t* __restrict__ dst_b, int rows_b, int ks, int kc_count, int kc_tiles)
 {
-    for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < words_a + words_b; idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const bool is_a = idx < words_a;
-        const size_t i = is_a ? idx : idx - words_a;
-        const uint8_t* src = is_a ? src_a : src_b;
-        const int rows = is_a ? rows_a : rows_b;
-        const int pos = static_cast<int>(i % 128);
-        const size_t chunk = i / 128;
-        const int kc = static_cast<int>(chunk % kc_count);
-        const int rb = static_cast<int>(chunk / kc_count);
-        const int r = rb * 128 + (pos & 3) * 32 + (pos >> 2);
-        uint32_t w = 0;
+    __shared__ uint32_t tile[128][33];  // [position inside a chunk][chunk]
+    int blk = blockIdx.x;
+    const bool is_a = blk < rb_a * kc_tiles;
+    if (!is_a) blk -= rb_a * kc_tiles;
+    const uint8_t* src = is_a ? src_a : src_b;
+    uint32_t* dst = is_a ? dst_a : dst_b;
+    const int rows = is_a ? rows_a : rows_b;
+    const int rb = blk / kc_tiles, kc0 = (blk % kc_tiles) * 32;
+    const bool words = (ks & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 3) == 0;
+    for (int idx = threadIdx.x; idx < 128 * 32; idx += 256) {
+        const int rl = idx >> 5, j = idx & 31;
+        const int r = rb * 128 + rl, k = (kc0 + j) * 4;
+        uint32_t w;
+        if (r < rows && k + 3 < ks && words) {
+            w = *reinterpret_cast<const uint32_t*>(src + static_cast<size_t>(r) * ks + k);
+        } else {
+            w = 0;
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const int k = kc * 4 + b;
-            const uint32_t v = (r < rows && k < ks) ? src[static_cast<size_t>(r) * ks + k] : 127u;
-            w |= v << (8 * b);
+            for (int b = 0; b < 4; ++b) w |= ((r < rows && k + b < ks) ? static_cast<uint32_t>(src[static_cast<size_t>(r) * ks + k + b]) : 127u) << (8 * b);
         }
-        (is_a ? dst_a : dst_b)[i] = w;
+        tile[(rl & 31) * 4 + (rl >> 5)][j] = w;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 128 * 32; idx += 256) {
+        const int j = idx >> 7, pos = idx & 127;
+        if (kc0 + j < kc_count) dst[(static_cast<size_t>(rb) * kc_count + kc0 + j) * 128 + pos] = tile[pos][j];
     }
 }
 
@@ -1396,9 +1406,10 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
             sfa = static_cast<uint8_t*>(st->scratch_dev);
         }
         uint8_t* sfb = sfa + bytes_a;
-        const int grid_rt = static_cast<int>(std::min<size_t>(((bytes_a + bytes_b) / 4 + 255) / 256, 4096));
-        retile_scales_kernel<<<grid_rt, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_a_dev), reinterpret_cast<uint32_t*>(sfa), m, bytes_a / 4,
-                                                          static_cast<const uint8_t*>(d->scale_b_dev), reinterpret_cast<uint32_t*>(sfb), n, bytes_b / 4, ks, kc);
+        const int kc_tiles = (kc + 31) / 32;
+        retile_scales_kernel<<<(rba + rbb) * kc_tiles, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_a_dev), reinterpret_cast<uint32_t*>(sfa), m, rba,
+                                                                         static_cast<const uint8_t*>(d->scale_b_dev), reinterpret_cast<uint32_t*>(sfb), n, ks, kc,
+                                                                         kc_tiles);
         ASCB200_CUDA(cudaGetLastError());
         p.sfa = sfa;
         p.sfb = sfb;
