@@ -51,10 +51,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 // ---- bulk tensor stores (shared -> global) -----------------------------------------------------
 // x * element size must be a multiple of 16 bytes; coordinates are never negative here.
+// The lines written are marked evict-first in L2: outputs are written once and should not push the
+// operands, which every tile re-reads, out of the cache.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int x, int y)
 {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                 :: "l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y) : "memory");
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+                 :: "l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "l"(policy) : "memory");
 }
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Returns once all but the newest N bulk groups of this thread have finished reading shared memory.
