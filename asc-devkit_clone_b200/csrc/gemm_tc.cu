@@ -61,6 +61,7 @@ struct GemmParams {
     const uint8_t* sfa;      // MXFP4: re-tiled scale factors (see retile_scales_kernel)
     const uint8_t* sfb;
     int sf_kc;               // 512-byte chunks per 128-row block in sfa / sfb
+    int pair_n;              // CTA-pair kernels for fp16 / bf16 / int8: columns per tile (multiple of 16, at most 256)
     uint32_t idesc;
     uint32_t* status;
 #ifdef ASCB200_PROBE
@@ -94,7 +95,7 @@ struct Cfg {
 };
 
 struct TileInfo {
-    int row0, row_end, n0, group;
+    int row0, row_end, n0, n_end, group;  // n_end: first column after the tile
 };
 
 // Tensor maps of the outputs (rank 2, box 32 x 32, swizzle = bytes of one box row).
@@ -160,11 +161,13 @@ __device__ __forceinline__ bool locate_tile(const GemmParams& p, int tile, int n
         t.row0 = row_start[cursor] + (local % m_tiles) * BLOCK_M;
         t.row_end = row_start[cursor + 1];
         t.n0 = (local / m_tiles) * BLOCK_N;
+        t.n_end = t.n0 + BLOCK_N;
     } else {
         t.group = 0;
         t.row0 = (tile % num_m) * BLOCK_M;
         t.row_end = p.m;
         t.n0 = (tile / num_m) * BLOCK_N;
+        t.n_end = t.n0 + BLOCK_N;
     }
     return true;
 }
@@ -230,6 +233,9 @@ __device__ __forceinline__ void store_row32(void* base, long long ld, int vec, i
         if (vec && ncols == 32) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) st_v4(out + 4 * j, w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        } else if (vec && ncols == 16) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) st_v4(out + 4 * j, w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
         } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -243,6 +249,9 @@ __device__ __forceinline__ void store_row32(void* base, long long ld, int vec, i
         if (vec && ncols == 32) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) st_v4(out + 8 * j, w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        } else if (vec && ncols == 16) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) st_v4(out + 8 * j, w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
         } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -257,6 +266,8 @@ __device__ __forceinline__ void store_row32(void* base, long long ld, int vec, i
         if (vec && ncols == 32) {
             st_v4(out, w[0], w[1], w[2], w[3]);
             st_v4(out + 16, w[4], w[5], w[6], w[7]);
+        } else if (vec && ncols == 16) {
+            st_v4(out, w[0], w[1], w[2], w[3]);
         } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -466,18 +477,22 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
     st.smem_c = stage_smem;
     st.smem_c2 = stage_smem + c_used;
     st.dual = stage_c && stage_c2;
+    const EpiStage direct = {nullptr, nullptr, 0u, 0u, st.row_base, false};
 #pragma unroll 1
     for (int c = chunk0; c < chunk1; ++c) {
         const int col0 = t.n0 + c * 32;
-        if (col0 >= p.n) break;  // uniform across the warp
+        if (col0 >= p.n || col0 >= t.n_end) break;  // uniform across the warp
         uint32_t r[32];
         tmem_ld_32x32(t_addr + c * 32, r);
         tmem_ld_wait();
 #ifdef ASCB200_PROBE
         if (p.probe & 4) continue;
 #endif
-        epilogue_chunk<ACC_INT, MODE, DT>(r, p.epi, st, row, row_ok, col0, min(32, p.n - col0), static_cast<size_t>(col0),
-                                          static_cast<size_t>(t.group) * p.n + col0, tok);
+        // a chunk that the tile only half owns (tile widths are multiples of 16) is stored from registers: the
+        // bulk store's 32-column box would reach into the neighbouring tile
+        const bool whole = col0 + 32 <= t.n_end;
+        epilogue_chunk<ACC_INT, MODE, DT>(r, p.epi, whole ? st : direct, row, row_ok, col0, min(whole ? 32 : t.n_end - col0, p.n - col0),
+                                          static_cast<size_t>(col0), static_cast<size_t>(t.group) * p.n + col0, tok);
     }
 }
 
@@ -860,7 +875,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #endif
     const int cluster_id = blockIdx.x >> 1;
     const int num_clusters = gridDim.x >> 1;
-    const int num_n = (p.n + BLOCK_N - 1) / BLOCK_N;
+    // tile width: fixed for MXFP4 (scale blocks), chosen per call otherwise (BLOCK_N is then the upper bound that sizes
+    // shared memory and the accumulator stages in TMEM)
+    const int bn = KIND == KIND_MXF4 ? BLOCK_N : p.pair_n;
+    const int num_n = (p.n + bn - 1) / bn;
     const int num_m = (p.m + PAIR_M - 1) / PAIR_M;
     const int total_tiles = num_m * num_n;
 
@@ -895,7 +913,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         bool ok = true;
         for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters) {
             const int row0 = (tile % num_m) * PAIR_M + static_cast<int>(rank) * BLOCK_M;
-            const int n0 = (tile / num_m) * BLOCK_N + static_cast<int>(rank) * (BLOCK_N / 2);
+            const int n0 = (tile / num_m) * bn + static_cast<int>(rank) * (bn / 2);
             for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                 ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_word, p.status);
                 if (!ok) break;
@@ -904,7 +922,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t bar = own_bar & kPeerBitMask;  // the leader's barrier counts both CTAs' bytes
                     const uint32_t sa = smem_u32(tiles + stage * C::STAGE_BYTES);
                     const uint32_t sb = sa + A_TILE_BYTES;
-                    if (rank == 0) mbar_expect_tx(own_bar, 2 * C::STAGE_BYTES);
+                    if (rank == 0) mbar_expect_tx(own_bar, 2 * (A_TILE_BYTES + (bn / 2) * ROW_BYTES + C::SF_BYTES));
                     const int k0 = kb * C::BLOCK_K;
                     const int kx = KIND == KIND_MXF4 ? k0 / 2 : k0;  // packed fp4: two values per tensor-map element
                     constexpr int MN_PER_BOX = KIND == KIND_F16 ? 64 : 128;
@@ -912,7 +930,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if constexpr (KIND == KIND_MXF4) {
                         // re-tiled scales as a [chunk, 128 x u32] tensor: the two chunks of this K block per 128-row block
                         const uint32_t ssf = sb + C::B_TILE_BYTES;
-                        const int tile_n0 = n0 - static_cast<int>(rank) * (BLOCK_N / 2);
+                        const int tile_n0 = n0 - static_cast<int>(rank) * (bn / 2);
                         tma_load_2d_pair(ssf, &tmap_sfa, 0, (row0 / 128) * p.sf_kc + 2 * kb, bar);
 #pragma unroll
                         for (int rb = 0; rb < C::SF_B_BLOCKS; ++rb)
@@ -974,7 +992,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #endif
             const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
             const uint32_t acc_full = smem_u32(&acc_full_bar[acc_stage]);
-            const uint32_t sfb_off = static_cast<uint32_t>(((tile / num_m) * BLOCK_N) % 128) / 32;
+            const uint32_t sfb_off = static_cast<uint32_t>(((tile / num_m) * bn) % 128) / 32;
             const int last = p.num_k_blocks - 1;
             int kb = 0;
             if constexpr (KIND == KIND_MXF4) {
@@ -1051,8 +1069,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // ===== epilogue (both CTAs, each for its own 128 rows) =====
         const int quad = warp & 3;
         const int half = (warp - 4) >> 2;
-        constexpr int CHUNKS = BLOCK_N / 32;
-        const int chunk0 = half * (CHUNKS / 2), chunk1 = chunk0 + CHUNKS / 2;
+        const int chunks = (bn + 31) / 32, split = (chunks + 1) / 2;
+        const int chunk0 = half * split, chunk1 = half ? chunks : split;
         int acc_iter = 0;
         bool ok = true;
         for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters, ++acc_iter) {
@@ -1065,7 +1083,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             t.group = 0;
             t.row0 = (tile % num_m) * PAIR_M + static_cast<int>(rank) * BLOCK_M;
             t.row_end = p.m;
-            t.n0 = (tile / num_m) * BLOCK_N;
+            t.n0 = (tile / num_m) * bn;
+            t.n_end = t.n0 + bn;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc_stage * BLOCK_N;
             epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, outs, smem_u32(epi_stage) + (warp - 4) * C::EPI_BYTES_PER_WARP, C::EPI_BYTES_PER_WARP, t_addr,
                                                         quad, lane, chunk0, chunk1);
@@ -1342,12 +1361,23 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         const long long m_tiles = grouped ? (m + BLOCK_M - 1) / BLOCK_M + groups : (m + BLOCK_M - 1) / BLOCK_M;
         double best = -1.0;
         struct Cand { int bn; bool pair; double eff; };
-        const Cand cands[] = {{wide, true, 1.0}, {wide, false, 0.88}, {128, false, 0.75}, {64, false, 0.5}};
-        for (const Cand& c : cands) {
+        Cand cands[20];
+        int num_cands = 0;
+        cands[num_cands++] = {wide, true, 1.0};
+        if (kind != ASCB200_KIND_MXFP4 && d->trans_b) {
+            // CTA-pair tiles of any width that is a multiple of 16: a narrower tile re-reads A more often per column
+            // (128 columns measured at 0.75 of the full width's rate), but may fill the last wave far better
+            for (int bn = 240; bn >= 64; bn -= 16) cands[num_cands++] = {bn, true, 1.0 / (1.0 + 0.33 * (256.0 / bn - 1.0))};
+        }
+        cands[num_cands++] = {wide, false, 0.88};
+        cands[num_cands++] = {128, false, 0.75};
+        cands[num_cands++] = {64, false, 0.5};
+        for (int ci = 0; ci < num_cands; ++ci) {
+            const Cand& c = cands[ci];
             if (c.pair && !pair_allowed) continue;
             if (c.bn == 64 && kind == ASCB200_KIND_MXFP4) continue;                          // scale blocks span 128 rows
-            if (c.bn == 64 && kind == ASCB200_KIND_S8 && !d->trans_b) continue;              // N-contiguous int8 B comes in boxes of 128 columns
-            if (c.bn > 64 && n <= c.bn / 2 && c.bn != 128) continue;                         // do not pad N by more than 2x
+            if (c.bn == 64 && !c.pair && kind == ASCB200_KIND_S8 && !d->trans_b) continue;   // N-contiguous int8 B comes in boxes of 128 columns
+            if (c.bn > 64 && n <= c.bn / 2 && (c.pair || c.bn != 128)) continue;             // do not pad N by more than 2x
             const long long n_tiles = (n + c.bn - 1) / c.bn;
             const long long tiles = c.pair ? static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * n_tiles : m_tiles * n_tiles;
             const long long slots = c.pair ? pair_clusters : sm_count;
@@ -1358,6 +1388,14 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
                 block_n = c.bn;
                 use_pair = c.pair;
             }
+        }
+    }
+    if (const char* force = getenv("ASCB200_PAIR_N")) {
+        // testing / tuning override: CTA-pair kernel with this tile width where the kernel supports it
+        const int bn = atoi(force);
+        if (pair_allowed && kind != ASCB200_KIND_MXFP4 && d->trans_b && bn >= 16 && bn <= 256 && bn % 16 == 0) {
+            block_n = bn;
+            use_pair = true;
         }
     }
     const long long pair_tiles = static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((n + block_n - 1) / block_n);
@@ -1382,6 +1420,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     p.a_mn = d->trans_a ? 1 : 0;
     p.b_mn = d->trans_b ? 0 : 1;
     p.groups = grouped ? groups : 0;
+    p.pair_n = block_n;
     p.group_counts = reinterpret_cast<const long long*>(group_counts);
     p.status = fixed ? fixed->status_dev : st->status_dev;
     p.epi = e;
@@ -1433,11 +1472,11 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
             return launch_gemm_pair<KIND_MXF4, 192>(ta, tb, tsfa, tsfb, outs, p, clusters, stream);
         }
         if (kind == ASCB200_KIND_S8) {
-            p.idesc = make_idesc(2, 1, 1, a_mn, b_mn, 2 * BLOCK_M, 256);
+            p.idesc = make_idesc(2, 1, 1, a_mn, b_mn, 2 * BLOCK_M, block_n);
             return launch_gemm_pair<KIND_I8, 256>(ta, tb, ta, tb, outs, p, clusters, stream);
         }
         const uint32_t fmt = kind == ASCB200_KIND_BF16 ? 1u : 0u;
-        p.idesc = make_idesc(1, fmt, fmt, a_mn, b_mn, 2 * BLOCK_M, 256);
+        p.idesc = make_idesc(1, fmt, fmt, a_mn, b_mn, 2 * BLOCK_M, block_n);
         return launch_gemm_pair<KIND_F16, 256>(ta, tb, ta, tb, outs, p, clusters, stream);
     }
     switch (kind) {

@@ -110,6 +110,43 @@ def test_gemm_a8w8_cta_pair_token_channel_dequant():
     assert (d_c.download() == orc.dequant_tok_ch(orc.gemm_i8(a, b, trans_b=True), tok, ch, orc.BF16)).all()
 
 
+@pytest.mark.parametrize("pair_n", [240, 208, 176, 144, 112, 80, 48])
+def test_gemm_i8_cta_pair_tile_widths(pair_n, monkeypatch):
+    """The CTA-pair kernel takes any tile width that is a multiple of 16; a half-owned 32-column chunk at the tile edge is stored
+    from registers, whole chunks by bulk stores.  int32 (direct), bf16 dequant and int8 requant (staged) outputs."""
+    monkeypatch.setenv("ASCB200_PAIR_N", str(pair_n))
+    ab = dev()
+    m, n, k = 520, 1000, 384
+    rng, a, b = _i8_inputs(m, n, k, False, True, pair_n)
+    acc = orc.gemm_i8(a, b, trans_b=True)
+    d_a, d_b = ab.to_dev(a), ab.to_dev(b)
+    d_c = ab.empty((m, n), np.int32)
+    d_c.fill(0x5A)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, d_a, d_b, d_c, ab.S32, trans_b=True))
+    ab.sync()
+    assert (d_c.download() == acc).all()
+    tok = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+    ch = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    d_y = ab.empty((m, n), np.uint16)
+    d_y.fill(0x5A)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, d_a, d_b, d_y, ab.BF16, epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, trans_b=True, tok=ab.to_dev(tok),
+                     ch=ab.to_dev(ch)))
+    ab.sync()
+    assert (d_y.download() == orc.dequant_tok_ch(acc, tok, ch, orc.BF16)).all()
+    q = quant_params(rng.uniform(2e-5, 2e-4, n).astype(np.float32), rng.integers(-20, 20, n))
+    d_q = ab.empty((m, n), np.int8)
+    d_q.fill(0x5A)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, d_a, d_b, d_q, ab.S8, epilogue=ab.EPI_FIXPIPE_QUANT, trans_b=True, quant=ab.to_dev(q)))
+    ab.sync()
+    assert (d_q.download() == orc.fixpipe_req8(acc, q)).all()
+
+
+@pytest.mark.parametrize("pair_n", [224, 96])
+def test_gemm_f16_cta_pair_tile_widths(pair_n, monkeypatch):
+    monkeypatch.setenv("ASCB200_PAIR_N", str(pair_n))
+    run_f16(300, 1336, 192, False, True, bias=True, c_dtype=1, seed=pair_n)
+
+
 @pytest.mark.parametrize("mode", ["req8", "req8_scalar_relu", "deqf16", "qs322bf16"])
 def test_gemm_i8_fixpipe_quant(mode):
     ab = dev()
