@@ -998,7 +998,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if constexpr (KIND == KIND_MXF4) {
                 // Every MMA waits until the scale copies queued before it have landed (a few hundred cycles),
                 // so the copies of two K blocks go out together and the wait is paid once per eight MMAs.
-                for (; kb < last; kb += 2) {
+                for (;
+#ifdef ASCB200_PROBE
+                     !(p.probe & 256) &&
+#endif
+                     kb < last; kb += 2) {
                     auto nxt = cur;
                     nxt.advance();
 #ifdef ASCB200_PROBE
@@ -1051,14 +1055,31 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
             }
             for (; ok && kb <= last; ++kb) {
+#ifdef ASCB200_PROBE
+                const long long t0 = clock64();
+#endif
                 ok = mbar_wait(cur.full_bar, cur.phase, abort_word, p.status);
                 if (!ok) break;
                 tc_fence_after();
+#ifdef ASCB200_PROBE
+                const long long t1 = clock64();
+                long long t3 = t1;
+#endif
                 if (elect_one()) {
                     issue_k_block<KIND, true, C::SF_B_BLOCKS>(cur, d_tmem, hi_word, a_k16, b_k16, p.idesc, idesc_hi_sf, sfb_off, kb == 0);
                     if (kb == last) tc_commit_pair(acc_full);
+#ifdef ASCB200_PROBE
+                    t3 = clock64();
+#endif
                 }
                 __syncwarp();
+#ifdef ASCB200_PROBE
+                if (lane == 0 && cluster_id == 0) {
+                    atomicAdd(&g_probe_times[0], static_cast<unsigned long long>(t1 - t0));
+                    atomicAdd(&g_probe_times[2], static_cast<unsigned long long>(t3 - t1));
+                    atomicAdd(&g_probe_times[3], 1ull);
+                }
+#endif
                 cur.advance();
             }
         }

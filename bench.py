@@ -122,7 +122,7 @@ class A8W8(Workload):
     name = "a8w8_gemm_4096x4096x11008_dequant_bf16"
     metric, unit, dtype = "quant-GEMM throughput (int8, fused per-token x per-channel dequant)", "TOPS", "s8"
     M, K, N = 4096, 4096, 11008
-    traffic_1gpu = 62.19e6 + 45.22e6   # profiles/gemm_tc_pair_kernel_int8_a8w8_4096x4096x11008.md
+    traffic_1gpu = 62.11e6 + 48.78e6   # profiles/gemm_tc_pair_kernel_int8_a8w8_4096x4096x11008.md
 
     def __init__(self, ab, rank, world, sets):
         self.ab, self.rank, self.world = ab, rank, world
@@ -191,7 +191,7 @@ class Grouped(Workload):
     metric, unit, dtype = "grouped quant-GEMM throughput (int8, fused dequant)", "TOPS", "s8"
     G, MTOT, K, N = 64, 32768, 7168, 2048
     OUT, ACT = "BF16", 0
-    traffic_1gpu = 1.2132e9 + 0.1228e9   # profiles/gemm_tc_kernel_int8_grouped_64groups_M32768_K7168_N2048.md
+    traffic_1gpu = 1.2225e9 + 0.1235e9   # profiles/gemm_tc_kernel_int8_grouped_64groups_M32768_K7168_N2048.md
 
     def counts(self):
         return dirichlet_counts(self.G, self.MTOT, 0xA5C00003)
@@ -271,7 +271,7 @@ class MXFP4(Workload):
     metric, unit, dtype = "quant-GEMM throughput (MXFP4 e2m1 x ue8m0, int8 requant + bf16 out)", "TFLOPS", "fp4_e2m1"
     M = K = N = 8192
     kernels_per_step = 3  # two scale re-tiling launches + the GEMM
-    traffic_1gpu = 138.1e6 + 170.4e6    # profiles/gemm_tc_pair_kernel_mxfp4_8192x8192x8192.md
+    traffic_1gpu = 94.2e6 + 167.3e6    # profiles/gemm_tc_pair_kernel_mxfp4_8192x8192x8192.md
     published = (1614.0, "Ascend 950PR basic-API MXFP4 8192^3, bf16 out (BASELINE.md)")
 
     def __init__(self, ab, rank, world, sets):
@@ -417,7 +417,7 @@ class SoftmaxQuantLarge(SoftmaxQuant):
     baseline shape lasts only a few microseconds, so launch ramp-up and tail dominate its bandwidth figure."""
     name = "softmax_ascendquant_262144x2048_fp16_int8"
     ROW_FACTOR = 64
-    traffic_1gpu = 1.0738e9 + 1.5555e9  # profiles/softmax_rows_kernel_fused_quant_262144x2048.md
+    traffic_1gpu = 1.0738e9 + 1.5580e9  # profiles/softmax_rows_kernel_fused_quant_262144x2048.md
 
 
 class FP16(Workload):
