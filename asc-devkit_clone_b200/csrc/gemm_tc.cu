@@ -115,7 +115,7 @@ struct EpiStage {
 };
 
 // Grouped mode: prefix sums of rows and of tiles per group, built once per CTA by warp 0.
-__device__ void build_group_tables(const long long* counts, int groups, int num_n, int* row_start, int* tile_start)
+__device__ void build_group_tables(const long long* counts, int groups, int num_n, int tile_rows, int* row_start, int* tile_start)
 {
     const int lane = threadIdx.x & 31;
     int rows_carry = 0, tiles_carry = 0;
@@ -123,7 +123,7 @@ __device__ void build_group_tables(const long long* counts, int groups, int num_
         const int g = base + lane;
         long long c = g < groups ? counts[g] : 0;
         int rows = c > 0 ? static_cast<int>(c) : 0;
-        int tiles = ((rows + BLOCK_M - 1) / BLOCK_M) * num_n;
+        int tiles = ((rows + tile_rows - 1) / tile_rows) * num_n;
         int rs = rows, ts = tiles;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -169,6 +169,29 @@ __device__ __forceinline__ bool locate_tile(const GemmParams& p, int tile, int n
         t.n0 = (tile / num_m) * BLOCK_N;
         t.n_end = t.n0 + BLOCK_N;
     }
+    return true;
+}
+
+// Same for the CTA-pair kernel: tiles of 256 rows and `bn` columns; row0 is the first row of the pair's tile.
+__device__ __forceinline__ bool locate_pair_tile(const GemmParams& p, int tile, int num_m, int total_tiles, int bn, const int* row_start, const int* tile_start,
+                                                 int& cursor, TileInfo& t)
+{
+    if (tile >= total_tiles) return false;
+    if (p.groups > 0) {
+        while (tile >= tile_start[cursor + 1]) ++cursor;
+        const int local = tile - tile_start[cursor];
+        const int m_tiles = (row_start[cursor + 1] - row_start[cursor] + 2 * BLOCK_M - 1) / (2 * BLOCK_M);
+        t.group = cursor;
+        t.row0 = row_start[cursor] + (local % m_tiles) * 2 * BLOCK_M;
+        t.row_end = row_start[cursor + 1];
+        t.n0 = (local / m_tiles) * bn;
+    } else {
+        t.group = 0;
+        t.row0 = (tile % num_m) * 2 * BLOCK_M;
+        t.row_end = p.m;
+        t.n0 = (tile / num_m) * bn;
+    }
+    t.n_end = t.n0 + bn;
     return true;
 }
 
@@ -667,7 +690,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
     }
-    if (warp == 0 && p.groups > 0) build_group_tables(p.group_counts, p.groups, num_n, row_start, tile_start);
+    if (warp == 0 && p.groups > 0) build_group_tables(p.group_counts, p.groups, num_n, BLOCK_M, row_start, tile_start);
     if (warp == 2) {
         tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
         tmem_relinquish();
@@ -833,15 +856,16 @@ struct Cfg2 {
     static constexpr int SF_COLS_PER_STAGE = 24;
     static constexpr int SF_COL0 = ACC_STAGES * BLOCK_N;
     static constexpr int MAX_SF_STAGES = KIND == KIND_MXF4 ? (512 - SF_COL0) / SF_COLS_PER_STAGE : 8;
-    static constexpr int EPI_BYTES_PER_WARP = KIND == KIND_MXF4 ? 3072 : 4096;  // staged output chunks (see Cfg)
+    static constexpr int EPI_BYTES_PER_WARP = 3072;  // staged output chunks (see Cfg)
     static constexpr int EPI_BYTES = NUM_EPI_WARPS * EPI_BYTES_PER_WARP;
-    static constexpr int NUM_STAGES = std::min(8, (227 * 1024 - 1024 - 256 - EPI_BYTES) / STAGE_BYTES);
+    static constexpr int TABLE_BYTES = 2 * (MAX_GROUPS + 1) * static_cast<int>(sizeof(int));  // grouped mode: row and tile prefix sums
+    static constexpr int NUM_STAGES = std::min(8, (227 * 1024 - 1024 - 256 - EPI_BYTES - TABLE_BYTES) / STAGE_BYTES);
     static constexpr int SF_SLOTS = std::min(NUM_STAGES, MAX_SF_STAGES);  // scale-factor slots in TMEM
     static constexpr int TMEM_COLS = 512;
     static_assert(ACC_STAGES * BLOCK_N + (KIND == KIND_MXF4 ? SF_SLOTS * SF_COLS_PER_STAGE : 0) <= 512, "TMEM budget");
     static constexpr int BLOCK_K = KIND == KIND_F16 ? 64 : KIND == KIND_I8 ? 128 : 256;
     static constexpr int UMMA_K = BLOCK_K / 4;
-    static constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
+    static constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256 + TABLE_BYTES;
 };
 
 template <int KIND, int BLOCK_N>
@@ -864,6 +888,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint64_t* acc_empty_bar = acc_full_bar + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
+    int* row_start = reinterpret_cast<int*>(epi_stage + C::EPI_BYTES + 256);  // both CTAs build identical tables
+    int* tile_start = row_start + (MAX_GROUPS + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -880,7 +906,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int bn = KIND == KIND_MXF4 ? BLOCK_N : p.pair_n;
     const int num_n = (p.n + bn - 1) / bn;
     const int num_m = (p.m + PAIR_M - 1) / PAIR_M;
-    const int total_tiles = num_m * num_n;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::NUM_STAGES; ++s) {
@@ -896,6 +921,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
     }
+    if (warp == 3 && p.groups > 0) build_group_tables(p.group_counts, p.groups, num_n, PAIR_M, row_start, tile_start);
     if (warp == 2) {
         tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
         tmem_relinquish_pair();
@@ -905,15 +931,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     cluster_sync_all();  // the peer's barriers exist before anything can arrive on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = p.groups > 0 ? tile_start[p.groups] : num_m * num_n;
 
     if (warp == 0) {
         // ===== TMA producer (both CTAs) =====
-        int stage = 0;
+        int stage = 0, cursor = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters) {
-            const int row0 = (tile % num_m) * PAIR_M + static_cast<int>(rank) * BLOCK_M;
-            const int n0 = (tile / num_m) * bn + static_cast<int>(rank) * (bn / 2);
+        TileInfo t;
+        for (int tile = cluster_id; ok && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t); tile += num_clusters) {
+            // rows past the end of a group belong to the next group (or lie outside the matrix and read as zero): they are
+            // multiplied like the others and never stored
+            const int row0 = t.row0 + static_cast<int>(rank) * BLOCK_M;
+            const int n0 = t.n0 + static_cast<int>(rank) * (bn / 2);
             for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                 ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_word, p.status);
                 if (!ok) break;
@@ -943,10 +973,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         for (int j = 0; j < BLOCK_M / MN_PER_BOX; ++j) tma_load_3d_pair(sa + j * BOX_BYTES, &tmap_a, row0 + j * MN_PER_BOX, k0, 0, bar);
                     }
                     if (!p.b_mn) {
-                        tma_load_3d_pair(sb, &tmap_b, kx, n0, 0, bar);
+                        tma_load_3d_pair(sb, &tmap_b, kx, n0, t.group, bar);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < (BLOCK_N / 2) / MN_PER_BOX; ++j) tma_load_3d_pair(sb + j * BOX_BYTES, &tmap_b, n0 + j * MN_PER_BOX, k0, 0, bar);
+                        for (int j = 0; j < (BLOCK_N / 2) / MN_PER_BOX; ++j) tma_load_3d_pair(sb + j * BOX_BYTES, &tmap_b, n0 + j * MN_PER_BOX, k0, t.group, bar);
                     }
                 }
                 __syncwarp();
@@ -1092,20 +1122,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int half = (warp - 4) >> 2;
         const int chunks = (bn + 31) / 32, split = (chunks + 1) / 2;
         const int chunk0 = half * split, chunk1 = half ? chunks : split;
-        int acc_iter = 0;
+        int acc_iter = 0, cursor = 0;
         bool ok = true;
-        for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters, ++acc_iter) {
+        TileInfo t;
+        for (int tile = cluster_id; ok && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t); tile += num_clusters, ++acc_iter) {
             const int acc_stage = acc_iter & 1;
             const uint32_t acc_phase = (acc_iter >> 1) & 1u;
             ok = mbar_wait_relaxed(smem_u32(&acc_full_bar[acc_stage]), acc_phase, abort_word, p.status);
             if (!ok) break;
             tc_fence_after();
-            TileInfo t;
-            t.group = 0;
-            t.row0 = (tile % num_m) * PAIR_M + static_cast<int>(rank) * BLOCK_M;
-            t.row_end = p.m;
-            t.n0 = (tile / num_m) * bn;
-            t.n_end = t.n0 + bn;
+            t.row0 += static_cast<int>(rank) * BLOCK_M;  // this CTA's half of the pair tile
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc_stage * BLOCK_N;
             epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, outs, smem_u32(epi_stage) + (warp - 4) * C::EPI_BYTES_PER_WARP, C::EPI_BYTES_PER_WARP, t_addr,
                                                         quad, lane, chunk0, chunk1);
@@ -1374,7 +1400,11 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     // memory and L2 per MAC; measured on 4096 x 4096 x 11008 int8: pair 256x256 1.0, single 128x256 0.88, 128x128 0.75,
     // 128x64 0.5).  Small problems and thin N-slabs get narrower tiles so that the last wave is not mostly idle.
     const int pair_clusters = sm_count / 2;
-    const bool pair_allowed = !grouped && !(fixed && kind == ASCB200_KIND_MXFP4) && !(getenv("ASCB200_NO_PAIR") && getenv("ASCB200_NO_PAIR")[0] == '1');
+    const bool pair_possible = !(fixed && kind == ASCB200_KIND_MXFP4) && !(getenv("ASCB200_NO_PAIR") && getenv("ASCB200_NO_PAIR")[0] == '1');
+    // Grouped problems take CTA pairs only when groups are long: a group's last 256-row tile is half empty on average, and
+    // under the board's power cap the wasted MMAs cost as much time as useful ones (64 groups of 512 rows on average:
+    // pairs 490 us at 1.09 GHz, single-CTA tiles 425-475 us at 1.25-1.32 GHz).
+    const bool pair_allowed = pair_possible && (!grouped || m / groups >= 16 * BLOCK_M);
     const int wide = kind == ASCB200_KIND_MXFP4 ? 192 : 256;   // fp4 at 256 columns cannot double-buffer its accumulators in TMEM
     int block_n = 64;
     bool use_pair = false;
@@ -1400,7 +1430,9 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
             if (c.bn == 64 && !c.pair && kind == ASCB200_KIND_S8 && !d->trans_b) continue;   // N-contiguous int8 B comes in boxes of 128 columns
             if (c.bn > 64 && n <= c.bn / 2 && (c.pair || c.bn != 128)) continue;             // do not pad N by more than 2x
             const long long n_tiles = (n + c.bn - 1) / c.bn;
-            const long long tiles = c.pair ? static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * n_tiles : m_tiles * n_tiles;
+            // grouped: the host does not see the counts; a group ends on average half a tile past its last full one
+            const long long pair_m_tiles = grouped ? (m + 2 * BLOCK_M - 1) / (2 * BLOCK_M) + (groups + 1) / 2 : (m + 2 * BLOCK_M - 1) / (2 * BLOCK_M);
+            const long long tiles = c.pair ? pair_m_tiles * n_tiles : m_tiles * n_tiles;
             const long long slots = c.pair ? pair_clusters : sm_count;
             const long long waves = (tiles + slots - 1) / slots;
             const double cost = static_cast<double>(waves) * (c.pair ? 2 : 1) * BLOCK_M * c.bn / c.eff / (c.pair ? 2 : 1);
@@ -1414,12 +1446,12 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     if (const char* force = getenv("ASCB200_PAIR_N")) {
         // testing / tuning override: CTA-pair kernel with this tile width where the kernel supports it
         const int bn = atoi(force);
-        if (pair_allowed && kind != ASCB200_KIND_MXFP4 && d->trans_b && bn >= 16 && bn <= 256 && bn % 16 == 0) {
+        if (pair_possible && kind != ASCB200_KIND_MXFP4 && (d->trans_b || bn == 256) && bn >= 16 && bn <= 256 && bn % 16 == 0) {
             block_n = bn;
             use_pair = true;
         }
     }
-    const long long pair_tiles = static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((n + block_n - 1) / block_n);
+    const long long pair_tiles = (static_cast<long long>((m + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) + (grouped ? groups : 0)) * ((n + block_n - 1) / block_n);
 
     const int b_box_rows = use_pair ? block_n / 2 : block_n;
 

@@ -211,6 +211,31 @@ def test_grouped_a8w8(counts, trans_b):
     assert (d_c.download() == ref).all()
 
 
+@pytest.mark.parametrize("trans_b", [True, False])
+@pytest.mark.parametrize("counts", [[300, 0, 517, 256, 1, 999, 130], [512, 512, 512], [1500, 40]])
+def test_grouped_a8w8_cta_pairs(counts, trans_b, monkeypatch):
+    """Grouped problems on the CTA-pair kernel (chosen by itself only for long groups, forced here): 256-row tiles whose tail
+    reaches into the next group (or past the matrix) must store only the group's own rows; groups of zero rows are skipped."""
+    monkeypatch.setenv("ASCB200_PAIR_N", "256" if not trans_b else "176")
+    ab = dev()
+    counts = np.array(counts, np.int64)
+    G, k, n = len(counts), 256, 608
+    m = int(counts.sum())
+    rng = np.random.default_rng(G * 1000 + m)
+    x = rng.integers(-127, 128, (m, k)).astype(np.int8)
+    w = rng.integers(-127, 128, (G, n, k) if trans_b else (G, k, n)).astype(np.int8)
+    tok = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+    ch = rng.uniform(1e-3, 1e-2, (G, n)).astype(np.float32)
+    d_c = ab.empty((m, n), np.uint16)
+    d_c.fill(0)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(x), ab.to_dev(w), d_c, ab.BF16, epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL,
+                     trans_b=trans_b, tok=ab.to_dev(tok), ch=ab.to_dev(ch), group_counts=ab.to_dev(counts), groups=G))
+    ab.sync()
+    ref = orc.grouped_i8(x, w, counts, tok, ch, orc.BF16, trans_b=trans_b)
+    got = d_c.download()
+    assert (got == ref).all(), f"{(got != ref).sum()} differ; first {np.argwhere(got != ref)[:5].tolist()}"
+
+
 def test_grouped_matches_reference_recipe(golden_dir):
     """The grouped example's own numpy recipe incl. FasterGelu and fp16 output (tests/golden/grouped.npz)."""
     import os
