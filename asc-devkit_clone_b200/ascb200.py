@@ -11,10 +11,10 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
-F32, F16, BF16, S8, S32, FP4 = 0, 1, 2, 3, 4, 5
+F32, F16, BF16, S8, S32, FP4, FP8_E4M3, FP8_E5M2 = 0, 1, 2, 3, 4, 5, 6, 7
 KIND_F16, KIND_BF16, KIND_S8, KIND_MXFP4 = 0, 1, 2, 3
 EPI_CAST, EPI_FIXPIPE_QUANT, EPI_DEQUANT_TOKEN_CHANNEL = 0, 1, 2
-ETIMEOUT = -6
+EINVAL, EALIGN, EUNSUPPORTED, ENODEV, ECUDA, ETIMEOUT, ETOOBIG = -1, -2, -3, -4, -5, -6, -7
 
 EXPORTS = [
     "ascb200_init", "ascb200_strerror", "ascb200_last_cuda_error", "ascb200_device_status", "ascb200_sm_count",
@@ -22,7 +22,7 @@ EXPORTS = [
     "ascb200_memset", "ascb200_stream_create", "ascb200_stream_destroy", "ascb200_stream_sync", "ascb200_event_create",
     "ascb200_event_destroy", "ascb200_event_record", "ascb200_stream_wait_event", "ascb200_event_elapsed_ms", "ascb200_gemm", "ascb200_grouped_gemm",
     "ascb200_gemm_mxfp4_noalloc", "ascb200_graph_begin", "ascb200_graph_end", "ascb200_graph_launch", "ascb200_graph_destroy",
-    "ascb200_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
+    "ascb200_nz_unpack", "ascb200_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
 ]
 
 
@@ -36,7 +36,7 @@ class GemmDesc(C.Structure):
         ("c2_dev", C.c_void_p), ("ldc2", C.c_int64), ("c2_dtype", C.c_int32),
         ("epilogue", C.c_int32), ("quant_dev", C.c_void_p), ("quant_scalar", C.c_uint64),
         ("tok_scale_dev", C.c_void_p), ("ch_scale_dev", C.c_void_p),
-        ("relu", C.c_int32), ("act", C.c_int32), ("reserved", C.c_int32 * 4),
+        ("relu", C.c_int32), ("act", C.c_int32), ("atomic", C.c_int32), ("reserved", C.c_int32 * 3),
     ]
 
 
@@ -60,6 +60,7 @@ def lib():
         if not os.path.exists(path):
             raise RuntimeError(f"{path} is missing: run `python asc-devkit_clone_b200/build.py` (there is no CPU fallback)")
         _lib = C.CDLL(path)
+        _lib.ascb200_init.argtypes = [C.c_int]
         _lib.ascb200_strerror.restype = C.c_char_p
         _lib.ascb200_strerror.argtypes = [C.c_int]
         _lib.ascb200_malloc.argtypes = [C.POINTER(C.c_void_p), C.c_size_t]
@@ -85,6 +86,7 @@ def lib():
         _lib.ascb200_graph_end.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
         _lib.ascb200_graph_launch.argtypes = [C.c_void_p, C.c_void_p]
         _lib.ascb200_graph_destroy.argtypes = [C.c_void_p]
+        _lib.ascb200_nz_unpack.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
         _lib.ascb200_softmax.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_void_p]
         _lib.ascb200_quant_per_tensor.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_float, C.c_void_p]
@@ -166,7 +168,7 @@ def _ptr(b):
 
 def gemm(kind, m, n, k, a, b, c, c_dtype, epilogue=EPI_CAST, trans_a=False, trans_b=False, lda=0, ldb=0, ldc=0, bias=None,
          scale_a=None, scale_b=None, c2=None, c2_dtype=0, ldc2=0, quant=None, quant_scalar=0, tok=None, ch=None, relu=False, act=0,
-         group_counts=None, groups=0, stream=None, noalloc=False):
+         group_counts=None, groups=0, stream=None, noalloc=False, atomic=0):
     d = GemmDesc()
     d.kind, d.m, d.n, d.k = kind, m, n, k
     d.a_dev, d.b_dev, d.lda, d.ldb = _ptr(a), _ptr(b), lda, ldb
@@ -176,11 +178,16 @@ def gemm(kind, m, n, k, a, b, c, c_dtype, epilogue=EPI_CAST, trans_a=False, tran
     d.c2_dev, d.ldc2, d.c2_dtype = _ptr(c2), ldc2, c2_dtype
     d.epilogue, d.quant_dev, d.quant_scalar = epilogue, _ptr(quant), int(quant_scalar)
     d.tok_scale_dev, d.ch_scale_dev, d.relu, d.act = _ptr(tok), _ptr(ch), int(relu), act
+    d.atomic = int(atomic)
     if noalloc:
         return lib().ascb200_gemm_mxfp4_noalloc(C.byref(d), stream)
     if groups:
         return lib().ascb200_grouped_gemm(C.byref(d), _ptr(group_counts), groups, stream)
     return lib().ascb200_gemm(C.byref(d), stream)
+
+
+def nz_unpack(src_nz, dst, groups, k, n, elem_bytes, to_nk=True, stream=None):
+    return lib().ascb200_nz_unpack(_ptr(src_nz), _ptr(dst), groups, k, n, elem_bytes, int(to_nk), stream)
 
 
 def softmax(src, dst, sum_, max_, m, k, dtype=F16, brc=False, stream=None):

@@ -31,7 +31,10 @@ constexpr int NUM_EPI_WARPS = 8;
 constexpr int MAX_GROUPS = 1024;
 constexpr int SF_CHUNK_BYTES = 512;     // scale factors of 128 rows x 4 K-blocks (of 32 elements)
 
-enum : int { OUT_F32 = ASCB200_F32, OUT_F16 = ASCB200_F16, OUT_BF16 = ASCB200_BF16, OUT_S8 = ASCB200_S8, OUT_S32 = ASCB200_S32 };
+enum : int {
+    OUT_F32 = ASCB200_F32, OUT_F16 = ASCB200_F16, OUT_BF16 = ASCB200_BF16, OUT_S8 = ASCB200_S8, OUT_S32 = ASCB200_S32,
+    OUT_E4M3 = ASCB200_FP8_E4M3, OUT_E5M2 = ASCB200_FP8_E5M2
+};
 
 struct EpiParams {
     void* c;
@@ -42,6 +45,7 @@ struct EpiParams {
     int relu, act;
     int vec_c, vec_c2;       // rows of c / c2 are 16-byte aligned at every 32-column boundary
     int tma_c, tma_c2;       // c / c2 (1- or 2-byte elements) may be written with bulk tensor stores
+    int atomic;              // 1: add into c instead of overwriting it (fp32 / int32 / fp16 / bf16 outputs)
     const void* bias;        // float (fp32 accumulators) or int32 (int32 accumulators)
     const float* tok;
     const float* ch;
@@ -243,6 +247,22 @@ __device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi)
 
 // Stores 32 consecutive outputs of one row; DT is the element type of the destination.
 // f: values for F32/F16/BF16, qi: values for S8/S32.
+// Adds 32 consecutive outputs of one row into the destination (enAtomic = 1 of GetTensorC / IterateAll): one reduction
+// per element, 16-bit types through the half / bfloat16 atomics (the sum is rounded to the destination type).
+template <int DT>
+__device__ __forceinline__ void atomic_row32(void* base, long long ld, int row, int col0, int ncols, const float (&f)[32], const int (&qi)[32])
+{
+    const size_t off = static_cast<size_t>(row) * static_cast<size_t>(ld) + col0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        if (j >= ncols) break;
+        if constexpr (DT == OUT_F32) atomicAdd(static_cast<float*>(base) + off + j, f[j]);
+        else if constexpr (DT == OUT_S32) atomicAdd(static_cast<int*>(base) + off + j, qi[j]);
+        else if constexpr (DT == OUT_F16) atomicAdd(static_cast<__half*>(base) + off + j, __float2half_rn(fminf(fmaxf(f[j], -65504.0f), 65504.0f)));
+        else if constexpr (DT == OUT_BF16) atomicAdd(static_cast<__nv_bfloat16*>(base) + off + j, __float2bfloat16_rn(f[j]));
+    }
+}
+
 template <int DT>
 __device__ __forceinline__ void store_row32(void* base, long long ld, int vec, int row, int col0, int ncols, const float (&f)[32],
                                             const int (&qi)[32])
@@ -306,7 +326,7 @@ __device__ __forceinline__ void store_row32(void* base, long long ld, int vec, i
 // other buffers; this buffer's previous group is older than those and has finished.
 template <int DT>
 __device__ __forceinline__ void stage_store32(const CUtensorMap* map, uint32_t smem, bool dual, int lane, int row_base, int col0,
-                                              const float (&f)[32], const int (&qi)[32])
+                                              const float (&f)[32], const int (&qi)[32], bool atomic = false)
 {
     static_assert(DT == OUT_F16 || DT == OUT_BF16 || DT == OUT_S8, "staged stores carry 1- and 2-byte outputs");
     if (lane == 0) {
@@ -333,7 +353,8 @@ __device__ __forceinline__ void stage_store32(const CUtensorMap* map, uint32_t s
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-        tma_store_2d(map, smem, col0, row_base);
+        if (atomic) tma_reduce_add_2d(map, smem, col0, row_base);  // the tensor map then carries the real element type
+        else tma_store_2d(map, smem, col0, row_base);
         bulk_commit_group();
     }
 }
@@ -470,13 +491,35 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
         if (acc != 12345.678f) return;
     }
 #endif
-    if constexpr (DT == OUT_F16 || DT == OUT_BF16 || DT == OUT_S8) {
-        if (st.map_c) {
-            stage_store32<DT>(st.map_c, st.smem_c, st.dual, threadIdx.x & 31, st.row_base, col0, f, qi);
-            return;
+    if constexpr (DT == OUT_E4M3 || DT == OUT_E5M2) {
+        // QF322FP8_PRE: the scaled value rounded to nearest even, saturating to the largest finite fp8; stored as bytes
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+            uint16_t pair;
+            if constexpr (DT == OUT_E4M3) asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(f[j + 1]), "f"(f[j]));
+            else asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(f[j + 1]), "f"(f[j]));
+            qi[j] = pair & 0xFF;
+            qi[j + 1] = pair >> 8;
         }
+        if (st.map_c) stage_store32<OUT_S8>(st.map_c, st.smem_c, st.dual, threadIdx.x & 31, st.row_base, col0, f, qi);
+        else if (row_ok) store_row32<OUT_S8>(e.c, e.ldc, e.vec_c, row, col0, ncols, f, qi);
+        return;
+    } else {
+        if constexpr (DT == OUT_F16 || DT == OUT_BF16 || DT == OUT_S8) {
+            if (st.map_c) {
+                stage_store32<DT>(st.map_c, st.smem_c, st.dual, threadIdx.x & 31, st.row_base, col0, f, qi, e.atomic != 0);
+                return;
+            }
+        }
+        if (!row_ok) return;
+        if constexpr (DT != OUT_S8) {
+            if (e.atomic) {
+                atomic_row32<DT>(e.c, e.ldc, row, col0, ncols, f, qi);
+                return;
+            }
+        }
+        store_row32<DT>(e.c, e.ldc, e.vec_c, row, col0, ncols, f, qi);
     }
-    if (row_ok) store_row32<DT>(e.c, e.ldc, e.vec_c, row, col0, ncols, f, qi);
 }
 
 // Drains this warp's share of one accumulator tile: TMEM lanes of `quad`, chunks [chunk0, chunk1).
@@ -491,8 +534,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
     st.row_base = t.row0 + quad * 32;
     // bulk stores clip at the matrix edge only: a group that ends inside this warp's rows is stored from registers
     const bool rows_mine = p.groups == 0 || st.row_base + 32 <= t.row_end;
-    constexpr int C_BYTES = DT == OUT_S8 ? 1024 : 2048;
-    const bool stage_c = (DT == OUT_F16 || DT == OUT_BF16 || DT == OUT_S8) && p.epi.tma_c && rows_mine && C_BYTES <= stage_bytes;
+    constexpr bool BYTE_OUT = DT == OUT_S8 || DT == OUT_E4M3 || DT == OUT_E5M2;
+    constexpr int C_BYTES = BYTE_OUT ? 1024 : 2048;
+    const bool stage_c = (DT == OUT_F16 || DT == OUT_BF16 || BYTE_OUT) && p.epi.tma_c && rows_mine && C_BYTES <= stage_bytes;
     const int c_used = stage_c ? C_BYTES : 0;
     const bool stage_c2 = !ACC_INT && p.epi.c2 && p.epi.tma_c2 && rows_mine && c_used + 2048 <= stage_bytes;
     st.map_c = stage_c ? &outs.c : nullptr;
@@ -544,6 +588,8 @@ __device__ __forceinline__ void epilogue_dispatch(const GemmParams& p, const Til
         ASCB200_EPI_CASE(ASCB200_EPI_FIXPIPE_QUANT, OUT_F16)
         ASCB200_EPI_CASE(ASCB200_EPI_FIXPIPE_QUANT, OUT_BF16)
         ASCB200_EPI_CASE(ASCB200_EPI_FIXPIPE_QUANT, OUT_F32)
+        ASCB200_EPI_CASE(ASCB200_EPI_FIXPIPE_QUANT, OUT_E4M3)
+        ASCB200_EPI_CASE(ASCB200_EPI_FIXPIPE_QUANT, OUT_E5M2)
     }
 #undef ASCB200_EPI_CASE
 }
@@ -1253,17 +1299,23 @@ int make_sf_map(CUtensorMap* map, const void* base, uint64_t chunks, uint32_t bo
     return r == CUDA_SUCCESS ? ASCB200_OK : ASCB200_ECUDA;
 }
 
+int out_bytes(int dt) { return (dt == OUT_S8 || dt == OUT_E4M3 || dt == OUT_E5M2) ? 1 : (dt == OUT_F16 || dt == OUT_BF16) ? 2 : 4; }
+
 // rank-2 map over an output [rows][cols] of 1- or 2-byte elements, box 32 x 32, swizzle = bytes of one box row.
 // Returns false when the tensor cannot be described (alignment): the kernel then stores from registers.
-bool make_out_map(CUtensorMap* map, int esz, const void* base, uint64_t cols, uint64_t rows, uint64_t ld_elems)
+bool make_out_map(CUtensorMap* map, int dtype, const void* base, uint64_t cols, uint64_t rows, uint64_t ld_elems)
 {
+    const int esz = out_bytes(dtype);
+    // plain stores move bits; a reducing store (atomic add) needs the arithmetic type
+    const CUtensorMapDataType mdt = dtype == OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : dtype == OUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                                                           : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     EncodeTiledFn fn = encode_fn();
     if (!fn || (esz != 1 && esz != 2) || !aligned_to(base, 16) || (ld_elems * esz) % 16 != 0 || cols == 0 || rows == 0) return false;
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {ld_elems * esz};
     cuuint32_t box[2] = {32, 32};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+    CUresult r = fn(map, mdt, 2, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, esz == 1 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
@@ -1303,7 +1355,6 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
 }
 
 int elem_bits(int kind) { return kind == ASCB200_KIND_MXFP4 ? 4 : kind == ASCB200_KIND_S8 ? 8 : 16; }
-int out_bytes(int dt) { return dt == OUT_S8 ? 1 : (dt == OUT_F16 || dt == OUT_BF16) ? 2 : 4; }
 
 // Device resources of one call when they do not come from the per-device state of ascb200_init.
 struct FixedResources {
@@ -1322,7 +1373,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     if (d->m < 0 || d->n < 0 || d->k < 0) return ASCB200_EINVAL;
     if (d->m == 0 || d->n == 0) return ASCB200_OK;
     if (!d->a_dev || !d->b_dev || !d->c_dev || d->k == 0) return ASCB200_EINVAL;
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 3; ++i)
         if (d->reserved[i] != 0) return ASCB200_EINVAL;
     const int kind = d->kind;
     if (kind < ASCB200_KIND_F16 || kind > ASCB200_KIND_MXFP4) return ASCB200_EINVAL;
@@ -1351,7 +1402,8 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
             break;
         case ASCB200_EPI_FIXPIPE_QUANT:
             if (acc_int ? !(d->c_dtype == OUT_F16 || d->c_dtype == OUT_S8 || d->c_dtype == OUT_BF16)
-                        : !(d->c_dtype == OUT_S8 || d->c_dtype == OUT_F16 || d->c_dtype == OUT_BF16 || d->c_dtype == OUT_F32))
+                        : !(d->c_dtype == OUT_S8 || d->c_dtype == OUT_F16 || d->c_dtype == OUT_BF16 || d->c_dtype == OUT_F32 || d->c_dtype == OUT_E4M3 ||
+                            d->c_dtype == OUT_E5M2))
                 return ASCB200_EUNSUPPORTED;
             break;
         case ASCB200_EPI_DEQUANT_TOKEN_CHANNEL:
@@ -1374,8 +1426,12 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     OutMaps outs;
     std::memset(&outs, 0, sizeof(outs));
     const bool no_tma_store = getenv("ASCB200_NO_TMA_STORE") && getenv("ASCB200_NO_TMA_STORE")[0] == '1';
-    e.tma_c = !no_tma_store && make_out_map(&outs.c, out_bytes(e.c_dtype), e.c, d->n, d->m, e.ldc);
-    e.tma_c2 = !no_tma_store && e.c2 && make_out_map(&outs.c2, out_bytes(e.c2_dtype), e.c2, d->n, d->m, e.ldc2);
+    e.tma_c = !no_tma_store && make_out_map(&outs.c, e.c_dtype, e.c, d->n, d->m, e.ldc);
+    e.tma_c2 = !no_tma_store && e.c2 && make_out_map(&outs.c2, e.c2_dtype, e.c2, d->n, d->m, e.ldc2);
+    e.atomic = d->atomic;
+    if (d->atomic != 0 && d->atomic != 1) return ASCB200_EUNSUPPORTED;                       // add only (enAtomic = 1)
+    if (d->atomic && out_bytes(e.c_dtype) == 1) return ASCB200_EUNSUPPORTED;                 // no 8-bit atomics
+    if (d->atomic && out_bytes(e.c_dtype) == 2 && (reinterpret_cast<uintptr_t>(e.c) & 1)) return ASCB200_EALIGN;
 
     // ---- operands ----
     const int bits = elem_bits(kind);

@@ -100,6 +100,8 @@ struct bfloat16_t {
 struct fp4x2_e2m1_t { uint8_t bits = 0; };  // two e2m1 values, even index in the low nibble
 struct fp4x2_e1m2_t { uint8_t bits = 0; };  // declared for completeness; B200 tensor cores have no e1m2 path
 struct fp8_e8m0_t { uint8_t bits = 0; };    // 2^(bits-127)
+struct fp8_e4m3fn_t { uint8_t bits = 0; };  // Matmul output of the QF322FP8_PRE fixpipe mode (no infinities, largest finite 448)
+struct fp8_e5m2_t { uint8_t bits = 0; };    // largest finite 57344
 
 // include/adv_api/matmul/matmul_config.h:26-37
 enum class CubeFormat { ND = 0, NZ, ZN, ZZ, NN, ND_ALIGN, SCALAR, VECTOR, ROW_MAJOR = ND, COLUMN_MAJOR = 8 };
@@ -137,6 +139,8 @@ template <> struct DTypeOf<bfloat16_t> { static constexpr int value = ASCB200_BF
 template <> struct DTypeOf<int8_t> { static constexpr int value = ASCB200_S8; };
 template <> struct DTypeOf<int32_t> { static constexpr int value = ASCB200_S32; };
 template <> struct DTypeOf<fp4x2_e2m1_t> { static constexpr int value = ASCB200_FP4_E2M1; };
+template <> struct DTypeOf<fp8_e4m3fn_t> { static constexpr int value = ASCB200_FP8_E4M3; };
+template <> struct DTypeOf<fp8_e5m2_t> { static constexpr int value = ASCB200_FP8_E5M2; };
 
 // First failing C-ABI code of the calling thread's operator calls (kernel-side APIs return void).
 inline int& LastError()

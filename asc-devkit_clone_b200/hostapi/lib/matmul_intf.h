@@ -60,10 +60,16 @@ public:
     using DstT = typename C_TYPE::T;
     using BiasT = typename BIAS_TYPE::T;
     static_assert(std::is_same<SrcAT, SrcBT>::value, "A and B must have the same element type");
-    static_assert(A_TYPE::format == CubeFormat::ND && B_TYPE::format == CubeFormat::ND && C_TYPE::format == CubeFormat::ND,
-                  "only ND (row-major) operands are implemented; use isTrans for the other orientation");
+    static_assert(A_TYPE::format == CubeFormat::ND, "A must be ND (row-major); use isTrans for the other orientation");
+    static_assert(B_TYPE::format == CubeFormat::ND || B_TYPE::format == CubeFormat::NZ, "B must be ND or the fractal NZ format");
+    static_assert(C_TYPE::format == CubeFormat::ND || C_TYPE::format == CubeFormat::ND_ALIGN, "C must be ND or ND_ALIGN");
+    static_assert(B_TYPE::format != CubeFormat::NZ || sizeof(SrcBT) <= 2, "NZ unpacking covers 1- and 2-byte elements");
     static constexpr bool isMx = std::is_same<SrcAT, fp4x2_e2m1_t>::value;
     static constexpr int elemsPerStorage = isMx ? 2 : 1;  // GlobalTensor offsets count storage units (bytes for packed fp4)
+
+    Matmul() = default;
+    Matmul(const Matmul&) = delete;  // the object may own the unpacked copy of an NZ operand
+    Matmul& operator=(const Matmul&) = delete;
 
     void Init(const TCubeTiling* cubeTiling, TPipe* tpipe = nullptr)
     {
@@ -111,6 +117,7 @@ public:
     }
     void SetTensorB(const GlobalTensor<SrcBT>& gm, bool isTransposeB = false)
     {
+        if (b_ != gm.GetPhyAddr()) unpackedFor_ = nullptr;  // another NZ tensor: unpack again
         b_ = gm.GetPhyAddr();
         transB_ = isTransposeB;
     }
@@ -150,8 +157,8 @@ public:
     {
         (void)waitIterateAll;
         (void)fakeMsg;
-        if (enAtomic != 0 || enSequentialWrite) {
-            AscendC::detail::Latch(ASCB200_EUNSUPPORTED, "Matmul::IterateAll (enAtomic / enSequentialWrite)");
+        if (enAtomic > 1 || enSequentialWrite) {  // 1 = add; max / min (2, 3) and block-sequential output are not implemented
+            AscendC::detail::Latch(ASCB200_EUNSUPPORTED, "Matmul::IterateAll (enAtomic max/min, enSequentialWrite)");
             return;
         }
         ascb200_gemm_desc d;
@@ -166,11 +173,48 @@ public:
         d.trans_b = transB_ ? 1 : 0;
         d.lda = transA_ ? orgM_ : orgKa_;
         d.ldb = transB_ ? orgKb_ : orgN_;
+        if constexpr (B_TYPE::format == CubeFormat::NZ) {
+            // A fractal B ([N/C0][Kb/16][16][C0] over the original shape) is unpacked once per tensor into a K-major copy
+            // that the object owns; End() releases it.  Sub-blocks of an NZ tensor are not addressable by element offset.
+            if (transB_ || singleN_ != orgN_ || singleK_ != orgKb_) {
+                AscendC::detail::Latch(ASCB200_EUNSUPPORTED, "Matmul::IterateAll (NZ B: whole, untransposed tensor only)");
+                return;
+            }
+            if (unpackedFor_ != b_) {
+                const size_t bytes = static_cast<size_t>(orgN_) * orgKb_ * sizeof(SrcBT);
+                if (bytes > unpackedBytes_) {
+                    if (unpacked_) (void)ascb200_free(unpacked_);
+                    unpacked_ = nullptr;
+                    unpackedBytes_ = 0;
+                    const int rc = ascb200_malloc(&unpacked_, bytes);
+                    if (rc != ASCB200_OK) {
+                        AscendC::detail::Latch(rc, "Matmul::IterateAll (NZ B buffer)");
+                        return;
+                    }
+                    unpackedBytes_ = bytes;
+                }
+                const int rc = ascb200_nz_unpack(b_, unpacked_, 1, orgKb_, orgN_, static_cast<int32_t>(sizeof(SrcBT)), 1, stream_);
+                if (rc != ASCB200_OK) {
+                    AscendC::detail::Latch(rc, "Matmul::IterateAll (NZ B unpack)");
+                    return;
+                }
+                unpackedFor_ = b_;
+            }
+            d.b_dev = unpacked_;
+            d.trans_b = 1;
+            d.ldb = orgKb_;
+        }
+        d.atomic = enAtomic;
         d.scale_a_dev = scaleA_;
         d.scale_b_dev = scaleB_;
         d.bias_dev = (biasOn_ && MM_CFG.enableSetBias) ? bias_ : nullptr;
         d.c_dev = gm.GetPhyAddr();
         d.ldc = orgKc_ > 0 ? orgKc_ : orgN_;
+        if constexpr (C_TYPE::format == CubeFormat::ND_ALIGN) {
+            // ND with every row padded to a multiple of 32 bytes
+            constexpr int perBlock = 32 / static_cast<int>(sizeof(DstT));
+            d.ldc = (d.ldc + perBlock - 1) / perBlock * perBlock;
+        }
         d.c_dtype = AscendC::detail::DTypeOf<DstT>::value;
         d.relu = MM_CFG.enableRelu ? 1 : 0;
         if (quantSet_) {
@@ -207,7 +251,17 @@ public:
     {
         if (iterPending_) IterateAll<sync>(gm, enAtomic, enSequentialWrite);
     }
-    void End() {}
+    void End()
+    {
+        if (unpacked_) {
+            (void)ascb200_stream_sync(stream_);
+            (void)ascb200_free(unpacked_);
+        }
+        unpacked_ = nullptr;
+        unpackedBytes_ = 0;
+        unpackedFor_ = nullptr;
+    }
+    ~Matmul() { End(); }
     void SetLocalWorkspace(const LocalTensor<uint8_t>&) {}
     int GetLastError() const { return AscendC::GetLastError(); }
 
@@ -216,6 +270,9 @@ private:
     void* stream_ = nullptr;
     const SrcAT* a_ = nullptr;
     const SrcBT* b_ = nullptr;
+    void* unpacked_ = nullptr;           // K-major copy of an NZ-format B
+    size_t unpackedBytes_ = 0;
+    const SrcBT* unpackedFor_ = nullptr;
     const fp8_e8m0_t* scaleA_ = nullptr;
     const fp8_e8m0_t* scaleB_ = nullptr;
     const BiasT* bias_ = nullptr;

@@ -46,7 +46,9 @@ enum {
     ASCB200_BF16 = 2,
     ASCB200_S8 = 3,
     ASCB200_S32 = 4,
-    ASCB200_FP4_E2M1 = 5      /* two values per byte, even index in the low nibble */
+    ASCB200_FP4_E2M1 = 5,     /* two values per byte, even index in the low nibble */
+    ASCB200_FP8_E4M3 = 6,     /* e4m3fn: no infinities, largest finite 448 (output of the QF322FP8_PRE fixpipe mode) */
+    ASCB200_FP8_E5M2 = 7      /* e5m2: largest finite 57344 */
 };
 
 /* ---- library / device ---------------------------------------------------------------------- */
@@ -122,7 +124,7 @@ typedef struct ascb200_gemm_desc {
     const void* bias_dev;    /* NULL or [n]: fp32 for fp32 accumulators, int32 for int32 accumulators */
     void* c_dev;             /* [m,n] row-major, leading dimension ldc (0 = n) */
     int64_t ldc;
-    int32_t c_dtype;         /* ASCB200_F32 / F16 / BF16 / S8 / S32 */
+    int32_t c_dtype;         /* ASCB200_F32 / F16 / BF16 / S8 / S32; FP8_E4M3 / FP8_E5M2 with FIXPIPE_QUANT on fp32 accumulators */
     void* c2_dev;            /* optional second output: the fp32 accumulator cast to c2_dtype (F16/BF16/F32) */
     int64_t ldc2;
     int32_t c2_dtype;
@@ -133,7 +135,8 @@ typedef struct ascb200_gemm_desc {
     const float* ch_scale_dev;  /* DEQUANT_TOKEN_CHANNEL: [n] */
     int32_t relu;            /* enableRelu of the fixpipe stage */
     int32_t act;             /* 0 none, 1 FasterGelu (DEQUANT_TOKEN_CHANNEL only) */
-    int32_t reserved[4];     /* must be zero */
+    int32_t atomic;          /* 0: C is overwritten; 1: C += result (enAtomic = 1 of IterateAll / GetTensorC); F32, S32, F16, BF16 outputs */
+    int32_t reserved[3];     /* must be zero */
 } ascb200_gemm_desc;
 
 /* One whole Matmul: what Matmul<...>::IterateAll produces for the object state set by
@@ -180,6 +183,14 @@ ASCB200_API int ascb200_grouped_gemm(const ascb200_gemm_desc* desc, const int64_
 ASCB200_API int ascb200_gemm_mxfp4_noalloc(const ascb200_gemm_desc* desc, void* stream);
 
 /* ---- SoftMax ------------------------------------------------------------------------------------ */
+
+/* Unpacks a fractal ("NZ") matrix [groups][n/C0][k/16][16][C0], C0 = 32 / elem_bytes columns per block (the format
+ * CubeFormat::NZ of include/adv_api/matmul/matmul_config.h:26-37; the grouped matmul example stores its int8 weights so:
+ * examples/.../quant_group_matmul_high_performance/scripts/gen_data.py:62), into row-major [groups][n][k] (to_nk = 1, the K-major
+ * layout of trans_b = 1) or [groups][k][n] (to_nk = 0).  k must be a multiple of 16, n of C0; elem_bytes 1 or 2.  Replaces the
+ * reference's on-the-fly NZ loads (impl/adv_api/detail/matmul/stage/copy_cube_in): weights are static, they are unpacked once. */
+ASCB200_API int ascb200_nz_unpack(const void* src_nz_dev, void* dst_dev, int32_t groups, int32_t k, int32_t n, int32_t elem_bytes,
+                                  int32_t to_nk, void* stream);
 
 /* SoftMax<T>(dst, sum, max, src, tiling, shapeInfo) over the last axis of src[m,k]
  * (include/adv_api/activation/softmax.h:92-109,229-247).  dtype F16 or F32; k*sizeof(T) must be a

@@ -299,6 +299,56 @@ ORC_API void orc_fixpipe_qf322b8(const float* acc, int8_t* out, int M, int N, co
         }
 }
 
+/* fp32 -> fp8 (e4m3fn: 4 exponent bits, bias 7, no infinities, largest finite 448; e5m2: 5 exponent bits, bias 15, largest
+ * finite 57344), round to nearest even, saturating to the largest finite value, NaN -> 0x7F (e4m3) / 0x7F (e5m2 quiet NaN).
+ * Format definitions: OCP 8-bit floating point specification; the reference only names the mode (QF322FP8_PRE,
+ * impl/adv_api/detail/matmul/stage/copy_cube_out/quant/quant_processor_fixpipe.h:103-104), its arithmetic lives in the closed
+ * CPU twin, so saturation instead of overflow-to-NaN is this build's choice (the same as the GPU's cvt.rn.satfinite). */
+ORC_API uint8_t orc_f32_to_fp8(float x, int e5m2)
+{
+    const int mbits = e5m2 ? 2 : 3, bias = e5m2 ? 15 : 7;
+    const float maxv = e5m2 ? 57344.0f : 448.0f;
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    const uint8_t sign = (uint8_t)((u >> 24) & 0x80u);
+    if (x != x) return (uint8_t)(sign | 0x7Fu);
+    float a = fabsf(x);
+    if (a >= maxv) a = maxv;  /* saturate (also infinities) */
+    /* quantum of the binade: 2^(e - mbits), subnormals share the quantum of the smallest normal binade */
+    int e;
+    frexpf(a, &e);            /* a = f * 2^e, f in [0.5, 1) -> unbiased exponent e - 1 */
+    int ue = e - 1;
+    if (a == 0.0f || ue < 1 - bias) ue = 1 - bias;
+    const float q = ldexpf(1.0f, ue - mbits);
+    float r = nearbyintf(a / q) * q;  /* exact: division by a power of two; ties to even */
+    if (r > maxv) r = maxv;
+    if (r == 0.0f) return sign;
+    int re;
+    const float rf = frexpf(r, &re);
+    int rue = re - 1;
+    uint32_t bits;
+    if (rue < 1 - bias) {  /* subnormal */
+        bits = (uint32_t)nearbyintf(r / ldexpf(1.0f, 1 - bias - mbits));
+    } else {
+        const uint32_t man = (uint32_t)nearbyintf((rf * 2.0f - 1.0f) * (float)(1 << mbits));
+        bits = ((uint32_t)(rue + bias) << mbits) | man;
+    }
+    return (uint8_t)(sign | bits);
+}
+
+/* QF322FP8_PRE / VQF322FP8_PRE (950 only): fp32 -> fp8 = fp8_sat(x * alpha), ReLU first when enabled. */
+ORC_API void orc_fixpipe_qf322fp8(const float* acc, uint8_t* out, int M, int N, const uint64_t* q, int per_channel, int relu, int e5m2)
+{
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            uint64_t p = q[per_channel ? n : 0];
+            float f = acc[(size_t)m * N + n];
+            f = (f >= 0.0f || !relu) ? f * orc_quant_alpha(p) : 0.0f;
+            out[(size_t)m * N + n] = orc_f32_to_fp8(f, e5m2);
+        }
+}
+
 /* DEQF16 / VDEQF16: int32 -> half = half_sat(float(x) * alpha) (gen_data_s322f16.py:66-83). */
 ORC_API void orc_fixpipe_deqf16(const int32_t* acc, uint16_t* out, int M, int N, const uint64_t* q, int per_channel, int relu)
 {

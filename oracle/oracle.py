@@ -102,6 +102,29 @@ def fixpipe_qf322b8(acc, q, relu=False):
     return _fix("orc_fixpipe_qf322b8", acc, np.float32, np.int8, q, relu)
 
 
+def fixpipe_qf322fp8(acc, q, relu=False, e5m2=False):
+    acc = _c(acc, np.float32)
+    q = _c(np.atleast_1d(q), np.uint64)
+    M, N = acc.shape
+    out = np.empty((M, N), np.uint8)
+    lib().orc_fixpipe_qf322fp8(_p(acc), _p(out), M, N, _p(q), int(q.size > 1), int(relu), int(e5m2))
+    return out
+
+
+def f32_to_fp8(x, e5m2=False):
+    fn = lib().orc_f32_to_fp8
+    fn.argtypes = [C.c_float, C.c_int]
+    fn.restype = C.c_uint8
+    return np.array([fn(float(v), int(e5m2)) for v in np.asarray(x, np.float32).ravel()], np.uint8).reshape(np.shape(x))
+
+
+def nz_pack(w, c0):
+    """[G, K, N] -> fractal NZ [G, N/c0, K/16, 16, c0] exactly as the grouped example stores its weights
+    (quant_group_matmul_high_performance/scripts/gen_data.py:62)."""
+    G, K, N = w.shape
+    return np.ascontiguousarray(w.reshape(G, K // 16, 16, N // c0, c0).transpose(0, 3, 1, 2, 4))
+
+
 def fixpipe_deqf16(acc, q, relu=False):
     return _fix("orc_fixpipe_deqf16", acc, np.int32, np.uint16, q, relu)
 

@@ -283,6 +283,94 @@ static void TestSoftmaxQuantDequant()
     CHECK(badd == 0, "AscendDequant: %d mismatches", badd);
 }
 
+// B in the fractal NZ format of the grouped example's weights, result added into C (enAtomic = 1), and an
+// ND_ALIGN output whose rows are padded to 32 bytes.
+static void TestMatmulNzAtomicAlign()
+{
+    using namespace AscendC;
+    const int M = 200, N = 96, K = 160;
+    std::mt19937 rng(7);
+    std::uniform_int_distribution<int> u(-10, 9);
+    std::vector<int8_t> a(M * K), b(K * N), bNz(K * N);
+    for (auto& v : a) v = static_cast<int8_t>(u(rng));
+    for (auto& v : b) v = static_cast<int8_t>(u(rng));
+    for (int k = 0; k < K; ++k)
+        for (int n = 0; n < N; ++n) bNz[((static_cast<size_t>(n / 32) * (K / 16) + k / 16) * 16 + k % 16) * 32 + n % 32] = b[k * N + n];
+    std::vector<int32_t> c0(M * N);
+    for (auto& v : c0) v = u(rng) * 100;
+    DevBuf<int8_t> dA(a), dB(bNz);
+    DevBuf<int32_t> dC(c0);
+    TCubeTiling tiling{};
+    tiling.M = tiling.singleCoreM = M;
+    tiling.N = tiling.singleCoreN = N;
+    tiling.Ka = tiling.Kb = tiling.singleCoreK = K;
+    {
+        TPipe pipe;
+        Matmul<MatmulType<TPosition::GM, CubeFormat::ND, int8_t>, MatmulType<TPosition::GM, CubeFormat::NZ, int8_t>,
+               MatmulType<TPosition::GM, CubeFormat::ND, int32_t>, MatmulType<TPosition::GM, CubeFormat::ND, int32_t>>
+            mm;
+        REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, &tiling);
+        GlobalTensor<int8_t> ga, gb;
+        GlobalTensor<int32_t> gc;
+        ga.SetGlobalBuffer(dA.p, a.size());
+        gb.SetGlobalBuffer(dB.p, bNz.size());
+        gc.SetGlobalBuffer(dC.p, c0.size());
+        mm.SetTensorA(ga);
+        mm.SetTensorB(gb);
+        mm.IterateAll(gc, 1);
+        mm.IterateAll(gc, 1);  // second call reuses the unpacked copy
+        mm.End();
+    }
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<int32_t> c = dC.Download();
+    int bad = 0;
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            int32_t acc = 0;
+            for (int k = 0; k < K; ++k) acc += static_cast<int32_t>(a[m * K + k]) * b[k * N + n];
+            if (c[m * N + n] != c0[m * N + n] + 2 * acc) ++bad;
+        }
+    CHECK(bad == 0, "NZ B + atomic add: %d wrong", bad);
+
+    const int N2 = 520, LD = 528;  // 520 halves = 1040 bytes -> padded to 1056
+    std::vector<half> ah(M * K), bh(K * N2);
+    std::uniform_real_distribution<float> uf(-1.f, 1.f);
+    for (auto& v : ah) v = half(uf(rng));
+    for (auto& v : bh) v = half(uf(rng));
+    std::vector<half> cInit(static_cast<size_t>(M) * LD, half(-77.0f));
+    DevBuf<half> dAh(ah), dBh(bh), dCh(cInit);
+    tiling.N = tiling.singleCoreN = N2;
+    {
+        TPipe pipe;
+        Matmul<MatmulType<TPosition::GM, CubeFormat::ND, half>, MatmulType<TPosition::GM, CubeFormat::ND, half>,
+               MatmulType<TPosition::GM, CubeFormat::ND_ALIGN, half>, MatmulType<TPosition::GM, CubeFormat::ND, float>>
+            mm;
+        REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, &tiling);
+        GlobalTensor<half> ga, gb, gc;
+        ga.SetGlobalBuffer(dAh.p, ah.size());
+        gb.SetGlobalBuffer(dBh.p, bh.size());
+        gc.SetGlobalBuffer(dCh.p, cInit.size());
+        mm.SetTensorA(ga);
+        mm.SetTensorB(gb);
+        mm.IterateAll(gc);
+        mm.End();
+    }
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<half> ch = dCh.Download();
+    bad = 0;
+    for (int m = 0; m < M; m += 3) {
+        for (int n = 0; n < N2; n += 7) {
+            float acc = 0;
+            for (int k = 0; k < K; ++k) acc += static_cast<float>(ah[m * K + k]) * static_cast<float>(bh[k * N2 + n]);
+            if (std::fabs(static_cast<float>(ch[static_cast<size_t>(m) * LD + n]) - acc) > 1e-3 + 1e-2 * std::fabs(acc)) ++bad;
+        }
+        for (int n = N2; n < LD; ++n)
+            if (static_cast<float>(ch[static_cast<size_t>(m) * LD + n]) != -77.0f) ++bad;  // padding stays untouched
+    }
+    CHECK(bad == 0, "ND_ALIGN output: %d wrong", bad);
+    std::printf("matmul NZ B + enAtomic, ND_ALIGN C: ok\n");
+}
+
 static void TestErrorLatch()
 {
     AscendC::ClearLastError();
@@ -305,6 +393,7 @@ int main()
     TestMatmulFp16();
     TestMatmulQuant();
     TestSoftmaxQuantDequant();
+    TestMatmulNzAtomicAlign();
     TestErrorLatch();
     std::printf(g_fail ? "%d checks failed\n" : "hostapi ok\n", g_fail);
     return g_fail ? 1 : 0;

@@ -34,3 +34,12 @@ def test_no_cpu_fallback_without_device():
     assert lib.ascb200_gemm(C.byref(d), None) == -4
     assert lib.ascb200_dequant(None, None, 1, 8, 8, 8, ab.F32, None, ab.F32, C.c_float(1.0), None) == -4
     assert b"sm_100" in lib.ascb200_strerror(-4)
+
+
+def test_binding_declares_argument_types_for_every_export():
+    """ctypes passes an untyped Python int as a 32-bit C int: an entry point without argtypes would receive truncated
+    device pointers.  Every export that takes arguments must have them declared."""
+    lib = ab.lib()
+    no_args = {"ascb200_last_cuda_error", "ascb200_sm_count"}
+    untyped = [n for n in ab.EXPORTS if n not in no_args and getattr(lib, n).argtypes is None]
+    assert not untyped, untyped

@@ -314,3 +314,119 @@ def test_gemm_argument_errors():
     assert ab.gemm(ab.KIND_MXFP4, 128, 128, 96, buf, buf, out, ab.F32, trans_b=True, scale_a=buf, scale_b=buf) == -1  # K % 64
     assert ab.gemm(ab.KIND_F16, 0, 128, 128, buf, buf, out, ab.F32) == 0                  # empty problem
     assert ab.gemm(7, 128, 128, 128, buf, buf, out, ab.F32) == -1
+
+
+@pytest.mark.parametrize("e5m2", [False, True])
+def test_gemm_f16_fixpipe_fp8_output(e5m2):
+    """QF322FP8_PRE: fp32 accumulator x per-channel scale -> fp8 (round to nearest even, saturating)."""
+    ab = dev()
+    m, n, k = 300, 416, 256
+    rng = np.random.default_rng(77 + e5m2)
+    a = f16_bits(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+    b = f16_bits(rng.uniform(-1, 1, (n, k)).astype(np.float32))
+    q = quant_params(rng.uniform(0.5, 60.0, n).astype(np.float32), np.zeros(n, np.int64))
+    d_c = ab.empty((m, n), np.uint8)
+    ab.check(ab.gemm(ab.KIND_F16, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.FP8_E5M2 if e5m2 else ab.FP8_E4M3, epilogue=ab.EPI_FIXPIPE_QUANT,
+                     trans_b=True, quant=ab.to_dev(q)))
+    ab.sync()
+    acc = orc.gemm_f16(a, b, None, trans_b=True, base_k=64)
+    ref = orc.fixpipe_qf322fp8(acc, q, e5m2=e5m2)
+    got = d_c.download()
+    # the two accumulations differ in the last fp32 bits, which can move a value across an fp8 rounding boundary
+    diff = got != ref
+    assert diff.mean() < 2e-3, f"{diff.sum()} of {diff.size} differ"
+    step = np.abs(got[diff].astype(np.int16) - ref[diff].astype(np.int16))
+    assert (step <= 1).all()
+    if not e5m2:
+        assert ((ref & 0x7F) == 0x7E).any(), "the e4m3 case must reach saturation (448)"
+
+
+def test_gemm_mxfp4_fp8_output():
+    ab = dev()
+    m, n, k = 256, 384, 512
+    rng, a, sa, b, sb = _mx_case(m, n, k, 99)
+    q = quant_params(rng.uniform(0.05, 0.5, n).astype(np.float32), np.zeros(n, np.int64))
+    d_c = ab.empty((m, n), np.uint8)
+    ab.check(ab.gemm(ab.KIND_MXFP4, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.FP8_E4M3, epilogue=ab.EPI_FIXPIPE_QUANT, trans_b=True,
+                     scale_a=ab.to_dev(sa), scale_b=ab.to_dev(sb), quant=ab.to_dev(q)))
+    ab.sync()
+    ref = orc.fixpipe_qf322fp8(orc.gemm_mxf4(a, sa, b, sb, base_k=256), q)
+    got = d_c.download()
+    diff = got != ref
+    assert diff.mean() < 5e-3 and (np.abs(got[diff].astype(np.int16) - ref[diff].astype(np.int16)) <= 1).all()
+
+
+@pytest.mark.parametrize("c_dtype", [0, 1, 2])
+def test_gemm_f16_atomic_add(c_dtype):
+    """enAtomic = 1: the result is added into C (bulk reducing stores for fp16 / bf16, reductions per element for fp32)."""
+    ab = dev()
+    m, n, k = 200, 328, 128   # ragged: edge chunks take the per-element path
+    rng = np.random.default_rng(3 + c_dtype)
+    a = f16_bits(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+    b = f16_bits(rng.uniform(-1, 1, (n, k)).astype(np.float32))
+    base = rng.integers(-8, 8, (m, n)).astype(np.float32)  # exactly representable in every output type
+    c0 = base if c_dtype == 0 else (f16_bits(base) if c_dtype == 1 else bf16_bits(base))
+    d_c = ab.to_dev(c0)
+    ab.check(ab.gemm(ab.KIND_F16, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, c_dtype, trans_b=True, atomic=1))
+    ab.sync()
+    got = out_to_f32(d_c.download().reshape(m, n), c_dtype)
+    acc = orc.gemm_f16(a, b, None, trans_b=True, base_k=64)
+    part = out_to_f32(orc.cast_f32(acc, c_dtype), c_dtype)          # the value that is added, in the output type
+    ref = out_to_f32(orc.cast_f32(base + part, c_dtype), c_dtype)   # one rounding of the sum
+    tol = 1e-5 if c_dtype == 0 else (2e-2 if c_dtype == 1 else 0.13)
+    assert np.abs(got - ref).max() <= tol * max(1.0, np.abs(ref).max())
+
+
+def test_gemm_i8_atomic_add_int32_exact():
+    ab = dev()
+    m, n, k = 256, 320, 256
+    rng, a, b = _i8_inputs(m, n, k, False, True, 8)
+    base = rng.integers(-1000, 1000, (m, n)).astype(np.int32)
+    d_c = ab.to_dev(base)
+    for _ in range(2):
+        ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.S32, trans_b=True, atomic=1))
+    ab.sync()
+    assert (d_c.download().reshape(m, n) == base + 2 * orc.gemm_i8(a, b, trans_b=True)).all()
+
+
+def test_gemm_atomic_rejects_int8_output():
+    ab = dev()
+    a = ab.to_dev(np.zeros((128, 128), np.int8))
+    c = ab.empty((128, 128), np.int8)
+    assert ab.gemm(ab.KIND_S8, 128, 128, 128, a, a, c, ab.S8, epilogue=ab.EPI_FIXPIPE_QUANT, trans_b=True, quant_scalar=0x3F800000, atomic=1) == ab.EUNSUPPORTED
+
+
+@pytest.mark.parametrize("esz,to_nk", [(1, True), (1, False), (2, True), (2, False)])
+def test_nz_unpack(esz, to_nk):
+    """Fractal NZ weights as the grouped example writes them -> row-major [G,N,K] or [G,K,N], bit exact."""
+    ab = dev()
+    G, k, n = 3, 304, 192
+    c0 = 32 // esz
+    rng = np.random.default_rng(esz * 2 + to_nk)
+    w = rng.integers(-128, 128, (G, k, n)).astype(np.int8) if esz == 1 else rng.integers(0, 65536, (G, k, n)).astype(np.uint16)
+    nz = orc.nz_pack(w, c0)
+    d_out = ab.empty((G, n, k) if to_nk else (G, k, n), w.dtype)
+    d_out.fill(0x5A)
+    ab.check(ab.nz_unpack(ab.to_dev(nz), d_out, G, k, n, esz, to_nk))
+    ab.sync()
+    got = d_out.download().reshape((G, n, k) if to_nk else (G, k, n))
+    assert (got == (w.transpose(0, 2, 1) if to_nk else w)).all()
+
+
+def test_grouped_reference_recipe_nz_weights(golden_dir):
+    """The grouped example end to end with its NZ-stored weights: unpack once, then the grouped kernel on K-major weights."""
+    import os
+    ab = dev()
+    g = np.load(os.path.join(golden_dir, "grouped.npz"))
+    x, w, counts = g["x"], g["w"], g["counts"]
+    m, k = x.shape
+    G, _, n = w.shape
+    d_w = ab.empty((G, n, k), np.int8)
+    ab.check(ab.nz_unpack(ab.to_dev(orc.nz_pack(w, 32)), d_w, G, k, n, 1, True))
+    d_c = ab.empty((m, n), np.uint16)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(x), d_w, d_c, ab.F16, epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, trans_b=True,
+                     tok=ab.to_dev(g["tok"]), ch=ab.to_dev(g["scale"]), group_counts=ab.to_dev(counts), groups=G, act=1))
+    ab.sync()
+    got = orc.f16_bits_to_f32(d_c.download())
+    ok = np.isclose(got, g["golden_gelu"].astype(np.float32), rtol=1e-3, atol=1e-3)
+    assert (~ok).mean() <= 1e-4  # the example's acceptance rule (verify_result.py:19-41)

@@ -132,3 +132,16 @@ def test_mxfp4_recipe(golden_dir):
     assert (bf != g["golden_bf16_bits"]).mean() < 1e-3  # float64 golden rounded straight to bf16
     c64 = orc.gemm_mxf4(g["a"], g["sa"], g["b"], g["sb"], base_k=64)
     assert np.abs(c64 - c).max() <= 1e-6 * np.abs(c).max()  # chunking only reorders fp32 additions
+
+
+def test_fp8_conversion_matches_ml_dtypes():
+    """The oracle's fp32 -> fp8 (round to nearest even) against ml_dtypes for finite in-range values, plus the saturation rule."""
+    ml_dtypes = pytest.importorskip("ml_dtypes")
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(4000).astype(np.float32) * s for s in (1e-3, 1e-2, 0.1, 1, 10, 100)] +
+                       [np.array([0, -0.0, 448, -448, 447.9, 1.0, 2.0**-9, 2.0**-10, 2.0**-6, 3 * 2.0**-10, 57344, 61000], np.float32)])
+    for e5m2, dt, mx in ((False, ml_dtypes.float8_e4m3fn, 448.0), (True, ml_dtypes.float8_e5m2, 57344.0)):
+        xs = x[np.abs(x) <= mx]
+        assert (orc.f32_to_fp8(xs, e5m2) == xs.astype(dt).view(np.uint8)).all()
+        top = 0x7B if e5m2 else 0x7E
+        assert orc.f32_to_fp8(np.array([1e9, -1e9, np.inf], np.float32), e5m2).tolist() == [top, top | 0x80, top]
