@@ -22,7 +22,7 @@ EXPORTS = [
     "ascb200_memset", "ascb200_stream_create", "ascb200_stream_destroy", "ascb200_stream_sync", "ascb200_event_create",
     "ascb200_event_destroy", "ascb200_event_record", "ascb200_stream_wait_event", "ascb200_event_elapsed_ms", "ascb200_gemm", "ascb200_grouped_gemm",
     "ascb200_gemm_mxfp4_noalloc", "ascb200_graph_begin", "ascb200_graph_end", "ascb200_graph_launch", "ascb200_graph_destroy",
-    "ascb200_nz_unpack", "ascb200_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
+    "ascb200_nz_unpack", "ascb200_quant_policy", "ascb200_dequant_policy", "ascb200_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
 ]
 
 
@@ -87,6 +87,10 @@ def lib():
         _lib.ascb200_graph_launch.argtypes = [C.c_void_p, C.c_void_p]
         _lib.ascb200_graph_destroy.argtypes = [C.c_void_p]
         _lib.ascb200_nz_unpack.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
+        _lib.ascb200_quant_policy.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                              C.c_int32, C.c_void_p, C.c_void_p, C.c_float, C.c_int32, C.c_void_p]
+        _lib.ascb200_dequant_policy.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                                C.c_int32, C.c_void_p, C.c_void_p]
         _lib.ascb200_softmax.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_void_p]
         _lib.ascb200_quant_per_tensor.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_float, C.c_void_p]
@@ -205,6 +209,23 @@ def quant_per_tensor(src, dst, n, dtype, scale, offset, stream=None):
 
 def quant_per_channel(src, dst, rows, k, dtype, scale, offset_t=None, offset=0.0, stream=None):
     return lib().ascb200_quant_per_channel(_ptr(src), _ptr(dst), rows, k, dtype, _ptr(scale), _ptr(offset_t), C.c_float(offset), stream)
+
+
+QUANT_PER_TOKEN, QUANT_PER_GROUP = 2, 3
+
+
+def quant_policy(src, dst, m, n, src_dtype, scale_dtype, dst_dtype, policy, scale, k_dim=1, group_size=0, offset=None, offset_scalar=0.0,
+                 has_offset=False, stream=None):
+    return lib().ascb200_quant_policy(_ptr(src), _ptr(dst), m, n, src_dtype, scale_dtype, dst_dtype, policy, k_dim, group_size, _ptr(scale),
+                                      _ptr(offset), C.c_float(offset_scalar), int(has_offset), stream)
+
+
+DEQUANT_PER_TOKEN, DEQUANT_PER_GROUP = 0, 1
+
+
+def dequant_policy(src, dst, m, n, src_dtype, scale_dtype, dst_dtype, policy, scale, k_dim=1, group_size=0, stream=None):
+    return lib().ascb200_dequant_policy(_ptr(src), _ptr(dst), m, n, src_dtype, scale_dtype, dst_dtype, policy, k_dim, group_size, _ptr(scale),
+                                        stream)
 
 
 def dequant(src, dst, m, n, cal, n_dst, dst_dtype, scale=None, scale_dtype=F32, scale_scalar=0.0, stream=None):

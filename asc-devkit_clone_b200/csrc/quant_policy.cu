@@ -1,0 +1,337 @@
+// AscendQuant with the PER_TOKEN and PER_GROUP policies (include/adv_api/quantization/ascend_quant.h:682-790,
+// impl/adv_api/detail/quantization/quant/ascend_quant_per_group_3510_impl.h): y = cast(x * scale [+ offset]) with one
+// scale per row (PER_TOKEN), per group of `group_size` columns of a row (PER_GROUP, kDim = 1) or per group of rows and
+// column (PER_GROUP, kDim = 0).  Destinations: int8, fp8 e4m3 / e5m2, and fp4 e2m1 (PER_GROUP only, no offset) - the
+// producer of block-scaled operands.  Arithmetic follows the reference's register code:
+//   fp8:  always fp32 (scale and offset widened), one rounding to fp8 (saturating);
+//   int8: in the scale's type (fp32 when the scale is fp32, else half / bfloat16 multiply and add), then round to
+//         nearest even and saturate (the reference goes fp32 -> int16 -> half -> int8, which is the same function);
+//   fp4:  in the scale's type, then to bfloat16 (nearest even) and from there to e2m1 (nearest even, saturating).
+// Element-wise and HBM bound: eight elements per thread, 16-byte loads, 8-byte (4-byte for fp4) stores.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <type_traits>
+
+#include "ascb200.h"
+#include "common.cuh"
+
+namespace ascb200 {
+namespace {
+
+enum : int { POL_TOKEN = ASCB200_QUANT_PER_TOKEN, POL_GROUP = ASCB200_QUANT_PER_GROUP };
+
+struct QuantPolicyArgs {
+    const void* src;
+    void* dst;
+    const void* scale;
+    const void* offset;  // tensor of the scale's shape, or nullptr
+    float offset_scalar;
+    int has_offset;
+    int m, n;
+    int policy, k_dim, group_size;
+    int scale_cols;  // columns of the scale tensor for PER_GROUP
+};
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// x * s (+ o) in the scale's type ST, result widened to fp32 (exact).
+template <typename ST>
+__device__ __forceinline__ float mul_add_in(float x, ST s, ST o, bool has_offset)
+{
+    if constexpr (sizeof(ST) == 4) {
+        float v = __fmul_rn(x, s);
+        return has_offset ? __fadd_rn(v, o) : v;
+    } else if constexpr (std::is_same<ST, __half>::value) {
+        // the _rn forms are never contracted into a fused multiply-add: the reference multiplies, rounds, then adds
+        __half v = __hmul_rn(__float2half_rn(x), s);  // x is a half widened exactly
+        if (has_offset) v = __hadd_rn(v, o);
+        return __half2float(v);
+    } else {
+        __nv_bfloat16 v = __hmul_rn(__float2bfloat16_rn(x), s);
+        if (has_offset) v = __hadd_rn(v, o);
+        return __bfloat162float(v);
+    }
+}
+
+template <int DST>
+__device__ __forceinline__ uint32_t to_byte(float v)
+{
+    if constexpr (DST == ASCB200_S8) {
+        int r;
+        asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));  // NaN -> 0
+        return static_cast<uint32_t>(r) & 0xFFu;
+    } else {
+        uint16_t pair;
+        if constexpr (DST == ASCB200_FP8_E4M3) asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(0.0f), "f"(v));
+        else asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(0.0f), "f"(v));
+        return pair & 0xFFu;
+    }
+}
+// two values -> one byte of packed e2m1, first value in the low nibble; via bfloat16 like the reference
+__device__ __forceinline__ uint32_t to_fp4_pair(float lo, float hi)
+{
+    lo = __bfloat162float(__float2bfloat16_rn(lo));
+    hi = __bfloat162float(__float2bfloat16_rn(hi));
+    uint16_t out;
+    asm("{\n\t.reg .b8 b;\n\tcvt.rn.satfinite.e2m1x2.f32 b, %1, %2;\n\tcvt.u16.u8 %0, b;\n\t}" : "=h"(out) : "f"(hi), "f"(lo));
+    return out & 0xFFu;
+}
+
+template <typename T, typename ST, int DST>
+__device__ __forceinline__ ST pick(const QuantPolicyArgs& a, const void* base, int row, int col)
+{
+    const ST* p = static_cast<const ST*>(base);
+    if (a.policy == POL_TOKEN) return p[row];
+    if (a.k_dim == 1) return p[static_cast<size_t>(row) * a.scale_cols + col / a.group_size];
+    return p[static_cast<size_t>(row / a.group_size) * a.n + col];
+}
+
+// One thread: eight consecutive elements of one row (n % 8 == 0), or one element (generic).
+template <typename T, typename ST, int DST, bool VEC8>
+__global__ void __launch_bounds__(256) quant_policy_kernel(const QuantPolicyArgs a)
+{
+    const size_t total = static_cast<size_t>(a.m) * a.n;
+    const T* src = static_cast<const T*>(a.src);
+    ST off_scalar;
+    if constexpr (sizeof(ST) == 4) off_scalar = a.offset_scalar;
+    else if constexpr (std::is_same<ST, __half>::value) off_scalar = __float2half_rn(a.offset_scalar);
+    else off_scalar = __float2bfloat16_rn(a.offset_scalar);
+    constexpr int STEP = VEC8 ? 8 : (DST == ASCB200_FP4_E2M1 ? 2 : 1);
+    for (size_t i = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * STEP; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x * STEP) {
+        const int row = static_cast<int>(i / a.n), col = static_cast<int>(i % a.n);
+        float v[STEP];
+        if constexpr (VEC8) {
+            if constexpr (sizeof(T) == 2) {
+                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + i));
+                const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = to_f32<T>(e[j]);
+            } else {
+                const float4 r0 = __ldg(reinterpret_cast<const float4*>(src + i)), r1 = __ldg(reinterpret_cast<const float4*>(src + i) + 1);
+                v[0] = r0.x; v[1] = r0.y; v[2] = r0.z; v[3] = r0.w;
+                v[4] = r1.x; v[5] = r1.y; v[6] = r1.z; v[7] = r1.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < STEP; ++j) v[j] = to_f32<T>(src[i + j]);
+        }
+        // groups are multiples of 32 columns: eight aligned columns share the scale unless it varies per column (kDim = 0)
+        const bool per_col = a.policy == POL_GROUP && a.k_dim == 0;
+        ST s = pick<T, ST, DST>(a, a.scale, row, col), o = off_scalar;
+        if (a.has_offset && a.offset) o = pick<T, ST, DST>(a, a.offset, row, col);
+#pragma unroll
+        for (int j = 0; j < STEP; ++j) {
+            if (per_col && j > 0) {
+                s = pick<T, ST, DST>(a, a.scale, row, col + j);
+                if (a.has_offset && a.offset) o = pick<T, ST, DST>(a, a.offset, row, col + j);
+            }
+            if constexpr (DST == ASCB200_FP8_E4M3 || DST == ASCB200_FP8_E5M2) {
+                // fp8: fp32 arithmetic whatever the scale's type
+                float r = __fmul_rn(v[j], to_f32<ST>(s));
+                v[j] = a.has_offset ? __fadd_rn(r, to_f32<ST>(o)) : r;
+            } else {
+                v[j] = mul_add_in<ST>(v[j], s, o, a.has_offset && DST != ASCB200_FP4_E2M1);
+            }
+        }
+        if constexpr (DST == ASCB200_FP4_E2M1) {
+            uint8_t* out = static_cast<uint8_t*>(a.dst) + i / 2;
+            if constexpr (VEC8) {
+                const uint32_t w = to_fp4_pair(v[0], v[1]) | (to_fp4_pair(v[2], v[3]) << 8) | (to_fp4_pair(v[4], v[5]) << 16) | (to_fp4_pair(v[6], v[7]) << 24);
+                *reinterpret_cast<uint32_t*>(out) = w;
+            } else {
+                *out = static_cast<uint8_t>(to_fp4_pair(v[0], v[1]));
+            }
+        } else {
+            uint8_t* out = static_cast<uint8_t*>(a.dst) + i;
+            if constexpr (VEC8) {
+                uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    w0 |= to_byte<DST>(v[j]) << (8 * j);
+                    w1 |= to_byte<DST>(v[4 + j]) << (8 * j);
+                }
+                *reinterpret_cast<uint2*>(out) = make_uint2(w0, w1);
+            } else {
+                *out = static_cast<uint8_t>(to_byte<DST>(v[0]));
+            }
+        }
+    }
+}
+
+template <typename T, typename ST, int DST>
+int launch_policy(const QuantPolicyArgs& a, bool vec8, int sms, cudaStream_t s)
+{
+    const size_t total = static_cast<size_t>(a.m) * a.n;
+    const size_t step = vec8 ? 8 : (DST == ASCB200_FP4_E2M1 ? 2 : 1);
+    const size_t threads = (total + step - 1) / step;
+    const unsigned grid = static_cast<unsigned>(std::min<size_t>((threads + 255) / 256, static_cast<size_t>(sms) * 16));
+    if (vec8) quant_policy_kernel<T, ST, DST, true><<<grid, 256, 0, s>>>(a);
+    else quant_policy_kernel<T, ST, DST, false><<<grid, 256, 0, s>>>(a);
+    ASCB200_CUDA(cudaGetLastError());
+    return ASCB200_OK;
+}
+
+template <typename T, typename ST>
+int dispatch_dst(const QuantPolicyArgs& a, int dst_dtype, bool vec8, int sms, cudaStream_t s)
+{
+    switch (dst_dtype) {
+        case ASCB200_S8: return launch_policy<T, ST, ASCB200_S8>(a, vec8, sms, s);
+        case ASCB200_FP8_E4M3: return launch_policy<T, ST, ASCB200_FP8_E4M3>(a, vec8, sms, s);
+        case ASCB200_FP8_E5M2: return launch_policy<T, ST, ASCB200_FP8_E5M2>(a, vec8, sms, s);
+        case ASCB200_FP4_E2M1: return launch_policy<T, ST, ASCB200_FP4_E2M1>(a, vec8, sms, s);
+        default: return ASCB200_EUNSUPPORTED;
+    }
+}
+
+// ---- AscendDequant with the PER_TOKEN / PER_GROUP policies ---------------------------------------------------------------
+// dst = cast(float(src) * float(scale)) (impl/adv_api/detail/quantization/dequant/ascend_dequant_3510_impl.h:253-286 per token,
+// :345-600 per group); src int32 or fp32, scale fp32 / half / bfloat16 (widened), dst fp32 / half / bfloat16 (round to nearest
+// even, fp16 saturating).  The offset tensor of the interface takes no part in the reference's arithmetic.
+struct DequantPolicyArgs {
+    const void* src;
+    void* dst;
+    const void* scale;
+    int m, n;
+    int per_group, k_dim, group_size, scale_cols;
+};
+
+template <typename SRC, typename ST, typename DT>
+__global__ void __launch_bounds__(256) dequant_policy_kernel(const DequantPolicyArgs a)
+{
+    const size_t total = static_cast<size_t>(a.m) * a.n;
+    const SRC* src = static_cast<const SRC*>(a.src);
+    const ST* scale = static_cast<const ST*>(a.scale);
+    DT* dst = static_cast<DT*>(a.dst);
+    const bool vec = a.n % 4 == 0;  // host checked the pointers' alignment
+    const int step = vec ? 4 : 1;
+    for (size_t i = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * step; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x * step) {
+        const int row = static_cast<int>(i / a.n), col = static_cast<int>(i % a.n);
+        float x[4];
+        if (vec) {
+            if constexpr (std::is_same<SRC, float>::value) {
+                const float4 r = __ldg(reinterpret_cast<const float4*>(src + i));
+                x[0] = r.x; x[1] = r.y; x[2] = r.z; x[3] = r.w;
+            } else {
+                const int4 r = __ldg(reinterpret_cast<const int4*>(src + i));
+                x[0] = __int2float_rn(r.x); x[1] = __int2float_rn(r.y); x[2] = __int2float_rn(r.z); x[3] = __int2float_rn(r.w);
+            }
+        } else {
+            x[0] = static_cast<float>(src[i]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (j >= step) break;
+            const size_t si = !a.per_group ? static_cast<size_t>(row)
+                              : a.k_dim == 1 ? static_cast<size_t>(row) * a.scale_cols + (col + j) / a.group_size
+                                             : static_cast<size_t>(row / a.group_size) * a.n + col + j;
+            const float v = __fmul_rn(x[j], to_f32<ST>(scale[si]));
+            if constexpr (std::is_same<DT, float>::value) dst[i + j] = v;
+            else if constexpr (std::is_same<DT, __half>::value) dst[i + j] = f32_to_f16_sat(v);
+            else dst[i + j] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+template <typename SRC, typename ST>
+int dequant_policy_dst(const DequantPolicyArgs& a, int dst_dtype, unsigned grid, cudaStream_t s)
+{
+    switch (dst_dtype) {
+        case ASCB200_F32: dequant_policy_kernel<SRC, ST, float><<<grid, 256, 0, s>>>(a); break;
+        case ASCB200_F16: dequant_policy_kernel<SRC, ST, __half><<<grid, 256, 0, s>>>(a); break;
+        case ASCB200_BF16: dequant_policy_kernel<SRC, ST, __nv_bfloat16><<<grid, 256, 0, s>>>(a); break;
+        default: return ASCB200_EUNSUPPORTED;
+    }
+    ASCB200_CUDA(cudaGetLastError());
+    return ASCB200_OK;
+}
+template <typename SRC>
+int dequant_policy_scale(const DequantPolicyArgs& a, int scale_dtype, int dst_dtype, unsigned grid, cudaStream_t s)
+{
+    switch (scale_dtype) {
+        case ASCB200_F32: return dequant_policy_dst<SRC, float>(a, dst_dtype, grid, s);
+        case ASCB200_F16: return dequant_policy_dst<SRC, __half>(a, dst_dtype, grid, s);
+        case ASCB200_BF16: return dequant_policy_dst<SRC, __nv_bfloat16>(a, dst_dtype, grid, s);
+        default: return ASCB200_EUNSUPPORTED;
+    }
+}
+
+}  // namespace
+}  // namespace ascb200
+
+extern "C" int ascb200_dequant_policy(const void* src, void* dst, int32_t m, int32_t n, int32_t src_dtype, int32_t scale_dtype, int32_t dst_dtype,
+                                      int32_t policy, int32_t k_dim, int32_t group_size, const void* scale, void* stream)
+{
+    using namespace ascb200;
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    if (!src || !dst || !scale || m < 0 || n < 0) return ASCB200_EINVAL;
+    if (policy != ASCB200_DEQUANT_PER_TOKEN && policy != ASCB200_DEQUANT_PER_GROUP) return ASCB200_EUNSUPPORTED;
+    if (policy == ASCB200_DEQUANT_PER_GROUP && (group_size <= 0 || group_size % 32 != 0 || (k_dim != 0 && k_dim != 1))) return ASCB200_EINVAL;
+    if (src_dtype != ASCB200_S32 && src_dtype != ASCB200_F32) return ASCB200_EUNSUPPORTED;
+    if (!aligned_to(src, 16) || !aligned_to(dst, 4)) return ASCB200_EALIGN;
+    if (m == 0 || n == 0) return ASCB200_OK;
+    DequantPolicyArgs a;
+    a.src = src;
+    a.dst = dst;
+    a.scale = scale;
+    a.m = m;
+    a.n = n;
+    a.per_group = policy == ASCB200_DEQUANT_PER_GROUP;
+    a.k_dim = k_dim;
+    a.group_size = a.per_group ? group_size : 1;
+    a.scale_cols = a.per_group ? (n + group_size - 1) / group_size : 1;
+    const size_t threads = (static_cast<size_t>(m) * n + 3) / 4;
+    const unsigned grid = static_cast<unsigned>(std::min<size_t>((threads + 255) / 256, static_cast<size_t>(st->sm_count) * 16));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (src_dtype == ASCB200_S32) return dequant_policy_scale<int32_t>(a, scale_dtype, dst_dtype, grid, s);
+    return dequant_policy_scale<float>(a, scale_dtype, dst_dtype, grid, s);
+}
+
+extern "C" int ascb200_quant_policy(const void* src, void* dst, int32_t m, int32_t n, int32_t src_dtype, int32_t scale_dtype, int32_t dst_dtype,
+                                    int32_t policy, int32_t k_dim, int32_t group_size, const void* scale, const void* offset_tensor,
+                                    float offset_scalar, int32_t has_offset, void* stream)
+{
+    using namespace ascb200;
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    if (!src || !dst || !scale || m < 0 || n < 0) return ASCB200_EINVAL;
+    if (policy != ASCB200_QUANT_PER_TOKEN && policy != ASCB200_QUANT_PER_GROUP) return ASCB200_EUNSUPPORTED;
+    if (policy == ASCB200_QUANT_PER_GROUP && (group_size <= 0 || group_size % 32 != 0 || (k_dim != 0 && k_dim != 1))) return ASCB200_EINVAL;
+    if (dst_dtype == ASCB200_FP4_E2M1 && (policy != ASCB200_QUANT_PER_GROUP || n % 2 != 0)) return ASCB200_EUNSUPPORTED;  // like the reference
+    // the scale is fp32, or has the source's 16-bit type (the reference loads the source into registers of the scale's type)
+    if (!(scale_dtype == ASCB200_F32 || (scale_dtype == src_dtype && (src_dtype == ASCB200_F16 || src_dtype == ASCB200_BF16)))) return ASCB200_EUNSUPPORTED;
+    if (m == 0 || n == 0) return ASCB200_OK;
+    QuantPolicyArgs a;
+    a.src = src;
+    a.dst = dst;
+    a.scale = scale;
+    a.offset = offset_tensor;
+    a.offset_scalar = offset_scalar;
+    a.has_offset = has_offset ? 1 : 0;
+    a.m = m;
+    a.n = n;
+    a.policy = policy;
+    a.k_dim = k_dim;
+    a.group_size = policy == ASCB200_QUANT_PER_GROUP ? group_size : 1;
+    a.scale_cols = policy == ASCB200_QUANT_PER_GROUP ? (n + group_size - 1) / group_size : 1;
+    const int esz = src_dtype == ASCB200_F32 ? 4 : 2;
+    const bool vec8 = n % 8 == 0 && aligned_to(src, 16) && aligned_to(dst, 8) && (src_dtype == ASCB200_F32 || esz == 2);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int sms = st->sm_count;
+    if (src_dtype == ASCB200_F16) {
+        if (scale_dtype == ASCB200_F32) return dispatch_dst<__half, float>(a, dst_dtype, vec8, sms, s);
+        return dispatch_dst<__half, __half>(a, dst_dtype, vec8, sms, s);
+    }
+    if (src_dtype == ASCB200_BF16) {
+        if (scale_dtype == ASCB200_F32) return dispatch_dst<__nv_bfloat16, float>(a, dst_dtype, vec8, sms, s);
+        return dispatch_dst<__nv_bfloat16, __nv_bfloat16>(a, dst_dtype, vec8, sms, s);
+    }
+    if (src_dtype == ASCB200_F32) return dispatch_dst<float, float>(a, dst_dtype, vec8, sms, s);
+    return ASCB200_EUNSUPPORTED;
+}

@@ -153,6 +153,65 @@ inline void AscendQuant(const LocalTensor<int8_t>& dst, const LocalTensor<T>& sr
     detail::QuantPerChannel<T>(dst, src, scaleTensor, offsetTensor.GetPhyAddr(), 0.0f, scaleTensor.GetSize(), src.GetSize());
 }
 
+// ---- AscendQuant with a policy (include/adv_api/quantization/ascend_quant.h:682-790) ---------------------------
+// include/adv_api/quantization/ascend_quant_utils.h:75-89
+enum class AscendQuantPolicy : int32_t { PER_TENSOR, PER_CHANNEL, PER_TOKEN, PER_GROUP, PER_CHANNEL_PER_GROUP, PER_TOKEN_PER_GROUP };
+struct AscendQuantParam {
+    uint32_t m;
+    uint32_t n;
+    uint32_t calCount;
+    uint32_t groupSize = 0;
+};
+
+namespace detail {
+template <typename dstT, typename srcT, typename scaleT, const AscendQuantConfig& config, const AscendQuantPolicy& policy>
+inline void QuantPolicy(const LocalTensor<dstT>& dst, const LocalTensor<srcT>& src, const LocalTensor<scaleT>& scale, const scaleT* offsetTensor,
+                        float offsetScalar, const AscendQuantParam& para)
+{
+    static_assert(policy == AscendQuantPolicy::PER_TOKEN || policy == AscendQuantPolicy::PER_GROUP,
+                  "unsupported policy for AscendQuant in current device!");  // the reference's own restriction
+    static_assert(config.roundMode == RoundMode::CAST_RINT, "only the default rounding (CAST_RINT) is implemented");
+    if (para.n == 0 || para.calCount % para.n != 0) {
+        Latch(ASCB200_EINVAL, "AscendQuant (calCount must be an integer multiple of n)");
+        return;
+    }
+    Latch(ascb200_quant_policy(src.GetPhyAddr(), dst.GetPhyAddr(), static_cast<int32_t>(para.calCount / para.n), static_cast<int32_t>(para.n),
+                               DTypeOf<srcT>::value, DTypeOf<scaleT>::value, DTypeOf<dstT>::value, static_cast<int32_t>(policy), config.kDim,
+                               static_cast<int32_t>(para.groupSize), scale.GetPhyAddr(), offsetTensor, offsetScalar, config.hasOffset ? 1 : 0,
+                               CurrentStream()),
+          "AscendQuant (policy)");
+}
+}  // namespace detail
+
+template <typename dstT, typename srcT, typename scaleT, bool isReuseSource = false, const AscendQuantConfig& config,
+          const AscendQuantPolicy& policy>
+inline void AscendQuant(const LocalTensor<dstT>& dstTensor, const LocalTensor<srcT>& srcTensor, const LocalTensor<scaleT>& scaleTensor,
+                        const LocalTensor<scaleT>& offsetTensor, const AscendQuantParam& para)
+{
+    detail::QuantPolicy<dstT, srcT, scaleT, config, policy>(dstTensor, srcTensor, scaleTensor, offsetTensor.GetPhyAddr(), 0.0f, para);
+}
+template <typename dstT, typename srcT, typename scaleT, bool isReuseSource = false, const AscendQuantConfig& config,
+          const AscendQuantPolicy& policy>
+inline void AscendQuant(const LocalTensor<dstT>& dstTensor, const LocalTensor<srcT>& srcTensor, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/,
+                        const LocalTensor<scaleT>& scaleTensor, const LocalTensor<scaleT>& offsetTensor, const AscendQuantParam& para)
+{
+    detail::QuantPolicy<dstT, srcT, scaleT, config, policy>(dstTensor, srcTensor, scaleTensor, offsetTensor.GetPhyAddr(), 0.0f, para);
+}
+template <typename dstT, typename srcT, typename scaleT, bool isReuseSource = false, const AscendQuantConfig& config,
+          const AscendQuantPolicy& policy>
+inline void AscendQuant(const LocalTensor<dstT>& dstTensor, const LocalTensor<srcT>& srcTensor, const LocalTensor<scaleT>& scaleTensor,
+                        const scaleT offset, const AscendQuantParam& para)
+{
+    detail::QuantPolicy<dstT, srcT, scaleT, config, policy>(dstTensor, srcTensor, scaleTensor, nullptr, static_cast<float>(offset), para);
+}
+template <typename dstT, typename srcT, typename scaleT, bool isReuseSource = false, const AscendQuantConfig& config,
+          const AscendQuantPolicy& policy>
+inline void AscendQuant(const LocalTensor<dstT>& dstTensor, const LocalTensor<srcT>& srcTensor, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/,
+                        const LocalTensor<scaleT>& scaleTensor, const scaleT offset, const AscendQuantParam& para)
+{
+    detail::QuantPolicy<dstT, srcT, scaleT, config, policy>(dstTensor, srcTensor, scaleTensor, nullptr, static_cast<float>(offset), para);
+}
+
 // include/adv_api/quantization/ascend_dequant_utils.h:26-30
 struct DequantParams {
     uint32_t m;         // rows of src
@@ -206,6 +265,42 @@ inline void AscendDequant(const LocalTensor<dstT>& dst, const LocalTensor<int32_
                                   static_cast<int32_t>(p.calCount), static_cast<int32_t>(detail::DequantDstRow<dstT>(p.n)),
                                   detail::DTypeOf<dstT>::value, nullptr, ASCB200_F32, static_cast<float>(deqScale), detail::CurrentStream()),
                   "AscendDequant");
+}
+
+// ---- AscendDequant with a policy (include/adv_api/quantization/ascend_dequant.h:293-318) ----------------------------
+// include/adv_api/quantization/ascend_dequant_utils.h:32-44
+struct AscendDeQuantConfig {
+    bool hasOffset;
+    int32_t kDim = 1;
+};
+enum class AscendDeQuantPolicy : int32_t { PER_TOKEN, PER_GROUP, PER_CHANNEL_PER_GROUP, PER_TOKEN_PER_GROUP };
+struct AscendDeQuantParam {
+    uint32_t m;
+    uint32_t n;
+    uint32_t calCount;
+    uint32_t groupSize = 0;
+};
+template <typename dstT, typename srcT, typename scaleT, const AscendDeQuantConfig& config, const AscendDeQuantPolicy& policy>
+inline void AscendDequant(const LocalTensor<dstT>& dstTensor, const LocalTensor<srcT>& srcTensor, const LocalTensor<scaleT>& scaleTensor,
+                          const LocalTensor<scaleT>& /*offsetTensor: not used by the reference's arithmetic*/, const AscendDeQuantParam& para)
+{
+    static_assert(policy == AscendDeQuantPolicy::PER_TOKEN || policy == AscendDeQuantPolicy::PER_GROUP,
+                  "unsupported policy for AscendDequant in current device!");
+    if (para.n == 0 || para.calCount % para.n != 0) {
+        detail::Latch(ASCB200_EINVAL, "AscendDequant (calCount must be an integer multiple of n)");
+        return;
+    }
+    detail::Latch(ascb200_dequant_policy(srcTensor.GetPhyAddr(), dstTensor.GetPhyAddr(), static_cast<int32_t>(para.calCount / para.n),
+                                         static_cast<int32_t>(para.n), detail::DTypeOf<srcT>::value, detail::DTypeOf<scaleT>::value,
+                                         detail::DTypeOf<dstT>::value, static_cast<int32_t>(policy), config.kDim,
+                                         static_cast<int32_t>(para.groupSize), scaleTensor.GetPhyAddr(), detail::CurrentStream()),
+                  "AscendDequant (policy)");
+}
+template <typename dstT, typename srcT, typename scaleT, const AscendDeQuantConfig& config, const AscendDeQuantPolicy& policy>
+inline void AscendDequant(const LocalTensor<dstT>& dstTensor, const LocalTensor<srcT>& srcTensor, const LocalTensor<scaleT>& scaleTensor,
+                          const LocalTensor<scaleT>& offsetTensor, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const AscendDeQuantParam& para)
+{
+    AscendDequant<dstT, srcT, scaleT, config, policy>(dstTensor, srcTensor, scaleTensor, offsetTensor, para);
 }
 
 }  // namespace AscendC

@@ -213,6 +213,30 @@ ASCB200_API int ascb200_quant_per_tensor(const void* src_dev, int8_t* dst_dev, i
 ASCB200_API int ascb200_quant_per_channel(const void* src_dev, int8_t* dst_dev, int32_t rows, int32_t scale_count, int32_t dtype,
                                           const void* scale_dev, const void* offset_dev, float offset, void* stream);
 
+/* AscendQuant with a policy (include/adv_api/quantization/ascend_quant.h:682-790; AscendQuantPolicy of
+ * include/adv_api/quantization/ascend_quant_utils.h:75-89; AscendQuantParam {m, n, calCount, groupSize}; implementation
+ * impl/adv_api/detail/quantization/quant/ascend_quant_per_group_3510_impl.h): dst[i,j] = cast(src[i,j] * scale [+ offset]).
+ *   ASCB200_QUANT_PER_TOKEN: scale / offset [m].
+ *   ASCB200_QUANT_PER_GROUP: k_dim = 1 (config.kDim): scale [m, ceil(n / group_size)]; k_dim = 0: scale [ceil(m / group_size), n];
+ *                            group_size a positive multiple of 32.
+ * src: F16 / BF16 / F32; scale (and offset tensor): F32, or the source's 16-bit type (arithmetic then runs in that type);
+ * dst: S8, FP8_E4M3, FP8_E5M2, or FP4_E2M1 (PER_GROUP only, two values per byte, n even, offset ignored like the reference).
+ * has_offset = config.hasOffset; the offset is offset_tensor (scale's shape) or, when that is NULL, offset_scalar.
+ * Rounding: CAST_RINT with saturation (the default config.roundMode). */
+enum { ASCB200_QUANT_PER_TOKEN = 2, ASCB200_QUANT_PER_GROUP = 3 };  /* values of AscendQuantPolicy */
+ASCB200_API int ascb200_quant_policy(const void* src_dev, void* dst_dev, int32_t m, int32_t n, int32_t src_dtype, int32_t scale_dtype,
+                                     int32_t dst_dtype, int32_t policy, int32_t k_dim, int32_t group_size, const void* scale_dev,
+                                     const void* offset_tensor_dev, float offset_scalar, int32_t has_offset, void* stream);
+
+/* AscendDequant with a policy (include/adv_api/quantization/ascend_dequant.h:293-318, AscendDeQuantPolicy / AscendDeQuantParam of
+ * include/adv_api/quantization/ascend_dequant_utils.h:32-44): dst[i,j] = cast(float(src[i,j]) * float(scale)), scale per row
+ * (PER_TOKEN: [m]) or per group (PER_GROUP: k_dim 1 -> [m, ceil(n / group_size)], k_dim 0 -> [ceil(m / group_size), n]).
+ * src S32 / F32; scale F32 / F16 / BF16; dst F32 / F16 / BF16.  The interface's offset tensor is unused by the reference. */
+enum { ASCB200_DEQUANT_PER_TOKEN = 0, ASCB200_DEQUANT_PER_GROUP = 1 };  /* values of AscendDeQuantPolicy */
+ASCB200_API int ascb200_dequant_policy(const void* src_dev, void* dst_dev, int32_t m, int32_t n, int32_t src_dtype, int32_t scale_dtype,
+                                       int32_t dst_dtype, int32_t policy, int32_t k_dim, int32_t group_size, const void* scale_dev,
+                                       void* stream);
+
 /* SoftMax immediately followed by per-channel AscendQuant of its output, one pass over src:
  * writes the fp16 SoftMax result, sum, max and the int8 tensor.  Equivalent to calling
  * ascb200_softmax then ascb200_quant_per_channel (dtype F16). */

@@ -27,7 +27,7 @@
 #define ORC_API __attribute__((visibility("default")))
 
 /* dtype codes shared with include/ascb200.h */
-enum { ORC_F32 = 0, ORC_F16 = 1, ORC_BF16 = 2, ORC_S8 = 3, ORC_S32 = 4 };
+enum { ORC_F32 = 0, ORC_F16 = 1, ORC_BF16 = 2, ORC_S8 = 3, ORC_S32 = 4, ORC_FP4_E2M1 = 5, ORC_FP8_E4M3 = 6, ORC_FP8_E5M2 = 7 };
 
 /* ---------------------------------------------------------------------------------------------
  * Scalar conversions.  CAST_RINT = round to nearest, ties to even
@@ -536,4 +536,92 @@ ORC_API int orc_num_threads(void)
 #else
     return 1;
 #endif
+}
+
+
+/* fp32 -> e2m1 code (sign, values 0, .5, 1, 1.5, 2, 3, 4, 6), round to nearest even code, saturating. */
+ORC_API uint8_t orc_f32_to_e2m1(float x)
+{
+    const uint8_t sign = (x < 0.0f || (x == 0.0f && signbit(x))) ? 8u : 0u;
+    const float a = fabsf(x);
+    uint8_t c;
+    if (a <= 0.25f) c = 0;          /* tie 0.25 -> 0 (even) */
+    else if (a < 0.75f) c = 1;
+    else if (a <= 1.25f) c = 2;     /* ties 0.75 and 1.25 -> 1.0 (even) */
+    else if (a < 1.75f) c = 3;
+    else if (a <= 2.5f) c = 4;      /* ties 1.75 and 2.5 -> 2.0 */
+    else if (a < 3.5f) c = 5;
+    else if (a <= 5.0f) c = 6;      /* ties 3.5 and 5.0 -> 4.0 */
+    else c = 7;
+    return (uint8_t)(sign | c);
+}
+
+/* AscendQuant with the PER_TOKEN (policy 2) and PER_GROUP (policy 3) policies, following the register code of
+ * impl/adv_api/detail/quantization/quant/ascend_quant_per_group_3510_impl.h:34-80 (fp8: fp32 arithmetic), :143-178 and :499-538
+ * (int8: arithmetic in the scale's type, then TransRegForS8 = round to nearest even, saturate,
+ * impl/adv_api/detail/quantization/quant/ascend_quant_3510_impl.h:935-990), :347-381 (fp4: scale's type -> bfloat16 -> e2m1,
+ * ascend_quant_3510_impl.h:992-1030; no offset).  Scale shapes: [m] | [m, ceil(n/group)] (k_dim 1) | [ceil(m/group), n] (k_dim 0). */
+static float load_f32(const void* p, size_t i, int dtype)
+{
+    if (dtype == ORC_F16) return orc_f16_to_f32(((const uint16_t*)p)[i]);
+    if (dtype == ORC_BF16) return orc_bf16_to_f32(((const uint16_t*)p)[i]);
+    return ((const float*)p)[i];
+}
+static float round_to(float v, int dtype)
+{
+    if (dtype == ORC_F16) return orc_f16_to_f32(f32_to_f16(v, 0));
+    if (dtype == ORC_BF16) return orc_bf16_to_f32(orc_f32_to_bf16(v));
+    return v;
+}
+ORC_API void orc_quant_policy(const void* src, uint8_t* dst, int m, int n, int src_dtype, int scale_dtype, int dst_dtype, int policy, int k_dim,
+                              int group_size, const void* scale, const void* offset_t, float offset_scalar, int has_offset)
+{
+    const int scale_cols = policy == 3 ? (n + group_size - 1) / group_size : 1;
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < m; ++i)
+        for (int j = 0; j < n; ++j) {
+            const size_t si = policy == 2 ? (size_t)i : (k_dim == 1 ? (size_t)i * scale_cols + j / group_size : (size_t)(i / group_size) * n + j);
+            const float x = load_f32(src, (size_t)i * n + j, src_dtype);
+            const float s = load_f32(scale, si, scale_dtype);
+            const float o = offset_t ? load_f32(offset_t, si, scale_dtype) : round_to(offset_scalar, scale_dtype);
+            float v;
+            if (dst_dtype == ORC_FP8_E4M3 || dst_dtype == ORC_FP8_E5M2) {
+                v = x * s;
+                if (has_offset) v = v + o;
+                dst[(size_t)i * n + j] = orc_f32_to_fp8(v, dst_dtype == ORC_FP8_E5M2);
+                continue;
+            }
+            /* products and sums of 16-bit floats are computed in fp32 and rounded once to the 16-bit type */
+            v = round_to(x * s, scale_dtype);
+            if (has_offset && dst_dtype != ORC_FP4_E2M1) v = round_to(v + o, scale_dtype);
+            if (dst_dtype == ORC_S8) {
+                dst[(size_t)i * n + j] = (uint8_t)orc_f32_to_s8(v);
+            } else {
+                const uint8_t c = orc_f32_to_e2m1(orc_bf16_to_f32(orc_f32_to_bf16(v)));
+                uint8_t* b = dst + ((size_t)i * n + j) / 2;
+                const int hi = (int)(((size_t)i * n + j) & 1);
+                /* n is even: a byte is written by one thread only */
+                *b = hi ? (uint8_t)((*b & 0x0F) | (c << 4)) : (uint8_t)((*b & 0xF0) | c);
+            }
+        }
+}
+
+
+/* AscendDequant PER_TOKEN (policy 0) / PER_GROUP (policy 1): dst = cast(float(src) * float(scale))
+ * (impl/adv_api/detail/quantization/dequant/ascend_dequant_3510_impl.h:253-286, 345-600). */
+ORC_API void orc_dequant_policy(const void* src, void* dst, int m, int n, int src_is_f32, int scale_dtype, int dst_dtype, int policy, int k_dim,
+                                int group_size, const void* scale)
+{
+    const int scale_cols = policy == 1 ? (n + group_size - 1) / group_size : 1;
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < m; ++i)
+        for (int j = 0; j < n; ++j) {
+            const size_t e = (size_t)i * n + j;
+            const size_t si = policy == 0 ? (size_t)i : (k_dim == 1 ? (size_t)i * scale_cols + j / group_size : (size_t)(i / group_size) * n + j);
+            const float x = src_is_f32 ? ((const float*)src)[e] : (float)((const int32_t*)src)[e];
+            const float v = x * load_f32(scale, si, scale_dtype);
+            if (dst_dtype == ORC_F32) ((float*)dst)[e] = v;
+            else if (dst_dtype == ORC_F16) ((uint16_t*)dst)[e] = f32_to_f16(v, 1);
+            else ((uint16_t*)dst)[e] = orc_f32_to_bf16(v);
+        }
 }

@@ -9,7 +9,7 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-F32, F16, BF16, S8, S32 = 0, 1, 2, 3, 4
+F32, F16, BF16, S8, S32, FP4_E2M1, FP8_E4M3, FP8_E5M2 = 0, 1, 2, 3, 4, 5, 6, 7
 _lib = None
 
 
@@ -210,3 +210,26 @@ def f16_bits_to_f32(bits):
 
 def bf16_bits_to_f32(bits):
     return (np.asarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def quant_policy(src, scale, src_dtype, scale_dtype, dst_dtype, policy, k_dim=1, group_size=0, offset=None, offset_scalar=0.0, has_offset=False):
+    """AscendQuant PER_TOKEN (policy 2) / PER_GROUP (policy 3). src [m, n] as stored (uint16 bits for F16 / BF16, float32 for F32);
+    returns uint8 [m, n] (int8 / fp8 bytes) or [m, n/2] packed e2m1."""
+    src = np.ascontiguousarray(src)
+    scale = np.ascontiguousarray(scale)
+    m, n = src.shape
+    out = np.zeros((m, n // 2) if dst_dtype == FP4_E2M1 else (m, n), np.uint8)
+    off = None if offset is None else np.ascontiguousarray(offset)
+    lib().orc_quant_policy(_p(src), _p(out), m, n, src_dtype, scale_dtype, dst_dtype, policy, k_dim, group_size, _p(scale),
+                           _p(off) if off is not None else None, C.c_float(offset_scalar), int(has_offset))
+    return out
+
+
+def dequant_policy(src, scale, scale_dtype, dst_dtype, policy, k_dim=1, group_size=0):
+    """AscendDequant PER_TOKEN (policy 0) / PER_GROUP (policy 1); src int32 or float32 [m, n]."""
+    src = np.ascontiguousarray(src)
+    scale = np.ascontiguousarray(scale)
+    m, n = src.shape
+    out = np.empty((m, n), _OUT[dst_dtype])
+    lib().orc_dequant_policy(_p(src), _p(out), m, n, int(src.dtype == np.float32), scale_dtype, dst_dtype, policy, k_dim, group_size, _p(scale))
+    return out

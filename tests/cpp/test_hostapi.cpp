@@ -371,6 +371,79 @@ static void TestMatmulNzAtomicAlign()
     std::printf("matmul NZ B + enAtomic, ND_ALIGN C: ok\n");
 }
 
+// AscendQuant<dstT, srcT, scaleT, isReuseSource, config, policy> with PER_TOKEN and PER_GROUP (fp4 destination).
+static constexpr AscendC::AscendQuantConfig kQuantCfgOffset = {0, 0, 0, 0, true, 1, AscendC::RoundMode::CAST_RINT};
+static constexpr AscendC::AscendQuantConfig kQuantCfgGroup = {0, 0, 0, 0, false, 1, AscendC::RoundMode::CAST_RINT};
+static constexpr AscendC::AscendQuantPolicy kPerToken = AscendC::AscendQuantPolicy::PER_TOKEN;
+static constexpr AscendC::AscendQuantPolicy kPerGroup = AscendC::AscendQuantPolicy::PER_GROUP;
+static void TestQuantPolicies()
+{
+    using namespace AscendC;
+    const uint32_t M = 24, N = 128;
+    std::mt19937 rng(11);
+    std::uniform_real_distribution<float> u(-4.f, 4.f);
+    std::vector<half> x(M * N);
+    for (auto& v : x) v = half(u(rng));
+    std::vector<float> scale(M), offset(M);
+    for (uint32_t i = 0; i < M; ++i) {
+        scale[i] = 5.0f + 0.5f * i;
+        offset[i] = static_cast<float>(i) - 10.0f;
+    }
+    DevBuf<half> dX(x);
+    DevBuf<float> dS(scale), dO(offset);
+    DevBuf<int8_t> dQ(M * N);
+    TPipe pipe;
+    AscendQuantParam para{M, N, M * N, 0};
+    AscendQuant<int8_t, half, float, false, kQuantCfgOffset, kPerToken>(LocalTensor<int8_t>(dQ.p, dQ.n), LocalTensor<half>(dX.p, dX.n),
+                                                                         LocalTensor<float>(dS.p, dS.n), LocalTensor<float>(dO.p, dO.n), para);
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<int8_t> q = dQ.Download();
+    int bad = 0;
+    for (uint32_t i = 0; i < M; ++i)
+        for (uint32_t j = 0; j < N; ++j) {
+            const float v = static_cast<float>(x[i * N + j]) * scale[i] + offset[i];
+            const float r = std::nearbyint(std::fmin(std::fmax(v, -128.f), 127.f));
+            if (q[i * N + j] != static_cast<int8_t>(r)) ++bad;
+        }
+    CHECK(bad == 0, "PER_TOKEN int8: %d wrong", bad);
+
+    // PER_GROUP, groups of 32 columns, fp4 e2m1 destination (two values per byte): spot-check the decoded values
+    std::vector<float> gscale(M * (N / 32), 0.5f);
+    DevBuf<float> dGs(gscale);
+    DevBuf<fp4x2_e2m1_t> dF(M * N / 2);
+    AscendQuantParam gpara{M, N, M * N, 32};
+    AscendQuant<fp4x2_e2m1_t, half, float, false, kQuantCfgGroup, kPerGroup>(LocalTensor<fp4x2_e2m1_t>(dF.p, dF.n), LocalTensor<half>(dX.p, dX.n),
+                                                                               LocalTensor<float>(dGs.p, dGs.n), 0.0f, gpara);
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<fp4x2_e2m1_t> f = dF.Download();
+    static const float grid[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+    bad = 0;
+    for (uint32_t e = 0; e < M * N; ++e) {
+        const uint8_t code = (f[e / 2].bits >> (4 * (e & 1))) & 0xF;
+        const float got = (code & 8 ? -1.f : 1.f) * grid[code & 7];
+        const float want = static_cast<float>(x[e]) * 0.5f;  // |want| <= 2: the nearest grid point is within 0.25 (0.5 above 2)
+        if (std::fabs(got - want) > 0.2501f) ++bad;
+    }
+    CHECK(bad == 0, "PER_GROUP fp4: %d values off the nearest grid point", bad);
+    // AscendDequant PER_TOKEN: int32 -> float with one scale per row
+    static constexpr AscendDeQuantConfig kDeqCfg = {false, 1};
+    static constexpr AscendDeQuantPolicy kDeqPerToken = AscendDeQuantPolicy::PER_TOKEN;
+    std::vector<int32_t> acc(M * N);
+    for (uint32_t e = 0; e < M * N; ++e) acc[e] = static_cast<int32_t>(e * 37u % 20011u) - 10000;
+    DevBuf<int32_t> dAcc(acc);
+    DevBuf<float> dDeq(M * N);
+    AscendDequant<float, int32_t, float, kDeqCfg, kDeqPerToken>(LocalTensor<float>(dDeq.p, dDeq.n), LocalTensor<int32_t>(dAcc.p, dAcc.n),
+                                                                 LocalTensor<float>(dS.p, dS.n), LocalTensor<float>(dO.p, dO.n),
+                                                                 AscendDeQuantParam{M, N, M * N, 0});
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<float> deq = dDeq.Download();
+    bad = 0;
+    for (uint32_t e = 0; e < M * N; ++e)
+        if (deq[e] != static_cast<float>(acc[e]) * scale[e / N]) ++bad;
+    CHECK(bad == 0, "AscendDequant PER_TOKEN: %d wrong", bad);
+    std::printf("AscendQuant PER_TOKEN / PER_GROUP, AscendDequant PER_TOKEN: ok\n");
+}
+
 static void TestErrorLatch()
 {
     AscendC::ClearLastError();
@@ -394,6 +467,7 @@ int main()
     TestMatmulQuant();
     TestSoftmaxQuantDequant();
     TestMatmulNzAtomicAlign();
+    TestQuantPolicies();
     TestErrorLatch();
     std::printf(g_fail ? "%d checks failed\n" : "hostapi ok\n", g_fail);
     return g_fail ? 1 : 0;

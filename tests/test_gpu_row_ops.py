@@ -167,3 +167,79 @@ def test_softmax_quant_fused_full_size():
         ab.sync()
         assert (d_y2.download() == y).all() and (d_q2.download() == q).all()
     assert (q == 0).all()  # literal scale: softmax <= 1 times <= 0.0158 rounds to zero everywhere
+
+
+def _as_stored(x, dtype):
+    return x.astype(np.float32) if dtype == 0 else (f16_bits(x) if dtype == 1 else bf16_bits(x))
+
+
+@pytest.mark.parametrize("dst_dtype", [3, 6, 7])          # int8, fp8 e4m3, fp8 e5m2
+@pytest.mark.parametrize("src_dtype,scale_dtype", [(1, 0), (2, 0), (0, 0), (1, 1), (2, 2)])
+@pytest.mark.parametrize("m,n,has_offset", [(64, 256, True), (37, 200, False), (5, 33, True)])
+def test_quant_per_token_policy(m, n, has_offset, src_dtype, scale_dtype, dst_dtype):
+    """AscendQuant PER_TOKEN: one scale (and offset) per row; bit exact against the oracle."""
+    ab = dev()
+    rng = np.random.default_rng(m * n + 7 * src_dtype + dst_dtype)
+    x = _as_stored(rng.standard_normal((m, n)).astype(np.float32) * 3, src_dtype)
+    scale = _as_stored(rng.uniform(2.0, 40.0, m).astype(np.float32), scale_dtype)
+    offset = _as_stored(rng.uniform(-8, 8, m).astype(np.float32), scale_dtype)
+    d_q = ab.empty((m, n), np.uint8)
+    d_q.fill(0x5A)
+    ab.check(ab.quant_policy(ab.to_dev(x), d_q, m, n, src_dtype, scale_dtype, dst_dtype, ab.QUANT_PER_TOKEN, ab.to_dev(scale),
+                             offset=ab.to_dev(offset) if has_offset else None, has_offset=has_offset))
+    ab.sync()
+    ref = orc.quant_policy(x, scale, src_dtype, scale_dtype, dst_dtype, 2, offset=offset if has_offset else None, has_offset=has_offset)
+    got = d_q.download().reshape(m, n)
+    assert (got == ref).all(), f"{(got != ref).sum()} of {ref.size} differ; first {np.argwhere(got != ref)[:4].tolist()}"
+
+
+@pytest.mark.parametrize("dst_dtype", [3, 6, 5])          # int8, fp8 e4m3, packed fp4 e2m1
+@pytest.mark.parametrize("src_dtype,scale_dtype", [(1, 0), (2, 0), (0, 0), (1, 1)])
+@pytest.mark.parametrize("m,n,group,k_dim", [(48, 256, 32, 1), (40, 320, 64, 1), (70, 96, 32, 0), (9, 250, 128, 1)])
+def test_quant_per_group_policy(m, n, group, k_dim, src_dtype, scale_dtype, dst_dtype):
+    """AscendQuant PER_GROUP along columns (kDim = 1) or rows (kDim = 0), incl. the fp4 destination that feeds block-scaled GEMMs."""
+    ab = dev()
+    rng = np.random.default_rng(m + n + group + 3 * src_dtype + dst_dtype)
+    x = _as_stored(rng.standard_normal((m, n)).astype(np.float32), src_dtype)
+    sshape = (m, -(-n // group)) if k_dim == 1 else (-(-m // group), n)
+    amp = 1.5 if dst_dtype == 5 else 30.0
+    scale = _as_stored(rng.uniform(0.5 * amp, amp, sshape).astype(np.float32), scale_dtype)
+    has_offset = dst_dtype != 5
+    d_q = ab.empty((m, n // 2) if dst_dtype == 5 else (m, n), np.uint8)
+    ab.check(ab.quant_policy(ab.to_dev(x), d_q, m, n, src_dtype, scale_dtype, dst_dtype, ab.QUANT_PER_GROUP, ab.to_dev(scale), k_dim=k_dim,
+                             group_size=group, offset_scalar=1.5, has_offset=has_offset))
+    ab.sync()
+    ref = orc.quant_policy(x, scale, src_dtype, scale_dtype, dst_dtype, 3, k_dim=k_dim, group_size=group, offset_scalar=1.5, has_offset=has_offset)
+    got = d_q.download().reshape(ref.shape)
+    assert (got == ref).all(), f"{(got != ref).sum()} of {ref.size} differ; first {np.argwhere(got != ref)[:4].tolist()}"
+
+
+def test_quant_policy_argument_errors():
+    ab = dev()
+    x = ab.to_dev(np.zeros((4, 64), np.float32))
+    s = ab.to_dev(np.ones(4, np.float32))
+    q = ab.empty((4, 64), np.uint8)
+    assert ab.quant_policy(x, q, 4, 64, ab.F32, ab.F32, ab.S8, 1, s) == ab.EUNSUPPORTED                      # PER_CHANNEL has its own entry point
+    assert ab.quant_policy(x, q, 4, 64, ab.F32, ab.F32, ab.S8, ab.QUANT_PER_GROUP, s, group_size=48) == ab.EINVAL  # groups are multiples of 32
+    assert ab.quant_policy(x, q, 4, 64, ab.F32, ab.F32, ab.FP4, ab.QUANT_PER_TOKEN, s) == ab.EUNSUPPORTED   # fp4 only per group
+    assert ab.quant_policy(x, q, 4, 64, ab.F32, ab.F16, ab.S8, ab.QUANT_PER_TOKEN, s) == ab.EUNSUPPORTED    # 16-bit scale needs the same source type
+
+
+@pytest.mark.parametrize("dst_dtype", [0, 1, 2])
+@pytest.mark.parametrize("src_f32,scale_dtype", [(False, 0), (False, 2), (True, 1), (True, 0)])
+@pytest.mark.parametrize("m,n,policy,group,k_dim", [(33, 256, 0, 0, 1), (48, 320, 1, 64, 1), (70, 96, 1, 32, 0), (5, 33, 0, 0, 1)])
+def test_dequant_policies(m, n, policy, group, k_dim, src_f32, scale_dtype, dst_dtype):
+    """AscendDequant PER_TOKEN / PER_GROUP: float(src) * float(scale), one rounding to the destination type; bit exact."""
+    ab = dev()
+    rng = np.random.default_rng(m * 31 + n + policy + scale_dtype + dst_dtype)
+    src = (rng.standard_normal((m, n)) * 1000).astype(np.float32) if src_f32 else rng.integers(-2**20, 2**20, (m, n)).astype(np.int32)
+    sshape = (m,) if policy == 0 else ((m, -(-n // group)) if k_dim == 1 else (-(-m // group), n))
+    scale = _as_stored(rng.uniform(1e-3, 1e-2, sshape).astype(np.float32), scale_dtype)
+    out_np = np.float32 if dst_dtype == 0 else np.uint16
+    d_out = ab.empty((m, n), out_np)
+    ab.check(ab.dequant_policy(ab.to_dev(src), d_out, m, n, ab.F32 if src_f32 else ab.S32, scale_dtype, dst_dtype, policy, ab.to_dev(scale),
+                               k_dim=k_dim, group_size=group))
+    ab.sync()
+    ref = orc.dequant_policy(src, scale, scale_dtype, dst_dtype, policy, k_dim=k_dim, group_size=group)
+    got = d_out.download().reshape(m, n)
+    assert (got.view(np.uint32 if dst_dtype == 0 else np.uint16) == ref.view(np.uint32 if dst_dtype == 0 else np.uint16)).all()
