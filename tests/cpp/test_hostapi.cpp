@@ -421,8 +421,8 @@ static void TestQuantPolicies()
     for (uint32_t e = 0; e < M * N; ++e) {
         const uint8_t code = (f[e / 2].bits >> (4 * (e & 1))) & 0xF;
         const float got = (code & 8 ? -1.f : 1.f) * grid[code & 7];
-        const float want = static_cast<float>(x[e]) * 0.5f;  // |want| <= 2: the nearest grid point is within 0.25 (0.5 above 2)
-        if (std::fabs(got - want) > 0.2501f) ++bad;
+        const float want = static_cast<float>(x[e]) * 0.5f;  // |want| <= 2: the nearest grid point is within 0.25
+        if (std::fabs(got - want) > 0.25f + 0.004f) ++bad;  // + half a bfloat16 step: the value passes through bfloat16 first
     }
     CHECK(bad == 0, "PER_GROUP fp4: %d values off the nearest grid point", bad);
     // AscendDequant PER_TOKEN: int32 -> float with one scale per row
