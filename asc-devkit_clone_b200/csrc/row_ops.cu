@@ -398,6 +398,124 @@ int launch_dequant(const int32_t* src, void* dst, int m, int n, int cal, int n_d
     return ASCB200_OK;
 }
 
+// ---- SoftmaxFlashV2 (include/adv_api/activation/softmaxflashv2.h:93-300) -------------------------------------------------
+// One step of the online softmax of FlashAttention-2 over rows [m, k]:
+//   update == 0:  max = rowmax(x);                 y = exp(x - max); expSum = rowsum(y)
+//   update == 1:  max = max(inMax, rowmax(x));     y = exp(x - max); expMax = exp(inMax - max); expSum = expMax * inExpSum + rowsum(y)
+// (formulas of docs/zh/api/SIMD-API/adv_api/activation_functions/SoftMax_interface/SoftmaxFlashV2.md:49-63).  y is not normalised.
+// T: element type of x, y and expMax; ST: type of the max / sum tensors (T, or float with half data).  Arithmetic is fp32
+// inside, like the reference's half path.  Same row mapping as softmax_rows_kernel (row in registers, read once).
+template <typename ST> __device__ __forceinline__ float stat_load(const ST* p, size_t i);
+template <> __device__ __forceinline__ float stat_load<float>(const float* p, size_t i) { return __ldg(p + i); }
+template <> __device__ __forceinline__ float stat_load<__half>(const __half* p, size_t i) { return __half2float(__ldg(p + i)); }
+template <typename ST> __device__ __forceinline__ void stat_store(ST* p, size_t i, float v);
+template <> __device__ __forceinline__ void stat_store<float>(float* p, size_t i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void stat_store<__half>(__half* p, size_t i, float v) { p[i] = __float2half_rn(clamp_half_range(v)); }
+
+template <typename T, typename ST, int TPR, int NCHUNK, bool UPDATE>
+__global__ void __launch_bounds__(TPR > 32 ? TPR : 128)
+softmax_flash_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, ST* __restrict__ sum_out, ST* __restrict__ max_out, T* __restrict__ expmax_out,
+                          const ST* __restrict__ in_sum, const ST* __restrict__ in_max, int m, int k, int stats_rep, int expmax_rep)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    __shared__ float red[32];
+    const int nchunks = k / VEC;
+    const int t = TPR > 32 ? threadIdx.x : (threadIdx.x & 31);
+    const int row = TPR > 32 ? blockIdx.x : blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= m) return;  // whole warp / block leaves together
+    uint4 raw[NCHUNK];
+    softmax_load_row<T, TPR, NCHUNK>(src + static_cast<size_t>(row) * k, t, nchunks, raw);
+    float v[NCHUNK * VEC];
+    float mx = kNegInf;
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+        const int c = t + i * TPR;
+        if (c < nchunks) {
+            if constexpr (sizeof(T) == 2) {
+                const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(h[j]);
+                    v[i * 8 + 2 * j] = f.x;
+                    v[i * 8 + 2 * j + 1] = f.y;
+                }
+            } else {
+                v[i * 4 + 0] = __uint_as_float(raw[i].x);
+                v[i * 4 + 1] = __uint_as_float(raw[i].y);
+                v[i * 4 + 2] = __uint_as_float(raw[i].z);
+                v[i * 4 + 3] = __uint_as_float(raw[i].w);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) v[i * VEC + j] = kNegInf;
+        }
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) mx = fmaxf(mx, v[i * VEC + j]);
+    }
+    mx = row_reduce_max<TPR>(mx, red);
+    float old_max = 0.0f, old_sum = 0.0f, exp_max = 1.0f;
+    if constexpr (UPDATE) {
+        old_max = stat_load<ST>(in_max, static_cast<size_t>(row) * stats_rep);
+        old_sum = stat_load<ST>(in_sum, static_cast<size_t>(row) * stats_rep);
+        mx = fmaxf(mx, old_max);
+        exp_max = exp2_approx((old_max - mx) * 1.4426950408889634f);
+    }
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NCHUNK * VEC; ++i) {
+        v[i] = exp2_approx((v[i] - mx) * 1.4426950408889634f);
+        s += v[i];
+    }
+    s = row_reduce_sum<TPR>(s, red);
+    if constexpr (UPDATE) s = __fadd_rn(__fmul_rn(exp_max, old_sum), s);
+
+    T* drow = dst + static_cast<size_t>(row) * k;
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+        const int c = t + i * TPR;
+        if (c < nchunks) {
+            if constexpr (sizeof(T) == 2) {
+                uint4 o;  // values lie in [0, 1]
+                __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(v[i * 8 + 2 * j], v[i * 8 + 2 * j + 1]);
+                *reinterpret_cast<uint4*>(drow + c * 8) = o;
+            } else {
+                *reinterpret_cast<float4*>(drow + c * 4) = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+            }
+        }
+    }
+    if (t < stats_rep) {
+        stat_store<ST>(sum_out, static_cast<size_t>(row) * stats_rep + t, s);
+        stat_store<ST>(max_out, static_cast<size_t>(row) * stats_rep + t, mx);
+    }
+    if (UPDATE && t < expmax_rep) {
+        if constexpr (sizeof(T) == 2) expmax_out[static_cast<size_t>(row) * expmax_rep + t] = __float2half_rn(exp_max);
+        else expmax_out[static_cast<size_t>(row) * expmax_rep + t] = exp_max;
+    }
+}
+
+template <typename T, typename ST, bool UPDATE>
+int launch_softmax_flash(const T* src, T* dst, ST* sum, ST* mx, T* expmax, const ST* in_sum, const ST* in_max, int m, int k, int stats_rep,
+                         int expmax_rep, cudaStream_t st)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    const int nchunks = k / VEC;
+#define ASCB200_SF_WARP(NC) softmax_flash_rows_kernel<T, ST, 32, NC, UPDATE><<<(m + 3) / 4, 128, 0, st>>>(src, dst, sum, mx, expmax, in_sum, in_max, m, k, stats_rep, expmax_rep)
+#define ASCB200_SF_BLOCK(TPR, NC) softmax_flash_rows_kernel<T, ST, TPR, NC, UPDATE><<<m, TPR, 0, st>>>(src, dst, sum, mx, expmax, in_sum, in_max, m, k, stats_rep, expmax_rep)
+    if (nchunks <= 32) ASCB200_SF_WARP(1);
+    else if (nchunks <= 64) ASCB200_SF_WARP(2);
+    else if (nchunks <= 128) ASCB200_SF_WARP(4);
+    else if (nchunks <= 256) ASCB200_SF_WARP(8);
+    else if (nchunks <= 1024) ASCB200_SF_BLOCK(256, 4);
+    else if (nchunks <= 2048) ASCB200_SF_BLOCK(256, 8);
+    else return ASCB200_ETOOBIG;
+#undef ASCB200_SF_WARP
+#undef ASCB200_SF_BLOCK
+    ASCB200_CUDA(cudaGetLastError());
+    return ASCB200_OK;
+}
+
 int check_softmax_args(const void* src, void* dst, float* sum, float* mx, int m, int k, int dtype)
 {
     if (!src || !dst || !sum || !mx || m < 0 || k <= 0) return ASCB200_EINVAL;
@@ -441,6 +559,39 @@ int ascb200_softmax(const void* src, void* dst, float* sum, float* mx, int32_t m
                                              nullptr, __half(), m, k, rep, st->sm_count, s);
     return launch_softmax<float, false>(static_cast<const float*>(src), static_cast<float*>(dst), sum, mx, nullptr, nullptr, nullptr,
                                         __half(), m, k, rep, st->sm_count, s);
+}
+
+int ascb200_softmax_flash_v2(const void* src, void* dst, void* exp_sum, void* max, void* exp_max, const void* in_exp_sum, const void* in_max,
+                             int32_t m, int32_t k, int32_t dtype, int32_t stats_dtype, int32_t update, int32_t stats_brc, void* stream)
+{
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    if (!src || !dst || !exp_sum || !max || m < 0 || k <= 0) return ASCB200_EINVAL;
+    if (update && (!exp_max || !in_exp_sum || !in_max)) return ASCB200_EINVAL;
+    if (dtype != ASCB200_F16 && dtype != ASCB200_F32) return ASCB200_EUNSUPPORTED;
+    if (!(stats_dtype == dtype || (dtype == ASCB200_F16 && stats_dtype == ASCB200_F32))) return ASCB200_EUNSUPPORTED;  // the reference's overloads
+    const int esz = dtype == ASCB200_F16 ? 2 : 4;
+    if ((static_cast<size_t>(k) * esz) % 32 != 0) return ASCB200_EALIGN;
+    if (!aligned_to(src, 16) || !aligned_to(dst, 16)) return ASCB200_EALIGN;
+    if (m == 0) return ASCB200_OK;
+    const int stats_rep = stats_brc ? 32 / (stats_dtype == ASCB200_F16 ? 2 : 4) : 1;  // one 32-byte block per row
+    const int expmax_rep = stats_brc ? 32 / esz : 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define ASCB200_SF_CALL(T, ST, UPD)                                                                                                      \
+    return launch_softmax_flash<T, ST, UPD>(static_cast<const T*>(src), static_cast<T*>(dst), static_cast<ST*>(exp_sum), static_cast<ST*>(max), \
+                                            static_cast<T*>(exp_max), static_cast<const ST*>(in_exp_sum), static_cast<const ST*>(in_max), m, k, \
+                                            stats_rep, expmax_rep, s)
+    if (dtype == ASCB200_F32) {
+        if (update) ASCB200_SF_CALL(float, float, true);
+        ASCB200_SF_CALL(float, float, false);
+    }
+    if (stats_dtype == ASCB200_F32) {
+        if (update) ASCB200_SF_CALL(__half, float, true);
+        ASCB200_SF_CALL(__half, float, false);
+    }
+    if (update) ASCB200_SF_CALL(__half, __half, true);
+    ASCB200_SF_CALL(__half, __half, false);
+#undef ASCB200_SF_CALL
 }
 
 int ascb200_softmax_quant(const void* src, void* dst, float* sum, float* mx, int8_t* q, const void* scale, const void* offset_t,

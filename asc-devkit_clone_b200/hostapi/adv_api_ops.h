@@ -49,6 +49,65 @@ inline void SoftMax(const LocalTensor<T>& dstTensor, const LocalTensor<float>& s
     SoftMax<T, isReuseSource, isBasicBlock, isDataFormatNZ, config>(dstTensor, sumTensor, maxTensor, srcTensor, tiling, softmaxShapeInfo);
 }
 
+// SoftmaxFlashV2<T, isUpdate>(dst, expSum, max, src, expMax, inExpSum, inMax, tiling, shapeInfo)
+// (include/adv_api/activation/softmaxflashv2.h:93-260): the all-T overloads and the half data / float statistics overloads,
+// each with and without sharedTmpBuffer.
+namespace detail {
+template <typename T, typename ST, bool isUpdate, const SoftmaxConfig& config>
+inline void SoftmaxFlashV2Call(const LocalTensor<T>& dst, const LocalTensor<ST>& expSum, const LocalTensor<ST>& max, const LocalTensor<T>& src,
+                               const LocalTensor<T>& expMax, const LocalTensor<ST>& inExpSum, const LocalTensor<ST>& inMax,
+                               const SoftMaxTiling& tiling, const SoftMaxShapeInfo& shape)
+{
+    const uint32_t m = shape.srcM ? shape.srcM : tiling.srcM;
+    const uint32_t k = shape.srcK ? shape.srcK : tiling.srcK;
+    const int brc = config.mode == SoftmaxMode::SOFTMAX_OUTPUT_WITHOUT_BRC ? 0 : 1;
+    Latch(ascb200_softmax_flash_v2(src.GetPhyAddr(), dst.GetPhyAddr(), expSum.GetPhyAddr(), max.GetPhyAddr(), expMax.GetPhyAddr(),
+                                   inExpSum.GetPhyAddr(), inMax.GetPhyAddr(), static_cast<int32_t>(m), static_cast<int32_t>(k), DTypeOf<T>::value,
+                                   DTypeOf<ST>::value, isUpdate ? 1 : 0, brc, CurrentStream()),
+          "SoftmaxFlashV2");
+}
+}  // namespace detail
+template <typename T, bool isUpdate = false, bool isReuseSource = false, bool isBasicBlock = false, bool isDataFormatNZ = false,
+          const SoftmaxConfig& config = SOFTMAX_DEFAULT_CFG>
+inline void SoftmaxFlashV2(const LocalTensor<T>& dstTensor, const LocalTensor<T>& expSumTensor, const LocalTensor<T>& maxTensor,
+                           const LocalTensor<T>& srcTensor, const LocalTensor<T>& expMaxTensor, const LocalTensor<T>& inExpSumTensor,
+                           const LocalTensor<T>& inMaxTensor, const SoftMaxTiling& tiling, const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    static_assert(!isDataFormatNZ, "NZ-format SoftmaxFlashV2 is not part of the B200 path");
+    detail::SoftmaxFlashV2Call<T, T, isUpdate, config>(dstTensor, expSumTensor, maxTensor, srcTensor, expMaxTensor, inExpSumTensor, inMaxTensor,
+                                                       tiling, softmaxShapeInfo);
+}
+template <typename T, bool isUpdate = false, bool isReuseSource = false, bool isBasicBlock = false, bool isDataFormatNZ = false,
+          const SoftmaxConfig& config = SOFTMAX_DEFAULT_CFG>
+inline void SoftmaxFlashV2(const LocalTensor<half>& dstTensor, const LocalTensor<float>& expSumTensor, const LocalTensor<float>& maxTensor,
+                           const LocalTensor<half>& srcTensor, const LocalTensor<half>& expMaxTensor, const LocalTensor<float>& inExpSumTensor,
+                           const LocalTensor<float>& inMaxTensor, const SoftMaxTiling& tiling, const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    static_assert(!isDataFormatNZ, "NZ-format SoftmaxFlashV2 is not part of the B200 path");
+    detail::SoftmaxFlashV2Call<half, float, isUpdate, config>(dstTensor, expSumTensor, maxTensor, srcTensor, expMaxTensor, inExpSumTensor,
+                                                              inMaxTensor, tiling, softmaxShapeInfo);
+}
+template <typename T, bool isUpdate = false, bool isReuseSource = false, bool isBasicBlock = false, bool isDataFormatNZ = false,
+          const SoftmaxConfig& config = SOFTMAX_DEFAULT_CFG>
+inline void SoftmaxFlashV2(const LocalTensor<T>& dstTensor, const LocalTensor<T>& expSumTensor, const LocalTensor<T>& maxTensor,
+                           const LocalTensor<T>& srcTensor, const LocalTensor<T>& expMaxTensor, const LocalTensor<T>& inExpSumTensor,
+                           const LocalTensor<T>& inMaxTensor, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const SoftMaxTiling& tiling,
+                           const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    SoftmaxFlashV2<T, isUpdate, isReuseSource, isBasicBlock, isDataFormatNZ, config>(dstTensor, expSumTensor, maxTensor, srcTensor, expMaxTensor,
+                                                                                      inExpSumTensor, inMaxTensor, tiling, softmaxShapeInfo);
+}
+template <typename T, bool isUpdate = false, bool isReuseSource = false, bool isBasicBlock = false, bool isDataFormatNZ = false,
+          const SoftmaxConfig& config = SOFTMAX_DEFAULT_CFG>
+inline void SoftmaxFlashV2(const LocalTensor<half>& dstTensor, const LocalTensor<float>& expSumTensor, const LocalTensor<float>& maxTensor,
+                           const LocalTensor<half>& srcTensor, const LocalTensor<half>& expMaxTensor, const LocalTensor<float>& inExpSumTensor,
+                           const LocalTensor<float>& inMaxTensor, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const SoftMaxTiling& tiling,
+                           const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    SoftmaxFlashV2<T, isUpdate, isReuseSource, isBasicBlock, isDataFormatNZ, config>(dstTensor, expSumTensor, maxTensor, srcTensor, expMaxTensor,
+                                                                                      inExpSumTensor, inMaxTensor, tiling, softmaxShapeInfo);
+}
+
 // include/adv_api/quantization/ascend_quant_utils.h:31-73
 struct AscendQuantConfig {
     constexpr AscendQuantConfig(uint32_t calcCountIn, uint32_t offsetCountIn, uint32_t scaleCountIn, uint32_t workLocalSizeIn,

@@ -237,6 +237,17 @@ ASCB200_API int ascb200_dequant_policy(const void* src_dev, void* dst_dev, int32
                                        int32_t dst_dtype, int32_t policy, int32_t k_dim, int32_t group_size, const void* scale_dev,
                                        void* stream);
 
+/* SoftmaxFlashV2<T, isUpdate>(dst, expSum, max, src, expMax, inExpSum, inMax, tiling, shapeInfo)
+ * (include/adv_api/activation/softmaxflashv2.h:93-300): one step of the online softmax over rows [m, k].
+ *   update == 0: max = rowmax(x); y = exp(x - max); expSum = rowsum(y).
+ *   update == 1: max = max(inMax, rowmax(x)); y = exp(x - max); expMax = exp(inMax - max); expSum = expMax * inExpSum + rowsum(y).
+ * dtype (x, y, expMax): F16 or F32; stats_dtype (max / sum tensors): the same, or F32 with F16 data (the half/float overload).
+ * stats_brc = 1: every per-row value fills one 32-byte block ([m, 8] floats / [m, 16] halves, SOFTMAX_NORMAL);
+ * 0: [m] (SOFTMAX_OUTPUT_WITHOUT_BRC).  k * sizeof(T) must be a multiple of 32 bytes; k up to 16384 halves / 8192 floats. */
+ASCB200_API int ascb200_softmax_flash_v2(const void* src_dev, void* dst_dev, void* exp_sum_dev, void* max_dev, void* exp_max_dev,
+                                         const void* in_exp_sum_dev, const void* in_max_dev, int32_t m, int32_t k, int32_t dtype,
+                                         int32_t stats_dtype, int32_t update, int32_t stats_brc, void* stream);
+
 /* SoftMax immediately followed by per-channel AscendQuant of its output, one pass over src:
  * writes the fp16 SoftMax result, sum, max and the int8 tensor.  Equivalent to calling
  * ascb200_softmax then ascb200_quant_per_channel (dtype F16). */

@@ -625,3 +625,53 @@ ORC_API void orc_dequant_policy(const void* src, void* dst, int m, int n, int sr
             else ((uint16_t*)dst)[e] = orc_f32_to_bf16(v);
         }
 }
+
+
+/* SoftmaxFlashV2 (docs/zh/api/SIMD-API/adv_api/activation_functions/SoftMax_interface/SoftmaxFlashV2.md:49-63):
+ *   update 0: max = rowmax(x); y = exp(x - max); sum = rowsum(y)
+ *   update 1: max = max(inmax, rowmax(x)); y = exp(x - max); expmax = exp(inmax - max); sum = expmax * insum + rowsum(y)
+ * fp32 arithmetic; x / y / expmax in `dtype`, max / sum tensors in `stats_dtype`; per-row values repeated over one 32-byte block
+ * when brc is set. */
+static void stat_put(void* p, size_t i, float v, int dtype)
+{
+    if (dtype == ORC_F16) ((uint16_t*)p)[i] = f32_to_f16(v, 1);
+    else ((float*)p)[i] = v;
+}
+ORC_API void orc_softmax_flash_v2(const void* x, void* y, void* sum_out, void* max_out, void* expmax_out, const void* in_sum, const void* in_max,
+                                  int M, int K, int dtype, int stats_dtype, int update, int brc)
+{
+    const int srep = brc ? 32 / (stats_dtype == ORC_F16 ? 2 : 4) : 1, erep = brc ? 32 / (dtype == ORC_F16 ? 2 : 4) : 1;
+#pragma omp parallel
+    {
+        float* row = (float*)malloc((size_t)K * sizeof(float));
+#pragma omp for schedule(static)
+        for (int m = 0; m < M; ++m) {
+            float mx = -INFINITY;
+            for (int k = 0; k < K; ++k) {
+                row[k] = load_f32(x, (size_t)m * K + k, dtype);
+                if (row[k] > mx) mx = row[k];
+            }
+            float em = 1.0f, old_sum = 0.0f;
+            if (update) {
+                const float old_max = load_f32(in_max, (size_t)m * srep, stats_dtype);
+                old_sum = load_f32(in_sum, (size_t)m * srep, stats_dtype);
+                if (old_max > mx) mx = old_max;
+                em = expf(old_max - mx);
+            }
+            float s = 0.0f;
+            for (int k = 0; k < K; ++k) {
+                row[k] = expf(row[k] - mx);
+                s += row[k];
+                stat_put(y, (size_t)m * K + k, row[k], dtype);
+            }
+            if (update) s = em * old_sum + s;
+            for (int r = 0; r < srep; ++r) {
+                stat_put(sum_out, (size_t)m * srep + r, s, stats_dtype);
+                stat_put(max_out, (size_t)m * srep + r, mx, stats_dtype);
+            }
+            if (update)
+                for (int r = 0; r < erep; ++r) stat_put(expmax_out, (size_t)m * erep + r, em, dtype);
+        }
+        free(row);
+    }
+}

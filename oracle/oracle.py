@@ -233,3 +233,19 @@ def dequant_policy(src, scale, scale_dtype, dst_dtype, policy, k_dim=1, group_si
     out = np.empty((m, n), _OUT[dst_dtype])
     lib().orc_dequant_policy(_p(src), _p(out), m, n, int(src.dtype == np.float32), scale_dtype, dst_dtype, policy, k_dim, group_size, _p(scale))
     return out
+
+
+def softmax_flash_v2(x, dtype, stats_dtype, in_sum=None, in_max=None, brc=True):
+    """SoftmaxFlashV2 step. x [M, K] as stored. Returns (y, sum, max, expmax or None); stats are [M, rep]."""
+    x = np.ascontiguousarray(x)
+    M, K = x.shape
+    update = in_sum is not None
+    srep = (32 // (2 if stats_dtype == F16 else 4)) if brc else 1
+    erep = (32 // (2 if dtype == F16 else 4)) if brc else 1
+    y = np.empty((M, K), _OUT[dtype])
+    s = np.empty((M, srep), _OUT[stats_dtype])
+    mx = np.empty((M, srep), _OUT[stats_dtype])
+    em = np.empty((M, erep), _OUT[dtype])
+    lib().orc_softmax_flash_v2(_p(x), _p(y), _p(s), _p(mx), _p(em), _p(np.ascontiguousarray(in_sum)) if update else None,
+                               _p(np.ascontiguousarray(in_max)) if update else None, M, K, dtype, stats_dtype, int(update), int(brc))
+    return y, s, mx, (em if update else None)

@@ -444,6 +444,42 @@ static void TestQuantPolicies()
     std::printf("AscendQuant PER_TOKEN / PER_GROUP, AscendDequant PER_TOKEN: ok\n");
 }
 
+// SoftmaxFlashV2 over two K tiles (half data, float statistics), checked through the online-softmax identity.
+static void TestSoftmaxFlashV2()
+{
+    using namespace AscendC;
+    const uint32_t M = 16, K = 256;
+    std::mt19937 rng(5);
+    std::normal_distribution<float> nd(0.f, 2.f);
+    std::vector<half> x1(M * K), x2(M * K);
+    for (auto& v : x1) v = half(nd(rng));
+    for (auto& v : x2) v = half(nd(rng) + 1.0f);
+    DevBuf<half> d1(x1), d2(x2), dY(M * K), dEm(M * 16);
+    DevBuf<float> dSum(M * 8), dMax(M * 8), dSum2(M * 8), dMax2(M * 8);
+    SoftMaxTiling tiling{};
+    tiling.srcM = M;
+    tiling.srcK = K;
+    TPipe pipe;
+    SoftmaxFlashV2<half, false>(LocalTensor<half>(dY.p, dY.n), LocalTensor<float>(dSum.p, dSum.n), LocalTensor<float>(dMax.p, dMax.n),
+                                LocalTensor<half>(d1.p, d1.n), LocalTensor<half>(dEm.p, dEm.n), LocalTensor<float>(dSum.p, dSum.n),
+                                LocalTensor<float>(dMax.p, dMax.n), tiling);
+    SoftmaxFlashV2<half, true>(LocalTensor<half>(dY.p, dY.n), LocalTensor<float>(dSum2.p, dSum2.n), LocalTensor<float>(dMax2.p, dMax2.n),
+                               LocalTensor<half>(d2.p, d2.n), LocalTensor<half>(dEm.p, dEm.n), LocalTensor<float>(dSum.p, dSum.n),
+                               LocalTensor<float>(dMax.p, dMax.n), tiling);
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<float> sum2 = dSum2.Download(), max2 = dMax2.Download();
+    int bad = 0;
+    for (uint32_t i = 0; i < M; ++i) {
+        float mx = -1e30f;
+        for (uint32_t j = 0; j < K; ++j) mx = std::fmax(mx, std::fmax(static_cast<float>(x1[i * K + j]), static_cast<float>(x2[i * K + j])));
+        double s = 0;
+        for (uint32_t j = 0; j < K; ++j) s += std::exp(static_cast<float>(x1[i * K + j]) - mx) + std::exp(static_cast<float>(x2[i * K + j]) - mx);
+        if (max2[i * 8] != mx || max2[i * 8 + 7] != mx || std::fabs(sum2[i * 8] - s) > 2e-3 * s) ++bad;
+    }
+    CHECK(bad == 0, "SoftmaxFlashV2: %d rows wrong", bad);
+    std::printf("SoftmaxFlashV2 two tiles: ok\n");
+}
+
 static void TestErrorLatch()
 {
     AscendC::ClearLastError();
@@ -468,6 +504,7 @@ int main()
     TestSoftmaxQuantDequant();
     TestMatmulNzAtomicAlign();
     TestQuantPolicies();
+    TestSoftmaxFlashV2();
     TestErrorLatch();
     std::printf(g_fail ? "%d checks failed\n" : "hostapi ok\n", g_fail);
     return g_fail ? 1 : 0;

@@ -243,3 +243,43 @@ def test_dequant_policies(m, n, policy, group, k_dim, src_f32, scale_dtype, dst_
     ref = orc.dequant_policy(src, scale, scale_dtype, dst_dtype, policy, k_dim=k_dim, group_size=group)
     got = d_out.download().reshape(m, n)
     assert (got.view(np.uint32 if dst_dtype == 0 else np.uint16) == ref.view(np.uint32 if dst_dtype == 0 else np.uint16)).all()
+
+
+def _to_f32(a, dtype):
+    return a.astype(np.float32) if dtype == 0 else orc.f16_bits_to_f32(a)
+
+
+@pytest.mark.parametrize("dtype,stats_dtype", [(1, 0), (1, 1), (0, 0)])
+@pytest.mark.parametrize("m,k,brc", [(64, 128, True), (37, 2048, True), (8, 4096, False), (3, 16, True)])
+def test_softmax_flash_v2_two_steps(m, k, brc, dtype, stats_dtype):
+    """Two SoftmaxFlashV2 steps over two K tiles (first without, then with update) against the oracle, and the online-softmax
+    identity: sum_2 equals the sum of exp(x - max_2) over both tiles."""
+    ab = dev()
+    rng = np.random.default_rng(m + k + dtype * 3 + stats_dtype)
+    x1 = (rng.standard_normal((m, k)) * 2).astype(np.float32)
+    x2 = (rng.standard_normal((m, k)) * 2 + 1).astype(np.float32)
+    s1, s2 = _as_stored(x1, dtype), _as_stored(x2, dtype)
+    srep = (32 // (2 if stats_dtype == 1 else 4)) if brc else 1
+    erep = (32 // (2 if dtype == 1 else 4)) if brc else 1
+    np_d, np_s = (np.float32 if dtype == 0 else np.uint16), (np.float32 if stats_dtype == 0 else np.uint16)
+    d_y, d_sum, d_max, d_em = ab.empty((m, k), np_d), ab.empty((m, srep), np_s), ab.empty((m, srep), np_s), ab.empty((m, erep), np_d)
+    ab.check(ab.softmax_flash_v2(ab.to_dev(s1), d_y, d_sum, d_max, None, None, None, m, k, dtype, stats_dtype, False, brc))
+    ab.sync()
+    y_r, sum_r, max_r, _ = orc.softmax_flash_v2(s1, dtype, stats_dtype, brc=brc)
+    sum1, max1 = d_sum.download().reshape(m, srep), d_max.download().reshape(m, srep)
+    assert (max1 == max_r).all()
+    assert np.allclose(_to_f32(sum1, stats_dtype), _to_f32(sum_r, stats_dtype), rtol=2e-3)
+    assert np.allclose(_to_f32(d_y.download().reshape(m, k), dtype), _to_f32(y_r, dtype), rtol=1e-3, atol=1e-6)
+    # second tile, update: the inputs are the first step's device outputs
+    d_sum2, d_max2 = ab.empty((m, srep), np_s), ab.empty((m, srep), np_s)
+    ab.check(ab.softmax_flash_v2(ab.to_dev(s2), d_y, d_sum2, d_max2, d_em, d_sum, d_max, m, k, dtype, stats_dtype, True, brc))
+    ab.sync()
+    y2_r, sum2_r, max2_r, em_r = orc.softmax_flash_v2(s2, dtype, stats_dtype, in_sum=sum1, in_max=max1, brc=brc)
+    sum2, max2 = d_sum2.download().reshape(m, srep), d_max2.download().reshape(m, srep)
+    assert (max2 == max2_r).all()
+    assert np.allclose(_to_f32(sum2, stats_dtype), _to_f32(sum2_r, stats_dtype), rtol=2e-3)
+    assert np.allclose(_to_f32(d_em.download().reshape(m, erep), dtype), _to_f32(em_r, dtype), rtol=2e-3, atol=1e-6)
+    assert np.allclose(_to_f32(d_y.download().reshape(m, k), dtype), _to_f32(y2_r, dtype), rtol=1e-3, atol=1e-6)
+    both = np.concatenate([_to_f32(s1, dtype), _to_f32(s2, dtype)], axis=1).astype(np.float64)
+    ident = np.exp(both - _to_f32(max2, stats_dtype)[:, :1].astype(np.float64)).sum(axis=1)
+    assert np.allclose(_to_f32(sum2, stats_dtype)[:, 0], ident, rtol=4e-3 if stats_dtype == 1 else 1e-3)
