@@ -15,7 +15,18 @@
 namespace ascb200 {
 namespace {
 
-constexpr int TILE_K = 256;  // K rows per block: 8 KB of source, contiguous in NZ
+constexpr int TILE_K = 512;  // K rows per block: 16 KB of source, contiguous in NZ
+
+// 4 x 4 byte transpose: in r[j] byte b = element (row j, column b); out c[b] byte j = the same element.
+__device__ __forceinline__ void transpose4x4_bytes(const uint32_t (&r)[4], uint32_t (&c)[4])
+{
+    const uint32_t t0 = __byte_perm(r[0], r[1], 0x5140), t1 = __byte_perm(r[2], r[3], 0x5140);  // columns 0,1 of rows (0,1) / (2,3)
+    const uint32_t t2 = __byte_perm(r[0], r[1], 0x7362), t3 = __byte_perm(r[2], r[3], 0x7362);  // columns 2,3
+    c[0] = __byte_perm(t0, t1, 0x5410);
+    c[1] = __byte_perm(t0, t1, 0x7632);
+    c[2] = __byte_perm(t2, t3, 0x5410);
+    c[3] = __byte_perm(t2, t3, 0x7632);
+}
 
 // grid = groups * (n / C0) * k_tiles blocks of 256 threads
 template <int ESZ, bool TO_NK>
@@ -29,8 +40,16 @@ __global__ void __launch_bounds__(256) nz_unpack_kernel(const uint8_t* __restric
     const int nb = (blockIdx.x / k_tiles) % n_blocks;
     const size_t g = blockIdx.x / (static_cast<size_t>(k_tiles) * n_blocks);
     const int k0 = kt * TILE_K;
-    const int rows = min(TILE_K, k - k0);
+    const int rows = min(TILE_K, k - k0);  // a multiple of 16
     const uint4* s16 = reinterpret_cast<const uint4*>(src + ((g * n_blocks + nb) * static_cast<size_t>(k) + k0) * 32);
+    if constexpr (!TO_NK) {
+        // [K, N]: every K row of the block is 32 contiguous bytes of the output row
+        for (int i = threadIdx.x; i < rows * 2; i += 256) {
+            const uint4 v = __ldg(s16 + i);
+            uint8_t* out = dst + ((g * k + k0 + (i >> 1)) * static_cast<size_t>(n) + static_cast<size_t>(nb) * C0) * ESZ + (i & 1) * 16;
+            *reinterpret_cast<uint4*>(out) = v;
+        }
+    } else {
     for (int i = threadIdx.x; i < rows * 2; i += 256) {
         const uint4 v = __ldg(s16 + i);
         uint32_t* t = tile + (i >> 1) * ROW_WORDS + (i & 1) * 4;
@@ -40,29 +59,42 @@ __global__ void __launch_bounds__(256) nz_unpack_kernel(const uint8_t* __restric
         t[3] = v.w;
     }
     __syncthreads();
-    if constexpr (TO_NK) {
-        // output row = one column of the block: 16-byte vectors of 16 / ESZ consecutive K
-        constexpr int KV = 16 / ESZ;
-        const int vec_per_row = rows / KV;  // rows is a multiple of 16
-        const uint8_t* tb = reinterpret_cast<const uint8_t*>(tile);
-        for (int v = threadIdx.x; v < C0 * vec_per_row; v += 256) {
-            const int nl = v % C0, kv = v / C0;
-            uint32_t w[4] = {0, 0, 0, 0};
+    if constexpr (ESZ == 1) {
+        // A thread owns 4 columns x 16 K: sixteen words in, four 4x4 byte transposes, one 16-byte vector out per column.
+        for (int task = threadIdx.x; task < 8 * (rows / 16); task += 256) {
+            const int nw = task & 7, kg = task >> 3;
+            uint32_t col[4][4];  // [column][quarter of the 16 K]
 #pragma unroll
-            for (int j = 0; j < KV; ++j) {
-                const uint8_t* e = tb + (kv * KV + j) * (ROW_WORDS * 4) + nl * ESZ;
-                if constexpr (ESZ == 1) w[j >> 2] |= static_cast<uint32_t>(e[0]) << (8 * (j & 3));
-                else w[j >> 1] |= static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(e)) << (16 * (j & 1));
+            for (int q = 0; q < 4; ++q) {
+                uint32_t r[4], c[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) r[j] = tile[(kg * 16 + q * 4 + j) * ROW_WORDS + nw];
+                transpose4x4_bytes(r, c);
+#pragma unroll
+                for (int b = 0; b < 4; ++b) col[b][q] = c[b];
             }
-            uint8_t* out = dst + ((g * n + static_cast<size_t>(nb) * C0 + nl) * k + k0 + kv * KV) * ESZ;
-            *reinterpret_cast<uint4*>(out) = make_uint4(w[0], w[1], w[2], w[3]);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                uint8_t* out = dst + (g * n + static_cast<size_t>(nb) * C0 + nw * 4 + b) * k + k0 + kg * 16;
+                *reinterpret_cast<uint4*>(out) = make_uint4(col[b][0], col[b][1], col[b][2], col[b][3]);
+            }
         }
     } else {
-        for (int i = threadIdx.x; i < rows * 2; i += 256) {
-            const uint32_t* t = tile + (i >> 1) * ROW_WORDS + (i & 1) * 4;
-            uint8_t* out = dst + ((g * k + k0 + (i >> 1)) * static_cast<size_t>(n) + static_cast<size_t>(nb) * C0) * ESZ + (i & 1) * 16;
-            *reinterpret_cast<uint4*>(out) = make_uint4(t[0], t[1], t[2], t[3]);
+        // 2-byte elements: a thread owns 2 columns x 8 K: eight words in, halves regrouped, one 16-byte vector per column.
+        for (int task = threadIdx.x; task < 8 * (rows / 8); task += 256) {
+            const int nw = task & 7, kg = task >> 3;
+            uint32_t lo[4], hi[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t a = tile[(kg * 8 + 2 * j) * ROW_WORDS + nw], b = tile[(kg * 8 + 2 * j + 1) * ROW_WORDS + nw];
+                lo[j] = __byte_perm(a, b, 0x5410);  // column 2 nw of rows (2j, 2j+1)
+                hi[j] = __byte_perm(a, b, 0x7632);  // column 2 nw + 1
+            }
+            uint8_t* out = dst + ((g * n + static_cast<size_t>(nb) * C0 + nw * 2) * k + k0 + kg * 8) * 2;
+            *reinterpret_cast<uint4*>(out) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            *reinterpret_cast<uint4*>(out + static_cast<size_t>(k) * 2) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
         }
+    }
     }
 }
 

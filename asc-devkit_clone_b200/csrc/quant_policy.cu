@@ -92,75 +92,155 @@ __device__ __forceinline__ ST pick(const QuantPolicyArgs& a, const void* base, i
     return p[static_cast<size_t>(row / a.group_size) * a.n + col];
 }
 
-// One thread: eight consecutive elements of one row (n % 8 == 0), or one element (generic).
-template <typename T, typename ST, int DST, bool VEC8>
+// Row and column of element i, and the scale / offset of that element.
+template <typename T, typename ST, int DST>
+__device__ __forceinline__ void quant_policy_params(const QuantPolicyArgs& a, size_t i, ST off_scalar, int& row, int& col, ST& s, ST& o)
+{
+    // 32-bit division where the element index allows it (a 64-bit division costs more than the conversion of the eight values)
+    row = i < 0xFFFFFFFFull ? static_cast<int>(static_cast<uint32_t>(i) / static_cast<uint32_t>(a.n)) : static_cast<int>(i / a.n);
+    col = static_cast<int>(i - static_cast<size_t>(row) * a.n);
+    s = pick<T, ST, DST>(a, a.scale, row, col);
+    o = off_scalar;
+    if (a.has_offset && a.offset) o = pick<T, ST, DST>(a, a.offset, row, col);
+}
+
+// Converts STEP consecutive elements of one row starting at element index i (values already widened to fp32 in v);
+// s / o: scale and offset of the first element.
+template <typename T, typename ST, int DST, int STEP>
+__device__ __forceinline__ void quant_policy_store(const QuantPolicyArgs& a, size_t i, int row, int col, ST s, ST o, float (&v)[STEP])
+{
+    // groups are multiples of 32 columns: eight aligned columns share the scale unless it varies per column (kDim = 0)
+    const bool per_col = a.policy == POL_GROUP && a.k_dim == 0;
+#pragma unroll
+    for (int j = 0; j < STEP; ++j) {
+        if (per_col && j > 0) {
+            s = pick<T, ST, DST>(a, a.scale, row, col + j);
+            if (a.has_offset && a.offset) o = pick<T, ST, DST>(a, a.offset, row, col + j);
+        }
+        if constexpr (DST == ASCB200_FP8_E4M3 || DST == ASCB200_FP8_E5M2) {
+            // fp8: fp32 arithmetic whatever the scale's type
+            float r = __fmul_rn(v[j], to_f32<ST>(s));
+            v[j] = a.has_offset ? __fadd_rn(r, to_f32<ST>(o)) : r;
+        } else {
+            v[j] = mul_add_in<ST>(v[j], s, o, a.has_offset && DST != ASCB200_FP4_E2M1);
+        }
+    }
+    if constexpr (DST == ASCB200_FP4_E2M1) {
+        uint8_t* out = static_cast<uint8_t*>(a.dst) + i / 2;
+        if constexpr (STEP == 8) {
+            const uint32_t w = to_fp4_pair(v[0], v[1]) | (to_fp4_pair(v[2], v[3]) << 8) | (to_fp4_pair(v[4], v[5]) << 16) | (to_fp4_pair(v[6], v[7]) << 24);
+            *reinterpret_cast<uint32_t*>(out) = w;
+        } else {
+            *out = static_cast<uint8_t>(to_fp4_pair(v[0], v[1]));
+        }
+    } else {
+        uint8_t* out = static_cast<uint8_t*>(a.dst) + i;
+        if constexpr (STEP == 8) {
+            uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                w0 |= to_byte<DST>(v[j]) << (8 * j);
+                w1 |= to_byte<DST>(v[4 + j]) << (8 * j);
+            }
+            *reinterpret_cast<uint2*>(out) = make_uint2(w0, w1);
+        } else {
+            *out = static_cast<uint8_t>(to_byte<DST>(v[0]));
+        }
+    }
+}
+
+template <typename ST>
+__device__ __forceinline__ ST offset_as(float v)
+{
+    if constexpr (sizeof(ST) == 4) return v;
+    else if constexpr (std::is_same<ST, __half>::value) return __float2half_rn(v);
+    else return __float2bfloat16_rn(v);
+}
+
+// Vector form (n % 8 == 0): a block covers 256 x 4 groups of eight consecutive elements; every thread issues its four
+// 16-byte loads before it converts anything, so that enough bytes are in flight per SM to cover the HBM latency.
+// SHARED (n a multiple of 32, scale constant over 32 aligned columns): the four lanes that hold one aligned run of 32 columns
+// share its scale, so one load instruction per warp fetches the parameters of all 32 runs the warp converts (lane u*8 + j holds
+// those of lanes 4j .. 4j+3 in round u) and shuffles hand them out: three quarters fewer parameter loads per data load.
+template <typename T, typename ST, int DST, bool SHARED>
+__global__ void __launch_bounds__(256) quant_policy_vec_kernel(const QuantPolicyArgs a)
+{
+    constexpr int VPT = 4;
+    const size_t vecs = static_cast<size_t>(a.m) * a.n / 8;
+    const T* src = static_cast<const T*>(a.src);
+    const ST off_scalar = offset_as<ST>(a.offset_scalar);
+    const size_t base = static_cast<size_t>(blockIdx.x) * (256 * VPT) + threadIdx.x;
+    uint4 raw[VPT][sizeof(T) == 2 ? 1 : 2];
+    int row[VPT], col[VPT];
+    ST sc[VPT], of[VPT];
+    int my_row = 0, my_col = 0;
+    ST my_sc = off_scalar, my_of = off_scalar;
+    if constexpr (SHARED) {
+        const int lane = threadIdx.x & 31;
+        const size_t mine = base - lane + static_cast<size_t>(lane >> 3) * 256 + (lane & 7) * 4;
+        if (mine < vecs) quant_policy_params<T, ST, DST>(a, mine * 8, off_scalar, my_row, my_col, my_sc, my_of);
+    }
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const size_t vi = base + static_cast<size_t>(u) * 256;
+        if (vi < vecs) {
+            raw[u][0] = __ldg(reinterpret_cast<const uint4*>(src + vi * 8));
+            if constexpr (sizeof(T) == 4) raw[u][1] = __ldg(reinterpret_cast<const uint4*>(src + vi * 8) + 1);
+            if constexpr (!SHARED) quant_policy_params<T, ST, DST>(a, vi * 8, off_scalar, row[u], col[u], sc[u], of[u]);  // with the data loads
+        }
+    }
+    if constexpr (SHARED) {
+        const int lane = threadIdx.x & 31;
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) {
+            const int from = u * 8 + (lane >> 2);
+            row[u] = __shfl_sync(0xFFFFFFFFu, my_row, from);
+            col[u] = __shfl_sync(0xFFFFFFFFu, my_col, from) + (lane & 3) * 8;
+            if constexpr (sizeof(ST) == 4) {
+                sc[u] = __shfl_sync(0xFFFFFFFFu, my_sc, from);
+                of[u] = __shfl_sync(0xFFFFFFFFu, my_of, from);
+            } else {
+                const unsigned short sb = __shfl_sync(0xFFFFFFFFu, *reinterpret_cast<const unsigned short*>(&my_sc), from);
+                const unsigned short ob = __shfl_sync(0xFFFFFFFFu, *reinterpret_cast<const unsigned short*>(&my_of), from);
+                sc[u] = *reinterpret_cast<const ST*>(&sb);
+                of[u] = *reinterpret_cast<const ST*>(&ob);
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const size_t vi = base + static_cast<size_t>(u) * 256;
+        if (vi >= vecs) break;
+        float v[8];
+        if constexpr (sizeof(T) == 2) {
+            const T* e = reinterpret_cast<const T*>(&raw[u][0]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = to_f32<T>(e[j]);
+        } else {
+            const float* e = reinterpret_cast<const float*>(&raw[u][0]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = e[j];
+        }
+        quant_policy_store<T, ST, DST, 8>(a, vi * 8, row[u], col[u], sc[u], of[u], v);
+    }
+}
+
+// Generic form: one element (two for fp4) per thread, grid-stride.
+template <typename T, typename ST, int DST>
 __global__ void __launch_bounds__(256) quant_policy_kernel(const QuantPolicyArgs a)
 {
     const size_t total = static_cast<size_t>(a.m) * a.n;
     const T* src = static_cast<const T*>(a.src);
-    ST off_scalar;
-    if constexpr (sizeof(ST) == 4) off_scalar = a.offset_scalar;
-    else if constexpr (std::is_same<ST, __half>::value) off_scalar = __float2half_rn(a.offset_scalar);
-    else off_scalar = __float2bfloat16_rn(a.offset_scalar);
-    constexpr int STEP = VEC8 ? 8 : (DST == ASCB200_FP4_E2M1 ? 2 : 1);
+    const ST off_scalar = offset_as<ST>(a.offset_scalar);
+    constexpr int STEP = DST == ASCB200_FP4_E2M1 ? 2 : 1;
     for (size_t i = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * STEP; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x * STEP) {
-        const int row = static_cast<int>(i / a.n), col = static_cast<int>(i % a.n);
         float v[STEP];
-        if constexpr (VEC8) {
-            if constexpr (sizeof(T) == 2) {
-                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + i));
-                const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = to_f32<T>(e[j]);
-            } else {
-                const float4 r0 = __ldg(reinterpret_cast<const float4*>(src + i)), r1 = __ldg(reinterpret_cast<const float4*>(src + i) + 1);
-                v[0] = r0.x; v[1] = r0.y; v[2] = r0.z; v[3] = r0.w;
-                v[4] = r1.x; v[5] = r1.y; v[6] = r1.z; v[7] = r1.w;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < STEP; ++j) v[j] = to_f32<T>(src[i + j]);
-        }
-        // groups are multiples of 32 columns: eight aligned columns share the scale unless it varies per column (kDim = 0)
-        const bool per_col = a.policy == POL_GROUP && a.k_dim == 0;
-        ST s = pick<T, ST, DST>(a, a.scale, row, col), o = off_scalar;
-        if (a.has_offset && a.offset) o = pick<T, ST, DST>(a, a.offset, row, col);
-#pragma unroll
-        for (int j = 0; j < STEP; ++j) {
-            if (per_col && j > 0) {
-                s = pick<T, ST, DST>(a, a.scale, row, col + j);
-                if (a.has_offset && a.offset) o = pick<T, ST, DST>(a, a.offset, row, col + j);
-            }
-            if constexpr (DST == ASCB200_FP8_E4M3 || DST == ASCB200_FP8_E5M2) {
-                // fp8: fp32 arithmetic whatever the scale's type
-                float r = __fmul_rn(v[j], to_f32<ST>(s));
-                v[j] = a.has_offset ? __fadd_rn(r, to_f32<ST>(o)) : r;
-            } else {
-                v[j] = mul_add_in<ST>(v[j], s, o, a.has_offset && DST != ASCB200_FP4_E2M1);
-            }
-        }
-        if constexpr (DST == ASCB200_FP4_E2M1) {
-            uint8_t* out = static_cast<uint8_t*>(a.dst) + i / 2;
-            if constexpr (VEC8) {
-                const uint32_t w = to_fp4_pair(v[0], v[1]) | (to_fp4_pair(v[2], v[3]) << 8) | (to_fp4_pair(v[4], v[5]) << 16) | (to_fp4_pair(v[6], v[7]) << 24);
-                *reinterpret_cast<uint32_t*>(out) = w;
-            } else {
-                *out = static_cast<uint8_t>(to_fp4_pair(v[0], v[1]));
-            }
-        } else {
-            uint8_t* out = static_cast<uint8_t*>(a.dst) + i;
-            if constexpr (VEC8) {
-                uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    w0 |= to_byte<DST>(v[j]) << (8 * j);
-                    w1 |= to_byte<DST>(v[4 + j]) << (8 * j);
-                }
-                *reinterpret_cast<uint2*>(out) = make_uint2(w0, w1);
-            } else {
-                *out = static_cast<uint8_t>(to_byte<DST>(v[0]));
-            }
-        }
+        for (int j = 0; j < STEP; ++j) v[j] = to_f32<T>(src[i + j]);
+        int row, col;
+        ST sc, of;
+        quant_policy_params<T, ST, DST>(a, i, off_scalar, row, col, sc, of);
+        quant_policy_store<T, ST, DST, STEP>(a, i, row, col, sc, of, v);
     }
 }
 
@@ -168,11 +248,18 @@ template <typename T, typename ST, int DST>
 int launch_policy(const QuantPolicyArgs& a, bool vec8, int sms, cudaStream_t s)
 {
     const size_t total = static_cast<size_t>(a.m) * a.n;
-    const size_t step = vec8 ? 8 : (DST == ASCB200_FP4_E2M1 ? 2 : 1);
-    const size_t threads = (total + step - 1) / step;
-    const unsigned grid = static_cast<unsigned>(std::min<size_t>((threads + 255) / 256, static_cast<size_t>(sms) * 16));
-    if (vec8) quant_policy_kernel<T, ST, DST, true><<<grid, 256, 0, s>>>(a);
-    else quant_policy_kernel<T, ST, DST, false><<<grid, 256, 0, s>>>(a);
+    if (vec8) {
+        const size_t blocks = (total / 8 + 256 * 4 - 1) / (256 * 4);
+        if (blocks > 0x7FFFFFFFull) return ASCB200_ETOOBIG;
+        const bool shared = a.n % 32 == 0 && !(a.policy == POL_GROUP && a.k_dim == 0);
+        if (shared) quant_policy_vec_kernel<T, ST, DST, true><<<static_cast<unsigned>(blocks), 256, 0, s>>>(a);
+        else quant_policy_vec_kernel<T, ST, DST, false><<<static_cast<unsigned>(blocks), 256, 0, s>>>(a);
+    } else {
+        const size_t step = DST == ASCB200_FP4_E2M1 ? 2 : 1;
+        const size_t threads = (total + step - 1) / step;
+        const unsigned grid = static_cast<unsigned>(std::min<size_t>((threads + 255) / 256, static_cast<size_t>(sms) * 16));
+        quant_policy_kernel<T, ST, DST><<<grid, 256, 0, s>>>(a);
+    }
     ASCB200_CUDA(cudaGetLastError());
     return ASCB200_OK;
 }

@@ -405,15 +405,27 @@ int launch_dequant(const int32_t* src, void* dst, int m, int n, int cal, int n_d
 // (formulas of docs/zh/api/SIMD-API/adv_api/activation_functions/SoftMax_interface/SoftmaxFlashV2.md:49-63).  y is not normalised.
 // T: element type of x, y and expMax; ST: type of the max / sum tensors (T, or float with half data).  Arithmetic is fp32
 // inside, like the reference's half path.  Same row mapping as softmax_rows_kernel (row in registers, read once).
+// Volatile loads: the compiler keeps them where they are written (ahead of the row loads) instead of sinking them to
+// their first use after the row maximum, where each would add a memory latency to the row's critical path.
 template <typename ST> __device__ __forceinline__ float stat_load(const ST* p, size_t i);
-template <> __device__ __forceinline__ float stat_load<float>(const float* p, size_t i) { return __ldg(p + i); }
-template <> __device__ __forceinline__ float stat_load<__half>(const __half* p, size_t i) { return __half2float(__ldg(p + i)); }
+template <> __device__ __forceinline__ float stat_load<float>(const float* p, size_t i)
+{
+    float v;
+    asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p + i));
+    return v;
+}
+template <> __device__ __forceinline__ float stat_load<__half>(const __half* p, size_t i)
+{
+    unsigned short b;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(b) : "l"(p + i));
+    return __half2float(__ushort_as_half(b));
+}
 template <typename ST> __device__ __forceinline__ void stat_store(ST* p, size_t i, float v);
 template <> __device__ __forceinline__ void stat_store<float>(float* p, size_t i, float v) { p[i] = v; }
 template <> __device__ __forceinline__ void stat_store<__half>(__half* p, size_t i, float v) { p[i] = __float2half_rn(clamp_half_range(v)); }
 
 template <typename T, typename ST, int TPR, int NCHUNK, bool UPDATE>
-__global__ void __launch_bounds__(TPR > 32 ? TPR : 128)
+__global__ void __launch_bounds__(TPR > 32 ? TPR : 128, TPR > 32 ? 1 : 5)
 softmax_flash_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, ST* __restrict__ sum_out, ST* __restrict__ max_out, T* __restrict__ expmax_out,
                           const ST* __restrict__ in_sum, const ST* __restrict__ in_max, int m, int k, int stats_rep, int expmax_rep)
 {
@@ -422,9 +434,31 @@ softmax_flash_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, ST* __
     const int nchunks = k / VEC;
     const int t = TPR > 32 ? threadIdx.x : (threadIdx.x & 31);
     const int row = TPR > 32 ? blockIdx.x : blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= m) return;  // whole warp / block leaves together
+    // The previous statistics are requested ahead of the row loads (asked for after the row maximum they would put a second
+    // memory latency on every row's critical path) and by as few load instructions as possible: every extra load
+    // instruction per row measurably costs bandwidth here (two loads per warp: 4.6 TB/s, one: 5.4, one per four rows: see
+    // the benchmark).  Warp rows: eight threads of the block fetch the values of its four rows and pass them through shared
+    // memory; block rows: threads 0 and 1.
+    __shared__ float prev[2][4];
+    const bool valid = row < m;
+    float old_max = 0.0f, old_sum = 0.0f, exp_max = 1.0f;
+    if constexpr (UPDATE) {
+        if constexpr (TPR == 32) {
+            const int r = blockIdx.x * 4 + (threadIdx.x >> 1);
+            if (threadIdx.x < 8 && r < m) old_max = stat_load<ST>((threadIdx.x & 1) ? in_sum : in_max, static_cast<size_t>(r) * stats_rep);
+        } else {
+            if (threadIdx.x < 2) old_max = stat_load<ST>((threadIdx.x & 1) ? in_sum : in_max, static_cast<size_t>(row) * stats_rep);
+        }
+    }
     uint4 raw[NCHUNK];
-    softmax_load_row<T, TPR, NCHUNK>(src + static_cast<size_t>(row) * k, t, nchunks, raw);
+    if (valid) softmax_load_row<T, TPR, NCHUNK>(src + static_cast<size_t>(row) * k, t, nchunks, raw);
+    if constexpr (UPDATE) {
+        if (threadIdx.x < (TPR == 32 ? 8 : 2)) prev[threadIdx.x & 1][TPR == 32 ? (threadIdx.x >> 1) : 0] = old_max;
+        __syncthreads();  // reached by every thread of the block; the row loads stay in flight meanwhile
+        old_max = prev[0][TPR == 32 ? (threadIdx.x >> 5) : 0];
+        old_sum = prev[1][TPR == 32 ? (threadIdx.x >> 5) : 0];
+    }
+    if (!valid) return;  // whole warp / block leaves together
     float v[NCHUNK * VEC];
     float mx = kNegInf;
 #pragma unroll
@@ -453,10 +487,7 @@ softmax_flash_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, ST* __
         for (int j = 0; j < VEC; ++j) mx = fmaxf(mx, v[i * VEC + j]);
     }
     mx = row_reduce_max<TPR>(mx, red);
-    float old_max = 0.0f, old_sum = 0.0f, exp_max = 1.0f;
     if constexpr (UPDATE) {
-        old_max = stat_load<ST>(in_max, static_cast<size_t>(row) * stats_rep);
-        old_sum = stat_load<ST>(in_sum, static_cast<size_t>(row) * stats_rep);
         mx = fmaxf(mx, old_max);
         exp_max = exp2_approx((old_max - mx) * 1.4426950408889634f);
     }

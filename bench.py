@@ -550,8 +550,177 @@ class GroupedRefShape(Grouped):
         return np.full(self.G, self.MTOT // self.G, np.int64)
 
 
+class RowOp(Workload):
+    """Common part of the HBM-bound layout / quantisation kernels of the widened path: replicas per rank, bytes per second."""
+    unit, bound, unit_scale, scaling = "GB/s", "hbm", 1e9, "weak"
+
+    def units_total(self):
+        return float(self.per_step_bytes()) * self.world
+
+    def units_rank(self):
+        return float(self.per_step_bytes())
+
+    def peak(self, peaks):
+        return peaks["hbm_gbs"], "GB/s", "measured STREAM-style copy"
+
+    def e2e_setup(self):
+        self.pin = PinnedSet(self.ab, self.h2d_arrays(), sum(n for _, n in self.d2h_buffers(0)))
+
+    def e2e_bytes(self):
+        return sum(a.nbytes for a in self.h2d_arrays()), sum(n for _, n in self.d2h_buffers(0))
+
+    def e2e_step(self, i, stream):
+        s = i % self.sets
+        self.pin.h2d(self.h2d_targets(s), stream)
+        self.step(i, stream)
+        off = 0
+        for buf, n in self.d2h_buffers(s):
+            self.pin.d2h(buf, stream, off)
+            off += n
+
+
+class QuantPerGroupFp4(RowOp):
+    name = "ascendquant_per_group32_fp16_to_fp4_32768x8192"
+    metric, dtype = "AscendQuant PER_GROUP (fp16 -> packed fp4 e2m1, fp32 scale per 32 columns) bandwidth", "f16"
+    M, N, G = 32768, 8192, 32
+
+    def __init__(self, ab, rank, world, sets):
+        from gpu_util import f16_bits
+        self.ab, self.rank, self.world = ab, rank, world
+        rng = np.random.default_rng(0xA5C00010 + rank)
+        self.x_h = np.tile(f16_bits(rng.standard_normal((4096, self.N), dtype=np.float32)), (self.M // 4096, 1))
+        self.s_h = np.tile(rng.uniform(0.75, 1.5, (4096, self.N // self.G)).astype(np.float32), (self.M // 4096, 1))
+        self.sets = sets = 2   # 704 MB per set
+        self.x = [ab.to_dev(self.x_h) for _ in range(sets)]
+        self.sc = [ab.to_dev(self.s_h) for _ in range(sets)]
+        self.q = [ab.empty((self.M, self.N // 2), np.uint8) for _ in range(sets)]
+        self.config = {"workload": self.name, "M": self.M, "N": self.N, "group": self.G, "shard": f"replica per rank x{world}",
+                       "cache": f"{sets} rotating buffer sets ({sets * self.per_step_bytes() // 2**20} MiB > L2)"}
+
+    def per_step_bytes(self):
+        return self.M * self.N * 2 + self.M * self.N // 2 + self.M * (self.N // self.G) * 4
+
+    def step(self, i, stream=None):
+        ab, s = self.ab, i % self.sets
+        ab.check(ab.quant_policy(self.x[s], self.q[s], self.M, self.N, ab.F16, ab.F32, ab.FP4, ab.QUANT_PER_GROUP, self.sc[s], k_dim=1,
+                                 group_size=self.G, stream=stream))
+
+    def h2d_arrays(self):
+        return [self.x_h, self.s_h]
+
+    def h2d_targets(self, s):
+        return [self.x[s], self.sc[s]]
+
+    def d2h_buffers(self, s):
+        return [(self.q[s], self.M * self.N // 2)]
+
+    def cpu_sample(self, orc, rows):
+        rows = min(rows * 8, self.M)
+        t0 = time.perf_counter()
+        orc.quant_policy(self.x_h[:rows], self.s_h[:rows], orc.F16, orc.F32, orc.FP4_E2M1, 3, k_dim=1, group_size=self.G)
+        return time.perf_counter() - t0, rows * (self.per_step_bytes() / self.M), f"{rows} of {self.M} rows"
+
+    def verify(self, orc):
+        ref = orc.quant_policy(self.x_h[:64], self.s_h[:64], orc.F16, orc.F32, orc.FP4_E2M1, 3, k_dim=1, group_size=self.G)
+        return bool((self.q[0].download().reshape(self.M, self.N // 2)[:64] == ref).all())
+
+
+class SoftmaxFlashStep(RowOp):
+    name = "softmaxflashv2_update_262144x2048_fp16"
+    metric, dtype = "SoftmaxFlashV2 update step (fp16 data, fp32 statistics) bandwidth", "f16"
+    M, K = 262144, 2048
+
+    def __init__(self, ab, rank, world, sets):
+        from gpu_util import f16_bits
+        self.ab, self.rank, self.world = ab, rank, world
+        rng = np.random.default_rng(0xA5C00011 + rank)
+        self.x_h = np.tile(f16_bits(rng.standard_normal((4096, self.K), dtype=np.float32) * 3.0), (self.M // 4096, 1))
+        self.in_max_h = np.repeat(rng.uniform(2, 8, (self.M, 1)).astype(np.float32), 8, axis=1)
+        self.in_sum_h = np.repeat(rng.uniform(100, 200, (self.M, 1)).astype(np.float32), 8, axis=1)
+        self.sets = sets = 2   # 2.2 GB per set
+        self.x = [ab.to_dev(self.x_h) for _ in range(sets)]
+        self.y = [ab.empty((self.M, self.K), np.uint16) for _ in range(sets)]
+        self.in_max, self.in_sum = ab.to_dev(self.in_max_h), ab.to_dev(self.in_sum_h)
+        self.mx, self.sm = ab.empty((self.M, 8), np.float32), ab.empty((self.M, 8), np.float32)
+        self.em = ab.empty((self.M, 16), np.uint16)
+        self.config = {"workload": self.name, "M": self.M, "K": self.K, "shard": f"replica per rank x{world}",
+                       "cache": f"{sets} rotating buffer sets ({sets * self.per_step_bytes() // 2**20} MiB > L2)"}
+
+    def per_step_bytes(self):
+        return self.M * self.K * 4 + self.M * (4 * 32 + 32)  # x in, y out; four statistics blocks of 32 bytes and expMax per row
+
+    def step(self, i, stream=None):
+        ab, s = self.ab, i % self.sets
+        ab.check(ab.softmax_flash_v2(self.x[s], self.y[s], self.sm, self.mx, self.em, self.in_sum, self.in_max, self.M, self.K, ab.F16, ab.F32,
+                                     True, True, stream=stream))
+
+    def h2d_arrays(self):
+        return [self.x_h, self.in_max_h, self.in_sum_h]
+
+    def h2d_targets(self, s):
+        return [self.x[s], self.in_max, self.in_sum]
+
+    def d2h_buffers(self, s):
+        return [(self.y[s], self.M * self.K * 2), (self.sm, self.M * 32), (self.mx, self.M * 32), (self.em, self.M * 32)]
+
+    def cpu_sample(self, orc, rows):
+        rows = min(rows * 16, self.M)
+        t0 = time.perf_counter()
+        orc.softmax_flash_v2(self.x_h[:rows], orc.F16, orc.F32, in_sum=self.in_sum_h[:rows], in_max=self.in_max_h[:rows])
+        return time.perf_counter() - t0, rows * (self.per_step_bytes() / self.M), f"{rows} of {self.M} rows"
+
+    def verify(self, orc):
+        y, s, mx, em = orc.softmax_flash_v2(self.x_h[:64], orc.F16, orc.F32, in_sum=self.in_sum_h[:64], in_max=self.in_max_h[:64])
+        got_y = orc.f16_bits_to_f32(self.y[0].download().reshape(self.M, self.K)[:64])
+        got_s = self.sm.download().reshape(self.M, 8)[:64]
+        return bool(np.allclose(got_y, orc.f16_bits_to_f32(y), rtol=1e-3, atol=1e-6) and np.allclose(got_s, s, rtol=2e-3) and
+                    (self.mx.download().reshape(self.M, 8)[:64] == mx).all())
+
+
+class NzUnpack(RowOp):
+    name = "nz_weight_unpack_int8_16x7168x2048"
+    metric, dtype = "fractal NZ -> K-major weight unpack bandwidth", "u8"
+    G, K, N = 16, 7168, 2048
+
+    def __init__(self, ab, rank, world, sets):
+        self.ab, self.rank, self.world = ab, rank, world
+        rng = np.random.default_rng(0xA5C00012 + rank)
+        self.w_h = rng.integers(-128, 128, (self.G, self.N // 32, self.K // 16, 16, 32), dtype=np.int8)  # already in NZ order
+        self.sets = sets = 2   # 470 MB per set
+        self.w = [ab.to_dev(self.w_h) for _ in range(sets)]
+        self.o = [ab.empty((self.G, self.N, self.K), np.int8) for _ in range(sets)]
+        self.config = {"workload": self.name, "groups": self.G, "K": self.K, "N": self.N, "shard": f"replica per rank x{world}",
+                       "cache": f"{sets} rotating buffer sets ({sets * self.per_step_bytes() // 2**20} MiB > L2)"}
+
+    def per_step_bytes(self):
+        return 2 * self.G * self.K * self.N
+
+    def step(self, i, stream=None):
+        ab, s = self.ab, i % self.sets
+        ab.check(ab.nz_unpack(self.w[s], self.o[s], self.G, self.K, self.N, 1, True, stream=stream))
+
+    def h2d_arrays(self):
+        return [self.w_h]
+
+    def h2d_targets(self, s):
+        return [self.w[s]]
+
+    def d2h_buffers(self, s):
+        return [(self.o[s], self.G * self.K * self.N)]
+
+    def cpu_sample(self, orc, rows):
+        t0 = time.perf_counter()
+        np.ascontiguousarray(self.w_h[:2].transpose(0, 1, 4, 2, 3))  # [g, n/32, 32, k/16, 16] = [g, n, k]
+        return time.perf_counter() - t0, 2.0 * 2 * self.K * self.N, "2 of 16 groups (numpy transpose, one thread)"
+
+    def verify(self, orc):
+        ref = self.w_h[:1].transpose(0, 1, 4, 2, 3).reshape(1, self.N, self.K)
+        return bool((self.o[0].download().reshape(self.G, self.N, self.K)[:1] == ref).all())
+
+
 WORKLOADS = {"a8w8": A8W8, "grouped": Grouped, "mxfp4": MXFP4, "softmax_quant": SoftmaxQuant, "softmax_quant_x64": SoftmaxQuantLarge,
-             "fp16": FP16, "fp16_8192": FP16Large, "grouped_ref_shape": GroupedRefShape}
+             "fp16": FP16, "fp16_8192": FP16Large, "grouped_ref_shape": GroupedRefShape, "quant_per_group_fp4": QuantPerGroupFp4,
+             "softmax_flash_v2": SoftmaxFlashStep, "nz_unpack": NzUnpack}
 
 
 class PinnedSet:
