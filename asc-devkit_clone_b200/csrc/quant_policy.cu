@@ -288,62 +288,133 @@ struct DequantPolicyArgs {
     int per_group, k_dim, group_size, scale_cols;
 };
 
+template <typename ST>
+__device__ __forceinline__ float dequant_scale_at(const DequantPolicyArgs& a, int row, int col)
+{
+    const ST* scale = static_cast<const ST*>(a.scale);
+    const size_t si = !a.per_group ? static_cast<size_t>(row)
+                      : a.k_dim == 1 ? static_cast<size_t>(row) * a.scale_cols + col / a.group_size
+                                     : static_cast<size_t>(row / a.group_size) * a.n + col;
+    return to_f32<ST>(scale[si]);
+}
+template <typename DT>
+__device__ __forceinline__ void dequant_store8(DT* out, const float (&v)[8])
+{
+    if constexpr (std::is_same<DT, float>::value) {
+        reinterpret_cast<float4*>(out)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(out)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if constexpr (std::is_same<DT, __half>::value) {
+                const __half2 h = __halves2half2(f32_to_f16_sat(v[2 * j]), f32_to_f16_sat(v[2 * j + 1]));
+                w[j] = *reinterpret_cast<const uint32_t*>(&h);
+            } else {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                w[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+        }
+        *reinterpret_cast<uint4*>(out) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// Vector form (n % 8 == 0): eight elements per thread, two vectors per thread in flight; with SHARED (n % 32 == 0, scale
+// constant over 32 aligned columns) one lane in four fetches the scale and shuffles hand it to its neighbours.
+template <typename SRC, typename ST, typename DT, bool SHARED>
+__global__ void __launch_bounds__(256) dequant_policy_vec_kernel(const DequantPolicyArgs a)
+{
+    constexpr int VPT = 2;
+    const size_t vecs = static_cast<size_t>(a.m) * a.n / 8;
+    const SRC* src = static_cast<const SRC*>(a.src);
+    DT* dst = static_cast<DT*>(a.dst);
+    const size_t base = static_cast<size_t>(blockIdx.x) * (256 * VPT) + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    uint4 raw[VPT][2];
+    float sc[VPT] = {};
+    int row[VPT] = {}, col[VPT] = {};
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const size_t vi = base + static_cast<size_t>(u) * 256;
+        if (vi < vecs) {
+            const size_t e = vi * 8;
+            raw[u][0] = __ldg(reinterpret_cast<const uint4*>(src + e));
+            raw[u][1] = __ldg(reinterpret_cast<const uint4*>(src + e) + 1);
+            row[u] = e < 0xFFFFFFFFull ? static_cast<int>(static_cast<uint32_t>(e) / static_cast<uint32_t>(a.n)) : static_cast<int>(e / a.n);
+            col[u] = static_cast<int>(e - static_cast<size_t>(row[u]) * a.n);
+            if (!SHARED || (lane & 3) == 0) sc[u] = dequant_scale_at<ST>(a, row[u], col[u]);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const size_t vi = base + static_cast<size_t>(u) * 256;
+        if constexpr (SHARED) sc[u] = __shfl_sync(0xFFFFFFFFu, sc[u], lane & ~3);  // lanes 4j .. 4j+3 are valid together
+        if (vi >= vecs) continue;
+        float v[8];
+        const bool per_col = a.per_group && a.k_dim == 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t w = j < 4 ? (&raw[u][0].x)[j] : (&raw[u][1].x)[j - 4];
+            const float x = std::is_same<SRC, float>::value ? __uint_as_float(w) : __int2float_rn(static_cast<int>(w));
+            const float s = (per_col && j > 0) ? dequant_scale_at<ST>(a, row[u], col[u] + j) : sc[u];
+            v[j] = __fmul_rn(x, s);
+        }
+        dequant_store8<DT>(dst + vi * 8, v);
+    }
+}
+
+// Generic form: one element per thread, grid-stride.
 template <typename SRC, typename ST, typename DT>
 __global__ void __launch_bounds__(256) dequant_policy_kernel(const DequantPolicyArgs a)
 {
     const size_t total = static_cast<size_t>(a.m) * a.n;
     const SRC* src = static_cast<const SRC*>(a.src);
-    const ST* scale = static_cast<const ST*>(a.scale);
     DT* dst = static_cast<DT*>(a.dst);
-    const bool vec = a.n % 4 == 0;  // host checked the pointers' alignment
-    const int step = vec ? 4 : 1;
-    for (size_t i = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * step; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x * step) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const int row = static_cast<int>(i / a.n), col = static_cast<int>(i % a.n);
-        float x[4];
-        if (vec) {
-            if constexpr (std::is_same<SRC, float>::value) {
-                const float4 r = __ldg(reinterpret_cast<const float4*>(src + i));
-                x[0] = r.x; x[1] = r.y; x[2] = r.z; x[3] = r.w;
-            } else {
-                const int4 r = __ldg(reinterpret_cast<const int4*>(src + i));
-                x[0] = __int2float_rn(r.x); x[1] = __int2float_rn(r.y); x[2] = __int2float_rn(r.z); x[3] = __int2float_rn(r.w);
-            }
-        } else {
-            x[0] = static_cast<float>(src[i]);
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (j >= step) break;
-            const size_t si = !a.per_group ? static_cast<size_t>(row)
-                              : a.k_dim == 1 ? static_cast<size_t>(row) * a.scale_cols + (col + j) / a.group_size
-                                             : static_cast<size_t>(row / a.group_size) * a.n + col + j;
-            const float v = __fmul_rn(x[j], to_f32<ST>(scale[si]));
-            if constexpr (std::is_same<DT, float>::value) dst[i + j] = v;
-            else if constexpr (std::is_same<DT, __half>::value) dst[i + j] = f32_to_f16_sat(v);
-            else dst[i + j] = __float2bfloat16_rn(v);
-        }
+        const float v = __fmul_rn(static_cast<float>(src[i]), dequant_scale_at<ST>(a, row, col));
+        if constexpr (std::is_same<DT, float>::value) dst[i] = v;
+        else if constexpr (std::is_same<DT, __half>::value) dst[i] = f32_to_f16_sat(v);
+        else dst[i] = __float2bfloat16_rn(v);
     }
 }
 
-template <typename SRC, typename ST>
-int dequant_policy_dst(const DequantPolicyArgs& a, int dst_dtype, unsigned grid, cudaStream_t s)
+template <typename SRC, typename ST, typename DT>
+int dequant_policy_launch(const DequantPolicyArgs& a, bool vec, unsigned grid, cudaStream_t s)
 {
+    if (vec) {
+        const size_t blocks = (static_cast<size_t>(a.m) * a.n / 8 + 511) / 512;
+        if (blocks > 0x7FFFFFFFull) return ASCB200_ETOOBIG;
+        const bool shared = a.n % 32 == 0 && !(a.per_group && a.k_dim == 0);
+        if (shared) dequant_policy_vec_kernel<SRC, ST, DT, true><<<static_cast<unsigned>(blocks), 256, 0, s>>>(a);
+        else dequant_policy_vec_kernel<SRC, ST, DT, false><<<static_cast<unsigned>(blocks), 256, 0, s>>>(a);
+    } else {
+        dequant_policy_kernel<SRC, ST, DT><<<grid, 256, 0, s>>>(a);
+    }
+    return ASCB200_OK;
+}
+
+template <typename SRC, typename ST>
+int dequant_policy_dst(const DequantPolicyArgs& a, int dst_dtype, bool vec, unsigned grid, cudaStream_t s)
+{
+    int rc;
     switch (dst_dtype) {
-        case ASCB200_F32: dequant_policy_kernel<SRC, ST, float><<<grid, 256, 0, s>>>(a); break;
-        case ASCB200_F16: dequant_policy_kernel<SRC, ST, __half><<<grid, 256, 0, s>>>(a); break;
-        case ASCB200_BF16: dequant_policy_kernel<SRC, ST, __nv_bfloat16><<<grid, 256, 0, s>>>(a); break;
+        case ASCB200_F32: rc = dequant_policy_launch<SRC, ST, float>(a, vec, grid, s); break;
+        case ASCB200_F16: rc = dequant_policy_launch<SRC, ST, __half>(a, vec, grid, s); break;
+        case ASCB200_BF16: rc = dequant_policy_launch<SRC, ST, __nv_bfloat16>(a, vec, grid, s); break;
         default: return ASCB200_EUNSUPPORTED;
     }
+    if (rc != ASCB200_OK) return rc;
     ASCB200_CUDA(cudaGetLastError());
     return ASCB200_OK;
 }
 template <typename SRC>
-int dequant_policy_scale(const DequantPolicyArgs& a, int scale_dtype, int dst_dtype, unsigned grid, cudaStream_t s)
+int dequant_policy_scale(const DequantPolicyArgs& a, int scale_dtype, int dst_dtype, bool vec, unsigned grid, cudaStream_t s)
 {
     switch (scale_dtype) {
-        case ASCB200_F32: return dequant_policy_dst<SRC, float>(a, dst_dtype, grid, s);
-        case ASCB200_F16: return dequant_policy_dst<SRC, __half>(a, dst_dtype, grid, s);
-        case ASCB200_BF16: return dequant_policy_dst<SRC, __nv_bfloat16>(a, dst_dtype, grid, s);
+        case ASCB200_F32: return dequant_policy_dst<SRC, float>(a, dst_dtype, vec, grid, s);
+        case ASCB200_F16: return dequant_policy_dst<SRC, __half>(a, dst_dtype, vec, grid, s);
+        case ASCB200_BF16: return dequant_policy_dst<SRC, __nv_bfloat16>(a, dst_dtype, vec, grid, s);
         default: return ASCB200_EUNSUPPORTED;
     }
 }
@@ -373,11 +444,12 @@ extern "C" int ascb200_dequant_policy(const void* src, void* dst, int32_t m, int
     a.k_dim = k_dim;
     a.group_size = a.per_group ? group_size : 1;
     a.scale_cols = a.per_group ? (n + group_size - 1) / group_size : 1;
-    const size_t threads = (static_cast<size_t>(m) * n + 3) / 4;
+    const size_t threads = static_cast<size_t>(m) * n;
     const unsigned grid = static_cast<unsigned>(std::min<size_t>((threads + 255) / 256, static_cast<size_t>(st->sm_count) * 16));
+    const bool vec = n % 8 == 0 && aligned_to(dst, 16);  // src is 16-byte aligned (checked above)
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (src_dtype == ASCB200_S32) return dequant_policy_scale<int32_t>(a, scale_dtype, dst_dtype, grid, s);
-    return dequant_policy_scale<float>(a, scale_dtype, dst_dtype, grid, s);
+    if (src_dtype == ASCB200_S32) return dequant_policy_scale<int32_t>(a, scale_dtype, dst_dtype, vec, grid, s);
+    return dequant_policy_scale<float>(a, scale_dtype, dst_dtype, vec, grid, s);
 }
 
 extern "C" int ascb200_quant_policy(const void* src, void* dst, int32_t m, int32_t n, int32_t src_dtype, int32_t scale_dtype, int32_t dst_dtype,

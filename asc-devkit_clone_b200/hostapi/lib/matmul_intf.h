@@ -4,7 +4,10 @@
 // implementation (L1/L0 depths, double-buffer switches, iterate order) are accepted and have no effect
 // on results.
 #pragma once
+#include <type_traits>
+
 #include "../kernel_operator.h"
+#include "matmul_config.h"
 
 namespace AscendC {
 
@@ -25,18 +28,6 @@ struct MatmulTypeWithScale : public MatmulType<POSITION, FORMAT, TYPE, ISTRANS> 
     constexpr static bool isScaleTrans = SCALE_ISTRANS;
 };
 
-// The fields of include/adv_api/matmul/matmul_config.h:143-207 that can change results; the presets keep their names.
-struct MatmulConfig {
-    bool enableRelu = false;       // fixpipe ReLU on the way out
-    bool enableSetBias = true;
-    bool isBiasBatch = true;
-    bool enableQuantVector = true;
-};
-constexpr MatmulConfig CFG_NORM = {};
-constexpr MatmulConfig CFG_MDL = {};
-constexpr MatmulConfig MM_CFG_BB = {};
-constexpr MatmulConfig CFG_IBSHARE_NORM = {};
-
 // impl/adv_api/detail/matmul/utils/matmul_call_back.h:26-39: only the all-default callback set is supported.
 template <void* DataCopyOut = nullptr, void* CopyA1 = nullptr, void* CopyB1 = nullptr>
 struct MatmulCallBackFunc {};
@@ -49,12 +40,17 @@ template <> struct KindOf<half> { static constexpr int value = ASCB200_KIND_F16;
 template <> struct KindOf<bfloat16_t> { static constexpr int value = ASCB200_KIND_BF16; };
 template <> struct KindOf<int8_t> { static constexpr int value = ASCB200_KIND_S8; };
 template <> struct KindOf<fp4x2_e2m1_t> { static constexpr int value = ASCB200_KIND_MXFP4; };
+// The fifth argument is a MatmulConfig or, for constant tiling, the MatmulApiStaticTiling made from one.
+constexpr const MatmulConfig& ToMatmulConfig(const MatmulConfig& cfg) { return cfg; }
+constexpr const MatmulConfig& ToMatmulConfig(const MatmulApiStaticTiling& tiling) { return tiling.cfg; }
 }  // namespace detail
 
-template <class A_TYPE, class B_TYPE, class C_TYPE, class BIAS_TYPE = C_TYPE, const MatmulConfig& MM_CFG = CFG_NORM,
+template <class A_TYPE, class B_TYPE, class C_TYPE, class BIAS_TYPE = C_TYPE, const auto& MM_CFG_OR_TILING = CFG_NORM,
           class MM_CB = MatmulCallBackFunc<>, class POLICY = MatmulPolicyDefault>
 class Matmul {
 public:
+    static constexpr const MatmulConfig& MM_CFG = detail::ToMatmulConfig(MM_CFG_OR_TILING);
+    static constexpr bool hasStaticTiling = std::is_same<std::decay_t<decltype(MM_CFG_OR_TILING)>, MatmulApiStaticTiling>::value;
     using SrcAT = typename A_TYPE::T;
     using SrcBT = typename B_TYPE::T;
     using DstT = typename C_TYPE::T;
@@ -73,7 +69,24 @@ public:
 
     void Init(const TCubeTiling* cubeTiling, TPipe* tpipe = nullptr)
     {
-        tiling_ = *cubeTiling;
+        if (cubeTiling) {
+            tiling_ = *cubeTiling;
+        } else {
+            // constant tiling: the shapes are compile-time constants of the fifth template argument; SetOrgShape refines them
+            tiling_ = TCubeTiling{};
+            if constexpr (hasStaticTiling) {
+                tiling_.M = MM_CFG_OR_TILING.M;
+                tiling_.N = MM_CFG_OR_TILING.N;
+                tiling_.Ka = MM_CFG_OR_TILING.Ka;
+                tiling_.Kb = MM_CFG_OR_TILING.Kb;
+                tiling_.singleCoreM = MM_CFG_OR_TILING.singleCoreM;
+                tiling_.singleCoreN = MM_CFG_OR_TILING.singleCoreN;
+                tiling_.singleCoreK = MM_CFG_OR_TILING.singleCoreK;
+                tiling_.isBias = MM_CFG_OR_TILING.isBias;
+            } else {
+                AscendC::detail::Latch(ASCB200_EINVAL, "Matmul::Init (null tiling without a constant tiling)");
+            }
+        }
         stream_ = tpipe ? tpipe->GetStream() : AscendC::detail::CurrentStream();
         orgM_ = tiling_.M;
         orgN_ = tiling_.N;

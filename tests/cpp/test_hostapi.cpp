@@ -72,7 +72,7 @@ public:
     }
     AscendC::Matmul<AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, AType>, AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, BType>,
                     AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, CType>, AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, BiasType>,
-                    AscendC::CFG_NORM>
+                    CFG_NORM>
         matmulObj;
 
 private:
@@ -480,6 +480,69 @@ static void TestSoftmaxFlashV2()
     std::printf("SoftmaxFlashV2 two tiles: ok\n");
 }
 
+// Constant tiling as in the reference's matmul_constant_tiling example: the shapes are template constants
+// (GetMMConfig + GetMatmulApiTiling), the object is initialised without a TCubeTiling.
+static constexpr MatmulShapeParams kConstShape = {256, 384, 128, 128, 256, 64};
+static constexpr MatmulApiStaticTiling GetCustomConstantCFG()
+{
+    using A_TYPE = AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, half>;
+    using C_TYPE = AscendC::MatmulType<AscendC::TPosition::GM, CubeFormat::ND, float>;
+    MatmulConfig mmCFG = GetMMConfig<MatmulConfigMode::CONFIG_MDL>(kConstShape, MatmulFuncParams{false, false, false, false, 0,
+                                                                                                   IterateOrder::UNDEF, ScheduleType::INNER_PRODUCT,
+                                                                                                   true, false, false, false, false, false, false,
+                                                                                                   /*enableRelu=*/true});
+    mmCFG.enUnitFlag = true;
+    auto constantCFG = AscendC::GetMatmulApiTiling<A_TYPE, A_TYPE, C_TYPE, C_TYPE>(mmCFG);
+    constantCFG.depthA1 = 8;
+    constantCFG.depthB1 = 8;
+    return constantCFG;
+}
+static constexpr MatmulApiStaticTiling kConstantCfg = GetCustomConstantCFG();
+static_assert(kConstantCfg.singleCoreM == 256 && kConstantCfg.N == 384 && kConstantCfg.baseK == 64 && kConstantCfg.cfg.doMultiDataLoad &&
+                  kConstantCfg.cfg.enableRelu && kConstantCfg.depthA1 == 8,
+              "constant tiling is evaluated at compile time");
+static void TestConstantTiling()
+{
+    using namespace AscendC;
+    const int M = 256, N = 384, K = 128;
+    std::mt19937 rng(3);
+    std::uniform_real_distribution<float> u(-1.f, 1.f);
+    std::vector<half> a(M * K), b(K * N);
+    for (auto& v : a) v = half(u(rng));
+    for (auto& v : b) v = half(u(rng));
+    DevBuf<half> dA(a), dB(b);
+    DevBuf<float> dC(static_cast<size_t>(M) * N);
+    {
+        TPipe pipe;
+        using A_TYPE = MatmulType<TPosition::GM, CubeFormat::ND, half>;
+        using C_TYPE = MatmulType<TPosition::GM, CubeFormat::ND, float>;
+        Matmul<A_TYPE, A_TYPE, C_TYPE, C_TYPE, kConstantCfg> mm;
+        REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, static_cast<TCubeTiling*>(nullptr));
+        GlobalTensor<half> ga, gb;
+        GlobalTensor<float> gc;
+        ga.SetGlobalBuffer(dA.p, a.size());
+        gb.SetGlobalBuffer(dB.p, b.size());
+        gc.SetGlobalBuffer(dC.p, dC.n);
+        mm.SetOrgShape(M, N, K);
+        mm.SetTensorA(ga);
+        mm.SetTensorB(gb);
+        mm.IterateAll(gc);
+        mm.End();
+    }
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<float> c = dC.Download();
+    int bad = 0;
+    for (int m = 0; m < M; m += 5)
+        for (int n = 0; n < N; n += 3) {
+            float acc = 0;
+            for (int k = 0; k < K; ++k) acc += static_cast<float>(a[m * K + k]) * static_cast<float>(b[k * N + n]);
+            acc = std::fmax(acc, 0.0f);  // enableRelu of the config
+            if (std::fabs(c[static_cast<size_t>(m) * N + n] - acc) > 1e-3 + 1e-2 * std::fabs(acc)) ++bad;
+        }
+    CHECK(bad == 0, "constant tiling + ReLU: %d wrong", bad);
+    std::printf("constant tiling (GetMMConfig / GetMatmulApiTiling): ok\n");
+}
+
 static void TestErrorLatch()
 {
     AscendC::ClearLastError();
@@ -505,6 +568,7 @@ int main()
     TestMatmulNzAtomicAlign();
     TestQuantPolicies();
     TestSoftmaxFlashV2();
+    TestConstantTiling();
     TestErrorLatch();
     std::printf(g_fail ? "%d checks failed\n" : "hostapi ok\n", g_fail);
     return g_fail ? 1 : 0;
