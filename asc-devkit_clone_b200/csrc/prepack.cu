@@ -33,8 +33,9 @@ template <int ESZ, bool TO_NK>
 __global__ void __launch_bounds__(256) nz_unpack_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int k, int n, int k_tiles)
 {
     constexpr int C0 = 32 / ESZ;
-    constexpr int ROW_WORDS = 9;  // 32 data bytes + 4 of padding per K row: column gathers spread over the banks
-    __shared__ uint32_t tile[TILE_K * ROW_WORDS];
+    // K row r sits at word r * 8 + (r / 16) * 4: 16 bytes of padding after every 16 rows, so that the lanes of a warp, which
+    // read the same column word of rows 16 apart, hit 32 different banks, and every row stays 16-byte aligned
+    __shared__ __align__(16) uint32_t tile[TILE_K * 8 + (TILE_K / 16) * 4];
     const int n_blocks = n / C0;
     const int kt = blockIdx.x % k_tiles;
     const int nb = (blockIdx.x / k_tiles) % n_blocks;
@@ -51,24 +52,25 @@ __global__ void __launch_bounds__(256) nz_unpack_kernel(const uint8_t* __restric
         }
     } else {
     for (int i = threadIdx.x; i < rows * 2; i += 256) {
-        const uint4 v = __ldg(s16 + i);
-        uint32_t* t = tile + (i >> 1) * ROW_WORDS + (i & 1) * 4;
-        t[0] = v.x;
-        t[1] = v.y;
-        t[2] = v.z;
-        t[3] = v.w;
+        const int r = i >> 1;
+        *reinterpret_cast<uint4*>(tile + r * 8 + (r >> 4) * 4 + (i & 1) * 4) = __ldg(s16 + i);
     }
     __syncthreads();
+    const auto word_at = [&](int r, int w) { return tile[r * 8 + (r >> 4) * 4 + w]; };
     if constexpr (ESZ == 1) {
         // A thread owns 4 columns x 16 K: sixteen words in, four 4x4 byte transposes, one 16-byte vector out per column.
-        for (int task = threadIdx.x; task < 8 * (rows / 16); task += 256) {
-            const int nw = task & 7, kg = task >> 3;
+        // Eight neighbouring lanes take eight consecutive K groups of the same columns: a store instruction of the warp
+        // then writes 128 contiguous bytes to each of four output rows.
+        static_assert(TILE_K / 16 * 8 == 256, "one task per thread");
+        for (int task = threadIdx.x; task < 256; task += 256) {
+            const int kg = (task & 7) + (task >> 6) * 8, nw = (task >> 3) & 7;
+            if (kg >= rows / 16) continue;
             uint32_t col[4][4];  // [column][quarter of the 16 K]
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint32_t r[4], c[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) r[j] = tile[(kg * 16 + q * 4 + j) * ROW_WORDS + nw];
+                for (int j = 0; j < 4; ++j) r[j] = word_at(kg * 16 + q * 4 + j, nw);
                 transpose4x4_bytes(r, c);
 #pragma unroll
                 for (int b = 0; b < 4; ++b) col[b][q] = c[b];
@@ -86,7 +88,7 @@ __global__ void __launch_bounds__(256) nz_unpack_kernel(const uint8_t* __restric
             uint32_t lo[4], hi[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint32_t a = tile[(kg * 8 + 2 * j) * ROW_WORDS + nw], b = tile[(kg * 8 + 2 * j + 1) * ROW_WORDS + nw];
+                const uint32_t a = word_at(kg * 8 + 2 * j, nw), b = word_at(kg * 8 + 2 * j + 1, nw);
                 lo[j] = __byte_perm(a, b, 0x5410);  // column 2 nw of rows (2j, 2j+1)
                 hi[j] = __byte_perm(a, b, 0x7632);  // column 2 nw + 1
             }

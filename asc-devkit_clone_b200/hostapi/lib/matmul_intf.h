@@ -246,6 +246,40 @@ public:
         if (sync) done_ = true;
     }
 
+    // IterateBatch(gm, batchA, batchB, enSequentialWrite, matrixStrideA, matrixStrideB, matrixStrideC, enPartialSum, enAtomic)
+    // (include/adv_api/matmul/matmul_client.h:1024-1027; use: examples/.../batch_matmul/batch_matmul.asc:193), NORMAL layout: A holds
+    // batchA matrices [M, K] (or [K, M]), B batchB matrices, C max(batchA, batchB) matrices, each `matrixStride` elements
+    // after the previous one (0 = densely packed); the smaller batch count is broadcast (it must divide the larger).
+    // One launch per matrix pair; the bias is per batch when MM_CFG.isBiasBatch, else shared.
+    void IterateBatch(const GlobalTensor<DstT>& gm, uint32_t batchA, uint32_t batchB, bool enSequentialWrite, const uint32_t matrixStrideA = 0,
+                      const uint32_t matrixStrideB = 0, const uint32_t matrixStrideC = 0, const bool enPartialSum = false, const uint8_t enAtomic = 0)
+    {
+        (void)enPartialSum;
+        if (batchA == 0 || batchB == 0 || enSequentialWrite) {
+            AscendC::detail::Latch(batchA == 0 || batchB == 0 ? ASCB200_EINVAL : ASCB200_EUNSUPPORTED, "Matmul::IterateBatch");
+            return;
+        }
+        const uint32_t batch = batchA > batchB ? batchA : batchB;
+        if (batch % batchA != 0 || batch % batchB != 0) {
+            AscendC::detail::Latch(ASCB200_EINVAL, "Matmul::IterateBatch (batch counts must divide each other)");
+            return;
+        }
+        const size_t strideA = matrixStrideA ? matrixStrideA : static_cast<size_t>(singleM_) * singleK_ / elemsPerStorage;
+        const size_t strideB = matrixStrideB ? matrixStrideB : static_cast<size_t>(singleK_) * singleN_ / elemsPerStorage;
+        const size_t strideC = matrixStrideC ? matrixStrideC : static_cast<size_t>(singleM_) * singleN_;
+        const SrcAT* a0 = a_;
+        const SrcBT* b0 = b_;
+        const BiasT* bias0 = bias_;
+        for (uint32_t i = 0; i < batch; ++i) {
+            a_ = a0 + (i / (batch / batchA)) * strideA;
+            b_ = b0 + (i / (batch / batchB)) * strideB;
+            if (biasOn_ && MM_CFG.isBiasBatch) bias_ = bias0 + static_cast<size_t>(i) * singleN_;
+            IterateAll<false>(gm[i * strideC], enAtomic);
+        }
+        a_ = a0;
+        b_ = b0;
+        bias_ = bias0;
+    }
     // Iterate / GetTensorC pair: the first Iterate() computes the whole block into the tensor that the
     // following GetTensorC names; later Iterate() calls report completion.
     template <bool sync = true>

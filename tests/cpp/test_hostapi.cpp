@@ -543,6 +543,54 @@ static void TestConstantTiling()
     std::printf("constant tiling (GetMMConfig / GetMatmulApiTiling): ok\n");
 }
 
+// IterateBatch, NORMAL layout: four A matrices against one shared (broadcast) B, transposed B as in the batch example.
+static void TestIterateBatch()
+{
+    using namespace AscendC;
+    const int BATCH = 4, M = 96, N = 160, K = 64;
+    std::mt19937 rng(9);
+    std::uniform_int_distribution<int> u(-5, 5);
+    std::vector<int8_t> a(BATCH * M * K), b(N * K);
+    for (auto& v : a) v = static_cast<int8_t>(u(rng));
+    for (auto& v : b) v = static_cast<int8_t>(u(rng));
+    DevBuf<int8_t> dA(a), dB(b);
+    DevBuf<int32_t> dC(static_cast<size_t>(BATCH) * M * N);
+    TCubeTiling tiling{};
+    tiling.M = tiling.singleCoreM = M;
+    tiling.N = tiling.singleCoreN = N;
+    tiling.Ka = tiling.Kb = tiling.singleCoreK = K;
+    tiling.BatchNum = BATCH;
+    {
+        TPipe pipe;
+        using T8 = MatmulType<TPosition::GM, CubeFormat::ND, int8_t>;
+        using T8T = MatmulType<TPosition::GM, CubeFormat::ND, int8_t, true>;
+        using T32 = MatmulType<TPosition::GM, CubeFormat::ND, int32_t>;
+        Matmul<T8, T8T, T32, T32> mm;
+        REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, &tiling);
+        GlobalTensor<int8_t> ga, gb;
+        GlobalTensor<int32_t> gc;
+        ga.SetGlobalBuffer(dA.p, a.size());
+        gb.SetGlobalBuffer(dB.p, b.size());
+        gc.SetGlobalBuffer(dC.p, dC.n);
+        mm.SetTensorA(ga, false);
+        mm.SetTensorB(gb, true);  // B stored [N, K]
+        mm.IterateBatch(gc, BATCH, 1, false);
+        mm.End();
+    }
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<int32_t> c = dC.Download();
+    int bad = 0;
+    for (int i = 0; i < BATCH; ++i)
+        for (int m = 0; m < M; ++m)
+            for (int n = 0; n < N; ++n) {
+                int32_t acc = 0;
+                for (int k = 0; k < K; ++k) acc += static_cast<int32_t>(a[(i * M + m) * K + k]) * b[n * K + k];
+                if (c[(static_cast<size_t>(i) * M + m) * N + n] != acc) ++bad;
+            }
+    CHECK(bad == 0, "IterateBatch: %d wrong", bad);
+    std::printf("IterateBatch (4 x A, shared B): ok\n");
+}
+
 static void TestErrorLatch()
 {
     AscendC::ClearLastError();
@@ -569,6 +617,7 @@ int main()
     TestQuantPolicies();
     TestSoftmaxFlashV2();
     TestConstantTiling();
+    TestIterateBatch();
     TestErrorLatch();
     std::printf(g_fail ? "%d checks failed\n" : "hostapi ok\n", g_fail);
     return g_fail ? 1 : 0;
