@@ -583,6 +583,7 @@ class QuantPerGroupFp4(RowOp):
     name = "ascendquant_per_group32_fp16_to_fp4_32768x8192"
     metric, dtype = "AscendQuant PER_GROUP (fp16 -> packed fp4 e2m1, fp32 scale per 32 columns) bandwidth", "f16"
     M, N, G = 32768, 8192, 32
+    traffic_1gpu = 570.5e6 + 120.6e6   # profiles/quant_policy_vec_kernel_per_group32_fp16_fp4_32768x8192.md
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
@@ -629,6 +630,7 @@ class SoftmaxFlashStep(RowOp):
     name = "softmaxflashv2_update_262144x2048_fp16"
     metric, dtype = "SoftmaxFlashV2 update step (fp16 data, fp32 statistics) bandwidth", "f16"
     M, K = 262144, 2048
+    traffic_1gpu = 1.0906e9 + 1.0412e9   # profiles/softmax_flash_rows_kernel_update_262144x2048_fp16.md
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
@@ -681,6 +683,7 @@ class NzUnpack(RowOp):
     name = "nz_weight_unpack_int8_16x7168x2048"
     metric, dtype = "fractal NZ -> K-major weight unpack bandwidth", "u8"
     G, K, N = 16, 7168, 2048
+    traffic_1gpu = 234.9e6 + 181.7e6   # profiles/nz_unpack_kernel_int8_16x7168x2048.md
 
     def __init__(self, ab, rank, world, sets):
         self.ab, self.rank, self.world = ab, rank, world
