@@ -63,6 +63,7 @@ struct GemmParams {
     const uint8_t* sfb;
     int sf_kc;               // 512-byte chunks per 128-row block in sfa / sfb
     int pair_n;              // CTA-pair kernels for fp16 / bf16 / int8: columns per tile (multiple of 16, at most 256)
+    int allow_m64;           // fp16 / bf16 / int8, single-CTA kernel: tiles of at most 64 rows use the 64-row instruction
     uint32_t idesc;
     uint32_t* status;
     EpiParams epi;
@@ -94,6 +95,7 @@ struct Cfg {
 
 struct TileInfo {
     int row0, row_end, n0, n_end, group;  // n_end: first column after the tile
+    int m64;  // the tile holds at most 64 rows (of its group, or of the matrix) and is multiplied with the 64-row instruction
 };
 
 // Tensor maps of the outputs (rank 2, box 32 x 32, swizzle = bytes of one box row).
@@ -160,12 +162,14 @@ __device__ __forceinline__ bool locate_tile(const GemmParams& p, int tile, int n
         t.row_end = row_start[cursor + 1];
         t.n0 = (local / m_tiles) * BLOCK_N;
         t.n_end = t.n0 + BLOCK_N;
+        t.m64 = p.allow_m64 && t.row_end - t.row0 <= 64;
     } else {
         t.group = 0;
         t.row0 = (tile % num_m) * BLOCK_M;
         t.row_end = p.m;
         t.n0 = (tile / num_m) * BLOCK_N;
         t.n_end = t.n0 + BLOCK_N;
+        t.m64 = p.allow_m64 && t.row_end - t.row0 <= 64;
     }
     return true;
 }
@@ -190,6 +194,7 @@ __device__ __forceinline__ bool locate_pair_tile(const GemmParams& p, int tile, 
         t.n0 = (tile / num_m) * bn;
     }
     t.n_end = t.n0 + bn;
+    t.m64 = 0;
     return true;
 }
 
@@ -507,13 +512,14 @@ template <bool ACC_INT, int MODE, int DT, int BLOCK_N>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInfo& t, const OutMaps& outs, uint32_t stage_smem, int stage_bytes,
                                               uint32_t t_addr, int quad, int lane, int chunk0, int chunk1)
 {
-    const int row = t.row0 + quad * 32 + lane;
-    const bool row_ok = row < t.row_end;
+    // 128-row tiles: lane l of quadrant q holds row 32 q + l; 64-row tiles: lanes 0-15 hold rows 16 q + l
+    const int row = t.m64 ? t.row0 + quad * 16 + lane : t.row0 + quad * 32 + lane;
+    const bool row_ok = row < t.row_end && !(t.m64 && lane >= 16);
     const float tok = (MODE == ASCB200_EPI_DEQUANT_TOKEN_CHANNEL && row_ok && p.epi.tok) ? __ldg(p.epi.tok + row) : 1.0f;
     EpiStage st;
     st.row_base = t.row0 + quad * 32;
     // bulk stores clip at the matrix edge only: a group that ends inside this warp's rows is stored from registers
-    const bool rows_mine = p.groups == 0 || st.row_base + 32 <= t.row_end;
+    const bool rows_mine = !t.m64 && (p.groups == 0 || st.row_base + 32 <= t.row_end);
     constexpr bool BYTE_OUT = DT == OUT_S8 || DT == OUT_E4M3 || DT == OUT_E5M2;
     constexpr int C_BYTES = BYTE_OUT ? 1024 : 2048;
     const bool stage_c = (DT == OUT_F16 || DT == OUT_BF16 || BYTE_OUT) && p.epi.tma_c && rows_mine && C_BYTES <= stage_bytes;
@@ -799,13 +805,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
             const uint32_t acc_full = smem_u32(&acc_full_bar[acc_stage]);
             const uint32_t sfb_off = static_cast<uint32_t>(t.n0 % 128) / 32;  // a 192-wide tile may start mid-way in a 128-row scale block
+            // A tile that holds at most 64 rows (the tail of a group or of the matrix) runs the M = 64 form of the instruction (M / 16 in
+            // bits 24-28 of the descriptor): half the multiplications, and under the power cap half the energy, of rows
+            // that would be thrown away.  Its accumulator rows 16 q .. 16 q + 15 land in lanes 0-15 of TMEM quadrant q.
+            const uint32_t idesc = t.m64 ? ((p.idesc & ~(0x1Fu << 24)) | (4u << 24)) : p.idesc;
             const int last = p.num_k_blocks - 1;
             for (int kb = 0; kb <= last; ++kb) {
                 ok = mbar_wait(cur.full_bar, cur.phase, abort_word, p.status);
                 if (!ok) break;
                 tc_fence_after();
                 if (elect_one()) {
-                    issue_k_block<KIND, false, C::SF_B_BLOCKS>(cur, d_tmem, hi_word, a_k16, b_k16, p.idesc, idesc_hi_sf, sfb_off, kb == 0);
+                    issue_k_block<KIND, false, C::SF_B_BLOCKS>(cur, d_tmem, hi_word, a_k16, b_k16, idesc, idesc_hi_sf, sfb_off, kb == 0);
                     if (kb == last) tc_commit(acc_full);
                 }
                 __syncwarp();
@@ -1419,6 +1429,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     p.b_mn = d->trans_b ? 0 : 1;
     p.groups = grouped ? groups : 0;
     p.pair_n = block_n;
+    p.allow_m64 = kind != ASCB200_KIND_MXFP4 && !(getenv("ASCB200_NO_M64") && getenv("ASCB200_NO_M64")[0] == '1');
     p.group_counts = reinterpret_cast<const long long*>(group_counts);
     p.status = fixed ? fixed->status_dev : st->status_dev;
     p.epi = e;
