@@ -191,7 +191,7 @@ class Grouped(Workload):
     metric, unit, dtype = "grouped quant-GEMM throughput (int8, fused dequant)", "TOPS", "s8"
     G, MTOT, K, N = 64, 32768, 7168, 2048
     OUT, ACT = "BF16", 0
-    traffic_1gpu = 1.2225e9 + 0.1235e9   # profiles/gemm_tc_kernel_int8_grouped_64groups_M32768_K7168_N2048.md
+    traffic_1gpu = 1.2107e9 + 0.1229e9   # profiles/gemm_tc_kernel_int8_grouped_64groups_M32768_K7168_N2048.md
 
     def counts(self):
         return dirichlet_counts(self.G, self.MTOT, 0xA5C00003)
