@@ -97,7 +97,7 @@ class Workload:
     bound = "tensor"
     scaling = "strong"
     kernels_per_step = 1
-    published = None  # (value, note) of a like-for-like number in BASELINE.md
+    published = None  # (value, note) of a like-for-like number the reference publishes (other hardware)
     # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, per launch, from the ncu capture summarised in
     # profiles/ (1 GPU, whole configuration); None where no capture exists
     traffic_1gpu = None
@@ -272,7 +272,7 @@ class MXFP4(Workload):
     M = K = N = 8192
     kernels_per_step = 3  # two scale re-tiling launches + the GEMM
     traffic_1gpu = 94.2e6 + 167.3e6    # profiles/gemm_tc_pair_kernel_mxfp4_8192x8192x8192.md
-    published = (1614.0, "Ascend 950PR basic-API MXFP4 8192^3, bf16 out (BASELINE.md)")
+    published = (1614.0, "Ascend 950PR basic-API MXFP4 8192^3, bf16 out; the reference's published figure")
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import mx_quantize, quant_params
@@ -485,7 +485,7 @@ class FP16Large(Workload):
     name = "matmul_fp16_8192x8192x8192_fp16_out"
     metric, unit, dtype = "adv_api Matmul fp16 -> fp16, 8192^3 (the reference's published shape)", "TFLOPS", "f16"
     M = K = N = 8192
-    published = (427.0, "Ascend 950PR basic-API fp16 8192^3, 2572 us (BASELINE.md); Atlas A2 adv_api: 269")
+    published = (427.0, "Ascend 950PR basic-API fp16 8192^3, 2572 us (the reference's published figure); Atlas A2 adv_api: 269")
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
@@ -543,7 +543,7 @@ class GroupedRefShape(Grouped):
     metric = "grouped quant-GEMM throughput (the reference example's shape, FasterGelu, fp16 out)"
     G, MTOT, K, N = 8, 8192, 1024, 8192
     traffic_1gpu = None
-    published = (2.0 * 8192 * 1024 * 8192 / 204.129e-6 / 1e12, "Ascend 950PR, 204.129 us (BASELINE.md)")
+    published = (2.0 * 8192 * 1024 * 8192 / 204.129e-6 / 1e12, "Ascend 950PR, 204.129 us (the reference's published figure)")
     OUT, ACT = "F16", 1
 
     def counts(self):

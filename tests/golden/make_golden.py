@@ -1,8 +1,8 @@
 """Regenerate the golden fixtures in this folder from the reference's own Python code.
 
-Run once, in a container that has the reference tree mounted (default /root/reference):
+Run once, on a machine that has the reference tree (pass its location with --ref):
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py --ref <path of the reference tree>
 
 The reference ships no stored result vectors for this path (its kernel unit tests assert all-zero
 outputs); what it does ship are Python golden generators and fixpipe algorithm scripts.  This
@@ -245,7 +245,7 @@ def casts(ref):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("ASC_REFERENCE_ROOT", "reference"))
     args = ap.parse_args()
     for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, quant, dequant, grouped, mxfp4, casts):
         fn(args.ref)
