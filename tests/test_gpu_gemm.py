@@ -430,3 +430,17 @@ def test_grouped_reference_recipe_nz_weights(golden_dir):
     got = orc.f16_bits_to_f32(d_c.download())
     ok = np.isclose(got, g["golden_gelu"].astype(np.float32), rtol=1e-3, atol=1e-3)
     assert (~ok).mean() <= 1e-4  # the example's acceptance rule (verify_result.py:19-41)
+
+
+def test_gemm_small_m_uses_the_64_row_instruction_exactly():
+    """M <= 64 (decode-sized batches) and ragged last tiles take the M = 64 instruction: int32 results stay exact, for every
+    layout of B and with a bias, incl. the rows that sit in lanes 0-15 of each TMEM quadrant."""
+    ab = dev()
+    for m, n, k, trans_b in [(64, 512, 256, True), (33, 320, 384, False), (192 + 17, 256, 128, True), (1, 64, 128, True)]:
+        rng, a, b = _i8_inputs(m, n, k, False, trans_b, m * 3 + n)
+        bias = rng.integers(-1000, 1000, n).astype(np.int32)
+        d_c = ab.empty((m, n), np.int32)
+        d_c.fill(0x5A)
+        ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.S32, trans_b=trans_b, bias=ab.to_dev(bias)))
+        ab.sync()
+        assert (d_c.download().reshape(m, n) == orc.gemm_i8(a, b, bias, trans_b=trans_b)).all(), (m, n, k)

@@ -283,3 +283,29 @@ def test_softmax_flash_v2_two_steps(m, k, brc, dtype, stats_dtype):
     both = np.concatenate([_to_f32(s1, dtype), _to_f32(s2, dtype)], axis=1).astype(np.float64)
     ident = np.exp(both - _to_f32(max2, stats_dtype)[:, :1].astype(np.float64)).sum(axis=1)
     assert np.allclose(_to_f32(sum2, stats_dtype)[:, 0], ident, rtol=4e-3 if stats_dtype == 1 else 1e-3)
+
+
+def test_new_entry_points_edge_cases():
+    """Zero extents succeed without touching memory; bad extents, types and alignments are refused with the documented codes."""
+    ab = dev()
+    x = ab.to_dev(np.zeros((4, 64), np.float32))
+    s = ab.to_dev(np.ones(4, np.float32))
+    q = ab.empty((4, 64), np.uint8)
+    assert ab.quant_policy(x, q, 0, 64, ab.F32, ab.F32, ab.S8, ab.QUANT_PER_TOKEN, s) == 0
+    assert ab.quant_policy(x, q, 4, 0, ab.F32, ab.F32, ab.S8, ab.QUANT_PER_TOKEN, s) == 0
+    assert ab.quant_policy(None, q, 4, 64, ab.F32, ab.F32, ab.S8, ab.QUANT_PER_TOKEN, s) == ab.EINVAL
+    assert ab.dequant_policy(x, q, 0, 64, ab.F32, ab.F32, ab.F32, ab.DEQUANT_PER_TOKEN, s) == 0
+    assert ab.dequant_policy(x, q, 4, 64, ab.F16, ab.F32, ab.F32, ab.DEQUANT_PER_TOKEN, s) == ab.EUNSUPPORTED   # source is int32 or fp32
+    assert ab.dequant_policy(x, q, 4, 64, ab.F32, ab.F32, ab.F32, 2, s) == ab.EUNSUPPORTED                     # PER_CHANNEL_PER_GROUP
+    assert ab.dequant_policy(x, q, 4, 64, ab.F32, ab.F32, ab.F32, ab.DEQUANT_PER_GROUP, s, group_size=0) == ab.EINVAL
+    st = ab.empty((4, 8), np.float32)
+    y = ab.empty((4, 64), np.float32)
+    assert ab.softmax_flash_v2(x, y, st, st, None, None, None, 0, 64, ab.F32, ab.F32, False, True) == 0
+    assert ab.softmax_flash_v2(x, y, st, st, None, None, None, 4, 64, ab.F32, ab.F32, True, True) == ab.EINVAL       # update needs the previous statistics
+    assert ab.softmax_flash_v2(x, y, st, st, None, None, None, 4, 64, ab.F32, ab.F16, False, True) == ab.EUNSUPPORTED
+    assert ab.softmax_flash_v2(x, y, st, st, None, None, None, 4, 60, ab.F32, ab.F32, False, True) == ab.EALIGN       # rows are multiples of 32 bytes
+    w = ab.empty((1, 64, 32), np.int8)
+    assert ab.nz_unpack(w, w, 0, 64, 32, 1, True) == 0
+    assert ab.nz_unpack(w, w, 1, 60, 32, 1, True) == ab.EINVAL      # whole fractal blocks only
+    assert ab.nz_unpack(w, w, 1, 64, 32, 4, True) == ab.EUNSUPPORTED
+    ab.sync()
