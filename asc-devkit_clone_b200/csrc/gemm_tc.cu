@@ -1114,35 +1114,45 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // the scales of rows rb*128 .. +127 and K-blocks kc*4 .. +3 at byte (r%32)*16 + (r/32)*4 + (ks%4),
 // the order tcgen05.cp (32x128b, warpx4) expects.  Missing rows / K-blocks are filled with 127 (1.0).
 // One launch covers both operands: blocks [0, rb_a * kc_tiles) re-tile A, the rest B.  A block moves
-// 128 rows x 32 chunks through shared memory so that rows are read and chunks written as whole lines.
+// 128 rows x 8 chunks through shared memory so that rows are read as whole sectors and chunks written as whole lines.
 __global__ void __launch_bounds__(256)
 retile_scales_kernel(const uint8_t* __restrict__ src_a, uint32_t* __restrict__ dst_a, int rows_a, int rb_a, const uint8_t* __restrict__ src_b,
                      uint32_t* __restrict__ dst_b, int rows_b, int ks, int kc_count, int kc_tiles)
 {
-    __shared__ uint32_t tile[128][33];  // [position inside a chunk][chunk]
+    constexpr int CH = 8;  // chunks per block: 32 bytes of every row, four words per thread, all loads issued before any is used
+    __shared__ uint32_t tile[128][CH + 1];  // [position inside a chunk][chunk]
     int blk = blockIdx.x;
     const bool is_a = blk < rb_a * kc_tiles;
     if (!is_a) blk -= rb_a * kc_tiles;
     const uint8_t* src = is_a ? src_a : src_b;
     uint32_t* dst = is_a ? dst_a : dst_b;
     const int rows = is_a ? rows_a : rows_b;
-    const int rb = blk / kc_tiles, kc0 = (blk % kc_tiles) * 32;
+    const int rb = blk / kc_tiles, kc0 = (blk % kc_tiles) * CH;
     const bool words = (ks & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 3) == 0;
-    for (int idx = threadIdx.x; idx < 128 * 32; idx += 256) {
-        const int rl = idx >> 5, j = idx & 31;
-        const int r = rb * 128 + rl, k = (kc0 + j) * 4;
-        uint32_t w;
-        if (r < rows && k + 3 < ks && words) {
-            w = *reinterpret_cast<const uint32_t*>(src + static_cast<size_t>(r) * ks + k);
-        } else {
-            w = 0;
+    uint32_t w[4];
 #pragma unroll
-            for (int b = 0; b < 4; ++b) w |= ((r < rows && k + b < ks) ? static_cast<uint32_t>(src[static_cast<size_t>(r) * ks + k + b]) : 127u) << (8 * b);
+    for (int u = 0; u < 4; ++u) {
+        const int idx = threadIdx.x + u * 256;
+        const int rl = idx / CH, j = idx % CH;
+        const int r = rb * 128 + rl, k = (kc0 + j) * 4;
+        if (r < rows && k + 3 < ks && words) {
+            w[u] = __ldg(reinterpret_cast<const uint32_t*>(src + static_cast<size_t>(r) * ks + k));
+        } else {
+            w[u] = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) w[u] |= ((r < rows && k + b < ks) ? static_cast<uint32_t>(src[static_cast<size_t>(r) * ks + k + b]) : 127u) << (8 * b);
         }
-        tile[(rl & 31) * 4 + (rl >> 5)][j] = w;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int idx = threadIdx.x + u * 256;
+        const int rl = idx / CH, j = idx % CH;
+        tile[(rl & 31) * 4 + (rl >> 5)][j] = w[u];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < 128 * 32; idx += 256) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int idx = threadIdx.x + u * 256;
         const int j = idx >> 7, pos = idx & 127;
         if (kc0 + j < kc_count) dst[(static_cast<size_t>(rb) * kc_count + kc0 + j) * 128 + pos] = tile[pos][j];
     }
@@ -1450,7 +1460,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
             sfa = static_cast<uint8_t*>(st->scratch_dev);
         }
         uint8_t* sfb = sfa + bytes_a;
-        const int kc_tiles = (kc + 31) / 32;
+        const int kc_tiles = (kc + 7) / 8;
         retile_scales_kernel<<<(rba + rbb) * kc_tiles, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_a_dev), reinterpret_cast<uint32_t*>(sfa), m, rba,
                                                                          static_cast<const uint8_t*>(d->scale_b_dev), reinterpret_cast<uint32_t*>(sfb), n, ks, kc,
                                                                          kc_tiles);
