@@ -539,8 +539,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
         tmem_ld_32x32(t_addr + c * 32, r);
         tmem_ld_wait();
         // a chunk that the tile only half owns (tile widths are multiples of 16) is stored from registers: the
-        // bulk store's 32-column box would reach into the neighbouring tile
-        const bool whole = col0 + 32 <= t.n_end;
+        // bulk store's 32-column box would reach into the neighbouring tile.  So is a chunk that crosses the right edge of
+        // the matrix: the TMA unit clips columns in 16-byte pieces, not per element (an int8 matrix of 328 columns got 8
+        // bytes past its edge written), so only whole rows are left to its clipping.
+        const bool whole = col0 + 32 <= t.n_end && col0 + 32 <= p.n;
         epilogue_chunk<ACC_INT, MODE, DT>(r, p.epi, whole ? st : direct, row, row_ok, col0, min(whole ? 32 : t.n_end - col0, p.n - col0),
                                           static_cast<size_t>(col0), static_cast<size_t>(t.group) * p.n + col0, tok);
     }

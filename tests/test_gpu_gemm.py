@@ -444,3 +444,42 @@ def test_gemm_small_m_uses_the_64_row_instruction_exactly():
         ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.S32, trans_b=trans_b, bias=ab.to_dev(bias)))
         ab.sync()
         assert (d_c.download().reshape(m, n) == orc.gemm_i8(a, b, bias, trans_b=trans_b)).all(), (m, n, k)
+
+
+@pytest.mark.parametrize("m,n,k", [(300, 328, 256), (2304, 1376, 384)])   # single-CTA kernel / CTA pairs with a 160-column slab tile
+def test_gemm_writes_a_column_slab_of_a_wider_c(m, n, k):
+    """N-slab sharding writes C[:, slab] of a wider matrix (ldc > n): bulk stores clip at the slab's width, the columns beside
+    it keep their contents.  bf16 (staged), int8 (staged) and int32 (from registers) outputs; lda / ldb padded too."""
+    ab = dev()
+    rng = np.random.default_rng(m + n)
+    lda, ldb, ldc, col0 = k + 32, k + 64, (n + 200 + 15) // 16 * 16, 80   # every row and the slab start stay 16-byte aligned
+    a_full = rng.integers(-127, 128, (m, lda), dtype=np.int8)
+    b_full = rng.integers(-127, 128, (n, ldb), dtype=np.int8)
+    a, b = a_full[:, :k], b_full[:, :k]
+    acc = orc.gemm_i8(np.ascontiguousarray(a), np.ascontiguousarray(b), trans_b=True)
+    tok = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+    ch = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    d_a, d_b = ab.to_dev(a_full), ab.to_dev(b_full)
+    for c_dtype, np_t, fill in ((ab.BF16, np.uint16, 0x5A5A), (ab.S32, np.int32, 0x5A5A5A5A), (ab.S8, np.int8, 0x5A)):
+        d_c = ab.empty((m, ldc), np_t)
+        d_c.fill(0x5A)
+        esz = np.dtype(np_t).itemsize
+        view = d_c.ptr + col0 * esz   # the entry points take plain device addresses
+        if c_dtype == ab.BF16:
+            rc = ab.gemm(ab.KIND_S8, m, n, k, d_a, d_b, view, c_dtype, epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, trans_b=True, lda=lda, ldb=ldb, ldc=ldc,
+                         tok=ab.to_dev(tok), ch=ab.to_dev(ch))
+            ref = orc.dequant_tok_ch(acc, tok, ch, orc.BF16)
+        elif c_dtype == ab.S32:
+            rc = ab.gemm(ab.KIND_S8, m, n, k, d_a, d_b, view, c_dtype, trans_b=True, lda=lda, ldb=ldb, ldc=ldc)
+            ref = acc
+        else:
+            q = quant_params(rng.uniform(2e-5, 2e-4, n).astype(np.float32), np.zeros(n, np.int64))
+            rc = ab.gemm(ab.KIND_S8, m, n, k, d_a, d_b, view, c_dtype, epilogue=ab.EPI_FIXPIPE_QUANT, trans_b=True, lda=lda, ldb=ldb, ldc=ldc,
+                         quant=ab.to_dev(q))
+            ref = orc.fixpipe_req8(acc, q)
+        ab.check(rc)
+        ab.sync()
+        got = d_c.download().reshape(m, ldc)
+        assert (got[:, col0:col0 + n] == ref).all()
+        rest = np.concatenate([got[:, :col0], got[:, col0 + n:]], axis=1)
+        assert (rest.view(np.uint8) == 0x5A).all(), "columns outside the slab were written"
