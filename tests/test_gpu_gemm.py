@@ -483,3 +483,47 @@ def test_gemm_writes_a_column_slab_of_a_wider_c(m, n, k):
         assert (got[:, col0:col0 + n] == ref).all()
         rest = np.concatenate([got[:, :col0], got[:, col0 + n:]], axis=1)
         assert (rest.view(np.uint8) == 0x5A).all(), "columns outside the slab were written"
+
+
+def test_gemm_outputs_stay_inside_their_buffers():
+    """Exactly sized outputs followed by a guard area, ragged M and N, every output width and both kernels."""
+    ab = dev()
+    rng = np.random.default_rng(21)
+
+    def guarded(nbytes):
+        buf = ab.DevBuf(nbytes + 512)
+        buf.fill(0x5A)
+        return buf
+
+    def tail_intact(buf, used):
+        host = np.zeros(buf.nbytes, np.uint8)
+        ab.check(ab.lib().ascb200_memcpy_d2h(host.ctypes.data, buf.ptr, buf.nbytes, None))
+        ab.sync()
+        return bool((host[used:] == 0x5A).all())
+
+    esz = {ab.F32: 4, ab.F16: 2, ab.BF16: 2, ab.S8: 1, ab.S32: 4, ab.FP8_E4M3: 1}
+    for m, n, k in [(200, 328, 128), (2304 + 9, 1000, 256), (61, 72, 64)]:
+        a8 = ab.to_dev(rng.integers(-127, 128, (m, k), dtype=np.int8))
+        b8 = ab.to_dev(rng.integers(-127, 128, (n, k), dtype=np.int8))
+        q = ab.to_dev(quant_params(np.full(n, 1e-4, np.float32), np.zeros(n, np.int64)))
+        for c_dtype, kw in [(ab.S32, {}), (ab.S8, dict(epilogue=ab.EPI_FIXPIPE_QUANT, quant=q)), (ab.BF16, dict(epilogue=ab.EPI_FIXPIPE_QUANT, quant=q)),
+                            (ab.F16, dict(epilogue=ab.EPI_FIXPIPE_QUANT, quant=q))]:
+            c = guarded(m * n * esz[c_dtype])
+            ab.check(ab.gemm(ab.KIND_S8, m, n, k, a8, b8, c, c_dtype, trans_b=True, **kw))
+            ab.sync()
+            assert tail_intact(c, m * n * esz[c_dtype]), ("int8", m, n, c_dtype)
+        a16 = ab.to_dev(f16_bits(rng.uniform(-1, 1, (m, k)).astype(np.float32)))
+        b16 = ab.to_dev(f16_bits(rng.uniform(-1, 1, (n, k)).astype(np.float32)))
+        for c_dtype, c2_dtype in [(ab.F32, ab.BF16), (ab.F16, ab.F32), (ab.BF16, ab.F16)]:
+            c, c2 = guarded(m * n * esz[c_dtype]), guarded(m * n * esz[c2_dtype])
+            ab.check(ab.gemm(ab.KIND_F16, m, n, k, a16, b16, c, c_dtype, trans_b=True, c2=c2, c2_dtype=c2_dtype))
+            ab.sync()
+            assert tail_intact(c, m * n * esz[c_dtype]) and tail_intact(c2, m * n * esz[c2_dtype]), ("fp16", m, n, c_dtype)
+    for m, n, k in [(100, 200, 192), (2048 + 40, 2600, 256)]:
+        _, a, sa, b, sb = _mx_case(m, n, k, m)
+        q = ab.to_dev(quant_params(np.full(n, 0.5, np.float32), np.zeros(n, np.int64)))
+        c, c2 = guarded(m * n), guarded(m * n * 2)
+        ab.check(ab.gemm(ab.KIND_MXFP4, m, n, k, ab.to_dev(a), ab.to_dev(b), c, ab.S8, epilogue=ab.EPI_FIXPIPE_QUANT, trans_b=True, scale_a=ab.to_dev(sa),
+                         scale_b=ab.to_dev(sb), quant=q, c2=c2, c2_dtype=ab.BF16))
+        ab.sync()
+        assert tail_intact(c, m * n) and tail_intact(c2, m * n * 2), ("mxfp4", m, n)

@@ -309,3 +309,52 @@ def test_new_entry_points_edge_cases():
     assert ab.nz_unpack(w, w, 1, 60, 32, 1, True) == ab.EINVAL      # whole fractal blocks only
     assert ab.nz_unpack(w, w, 1, 64, 32, 4, True) == ab.EUNSUPPORTED
     ab.sync()
+
+
+def _guarded(ab, nbytes):
+    buf = ab.DevBuf(nbytes + 512)
+    buf.fill(0x5A)
+    return buf
+
+
+def test_row_kernels_write_nothing_past_their_outputs():
+    """Outputs sized exactly, followed by a guard area: ragged extents must not spill over the end of any destination."""
+    ab = dev()
+    rng = np.random.default_rng(11)
+
+    def tail_intact(buf, used):
+        host = np.zeros(buf.nbytes, np.uint8)
+        ab.check(ab.lib().ascb200_memcpy_d2h(host.ctypes.data, buf.ptr, buf.nbytes, None))
+        ab.sync()
+        return bool((host[used:] == 0x5A).all())
+
+    for m, n, dst, policy, group in [(37, 200, ab.S8, ab.QUANT_PER_TOKEN, 0), (5, 250, ab.FP4, ab.QUANT_PER_GROUP, 32), (9, 264, ab.FP8_E4M3, ab.QUANT_PER_GROUP, 64),
+                                     (1029, 32, ab.S8, ab.QUANT_PER_TOKEN, 0)]:
+        x = ab.to_dev(f16_bits(rng.standard_normal((m, n)).astype(np.float32)))
+        sshape = (m,) if policy == ab.QUANT_PER_TOKEN else (m, -(-n // group))
+        s = ab.to_dev(np.ones(sshape, np.float32))
+        used = m * n // 2 if dst == ab.FP4 else m * n
+        q = _guarded(ab, used)
+        ab.check(ab.quant_policy(x, q, m, n, ab.F16, ab.F32, dst, policy, s, k_dim=1, group_size=group))
+        ab.sync()
+        assert tail_intact(q, used), ("quant_policy", m, n)
+    for m, n, dst_dtype, esz in [(33, 200, ab.BF16, 2), (7, 24, ab.F32, 4), (5, 33, ab.F16, 2)]:
+        src = ab.to_dev(rng.integers(-1000, 1000, (m, n)).astype(np.int32))
+        s = ab.to_dev(np.ones(m, np.float32))
+        out = _guarded(ab, m * n * esz)
+        ab.check(ab.dequant_policy(src, out, m, n, ab.S32, ab.F32, dst_dtype, ab.DEQUANT_PER_TOKEN, s))
+        ab.sync()
+        assert tail_intact(out, m * n * esz), ("dequant_policy", m, n)
+    for rows, cols in [(37, 2048), (3, 64), (1025, 8)]:
+        x = ab.to_dev(f16_bits(rng.standard_normal((rows, cols)).astype(np.float32)))
+        sc = ab.to_dev(f16_bits(np.ones(cols, np.float32)))
+        q = _guarded(ab, rows * cols)
+        ab.check(ab.quant_per_channel(x, q, rows, cols, ab.F16, sc, None, 0.0))
+        ab.sync()
+        assert tail_intact(q, rows * cols), ("quant_per_channel", rows, cols)
+    for m, k in [(5, 2048), (131, 64), (3, 4096)]:
+        x = ab.to_dev(f16_bits(rng.standard_normal((m, k)).astype(np.float32)))
+        y, sm, mx = _guarded(ab, m * k * 2), _guarded(ab, m * 32), _guarded(ab, m * 32)
+        ab.check(ab.softmax_flash_v2(x, y, sm, mx, None, None, None, m, k, ab.F16, ab.F32, False, True))
+        ab.sync()
+        assert tail_intact(y, m * k * 2) and tail_intact(sm, m * 32) and tail_intact(mx, m * 32), ("softmax_flash_v2", m, k)
