@@ -28,6 +28,34 @@ int cuda_fail(cudaError_t e);           // records e, returns ASCB200_ECUDA
         if (e__ != cudaSuccess) return ::ascb200::cuda_fail(e__); \
     } while (0)
 
+// Launch with programmatic stream serialisation: the grid may be scheduled while the kernel before it in the stream is
+// still draining, which hides the launch latency between back-to-back kernels.  The kernel must execute
+// grid_dependency_wait() before it touches global memory; then nothing it reads or writes can race with its predecessor.
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+// Lets the next kernel of the stream start its launch, then waits until every kernel before this one has completed and its
+// writes are visible.  A no-op pair when the kernel was launched without the attribute.
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+#endif
+
 static inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 #ifdef __CUDACC__

@@ -205,6 +205,7 @@ softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __res
     constexpr int VEC = 16 / sizeof(T);
     __shared__ float red[32];
     const int nchunks = k / VEC;
+    grid_dependency_wait();
     if constexpr (TPR > 32) {
         const int row = blockIdx.x;
         uint4 raw[NCHUNK];
@@ -249,8 +250,8 @@ int launch_softmax(const T* src, T* dst, float* sum, float* mx, int8_t* q, const
     const int nchunks = k / VEC;
 #define ASCB200_SM_WARP(NC)                                                                                              \
     do {                                                                                                                  \
-        if (persist) softmax_rows_kernel<T, 32, NC, QUANT, true><<<warp_grid, kSoftmaxWarpBlock, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep); \
-        else softmax_rows_kernel<T, 32, NC, QUANT, false><<<(m + 3) / 4, 128, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep);                \
+        if (persist) ASCB200_CUDA(launch_pdl(softmax_rows_kernel<T, 32, NC, QUANT, true>, warp_grid, kSoftmaxWarpBlock, 0, st, src, dst, sum, mx, q, qs, qo, qos, m, k, rep)); \
+        else ASCB200_CUDA(launch_pdl(softmax_rows_kernel<T, 32, NC, QUANT, false>, (m + 3) / 4, 128, 0, st, src, dst, sum, mx, q, qs, qo, qos, m, k, rep));                \
     } while (0)
 #define ASCB200_SM_BLOCK(TPR, NC) softmax_rows_kernel<T, TPR, NC, QUANT, false><<<m, TPR, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep)
     if (nchunks <= 32) ASCB200_SM_WARP(1);
