@@ -721,6 +721,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
     }
+    // Launched with programmatic stream serialisation: everything above overlaps the tail of the previous kernel in the
+    // stream; from here on global memory is read and written, so that kernel must have completed.
+    grid_dependency_wait();
     if (warp == 0 && p.groups > 0) build_group_tables(p.group_counts, p.groups, num_n, BLOCK_M, row_start, tile_start);
     if (warp == 2) {
         tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
@@ -943,6 +946,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
     }
+    grid_dependency_wait();  // see gemm_tc_kernel
     if (warp == 3 && p.groups > 0) build_group_tables(p.group_counts, p.groups, num_n, PAIR_M, row_start, tile_start);
     if (warp == 2) {
         tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
@@ -1123,6 +1127,7 @@ retile_scales_kernel(const uint8_t* __restrict__ src_a, uint32_t* __restrict__ d
 {
     constexpr int CH = 8;  // chunks per block: 32 bytes of every row, four words per thread, all loads issued before any is used
     __shared__ uint32_t tile[128][CH + 1];  // [position inside a chunk][chunk]
+    grid_dependency_wait();
     int blk = blockIdx.x;
     const bool is_a = blk < rb_a * kc_tiles;
     if (!is_a) blk -= rb_a * kc_tiles;
@@ -1243,8 +1248,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& out
         ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured[dev & 15] = true;
     }
-    gemm_tc_kernel<KIND, BLOCK_N><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, outs, p);
-    ASCB200_CUDA(cudaGetLastError());
+    ASCB200_CUDA(launch_pdl(gemm_tc_kernel<KIND, BLOCK_N>, grid, NUM_THREADS, C::SMEM_BYTES, stream, ta, tb, outs, p));
     return ASCB200_OK;
 }
 
@@ -1260,8 +1264,7 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
         ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured[dev & 15] = true;
     }
-    gemm_tc_pair_kernel<KIND, BLOCK_N><<<2 * clusters, NUM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, tsfa, tsfb, outs, p);
-    ASCB200_CUDA(cudaGetLastError());
+    ASCB200_CUDA(launch_pdl(gemm_tc_pair_kernel<KIND, BLOCK_N>, 2 * clusters, NUM_THREADS, C::SMEM_BYTES, stream, ta, tb, tsfa, tsfb, outs, p));
     return ASCB200_OK;
 }
 
