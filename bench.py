@@ -122,7 +122,7 @@ class A8W8(Workload):
     name = "a8w8_gemm_4096x4096x11008_dequant_bf16"
     metric, unit, dtype = "quant-GEMM throughput (int8, fused per-token x per-channel dequant)", "TOPS", "s8"
     M, K, N = 4096, 4096, 11008
-    traffic_1gpu = 62.11e6 + 48.78e6   # profiles/gemm_tc_pair_kernel_int8_a8w8_4096x4096x11008.md
+    traffic_1gpu = 62.05e6 + 48.92e6   # profiles/gemm_tc_pair_kernel_int8_a8w8_4096x4096x11008.md
 
     def __init__(self, ab, rank, world, sets):
         self.ab, self.rank, self.world = ab, rank, world
@@ -271,7 +271,7 @@ class MXFP4(Workload):
     metric, unit, dtype = "quant-GEMM throughput (MXFP4 e2m1 x ue8m0, int8 requant + bf16 out)", "TFLOPS", "fp4_e2m1"
     M = K = N = 8192
     kernels_per_step = 3  # two scale re-tiling launches + the GEMM
-    traffic_1gpu = 94.2e6 + 167.3e6    # profiles/gemm_tc_pair_kernel_mxfp4_8192x8192x8192.md
+    traffic_1gpu = 95.2e6 + 168.0e6    # profiles/gemm_tc_pair_kernel_mxfp4_8192x8192x8192.md
     published = (1614.0, "Ascend 950PR basic-API MXFP4 8192^3, bf16 out; the reference's published figure")
 
     def __init__(self, ab, rank, world, sets):
