@@ -527,3 +527,67 @@ def test_gemm_outputs_stay_inside_their_buffers():
                          scale_b=ab.to_dev(sb), quant=q, c2=c2, c2_dtype=ab.BF16))
         ab.sync()
         assert tail_intact(c, m * n) and tail_intact(c2, m * n * 2), ("mxfp4", m, n)
+
+
+def test_gemm_i8_random_shapes_layouts_and_outputs():
+    """Seeded random sweep: extents that are multiples of nothing in particular, both B layouts, padded leading dimensions,
+    int32 / int8 / bf16 outputs, bit exact against the oracle and with a guard behind every output."""
+    ab = dev()
+    rng = np.random.default_rng(20251125)
+    for case in range(28):
+        big = case % 7 == 0
+        m = int(rng.integers(1, 2700 if big else 400))
+        n = int(rng.integers(1, 1600 if big else 700))
+        k = int(rng.integers(1, 40)) * 16
+        trans_b = bool(rng.integers(0, 2)) or n % 16 != 0      # [K, N] storage needs 16-byte aligned rows
+        ldc = n + int(rng.integers(0, 3)) * 16
+        a = rng.integers(-127, 128, (m, k), dtype=np.int8)
+        b = rng.integers(-127, 128, (n, k) if trans_b else (k, n), dtype=np.int8)
+        acc = orc.gemm_i8(a, b, trans_b=trans_b)
+        d_a, d_b = ab.to_dev(a), ab.to_dev(b)
+        kind = case % 3
+        if kind == 0:
+            c_dtype, np_t, kw, ref = ab.S32, np.int32, {}, acc
+        elif kind == 1:
+            q = quant_params(rng.uniform(2e-5, 3e-4, n).astype(np.float32), rng.integers(-30, 30, n))
+            c_dtype, np_t, kw, ref = ab.S8, np.int8, dict(epilogue=ab.EPI_FIXPIPE_QUANT, quant=ab.to_dev(q)), orc.fixpipe_req8(acc, q)
+        else:
+            tok, ch = rng.uniform(1e-3, 1e-2, m).astype(np.float32), rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+            c_dtype, np_t = ab.BF16, np.uint16
+            kw, ref = dict(epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, tok=ab.to_dev(tok), ch=ab.to_dev(ch)), orc.dequant_tok_ch(acc, tok, ch, orc.BF16)
+        esz = np.dtype(np_t).itemsize
+        used = ((m - 1) * ldc + n) * esz
+        d_c = ab.DevBuf(used + 256)
+        d_c.fill(0x5A)
+        ab.check(ab.gemm(ab.KIND_S8, m, n, k, d_a, d_b, d_c, c_dtype, trans_b=trans_b, ldc=ldc, **kw), f"case {case}: {m}x{n}x{k}")
+        ab.sync()
+        host = np.zeros(used + 256, np.uint8)
+        ab.check(ab.lib().ascb200_memcpy_d2h(host.ctypes.data, d_c.ptr, used + 256, None))
+        ab.sync()
+        assert (host[used:] == 0x5A).all(), f"case {case}: wrote past the end ({m}x{n}x{k}, ldc {ldc})"
+        rows = np.zeros((m, ldc * esz), np.uint8).reshape(-1)
+        rows[:used] = host[:used]
+        got = rows.reshape(m, ldc * esz)[:, :n * esz].copy().view(np_t)
+        assert (got == ref).all(), f"case {case}: {m}x{n}x{k} trans_b={trans_b} out={c_dtype}: {(got != ref).sum()} differ"
+        pad = rows.reshape(m, ldc * esz)[:-1, n * esz:]
+        assert (pad == 0x5A).all(), f"case {case}: padding between rows was written"
+
+
+def test_gemm_mxfp4_and_f16_random_shapes():
+    """Seeded random extents for the fp32-accumulating kinds (K a multiple of 64 for MXFP4), within the north-star tolerance."""
+    ab = dev()
+    rng = np.random.default_rng(7)
+    for case in range(8):
+        m, n, k = int(rng.integers(1, 600)), int(rng.integers(1, 900)), int(rng.integers(1, 12)) * 64
+        _, a, sa, b, sb = _mx_case(m, n, k, case)
+        d_c = ab.empty((m, n), np.float32)
+        ab.check(ab.gemm(ab.KIND_MXFP4, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.F32, trans_b=True, scale_a=ab.to_dev(sa), scale_b=ab.to_dev(sb)),
+                 f"mxfp4 {m}x{n}x{k}")
+        ab.sync()
+        ref = orc.gemm_mxf4(a, sa, b, sb, base_k=256)
+        assert np.allclose(d_c.download().reshape(m, n), ref, rtol=RTOL, atol=ATOL), f"mxfp4 {m}x{n}x{k}"
+    for case in range(8):
+        m, n, k = int(rng.integers(1, 500)), int(rng.integers(1, 90)) * 8, int(rng.integers(1, 60)) * 8
+        if case & 1:
+            m = (m + 7) // 8 * 8   # A stored [K, M]: rows of 16-byte multiples, the tensor-map rule
+        run_f16(m, n, k, bool(case & 1), bool(case & 2), bf16=bool(case & 4), bias=bool(case % 3), c_dtype=case % 3, seed=case)
