@@ -591,3 +591,35 @@ def test_gemm_mxfp4_and_f16_random_shapes():
         if case & 1:
             m = (m + 7) // 8 * 8   # A stored [K, M]: rows of 16-byte multiples, the tensor-map rule
         run_f16(m, n, k, bool(case & 1), bool(case & 2), bf16=bool(case & 4), bias=bool(case % 3), c_dtype=case % 3, seed=case)
+
+
+def test_grouped_random_counts_and_shapes():
+    """Seeded random group lists (empty groups, single rows, tails of every length), both weight layouts, bf16 and fp16 outputs."""
+    ab = dev()
+    rng = np.random.default_rng(99)
+    for case in range(12):
+        G = int(rng.integers(1, 13))
+        counts = rng.integers(0, 400, G).astype(np.int64) * (rng.random(G) > 0.2)
+        counts = counts.astype(np.int64)
+        m = int(counts.sum())
+        if m == 0:
+            counts[0], m = 5, 5
+        n, k = int(rng.integers(1, 40)) * 16, int(rng.integers(1, 24)) * 16
+        trans_b = bool(case & 1)
+        x = rng.integers(-127, 128, (m, k), dtype=np.int8)
+        w = rng.integers(-127, 128, (G, n, k) if trans_b else (G, k, n), dtype=np.int8)
+        tok = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+        ch = rng.uniform(1e-3, 1e-2, (G, n)).astype(np.float32)
+        c_dtype = ab.BF16 if case % 3 else ab.F16
+        d_c = ab.DevBuf(m * n * 2 + 256)
+        d_c.fill(0x5A)
+        ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(x), ab.to_dev(w), d_c, c_dtype, epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, trans_b=trans_b,
+                         tok=ab.to_dev(tok), ch=ab.to_dev(ch), group_counts=ab.to_dev(counts), groups=G), f"case {case}")
+        ab.sync()
+        host = np.zeros(m * n * 2 + 256, np.uint8)
+        ab.check(ab.lib().ascb200_memcpy_d2h(host.ctypes.data, d_c.ptr, host.size, None))
+        ab.sync()
+        assert (host[m * n * 2:] == 0x5A).all(), f"case {case}: wrote past the end"
+        ref = orc.grouped_i8(x, w, counts, tok, ch, orc.BF16 if c_dtype == ab.BF16 else orc.F16, trans_b=trans_b)
+        got = host[:m * n * 2].view(np.uint16).reshape(m, n)
+        assert (got == ref).all(), f"case {case}: counts {counts.tolist()} n {n} k {k}: {(got != ref).sum()} differ"
