@@ -112,15 +112,46 @@ __device__ __forceinline__ void softmax_load_row(const T* __restrict__ srow, int
     }
 }
 
-template <typename T, int TPR, int NCHUNK, bool QUANT>
+// One statistic of a row.  Volatile: the compiler keeps the load where it is written (ahead of the first use of the row's
+// data) instead of sinking it to its first use, where it would add a memory latency to the row's critical path.
+template <typename ST> __device__ __forceinline__ float stat_load(const ST* p, size_t i);
+template <> __device__ __forceinline__ float stat_load<float>(const float* p, size_t i)
+{
+    float v;
+    asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p + i));
+    return v;
+}
+template <> __device__ __forceinline__ float stat_load<__half>(const __half* p, size_t i)
+{
+    unsigned short b;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(b) : "l"(p + i));
+    return __half2float(__ushort_as_half(b));
+}
+// MODE: kSoftmaxPlain, kSoftmaxQuant (also writes the int8 AscendQuant of the result) or kSoftmaxLog
+// (LogSoftMax: y = ln(e / sum) * log10(e) computed in fp32, statistics stored in T;
+// impl/adv_api/detail/activation/softmax/membase/common/logsoftmax_common_impl.h:277-376).
+// kSoftmaxSimpleF32 / kSoftmaxSimpleF16: SimpleSoftMax, y = exp(x - inMax) / inSum with the statistics READ from
+// max_out / sum_out (fp32, or half behind the same pointers) instead of reduced from the row
+// (impl/adv_api/detail/activation/softmax/membase/common/simple_softmax_common_impl.h:320-502).
+constexpr int kSoftmaxPlain = 0, kSoftmaxQuant = 1, kSoftmaxLog = 2, kSoftmaxSimpleF32 = 3, kSoftmaxSimpleF16 = 4;
+
+template <typename T, int TPR, int NCHUNK, int MODE>
 __device__ __forceinline__ void softmax_one_row(const uint4 (&raw)[NCHUNK], int row, int t, int nchunks, T* __restrict__ dst,
                                                 float* __restrict__ sum_out, float* __restrict__ max_out, int8_t* __restrict__ q_out,
                                                 const __half* __restrict__ q_scale, const __half* __restrict__ q_offset, __half q_offset_scalar,
                                                 int k, int stats_rep, float* red)
 {
     constexpr int VEC = 16 / sizeof(T);
+    constexpr bool SIMPLE = MODE == kSoftmaxSimpleF32 || MODE == kSoftmaxSimpleF16;
     float v[NCHUNK * VEC];
-    float mx = kNegInf;
+    float mx = kNegInf, given_sum = 1.0f;
+    if constexpr (MODE == kSoftmaxSimpleF32) {
+        mx = stat_load<float>(max_out, static_cast<size_t>(row) * stats_rep);
+        given_sum = stat_load<float>(sum_out, static_cast<size_t>(row) * stats_rep);
+    } else if constexpr (MODE == kSoftmaxSimpleF16) {
+        mx = stat_load<__half>(reinterpret_cast<const __half*>(max_out), static_cast<size_t>(row) * stats_rep);
+        given_sum = stat_load<__half>(reinterpret_cast<const __half*>(sum_out), static_cast<size_t>(row) * stats_rep);
+    }
 #pragma unroll
     for (int i = 0; i < NCHUNK; ++i) {
         const int c = t + i * TPR;
@@ -143,10 +174,12 @@ __device__ __forceinline__ void softmax_one_row(const uint4 (&raw)[NCHUNK], int 
 #pragma unroll
             for (int j = 0; j < VEC; ++j) v[i * VEC + j] = kNegInf;
         }
+        if constexpr (!SIMPLE) {
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) mx = fmaxf(mx, v[i * VEC + j]);
+            for (int j = 0; j < VEC; ++j) mx = fmaxf(mx, v[i * VEC + j]);
+        }
     }
-    mx = row_reduce_max<TPR>(mx, red);
+    if constexpr (!SIMPLE) mx = row_reduce_max<TPR>(mx, red);
 
     float s = 0.0f;
 #pragma unroll
@@ -154,8 +187,18 @@ __device__ __forceinline__ void softmax_one_row(const uint4 (&raw)[NCHUNK], int 
         v[i] = exp2_approx((v[i] - mx) * 1.4426950408889634f);  // exp(x - max); -inf padding gives 0
         s += v[i];
     }
-    s = row_reduce_sum<TPR>(s, red);
+    if constexpr (SIMPLE) s = given_sum;
+    else s = row_reduce_sum<TPR>(s, red);
     const float inv = __frcp_rn(s);
+    if constexpr (SIMPLE && sizeof(T) == 2) {  // foreign statistics can push y past the half range: saturate like the reference's cast
+#pragma unroll
+        for (int i = 0; i < NCHUNK * VEC; ++i) v[i] = clamp_half_range(v[i] * inv);
+    }
+    if constexpr (MODE == kSoftmaxLog) {
+#pragma unroll
+        for (int i = 0; i < NCHUNK * VEC; ++i) v[i] = __log2f(v[i] * inv) * (0.6931471805599453f * 0.4342944819f);  // ln(.) * SCALAR_NATURE_LOG_10
+    }
+    const float outmul = (MODE == kSoftmaxLog || (SIMPLE && sizeof(T) == 2)) ? 1.0f : inv;
 
     T* drow = dst + static_cast<size_t>(row) * k;
 #pragma unroll
@@ -163,12 +206,12 @@ __device__ __forceinline__ void softmax_one_row(const uint4 (&raw)[NCHUNK], int 
         const int c = t + i * TPR;
         if (c < nchunks) {
             if constexpr (sizeof(T) == 2) {
-                uint4 o;  // softmax values lie in [0, 1]: the half cast cannot overflow
+                uint4 o;  // softmax values lie in [0, 1] and their log10 above -46: the half cast cannot overflow
                 __half2* h = reinterpret_cast<__half2*>(&o);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(v[i * 8 + 2 * j] * inv, v[i * 8 + 2 * j + 1] * inv);
+                for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(v[i * 8 + 2 * j] * outmul, v[i * 8 + 2 * j + 1] * outmul);
                 *reinterpret_cast<uint4*>(drow + c * 8) = o;
-                if constexpr (QUANT) {
+                if constexpr (MODE == kSoftmaxQuant) {
                     const uint4 sc = __ldg(reinterpret_cast<const uint4*>(q_scale + c * 8));
                     uint4 of = make_uint4(0u, 0u, 0u, 0u);
                     if (q_offset) of = __ldg(reinterpret_cast<const uint4*>(q_offset + c * 8));
@@ -181,14 +224,20 @@ __device__ __forceinline__ void softmax_one_row(const uint4 (&raw)[NCHUNK], int 
                     *reinterpret_cast<uint2*>(q_out + static_cast<size_t>(row) * k + c * 8) = make_uint2(pack_s8x4(w[0], w[1]), pack_s8x4(w[2], w[3]));
                 }
             } else {
-                float4 o = make_float4(v[i * 4] * inv, v[i * 4 + 1] * inv, v[i * 4 + 2] * inv, v[i * 4 + 3] * inv);
+                float4 o = make_float4(v[i * 4] * outmul, v[i * 4 + 1] * outmul, v[i * 4 + 2] * outmul, v[i * 4 + 3] * outmul);
                 *reinterpret_cast<float4*>(drow + c * 4) = o;
             }
         }
     }
+    if constexpr (SIMPLE) return;
     if (t < stats_rep) {
-        sum_out[static_cast<size_t>(row) * stats_rep + t] = s;
-        max_out[static_cast<size_t>(row) * stats_rep + t] = mx;
+        if constexpr (MODE == kSoftmaxLog && sizeof(T) == 2) {  // LogSoftMax keeps its statistics in T
+            reinterpret_cast<__half*>(sum_out)[static_cast<size_t>(row) * stats_rep + t] = __float2half_rn(s);
+            reinterpret_cast<__half*>(max_out)[static_cast<size_t>(row) * stats_rep + t] = __float2half_rn(mx);
+        } else {
+            sum_out[static_cast<size_t>(row) * stats_rep + t] = s;
+            max_out[static_cast<size_t>(row) * stats_rep + t] = mx;
+        }
     }
 }
 
@@ -196,7 +245,7 @@ constexpr int kSoftmaxWarpBlock = 224;  // 7 warps; two such blocks per SM
 
 // PERSIST (warp rows only): few rows per warp -> machine-sized grid with next-row prefetch; many rows ->
 // one row per warp and small blocks, where 20 resident warps per SM keep more requests in flight.
-template <typename T, int TPR, int NCHUNK, bool QUANT, bool PERSIST>
+template <typename T, int TPR, int NCHUNK, int MODE, bool PERSIST>
 __global__ void __launch_bounds__(TPR > 32 ? TPR : (PERSIST ? kSoftmaxWarpBlock : 128), TPR > 32 ? 1 : (PERSIST ? 2 : 5))
 softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __restrict__ sum_out, float* __restrict__ max_out,
                     int8_t* __restrict__ q_out, const __half* __restrict__ q_scale, const __half* __restrict__ q_offset,
@@ -210,7 +259,7 @@ softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __res
         const int row = blockIdx.x;
         uint4 raw[NCHUNK];
         softmax_load_row<T, TPR, NCHUNK>(src + static_cast<size_t>(row) * k, threadIdx.x, nchunks, raw);
-        softmax_one_row<T, TPR, NCHUNK, QUANT>(raw, row, threadIdx.x, nchunks, dst, sum_out, max_out, q_out, q_scale, q_offset, q_offset_scalar, k,
+        softmax_one_row<T, TPR, NCHUNK, MODE>(raw, row, threadIdx.x, nchunks, dst, sum_out, max_out, q_out, q_scale, q_offset, q_offset_scalar, k,
                                                stats_rep, red);
     } else {
         const int t = threadIdx.x & 31;
@@ -221,14 +270,14 @@ softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __res
         uint4 raw[NCHUNK];
         softmax_load_row<T, TPR, NCHUNK>(src + static_cast<size_t>(row) * k, t, nchunks, raw);
         if constexpr (!PERSIST) {
-            softmax_one_row<T, TPR, NCHUNK, QUANT>(raw, row, t, nchunks, dst, sum_out, max_out, q_out, q_scale, q_offset, q_offset_scalar, k,
+            softmax_one_row<T, TPR, NCHUNK, MODE>(raw, row, t, nchunks, dst, sum_out, max_out, q_out, q_scale, q_offset, q_offset_scalar, k,
                                                    stats_rep, red);
         } else {
             while (true) {
                 const int next = row + stride;
                 uint4 ahead[NCHUNK];
                 if (next < m) softmax_load_row<T, TPR, NCHUNK>(src + static_cast<size_t>(next) * k, t, nchunks, ahead);
-                softmax_one_row<T, TPR, NCHUNK, QUANT>(raw, row, t, nchunks, dst, sum_out, max_out, q_out, q_scale, q_offset, q_offset_scalar,
+                softmax_one_row<T, TPR, NCHUNK, MODE>(raw, row, t, nchunks, dst, sum_out, max_out, q_out, q_scale, q_offset, q_offset_scalar,
                                                        k, stats_rep, red);
                 if (next >= m) break;
 #pragma unroll
@@ -239,7 +288,7 @@ softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __res
     }
 }
 
-template <typename T, bool QUANT>
+template <typename T, int MODE>
 int launch_softmax(const T* src, T* dst, float* sum, float* mx, int8_t* q, const __half* qs, const __half* qo, __half qos, int m,
                    int k, int rep, int sms, cudaStream_t st)
 {
@@ -250,10 +299,10 @@ int launch_softmax(const T* src, T* dst, float* sum, float* mx, int8_t* q, const
     const int nchunks = k / VEC;
 #define ASCB200_SM_WARP(NC)                                                                                              \
     do {                                                                                                                  \
-        if (persist) ASCB200_CUDA(launch_pdl(softmax_rows_kernel<T, 32, NC, QUANT, true>, warp_grid, kSoftmaxWarpBlock, 0, st, src, dst, sum, mx, q, qs, qo, qos, m, k, rep)); \
-        else ASCB200_CUDA(launch_pdl(softmax_rows_kernel<T, 32, NC, QUANT, false>, (m + 3) / 4, 128, 0, st, src, dst, sum, mx, q, qs, qo, qos, m, k, rep));                \
+        if (persist) ASCB200_CUDA(launch_pdl(softmax_rows_kernel<T, 32, NC, MODE, true>, warp_grid, kSoftmaxWarpBlock, 0, st, src, dst, sum, mx, q, qs, qo, qos, m, k, rep)); \
+        else ASCB200_CUDA(launch_pdl(softmax_rows_kernel<T, 32, NC, MODE, false>, (m + 3) / 4, 128, 0, st, src, dst, sum, mx, q, qs, qo, qos, m, k, rep));                \
     } while (0)
-#define ASCB200_SM_BLOCK(TPR, NC) softmax_rows_kernel<T, TPR, NC, QUANT, false><<<m, TPR, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep)
+#define ASCB200_SM_BLOCK(TPR, NC) softmax_rows_kernel<T, TPR, NC, MODE, false><<<m, TPR, 0, st>>>(src, dst, sum, mx, q, qs, qo, qos, m, k, rep)
     if (nchunks <= 32) ASCB200_SM_WARP(1);
     else if (nchunks <= 64) ASCB200_SM_WARP(2);
     else if (nchunks <= 128) ASCB200_SM_WARP(4);
@@ -455,19 +504,6 @@ int launch_dequant(const int32_t* src, void* dst, int m, int n, int cal, int n_d
 // inside, like the reference's half path.  Same row mapping as softmax_rows_kernel (row in registers, read once).
 // Volatile loads: the compiler keeps them where they are written (ahead of the row loads) instead of sinking them to
 // their first use after the row maximum, where each would add a memory latency to the row's critical path.
-template <typename ST> __device__ __forceinline__ float stat_load(const ST* p, size_t i);
-template <> __device__ __forceinline__ float stat_load<float>(const float* p, size_t i)
-{
-    float v;
-    asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p + i));
-    return v;
-}
-template <> __device__ __forceinline__ float stat_load<__half>(const __half* p, size_t i)
-{
-    unsigned short b;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(b) : "l"(p + i));
-    return __half2float(__ushort_as_half(b));
-}
 template <typename ST> __device__ __forceinline__ void stat_store(ST* p, size_t i, float v);
 template <> __device__ __forceinline__ void stat_store<float>(float* p, size_t i, float v) { p[i] = v; }
 template <> __device__ __forceinline__ void stat_store<__half>(__half* p, size_t i, float v) { p[i] = __float2half_rn(clamp_half_range(v)); }
@@ -634,10 +670,56 @@ int ascb200_softmax(const void* src, void* dst, float* sum, float* mx, int32_t m
     const int rep = stats_brc ? 8 : 1;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == ASCB200_F16)
-        return launch_softmax<__half, false>(static_cast<const __half*>(src), static_cast<__half*>(dst), sum, mx, nullptr, nullptr,
+        return launch_softmax<__half, kSoftmaxPlain>(static_cast<const __half*>(src), static_cast<__half*>(dst), sum, mx, nullptr, nullptr,
                                              nullptr, __half(), m, k, rep, st->sm_count, s);
-    return launch_softmax<float, false>(static_cast<const float*>(src), static_cast<float*>(dst), sum, mx, nullptr, nullptr, nullptr,
+    return launch_softmax<float, kSoftmaxPlain>(static_cast<const float*>(src), static_cast<float*>(dst), sum, mx, nullptr, nullptr, nullptr,
                                         __half(), m, k, rep, st->sm_count, s);
+}
+
+int ascb200_log_softmax(const void* src, void* dst, void* sum, void* mx, int32_t m, int32_t k, int32_t dtype, int32_t stats_brc,
+                        void* stream)
+{
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    int rc = check_softmax_args(src, dst, static_cast<float*>(sum), static_cast<float*>(mx), m, k, dtype);
+    if (rc != ASCB200_OK) return rc;
+    if (m == 0) return ASCB200_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == ASCB200_F16)  // statistics in half: one 32-byte block holds 16 of them
+        return launch_softmax<__half, kSoftmaxLog>(static_cast<const __half*>(src), static_cast<__half*>(dst), static_cast<float*>(sum),
+                                                   static_cast<float*>(mx), nullptr, nullptr, nullptr, __half(), m, k, stats_brc ? 16 : 1,
+                                                   st->sm_count, s);
+    return launch_softmax<float, kSoftmaxLog>(static_cast<const float*>(src), static_cast<float*>(dst), static_cast<float*>(sum),
+                                              static_cast<float*>(mx), nullptr, nullptr, nullptr, __half(), m, k, stats_brc ? 8 : 1,
+                                              st->sm_count, s);
+}
+
+int ascb200_simple_softmax(const void* src, void* dst, const void* in_sum, const void* in_max, int32_t m, int32_t k, int32_t dtype,
+                           int32_t stats_dtype, int32_t stats_brc, void* stream)
+{
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    if (!src || !dst || !in_sum || !in_max || m < 0 || k <= 0) return ASCB200_EINVAL;
+    if (dtype != ASCB200_F16 && dtype != ASCB200_F32) return ASCB200_EUNSUPPORTED;
+    // statistics have the data type, or fp32 beside half data (the two overload families of the reference)
+    if (stats_dtype != dtype && !(dtype == ASCB200_F16 && stats_dtype == ASCB200_F32)) return ASCB200_EUNSUPPORTED;
+    const int esz = dtype == ASCB200_F16 ? 2 : 4;
+    if ((static_cast<size_t>(k) * esz) % 32 != 0) return ASCB200_EALIGN;
+    if (!aligned_to(src, 16) || !aligned_to(dst, 16)) return ASCB200_EALIGN;
+    if (m == 0) return ASCB200_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int rep = stats_brc ? (stats_dtype == ASCB200_F16 ? 16 : 8) : 1;
+    // the row kernel reads the statistics through its (otherwise output) statistics pointers
+    float* sum = static_cast<float*>(const_cast<void*>(in_sum));
+    float* mx = static_cast<float*>(const_cast<void*>(in_max));
+    if (dtype == ASCB200_F32)
+        return launch_softmax<float, kSoftmaxSimpleF32>(static_cast<const float*>(src), static_cast<float*>(dst), sum, mx, nullptr, nullptr,
+                                                        nullptr, __half(), m, k, rep, st->sm_count, s);
+    if (stats_dtype == ASCB200_F32)
+        return launch_softmax<__half, kSoftmaxSimpleF32>(static_cast<const __half*>(src), static_cast<__half*>(dst), sum, mx, nullptr, nullptr,
+                                                         nullptr, __half(), m, k, rep, st->sm_count, s);
+    return launch_softmax<__half, kSoftmaxSimpleF16>(static_cast<const __half*>(src), static_cast<__half*>(dst), sum, mx, nullptr, nullptr,
+                                                     nullptr, __half(), m, k, rep, st->sm_count, s);
 }
 
 int ascb200_softmax_flash_v2(const void* src, void* dst, void* exp_sum, void* max, void* exp_max, const void* in_exp_sum, const void* in_max,
@@ -683,7 +765,7 @@ int ascb200_softmax_quant(const void* src, void* dst, float* sum, float* mx, int
     if (!q || !scale) return ASCB200_EINVAL;
     if (!aligned_to(q, 8) || !aligned_to(scale, 16) || (offset_t && !aligned_to(offset_t, 16))) return ASCB200_EALIGN;
     if (m == 0) return ASCB200_OK;
-    return launch_softmax<__half, true>(static_cast<const __half*>(src), static_cast<__half*>(dst), sum, mx, q,
+    return launch_softmax<__half, kSoftmaxQuant>(static_cast<const __half*>(src), static_cast<__half*>(dst), sum, mx, q,
                                         static_cast<const __half*>(scale), static_cast<const __half*>(offset_t),
                                         __float2half_rn(offset), m, k, stats_brc ? 8 : 1, st->sm_count, static_cast<cudaStream_t>(stream));
 }

@@ -49,6 +49,69 @@ inline void SoftMax(const LocalTensor<T>& dstTensor, const LocalTensor<float>& s
     SoftMax<T, isReuseSource, isBasicBlock, isDataFormatNZ, config>(dstTensor, sumTensor, maxTensor, srcTensor, tiling, softmaxShapeInfo);
 }
 
+// LogSoftMax<T>(dst, sum, max, src, sharedTmpBuffer, tiling, shapeInfo)  (include/adv_api/activation/logsoftmax.h:56-71).
+// y = log10(softmax(x)); sum / max are LocalTensor<T> holding one 32-byte block per row ([srcM, 16] half or [srcM, 8] float).
+template <typename T, bool isReuseSource = false, bool isDataFormatNZ = false>
+inline void LogSoftMax(const LocalTensor<T>& dst, const LocalTensor<T>& sum, const LocalTensor<T>& max, const LocalTensor<T>& src,
+                       const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const LogSoftMaxTiling& tiling,
+                       const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    static_assert(!isDataFormatNZ, "NZ-format LogSoftMax is not part of the B200 path");
+    const uint32_t m = softmaxShapeInfo.srcM ? softmaxShapeInfo.srcM : tiling.srcM;
+    const uint32_t k = softmaxShapeInfo.srcK ? softmaxShapeInfo.srcK : tiling.srcK;
+    detail::Latch(ascb200_log_softmax(src.GetPhyAddr(), dst.GetPhyAddr(), sum.GetPhyAddr(), max.GetPhyAddr(), static_cast<int32_t>(m),
+                                      static_cast<int32_t>(k), detail::DTypeOf<T>::value, 1, detail::CurrentStream()),
+                  "LogSoftMax");
+}
+
+// SimpleSoftMax<T>(dst, inSum, inMax, src, tiling, shapeInfo)  (include/adv_api/activation/simplesoftmax.h:55-190):
+// the all-T form, the half-data / float-statistics form, and both again with a sharedTmpBuffer.
+namespace detail {
+template <typename T, typename ST>
+inline void SimpleSoftMaxCall(const LocalTensor<T>& dst, const LocalTensor<ST>& inSum, const LocalTensor<ST>& inMax, const LocalTensor<T>& src,
+                              const SoftMaxTiling& tiling, const SoftMaxShapeInfo& info, const SoftmaxConfig& config)
+{
+    const uint32_t m = info.srcM ? info.srcM : tiling.srcM;
+    const uint32_t k = info.srcK ? info.srcK : tiling.srcK;
+    const int brc = config.mode == SoftmaxMode::SOFTMAX_OUTPUT_WITHOUT_BRC ? 0 : 1;
+    Latch(ascb200_simple_softmax(src.GetPhyAddr(), dst.GetPhyAddr(), inSum.GetPhyAddr(), inMax.GetPhyAddr(), static_cast<int32_t>(m),
+                                 static_cast<int32_t>(k), DTypeOf<T>::value, DTypeOf<ST>::value, brc, CurrentStream()),
+          "SimpleSoftMax");
+}
+}  // namespace detail
+template <typename T, bool isReuseSource = false, bool isBasicBlock = false, bool isDataFormatNZ = false,
+          const SoftmaxConfig& config = SOFTMAX_DEFAULT_CFG>
+inline void SimpleSoftMax(const LocalTensor<T>& dstTensor, const LocalTensor<T>& inSumTensor, const LocalTensor<T>& inMaxTensor,
+                          const LocalTensor<T>& srcTensor, const SoftMaxTiling& tiling, const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    static_assert(!isDataFormatNZ, "NZ-format SimpleSoftMax is not part of the B200 path");
+    detail::SimpleSoftMaxCall(dstTensor, inSumTensor, inMaxTensor, srcTensor, tiling, softmaxShapeInfo, config);
+}
+template <typename T, bool isReuseSource = false, bool isBasicBlock = false, bool isDataFormatNZ = false,
+          const SoftmaxConfig& config = SOFTMAX_DEFAULT_CFG>
+inline void SimpleSoftMax(const LocalTensor<half>& dstTensor, const LocalTensor<float>& inSumTensor, const LocalTensor<float>& inMaxTensor,
+                          const LocalTensor<half>& srcTensor, const SoftMaxTiling& tiling, const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    static_assert(!isDataFormatNZ, "NZ-format SimpleSoftMax is not part of the B200 path");
+    detail::SimpleSoftMaxCall(dstTensor, inSumTensor, inMaxTensor, srcTensor, tiling, softmaxShapeInfo, config);
+}
+template <typename T, bool isReuseSource = false, bool isBasicBlock = false, bool isDataFormatNZ = false,
+          const SoftmaxConfig& config = SOFTMAX_DEFAULT_CFG>
+inline void SimpleSoftMax(const LocalTensor<T>& dstTensor, const LocalTensor<T>& inSumTensor, const LocalTensor<T>& inMaxTensor,
+                          const LocalTensor<T>& srcTensor, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const SoftMaxTiling& tiling,
+                          const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    SimpleSoftMax<T, isReuseSource, isBasicBlock, isDataFormatNZ, config>(dstTensor, inSumTensor, inMaxTensor, srcTensor, tiling, softmaxShapeInfo);
+}
+template <typename T, bool isReuseSource = false, bool isBasicBlock = false, bool isDataFormatNZ = false,
+          const SoftmaxConfig& config = SOFTMAX_DEFAULT_CFG>
+inline void SimpleSoftMax(const LocalTensor<half>& dstTensor, const LocalTensor<float>& inSumTensor, const LocalTensor<float>& inMaxTensor,
+                          const LocalTensor<half>& srcTensor, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const SoftMaxTiling& tiling,
+                          const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    SimpleSoftMax<T, isReuseSource, isBasicBlock, isDataFormatNZ, config>(dstTensor, inSumTensor, inMaxTensor, srcTensor, tiling, softmaxShapeInfo);
+}
+
 // SoftmaxFlashV2<T, isUpdate>(dst, expSum, max, src, expMax, inExpSum, inMax, tiling, shapeInfo)
 // (include/adv_api/activation/softmaxflashv2.h:93-260): the all-T overloads and the half data / float statistics overloads,
 // each with and without sharedTmpBuffer.

@@ -122,6 +122,11 @@ struct SoftMaxTiling {
         tailSplitSize, tailReduceSize;
 };
 static_assert(sizeof(SoftMaxTiling) == 64, "SoftMaxTiling is 16 uint32 fields");
+// include/adv_api/activation/logsoftmax_tilingdata.h:20-37: the same 16 fields under its own name.
+struct LogSoftMaxTiling {
+    uint32_t srcM, srcK, srcSize, outMaxM, outMaxK, outMaxSize, splitM, splitK, splitSize, reduceM, reduceK, reduceSize, rangeM, tailM,
+        tailSplitSize, tailReduceSize;
+};
 
 namespace AscendC {
 

@@ -200,6 +200,24 @@ ASCB200_API int ascb200_nz_unpack(const void* src_nz_dev, void* dst_dev, int32_t
 ASCB200_API int ascb200_softmax(const void* src_dev, void* dst_dev, float* sum_dev, float* max_dev, int32_t m, int32_t k,
                                 int32_t dtype, int32_t stats_brc, void* stream);
 
+/* LogSoftMax<T>(dst, sum, max, src, sharedTmpBuffer, tiling, shapeInfo)
+ * (include/adv_api/activation/logsoftmax.h:56-71; formula of LogSoftMax.md): per row max, e = exp(x - max), sum,
+ * y = log10(e / sum), evaluated in fp32 as ln(.) * 0.4342944819 like the reference
+ * (impl/adv_api/detail/activation/softmax/membase/common/logsoftmax_common_impl.h:277-376).  dtype F16 or F32;
+ * sum/max have the SAME dtype as src (the reference's LocalTensor<T> statistics) and are written once per row
+ * (stats_brc == 0) or broadcast over one 32-byte block (stats_brc != 0: 16 halves or 8 floats per row).
+ * Same argument checks as ascb200_softmax. */
+ASCB200_API int ascb200_log_softmax(const void* src_dev, void* dst_dev, void* sum_dev, void* max_dev, int32_t m, int32_t k,
+                                    int32_t dtype, int32_t stats_brc, void* stream);
+
+/* SimpleSoftMax<T>(dst, inSum, inMax, src, tiling, shapeInfo) (include/adv_api/activation/simplesoftmax.h:55-190):
+ * y = exp(x - inMax) / inSum per row with statistics computed earlier, fp32 arithmetic, cast RINT
+ * (impl/adv_api/detail/activation/softmax/membase/common/simple_softmax_common_impl.h:320-502).  dtype F16 or F32;
+ * stats_dtype == dtype (the all-T overloads) or F32 beside F16 data (the half / float overloads); statistics hold one
+ * value per row (stats_brc == 0) or one 32-byte block per row (stats_brc != 0).  k * sizeof(T) a multiple of 32. */
+ASCB200_API int ascb200_simple_softmax(const void* src_dev, void* dst_dev, const void* in_sum_dev, const void* in_max_dev, int32_t m,
+                                       int32_t k, int32_t dtype, int32_t stats_dtype, int32_t stats_brc, void* stream);
+
 /* ---- AscendQuant -------------------------------------------------------------------------------- */
 
 /* AscendQuant per tensor: dst = int8(rint_sat(half(src) * half(scale) + half(offset))), arithmetic in fp16

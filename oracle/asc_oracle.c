@@ -461,6 +461,74 @@ ORC_API void orc_softmax(const void* x, void* y, float* max_out, float* sum_out,
 }
 
 /* ---------------------------------------------------------------------------------------------
+ * LogSoftMax: the SoftMax above followed by y = ln(e / sum) * 0.4342944819 (= log10), all in fp32;
+ * for half sources the row is widened to fp32 first and y, max and sum are cast to half RINT at the end
+ * (impl/adv_api/detail/activation/softmax/membase/common/logsoftmax_common_impl.h:277-311 log step,
+ *  :313-338 fp32, :341-376 half; constant SCALAR_NATURE_LOG_10 at :30; golden
+ *  examples/01_simd_cpp_api/04_advanced_api/01_activation/logsoftmax/scripts/gen_data.py:19-33).
+ * max/sum have the source dtype (include/adv_api/activation/logsoftmax.h:56-59): once per row (brc == 0)
+ * or over one 32-byte block (brc == 1: 16 halves / 8 floats).
+ * ------------------------------------------------------------------------------------------- */
+ORC_API void orc_log_softmax(const void* x, void* y, void* max_out, void* sum_out, int M, int K, int dtype, int brc)
+{
+    const int rep = brc ? (dtype == ORC_F16 ? 16 : 8) : 1;
+#pragma omp parallel
+    {
+        float* row = (float*)malloc((size_t)K * sizeof(float));
+#pragma omp for schedule(static)
+        for (int m = 0; m < M; ++m) {
+            float mx = -INFINITY;
+            for (int k = 0; k < K; ++k) {
+                float v = dtype == ORC_F16 ? orc_f16_to_f32(((const uint16_t*)x)[(size_t)m * K + k]) : ((const float*)x)[(size_t)m * K + k];
+                row[k] = v;
+                if (v > mx) mx = v;
+            }
+            float s = 0.0f;
+            for (int k = 0; k < K; ++k) {
+                row[k] = expf(row[k] - mx);
+                s += row[k];
+            }
+            for (int k = 0; k < K; ++k) {
+                float v = logf(row[k] / s) * 0.4342944819f;
+                if (dtype == ORC_F16) ((uint16_t*)y)[(size_t)m * K + k] = f32_to_f16(v, 1);
+                else ((float*)y)[(size_t)m * K + k] = v;
+            }
+            for (int r = 0; r < rep; ++r) {
+                if (dtype == ORC_F16) {
+                    ((uint16_t*)max_out)[(size_t)m * rep + r] = f32_to_f16(mx, 1);
+                    ((uint16_t*)sum_out)[(size_t)m * rep + r] = f32_to_f16(s, 1);
+                } else {
+                    ((float*)max_out)[(size_t)m * rep + r] = mx;
+                    ((float*)sum_out)[(size_t)m * rep + r] = s;
+                }
+            }
+        }
+        free(row);
+    }
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * SimpleSoftMax: y = exp(float(x) - float(inMax)) / float(inSum), cast RINT; the statistics are given
+ * (impl/adv_api/detail/activation/softmax/membase/common/simple_softmax_common_impl.h:320-364 all half,
+ *  :367-389 fp32, :466-502 half data with fp32 statistics).  rep = values stored per row.
+ * ------------------------------------------------------------------------------------------- */
+ORC_API void orc_simple_softmax(const void* x, void* y, const void* in_sum, const void* in_max, int M, int K, int dtype, int stats_dtype,
+                                int rep)
+{
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m) {
+        const float mx = stats_dtype == ORC_F16 ? orc_f16_to_f32(((const uint16_t*)in_max)[(size_t)m * rep]) : ((const float*)in_max)[(size_t)m * rep];
+        const float sm = stats_dtype == ORC_F16 ? orc_f16_to_f32(((const uint16_t*)in_sum)[(size_t)m * rep]) : ((const float*)in_sum)[(size_t)m * rep];
+        for (int k = 0; k < K; ++k) {
+            const float v = dtype == ORC_F16 ? orc_f16_to_f32(((const uint16_t*)x)[(size_t)m * K + k]) : ((const float*)x)[(size_t)m * K + k];
+            const float r = expf(v - mx) / sm;
+            if (dtype == ORC_F16) ((uint16_t*)y)[(size_t)m * K + k] = f32_to_f16(r, 1);
+            else ((float*)y)[(size_t)m * K + k] = r;
+        }
+    }
+}
+
+/* ---------------------------------------------------------------------------------------------
  * AscendQuant -> int8.  All arithmetic in fp16: src (and fp32 scale/offset) cast to half RINT with
  * saturation, Mul in half, Add in half, half -> int8 RINT with saturation
  * (impl/adv_api/detail/quantization/quant/ascend_quant_3510_impl.h:34-66 per tensor,

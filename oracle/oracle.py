@@ -164,6 +164,29 @@ def softmax(x, dtype=F16, brc=False):
     return (y, mx, sm) if brc else (y, mx[:, 0], sm[:, 0])
 
 
+def log_softmax(x, dtype=F16, brc=False):
+    """x: uint16 half bits (dtype F16) or float32 [M,K]. Returns (y, max, sum); max/sum in the source dtype."""
+    t = np.uint16 if dtype == F16 else np.float32
+    x = _c(x, t)
+    M, K = x.shape
+    y = np.empty_like(x)
+    rep = (16 if dtype == F16 else 8) if brc else 1
+    mx = np.empty((M, rep), t)
+    sm = np.empty((M, rep), t)
+    lib().orc_log_softmax(_p(x), _p(y), _p(mx), _p(sm), M, K, dtype, int(brc))
+    return (y, mx, sm) if brc else (y, mx[:, 0], sm[:, 0])
+
+
+def simple_softmax(x, in_sum, in_max, dtype=F16, stats_dtype=F32):
+    """x [M,K] (uint16 half bits or float32); in_sum / in_max [M] or [M, rep] in stats_dtype storage. Returns y."""
+    x = _c(x, np.uint16 if dtype == F16 else np.float32)
+    st = np.uint16 if stats_dtype == F16 else np.float32
+    in_sum, in_max = _c(in_sum, st).reshape(x.shape[0], -1), _c(in_max, st).reshape(x.shape[0], -1)
+    y = np.empty_like(x)
+    lib().orc_simple_softmax(_p(x), _p(y), _p(in_sum), _p(in_max), x.shape[0], x.shape[1], dtype, stats_dtype, in_sum.shape[1])
+    return y
+
+
 def _src(x, dtype):
     return _c(x, np.float32 if dtype == F32 else np.uint16)
 

@@ -480,6 +480,52 @@ static void TestSoftmaxFlashV2()
     std::printf("SoftmaxFlashV2 two tiles: ok\n");
 }
 
+// LogSoftMax as in the reference's logsoftmax example: statistics are LocalTensor<T>, one 32-byte block per row.
+static void TestLogSoftMax()
+{
+    using namespace AscendC;
+    const uint32_t M = 24, K = 512;
+    std::mt19937 rng(21);
+    std::normal_distribution<float> nd(0.f, 2.f);
+    std::vector<float> x(M * K);
+    for (auto& v : x) v = nd(rng);
+    DevBuf<float> dX(x), dY(M * K), dSum(M * 8), dMax(M * 8);
+    DevBuf<uint8_t> dTmp(32);
+    LogSoftMaxTiling tiling{};
+    tiling.srcM = M;
+    tiling.srcK = K;
+    TPipe pipe;
+    LogSoftMax<float>(LocalTensor<float>(dY.p, dY.n), LocalTensor<float>(dSum.p, dSum.n), LocalTensor<float>(dMax.p, dMax.n),
+                      LocalTensor<float>(dX.p, dX.n), LocalTensor<uint8_t>(dTmp.p, dTmp.n), tiling);
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<float> y = dY.Download(), sum = dSum.Download(), mxv = dMax.Download();
+    int bad = 0;
+    for (uint32_t i = 0; i < M; ++i) {
+        float mx = -1e30f;
+        for (uint32_t j = 0; j < K; ++j) mx = std::fmax(mx, x[i * K + j]);
+        double s = 0;
+        for (uint32_t j = 0; j < K; ++j) s += std::exp(static_cast<double>(x[i * K + j] - mx));
+        if (mxv[i * 8] != mx || mxv[i * 8 + 7] != mx || std::fabs(sum[i * 8 + 3] - s) > 1e-5 * s) ++bad;
+        for (uint32_t j = 0; j < K; ++j) {
+            const double want = std::log10(std::exp(static_cast<double>(x[i * K + j] - mx)) / s);
+            if (std::fabs(y[i * K + j] - want) > 1e-3 + 1e-3 * std::fabs(want)) ++bad;
+        }
+    }
+    CHECK(bad == 0, "LogSoftMax: %d values wrong", bad);
+    std::printf("LogSoftMax: ok\n");
+    // SimpleSoftMax with the statistics LogSoftMax just wrote: 10^y_log must equal its result
+    DevBuf<float> dY2(M * K);
+    SimpleSoftMax<float>(LocalTensor<float>(dY2.p, dY2.n), LocalTensor<float>(dSum.p, dSum.n), LocalTensor<float>(dMax.p, dMax.n),
+                         LocalTensor<float>(dX.p, dX.n), SoftMaxTiling{M, K});
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<float> y2 = dY2.Download();
+    bad = 0;
+    for (uint32_t i = 0; i < M * K; ++i)
+        if (std::fabs(y2[i] - std::pow(10.0, static_cast<double>(y[i]))) > 1e-3 * y2[i] + 1e-9) ++bad;
+    CHECK(bad == 0, "SimpleSoftMax: %d values wrong", bad);
+    std::printf("SimpleSoftMax: ok\n");
+}
+
 // Constant tiling as in the reference's matmul_constant_tiling example: the shapes are template constants
 // (GetMMConfig + GetMatmulApiTiling), the object is initialised without a TCubeTiling.
 static constexpr MatmulShapeParams kConstShape = {256, 384, 128, 128, 256, 64};
@@ -616,6 +662,7 @@ int main()
     TestMatmulNzAtomicAlign();
     TestQuantPolicies();
     TestSoftmaxFlashV2();
+    TestLogSoftMax();
     TestConstantTiling();
     TestIterateBatch();
     TestErrorLatch();

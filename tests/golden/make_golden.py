@@ -14,6 +14,8 @@ input+output samples as .npz, so the tests can pin the CPU oracle without the re
   matmul_fp16.npz    04_advanced_api/00_matmul/matmul/scripts/gen_data.py (rows/cols sampled)
   matmul_quant.npz   04_advanced_api/00_matmul/matmul_quant/scripts/gen_data.py, vector mode (sampled)
   softmax.npz        04_advanced_api/01_activation/softmax/scripts/gen_data.py: softmax_py_float
+  logsoftmax.npz     04_advanced_api/01_activation/logsoftmax/scripts/gen_data.py: softmax_2d_py_float(log=True) on the
+                     example's 128x128 uniform(-10, 10) input, plus a half input widened to fp32
   quant.npz          04_advanced_api/03_quantization/quant/scripts/gen_data.py (both arch variants)
   dequant.npz        04_advanced_api/03_quantization/dequant/scripts/gen_data.py
   grouped.npz        05_best_practices/03_fusion_compute/quant_group_matmul_high_performance/scripts/gen_data.py
@@ -158,6 +160,17 @@ def softmax(ref):
                         y16=y16.astype(np.float32), max16=mx16, sum16=sm16)
 
 
+def logsoftmax(ref):
+    mod = load_module(os.path.join(ref, EX, "04_advanced_api/01_activation/logsoftmax/scripts/gen_data.py"), "ref_logsoftmax")
+    rng = np.random.default_rng(17)
+    x32 = rng.uniform(-10, 10, (128, 128)).astype(np.float32)
+    y32, mx32, sm32, _ = mod.softmax_2d_py_float(x32.copy(), update=False, log=True)
+    x16 = rng.uniform(-10, 10, (40, 512)).astype(np.float16)
+    y16, mx16, sm16, _ = mod.softmax_2d_py_float(x16.astype(np.float32), update=False, log=True)
+    np.savez_compressed(os.path.join(HERE, "logsoftmax.npz"), x32=x32, y32=y32.astype(np.float32), max32=mx32, sum32=sm32, x16=x16,
+                        y16=y16.astype(np.float32), max16=mx16, sum16=sm16)
+
+
 def quant(ref):
     p = os.path.join(ref, EX, "04_advanced_api/03_quantization/quant/scripts/gen_data.py")
     out = {}
@@ -247,6 +260,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("ASC_REFERENCE_ROOT", "reference"))
     args = ap.parse_args()
-    for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, quant, dequant, grouped, mxfp4, casts):
+    for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, logsoftmax, quant, dequant, grouped, mxfp4, casts):
         fn(args.ref)
         print("wrote", fn.__name__)

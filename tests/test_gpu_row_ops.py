@@ -285,6 +285,83 @@ def test_softmax_flash_v2_two_steps(m, k, brc, dtype, stats_dtype):
     assert np.allclose(_to_f32(sum2, stats_dtype)[:, 0], ident, rtol=4e-3 if stats_dtype == 1 else 1e-3)
 
 
+@pytest.mark.parametrize("dtype", [1, 0])
+@pytest.mark.parametrize("m,k,brc", [(1, 16, True), (37, 2048, True), (64, 4096, False), (5, 16384, True), (2, 32768, True), (4096, 2048, True),
+                                     (300, 64, False)])
+def test_log_softmax(m, k, brc, dtype):
+    """LogSoftMax against the oracle: max bit exact, sum and y within 1e-3; statistics in the source dtype."""
+    ab = dev()
+    rng = np.random.default_rng(m * 7 + k + dtype)
+    x = (rng.standard_normal((m, k)) * 3).astype(np.float32)
+    xin = _as_stored(x, dtype)
+    rep = (16 if dtype == 1 else 8) if brc else 1
+    d_y, d_sum, d_max = ab.empty((m, k), xin.dtype), ab.empty((m, rep), xin.dtype), ab.empty((m, rep), xin.dtype)
+    ab.check(ab.log_softmax(ab.to_dev(xin), d_y, d_sum, d_max, m, k, dtype, brc), "log_softmax")
+    ab.sync()
+    ry, rmx, rs = orc.log_softmax(xin, dtype, brc=brc)
+    y, s, mx = d_y.download().reshape(m, k), d_sum.download().reshape(m, rep), d_max.download().reshape(m, rep)
+    assert (mx == rmx.reshape(m, rep)).all()
+    assert np.allclose(_to_f32(s, dtype), _to_f32(rs.reshape(m, rep), dtype), rtol=2e-3 if dtype == 1 else 1e-4)
+    yf, rf = _to_f32(y, dtype), _to_f32(ry, dtype)
+    assert (np.abs(yf - rf) <= 1e-3 * np.abs(rf) + (2e-3 if dtype == 1 else 1e-5)).all()
+    # against the reference's golden formula (log10 of the softmax) in float64
+    xs = _to_f32(xin, dtype).astype(np.float64)
+    e = np.exp(xs - xs.max(axis=1, keepdims=True))
+    gold = np.log10(e / e.sum(axis=1, keepdims=True))
+    assert (np.abs(yf - gold) <= 1e-3 * np.abs(gold) + (4e-3 if dtype == 1 else 1e-4)).all()
+
+
+def test_log_softmax_underflow_and_errors():
+    """Entries far below the row maximum underflow exp() to 0 and give -inf like the reference's ln(0); argument checks as SoftMax."""
+    ab = dev()
+    x = np.zeros((4, 64), np.float32)
+    x[:, 0] = 200.0
+    d_y, d_s, d_m = ab.empty((4, 64), np.float32), ab.empty((4, 8), np.float32), ab.empty((4, 8), np.float32)
+    ab.check(ab.log_softmax(ab.to_dev(x), d_y, d_s, d_m, 4, 64, 0, True))
+    ab.sync()
+    y = d_y.download().reshape(4, 64)
+    assert (y[:, 0] == 0).all() and np.isneginf(y[:, 1:]).all()
+    assert (d_s.download() == 1).all() and (d_m.download() == 200).all()
+    assert ab.log_softmax(ab.to_dev(x), d_y, d_s, d_m, 4, 60, 0, True) == ab.EALIGN      # 60 floats: not whole 32-byte blocks
+    assert ab.log_softmax(ab.to_dev(x), d_y, d_s, d_m, 4, 64, 2, True) == ab.EUNSUPPORTED  # bf16 is not a LogSoftMax type
+    assert ab.log_softmax(None, d_y, d_s, d_m, 4, 64, 0, True) == ab.EINVAL
+    assert ab.log_softmax(ab.to_dev(x), d_y, d_s, d_m, 0, 64, 0, True) == 0
+
+
+@pytest.mark.parametrize("dtype,stats_dtype", [(1, 0), (1, 1), (0, 0)])
+@pytest.mark.parametrize("m,k,brc", [(1, 16, True), (37, 2048, True), (64, 4096, False), (3, 32768, True), (4096, 2048, True), (301, 80, False)])
+def test_simple_softmax(m, k, brc, dtype, stats_dtype):
+    """SimpleSoftMax with the statistics of a SoftMax over the same rows: equals the oracle within 1e-3 and reproduces SoftMax itself."""
+    ab = dev()
+    rng = np.random.default_rng(m * 3 + k + dtype + stats_dtype)
+    x = (rng.standard_normal((m, k)) * 3).astype(np.float32)
+    xin = _as_stored(x, dtype)
+    xf = _to_f32(xin, dtype)
+    mx = xf.max(axis=1)
+    sm = np.exp(xf - mx[:, None]).sum(axis=1, dtype=np.float64).astype(np.float32)
+    rep = (16 if stats_dtype == 1 else 8) if brc else 1
+    mx_s, sm_s = _as_stored(np.repeat(mx[:, None], rep, 1), stats_dtype), _as_stored(np.repeat(sm[:, None], rep, 1), stats_dtype)
+    d_y = ab.empty((m, k), xin.dtype)
+    ab.check(ab.simple_softmax(ab.to_dev(xin), d_y, ab.to_dev(sm_s), ab.to_dev(mx_s), m, k, dtype, stats_dtype, brc), "simple_softmax")
+    ab.sync()
+    y = _to_f32(d_y.download().reshape(m, k), dtype)
+    ref = _to_f32(orc.simple_softmax(xin, sm_s, mx_s, dtype, stats_dtype), dtype)
+    assert (np.abs(y - ref) <= 1e-3 * np.abs(ref) + (HALF_STEP if dtype == 1 else 1e-30)).all()
+    if stats_dtype == 0:  # exact statistics: the two-pass result is the softmax
+        gold = np.exp(xf.astype(np.float64) - mx[:, None]) / sm[:, None].astype(np.float64)
+        assert (np.abs(y - gold) <= 1e-3 * gold + (HALF_STEP if dtype == 1 else 1e-30)).all()
+
+
+def test_simple_softmax_argument_errors():
+    ab = dev()
+    x, y, st = ab.empty((4, 64), np.float32), ab.empty((4, 64), np.float32), ab.empty((4, 8), np.float32)
+    assert ab.simple_softmax(x, y, st, st, 0, 64, ab.F32, ab.F32) == 0
+    assert ab.simple_softmax(x, y, None, st, 4, 64, ab.F32, ab.F32) == ab.EINVAL
+    assert ab.simple_softmax(x, y, st, st, 4, 60, ab.F32, ab.F32) == ab.EALIGN
+    assert ab.simple_softmax(x, y, st, st, 4, 64, ab.F32, ab.F16) == ab.EUNSUPPORTED   # half statistics beside float data: no such overload
+    assert ab.simple_softmax(x, y, st, st, 4, 64, ab.BF16, ab.F32) == ab.EUNSUPPORTED
+
+
 def test_new_entry_points_edge_cases():
     """Zero extents succeed without touching memory; bad extents, types and alignments are refused with the documented codes."""
     ab = dev()

@@ -89,6 +89,31 @@ def test_softmax_recipe(golden_dir):
     assert (mx32[:, 0] == g["max32"][:, 0]).all()
 
 
+def test_logsoftmax_recipe(golden_dir):
+    """LogSoftMax oracle against the reference example's golden generator (log10 of the softmax)."""
+    g = load(golden_dir, "logsoftmax.npz")
+    y32, mx32, sm32 = orc.log_softmax(g["x32"], orc.F32, brc=True)
+    assert mx32.shape == (128, 8) and (mx32 == g["max32"]).all() and (sm32 == sm32[:, :1]).all()
+    assert np.allclose(sm32[:, :1], g["sum32"], rtol=1e-5)
+    assert np.allclose(y32, g["y32"], rtol=1e-5, atol=1e-5)
+    y16, mx16, sm16 = orc.log_softmax(g["x16"].view(np.uint16), orc.F16)
+    assert (mx16.view(np.float16).astype(np.float32) == g["max16"][:, 0]).all()
+    assert np.allclose(sm16.view(np.float16).astype(np.float32), g["sum16"][:, 0], rtol=1e-3)
+    assert np.allclose(y16.view(np.float16).astype(np.float32), g["y16"], rtol=1e-3, atol=1e-3)
+
+
+def test_simple_softmax_reproduces_the_softmax_recipe(golden_dir):
+    """SimpleSoftMax fed with SoftMax's own max / sum is the same arithmetic: bit-identical y, hence pinned by the softmax golden."""
+    g = load(golden_dir, "softmax.npz")
+    x16 = g["x16"].view(np.uint16)
+    y, mx, sm = orc.softmax(x16, orc.F16)
+    assert (orc.simple_softmax(x16, sm, mx, orc.F16, orc.F32) == y).all()
+    y32, mx32, sm32 = orc.softmax(g["x32"], orc.F32, brc=True)
+    assert (orc.simple_softmax(g["x32"], sm32, mx32, orc.F32, orc.F32) == y32).all()
+    ys = orc.simple_softmax(x16, sm, mx, orc.F16, orc.F32).view(np.float16).astype(np.float32)
+    assert np.allclose(ys, g["y16"], rtol=1e-3, atol=1e-7)
+
+
 def test_quant_recipe(golden_dir):
     g = load(golden_dir, "quant.npz")
     # dav-2201 variant: half source; round(src*2+0.9) evaluated by numpy in half precision
