@@ -631,6 +631,106 @@ int launch_softmax_flash(const T* src, T* dst, ST* sum, ST* mx, T* expmax, const
     return ASCB200_OK;
 }
 
+// ---- SoftmaxGrad / SoftmaxGradFront (include/adv_api/activation/softmaxgrad.h:57-175) ------------------------------------
+// Per row of grad and src (the softmax output y): s = rowsum(grad * src) in fp32;
+//   FRONT:  dst[m, rep] = s (one 32-byte block per row);      else: dst[m, k] = (grad - s) * src, cast RINT
+// (impl/adv_api/detail/activation/softmax/membase/common/softmax_grad_nd_impl.h:27-60).  Both rows stay in registers between
+// the reduction and the output pass: 6 bytes of traffic per half element (4 in FRONT mode), each byte moved once.
+template <typename T>
+__device__ __forceinline__ void unpack_chunk(const uint4& raw, float (&f)[16 / sizeof(T)])
+{
+    if constexpr (sizeof(T) == 2) {
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 v = __half22float2(h[j]);
+            f[2 * j] = v.x;
+            f[2 * j + 1] = v.y;
+        }
+    } else {
+        f[0] = __uint_as_float(raw.x);
+        f[1] = __uint_as_float(raw.y);
+        f[2] = __uint_as_float(raw.z);
+        f[3] = __uint_as_float(raw.w);
+    }
+}
+
+template <typename T, int TPR, int NCHUNK, bool FRONT>
+__global__ void __launch_bounds__(TPR > 32 ? TPR : 128, TPR > 32 ? 1 : 4)
+softmax_grad_rows_kernel(const T* __restrict__ grad, const T* __restrict__ src, T* __restrict__ dst, int m, int k, int front_rep)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    __shared__ float red[32];
+    const int nchunks = k / VEC;
+    const int t = TPR > 32 ? threadIdx.x : (threadIdx.x & 31);
+    const int row = TPR > 32 ? blockIdx.x : blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= m) return;  // a whole warp (or block) leaves together
+    uint4 rg[NCHUNK], rs[NCHUNK];
+    softmax_load_row<T, TPR, NCHUNK>(grad + static_cast<size_t>(row) * k, t, nchunks, rg);
+    softmax_load_row<T, TPR, NCHUNK>(src + static_cast<size_t>(row) * k, t, nchunks, rs);
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+        if (t + i * TPR < nchunks) {
+            float g[VEC], y[VEC];
+            unpack_chunk<T>(rg[i], g);
+            unpack_chunk<T>(rs[i], y);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) s += __fmul_rn(g[j], y[j]);  // Mul then ReduceSum: the product is rounded before it is added
+        }
+    }
+    s = row_reduce_sum<TPR>(s, red);
+    if constexpr (FRONT) {
+        if (t < front_rep) {
+            if constexpr (sizeof(T) == 2) dst[static_cast<size_t>(row) * front_rep + t] = __float2half_rn(clamp_half_range(s));
+            else dst[static_cast<size_t>(row) * front_rep + t] = s;
+        }
+    } else {
+        T* drow = dst + static_cast<size_t>(row) * k;
+#pragma unroll
+        for (int i = 0; i < NCHUNK; ++i) {
+            const int c = t + i * TPR;
+            if (c < nchunks) {
+                float g[VEC], y[VEC];
+                unpack_chunk<T>(rg[i], g);
+                unpack_chunk<T>(rs[i], y);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) g[j] = __fmul_rn(__fsub_rn(g[j], s), y[j]);
+                if constexpr (sizeof(T) == 2) {
+                    uint4 o;
+                    __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(clamp_half_range(g[2 * j]), clamp_half_range(g[2 * j + 1]));
+                    *reinterpret_cast<uint4*>(drow + c * 8) = o;
+                } else {
+                    *reinterpret_cast<float4*>(drow + c * 4) = make_float4(g[0], g[1], g[2], g[3]);
+                }
+            }
+        }
+    }
+}
+
+template <typename T, bool FRONT>
+int launch_softmax_grad(const T* grad, const T* src, T* dst, int m, int k, int front_rep, cudaStream_t st)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    const int nchunks = k / VEC;
+#define ASCB200_SG_WARP(NC) softmax_grad_rows_kernel<T, 32, NC, FRONT><<<(m + 3) / 4, 128, 0, st>>>(grad, src, dst, m, k, front_rep)
+#define ASCB200_SG_BLOCK(TPR, NC) softmax_grad_rows_kernel<T, TPR, NC, FRONT><<<m, TPR, 0, st>>>(grad, src, dst, m, k, front_rep)
+    if (nchunks <= 32) ASCB200_SG_WARP(1);
+    else if (nchunks <= 64) ASCB200_SG_WARP(2);
+    else if (nchunks <= 128) ASCB200_SG_WARP(4);
+    else if (nchunks <= 256) ASCB200_SG_WARP(8);
+    else if (nchunks <= 1024) ASCB200_SG_BLOCK(256, 4);
+    else if (nchunks <= 2048) ASCB200_SG_BLOCK(256, 8);
+    else if (nchunks <= 8192) ASCB200_SG_BLOCK(1024, 8);
+    else return ASCB200_ETOOBIG;
+#undef ASCB200_SG_WARP
+#undef ASCB200_SG_BLOCK
+    ASCB200_CUDA(cudaGetLastError());
+    return ASCB200_OK;
+}
+
 int check_softmax_args(const void* src, void* dst, float* sum, float* mx, int m, int k, int dtype)
 {
     if (!src || !dst || !sum || !mx || m < 0 || k <= 0) return ASCB200_EINVAL;
@@ -720,6 +820,28 @@ int ascb200_simple_softmax(const void* src, void* dst, const void* in_sum, const
                                                          nullptr, __half(), m, k, rep, st->sm_count, s);
     return launch_softmax<__half, kSoftmaxSimpleF16>(static_cast<const __half*>(src), static_cast<__half*>(dst), sum, mx, nullptr, nullptr,
                                                      nullptr, __half(), m, k, rep, st->sm_count, s);
+}
+
+int ascb200_softmax_grad(const void* grad, const void* src, void* dst, int32_t m, int32_t k, int32_t dtype, int32_t is_front, void* stream)
+{
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    if (!grad || !src || !dst || m < 0 || k <= 0) return ASCB200_EINVAL;
+    if (dtype != ASCB200_F16 && dtype != ASCB200_F32) return ASCB200_EUNSUPPORTED;
+    const int esz = dtype == ASCB200_F16 ? 2 : 4;
+    if ((static_cast<size_t>(k) * esz) % 32 != 0) return ASCB200_EALIGN;
+    if (!aligned_to(grad, 16) || !aligned_to(src, 16) || !aligned_to(dst, is_front ? esz : 16)) return ASCB200_EALIGN;
+    if (m == 0) return ASCB200_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int rep = 32 / esz;
+    if (dtype == ASCB200_F16) {
+        const __half *g = static_cast<const __half*>(grad), *y = static_cast<const __half*>(src);
+        return is_front ? launch_softmax_grad<__half, true>(g, y, static_cast<__half*>(dst), m, k, rep, s)
+                        : launch_softmax_grad<__half, false>(g, y, static_cast<__half*>(dst), m, k, rep, s);
+    }
+    const float *g = static_cast<const float*>(grad), *y = static_cast<const float*>(src);
+    return is_front ? launch_softmax_grad<float, true>(g, y, static_cast<float*>(dst), m, k, rep, s)
+                    : launch_softmax_grad<float, false>(g, y, static_cast<float*>(dst), m, k, rep, s);
 }
 
 int ascb200_softmax_flash_v2(const void* src, void* dst, void* exp_sum, void* max, void* exp_max, const void* in_exp_sum, const void* in_max,

@@ -112,6 +112,40 @@ inline void SimpleSoftMax(const LocalTensor<half>& dstTensor, const LocalTensor<
     SimpleSoftMax<T, isReuseSource, isBasicBlock, isDataFormatNZ, config>(dstTensor, inSumTensor, inMaxTensor, srcTensor, tiling, softmaxShapeInfo);
 }
 
+// SoftmaxGrad<T>(dst, grad, src, [sharedTmpBuffer,] tiling, isFront, shapeInfo) and SoftmaxGradFront<T>(dst, grad, src,
+// [sharedTmpBuffer,] tiling, shapeInfo)  (include/adv_api/activation/softmaxgrad.h:57-175).  src is the softmax output y.
+template <typename T, bool isReuseSource = false, bool isDataFormatNZ = false>
+inline void SoftmaxGrad(const LocalTensor<T>& dstTensor, const LocalTensor<T>& gradTensor, const LocalTensor<T>& srcTensor,
+                        const SoftMaxTiling& tiling, bool isFront = false, const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    static_assert(!isDataFormatNZ, "NZ-format SoftmaxGrad is not part of the B200 path");
+    const uint32_t m = softmaxShapeInfo.srcM ? softmaxShapeInfo.srcM : tiling.srcM;
+    const uint32_t k = softmaxShapeInfo.srcK ? softmaxShapeInfo.srcK : tiling.srcK;
+    detail::Latch(ascb200_softmax_grad(gradTensor.GetPhyAddr(), srcTensor.GetPhyAddr(), dstTensor.GetPhyAddr(), static_cast<int32_t>(m),
+                                       static_cast<int32_t>(k), detail::DTypeOf<T>::value, isFront ? 1 : 0, detail::CurrentStream()),
+                  "SoftmaxGrad");
+}
+template <typename T, bool isReuseSource = false, bool isDataFormatNZ = false>
+inline void SoftmaxGrad(const LocalTensor<T>& dstTensor, const LocalTensor<T>& gradTensor, const LocalTensor<T>& srcTensor,
+                        const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const SoftMaxTiling& tiling, bool isFront = false,
+                        const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    SoftmaxGrad<T, isReuseSource, isDataFormatNZ>(dstTensor, gradTensor, srcTensor, tiling, isFront, softmaxShapeInfo);
+}
+template <typename T, bool isBasicBlock = false, bool isDataFormatNZ = false>
+inline void SoftmaxGradFront(const LocalTensor<T>& dstTensor, const LocalTensor<T>& gradTensor, const LocalTensor<T>& srcTensor,
+                             const SoftMaxTiling& tiling, const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    SoftmaxGrad<T, false, isDataFormatNZ>(dstTensor, gradTensor, srcTensor, tiling, true, softmaxShapeInfo);
+}
+template <typename T, bool isBasicBlock = false, bool isDataFormatNZ = false>
+inline void SoftmaxGradFront(const LocalTensor<T>& dstTensor, const LocalTensor<T>& gradTensor, const LocalTensor<T>& srcTensor,
+                             const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const SoftMaxTiling& tiling,
+                             const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    SoftmaxGrad<T, false, isDataFormatNZ>(dstTensor, gradTensor, srcTensor, tiling, true, softmaxShapeInfo);
+}
+
 // SoftmaxFlashV2<T, isUpdate>(dst, expSum, max, src, expMax, inExpSum, inMax, tiling, shapeInfo)
 // (include/adv_api/activation/softmaxflashv2.h:93-260): the all-T overloads and the half data / float statistics overloads,
 // each with and without sharedTmpBuffer.

@@ -218,6 +218,14 @@ ASCB200_API int ascb200_log_softmax(const void* src_dev, void* dst_dev, void* su
 ASCB200_API int ascb200_simple_softmax(const void* src_dev, void* dst_dev, const void* in_sum_dev, const void* in_max_dev, int32_t m,
                                        int32_t k, int32_t dtype, int32_t stats_dtype, int32_t stats_brc, void* stream);
 
+/* SoftmaxGrad<T>(dst, grad, src, tiling, isFront, shapeInfo) and SoftmaxGradFront<T>(dst, grad, src, tiling, shapeInfo)
+ * (include/adv_api/activation/softmaxgrad.h:57-175): per row s = sum(grad * src) in fp32; is_front == 0 writes
+ * dst[m, k] = (grad - s) * src, is_front != 0 writes dst[m, 32 / sizeof(T)] = s (one 32-byte block per row)
+ * (impl/adv_api/detail/activation/softmax/membase/common/softmax_grad_nd_impl.h:27-60).  dtype F16 or F32;
+ * k * sizeof(T) a multiple of 32. */
+ASCB200_API int ascb200_softmax_grad(const void* grad_dev, const void* src_dev, void* dst_dev, int32_t m, int32_t k, int32_t dtype,
+                                     int32_t is_front, void* stream);
+
 /* ---- AscendQuant -------------------------------------------------------------------------------- */
 
 /* AscendQuant per tensor: dst = int8(rint_sat(half(src) * half(scale) + half(offset))), arithmetic in fp16

@@ -529,6 +529,43 @@ ORC_API void orc_simple_softmax(const void* x, void* y, const void* in_sum, cons
 }
 
 /* ---------------------------------------------------------------------------------------------
+ * SoftmaxGrad / SoftmaxGradFront: s = rowsum(float(grad) * float(src)); front: dst[m, rep] = s;
+ * else dst = (grad - s) * src; fp32 arithmetic, cast RINT for half
+ * (impl/adv_api/detail/activation/softmax/membase/common/softmax_grad_nd_impl.h:27-60; golden
+ *  examples/01_simd_cpp_api/04_advanced_api/01_activation/softmaxgrad/scripts/gen_data.py:20-27).
+ * rep = 32 / sizeof(T).  Row sums add k ascending.
+ * ------------------------------------------------------------------------------------------- */
+ORC_API void orc_softmax_grad(const void* grad, const void* src, void* dst, int M, int K, int dtype, int front)
+{
+    const int rep = dtype == ORC_F16 ? 16 : 8;
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m) {
+        float s = 0.0f;
+        for (int k = 0; k < K; ++k) {
+            const size_t i = (size_t)m * K + k;
+            const float g = dtype == ORC_F16 ? orc_f16_to_f32(((const uint16_t*)grad)[i]) : ((const float*)grad)[i];
+            const float y = dtype == ORC_F16 ? orc_f16_to_f32(((const uint16_t*)src)[i]) : ((const float*)src)[i];
+            s += g * y;
+        }
+        if (front) {
+            for (int r = 0; r < rep; ++r) {
+                if (dtype == ORC_F16) ((uint16_t*)dst)[(size_t)m * rep + r] = f32_to_f16(s, 1);
+                else ((float*)dst)[(size_t)m * rep + r] = s;
+            }
+            continue;
+        }
+        for (int k = 0; k < K; ++k) {
+            const size_t i = (size_t)m * K + k;
+            const float g = dtype == ORC_F16 ? orc_f16_to_f32(((const uint16_t*)grad)[i]) : ((const float*)grad)[i];
+            const float y = dtype == ORC_F16 ? orc_f16_to_f32(((const uint16_t*)src)[i]) : ((const float*)src)[i];
+            const float r = (g - s) * y;
+            if (dtype == ORC_F16) ((uint16_t*)dst)[i] = f32_to_f16(r, 1);
+            else ((float*)dst)[i] = r;
+        }
+    }
+}
+
+/* ---------------------------------------------------------------------------------------------
  * AscendQuant -> int8.  All arithmetic in fp16: src (and fp32 scale/offset) cast to half RINT with
  * saturation, Mul in half, Add in half, half -> int8 RINT with saturation
  * (impl/adv_api/detail/quantization/quant/ascend_quant_3510_impl.h:34-66 per tensor,

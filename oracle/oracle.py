@@ -187,6 +187,16 @@ def simple_softmax(x, in_sum, in_max, dtype=F16, stats_dtype=F32):
     return y
 
 
+def softmax_grad(grad, src, dtype=F16, front=False):
+    """grad, src [M,K] (uint16 half bits or float32). Returns dst [M,K], or [M, 32/sizeof(T)] when front."""
+    t = np.uint16 if dtype == F16 else np.float32
+    grad, src = _c(grad, t), _c(src, t)
+    M, K = grad.shape
+    out = np.empty((M, (16 if dtype == F16 else 8)) if front else (M, K), t)
+    lib().orc_softmax_grad(_p(grad), _p(src), _p(out), M, K, dtype, int(front))
+    return out
+
+
 def _src(x, dtype):
     return _c(x, np.float32 if dtype == F32 else np.uint16)
 

@@ -524,6 +524,22 @@ static void TestLogSoftMax()
         if (std::fabs(y2[i] - std::pow(10.0, static_cast<double>(y[i]))) > 1e-3 * y2[i] + 1e-9) ++bad;
     CHECK(bad == 0, "SimpleSoftMax: %d values wrong", bad);
     std::printf("SimpleSoftMax: ok\n");
+    // SoftmaxGrad of that softmax output with grad = x, then SoftmaxGradFront: the row sums
+    DevBuf<float> dG(M * K), dF(M * 8);
+    SoftmaxGrad<float>(LocalTensor<float>(dG.p, dG.n), LocalTensor<float>(dX.p, dX.n), LocalTensor<float>(dY2.p, dY2.n), SoftMaxTiling{M, K});
+    SoftmaxGradFront<float>(LocalTensor<float>(dF.p, dF.n), LocalTensor<float>(dX.p, dX.n), LocalTensor<float>(dY2.p, dY2.n), SoftMaxTiling{M, K});
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<float> gr = dG.Download(), fr = dF.Download();
+    bad = 0;
+    for (uint32_t i = 0; i < M; ++i) {
+        double s = 0;
+        for (uint32_t j = 0; j < K; ++j) s += static_cast<double>(x[i * K + j]) * y2[i * K + j];
+        if (std::fabs(fr[i * 8] - s) > 1e-4 * (1 + std::fabs(s)) || fr[i * 8 + 7] != fr[i * 8]) ++bad;
+        for (uint32_t j = 0; j < K; ++j)
+            if (std::fabs(gr[i * K + j] - (x[i * K + j] - s) * y2[i * K + j]) > 1e-4) ++bad;
+    }
+    CHECK(bad == 0, "SoftmaxGrad: %d values wrong", bad);
+    std::printf("SoftmaxGrad: ok\n");
 }
 
 // Constant tiling as in the reference's matmul_constant_tiling example: the shapes are template constants

@@ -16,6 +16,8 @@ input+output samples as .npz, so the tests can pin the CPU oracle without the re
   softmax.npz        04_advanced_api/01_activation/softmax/scripts/gen_data.py: softmax_py_float
   logsoftmax.npz     04_advanced_api/01_activation/logsoftmax/scripts/gen_data.py: softmax_2d_py_float(log=True) on the
                      example's 128x128 uniform(-10, 10) input, plus a half input widened to fp32
+  softmaxgrad.npz    04_advanced_api/01_activation/softmaxgrad/scripts/gen_data.py: softmax_grad_float, both modes, on the
+                     example's uniform(-1, 1) inputs (rows sampled from its 960x960 shape)
   quant.npz          04_advanced_api/03_quantization/quant/scripts/gen_data.py (both arch variants)
   dequant.npz        04_advanced_api/03_quantization/dequant/scripts/gen_data.py
   grouped.npz        05_best_practices/03_fusion_compute/quant_group_matmul_high_performance/scripts/gen_data.py
@@ -171,6 +173,15 @@ def logsoftmax(ref):
                         y16=y16.astype(np.float32), max16=mx16, sum16=sm16)
 
 
+def softmaxgrad(ref):
+    mod = load_module(os.path.join(ref, EX, "04_advanced_api/01_activation/softmaxgrad/scripts/gen_data.py"), "ref_softmaxgrad")
+    rng = np.random.default_rng(19)
+    grad = rng.uniform(-1, 1, (16, 960)).astype(np.float32)
+    src = rng.uniform(-1, 1, (16, 960)).astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, "softmaxgrad.npz"), grad=grad, src=src, golden=mod.softmax_grad_float(grad, src, isFront=False),
+                        front=mod.softmax_grad_float(grad, src, isFront=True))
+
+
 def quant(ref):
     p = os.path.join(ref, EX, "04_advanced_api/03_quantization/quant/scripts/gen_data.py")
     out = {}
@@ -260,6 +271,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("ASC_REFERENCE_ROOT", "reference"))
     args = ap.parse_args()
-    for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, logsoftmax, quant, dequant, grouped, mxfp4, casts):
+    for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, logsoftmax, softmaxgrad, quant, dequant, grouped, mxfp4, casts):
         fn(args.ref)
         print("wrote", fn.__name__)

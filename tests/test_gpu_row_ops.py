@@ -362,6 +362,40 @@ def test_simple_softmax_argument_errors():
     assert ab.simple_softmax(x, y, st, st, 4, 64, ab.BF16, ab.F32) == ab.EUNSUPPORTED
 
 
+@pytest.mark.parametrize("dtype", [1, 0])
+@pytest.mark.parametrize("front", [False, True])
+@pytest.mark.parametrize("m,k", [(1, 16), (37, 2048), (64, 4096), (5, 16384), (2, 32768), (4096, 2048), (301, 960)])
+def test_softmax_grad(m, k, front, dtype):
+    """SoftmaxGrad / SoftmaxGradFront against the oracle: the row sum within fp32 reordering, the output within 1e-3."""
+    ab = dev()
+    rng = np.random.default_rng(m * 5 + k + dtype)
+    grad = _as_stored(rng.uniform(-1, 1, (m, k)).astype(np.float32), dtype)
+    x = rng.standard_normal((m, k)) * 2
+    y = np.exp(x - x.max(axis=1, keepdims=True))
+    src = _as_stored((y / y.sum(axis=1, keepdims=True)).astype(np.float32), dtype)   # a softmax output, as in a backward pass
+    rep = 16 if dtype == 1 else 8
+    d_out = ab.empty((m, rep) if front else (m, k), grad.dtype)
+    ab.check(ab.softmax_grad(ab.to_dev(grad), ab.to_dev(src), d_out, m, k, dtype, front), "softmax_grad")
+    ab.sync()
+    got = _to_f32(d_out.download().reshape(m, -1), dtype)
+    ref = _to_f32(orc.softmax_grad(grad, src, dtype, front=front), dtype)
+    scale = np.abs(_to_f32(grad, dtype)).max() * np.abs(_to_f32(src, dtype)).max(axis=1, keepdims=True)
+    tol = 1e-3 * np.abs(ref) + (1e-3 if dtype == 1 else 1e-5) * (1.0 if front else scale) + (HALF_STEP if dtype == 1 else 0)
+    assert (np.abs(got - ref) <= tol).all()
+    if front:
+        assert (got == got[:, :1]).all()
+
+
+def test_softmax_grad_argument_errors():
+    ab = dev()
+    g, y, o = ab.empty((4, 64), np.float32), ab.empty((4, 64), np.float32), ab.empty((4, 64), np.float32)
+    assert ab.softmax_grad(g, y, o, 0, 64, ab.F32) == 0
+    assert ab.softmax_grad(g, None, o, 4, 64, ab.F32) == ab.EINVAL
+    assert ab.softmax_grad(g, y, o, 4, 60, ab.F32) == ab.EALIGN
+    assert ab.softmax_grad(g, y, o, 4, 64, ab.BF16) == ab.EUNSUPPORTED
+    assert ab.softmax_grad(g, y, o, 4, 1 << 20, ab.F32) == ab.ETOOBIG
+
+
 def test_new_entry_points_edge_cases():
     """Zero extents succeed without touching memory; bad extents, types and alignments are refused with the documented codes."""
     ab = dev()

@@ -114,6 +114,20 @@ def test_simple_softmax_reproduces_the_softmax_recipe(golden_dir):
     assert np.allclose(ys, g["y16"], rtol=1e-3, atol=1e-7)
 
 
+def test_softmaxgrad_recipe(golden_dir):
+    """SoftmaxGrad / SoftmaxGradFront oracle against the reference example's generator."""
+    g = load(golden_dir, "softmaxgrad.npz")
+    out = orc.softmax_grad(g["grad"], g["src"], orc.F32)
+    assert np.allclose(out, g["golden"], rtol=1e-4, atol=1e-5)
+    front = orc.softmax_grad(g["grad"], g["src"], orc.F32, front=True)
+    assert front.shape == (16, 8) and (front == front[:, :1]).all()
+    assert np.allclose(front[:, :1], g["front"], rtol=1e-4, atol=1e-5)
+    g16, s16 = g["grad"].astype(np.float16), g["src"].astype(np.float16)
+    out16 = orc.softmax_grad(g16.view(np.uint16), s16.view(np.uint16), orc.F16).view(np.float16).astype(np.float32)
+    gf, sf = g16.astype(np.float32), s16.astype(np.float32)
+    assert np.allclose(out16, (gf - (gf * sf).sum(axis=1, keepdims=True)) * sf, rtol=2e-3, atol=1e-3)
+
+
 def test_quant_recipe(golden_dir):
     g = load(golden_dir, "quant.npz")
     # dav-2201 variant: half source; round(src*2+0.9) evaluated by numpy in half precision
