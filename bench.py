@@ -679,6 +679,55 @@ class SoftmaxFlashStep(RowOp):
                     (self.mx.download().reshape(self.M, 8)[:64] == mx).all())
 
 
+class SoftmaxGradStep(RowOp):
+    name = "softmaxgrad_131072x2048_fp16"
+    metric, dtype = "SoftmaxGrad (fp16 grad and softmax output in, fp16 out) bandwidth", "f16"
+    M, K = 131072, 2048
+    traffic_1gpu = None
+
+    def __init__(self, ab, rank, world, sets):
+        from gpu_util import f16_bits
+        self.ab, self.rank, self.world = ab, rank, world
+        rng = np.random.default_rng(0xA5C00013 + rank)
+        x = rng.standard_normal((4096, self.K), dtype=np.float32) * 2.0
+        e = np.exp(x - x.max(axis=1, keepdims=True))
+        self.y_h = np.tile(f16_bits(e / e.sum(axis=1, keepdims=True)), (self.M // 4096, 1))
+        self.g_h = np.tile(f16_bits(rng.uniform(-1, 1, (4096, self.K)).astype(np.float32)), (self.M // 4096, 1))
+        self.sets = sets = 2   # 1.6 GB per set
+        self.g = [ab.to_dev(self.g_h) for _ in range(sets)]
+        self.y = [ab.to_dev(self.y_h) for _ in range(sets)]
+        self.o = [ab.empty((self.M, self.K), np.uint16) for _ in range(sets)]
+        self.config = {"workload": self.name, "M": self.M, "K": self.K, "shard": f"replica per rank x{world}",
+                       "cache": f"{sets} rotating buffer sets ({sets * self.per_step_bytes() // 2**20} MiB > L2)"}
+
+    def per_step_bytes(self):
+        return self.M * self.K * 6   # grad and y in, dst out
+
+    def step(self, i, stream=None):
+        ab, s = self.ab, i % self.sets
+        ab.check(ab.softmax_grad(self.g[s], self.y[s], self.o[s], self.M, self.K, ab.F16, False, stream=stream))
+
+    def h2d_arrays(self):
+        return [self.g_h, self.y_h]
+
+    def h2d_targets(self, s):
+        return [self.g[s], self.y[s]]
+
+    def d2h_buffers(self, s):
+        return [(self.o[s], self.M * self.K * 2)]
+
+    def cpu_sample(self, orc, rows):
+        rows = min(rows * 16, self.M)
+        t0 = time.perf_counter()
+        orc.softmax_grad(self.g_h[:rows], self.y_h[:rows], orc.F16)
+        return time.perf_counter() - t0, rows * (self.per_step_bytes() / self.M), f"{rows} of {self.M} rows"
+
+    def verify(self, orc):
+        ref = orc.f16_bits_to_f32(orc.softmax_grad(self.g_h[:64], self.y_h[:64], orc.F16))
+        got = orc.f16_bits_to_f32(self.o[0].download().reshape(self.M, self.K)[:64])
+        return bool((np.abs(got - ref) <= 1e-3 * np.abs(ref) + 1e-5).all())
+
+
 class NzUnpack(RowOp):
     name = "nz_weight_unpack_int8_16x7168x2048"
     metric, dtype = "fractal NZ -> K-major weight unpack bandwidth", "u8"
@@ -723,7 +772,7 @@ class NzUnpack(RowOp):
 
 WORKLOADS = {"a8w8": A8W8, "grouped": Grouped, "mxfp4": MXFP4, "softmax_quant": SoftmaxQuant, "softmax_quant_x64": SoftmaxQuantLarge,
              "fp16": FP16, "fp16_8192": FP16Large, "grouped_ref_shape": GroupedRefShape, "quant_per_group_fp4": QuantPerGroupFp4,
-             "softmax_flash_v2": SoftmaxFlashStep, "nz_unpack": NzUnpack}
+             "softmax_flash_v2": SoftmaxFlashStep, "softmax_grad": SoftmaxGradStep, "nz_unpack": NzUnpack}
 
 
 class PinnedSet:
