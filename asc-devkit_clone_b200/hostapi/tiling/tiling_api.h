@@ -198,6 +198,27 @@ public:
         return 0;
     }
     int32_t SetBufferSpace(int32_t = -1, int32_t = -1, int32_t = -1, int32_t = -1) { return 0; }
+    // Batch layouts (include/adv_api/matmul/matmul_tiling_base.h:406-438): the B, S, N, G, D extents of each operand are
+    // copied into the tiling (ALayoutInfoB ... CLayoutInfoS2, BatchNum) for IterateBatch to read.
+    int32_t SetALayout(int32_t b, int32_t s, int32_t n, int32_t g, int32_t d) { return SetLayout(aLayout_, b, s, n, g, d); }
+    int32_t SetBLayout(int32_t b, int32_t s, int32_t n, int32_t g, int32_t d) { return SetLayout(bLayout_, b, s, n, g, d); }
+    int32_t SetCLayout(int32_t b, int32_t s, int32_t n, int32_t g, int32_t d) { return SetLayout(cLayout_, b, s, n, g, d); }
+    // NORMAL layout: A [batchA, m, k], B [batchB, k, n] (or transposed), C [max(batchA, batchB), m, n]
+    // (impl/adv_api/tiling/matmul/matmul_tiling_base.cpp:365-400).
+    int32_t SetBatchInfoForNormal(int32_t batchA, int32_t batchB, int32_t m, int32_t n, int32_t k)
+    {
+        if (batchA <= 0 || batchB <= 0 || m <= 0 || n <= 0 || k <= 0) return -1;
+        SetLayout(aLayout_, batchA, m, 1, 1, k);
+        SetLayout(bLayout_, batchB, n, 1, 1, k);
+        SetLayout(cLayout_, std::max(batchA, batchB), m, 1, 1, n);
+        return 0;
+    }
+    int32_t SetBatchNum(int32_t batch)
+    {
+        if (batch <= 0) return -1;
+        batchNum_ = batch;
+        return 0;
+    }
     int32_t SetTraverse(MatrixTraverse t)
     {
         traverse_ = t;
@@ -232,6 +253,15 @@ protected:
         d.dtype = t;
         d.isTrans = trans;
         d.set = true;
+        return 0;
+    }
+    static int32_t SetLayout(int32_t (&l)[5], int32_t b, int32_t s, int32_t n, int32_t g, int32_t d)
+    {
+        l[0] = b;
+        l[1] = s;
+        l[2] = n;
+        l[3] = g;
+        l[4] = d;
         return 0;
     }
     static bool IsBf16(DataType t) { return t == DataType::DT_BF16 || t == DataType::DT_BFLOAT16; }
@@ -306,7 +336,22 @@ protected:
         t.set_batchN(1);
         t.set_singleBatchM(1);
         t.set_singleBatchN(1);
-        t.set_BatchNum(1);
+        t.set_BatchNum(batchNum_ > 0 ? batchNum_ : 1);
+        t.set_ALayoutInfoB(aLayout_[0]);
+        t.set_ALayoutInfoS(aLayout_[1]);
+        t.set_ALayoutInfoN(aLayout_[2]);
+        t.set_ALayoutInfoG(aLayout_[3]);
+        t.set_ALayoutInfoD(aLayout_[4]);
+        t.set_BLayoutInfoB(bLayout_[0]);
+        t.set_BLayoutInfoS(bLayout_[1]);
+        t.set_BLayoutInfoN(bLayout_[2]);
+        t.set_BLayoutInfoG(bLayout_[3]);
+        t.set_BLayoutInfoD(bLayout_[4]);
+        t.set_CLayoutInfoB(cLayout_[0]);
+        t.set_CLayoutInfoS1(cLayout_[1]);
+        t.set_CLayoutInfoN(cLayout_[2]);
+        t.set_CLayoutInfoG(cLayout_[3]);
+        t.set_CLayoutInfoS2(cLayout_[4]);
         t.set_mxTypePara(mad_ == MatrixMadType::MXMODE ? 1 : 0);
         return 0;
     }
@@ -317,6 +362,7 @@ protected:
     MatrixTraverse traverse_ = MatrixTraverse::NOSET;
     MatrixMadType mad_ = MatrixMadType::NORMAL;
     int32_t m_ = 0, n_ = 0, k_ = 0, orgM_ = 0, orgN_ = 0, orgKa_ = 0, orgKb_ = 0;
+    int32_t aLayout_[5] = {0, 0, 0, 0, 0}, bLayout_[5] = {0, 0, 0, 0, 0}, cLayout_[5] = {0, 0, 0, 0, 0}, batchNum_ = 0;
     int32_t fixM_ = -1, fixN_ = -1, fixK_ = -1, baseM_ = 0, baseN_ = 0, baseK_ = 0;
     int32_t cores_ = 1;
 };
@@ -392,6 +438,20 @@ public:
 
 private:
     int32_t dim_ = 1, userM_ = -1, userN_ = -1, userK_ = -1, singleM_ = 0, singleN_ = 0, singleK_ = 0, mDim_ = 1, nDim_ = 1;
+};
+
+// Batch tiling (include/adv_api/matmul/bmm_tiling.h:186-242): one block computes whole matrices of the batch; on a B200 the
+// batch runs as one launch per matrix pair on one device, so the used core count is 1 and no batch axis is split.
+class BatchMatmulTiling : public MatmulApiTilingBase {
+public:
+    using MatmulApiTilingBase::GetTiling;
+    using MatmulApiTilingBase::MatmulApiTilingBase;
+    int32_t GetCoreNum(int32_t& dim, int32_t& mDim, int32_t& nDim, int32_t& batchCoreM, int32_t& batchCoreN) const
+    {
+        dim = mDim = nDim = batchCoreM = batchCoreN = 1;
+        return 0;
+    }
+    int64_t GetTiling(optiling::TCubeTiling& tiling) override { return Fill(tiling, 1, m_, n_, k_); }
 };
 }  // namespace matmul_tiling
 

@@ -617,11 +617,25 @@ static void TestIterateBatch()
     for (auto& v : b) v = static_cast<int8_t>(u(rng));
     DevBuf<int8_t> dA(a), dB(b);
     DevBuf<int32_t> dC(static_cast<size_t>(BATCH) * M * N);
+    // tiling as in the reference's batch_matmul_bias_reuse example (BatchMatmulTiling + SetBatchInfoForNormal + SetBatchNum)
+    matmul_tiling::BatchMatmulTiling api;
+    api.SetAType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_INT8, false);
+    api.SetBType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_INT8, true);
+    api.SetCType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_INT32);
+    api.SetOrgShape(M, N, K);
+    api.SetShape(M, N, K);
+    api.SetBatchInfoForNormal(BATCH, 1, M, N, K);
+    api.SetBatchNum(BATCH);
     TCubeTiling tiling{};
-    tiling.M = tiling.singleCoreM = M;
-    tiling.N = tiling.singleCoreN = N;
-    tiling.Ka = tiling.Kb = tiling.singleCoreK = K;
-    tiling.BatchNum = BATCH;
+    CHECK(api.GetTiling(tiling) == 0, "BatchMatmulTiling::GetTiling");
+    CHECK(tiling.BatchNum == BATCH && tiling.ALayoutInfoB == BATCH && tiling.ALayoutInfoS == M && tiling.ALayoutInfoD == K &&
+              tiling.BLayoutInfoB == 1 && tiling.BLayoutInfoS == N && tiling.CLayoutInfoB == BATCH && tiling.CLayoutInfoS1 == M &&
+              tiling.CLayoutInfoS2 == N && tiling.ALayoutInfoN == 1 && tiling.CLayoutInfoG == 1,
+          "batch layout fields of the tiling");
+    int32_t dim = 0, mDim = 0, nDim = 0, bM = 0, bN = 0;
+    api.GetCoreNum(dim, mDim, nDim, bM, bN);
+    CHECK(dim == 1 && mDim == 1 && nDim == 1 && bM == 1 && bN == 1, "BatchMatmulTiling::GetCoreNum");
+    CHECK(api.SetBatchNum(0) == -1 && api.SetBatchInfoForNormal(0, 1, M, N, K) == -1, "batch setters refuse non-positive extents");
     {
         TPipe pipe;
         using T8 = MatmulType<TPosition::GM, CubeFormat::ND, int8_t>;
