@@ -45,7 +45,7 @@ struct EpiParams {
     int relu, act;
     int vec_c, vec_c2;       // rows of c / c2 are 16-byte aligned at every 32-column boundary
     int tma_c, tma_c2;       // c / c2 (1- or 2-byte elements) may be written with bulk tensor stores
-    int atomic;              // 1: add into c instead of overwriting it (fp32 / int32 / fp16 / bf16 outputs)
+    int atomic;              // 1 add / 2 max / 3 min into c instead of overwriting it (fp32 / int32 / fp16 / bf16 outputs)
     const void* bias;        // float (fp32 accumulators) or int32 (int32 accumulators)
     const float* tok;
     const float* ch;
@@ -246,19 +246,66 @@ __device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi)
 
 // Stores 32 consecutive outputs of one row; DT is the element type of the destination.
 // f: values for F32/F16/BF16, qi: values for S8/S32.
-// Adds 32 consecutive outputs of one row into the destination (enAtomic = 1 of GetTensorC / IterateAll): one reduction
-// per element, 16-bit types through the half / bfloat16 atomics (the sum is rounded to the destination type).
+// Reduces 32 consecutive outputs of one row into the destination (enAtomic of GetTensorC / IterateAll: 1 add, 2 max,
+// 3 min; impl/adv_api/detail/matmul/utils/matmul_config_utils.h:53-55): one reduction per element.  Sums of 16-bit types go
+// through the half / bfloat16 atomics (rounded to the destination type); max / min of floats through the integer order of
+// their bit patterns (ascending for positive, descending for negative values), of 16-bit types through a
+// compare-and-swap on the element.
+constexpr int kAtomicAdd = 1, kAtomicMax = 2, kAtomicMin = 3;
+
+__device__ __forceinline__ void atomic_maxmin_f32(float* p, float v, bool is_max)
+{
+    // max with v >= 0 or min with v < 0 can only move the stored bits up in signed / unsigned integer order respectively
+    if (is_max == !signbit(v)) {
+        if (is_max) atomicMax(reinterpret_cast<int*>(p), __float_as_int(v));
+        else atomicMax(reinterpret_cast<unsigned*>(p), __float_as_uint(v));
+    } else {
+        if (is_max) atomicMin(reinterpret_cast<unsigned*>(p), __float_as_uint(v));
+        else atomicMin(reinterpret_cast<int*>(p), __float_as_int(v));
+    }
+}
+template <typename H>
+__device__ __forceinline__ void atomic_maxmin_16(H* p, H v, bool is_max)
+{
+    unsigned short* u = reinterpret_cast<unsigned short*>(p);
+    unsigned short old = *u;
+    for (int guard = 0; guard < 4096; ++guard) {  // every failed exchange means another thread made progress
+        const H cur = *reinterpret_cast<const H*>(&old);
+        const float c = static_cast<float>(cur), w = static_cast<float>(v);
+        if (is_max ? !(w > c) : !(w < c)) return;
+        const unsigned short seen = atomicCAS(u, old, *reinterpret_cast<const unsigned short*>(&v));
+        if (seen == old) return;
+        old = seen;
+    }
+}
+
 template <int DT>
-__device__ __forceinline__ void atomic_row32(void* base, long long ld, int row, int col0, int ncols, const float (&f)[32], const int (&qi)[32])
+__device__ __forceinline__ void atomic_row32(void* base, long long ld, int row, int col0, int ncols, const float (&f)[32], const int (&qi)[32],
+                                             int op)
 {
     const size_t off = static_cast<size_t>(row) * static_cast<size_t>(ld) + col0;
+    if (op == kAtomicAdd) {
 #pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (j >= ncols) break;
+            if constexpr (DT == OUT_F32) atomicAdd(static_cast<float*>(base) + off + j, f[j]);
+            else if constexpr (DT == OUT_S32) atomicAdd(static_cast<int*>(base) + off + j, qi[j]);
+            else if constexpr (DT == OUT_F16) atomicAdd(static_cast<__half*>(base) + off + j, __float2half_rn(fminf(fmaxf(f[j], -65504.0f), 65504.0f)));
+            else if constexpr (DT == OUT_BF16) atomicAdd(static_cast<__nv_bfloat16*>(base) + off + j, __float2bfloat16_rn(f[j]));
+        }
+        return;
+    }
+    const bool is_max = op == kAtomicMax;
+#pragma unroll  // full: a partial unroll would index f / qi dynamically and push them into local memory
     for (int j = 0; j < 32; ++j) {
         if (j >= ncols) break;
-        if constexpr (DT == OUT_F32) atomicAdd(static_cast<float*>(base) + off + j, f[j]);
-        else if constexpr (DT == OUT_S32) atomicAdd(static_cast<int*>(base) + off + j, qi[j]);
-        else if constexpr (DT == OUT_F16) atomicAdd(static_cast<__half*>(base) + off + j, __float2half_rn(fminf(fmaxf(f[j], -65504.0f), 65504.0f)));
-        else if constexpr (DT == OUT_BF16) atomicAdd(static_cast<__nv_bfloat16*>(base) + off + j, __float2bfloat16_rn(f[j]));
+        if constexpr (DT == OUT_F32) atomic_maxmin_f32(static_cast<float*>(base) + off + j, f[j], is_max);
+        else if constexpr (DT == OUT_S32) {
+            if (is_max) atomicMax(static_cast<int*>(base) + off + j, qi[j]);
+            else atomicMin(static_cast<int*>(base) + off + j, qi[j]);
+        } else if constexpr (DT == OUT_F16)
+            atomic_maxmin_16(static_cast<__half*>(base) + off + j, __float2half_rn(fminf(fmaxf(f[j], -65504.0f), 65504.0f)), is_max);
+        else if constexpr (DT == OUT_BF16) atomic_maxmin_16(static_cast<__nv_bfloat16*>(base) + off + j, __float2bfloat16_rn(f[j]), is_max);
     }
 }
 
@@ -325,7 +372,7 @@ __device__ __forceinline__ void store_row32(void* base, long long ld, int vec, i
 // other buffers; this buffer's previous group is older than those and has finished.
 template <int DT>
 __device__ __forceinline__ void stage_store32(const CUtensorMap* map, uint32_t smem, bool dual, int lane, int row_base, int col0,
-                                              const float (&f)[32], const int (&qi)[32], bool atomic = false)
+                                              const float (&f)[32], const int (&qi)[32], int atomic = 0)
 {
     static_assert(DT == OUT_F16 || DT == OUT_BF16 || DT == OUT_S8, "staged stores carry 1- and 2-byte outputs");
     if (lane == 0) {
@@ -352,8 +399,10 @@ __device__ __forceinline__ void stage_store32(const CUtensorMap* map, uint32_t s
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-        if (atomic) tma_reduce_add_2d(map, smem, col0, row_base);  // the tensor map then carries the real element type
-        else tma_store_2d(map, smem, col0, row_base);
+        if (atomic == 0) tma_store_2d(map, smem, col0, row_base);
+        else if (atomic == kAtomicAdd) tma_reduce_add_2d(map, smem, col0, row_base);  // the tensor map then carries the real element type
+        else if (atomic == kAtomicMax) tma_reduce_max_2d(map, smem, col0, row_base);
+        else tma_reduce_min_2d(map, smem, col0, row_base);
         bulk_commit_group();
     }
 }
@@ -492,14 +541,14 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
     } else {
         if constexpr (DT == OUT_F16 || DT == OUT_BF16 || DT == OUT_S8) {
             if (st.map_c) {
-                stage_store32<DT>(st.map_c, st.smem_c, st.dual, threadIdx.x & 31, st.row_base, col0, f, qi, e.atomic != 0);
+                stage_store32<DT>(st.map_c, st.smem_c, st.dual, threadIdx.x & 31, st.row_base, col0, f, qi, e.atomic);
                 return;
             }
         }
         if (!row_ok) return;
         if constexpr (DT != OUT_S8) {
             if (e.atomic) {
-                atomic_row32<DT>(e.c, e.ldc, row, col0, ncols, f, qi);
+                atomic_row32<DT>(e.c, e.ldc, row, col0, ncols, f, qi, e.atomic);
                 return;
             }
         }
@@ -1343,7 +1392,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     e.tma_c = !no_tma_store && make_out_map(&outs.c, e.c_dtype, e.c, d->n, d->m, e.ldc);
     e.tma_c2 = !no_tma_store && e.c2 && make_out_map(&outs.c2, e.c2_dtype, e.c2, d->n, d->m, e.ldc2);
     e.atomic = d->atomic;
-    if (d->atomic != 0 && d->atomic != 1) return ASCB200_EUNSUPPORTED;                       // add only (enAtomic = 1)
+    if (d->atomic < 0 || d->atomic > 3) return ASCB200_EUNSUPPORTED;                         // enAtomic: 0 off, 1 add, 2 max, 3 min
     if (d->atomic && out_bytes(e.c_dtype) == 1) return ASCB200_EUNSUPPORTED;                 // no 8-bit atomics
     if (d->atomic && out_bytes(e.c_dtype) == 2 && (reinterpret_cast<uintptr_t>(e.c) & 1)) return ASCB200_EALIGN;
 

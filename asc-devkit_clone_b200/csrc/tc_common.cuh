@@ -66,6 +66,17 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, uint32_t
     asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
                  :: "l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y) : "memory");
 }
+// Element-wise maximum / minimum into global memory (enAtomic = 2 / 3); the element type comes from the tensor map.
+__device__ __forceinline__ void tma_reduce_max_2d(const CUtensorMap* m, uint32_t src, int x, int y)
+{
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.max.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 :: "l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_min_2d(const CUtensorMap* m, uint32_t src, int x, int y)
+{
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.min.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 :: "l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Returns once all but the newest N bulk groups of this thread have finished reading shared memory.
 template <int N>

@@ -170,8 +170,8 @@ public:
     {
         (void)waitIterateAll;
         (void)fakeMsg;
-        if (enAtomic > 1 || enSequentialWrite) {  // 1 = add; max / min (2, 3) and block-sequential output are not implemented
-            AscendC::detail::Latch(ASCB200_EUNSUPPORTED, "Matmul::IterateAll (enAtomic max/min, enSequentialWrite)");
+        if (enAtomic > 3 || enSequentialWrite) {  // enAtomic: 1 add, 2 max, 3 min; block-sequential output is not implemented
+            AscendC::detail::Latch(ASCB200_EUNSUPPORTED, "Matmul::IterateAll (enAtomic > 3, enSequentialWrite)");
             return;
         }
         ascb200_gemm_desc d;

@@ -135,7 +135,7 @@ typedef struct ascb200_gemm_desc {
     const float* ch_scale_dev;  /* DEQUANT_TOKEN_CHANNEL: [n] */
     int32_t relu;            /* enableRelu of the fixpipe stage */
     int32_t act;             /* 0 none, 1 FasterGelu (DEQUANT_TOKEN_CHANNEL only) */
-    int32_t atomic;          /* 0: C is overwritten; 1: C += result (enAtomic = 1 of IterateAll / GetTensorC); F32, S32, F16, BF16 outputs */
+    int32_t atomic;          /* enAtomic of IterateAll / GetTensorC: 0 C is overwritten, 1 C += result, 2 C = max(C, result), 3 C = min(C, result); F32, S32, F16, BF16 outputs */
     int32_t reserved[3];     /* must be zero */
 } ascb200_gemm_desc;
 

@@ -389,11 +389,50 @@ def test_gemm_i8_atomic_add_int32_exact():
     assert (d_c.download().reshape(m, n) == base + 2 * orc.gemm_i8(a, b, trans_b=True)).all()
 
 
+@pytest.mark.parametrize("op", [2, 3])
+@pytest.mark.parametrize("c_dtype", [0, 1, 2])
+def test_gemm_f16_atomic_max_min(c_dtype, op):
+    """enAtomic = 2 / 3: C = max(C, result) / min(C, result); exact, since a maximum involves no rounding beyond the cast of the result."""
+    ab = dev()
+    m, n, k = 200, 328, 128   # ragged: edge chunks take the per-element path
+    rng = np.random.default_rng(31 + c_dtype * 2 + op)
+    a = f16_bits(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+    b = f16_bits(rng.uniform(-1, 1, (n, k)).astype(np.float32))
+    base = rng.integers(-4, 5, (m, n)).astype(np.float32)   # results spread over about +-8: both signs on both sides
+    c0 = base if c_dtype == 0 else (f16_bits(base) if c_dtype == 1 else bf16_bits(base))
+    d_c = ab.to_dev(c0)
+    ab.check(ab.gemm(ab.KIND_F16, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, c_dtype, trans_b=True, atomic=op))
+    ab.sync()
+    d_p = ab.empty((m, n), c0.dtype)
+    ab.check(ab.gemm(ab.KIND_F16, m, n, k, ab.to_dev(a), ab.to_dev(b), d_p, c_dtype, trans_b=True))
+    ab.sync()
+    part = out_to_f32(d_p.download().reshape(m, n), c_dtype)   # the plain result in the output type
+    got = out_to_f32(d_c.download().reshape(m, n), c_dtype)
+    ref = np.maximum(base, part) if op == 2 else np.minimum(base, part)
+    assert (got == ref).all()
+    assert (got != base).any() and (got == base).any()
+
+
+@pytest.mark.parametrize("op", [2, 3])
+def test_gemm_i8_atomic_max_min_int32(op):
+    ab = dev()
+    m, n, k = 256, 320, 256
+    rng, a, b = _i8_inputs(m, n, k, False, True, 18)
+    acc = orc.gemm_i8(a, b, trans_b=True)
+    base = rng.integers(-100000, 100000, (m, n)).astype(np.int32)
+    d_c = ab.to_dev(base)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.S32, trans_b=True, atomic=op))
+    ab.sync()
+    assert (d_c.download().reshape(m, n) == (np.maximum(base, acc) if op == 2 else np.minimum(base, acc))).all()
+
+
 def test_gemm_atomic_rejects_int8_output():
     ab = dev()
     a = ab.to_dev(np.zeros((128, 128), np.int8))
     c = ab.empty((128, 128), np.int8)
     assert ab.gemm(ab.KIND_S8, 128, 128, 128, a, a, c, ab.S8, epilogue=ab.EPI_FIXPIPE_QUANT, trans_b=True, quant_scalar=0x3F800000, atomic=1) == ab.EUNSUPPORTED
+    c32 = ab.empty((128, 128), np.int32)
+    assert ab.gemm(ab.KIND_S8, 128, 128, 128, a, a, c32, ab.S32, trans_b=True, atomic=4) == ab.EUNSUPPORTED   # enAtomic stops at 3
 
 
 @pytest.mark.parametrize("esz,to_nk", [(1, True), (1, False), (2, True), (2, False)])
