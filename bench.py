@@ -683,7 +683,7 @@ class SoftmaxGradStep(RowOp):
     name = "softmaxgrad_131072x2048_fp16"
     metric, dtype = "SoftmaxGrad (fp16 grad and softmax output in, fp16 out) bandwidth", "f16"
     M, K = 131072, 2048
-    traffic_1gpu = None
+    traffic_1gpu = 1.0738e9 + 0.4822e9   # profiles/softmax_grad_rows_kernel_131072x2048_fp16.md
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
