@@ -511,7 +511,8 @@ template <> __device__ __forceinline__ void stat_store<__half>(__half* p, size_t
 template <typename T, typename ST, int TPR, int NCHUNK, bool UPDATE>
 __global__ void __launch_bounds__(TPR > 32 ? TPR : 128, TPR > 32 ? 1 : 5)
 softmax_flash_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, ST* __restrict__ sum_out, ST* __restrict__ max_out, T* __restrict__ expmax_out,
-                          const ST* __restrict__ in_sum, const ST* __restrict__ in_max, int m, int k, int stats_rep, int expmax_rep)
+                          const ST* __restrict__ in_sum, const ST* __restrict__ in_max, int m, int k, int stats_rep, int expmax_rep,
+                          int normalise)
 {
     constexpr int VEC = 16 / sizeof(T);
     __shared__ float red[32];
@@ -583,6 +584,12 @@ softmax_flash_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, ST* __
     }
     s = row_reduce_sum<TPR>(s, red);
     if constexpr (UPDATE) s = __fadd_rn(__fmul_rn(exp_max, old_sum), s);
+    if (normalise) {  // SoftmaxFlash (the first version): y = exp(x - max) / sum, expMax = exp(inMax - max) * inSum / sum
+        const float inv = __frcp_rn(s);
+#pragma unroll
+        for (int i = 0; i < NCHUNK * VEC; ++i) v[i] *= inv;
+        if constexpr (UPDATE) exp_max = __fmul_rn(exp_max, old_sum) * inv;
+    }
 
     T* drow = dst + static_cast<size_t>(row) * k;
 #pragma unroll
@@ -612,12 +619,12 @@ softmax_flash_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, ST* __
 
 template <typename T, typename ST, bool UPDATE>
 int launch_softmax_flash(const T* src, T* dst, ST* sum, ST* mx, T* expmax, const ST* in_sum, const ST* in_max, int m, int k, int stats_rep,
-                         int expmax_rep, cudaStream_t st)
+                         int expmax_rep, int normalise, cudaStream_t st)
 {
     constexpr int VEC = 16 / sizeof(T);
     const int nchunks = k / VEC;
-#define ASCB200_SF_WARP(NC) softmax_flash_rows_kernel<T, ST, 32, NC, UPDATE><<<(m + 3) / 4, 128, 0, st>>>(src, dst, sum, mx, expmax, in_sum, in_max, m, k, stats_rep, expmax_rep)
-#define ASCB200_SF_BLOCK(TPR, NC) softmax_flash_rows_kernel<T, ST, TPR, NC, UPDATE><<<m, TPR, 0, st>>>(src, dst, sum, mx, expmax, in_sum, in_max, m, k, stats_rep, expmax_rep)
+#define ASCB200_SF_WARP(NC) softmax_flash_rows_kernel<T, ST, 32, NC, UPDATE><<<(m + 3) / 4, 128, 0, st>>>(src, dst, sum, mx, expmax, in_sum, in_max, m, k, stats_rep, expmax_rep, normalise)
+#define ASCB200_SF_BLOCK(TPR, NC) softmax_flash_rows_kernel<T, ST, TPR, NC, UPDATE><<<m, TPR, 0, st>>>(src, dst, sum, mx, expmax, in_sum, in_max, m, k, stats_rep, expmax_rep, normalise)
     if (nchunks <= 32) ASCB200_SF_WARP(1);
     else if (nchunks <= 64) ASCB200_SF_WARP(2);
     else if (nchunks <= 128) ASCB200_SF_WARP(4);
@@ -844,8 +851,8 @@ int ascb200_softmax_grad(const void* grad, const void* src, void* dst, int32_t m
                     : launch_softmax_grad<float, false>(g, y, static_cast<float*>(dst), m, k, rep, s);
 }
 
-int ascb200_softmax_flash_v2(const void* src, void* dst, void* exp_sum, void* max, void* exp_max, const void* in_exp_sum, const void* in_max,
-                             int32_t m, int32_t k, int32_t dtype, int32_t stats_dtype, int32_t update, int32_t stats_brc, void* stream)
+static int softmax_flash_entry(const void* src, void* dst, void* exp_sum, void* max, void* exp_max, const void* in_exp_sum, const void* in_max,
+                        int32_t m, int32_t k, int32_t dtype, int32_t stats_dtype, int32_t update, int32_t stats_brc, int normalise, void* stream)
 {
     DeviceState* st = current_state();
     if (!st) return ASCB200_ENODEV;
@@ -863,7 +870,7 @@ int ascb200_softmax_flash_v2(const void* src, void* dst, void* exp_sum, void* ma
 #define ASCB200_SF_CALL(T, ST, UPD)                                                                                                      \
     return launch_softmax_flash<T, ST, UPD>(static_cast<const T*>(src), static_cast<T*>(dst), static_cast<ST*>(exp_sum), static_cast<ST*>(max), \
                                             static_cast<T*>(exp_max), static_cast<const ST*>(in_exp_sum), static_cast<const ST*>(in_max), m, k, \
-                                            stats_rep, expmax_rep, s)
+                                            stats_rep, expmax_rep, normalise, s)
     if (dtype == ASCB200_F32) {
         if (update) ASCB200_SF_CALL(float, float, true);
         ASCB200_SF_CALL(float, float, false);
@@ -875,6 +882,18 @@ int ascb200_softmax_flash_v2(const void* src, void* dst, void* exp_sum, void* ma
     if (update) ASCB200_SF_CALL(__half, __half, true);
     ASCB200_SF_CALL(__half, __half, false);
 #undef ASCB200_SF_CALL
+}
+
+int ascb200_softmax_flash_v2(const void* src, void* dst, void* exp_sum, void* max, void* exp_max, const void* in_exp_sum, const void* in_max,
+                             int32_t m, int32_t k, int32_t dtype, int32_t stats_dtype, int32_t update, int32_t stats_brc, void* stream)
+{
+    return softmax_flash_entry(src, dst, exp_sum, max, exp_max, in_exp_sum, in_max, m, k, dtype, stats_dtype, update, stats_brc, 0, stream);
+}
+
+int ascb200_softmax_flash(const void* src, void* dst, void* sum, void* max, void* exp_max, const void* in_sum, const void* in_max, int32_t m,
+                          int32_t k, int32_t dtype, int32_t stats_dtype, int32_t update, int32_t stats_brc, void* stream)
+{
+    return softmax_flash_entry(src, dst, sum, max, exp_max, in_sum, in_max, m, k, dtype, stats_dtype, update, stats_brc, 1, stream);
 }
 
 int ascb200_softmax_quant(const void* src, void* dst, float* sum, float* mx, int8_t* q, const void* scale, const void* offset_t,

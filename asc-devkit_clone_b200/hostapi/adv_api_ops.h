@@ -146,6 +146,55 @@ inline void SoftmaxGradFront(const LocalTensor<T>& dstTensor, const LocalTensor<
     SoftmaxGrad<T, false, isDataFormatNZ>(dstTensor, gradTensor, srcTensor, tiling, true, softmaxShapeInfo);
 }
 
+// SoftmaxFlash<T>(dst, sum, max, src, expMax, inSum, inMax, [sharedTmpBuffer,] tiling, isUpdate, shapeInfo)
+// (include/adv_api/activation/softmaxflash.h:65-215; deprecated by the reference in favour of SoftmaxFlashV2, kept for existing callers).
+namespace detail {
+template <typename T, typename ST>
+inline void SoftmaxFlashCall(const LocalTensor<T>& dst, const LocalTensor<ST>& sum, const LocalTensor<ST>& max, const LocalTensor<T>& src,
+                             const LocalTensor<T>& expMax, const LocalTensor<ST>& inSum, const LocalTensor<ST>& inMax, const SoftMaxTiling& tiling,
+                             bool isUpdate, const SoftMaxShapeInfo& info)
+{
+    const uint32_t m = info.srcM ? info.srcM : tiling.srcM;
+    const uint32_t k = info.srcK ? info.srcK : tiling.srcK;
+    Latch(ascb200_softmax_flash(src.GetPhyAddr(), dst.GetPhyAddr(), sum.GetPhyAddr(), max.GetPhyAddr(), expMax.GetPhyAddr(), inSum.GetPhyAddr(),
+                                inMax.GetPhyAddr(), static_cast<int32_t>(m), static_cast<int32_t>(k), DTypeOf<T>::value, DTypeOf<ST>::value,
+                                isUpdate ? 1 : 0, 1, CurrentStream()),
+          "SoftmaxFlash");
+}
+}  // namespace detail
+template <typename T, bool isReuseSource = false, bool isBasicBlock = false>
+inline void SoftmaxFlash(const LocalTensor<T>& dstTensor, const LocalTensor<T>& sumTensor, const LocalTensor<T>& maxTensor,
+                         const LocalTensor<T>& srcTensor, const LocalTensor<T>& expMaxTensor, const LocalTensor<T>& inSumTensor,
+                         const LocalTensor<T>& inMaxTensor, const SoftMaxTiling& tiling, bool isUpdate = false,
+                         const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    detail::SoftmaxFlashCall(dstTensor, sumTensor, maxTensor, srcTensor, expMaxTensor, inSumTensor, inMaxTensor, tiling, isUpdate, softmaxShapeInfo);
+}
+template <typename T, bool isReuseSource = false, bool isBasicBlock = false>
+inline void SoftmaxFlash(const LocalTensor<half>& dstTensor, const LocalTensor<float>& sumTensor, const LocalTensor<float>& maxTensor,
+                         const LocalTensor<half>& srcTensor, const LocalTensor<half>& expMaxTensor, const LocalTensor<float>& inSumTensor,
+                         const LocalTensor<float>& inMaxTensor, const SoftMaxTiling& tiling, bool isUpdate = false,
+                         const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    detail::SoftmaxFlashCall(dstTensor, sumTensor, maxTensor, srcTensor, expMaxTensor, inSumTensor, inMaxTensor, tiling, isUpdate, softmaxShapeInfo);
+}
+template <typename T, bool isReuseSource = false, bool isBasicBlock = false>
+inline void SoftmaxFlash(const LocalTensor<T>& dstTensor, const LocalTensor<T>& sumTensor, const LocalTensor<T>& maxTensor,
+                         const LocalTensor<T>& srcTensor, const LocalTensor<T>& expMaxTensor, const LocalTensor<T>& inSumTensor,
+                         const LocalTensor<T>& inMaxTensor, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const SoftMaxTiling& tiling,
+                         bool isUpdate = false, const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    detail::SoftmaxFlashCall(dstTensor, sumTensor, maxTensor, srcTensor, expMaxTensor, inSumTensor, inMaxTensor, tiling, isUpdate, softmaxShapeInfo);
+}
+template <typename T, bool isReuseSource = false, bool isBasicBlock = false>
+inline void SoftmaxFlash(const LocalTensor<half>& dstTensor, const LocalTensor<float>& sumTensor, const LocalTensor<float>& maxTensor,
+                         const LocalTensor<half>& srcTensor, const LocalTensor<half>& expMaxTensor, const LocalTensor<float>& inSumTensor,
+                         const LocalTensor<float>& inMaxTensor, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const SoftMaxTiling& tiling,
+                         bool isUpdate = false, const SoftMaxShapeInfo& softmaxShapeInfo = {})
+{
+    detail::SoftmaxFlashCall(dstTensor, sumTensor, maxTensor, srcTensor, expMaxTensor, inSumTensor, inMaxTensor, tiling, isUpdate, softmaxShapeInfo);
+}
+
 // SoftmaxFlashV2<T, isUpdate>(dst, expSum, max, src, expMax, inExpSum, inMax, tiling, shapeInfo)
 // (include/adv_api/activation/softmaxflashv2.h:93-260): the all-T overloads and the half data / float statistics overloads,
 // each with and without sharedTmpBuffer.

@@ -274,6 +274,17 @@ ASCB200_API int ascb200_softmax_flash_v2(const void* src_dev, void* dst_dev, voi
                                          const void* in_exp_sum_dev, const void* in_max_dev, int32_t m, int32_t k, int32_t dtype,
                                          int32_t stats_dtype, int32_t update, int32_t stats_brc, void* stream);
 
+/* SoftmaxFlash<T>(dst, sum, max, src, expMax, inSum, inMax, tiling, isUpdate, shapeInfo)
+ * (include/adv_api/activation/softmaxflash.h:65-215, the first version, kept by the reference as deprecated; formulas of
+ * SoftmaxFlash.md): the step above followed by the normalisation.
+ *   update == 0: the same result as SoftMax (y = exp(x - max) / sum).
+ *   update == 1: max = max(inMax, rowmax(x)); e = exp(x - max); sum = exp(inMax - max) * inSum + rowsum(e);
+ *                expMax = exp(inMax - max) * inSum / sum; y = e / sum.
+ * Arguments as ascb200_softmax_flash_v2. */
+ASCB200_API int ascb200_softmax_flash(const void* src_dev, void* dst_dev, void* sum_dev, void* max_dev, void* exp_max_dev,
+                                      const void* in_sum_dev, const void* in_max_dev, int32_t m, int32_t k, int32_t dtype,
+                                      int32_t stats_dtype, int32_t update, int32_t stats_brc, void* stream);
+
 /* SoftMax immediately followed by per-channel AscendQuant of its output, one pass over src:
  * writes the fp16 SoftMax result, sum, max and the int8 tensor.  Equivalent to calling
  * ascb200_softmax then ascb200_quant_per_channel (dtype F16). */

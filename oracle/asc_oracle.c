@@ -742,8 +742,8 @@ static void stat_put(void* p, size_t i, float v, int dtype)
     if (dtype == ORC_F16) ((uint16_t*)p)[i] = f32_to_f16(v, 1);
     else ((float*)p)[i] = v;
 }
-ORC_API void orc_softmax_flash_v2(const void* x, void* y, void* sum_out, void* max_out, void* expmax_out, const void* in_sum, const void* in_max,
-                                  int M, int K, int dtype, int stats_dtype, int update, int brc)
+static void softmax_flash_rows(const void* x, void* y, void* sum_out, void* max_out, void* expmax_out, const void* in_sum, const void* in_max,
+                               int M, int K, int dtype, int stats_dtype, int update, int brc, int normalise)
 {
     const int srep = brc ? 32 / (stats_dtype == ORC_F16 ? 2 : 4) : 1, erep = brc ? 32 / (dtype == ORC_F16 ? 2 : 4) : 1;
 #pragma omp parallel
@@ -767,9 +767,10 @@ ORC_API void orc_softmax_flash_v2(const void* x, void* y, void* sum_out, void* m
             for (int k = 0; k < K; ++k) {
                 row[k] = expf(row[k] - mx);
                 s += row[k];
-                stat_put(y, (size_t)m * K + k, row[k], dtype);
             }
             if (update) s = em * old_sum + s;
+            if (normalise && update) em = em * old_sum / s;
+            for (int k = 0; k < K; ++k) stat_put(y, (size_t)m * K + k, normalise ? row[k] / s : row[k], dtype);
             for (int r = 0; r < srep; ++r) {
                 stat_put(sum_out, (size_t)m * srep + r, s, stats_dtype);
                 stat_put(max_out, (size_t)m * srep + r, mx, stats_dtype);
@@ -779,4 +780,19 @@ ORC_API void orc_softmax_flash_v2(const void* x, void* y, void* sum_out, void* m
         }
         free(row);
     }
+}
+
+ORC_API void orc_softmax_flash_v2(const void* x, void* y, void* sum_out, void* max_out, void* expmax_out, const void* in_sum, const void* in_max,
+                                  int M, int K, int dtype, int stats_dtype, int update, int brc)
+{
+    softmax_flash_rows(x, y, sum_out, max_out, expmax_out, in_sum, in_max, M, K, dtype, stats_dtype, update, brc, 0);
+}
+
+/* SoftmaxFlash, the first version (docs/zh/api/SIMD-API/adv_api/activation_functions/SoftMax_interface/SoftmaxFlash.md:43-62):
+ * the V2 step followed by the normalisation: sum as above, expmax = exp(inmax - max) * insum / sum, y = exp(x - max) / sum;
+ * without update it is SoftMax. */
+ORC_API void orc_softmax_flash(const void* x, void* y, void* sum_out, void* max_out, void* expmax_out, const void* in_sum, const void* in_max,
+                               int M, int K, int dtype, int stats_dtype, int update, int brc)
+{
+    softmax_flash_rows(x, y, sum_out, max_out, expmax_out, in_sum, in_max, M, K, dtype, stats_dtype, update, brc, 1);
 }

@@ -268,7 +268,12 @@ def dequant_policy(src, scale, scale_dtype, dst_dtype, policy, k_dim=1, group_si
     return out
 
 
-def softmax_flash_v2(x, dtype, stats_dtype, in_sum=None, in_max=None, brc=True):
+def softmax_flash(x, dtype, stats_dtype, in_sum=None, in_max=None, brc=True):
+    """SoftmaxFlash (first version) step: the V2 step plus the normalisation. Same arguments and returns as softmax_flash_v2."""
+    return softmax_flash_v2(x, dtype, stats_dtype, in_sum, in_max, brc, _fn="orc_softmax_flash")
+
+
+def softmax_flash_v2(x, dtype, stats_dtype, in_sum=None, in_max=None, brc=True, _fn="orc_softmax_flash_v2"):
     """SoftmaxFlashV2 step. x [M, K] as stored. Returns (y, sum, max, expmax or None); stats are [M, rep]."""
     x = np.ascontiguousarray(x)
     M, K = x.shape
@@ -279,6 +284,6 @@ def softmax_flash_v2(x, dtype, stats_dtype, in_sum=None, in_max=None, brc=True):
     s = np.empty((M, srep), _OUT[stats_dtype])
     mx = np.empty((M, srep), _OUT[stats_dtype])
     em = np.empty((M, erep), _OUT[dtype])
-    lib().orc_softmax_flash_v2(_p(x), _p(y), _p(s), _p(mx), _p(em), _p(np.ascontiguousarray(in_sum)) if update else None,
-                               _p(np.ascontiguousarray(in_max)) if update else None, M, K, dtype, stats_dtype, int(update), int(brc))
+    getattr(lib(), _fn)(_p(x), _p(y), _p(s), _p(mx), _p(em), _p(np.ascontiguousarray(in_sum)) if update else None,
+                        _p(np.ascontiguousarray(in_max)) if update else None, M, K, dtype, stats_dtype, int(update), int(brc))
     return y, s, mx, (em if update else None)

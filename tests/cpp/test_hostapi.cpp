@@ -478,6 +478,21 @@ static void TestSoftmaxFlashV2()
     }
     CHECK(bad == 0, "SoftmaxFlashV2: %d rows wrong", bad);
     std::printf("SoftmaxFlashV2 two tiles: ok\n");
+    // the first version (SoftmaxFlash) normalises: without update every row of dst sums to 1
+    DevBuf<half> dY1(M * K);
+    SoftmaxFlash<half>(LocalTensor<half>(dY1.p, dY1.n), LocalTensor<float>(dSum.p, dSum.n), LocalTensor<float>(dMax.p, dMax.n),
+                       LocalTensor<half>(d1.p, d1.n), LocalTensor<half>(dEm.p, dEm.n), LocalTensor<float>(dSum.p, dSum.n),
+                       LocalTensor<float>(dMax.p, dMax.n), tiling, false);
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<half> yn = dY1.Download();
+    bad = 0;
+    for (uint32_t i = 0; i < M; ++i) {
+        double tot = 0;
+        for (uint32_t j = 0; j < K; ++j) tot += static_cast<float>(yn[i * K + j]);
+        if (std::fabs(tot - 1.0) > 2e-3) ++bad;
+    }
+    CHECK(bad == 0, "SoftmaxFlash: %d rows do not sum to 1", bad);
+    std::printf("SoftmaxFlash (first version): ok\n");
 }
 
 // LogSoftMax as in the reference's logsoftmax example: statistics are LocalTensor<T>, one 32-byte block per row.

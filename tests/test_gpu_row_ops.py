@@ -396,6 +396,45 @@ def test_softmax_grad_argument_errors():
     assert ab.softmax_grad(g, y, o, 4, 1 << 20, ab.F32) == ab.ETOOBIG
 
 
+@pytest.mark.parametrize("dtype,stats_dtype", [(1, 0), (1, 1), (0, 0)])
+@pytest.mark.parametrize("m,k,brc", [(64, 128, True), (37, 2048, True), (8, 4096, False), (3, 16, True)])
+def test_softmax_flash_first_version_two_steps(m, k, brc, dtype, stats_dtype):
+    """SoftmaxFlash (the normalising first version): both steps against the oracle, and the identity that tile 1 rescaled by expMax
+    next to tile 2 is the softmax of the whole row."""
+    ab = dev()
+    rng = np.random.default_rng(m + k + dtype * 5 + stats_dtype)
+    x1 = (rng.standard_normal((m, k)) * 2).astype(np.float32)
+    x2 = (rng.standard_normal((m, k)) * 2 + 1).astype(np.float32)
+    s1, s2 = _as_stored(x1, dtype), _as_stored(x2, dtype)
+    srep = (32 // (2 if stats_dtype == 1 else 4)) if brc else 1
+    erep = (32 // (2 if dtype == 1 else 4)) if brc else 1
+    np_d, np_s = (np.float32 if dtype == 0 else np.uint16), (np.float32 if stats_dtype == 0 else np.uint16)
+    d_y1, d_sum, d_max, d_em = ab.empty((m, k), np_d), ab.empty((m, srep), np_s), ab.empty((m, srep), np_s), ab.empty((m, erep), np_d)
+    ab.check(ab.softmax_flash(ab.to_dev(s1), d_y1, d_sum, d_max, None, None, None, m, k, dtype, stats_dtype, False, brc))
+    ab.sync()
+    y_r, sum_r, max_r, _ = orc.softmax_flash(s1, dtype, stats_dtype, brc=brc)
+    sum1, max1 = d_sum.download().reshape(m, srep), d_max.download().reshape(m, srep)
+    y1 = _to_f32(d_y1.download().reshape(m, k), dtype)
+    assert (max1 == max_r).all()
+    assert np.allclose(_to_f32(sum1, stats_dtype), _to_f32(sum_r, stats_dtype), rtol=2e-3)
+    assert (np.abs(y1 - _to_f32(y_r, dtype)) <= 1e-3 * _to_f32(y_r, dtype) + (HALF_STEP if dtype == 1 else 1e-30)).all()
+    d_y2, d_sum2, d_max2 = ab.empty((m, k), np_d), ab.empty((m, srep), np_s), ab.empty((m, srep), np_s)
+    ab.check(ab.softmax_flash(ab.to_dev(s2), d_y2, d_sum2, d_max2, d_em, d_sum, d_max, m, k, dtype, stats_dtype, True, brc))
+    ab.sync()
+    y2_r, sum2_r, max2_r, em_r = orc.softmax_flash(s2, dtype, stats_dtype, in_sum=sum1, in_max=max1, brc=brc)
+    y2, em = _to_f32(d_y2.download().reshape(m, k), dtype), _to_f32(d_em.download().reshape(m, erep), dtype)
+    assert (d_max2.download().reshape(m, srep) == max2_r).all()
+    assert np.allclose(_to_f32(d_sum2.download().reshape(m, srep), stats_dtype), _to_f32(sum2_r, stats_dtype), rtol=2e-3)
+    assert np.allclose(em, _to_f32(em_r, dtype), rtol=3e-3, atol=1e-6)
+    assert (np.abs(y2 - _to_f32(y2_r, dtype)) <= 2e-3 * _to_f32(y2_r, dtype) + (HALF_STEP if dtype == 1 else 1e-30)).all()
+    both = np.concatenate([_to_f32(s1, dtype), _to_f32(s2, dtype)], axis=1).astype(np.float64)
+    e = np.exp(both - both.max(axis=1, keepdims=True))
+    whole = e / e.sum(axis=1, keepdims=True)
+    got = np.concatenate([y1 * em[:, :1], y2], axis=1)
+    rt = 1.2e-2 if stats_dtype == 1 else (6e-3 if dtype == 1 else 1e-4)   # half statistics carry 2^-11 each
+    assert (np.abs(got - whole) <= rt * whole + (2 * HALF_STEP if dtype == 1 else 1e-12)).all()
+
+
 def test_new_entry_points_edge_cases():
     """Zero extents succeed without touching memory; bad extents, types and alignments are refused with the documented codes."""
     ab = dev()

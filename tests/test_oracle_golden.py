@@ -128,6 +128,23 @@ def test_softmaxgrad_recipe(golden_dir):
     assert np.allclose(out16, (gf - (gf * sf).sum(axis=1, keepdims=True)) * sf, rtol=2e-3, atol=1e-3)
 
 
+def test_softmax_flash_first_version_on_the_softmax_recipe(golden_dir):
+    """SoftmaxFlash without update is SoftMax; two steps over two K tiles rebuild the softmax of the whole row
+    (tile 1 rescaled by expMax, tile 2 as returned), checked against the softmax example's golden."""
+    g = load(golden_dir, "softmax.npz")
+    x16 = g["x16"].view(np.uint16)
+    y, mx, sm = orc.softmax(x16, orc.F16)
+    y1, s1, m1, _ = orc.softmax_flash(x16, orc.F16, orc.F32, brc=False)
+    assert (y1 == y).all() and (m1[:, 0] == mx).all() and (s1[:, 0] == sm).all()
+    a, b = np.ascontiguousarray(x16[:, :128]), np.ascontiguousarray(x16[:, 128:])
+    ya, sa, ma, _ = orc.softmax_flash(a, orc.F16, orc.F32)
+    yb, sb, mb, em = orc.softmax_flash(b, orc.F16, orc.F32, in_sum=sa, in_max=ma)
+    f = lambda h: h.view(np.float16).astype(np.float32)
+    whole = np.concatenate([f(ya) * f(em)[:, :1], f(yb)], axis=1)
+    assert np.allclose(whole, g["y16"], rtol=4e-3, atol=1e-6)
+    assert (mb[:, 0] == g["max16"][:, 0]).all() and np.allclose(sb[:, 0], g["sum16"][:, 0], rtol=1e-5)
+
+
 def test_quant_recipe(golden_dir):
     g = load(golden_dir, "quant.npz")
     # dav-2201 variant: half source; round(src*2+0.9) evaluated by numpy in half precision
