@@ -22,7 +22,7 @@ EXPORTS = [
     "ascb200_memset", "ascb200_stream_create", "ascb200_stream_destroy", "ascb200_stream_sync", "ascb200_event_create",
     "ascb200_event_destroy", "ascb200_event_record", "ascb200_stream_wait_event", "ascb200_event_elapsed_ms", "ascb200_gemm", "ascb200_grouped_gemm",
     "ascb200_gemm_mxfp4_noalloc", "ascb200_graph_begin", "ascb200_graph_end", "ascb200_graph_launch", "ascb200_graph_destroy",
-    "ascb200_nz_unpack", "ascb200_quant_policy", "ascb200_dequant_policy", "ascb200_softmax_flash_v2", "ascb200_softmax", "ascb200_log_softmax", "ascb200_softmax_flash", "ascb200_softmax_grad", "ascb200_simple_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
+    "ascb200_nz_unpack", "ascb200_quant_policy", "ascb200_dequant_policy", "ascb200_softmax_flash_v2", "ascb200_softmax", "ascb200_log_softmax", "ascb200_antiquant", "ascb200_softmax_flash", "ascb200_softmax_grad", "ascb200_simple_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
 ]
 
 
@@ -95,6 +95,8 @@ def lib():
         _lib.ascb200_simple_softmax.argtypes = [C.c_void_p] * 4 + [C.c_int32] * 5 + [C.c_void_p]
         _lib.ascb200_softmax_grad.argtypes = [C.c_void_p] * 3 + [C.c_int32] * 4 + [C.c_void_p]
         _lib.ascb200_softmax_flash.argtypes = [C.c_void_p] * 7 + [C.c_int32] * 6 + [C.c_void_p]
+        _lib.ascb200_antiquant.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                           C.c_float, C.c_float, C.c_void_p]
         _lib.ascb200_log_softmax.argtypes = [C.c_void_p] * 4 + [C.c_int32] * 4 + [C.c_void_p]
         _lib.ascb200_softmax.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_void_p]
@@ -223,6 +225,11 @@ def softmax_flash_v2(src, dst, exp_sum, max_, exp_max, in_exp_sum, in_max, m, k,
 def softmax_flash(src, dst, sum_, max_, exp_max, in_sum, in_max, m, k, dtype=F16, stats_dtype=F32, update=False, brc=True, stream=None):
     return lib().ascb200_softmax_flash(_ptr(src), _ptr(dst), _ptr(sum_), _ptr(max_), _ptr(exp_max), _ptr(in_sum), _ptr(in_max), m, k,
                                        dtype, stats_dtype, int(update), int(brc), stream)
+
+
+def antiquant(src, dst, rows, cols, dst_dtype, mode, scale=None, offset=None, scale_scalar=1.0, offset_scalar=0.0, stream=None):
+    return lib().ascb200_antiquant(_ptr(src), _ptr(dst), rows, cols, dst_dtype, mode, _ptr(scale), _ptr(offset), C.c_float(scale_scalar),
+                                   C.c_float(offset_scalar), stream)
 
 
 def softmax_quant(src, dst, sum_, max_, q, scale, offset_t, offset, m, k, brc=False, stream=None):

@@ -419,6 +419,124 @@ int dequant_policy_scale(const DequantPolicyArgs& a, int scale_dtype, int dst_dt
     }
 }
 
+
+// ---- AscendAntiQuant, int8 source (include/adv_api/quantization/ascend_antiquant.h:47-200) ---------------------------------
+// dst = scale * (src + offset) with the arithmetic of the reference's register code
+// (impl/adv_api/detail/quantization/antiquant/ascend_antiquant_3510_impl.h): half outputs add and multiply in half (two
+// roundings, :336-358 per tensor, :461-495 and :615-645 per channel); bfloat16 outputs add and multiply in bfloat16 for
+// per-channel parameters along the row (:461-495) and in fp32 with one rounding for a per-tensor pair (:360-392) or
+// per-row parameters (the transposed form, :647-690).  int8 -> half / bfloat16 is exact.
+// MODE 0: one (scale, offset) pair; 1: one pair per column (no transpose: src [K, N], parameters [N]); 2: one pair per row
+// (isTranspose: src [N, K], parameters [N]).  A thread converts 16 consecutive elements of one row.
+template <typename DT, int MODE, bool F32_MATH>
+__global__ void __launch_bounds__(256)
+antiquant_i8_kernel(const int8_t* __restrict__ src, DT* __restrict__ dst, const DT* __restrict__ scale, const DT* __restrict__ offset, DT scale_s,
+                    DT offset_s, size_t nvec, int vec_per_row)
+{
+    const size_t v = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (v >= nvec) return;
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + v * 16));
+    const size_t row = v / static_cast<size_t>(vec_per_row);
+    const int col0 = static_cast<int>(v - row * vec_per_row) * 16;
+    DT sc[16], of[16];
+    if constexpr (MODE == 1) {
+        *reinterpret_cast<uint4*>(sc) = __ldg(reinterpret_cast<const uint4*>(scale + col0));
+        *reinterpret_cast<uint4*>(sc + 8) = __ldg(reinterpret_cast<const uint4*>(scale + col0 + 8));
+        if (offset) {
+            *reinterpret_cast<uint4*>(of) = __ldg(reinterpret_cast<const uint4*>(offset + col0));
+            *reinterpret_cast<uint4*>(of + 8) = __ldg(reinterpret_cast<const uint4*>(offset + col0 + 8));
+        }
+    }
+    DT s1 = scale_s, o1 = offset_s;
+    if constexpr (MODE == 2) {
+        s1 = scale[row];
+        if (offset) o1 = offset[row];
+    }
+    const int8_t* b = reinterpret_cast<const int8_t*>(&raw);
+    DT out[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const DT s = MODE == 1 ? sc[j] : s1;
+        const DT o = MODE == 1 ? (offset ? of[j] : offset_s) : o1;
+        if constexpr (F32_MATH) {
+            const float r = __fmul_rn(__fadd_rn(static_cast<float>(b[j]), static_cast<float>(o)), static_cast<float>(s));
+            if constexpr (std::is_same<DT, __half>::value) out[j] = __float2half_rn(fminf(fmaxf(r, -65504.0f), 65504.0f));
+            else out[j] = __float2bfloat16_rn(r);
+        } else {
+            DT x;
+            if constexpr (std::is_same<DT, __half>::value) x = __short2half_rn(b[j]);
+            else x = __float2bfloat16_rn(static_cast<float>(b[j]));
+            out[j] = __hmul_rn(__hadd_rn(x, o), s);
+        }
+    }
+    *reinterpret_cast<uint4*>(dst + v * 16) = *reinterpret_cast<const uint4*>(out);
+    *reinterpret_cast<uint4*>(dst + v * 16 + 8) = *reinterpret_cast<const uint4*>(out + 8);
+}
+
+// Per-column parameters: a thread keeps the 16 (scale, offset) pairs of its columns in registers and walks kAntiRows rows,
+// so that the parameters are loaded once per eight vectors instead of once per vector.
+constexpr int kAntiRows = 8;
+template <typename DT>
+__global__ void __launch_bounds__(128)
+antiquant_i8_columns_kernel(const int8_t* __restrict__ src, DT* __restrict__ dst, const DT* __restrict__ scale, const DT* __restrict__ offset,
+                            DT offset_s, int rows, int vec_per_row)
+{
+    const int cv = blockIdx.x * 128 + threadIdx.x;
+    if (cv >= vec_per_row) return;
+    const int r0 = blockIdx.y * kAntiRows;
+    const size_t cols = static_cast<size_t>(vec_per_row) * 16;
+    uint4 raw[kAntiRows];
+#pragma unroll
+    for (int r = 0; r < kAntiRows; ++r)
+        if (r0 + r < rows) raw[r] = __ldg(reinterpret_cast<const uint4*>(src + (r0 + r) * cols + cv * 16));
+    DT sc[16], of[16];
+    *reinterpret_cast<uint4*>(sc) = __ldg(reinterpret_cast<const uint4*>(scale + cv * 16));
+    *reinterpret_cast<uint4*>(sc + 8) = __ldg(reinterpret_cast<const uint4*>(scale + cv * 16 + 8));
+    if (offset) {
+        *reinterpret_cast<uint4*>(of) = __ldg(reinterpret_cast<const uint4*>(offset + cv * 16));
+        *reinterpret_cast<uint4*>(of + 8) = __ldg(reinterpret_cast<const uint4*>(offset + cv * 16 + 8));
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) of[j] = offset_s;
+    }
+#pragma unroll
+    for (int r = 0; r < kAntiRows; ++r) {
+        if (r0 + r >= rows) break;
+        const int8_t* b = reinterpret_cast<const int8_t*>(&raw[r]);
+        DT out[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            DT x;
+            if constexpr (std::is_same<DT, __half>::value) x = __short2half_rn(b[j]);
+            else x = __float2bfloat16_rn(static_cast<float>(b[j]));
+            out[j] = __hmul_rn(__hadd_rn(x, of[j]), sc[j]);
+        }
+        DT* d = dst + (r0 + r) * cols + cv * 16;
+        *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(out);
+        *reinterpret_cast<uint4*>(d + 8) = *reinterpret_cast<const uint4*>(out + 8);
+    }
+}
+
+template <typename DT>
+int launch_antiquant(const int8_t* src, DT* dst, int rows, int cols, int mode, const DT* scale, const DT* offset, float scale_f, float offset_f,
+                     cudaStream_t st)
+{
+    const size_t nvec = static_cast<size_t>(rows) * (cols / 16);
+    const size_t blocks = (nvec + 255) / 256;
+    if (blocks > 0x7FFFFFFFull) return ASCB200_ETOOBIG;
+    const DT ss = static_cast<DT>(scale_f), os = static_cast<DT>(offset_f);  // the scalars arrive in the output type
+    constexpr bool BF = std::is_same<DT, __nv_bfloat16>::value;
+    const unsigned g = static_cast<unsigned>(blocks);
+    if (mode == 0) antiquant_i8_kernel<DT, 0, BF><<<g, 256, 0, st>>>(src, dst, scale, offset, ss, os, nvec, cols / 16);
+    else if (mode == 1) {
+        const int row_blocks = (rows + kAntiRows - 1) / kAntiRows;
+        if (row_blocks > 65535) antiquant_i8_kernel<DT, 1, false><<<g, 256, 0, st>>>(src, dst, scale, offset, ss, os, nvec, cols / 16);
+        else antiquant_i8_columns_kernel<DT><<<dim3((cols / 16 + 127) / 128, row_blocks), 128, 0, st>>>(src, dst, scale, offset, os, rows, cols / 16);
+    }
+    else antiquant_i8_kernel<DT, 2, BF><<<g, 256, 0, st>>>(src, dst, scale, offset, ss, os, nvec, cols / 16);
+    ASCB200_CUDA(cudaGetLastError());
+    return ASCB200_OK;
+}
 }  // namespace
 }  // namespace ascb200
 
@@ -493,4 +611,25 @@ extern "C" int ascb200_quant_policy(const void* src, void* dst, int32_t m, int32
     }
     if (src_dtype == ASCB200_F32) return dispatch_dst<float, float>(a, dst_dtype, vec8, sms, s);
     return ASCB200_EUNSUPPORTED;
+}
+
+extern "C" int ascb200_antiquant(const int8_t* src, void* dst, int32_t rows, int32_t cols, int32_t dst_dtype, int32_t mode, const void* scale,
+                                 const void* offset, float scale_scalar, float offset_scalar, void* stream)
+{
+    using namespace ascb200;
+    DeviceState* st = current_state();
+    if (!st) return ASCB200_ENODEV;
+    if (!src || !dst || rows < 0 || cols < 0 || mode < 0 || mode > 2) return ASCB200_EINVAL;
+    if (mode != 0 && !scale) return ASCB200_EINVAL;
+    if (dst_dtype != ASCB200_F16 && dst_dtype != ASCB200_BF16) return ASCB200_EUNSUPPORTED;
+    if (cols % 32 != 0) return ASCB200_EALIGN;  // rows of whole 32-byte blocks, like the reference's tensors
+    if (!aligned_to(src, 16) || !aligned_to(dst, 16)) return ASCB200_EALIGN;
+    if (mode == 1 && (!aligned_to(scale, 16) || (offset && !aligned_to(offset, 16)))) return ASCB200_EALIGN;
+    if (rows == 0 || cols == 0) return ASCB200_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dst_dtype == ASCB200_F16)
+        return launch_antiquant<__half>(src, static_cast<__half*>(dst), rows, cols, mode, static_cast<const __half*>(scale),
+                                        static_cast<const __half*>(offset), scale_scalar, offset_scalar, s);
+    return launch_antiquant<__nv_bfloat16>(src, static_cast<__nv_bfloat16*>(dst), rows, cols, mode, static_cast<const __nv_bfloat16*>(scale),
+                                           static_cast<const __nv_bfloat16*>(offset), scale_scalar, offset_scalar, s);
 }

@@ -146,6 +146,81 @@ inline void SoftmaxGradFront(const LocalTensor<T>& dstTensor, const LocalTensor<
     SoftmaxGrad<T, false, isDataFormatNZ>(dstTensor, gradTensor, srcTensor, tiling, true, softmaxShapeInfo);
 }
 
+// AscendAntiQuant<InputDataType, OutputDataType, isTranspose>(dst, src, [offset,] scale, [sharedTmpBuffer,] k, shapeInfo)
+// (include/adv_api/quantization/ascend_antiquant.h:47-200), int8 source, half / bfloat16 output: dst = scale * (src + offset).
+// Per channel: src is [k, n] with one (scale, offset) pair per column (isTranspose = false) or [n, k] with one pair per row
+// (isTranspose = true); n = src.GetSize() / k.  Per tensor: scalar scale / offset in the output type.
+struct AntiQuantShapeInfo {  // include/adv_api/quantization/ascend_antiquant_utils.h:27-32
+    uint32_t offsetHeight{0};
+    uint32_t offsetWidth{0};
+    uint32_t scaleHeight{0};
+    uint32_t scaleWidth{0};
+};
+namespace detail {
+template <typename OutputDataType, bool isTranspose>
+inline void AntiQuantChannel(const LocalTensor<OutputDataType>& dst, const LocalTensor<int8_t>& src, const void* offset,
+                             const LocalTensor<OutputDataType>& scale, uint32_t k)
+{
+    const uint32_t n = k ? static_cast<uint32_t>(src.GetSize() / k) : 0;
+    Latch(ascb200_antiquant(src.GetPhyAddr(), dst.GetPhyAddr(), static_cast<int32_t>(isTranspose ? n : k), static_cast<int32_t>(isTranspose ? k : n),
+                            DTypeOf<OutputDataType>::value, isTranspose ? 2 : 1, scale.GetPhyAddr(), offset, 1.0f, 0.0f, CurrentStream()),
+          "AscendAntiQuant");
+}
+template <typename OutputDataType>
+inline void AntiQuantTensor(const LocalTensor<OutputDataType>& dst, const LocalTensor<int8_t>& src, OutputDataType offset, OutputDataType scale,
+                            uint32_t k)
+{
+    const uint32_t n = k ? static_cast<uint32_t>(src.GetSize() / k) : 0;
+    Latch(ascb200_antiquant(src.GetPhyAddr(), dst.GetPhyAddr(), static_cast<int32_t>(k), static_cast<int32_t>(n), DTypeOf<OutputDataType>::value, 0,
+                            nullptr, nullptr, static_cast<float>(scale), static_cast<float>(offset), CurrentStream()),
+          "AscendAntiQuant");
+}
+}  // namespace detail
+template <typename InputDataType, typename OutputDataType, bool isTranspose>
+inline void AscendAntiQuant(const LocalTensor<OutputDataType>& dst, const LocalTensor<InputDataType>& src, const LocalTensor<OutputDataType>& offset,
+                            const LocalTensor<OutputDataType>& scale, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const uint32_t k,
+                            const AntiQuantShapeInfo& = {})
+{
+    static_assert(std::is_same<InputDataType, int8_t>::value, "the B200 path anti-quantises int8 sources");
+    detail::AntiQuantChannel<OutputDataType, isTranspose>(dst, src, offset.GetPhyAddr(), scale, k);
+}
+template <typename InputDataType, typename OutputDataType, bool isTranspose>
+inline void AscendAntiQuant(const LocalTensor<OutputDataType>& dst, const LocalTensor<InputDataType>& src, const LocalTensor<OutputDataType>& scale,
+                            const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const uint32_t k, const AntiQuantShapeInfo& = {})
+{
+    static_assert(std::is_same<InputDataType, int8_t>::value, "the B200 path anti-quantises int8 sources");
+    detail::AntiQuantChannel<OutputDataType, isTranspose>(dst, src, nullptr, scale, k);
+}
+template <typename InputDataType, typename OutputDataType, bool isTranspose>
+inline void AscendAntiQuant(const LocalTensor<OutputDataType>& dst, const LocalTensor<InputDataType>& src, const LocalTensor<OutputDataType>& offset,
+                            const LocalTensor<OutputDataType>& scale, const uint32_t k, const AntiQuantShapeInfo& = {})
+{
+    static_assert(std::is_same<InputDataType, int8_t>::value, "the B200 path anti-quantises int8 sources");
+    detail::AntiQuantChannel<OutputDataType, isTranspose>(dst, src, offset.GetPhyAddr(), scale, k);
+}
+template <typename InputDataType, typename OutputDataType, bool isTranspose>
+inline void AscendAntiQuant(const LocalTensor<OutputDataType>& dst, const LocalTensor<InputDataType>& src, const OutputDataType offset,
+                            const OutputDataType scale, const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const uint32_t k,
+                            const AntiQuantShapeInfo& = {})
+{
+    static_assert(std::is_same<InputDataType, int8_t>::value, "the B200 path anti-quantises int8 sources");
+    detail::AntiQuantTensor<OutputDataType>(dst, src, offset, scale, k);
+}
+template <typename InputDataType, typename OutputDataType, bool isTranspose>
+inline void AscendAntiQuant(const LocalTensor<OutputDataType>& dst, const LocalTensor<InputDataType>& src, const OutputDataType scale,
+                            const LocalTensor<uint8_t>& /*sharedTmpBuffer*/, const uint32_t k, const AntiQuantShapeInfo& = {})
+{
+    static_assert(std::is_same<InputDataType, int8_t>::value, "the B200 path anti-quantises int8 sources");
+    detail::AntiQuantTensor<OutputDataType>(dst, src, OutputDataType(0.0f), scale, k);
+}
+template <typename InputDataType, typename OutputDataType, bool isTranspose>
+inline void AscendAntiQuant(const LocalTensor<OutputDataType>& dst, const LocalTensor<InputDataType>& src, const OutputDataType offset,
+                            const OutputDataType scale, const uint32_t k, const AntiQuantShapeInfo& = {})
+{
+    static_assert(std::is_same<InputDataType, int8_t>::value, "the B200 path anti-quantises int8 sources");
+    detail::AntiQuantTensor<OutputDataType>(dst, src, offset, scale, k);
+}
+
 // SoftmaxFlash<T>(dst, sum, max, src, expMax, inSum, inMax, [sharedTmpBuffer,] tiling, isUpdate, shapeInfo)
 // (include/adv_api/activation/softmaxflash.h:65-215; deprecated by the reference in favour of SoftmaxFlashV2, kept for existing callers).
 namespace detail {

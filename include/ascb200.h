@@ -263,6 +263,18 @@ ASCB200_API int ascb200_dequant_policy(const void* src_dev, void* dst_dev, int32
                                        int32_t dst_dtype, int32_t policy, int32_t k_dim, int32_t group_size, const void* scale_dev,
                                        void* stream);
 
+/* AscendAntiQuant<int8_t, OutputDataType, isTranspose>(dst, src, [offset,] scale, [sharedTmpBuffer,] k, shapeInfo)
+ * (include/adv_api/quantization/ascend_antiquant.h:47-200): dst = scale * (src + offset), src int8 [rows, cols], dst F16 or BF16.
+ *   mode 0  per tensor: scale_scalar / offset_scalar (rounded to the output type first, as the interface takes them in it);
+ *   mode 1  per channel, isTranspose = false: src [K, N], scale_dev / offset_dev [N] of the output type, one pair per column;
+ *   mode 2  per channel, isTranspose = true:  src [N, K], scale_dev / offset_dev [N], one pair per row.
+ * offset_dev == NULL in modes 1 / 2 uses offset_scalar (0 for the overloads without offset).  Arithmetic follows the
+ * reference's register code (impl/adv_api/detail/quantization/antiquant/ascend_antiquant_3510_impl.h): half outputs add and
+ * multiply in half; bfloat16 outputs in bfloat16 for mode 1 and in fp32 with one rounding for modes 0 and 2.
+ * cols must be a multiple of 32. */
+ASCB200_API int ascb200_antiquant(const int8_t* src_dev, void* dst_dev, int32_t rows, int32_t cols, int32_t dst_dtype, int32_t mode,
+                                  const void* scale_dev, const void* offset_dev, float scale_scalar, float offset_scalar, void* stream);
+
 /* SoftmaxFlashV2<T, isUpdate>(dst, expSum, max, src, expMax, inExpSum, inMax, tiling, shapeInfo)
  * (include/adv_api/activation/softmaxflashv2.h:93-300): one step of the online softmax over rows [m, k].
  *   update == 0: max = rowmax(x); y = exp(x - max); expSum = rowsum(y).

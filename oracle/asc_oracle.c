@@ -796,3 +796,32 @@ ORC_API void orc_softmax_flash(const void* x, void* y, void* sum_out, void* max_
 {
     softmax_flash_rows(x, y, sum_out, max_out, expmax_out, in_sum, in_max, M, K, dtype, stats_dtype, update, brc, 1);
 }
+
+/* ---------------------------------------------------------------------------------------------
+ * AscendAntiQuant, int8 source: dst = scale * (src + offset)
+ * (impl/adv_api/detail/quantization/antiquant/ascend_antiquant_3510_impl.h: per tensor half :336-358 (half add, half mul),
+ *  per tensor bfloat16 :360-392 (fp32 add, fp32 mul, one cast), per channel along the row :461-495 (add and mul in the output
+ *  type), per channel transposed :615-645 half / :647-690 bfloat16 in fp32; golden
+ *  examples/01_simd_cpp_api/04_advanced_api/03_quantization/antiquant/scripts/gen_data.py:21-44).
+ * mode 0 scalar pair, 1 one pair per column, 2 one pair per row; scale / offset in the output type (offset may be NULL).
+ * ------------------------------------------------------------------------------------------- */
+static inline uint16_t round16(float v, int dtype, int sat) { return dtype == ORC_F16 ? f32_to_f16(v, sat) : orc_f32_to_bf16(v); }
+static inline float widen16(uint16_t v, int dtype) { return dtype == ORC_F16 ? orc_f16_to_f32(v) : orc_bf16_to_f32(v); }
+ORC_API void orc_antiquant(const int8_t* src, uint16_t* dst, int rows, int cols, int dtype, int mode, const uint16_t* scale, const uint16_t* offset,
+                           float scale_scalar, float offset_scalar)
+{
+    const uint16_t ss = round16(scale_scalar, dtype, 0), os = round16(offset_scalar, dtype, 0);
+    const int f32_math = dtype == ORC_BF16 && mode != 1;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c) {
+            const int p = mode == 1 ? c : r;
+            const float s = widen16(mode == 0 ? ss : scale[p], dtype);
+            const float o = widen16((mode == 0 || !offset) ? os : offset[p], dtype);
+            const float x = (float)src[(size_t)r * cols + c];
+            uint16_t out;
+            if (f32_math) out = round16((x + o) * s, dtype, 1);
+            else out = round16(widen16(round16(x + o, dtype, 0), dtype) * s, dtype, 0);
+            dst[(size_t)r * cols + c] = out;
+        }
+}

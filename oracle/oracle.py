@@ -197,6 +197,17 @@ def softmax_grad(grad, src, dtype=F16, front=False):
     return out
 
 
+def antiquant(src, dtype, mode, scale=None, offset=None, scale_scalar=1.0, offset_scalar=0.0):
+    """AscendAntiQuant of int8 src [rows, cols]; scale / offset are uint16 bit patterns of `dtype` (F16 / BF16). Returns uint16 bits."""
+    src = _c(src, np.int8)
+    out = np.empty(src.shape, np.uint16)
+    sc = None if scale is None else _c(scale, np.uint16)
+    of = None if offset is None else _c(offset, np.uint16)
+    lib().orc_antiquant(_p(src), _p(out), src.shape[0], src.shape[1], dtype, mode, _p(sc) if sc is not None else None,
+                        _p(of) if of is not None else None, C.c_float(scale_scalar), C.c_float(offset_scalar))
+    return out
+
+
 def _src(x, dtype):
     return _c(x, np.float32 if dtype == F32 else np.uint16)
 

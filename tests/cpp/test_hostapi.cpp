@@ -557,6 +557,40 @@ static void TestLogSoftMax()
     std::printf("SoftmaxGrad: ok\n");
 }
 
+// AscendAntiQuant as in the reference's antiquant example: int8 [8, 128] -> half with one (scale, offset) pair per column.
+static void TestAntiQuant()
+{
+    using namespace AscendC;
+    const uint32_t K = 8, N = 128;
+    std::mt19937 rng(33);
+    std::uniform_int_distribution<int> ui(-10, 10);
+    std::uniform_real_distribution<float> uf(-10.f, 10.f);
+    std::vector<int8_t> src(K * N);
+    std::vector<half> off(N), sc(N);
+    for (auto& v : src) v = static_cast<int8_t>(ui(rng));
+    for (auto& v : off) v = half(uf(rng));
+    for (auto& v : sc) v = half(uf(rng));
+    DevBuf<int8_t> dS(src);
+    DevBuf<half> dO(off), dC(sc), dD(K * N), dT(K * N);
+    DevBuf<uint8_t> tmp(32);
+    AscendAntiQuant<int8_t, half, false>(LocalTensor<half>(dD.p, dD.n), LocalTensor<int8_t>(dS.p, dS.n), LocalTensor<half>(dO.p, dO.n),
+                                         LocalTensor<half>(dC.p, dC.n), LocalTensor<uint8_t>(tmp.p, tmp.n), K);
+    AscendAntiQuant<int8_t, half, false>(LocalTensor<half>(dT.p, dT.n), LocalTensor<int8_t>(dS.p, dS.n), half(1.5f), half(0.5f),
+                                         LocalTensor<uint8_t>(tmp.p, tmp.n), K);
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<half> d = dD.Download(), t = dT.Download();
+    int bad = 0;
+    for (uint32_t i = 0; i < K; ++i)
+        for (uint32_t j = 0; j < N; ++j) {
+            const half sum = half(static_cast<float>(src[i * N + j]) + static_cast<float>(off[j]));  // half add
+            const half want = half(static_cast<float>(sum) * static_cast<float>(sc[j]));            // half multiply
+            if (static_cast<float>(d[i * N + j]) != static_cast<float>(want)) ++bad;
+            if (static_cast<float>(t[i * N + j]) != (src[i * N + j] + 1.5f) * 0.5f) ++bad;
+        }
+    CHECK(bad == 0, "AscendAntiQuant: %d values wrong", bad);
+    std::printf("AscendAntiQuant: ok\n");
+}
+
 // Constant tiling as in the reference's matmul_constant_tiling example: the shapes are template constants
 // (GetMMConfig + GetMatmulApiTiling), the object is initialised without a TCubeTiling.
 static constexpr MatmulShapeParams kConstShape = {256, 384, 128, 128, 256, 64};
@@ -708,6 +742,7 @@ int main()
     TestQuantPolicies();
     TestSoftmaxFlashV2();
     TestLogSoftMax();
+    TestAntiQuant();
     TestConstantTiling();
     TestIterateBatch();
     TestErrorLatch();

@@ -18,6 +18,7 @@ input+output samples as .npz, so the tests can pin the CPU oracle without the re
                      example's 128x128 uniform(-10, 10) input, plus a half input widened to fp32
   softmaxgrad.npz    04_advanced_api/01_activation/softmaxgrad/scripts/gen_data.py: softmax_grad_float, both modes, on the
                      example's uniform(-1, 1) inputs (rows sampled from its 960x960 shape)
+  antiquant.npz      04_advanced_api/03_quantization/antiquant/scripts/gen_data.py, both arch variants (half arithmetic / fp32 arithmetic)
   quant.npz          04_advanced_api/03_quantization/quant/scripts/gen_data.py (both arch variants)
   dequant.npz        04_advanced_api/03_quantization/dequant/scripts/gen_data.py
   grouped.npz        05_best_practices/03_fusion_compute/quant_group_matmul_high_performance/scripts/gen_data.py
@@ -200,6 +201,25 @@ def quant(ref):
     np.savez_compressed(os.path.join(HERE, "quant.npz"), **out)
 
 
+def antiquant(ref):
+    p = os.path.join(ref, EX, "04_advanced_api/03_quantization/antiquant/scripts/gen_data.py")
+    out = {}
+    for arch, tag in (("dav-2201", "f16math"), ("dav-3510", "f32math")):
+        mod = load_module(p, "ref_antiquant_" + tag)
+        with tempfile.TemporaryDirectory() as tmp:
+            cwd = os.getcwd()
+            os.chdir(tmp)
+            try:
+                mod.gen_golden_data_simple(arch)   # seeds numpy itself
+                out["src"] = np.fromfile("input/input_src.bin", np.int8).reshape(8, 128)
+                out["offset"] = np.fromfile("input/input_offset.bin", np.float16)
+                out["scale"] = np.fromfile("input/input_scale.bin", np.float16)
+                out["golden_" + tag] = np.fromfile("output/golden.bin", np.float16).reshape(8, 128)
+            finally:
+                os.chdir(cwd)
+    np.savez_compressed(os.path.join(HERE, "antiquant.npz"), **out)
+
+
 def dequant(ref):
     files = run_script_in_tmp(os.path.join(ref, EX, "04_advanced_api/03_quantization/dequant/scripts/gen_data.py"), 15)
     np.savez_compressed(os.path.join(HERE, "dequant.npz"),
@@ -271,6 +291,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("ASC_REFERENCE_ROOT", "reference"))
     args = ap.parse_args()
-    for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, logsoftmax, softmaxgrad, quant, dequant, grouped, mxfp4, casts):
+    for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, logsoftmax, softmaxgrad, quant, antiquant, dequant, grouped, mxfp4, casts):
         fn(args.ref)
         print("wrote", fn.__name__)

@@ -435,6 +435,40 @@ def test_softmax_flash_first_version_two_steps(m, k, brc, dtype, stats_dtype):
     assert (np.abs(got - whole) <= rt * whole + (2 * HALF_STEP if dtype == 1 else 1e-12)).all()
 
 
+@pytest.mark.parametrize("dst_dtype", [1, 2])
+@pytest.mark.parametrize("mode,with_offset", [(0, True), (1, True), (1, False), (2, True), (2, False)])
+@pytest.mark.parametrize("rows,cols", [(8, 128), (37, 2048), (300, 96), (1, 32)])
+def test_antiquant(rows, cols, mode, with_offset, dst_dtype):
+    """AscendAntiQuant int8 -> half / bfloat16: bit exact against the oracle in every mode (the arithmetic type is part of the contract)."""
+    ab = dev()
+    rng = np.random.default_rng(rows + cols * 3 + mode * 7 + dst_dtype)
+    src = rng.integers(-128, 128, (rows, cols), dtype=np.int8)
+    npar = cols if mode == 1 else rows
+    sc = _as_stored(rng.uniform(-4, 4, npar).astype(np.float32), dst_dtype)
+    of = _as_stored(rng.uniform(-10, 10, npar).astype(np.float32), dst_dtype)
+    d_out = ab.empty((rows, cols), np.uint16)
+    kw = dict(scale_scalar=0.37, offset_scalar=-2.25 if with_offset else 0.0)
+    if mode == 0:
+        ab.check(ab.antiquant(ab.to_dev(src), d_out, rows, cols, dst_dtype, 0, **kw))
+        ref = orc.antiquant(src, dst_dtype, 0, **kw)
+    else:
+        ab.check(ab.antiquant(ab.to_dev(src), d_out, rows, cols, dst_dtype, mode, ab.to_dev(sc), ab.to_dev(of) if with_offset else None))
+        ref = orc.antiquant(src, dst_dtype, mode, scale=sc, offset=of if with_offset else None)
+    ab.sync()
+    got = d_out.download().reshape(rows, cols)
+    assert (got == ref).all(), f"{(got != ref).sum()} of {got.size} differ"
+
+
+def test_antiquant_argument_errors():
+    ab = dev()
+    s, d, p = ab.empty((4, 64), np.int8), ab.empty((4, 64), np.uint16), ab.empty((64,), np.uint16)
+    assert ab.antiquant(s, d, 0, 64, ab.F16, 0) == 0
+    assert ab.antiquant(s, d, 4, 48, ab.F16, 0) == ab.EALIGN          # rows are whole 32-byte blocks
+    assert ab.antiquant(s, d, 4, 64, ab.F32, 0) == ab.EUNSUPPORTED    # half / bfloat16 outputs only
+    assert ab.antiquant(s, d, 4, 64, ab.F16, 1) == ab.EINVAL          # per channel needs the scale tensor
+    assert ab.antiquant(s, d, 4, 64, ab.F16, 3, p) == ab.EINVAL
+
+
 def test_new_entry_points_edge_cases():
     """Zero extents succeed without touching memory; bad extents, types and alignments are refused with the documented codes."""
     ab = dev()

@@ -145,6 +145,23 @@ def test_softmax_flash_first_version_on_the_softmax_recipe(golden_dir):
     assert (mb[:, 0] == g["max16"][:, 0]).all() and np.allclose(sb[:, 0], g["sum16"][:, 0], rtol=1e-5)
 
 
+def test_antiquant_recipe(golden_dir):
+    """AscendAntiQuant per channel (int8 -> half) against the reference example's generator: bit exact with its half-arithmetic
+    variant (the register code adds and multiplies in half), within one half step of its fp32-arithmetic variant."""
+    g = load(golden_dir, "antiquant.npz")
+    out = orc.antiquant(g["src"], orc.F16, 1, scale=g["scale"].view(np.uint16), offset=g["offset"].view(np.uint16))
+    assert (out == g["golden_f16math"].view(np.uint16)).all()
+    a, b = out.view(np.float16).astype(np.float32), g["golden_f32math"].astype(np.float32)
+    assert (np.abs(a - b) <= np.abs(b) * 2.0 ** -10).all()
+    # transposed form: the same numbers with one pair per row
+    out_t = orc.antiquant(np.ascontiguousarray(g["src"].T), orc.F16, 2, scale=g["scale"].view(np.uint16), offset=g["offset"].view(np.uint16))
+    assert (out_t == out.T).all()
+    # per tensor, bfloat16: fp32 arithmetic and a single rounding
+    bf = orc.antiquant(g["src"], orc.BF16, 0, scale_scalar=0.75, offset_scalar=-1.5)
+    want = ((g["src"].astype(np.float32) - 1.5) * 0.75)
+    assert (orc.bf16_bits_to_f32(bf) == orc.bf16_bits_to_f32(orc.cast_f32(want, orc.BF16))).all()
+
+
 def test_quant_recipe(golden_dir):
     g = load(golden_dir, "quant.npz")
     # dav-2201 variant: half source; round(src*2+0.9) evaluated by numpy in half precision
