@@ -729,6 +729,53 @@ class SoftmaxGradStep(RowOp):
         return bool((np.abs(got - ref) <= 1e-3 * np.abs(ref) + 1e-5).all())
 
 
+class AntiQuantPerChannel(RowOp):
+    name = "ascendantiquant_per_channel_int8_to_fp16_131072x2048"
+    metric, dtype = "AscendAntiQuant per channel (int8 -> fp16, fp16 scale and offset per column) bandwidth", "f16"
+    M, N = 131072, 2048
+    traffic_1gpu = 268.9e6 + 477.8e6   # profiles/antiquant_i8_columns_kernel_int8_fp16_131072x2048.md
+
+    def __init__(self, ab, rank, world, sets):
+        from gpu_util import f16_bits
+        self.ab, self.rank, self.world = ab, rank, world
+        rng = np.random.default_rng(0xA5C00014 + rank)
+        self.x_h = np.tile(rng.integers(-128, 128, (4096, self.N), dtype=np.int8), (self.M // 4096, 1))
+        self.sc_h = f16_bits(rng.uniform(-2, 2, self.N).astype(np.float32))
+        self.of_h = f16_bits(rng.uniform(-8, 8, self.N).astype(np.float32))
+        self.sets = sets = 2   # 805 MB per set
+        self.x = [ab.to_dev(self.x_h) for _ in range(sets)]
+        self.o = [ab.empty((self.M, self.N), np.uint16) for _ in range(sets)]
+        self.sc, self.of = ab.to_dev(self.sc_h), ab.to_dev(self.of_h)
+        self.config = {"workload": self.name, "M": self.M, "N": self.N, "shard": f"replica per rank x{world}",
+                       "cache": f"{sets} rotating buffer sets ({sets * self.per_step_bytes() // 2**20} MiB > L2)"}
+
+    def per_step_bytes(self):
+        return self.M * self.N * 3 + self.N * 4
+
+    def step(self, i, stream=None):
+        ab, s = self.ab, i % self.sets
+        ab.check(ab.antiquant(self.x[s], self.o[s], self.M, self.N, ab.F16, 1, self.sc, self.of, stream=stream))
+
+    def h2d_arrays(self):
+        return [self.x_h, self.sc_h, self.of_h]
+
+    def h2d_targets(self, s):
+        return [self.x[s], self.sc, self.of]
+
+    def d2h_buffers(self, s):
+        return [(self.o[s], self.M * self.N * 2)]
+
+    def cpu_sample(self, orc, rows):
+        rows = min(rows * 16, self.M)
+        t0 = time.perf_counter()
+        orc.antiquant(self.x_h[:rows], orc.F16, 1, scale=self.sc_h, offset=self.of_h)
+        return time.perf_counter() - t0, rows * (self.per_step_bytes() / self.M), f"{rows} of {self.M} rows"
+
+    def verify(self, orc):
+        ref = orc.antiquant(self.x_h[:64], orc.F16, 1, scale=self.sc_h, offset=self.of_h)
+        return bool((self.o[0].download().reshape(self.M, self.N)[:64] == ref).all())
+
+
 class NzUnpack(RowOp):
     name = "nz_weight_unpack_int8_16x7168x2048"
     metric, dtype = "fractal NZ -> K-major weight unpack bandwidth", "u8"
@@ -773,7 +820,7 @@ class NzUnpack(RowOp):
 
 WORKLOADS = {"a8w8": A8W8, "grouped": Grouped, "mxfp4": MXFP4, "softmax_quant": SoftmaxQuant, "softmax_quant_x64": SoftmaxQuantLarge,
              "fp16": FP16, "fp16_8192": FP16Large, "grouped_ref_shape": GroupedRefShape, "quant_per_group_fp4": QuantPerGroupFp4,
-             "softmax_flash_v2": SoftmaxFlashStep, "softmax_grad": SoftmaxGradStep, "nz_unpack": NzUnpack}
+             "softmax_flash_v2": SoftmaxFlashStep, "softmax_grad": SoftmaxGradStep, "antiquant": AntiQuantPerChannel, "nz_unpack": NzUnpack}
 
 
 class PinnedSet:
