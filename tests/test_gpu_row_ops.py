@@ -542,3 +542,33 @@ def test_row_kernels_write_nothing_past_their_outputs():
         ab.check(ab.softmax_flash_v2(x, y, sm, mx, None, None, None, m, k, ab.F16, ab.F32, False, True))
         ab.sync()
         assert tail_intact(y, m * k * 2) and tail_intact(sm, m * 32) and tail_intact(mx, m * 32), ("softmax_flash_v2", m, k)
+    # the softmax family added beside SoftMax, and AscendAntiQuant: ragged row counts at every launch shape
+    for m, k in [(5, 2048), (131, 64), (3, 4096), (2, 16384)]:
+        x = ab.to_dev(f16_bits(rng.standard_normal((m, k)).astype(np.float32)))
+        g = ab.to_dev(f16_bits(rng.uniform(-1, 1, (m, k)).astype(np.float32)))
+        st = ab.to_dev(f16_bits(np.ones((m, 16), np.float32)))
+        y, sm, mx = _guarded(ab, m * k * 2), _guarded(ab, m * 32), _guarded(ab, m * 32)
+        ab.check(ab.log_softmax(x, y, sm, mx, m, k, ab.F16, True))
+        ab.sync()
+        assert tail_intact(y, m * k * 2) and tail_intact(sm, m * 32) and tail_intact(mx, m * 32), ("log_softmax", m, k)
+        y = _guarded(ab, m * k * 2)
+        ab.check(ab.simple_softmax(x, y, st, st, m, k, ab.F16, ab.F16, True))
+        ab.sync()
+        assert tail_intact(y, m * k * 2), ("simple_softmax", m, k)
+        y, fr = _guarded(ab, m * k * 2), _guarded(ab, m * 32)
+        ab.check(ab.softmax_grad(g, x, y, m, k, ab.F16, False))
+        ab.check(ab.softmax_grad(g, x, fr, m, k, ab.F16, True))
+        ab.sync()
+        assert tail_intact(y, m * k * 2) and tail_intact(fr, m * 32), ("softmax_grad", m, k)
+        y, em = _guarded(ab, m * k * 2), _guarded(ab, m * 32)
+        sm2, mx2 = _guarded(ab, m * 32), _guarded(ab, m * 32)
+        ab.check(ab.softmax_flash(x, y, sm2, mx2, em, st, st, m, k, ab.F16, ab.F16, True, True))
+        ab.sync()
+        assert tail_intact(y, m * k * 2) and tail_intact(em, m * 32) and tail_intact(sm2, m * 32) and tail_intact(mx2, m * 32), ("softmax_flash", m, k)
+    for rows, cols, mode in [(37, 2048, 1), (9, 96, 1), (1025, 32, 2), (5, 160, 0)]:
+        src = ab.to_dev(rng.integers(-128, 128, (rows, cols), dtype=np.int8))
+        par = ab.to_dev(f16_bits(np.ones(max(rows, cols), np.float32)))
+        out = _guarded(ab, rows * cols * 2)
+        ab.check(ab.antiquant(src, out, rows, cols, ab.F16, mode, par, par))
+        ab.sync()
+        assert tail_intact(out, rows * cols * 2), ("antiquant", rows, cols, mode)
