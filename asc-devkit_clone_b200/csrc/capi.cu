@@ -1,4 +1,5 @@
 // Library state, error reporting and the memory / stream shims of the C ABI.
+#include <algorithm>
 #include <mutex>
 
 #include "common.cuh"
@@ -24,18 +25,48 @@ DeviceState* current_state()
     return st->ready ? st : nullptr;
 }
 
-int ensure_scratch(DeviceState* st, size_t bytes, cudaStream_t stream)
+int stream_scratch(DeviceState* st, size_t bytes, cudaStream_t stream, void** out)
 {
-    if (bytes <= st->scratch_bytes) return ASCB200_OK;
-    // Work queued on other streams may still read the old block: wait for the device first.
-    ASCB200_CUDA(cudaDeviceSynchronize());
-    (void)stream;
-    if (st->scratch_dev) ASCB200_CUDA(cudaFree(st->scratch_dev));
-    st->scratch_dev = nullptr;
-    st->scratch_bytes = 0;
-    size_t want = bytes + (bytes >> 2);
-    ASCB200_CUDA(cudaMalloc(&st->scratch_dev, want));
-    st->scratch_bytes = want;
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceState::StreamScratch* e = nullptr;
+    for (int i = 0; i < st->scratch_count; ++i)
+        if (st->scratch[i].stream == stream) e = &st->scratch[i];
+    if (!e) {
+        if (st->scratch_count == DeviceState::kMaxStreamScratch) {
+            // Table full: release the older half.  Their streams may still be running kernels that read the blocks.
+            ASCB200_CUDA(cudaDeviceSynchronize());
+            unsigned long long order[DeviceState::kMaxStreamScratch];
+            for (int i = 0; i < st->scratch_count; ++i) order[i] = st->scratch[i].last_use;
+            std::nth_element(order, order + st->scratch_count / 2, order + st->scratch_count);
+            const unsigned long long cut = order[st->scratch_count / 2];
+            int kept = 0;
+            for (int i = 0; i < st->scratch_count; ++i) {
+                if (st->scratch[i].last_use < cut) {
+                    if (st->scratch[i].dev) (void)cudaFree(st->scratch[i].dev);
+                } else {
+                    st->scratch[kept++] = st->scratch[i];
+                }
+            }
+            st->scratch_count = kept;
+        }
+        e = &st->scratch[st->scratch_count++];
+        *e = DeviceState::StreamScratch();
+        e->stream = stream;
+    }
+    e->last_use = ++st->scratch_clock;
+    if (bytes > e->bytes) {
+        // kernels queued on this stream may still read the old block
+        if (e->dev) {
+            ASCB200_CUDA(cudaStreamSynchronize(stream));
+            ASCB200_CUDA(cudaFree(e->dev));
+        }
+        e->dev = nullptr;
+        e->bytes = 0;
+        const size_t want = bytes + (bytes >> 2);
+        ASCB200_CUDA(cudaMalloc(&e->dev, want));
+        e->bytes = want;
+    }
+    *out = e->dev;
     return ASCB200_OK;
 }
 

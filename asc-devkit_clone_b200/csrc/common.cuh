@@ -15,12 +15,22 @@ struct DeviceState {
     int device = -1;
     int sm_count = 0;
     uint32_t* status_dev = nullptr;  // bit 0: bounded wait expired inside a GEMM kernel
-    void* scratch_dev = nullptr;     // grows on demand (scale re-tiling, padded operands)
-    size_t scratch_bytes = 0;
+    // scratch for re-tiled MX scale factors, one block per stream that asked for one (grows on demand)
+    struct StreamScratch {
+        cudaStream_t stream = nullptr;
+        void* dev = nullptr;
+        size_t bytes = 0;
+        unsigned long long last_use = 0;
+    };
+    static constexpr int kMaxStreamScratch = 64;
+    StreamScratch scratch[kMaxStreamScratch];
+    int scratch_count = 0;
+    unsigned long long scratch_clock = 0;
 };
 
 DeviceState* current_state();           // nullptr (and ASCB200_ENODEV recorded) when init has not run
-int ensure_scratch(DeviceState* st, size_t bytes, cudaStream_t stream);
+// Scratch of at least `bytes` that belongs to `stream` (see the note on MXFP4 scratch at ascb200_gemm).  Thread-safe.
+int stream_scratch(DeviceState* st, size_t bytes, cudaStream_t stream, void** out);
 int cuda_fail(cudaError_t e);           // records e, returns ASCB200_ECUDA
 #define ASCB200_CUDA(call)                                   \
     do {                                                     \

@@ -30,6 +30,7 @@ constexpr int NUM_THREADS = 384;        // 4 control warps + 8 epilogue warps
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int MAX_GROUPS = 1024;
 constexpr int SF_CHUNK_BYTES = 512;     // scale factors of 128 rows x 4 K-blocks (of 32 elements)
+constexpr int kSfPadBlocks = 2;         // re-tiled scale tensors carry two 128-row blocks of padding: a tile may start in the last block and read two more
 
 enum : int {
     OUT_F32 = ASCB200_F32, OUT_F16 = ASCB200_F16, OUT_BF16 = ASCB200_BF16, OUT_S8 = ASCB200_S8, OUT_S32 = ASCB200_S32,
@@ -64,7 +65,10 @@ struct GemmParams {
     int sf_kc;               // 512-byte chunks per 128-row block in sfa / sfb
     int pair_n;              // CTA-pair kernels for fp16 / bf16 / int8: columns per tile (multiple of 16, at most 256)
     int allow_m64;           // fp16 / bf16 / int8, single-CTA kernel: tiles of at most 64 rows use the 64-row instruction
+    int group_swap;          // grouped int8 on CTA pairs: a group's last, partial 256-row block is multiplied with the operand roles swapped
     uint32_t idesc;
+    uint32_t idesc_swap;     // instruction descriptor of such a block without its N field (the weights are then the 256-row operand)
+    int* tile_counter;       // CTA-pair kernel: not null = tiles are handed out at run time from this counter (zero at launch)
     uint32_t* status;
     EpiParams epi;
 };
@@ -96,6 +100,7 @@ struct Cfg {
 struct TileInfo {
     int row0, row_end, n0, n_end, group;  // n_end: first column after the tile
     int m64;  // the tile holds at most 64 rows (of its group, or of the matrix) and is multiplied with the 64-row instruction
+    int swap_n;  // CTA pairs, grouped: > 0 for a group's partial last block: its rows rounded up to 16, the N of the swapped instruction
 };
 
 // Tensor maps of the outputs (rank 2, box 32 x 32, swizzle = bytes of one box row).
@@ -163,7 +168,9 @@ __device__ __forceinline__ bool locate_tile(const GemmParams& p, int tile, int n
         t.n0 = (local / m_tiles) * BLOCK_N;
         t.n_end = t.n0 + BLOCK_N;
         t.m64 = p.allow_m64 && t.row_end - t.row0 <= 64;
+        t.swap_n = 0;
     } else {
+        t.swap_n = 0;
         t.group = 0;
         t.row0 = (tile % num_m) * BLOCK_M;
         t.row_end = p.m;
@@ -187,11 +194,14 @@ __device__ __forceinline__ bool locate_pair_tile(const GemmParams& p, int tile, 
         t.row0 = row_start[cursor] + (local % m_tiles) * 2 * BLOCK_M;
         t.row_end = row_start[cursor + 1];
         t.n0 = (local / m_tiles) * bn;
+        const int rows = t.row_end - t.row0;
+        t.swap_n = (p.group_swap && rows < 2 * BLOCK_M) ? (rows + 15) & ~15 : 0;
     } else {
         t.group = 0;
         t.row0 = (tile % num_m) * 2 * BLOCK_M;
         t.row_end = p.m;
         t.n0 = (tile / num_m) * bn;
+        t.swap_n = 0;
     }
     t.n_end = t.n0 + bn;
     t.m64 = 0;
@@ -628,6 +638,44 @@ __device__ __forceinline__ void epilogue_dispatch(const GemmParams& p, const Til
 #undef ASCB200_EPI_CASE
 }
 
+// Epilogue of a block that was multiplied with the operand roles swapped (grouped int8 on CTA pairs: the last, partial
+// 256-row block of a group).  The accumulator is the transpose of the output tile: TMEM lane = weight column, TMEM
+// column j = row t.row0 + j of the group, so a thread owns one output column and walks down the rows; the 32 lanes of a
+// warp write 32 consecutive elements of one output row per step.  Same arithmetic and rounding as the row-major path:
+// (float(acc) * ch[n]) * tok[m], each product rounded, optional FasterGelu, one conversion to the output type.
+template <int DT>
+__device__ __forceinline__ void epilogue_tile_swapped(const GemmParams& p, const TileInfo& t, uint32_t t_addr, int n_lane, int lane, int chunk0,
+                                                      int chunk1)
+{
+    static_assert(DT == OUT_F32 || DT == OUT_F16 || DT == OUT_BF16, "token x channel dequant writes floating-point outputs");
+    const bool n_ok = n_lane < p.n;
+    const float ch = n_ok ? __ldg(p.epi.ch + static_cast<size_t>(t.group) * p.n + n_lane) : 0.0f;
+    const int act = p.epi.act;
+#pragma unroll 1
+    for (int c = chunk0; c < chunk1; ++c) {
+        const int row_c = t.row0 + c * 32;
+        if (row_c >= t.row_end) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const int my_row = row_c + lane;
+        const float my_tok = (p.epi.tok && my_row < t.row_end) ? __ldg(p.epi.tok + my_row) : 1.0f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float tok = __shfl_sync(0xFFFFFFFFu, my_tok, j);
+            float v = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(r[j])), ch), tok);
+            if (act == 1) v = faster_gelu(v);
+            const int row = row_c + j;
+            if (row < t.row_end && n_ok) {
+                const size_t off = static_cast<size_t>(row) * static_cast<size_t>(p.epi.ldc) + n_lane;
+                if constexpr (DT == OUT_F32) static_cast<float*>(p.epi.c)[off] = v;
+                else if constexpr (DT == OUT_F16) static_cast<uint16_t*>(p.epi.c)[off] = static_cast<uint16_t>(pack_f16x2_sat(v, 0.0f));
+                else static_cast<uint16_t*>(p.epi.c)[off] = static_cast<uint16_t>(pack_bf16x2(v, 0.0f));
+            }
+        }
+    }
+}
+
 // ---- MMA issue (one thread) -------------------------------------------------------------------
 // State of the issuing thread for the shared-memory ring: low descriptor words of the current
 // stage's A / B / scale tiles and the addresses of its barriers, advanced by one add per stage.
@@ -924,6 +972,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // CTAs with multicast commits; epilogue warps of both CTAs release the accumulator stage on the
 // leader's barrier.  Plain (non-grouped) problems only.
 
+// Where a role of the CTA-pair kernel gets its next tile from.  Static: cluster c takes tiles c, c + clusters, ...  Dynamic
+// (grouped problems, whose tiles differ in cost by more than a factor of ten): warp 3 of the leader CTA draws tile numbers
+// from a counter in global memory and publishes each one in a two-slot ring that exists in both CTAs' shared memory; every
+// role (producer and epilogue warps of both CTAs, the leader's MMA warp) reads the slot and releases it on the leader's
+// barrier.  A negative number ends the kernel.  The ring lets the producer run one tile ahead of the epilogue and no more,
+// so that at the end of the kernel no cluster sits on tiles that an idle one could take.
+constexpr int kSchedSlots = 2;
+constexpr int kSchedConsumersLeader = 1 + 1 + NUM_EPI_WARPS, kSchedConsumersPeer = 1 + NUM_EPI_WARPS;
+struct TileFeed {
+    int next, stride;            // static
+    uint32_t full0, empty0;      // dynamic: own full barriers, the leader's empty barriers (cluster address)
+    const volatile int* slots;
+    int it;
+    bool dynamic, relaxed;
+    __device__ __forceinline__ void init(bool dyn, int cluster_id, int num_clusters, uint64_t* sched_full, uint64_t* sched_empty, const volatile int* sl,
+                                         bool relaxed_wait)
+    {
+        dynamic = dyn;
+        next = cluster_id;
+        stride = num_clusters;
+        full0 = smem_u32(sched_full);
+        empty0 = smem_u32(sched_empty) & kPeerBitMask;
+        slots = sl;
+        it = 0;
+        relaxed = relaxed_wait;
+    }
+    // Called by all lanes of a warp.  False: no more tiles (or the wait was abandoned: `ok` is cleared).
+    __device__ __forceinline__ bool take(int total_tiles, int& tile, bool& ok, volatile uint32_t* abort_smem, uint32_t* status)
+    {
+        if (!dynamic) {
+            tile = next;
+            next += stride;
+            return tile < total_tiles;
+        }
+        const int s = it % kSchedSlots;
+        const uint32_t ph = static_cast<uint32_t>(it / kSchedSlots) & 1u;
+        ++it;
+        if (!mbar_wait_cluster(full0 + 8 * s, ph, relaxed, abort_smem, status)) {
+            ok = false;
+            return false;
+        }
+        tile = slots[s];
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) mbar_arrive_cluster(empty0 + 8 * s);
+        return tile >= 0;
+    }
+};
+
 template <int KIND, int BLOCK_N>
 struct Cfg2 {
     static constexpr int B_TILE_BYTES = (BLOCK_N / 2) * ROW_BYTES;
@@ -967,6 +1063,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint64_t* acc_empty_bar = acc_full_bar + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
+    uint64_t* sched_full = reinterpret_cast<uint64_t*>(tmem_slot + 2);   // [kSchedSlots] in each CTA
+    uint64_t* sched_empty = sched_full + kSchedSlots;                   // [kSchedSlots], the leader's are used
+    volatile int* sched_tile = reinterpret_cast<volatile int*>(sched_empty + kSchedSlots);  // [kSchedSlots] in each CTA
+    static_assert((2 * 8 + 4 + 2 * kSchedSlots) * 8 + 8 + kSchedSlots * 4 <= 256, "barrier area");
     int* row_start = reinterpret_cast<int*>(epi_stage + C::EPI_BYTES + 256);  // both CTAs build identical tables
     int* tile_start = row_start + (MAX_GROUPS + 1);
 
@@ -990,6 +1090,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             mbar_init(smem_u32(&acc_full_bar[s]), 1);
             mbar_init(smem_u32(&acc_empty_bar[s]), 2 * NUM_EPI_WARPS);  // epilogue warps of both CTAs
         }
+        for (int s = 0; s < kSchedSlots; ++s) {
+            mbar_init(smem_u32(&sched_full[s]), 1);
+            mbar_init(smem_u32(&sched_empty[s]), kSchedConsumersLeader + kSchedConsumersPeer);
+        }
         *abort_word = 0u;
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
@@ -1007,6 +1111,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = p.groups > 0 ? tile_start[p.groups] : num_m * num_n;
+    const bool dynamic_tiles = p.tile_counter != nullptr;
 
     if (warp == 0) {
         // ===== TMA producer (both CTAs) =====
@@ -1014,11 +1119,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint32_t phase = 0;
         bool ok = true;
         TileInfo t;
-        for (int tile = cluster_id; ok && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t); tile += num_clusters) {
+        TileFeed feed;
+        feed.init(dynamic_tiles, cluster_id, num_clusters, sched_full, sched_empty, sched_tile, false);
+        for (int tile; ok && feed.take(total_tiles, tile, ok, abort_word, p.status) && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t);) {
             // rows past the end of a group belong to the next group (or lie outside the matrix and read as zero): they are
             // multiplied like the others and never stored
-            const int row0 = t.row0 + static_cast<int>(rank) * BLOCK_M;
+            // A swapped block (see GemmParams::group_swap) takes its swap_n rows as the narrow operand: each CTA loads half of
+            // them, in boxes of 32 rows (or one box of 128), into the start of its A buffer; the weights are loaded as always.
+            const int swap_half = t.swap_n / 2;
+            const int row0 = t.swap_n ? t.row0 + static_cast<int>(rank) * swap_half : t.row0 + static_cast<int>(rank) * BLOCK_M;
             const int n0 = t.n0 + static_cast<int>(rank) * (bn / 2);
+            const int x_boxes = (swap_half + 31) / 32;  // 1 .. 4
+            const uint32_t a_bytes = t.swap_n ? static_cast<uint32_t>(x_boxes) * 32 * ROW_BYTES : A_TILE_BYTES;
             for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                 ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_word, p.status);
                 if (!ok) break;
@@ -1027,7 +1139,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t bar = own_bar & kPeerBitMask;  // the leader's barrier counts both CTAs' bytes
                     const uint32_t sa = smem_u32(tiles + stage * C::STAGE_BYTES);
                     const uint32_t sb = sa + A_TILE_BYTES;
-                    if (rank == 0) mbar_expect_tx(own_bar, 2 * (A_TILE_BYTES + (bn / 2) * ROW_BYTES + C::SF_BYTES));
+                    if (rank == 0) mbar_expect_tx(own_bar, 2 * (a_bytes + (bn / 2) * ROW_BYTES + C::SF_BYTES));
                     const int k0 = kb * C::BLOCK_K;
                     const int kx = KIND == KIND_MXF4 ? k0 / 2 : k0;  // packed fp4: two values per tensor-map element
                     constexpr int MN_PER_BOX = KIND == KIND_F16 ? 64 : 128;
@@ -1041,7 +1153,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         for (int rb = 0; rb < C::SF_B_BLOCKS; ++rb)
                             tma_load_2d_pair(ssf + (1 + rb) * C::SF_BLOCK_BYTES, &tmap_sfb, 0, (tile_n0 / 128 + rb) * p.sf_kc + 2 * kb, bar);
                     }
-                    if (!p.a_mn) {
+                    if (KIND == KIND_I8 && t.swap_n && x_boxes < 4) {
+                        // tmap_sfa is here the map of A with boxes of 32 rows
+                        for (int j = 0; j < x_boxes; ++j) tma_load_3d_pair(sa + j * 32 * ROW_BYTES, &tmap_sfa, kx, row0 + 32 * j, 0, bar);
+                    } else if (!p.a_mn) {
                         tma_load_3d_pair(sa, &tmap_a, kx, row0, 0, bar);
                     } else {
 #pragma unroll
@@ -1080,7 +1195,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t idesc_hi_sf = p.idesc | (2u << 4) | (2u << 29);
         IssueCursor<C::STAGE_BYTES, C::NUM_STAGES, A_TILE_BYTES, A_TILE_BYTES + C::B_TILE_BYTES, C::SF_COLS_PER_STAGE, C::SF_SLOTS> cur;
         cur.init(smem_u32(tiles), a_lbo, b_lbo, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]), tmem_base + C::SF_COL0);
-        for (int tile = cluster_id; ok && tile < total_tiles; tile += num_clusters, ++acc_iter) {
+        int cursor = 0;
+        TileInfo t;
+        TileFeed feed;
+        feed.init(dynamic_tiles, cluster_id, num_clusters, sched_full, sched_empty, sched_tile, false);
+        for (int tile; ok && feed.take(total_tiles, tile, ok, abort_word, p.status) && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t); ++acc_iter) {
             const int acc_stage = acc_iter & 1;
             const uint32_t acc_phase = (acc_iter >> 1) & 1u;
             ok = mbar_wait(smem_u32(&acc_empty_bar[acc_stage]), acc_phase ^ 1u, abort_word, p.status);
@@ -1088,9 +1207,30 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
             const uint32_t acc_full = smem_u32(&acc_full_bar[acc_stage]);
-            const uint32_t sfb_off = static_cast<uint32_t>(((tile / num_m) * bn) % 128) / 32;
+            const uint32_t sfb_off = static_cast<uint32_t>(t.n0 % 128) / 32;
             const int last = p.num_k_blocks - 1;
             int kb = 0;
+            if (KIND == KIND_I8 && t.swap_n) {
+                // Swapped block: the pair's 256 weight rows (B buffers) are the wide operand, the block's swap_n rows of A the
+                // narrow one; the accumulator holds the transpose of the output tile in swap_n columns.
+                const uint32_t idesc = p.idesc_swap | (static_cast<uint32_t>(t.swap_n >> 3) << 17);
+                for (; kb <= last; ++kb) {
+                    ok = mbar_wait(cur.full_bar, cur.phase, abort_word, p.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (elect_one()) {
+                        mma_issue<KIND_I8, true>(d_tmem, cur.b_lo, hi_word, cur.a_lo, hi_word, idesc, kb == 0 ? 0u : 1u);
+                        mma_issue<KIND_I8, true>(d_tmem, cur.b_lo + b_k16, hi_word, cur.a_lo + a_k16, hi_word, idesc, 1u);
+                        mma_issue<KIND_I8, true>(d_tmem, cur.b_lo + 2 * b_k16, hi_word, cur.a_lo + 2 * a_k16, hi_word, idesc, 1u);
+                        mma_issue<KIND_I8, true>(d_tmem, cur.b_lo + 3 * b_k16, hi_word, cur.a_lo + 3 * a_k16, hi_word, idesc, 1u);
+                        commit_issue<true>(cur.empty_bar);
+                        if (kb == last) tc_commit_pair(acc_full);
+                    }
+                    __syncwarp();
+                    cur.advance();
+                }
+                continue;
+            }
             if constexpr (KIND == KIND_MXF4) {
                 // Copies and MMAs run through one in-order pipe; issuing the scale copies of two K blocks together and then
                 // eight MMAs back to back measured 3 % faster than alternating per K block.
@@ -1124,6 +1264,27 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 cur.advance();
             }
         }
+    } else if (warp == 3 && rank == 0 && dynamic_tiles) {
+        // ===== tile scheduler (leader CTA only) =====
+        const uint32_t peer_tile0 = map_to_cta(smem_u32(const_cast<int*>(sched_tile)), 1), peer_full0 = map_to_cta(smem_u32(sched_full), 1);
+        bool ok = true;
+        for (int it = 0; ok; ++it) {
+            const int s = it % kSchedSlots;
+            const uint32_t ph = static_cast<uint32_t>(it / kSchedSlots) & 1u;
+            ok = mbar_wait_cluster(smem_u32(&sched_empty[s]), ph ^ 1u, true, abort_word, p.status);
+            if (!ok) break;
+            int tile = 0;
+            if (lane == 0) {
+                tile = atomicAdd(p.tile_counter, 1);
+                if (tile >= total_tiles) tile = -1;
+                sched_tile[s] = tile;
+                st_cluster_u32(peer_tile0 + 4 * s, static_cast<uint32_t>(tile));
+                mbar_arrive_cluster(smem_u32(&sched_full[s]));   // release at cluster scope: the slot is written before the arrival is seen
+                mbar_arrive_cluster(peer_full0 + 8 * s);
+            }
+            tile = __shfl_sync(0xFFFFFFFFu, tile, 0);
+            if (tile < 0) break;
+        }
     } else if (warp >= 4) {
         // ===== epilogue (both CTAs, each for its own 128 rows) =====
         const int quad = warp & 3;
@@ -1133,16 +1294,28 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         int acc_iter = 0, cursor = 0;
         bool ok = true;
         TileInfo t;
-        for (int tile = cluster_id; ok && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t); tile += num_clusters, ++acc_iter) {
+        TileFeed feed;
+        feed.init(dynamic_tiles, cluster_id, num_clusters, sched_full, sched_empty, sched_tile, true);
+        for (int tile; ok && feed.take(total_tiles, tile, ok, abort_word, p.status) && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t); ++acc_iter) {
             const int acc_stage = acc_iter & 1;
             const uint32_t acc_phase = (acc_iter >> 1) & 1u;
             ok = mbar_wait_relaxed(smem_u32(&acc_full_bar[acc_stage]), acc_phase, abort_word, p.status);
             if (!ok) break;
             tc_fence_after();
-            t.row0 += static_cast<int>(rank) * BLOCK_M;  // this CTA's half of the pair tile
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc_stage * BLOCK_N;
-            epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, outs, smem_u32(epi_stage) + (warp - 4) * C::EPI_BYTES_PER_WARP, C::EPI_BYTES_PER_WARP, t_addr,
-                                                        quad, lane, chunk0, chunk1);
+            if (KIND == KIND_I8 && t.swap_n) {
+                // transposed accumulator: this lane owns output column n_lane, the warps of a quadrant split the rows
+                const int n_lane = t.n0 + static_cast<int>(rank) * BLOCK_M + quad * 32 + lane;
+                const int sw_chunks = (t.swap_n + 31) / 32, sw_split = (sw_chunks + 1) / 2;
+                const int c0 = half * sw_split, c1 = half ? sw_chunks : sw_split;
+                if (p.epi.c_dtype == OUT_BF16) epilogue_tile_swapped<OUT_BF16>(p, t, t_addr, n_lane, lane, c0, c1);
+                else if (p.epi.c_dtype == OUT_F16) epilogue_tile_swapped<OUT_F16>(p, t, t_addr, n_lane, lane, c0, c1);
+                else epilogue_tile_swapped<OUT_F32>(p, t, t_addr, n_lane, lane, c0, c1);
+            } else {
+                t.row0 += static_cast<int>(rank) * BLOCK_M;  // this CTA's half of the pair tile
+                epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, outs, smem_u32(epi_stage) + (warp - 4) * C::EPI_BYTES_PER_WARP, C::EPI_BYTES_PER_WARP,
+                                                            t_addr, quad, lane, chunk0, chunk1);
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(smem_u32(&acc_empty_bar[acc_stage]) & kPeerBitMask);
@@ -1336,8 +1509,9 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     if (d->m < 0 || d->n < 0 || d->k < 0) return ASCB200_EINVAL;
     if (d->m == 0 || d->n == 0) return ASCB200_OK;
     if (!d->a_dev || !d->b_dev || !d->c_dev || d->k == 0) return ASCB200_EINVAL;
-    for (int i = 0; i < 3; ++i)
+    for (int i = 0; i < 2; ++i)
         if (d->reserved[i] != 0) return ASCB200_EINVAL;
+    if (d->scale_flags & ~(ASCB200_SCALE_A_PREPACKED | ASCB200_SCALE_B_PREPACKED)) return ASCB200_EINVAL;
     const int kind = d->kind;
     if (kind < ASCB200_KIND_F16 || kind > ASCB200_KIND_MXFP4) return ASCB200_EINVAL;
     const bool acc_int = kind == ASCB200_KIND_S8;
@@ -1419,11 +1593,14 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     // memory and L2 per MAC; measured on 4096 x 4096 x 11008 int8: pair 256x256 1.0, single 128x256 0.88, 128x128 0.75,
     // 128x64 0.5).  Small problems and thin N-slabs get narrower tiles so that the last wave is not mostly idle.
     const int pair_clusters = sm_count / 2;
-    const bool pair_possible = !(fixed && kind == ASCB200_KIND_MXFP4) && !(getenv("ASCB200_NO_PAIR") && getenv("ASCB200_NO_PAIR")[0] == '1');
-    // Grouped problems take CTA pairs only when groups are long: a group's last 256-row tile is half empty on average, and
-    // under the board's power cap the wasted MMAs cost as much time as useful ones (64 groups of 512 rows on average:
-    // pairs 490 us at 1.09 GHz, single-CTA tiles 425-475 us at 1.25-1.32 GHz).
-    const bool pair_allowed = pair_possible && (!grouped || m / groups >= 16 * BLOCK_M);
+    const bool pair_possible = !(getenv("ASCB200_NO_PAIR") && getenv("ASCB200_NO_PAIR")[0] == '1');
+    // Grouped problems on CTA pairs: full 256-row blocks of a group run like a plain GEMM; the group's last, partial block
+    // is multiplied with the operand roles swapped (the pair's 256 weight rows become the M side of the instruction, the
+    // block's rows, rounded up to 16, its N side), so that at most 15 rows per group are multiplied in vain.  Without the
+    // swap a group's last 256-row tile is half empty on average, and under the board's power cap the wasted MMAs cost as
+    // much time as useful ones (64 groups of 512 rows on average: masked pairs 490 us, single-CTA tiles 406-475 us).
+    const bool group_swap_ok = grouped && !(getenv("ASCB200_NO_GROUP_SWAP") && getenv("ASCB200_NO_GROUP_SWAP")[0] == '1');
+    const bool pair_allowed = pair_possible && (!grouped || group_swap_ok || m / groups >= 16 * BLOCK_M);
     const int wide = kind == ASCB200_KIND_MXFP4 ? 192 : 256;   // fp4 at 256 columns cannot double-buffer its accumulators in TMEM
     int block_n = 64;
     bool use_pair = false;
@@ -1434,7 +1611,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         Cand cands[20];
         int num_cands = 0;
         cands[num_cands++] = {wide, true, 1.0};
-        if (kind != ASCB200_KIND_MXFP4 && d->trans_b) {
+        if (kind != ASCB200_KIND_MXFP4 && d->trans_b && !(grouped && group_swap_ok)) {
             // CTA-pair tiles of any width that is a multiple of 16: a narrower tile re-reads A more often per column
             // (128 columns measured at 0.75 of the full width's rate), but may fill the last wave far better
             for (int bn = 240; bn >= 64; bn -= 16) cands[num_cands++] = {bn, true, 1.0 / (1.0 + 0.33 * (256.0 / bn - 1.0))};
@@ -1450,6 +1627,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
             if (c.bn > 64 && n <= c.bn / 2 && (c.pair || c.bn != 128)) continue;             // do not pad N by more than 2x
             const long long n_tiles = (n + c.bn - 1) / c.bn;
             // grouped: the host does not see the counts; a group ends on average half a tile past its last full one
+            // (a swapped block costs its share of rows: half a tile on average, like the masked tail it replaces costs in tiles)
             const long long pair_m_tiles = grouped ? (m + 2 * BLOCK_M - 1) / (2 * BLOCK_M) + (groups + 1) / 2 : (m + 2 * BLOCK_M - 1) / (2 * BLOCK_M);
             const long long tiles = c.pair ? pair_m_tiles * n_tiles : m_tiles * n_tiles;
             const long long slots = c.pair ? pair_clusters : sm_count;
@@ -1494,31 +1672,42 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     p.groups = grouped ? groups : 0;
     p.pair_n = block_n;
     p.allow_m64 = kind != ASCB200_KIND_MXFP4 && !(getenv("ASCB200_NO_M64") && getenv("ASCB200_NO_M64")[0] == '1');
+    p.group_swap = (grouped && use_pair && block_n == 256 && group_swap_ok) ? 1 : 0;
     p.group_counts = reinterpret_cast<const long long*>(group_counts);
     p.status = fixed ? fixed->status_dev : st->status_dev;
     p.epi = e;
 
     if (kind == ASCB200_KIND_MXFP4) {
-        // re-tile both scale tensors into scratch (layout documented at retile_scales_kernel)
+        // Scale factors in the 512-byte chunk order the kernels copy into TMEM (layout documented at retile_scales_kernel):
+        // taken as they are when the caller prepacked them (ascb200_mx_scale_prepack: static weights), else re-tiled here
+        // into scratch that belongs to `stream`, so that calls on different streams do not overwrite each other's scales.
         const int ks = k / 32;
         const int kc = 2 * p.num_k_blocks;
-        const int rba = (m + 127) / 128, rbb = (n + 127) / 128 + 2;  // B tiles may read up to two blocks past the last row
-        const size_t bytes_a = static_cast<size_t>(rba) * kc * SF_CHUNK_BYTES, bytes_b = static_cast<size_t>(rbb) * kc * SF_CHUNK_BYTES;
-        uint8_t* sfa;
-        if (fixed) {
-            if (bytes_a + bytes_b > fixed->scale_scratch_bytes) return ASCB200_ETOOBIG;
-            sfa = fixed->scale_scratch_dev;
-        } else {
-            rc = ensure_scratch(st, bytes_a + bytes_b, stream);
-            if (rc != ASCB200_OK) return rc;
-            sfa = static_cast<uint8_t*>(st->scratch_dev);
+        const bool pre_a = (d->scale_flags & ASCB200_SCALE_A_PREPACKED) != 0, pre_b = (d->scale_flags & ASCB200_SCALE_B_PREPACKED) != 0;
+        const int rba = (m + 127) / 128, rbb = (n + 127) / 128 + kSfPadBlocks;  // B tiles may read up to two blocks past the last row
+        const size_t bytes_a = pre_a ? 0 : static_cast<size_t>(rba) * kc * SF_CHUNK_BYTES, bytes_b = pre_b ? 0 : static_cast<size_t>(rbb) * kc * SF_CHUNK_BYTES;
+        uint8_t* scratch = nullptr;
+        if (bytes_a + bytes_b > 0) {
+            if (fixed) {
+                if (bytes_a + bytes_b > fixed->scale_scratch_bytes) return ASCB200_ETOOBIG;
+                scratch = fixed->scale_scratch_dev;
+            } else {
+                void* ptr = nullptr;
+                rc = stream_scratch(st, bytes_a + bytes_b, stream, &ptr);
+                if (rc != ASCB200_OK) return rc;
+                scratch = static_cast<uint8_t*>(ptr);
+            }
         }
-        uint8_t* sfb = sfa + bytes_a;
-        const int kc_tiles = (kc + 7) / 8;
-        retile_scales_kernel<<<(rba + rbb) * kc_tiles, 256, 0, stream>>>(static_cast<const uint8_t*>(d->scale_a_dev), reinterpret_cast<uint32_t*>(sfa), m, rba,
-                                                                         static_cast<const uint8_t*>(d->scale_b_dev), reinterpret_cast<uint32_t*>(sfb), n, ks, kc,
-                                                                         kc_tiles);
-        ASCB200_CUDA(cudaGetLastError());
+        const uint8_t* sfa = pre_a ? static_cast<const uint8_t*>(d->scale_a_dev) : scratch;
+        const uint8_t* sfb = pre_b ? static_cast<const uint8_t*>(d->scale_b_dev) : scratch + bytes_a;
+        if (!aligned_to(sfa, 16) || !aligned_to(sfb, 16)) return ASCB200_EALIGN;
+        if (scratch) {
+            const int kc_tiles = (kc + 7) / 8;
+            const int blocks_a = pre_a ? 0 : rba * kc_tiles, blocks_b = pre_b ? 0 : rbb * kc_tiles;
+            ASCB200_CUDA(launch_pdl(retile_scales_kernel, dim3(blocks_a + blocks_b), dim3(256), 0, stream, static_cast<const uint8_t*>(d->scale_a_dev),
+                                    reinterpret_cast<uint32_t*>(scratch), m, pre_a ? 0 : rba, static_cast<const uint8_t*>(d->scale_b_dev),
+                                    reinterpret_cast<uint32_t*>(scratch + bytes_a), n, ks, kc, kc_tiles));
+        }
         p.sfa = sfa;
         p.sfb = sfb;
         p.sf_kc = kc;
@@ -1535,14 +1724,34 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
             // the re-tiled scales as rank-2 tensors [chunk][128 x u32] for tile loads
             CUtensorMap tsfa, tsfb;
             rc = make_sf_map(&tsfa, p.sfa, static_cast<uint64_t>((m + 127) / 128) * p.sf_kc, 2);
-            if (rc == ASCB200_OK) rc = make_sf_map(&tsfb, p.sfb, static_cast<uint64_t>((n + 127) / 128 + 2) * p.sf_kc, 2);
+            if (rc == ASCB200_OK) rc = make_sf_map(&tsfb, p.sfb, static_cast<uint64_t>((n + 127) / 128 + kSfPadBlocks) * p.sf_kc, 2);
             if (rc != ASCB200_OK) return rc;
             p.idesc = make_idesc_mxf4(2 * BLOCK_M, 192);
             return launch_gemm_pair<KIND_MXF4, 192>(ta, tb, tsfa, tsfb, outs, p, clusters, stream);
         }
         if (kind == ASCB200_KIND_S8) {
             p.idesc = make_idesc(2, 1, 1, a_mn, b_mn, 2 * BLOCK_M, block_n);
-            return launch_gemm_pair<KIND_I8, 256>(ta, tb, ta, tb, outs, p, clusters, stream);
+            CUtensorMap tx32 = ta;
+            if (grouped && !fixed && getenv("ASCB200_DYNAMIC_TILES") && getenv("ASCB200_DYNAMIC_TILES")[0] == '1') {
+                // Opt-in: tiles are handed out at run time from a counter in this stream's scratch, cleared on the stream
+                // before the launch.  Tiles of a grouped problem differ widely in cost (a swapped block of 16 rows against a
+                // full one), and with the static assignment the busiest SM of the 64-group configuration spends 90 % of
+                // the kernel in MMAs, the idlest 52 %; yet the kernel did not get shorter with run-time hand-out (576 k against 551 k
+                // cycles): its small groups are bound by the one read of their weights from HBM, not by the tile order.
+                void* ptr = nullptr;
+                rc = stream_scratch(st, 256, stream, &ptr);
+                if (rc != ASCB200_OK) return rc;
+                ASCB200_CUDA(cudaMemsetAsync(ptr, 0, sizeof(int), stream));
+                p.tile_counter = static_cast<int*>(ptr);
+            }
+            if (p.group_swap) {
+                // the weights as the 256-row operand, rows of A as the narrow one (its N field is filled in per block);
+                // A once more with boxes of 32 rows, for blocks that hold fewer than 97 rows per CTA
+                p.idesc_swap = make_idesc(2, 1, 1, b_mn, a_mn, 2 * BLOCK_M, 0);
+                rc = make_map(&tx32, dt, esz, d->a_dev, k, m, 1, lda, static_cast<uint64_t>(lda) * m, row_elems, 32);
+                if (rc != ASCB200_OK) return rc;
+            }
+            return launch_gemm_pair<KIND_I8, 256>(ta, tb, tx32, tb, outs, p, clusters, stream);
         }
         const uint32_t fmt = kind == ASCB200_KIND_BF16 ? 1u : 0u;
         p.idesc = make_idesc(1, fmt, fmt, a_mn, b_mn, 2 * BLOCK_M, block_n);
@@ -1623,16 +1832,62 @@ int run_gemm_mxfp4_noalloc(const ascb200_gemm_desc* d, cudaStream_t stream)
     fixed.scale_scratch_dev = nd->base + NOALLOC_HEAD_BYTES;
     fixed.scale_scratch_bytes = NOALLOC_SCALE_BYTES;
     fixed.sm_count = nd->sm_count;
-    // the array keeps whatever the previous call left: the status word must start at zero; the scale
-    // area needs no clearing because the re-tiling kernels rewrite every byte the GEMM reads
-    ASCB200_CUDA(cudaMemsetAsync(fixed.status_dev, 0, sizeof(uint32_t), stream));
+    // The array keeps whatever the previous call left.  Nothing in it has to start at zero: the re-tiling kernel rewrites
+    // every scale byte the GEMM reads, and the status word is a latch (zero when the library image is loaded, set by an
+    // expired wait, read and cleared by ascb200_noalloc_status).
     return run_gemm(d, nullptr, 0, stream, &fixed);
+}
+
+int noalloc_status(cudaStream_t stream, uint32_t* status_host)
+{
+    NoAllocDevice* nd = nullptr;
+    int rc = noalloc_setup(&nd);
+    if (rc != ASCB200_OK) return rc;
+    uint32_t v = 0;
+    ASCB200_CUDA(cudaMemcpyAsync(&v, nd->base, sizeof(v), cudaMemcpyDeviceToHost, stream));
+    ASCB200_CUDA(cudaStreamSynchronize(stream));
+    if (status_host) *status_host = v;
+    if (v != 0) {
+        ASCB200_CUDA(cudaMemsetAsync(nd->base, 0, sizeof(v), stream));
+        return ASCB200_ETIMEOUT;
+    }
+    return ASCB200_OK;
+}
+
+// Re-tiles one scale tensor [rows, k / 32] into the chunk order of the kernels, padding blocks included.
+int mx_scale_prepack(const void* scale_dev, int rows, int k, void* out_dev, size_t out_bytes, cudaStream_t stream)
+{
+    if (!scale_dev || !out_dev || rows <= 0 || k <= 0 || k % 64 != 0) return ASCB200_EINVAL;
+    if (!aligned_to(out_dev, 16)) return ASCB200_EALIGN;
+    const int block_k = 256;
+    const int kc = 2 * ((k + block_k - 1) / block_k);
+    const int rb = (rows + 127) / 128 + kSfPadBlocks;
+    if (out_bytes < static_cast<size_t>(rb) * kc * SF_CHUNK_BYTES) return ASCB200_EINVAL;
+    const int kc_tiles = (kc + 7) / 8;
+    ASCB200_CUDA(launch_pdl(retile_scales_kernel, dim3(rb * kc_tiles), dim3(256), 0, stream, static_cast<const uint8_t*>(scale_dev),
+                            static_cast<uint32_t*>(out_dev), rows, rb, static_cast<const uint8_t*>(nullptr), static_cast<uint32_t*>(nullptr), 0, k / 32,
+                            kc, kc_tiles));
+    return ASCB200_OK;
 }
 
 }  // namespace
 }  // namespace ascb200
 
 extern "C" {
+
+int ascb200_noalloc_status(void* stream, uint32_t* status_host) { return ascb200::noalloc_status(static_cast<cudaStream_t>(stream), status_host); }
+
+size_t ascb200_mx_scale_prepacked_bytes(int32_t rows, int32_t k)
+{
+    if (rows <= 0 || k <= 0) return 0;
+    return static_cast<size_t>((rows + 127) / 128 + ascb200::kSfPadBlocks) * (2 * ((k + 255) / 256)) * ascb200::SF_CHUNK_BYTES;
+}
+
+int ascb200_mx_scale_prepack(const void* scale_dev, int32_t rows, int32_t k, void* out_dev, size_t out_bytes, void* stream)
+{
+    if (!ascb200::current_state()) return ASCB200_ENODEV;
+    return ascb200::mx_scale_prepack(scale_dev, rows, k, out_dev, out_bytes, static_cast<cudaStream_t>(stream));
+}
 
 int ascb200_gemm_mxfp4_noalloc(const ascb200_gemm_desc* desc, void* stream)
 {

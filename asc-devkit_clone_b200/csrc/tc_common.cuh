@@ -227,6 +227,42 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
 {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// Waits that observe data written by the other CTA of the pair (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_test_wait_cluster(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded like mbar_wait; `relaxed` backs off between polls (for waits that are expected to last long).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, bool relaxed, volatile uint32_t* abort_smem, uint32_t* status)
+{
+    if (mbar_test_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t it = 0;
+    while (true) {
+        if (relaxed) __nanosleep(64);
+        if (mbar_test_wait_cluster(bar, parity)) return true;
+        if ((++it & 255u) == 0u && mbar_wait_expired(t0, abort_smem, status)) return false;
+    }
+}
+// The address, in the cluster's shared-memory window, of `addr` in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v)
+{
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
 // Tile load issued by either CTA of a pair: data lands in the issuing CTA, the bytes are counted on
 // the leader's barrier.  No multicast: every CTA fetches exactly the rows it owns.
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, int x, int y, int z, uint32_t leader_bar)

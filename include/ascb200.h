@@ -87,7 +87,7 @@ ASCB200_API int ascb200_event_elapsed_ms(void* start, void* stop, float* ms); /*
 /* CUDA-graph shims: record the calls issued on `stream` between begin and end into one graph and
  * replay it with a single launch.  For launch-bound sequences of small operators (the role the
  * reference gives to a single kernel that calls several adv_api operators back to back).  A call
- * that may allocate (the first MXFP4 ascb200_gemm of a larger size) must be made once before capture. */
+ * that may allocate (the first MXFP4 ascb200_gemm of a larger size on that stream) must be made once before capture. */
 ASCB200_API int ascb200_graph_begin(void* stream);
 ASCB200_API int ascb200_graph_end(void* stream, void** graph_exec);
 ASCB200_API int ascb200_graph_launch(void* graph_exec, void* stream);
@@ -136,14 +136,35 @@ typedef struct ascb200_gemm_desc {
     int32_t relu;            /* enableRelu of the fixpipe stage */
     int32_t act;             /* 0 none, 1 FasterGelu (DEQUANT_TOKEN_CHANNEL only) */
     int32_t atomic;          /* enAtomic of IterateAll / GetTensorC: 0 C is overwritten, 1 C += result, 2 C = max(C, result), 3 C = min(C, result); F32, S32, F16, BF16 outputs */
-    int32_t reserved[3];     /* must be zero */
+    int32_t scale_flags;     /* MXFP4: ASCB200_SCALE_*_PREPACKED bits; 0 = scale_a_dev / scale_b_dev are plain [rows, k/32] tensors */
+    int32_t reserved[2];     /* must be zero */
 } ascb200_gemm_desc;
+
+/* scale_flags: the scale tensor was re-tiled once with ascb200_mx_scale_prepack (static weights); the call then skips its
+ * own re-tiling of that tensor and reads the prepacked copy in place. */
+enum { ASCB200_SCALE_A_PREPACKED = 1, ASCB200_SCALE_B_PREPACKED = 2 };
 
 /* One whole Matmul: what Matmul<...>::IterateAll produces for the object state set by
  * SetTensorA / SetTensorB / SetBias / SetQuantScalar / SetQuantVector
  * (include/adv_api/matmul/matmul.h:79-399; impl/adv_api/detail/matmul/matmul_impl.h:119-139),
  * MX variant with SetTensorScaleA/B (impl/adv_api/detail/matmul/mx_matmul_impl.h:136-173). */
 ASCB200_API int ascb200_gemm(const ascb200_gemm_desc* desc, void* stream);
+/* MXFP4 and scratch memory.  The tensor core reads MX scale factors in tiles of 128 rows x 4 K-blocks, so ascb200_gemm re-tiles
+ * every scale tensor that is not prepacked into device scratch before the GEMM (one extra, small launch).  The scratch belongs
+ * to `stream`: calls on different streams use different blocks and may overlap freely; calls on one stream are ordered by it.
+ * The first MXFP4 call on a stream, and a call that needs more scratch than any before it on that stream, allocates (and, when it
+ * grows, synchronises that stream first): make such a call once before capturing the stream into a graph.  Up to 64 streams per
+ * device keep their own block; beyond that the oldest blocks are released after a device-wide synchronisation.  A stream that was
+ * destroyed and whose handle value the runtime hands out again simply inherits the block. */
+
+/* The step the reference performs when it moves MX scales GM -> L1 -> L0A_MX / L0B_MX in its pair-interleaved fractal order
+ * (LoadData with LoadData2DMxParams: include/basic_api/kernel_struct_mm.h:132-153; examples/.../load_data_2dmx_l12l0), done once
+ * for a tensor that does not change between calls (the weights' scales): re-tiles scale_dev, e8m0 bytes [rows, k/32] row-major,
+ * into out_dev in the order ascb200_gemm reads (512-byte chunks of 128 rows x 4 K-blocks, two padding blocks of rows at the end).
+ * out_dev must be 16-byte aligned and hold ascb200_mx_scale_prepacked_bytes(rows, k) bytes; k a multiple of 64.  Pass out_dev as
+ * scale_a_dev / scale_b_dev with the matching ASCB200_SCALE_*_PREPACKED flag. */
+ASCB200_API size_t ascb200_mx_scale_prepacked_bytes(int32_t rows, int32_t k);
+ASCB200_API int ascb200_mx_scale_prepack(const void* scale_dev, int32_t rows, int32_t k, void* out_dev, size_t out_bytes, void* stream);
 
 /* Grouped int8 matmul of the reference's QuantGroupMatmul example kernel
  * (examples/01_simd_cpp_api/05_best_practices/03_fusion_compute/quant_group_matmul_high_performance/
@@ -168,19 +189,22 @@ ASCB200_API int ascb200_grouped_gemm(const ascb200_gemm_desc* desc, const int64_
  * library, held until the process exits).  It calls no cudaMalloc / cudaFree and needs no ascb200_init;
  * it works on the calling thread's current device.  Inputs and outputs are still the caller's.
  *
- *  - desc: exactly as for ascb200_gemm with kind == ASCB200_KIND_MXFP4 (other kinds: ASCB200_EUNSUPPORTED);
- *  - limit: the re-tiled scales take (ceil(m/128) + 2*ceil(n/256)) * 2*ceil(k/256) * 512 bytes; if that
- *    exceeds ASCB200_NOALLOC_MAX_SCALE_BYTES the call returns ASCB200_ETOOBIG and launches nothing
- *    (m = n = k = 8192 just fits);
+ *  - desc: exactly as for ascb200_gemm with kind == ASCB200_KIND_MXFP4 (other kinds: ASCB200_EUNSUPPORTED); it runs the same
+ *    kernels as ascb200_gemm and gives the same bytes;
+ *  - limit: the re-tiled scales take (ceil(m/128) + ceil(n/128) + 2) * 2*ceil(k/256) * 512 bytes (the 2 are padding blocks that
+ *    tiles at the right edge read); if that exceeds ASCB200_NOALLOC_MAX_SCALE_BYTES the call returns ASCB200_ETOOBIG and launches
+ *    nothing (m = n = k = 8192 needs 4,259,840 bytes and fits; a prepacked scale tensor does not count);
  *  - the first call on each device looks up the array's device address; make that first call outside
  *    any stream capture;
- *  - all calls on one device share the array, which keeps the previous call's contents (the part that
- *    must start at zero is cleared on the stream at the start of each call): two calls whose GPU work
+ *  - all calls on one device share the array, which keeps the previous call's contents (every scale byte a call reads is
+ *    rewritten by that call first; the status word is a latch and needs no clearing): two calls whose GPU work
  *    may overlap - different streams, or different host threads - race on it; serialise them;
- *  - an expired device-side wait is recorded in the array's first word, not in the word that
- *    ascb200_device_status reads. */
-#define ASCB200_NOALLOC_MAX_SCALE_BYTES (4u << 20)
+ *  - an expired device-side wait is latched in the array's first word, not in the word that ascb200_device_status reads:
+ *    ascb200_noalloc_status (which allocates nothing either) copies it to *status_host after synchronising `stream`, returns
+ *    ASCB200_ETIMEOUT when it is non-zero and clears it. */
+#define ASCB200_NOALLOC_MAX_SCALE_BYTES ((4u << 20) + (512u << 10))
 ASCB200_API int ascb200_gemm_mxfp4_noalloc(const ascb200_gemm_desc* desc, void* stream);
+ASCB200_API int ascb200_noalloc_status(void* stream, uint32_t* status_host);
 
 /* ---- SoftMax ------------------------------------------------------------------------------------ */
 

@@ -18,6 +18,9 @@ input+output samples as .npz, so the tests can pin the CPU oracle without the re
                      example's 128x128 uniform(-10, 10) input, plus a half input widened to fp32
   softmaxgrad.npz    04_advanced_api/01_activation/softmaxgrad/scripts/gen_data.py: softmax_grad_float, both modes, on the
                      example's uniform(-1, 1) inputs (rows sampled from its 960x960 shape)
+  softmaxflashv2.npz 04_advanced_api/01_activation/softmaxflashv2/scripts/gen_data.py run as a script: its 960x960 uniform(-1, 1)
+                     fp32 input and the golden_max / golden_sum files it writes ([M, 8]: every row's value repeated over one
+                     32-byte block), rows sampled
   antiquant.npz      04_advanced_api/03_quantization/antiquant/scripts/gen_data.py, both arch variants (half arithmetic / fp32 arithmetic)
   quant.npz          04_advanced_api/03_quantization/quant/scripts/gen_data.py (both arch variants)
   dequant.npz        04_advanced_api/03_quantization/dequant/scripts/gen_data.py
@@ -183,6 +186,15 @@ def softmaxgrad(ref):
                         front=mod.softmax_grad_float(grad, src, isFront=True))
 
 
+def softmaxflashv2(ref):
+    files = run_script_in_tmp(os.path.join(ref, EX, "04_advanced_api/01_activation/softmaxflashv2/scripts/gen_data.py"), 21)
+    x = np.frombuffer(files["input/input_x.bin"], np.float32).reshape(960, 960)
+    gmax = np.frombuffer(files["output/golden_max.bin"], np.float32).reshape(960, 8)
+    gsum = np.frombuffer(files["output/golden_sum.bin"], np.float32).reshape(960, 8)
+    rows = np.arange(0, 960, 24)
+    np.savez_compressed(os.path.join(HERE, "softmaxflashv2.npz"), x=x[rows], golden_max=gmax[rows], golden_sum=gsum[rows])
+
+
 def quant(ref):
     p = os.path.join(ref, EX, "04_advanced_api/03_quantization/quant/scripts/gen_data.py")
     out = {}
@@ -291,6 +303,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("ASC_REFERENCE_ROOT", "reference"))
     args = ap.parse_args()
-    for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, logsoftmax, softmaxgrad, quant, antiquant, dequant, grouped, mxfp4, casts):
+    for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, logsoftmax, softmaxgrad, softmaxflashv2, quant, antiquant, dequant, grouped, mxfp4, casts):
         fn(args.ref)
         print("wrote", fn.__name__)

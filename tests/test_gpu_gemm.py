@@ -236,6 +236,40 @@ def test_grouped_a8w8_cta_pairs(counts, trans_b, monkeypatch):
     assert (got == ref).all(), f"{(got != ref).sum()} differ; first {np.argwhere(got != ref)[:5].tolist()}"
 
 
+@pytest.mark.parametrize("trans_b", [True, False])
+@pytest.mark.parametrize("c_dtype", [0, 1, 2])
+def test_grouped_a8w8_swapped_tail_blocks(trans_b, c_dtype, monkeypatch):
+    """CTA pairs multiply a group's partial last 256-row block with the operand roles swapped (weights on the M side, the
+    block's rows, rounded up to 16, on the N side).  Group sizes cover every box count of the narrow operand, tails that end on
+    and next to multiples of 16 and 32, whole blocks before a tail, and a column count that is no multiple of the tile width."""
+    monkeypatch.setenv("ASCB200_PAIR_N", "256")
+    if c_dtype == 2 and trans_b:
+        monkeypatch.setenv("ASCB200_DYNAMIC_TILES", "1")   # tiles handed out at run time from a counter instead of by cluster number
+    ab = dev()
+    counts = np.array([1, 15, 16, 17, 0, 63, 64, 65, 96, 97, 128, 129, 191, 193, 240, 241, 255, 256, 257, 512 + 33, 768], np.int64)
+    G, k, n = len(counts), 384, 608
+    m = int(counts.sum())
+    rng = np.random.default_rng(4242 + c_dtype)
+    x = rng.integers(-127, 128, (m, k)).astype(np.int8)
+    w = rng.integers(-127, 128, (G, n, k) if trans_b else (G, k, n)).astype(np.int8)
+    tok = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+    ch = rng.uniform(1e-3, 1e-2, (G, n)).astype(np.float32)
+    esz = 4 if c_dtype == ab.F32 else 2
+    d_c = ab.DevBuf(m * n * esz + 256)
+    d_c.fill(0x5A)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(x), ab.to_dev(w), d_c, c_dtype, epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL,
+                     trans_b=trans_b, tok=ab.to_dev(tok), ch=ab.to_dev(ch), group_counts=ab.to_dev(counts), groups=G))
+    ab.sync()
+    host = d_c.download(shape=(m * n * esz + 256,), dtype=np.uint8)
+    assert (host[m * n * esz:] == 0x5A).all(), "wrote past the end"
+    ref = orc.grouped_i8(x, w, counts, tok, ch, c_dtype, trans_b=trans_b)
+    got = host[:m * n * esz].view(ref.dtype).reshape(m, n)
+    if c_dtype == ab.F32:
+        assert (got.view(np.uint32) == ref.view(np.uint32)).all()
+    else:
+        assert (got == ref).all(), f"{(got != ref).sum()} differ; first {np.argwhere(got != ref)[:5].tolist()}"
+
+
 def test_grouped_matches_reference_recipe(golden_dir):
     """The grouped example's own numpy recipe incl. FasterGelu and fp16 output (tests/golden/grouped.npz)."""
     import os

@@ -218,3 +218,75 @@ def test_fp8_conversion_matches_ml_dtypes():
         assert (orc.f32_to_fp8(xs, e5m2) == xs.astype(dt).view(np.uint8)).all()
         top = 0x7B if e5m2 else 0x7E
         assert orc.f32_to_fp8(np.array([1e9, -1e9, np.inf], np.float32), e5m2).tolist() == [top, top | 0x80, top]
+
+
+def test_softmax_flash_v2_recipe(golden_dir):
+    """SoftmaxFlashV2 against the golden_max / golden_sum files its example's generator writes ([M, 8] blocks, fp32 rows of 960):
+    one step over the whole row, and two steps over two K tiles with the update formulas in between."""
+    g = load(golden_dir, "softmaxflashv2.npz")
+    x, gmax, gsum = g["x"], g["golden_max"], g["golden_sum"]
+    y, s, mx, em = orc.softmax_flash_v2(x, orc.F32, orc.F32, brc=True)
+    assert em is None and mx.shape == gmax.shape and s.shape == gsum.shape
+    assert (mx == gmax).all()
+    assert np.allclose(s, gsum, rtol=1e-6)
+    assert np.allclose(y, np.exp(x - gmax[:, :1]), rtol=2e-6, atol=1e-7)
+    # online form: tile 1 without update, tile 2 with it; the running maximum and sum end at the whole row's
+    a, b = np.ascontiguousarray(x[:, :480]), np.ascontiguousarray(x[:, 480:])
+    ya, sa, ma, _ = orc.softmax_flash_v2(a, orc.F32, orc.F32, brc=True)
+    yb, sb, mb, emb = orc.softmax_flash_v2(b, orc.F32, orc.F32, in_sum=sa, in_max=ma, brc=True)
+    assert (mb == gmax).all()
+    assert np.allclose(sb, gsum, rtol=2e-6)
+    assert np.allclose(emb[:, :1], np.exp(ma[:, :1] - mb[:, :1]), rtol=2e-6)
+    whole = np.concatenate([ya * emb[:, :1], yb], axis=1)
+    assert np.allclose(whole, np.exp(x - gmax[:, :1]), rtol=4e-6, atol=1e-7)
+    # half data with float statistics: the same step on the rounded input
+    xh = x.astype(np.float16)
+    _, sh, mh, _ = orc.softmax_flash_v2(xh.view(np.uint16), orc.F16, orc.F32, brc=True)
+    xf = xh.astype(np.float32)
+    assert (mh[:, 0] == xf.max(axis=1)).all()
+    assert np.allclose(sh[:, 0], np.exp(xf - xf.max(axis=1, keepdims=True)).sum(axis=1), rtol=2e-3)
+
+
+def test_quant_policies_reduce_to_the_pinned_forms(golden_dir):
+    """The PER_TOKEN / PER_GROUP policies have no generator in the reference; they are tied to the forms that have one.
+    AscendQuant: a PER_TOKEN scale that is the same for every row is the per-tensor form (pinned on the quant example);
+    PER_GROUP with one group per row is PER_TOKEN; PER_GROUP along rows (kDim 0) with one group over all rows is the
+    per-channel form.  AscendDequant: PER_GROUP along rows with one group is the per-channel form pinned on the dequant
+    example; PER_TOKEN is that form on the transposed matrix."""
+    rng = np.random.default_rng(77)
+    m, n = 24, 128
+    src = (rng.standard_normal((m, n)) * 40).astype(np.float16)
+    bits = src.view(np.uint16)
+    scale, offset = np.float16(1.75), np.float16(-3.5)
+    per_tensor = orc.quant_per_tensor(bits, orc.F16, float(scale), float(offset))
+    tok_scale = np.full(m, scale, np.float16).view(np.uint16)
+    tok_off = np.full(m, offset, np.float16).view(np.uint16)
+    per_token = orc.quant_policy(bits, tok_scale, orc.F16, orc.F16, orc.S8, 2, offset=tok_off, has_offset=True)
+    assert (per_token.view(np.int8) == per_tensor).all()
+    per_token_scalar_off = orc.quant_policy(bits, tok_scale, orc.F16, orc.F16, orc.S8, 2, offset_scalar=float(offset), has_offset=True)
+    assert (per_token_scalar_off.view(np.int8) == per_tensor).all()
+    # a different scale per row, fp32 scales; one group per row of PER_GROUP must give the same bytes
+    s_row = rng.uniform(0.5, 3.0, m).astype(np.float32)
+    for dst in (orc.S8, orc.FP8_E4M3, orc.FP8_E5M2):
+        a = orc.quant_policy(bits, s_row, orc.F16, orc.F32, dst, 2)
+        b = orc.quant_policy(bits, s_row.reshape(m, 1), orc.F16, orc.F32, dst, 3, k_dim=1, group_size=n)
+        assert (a == b).all()
+    # kDim 0, one group over all rows: a scale per column = the per-channel form
+    s_col = rng.uniform(0.5, 3.0, n).astype(np.float16)
+    per_channel = orc.quant_per_channel(bits, orc.F16, s_col.view(np.uint16), 0.0)
+    per_group0 = orc.quant_policy(bits, s_col.view(np.uint16).reshape(1, n), orc.F16, orc.F16, orc.S8, 3, k_dim=0, group_size=32)
+    assert (per_group0[:32].view(np.int8) == per_channel[:32]).all()
+    # AscendDequant on the dequant example's data
+    g = load(golden_dir, "dequant.npz")
+    acc, sc = g["src"], g["scale"]
+    rows = acc.shape[0]
+    gs = (rows + 31) // 32 * 32
+    pinned = orc.dequant(acc, sc, orc.F32, orc.F32)
+    assert np.allclose(pinned, g["golden"], rtol=1e-6)
+    grp = orc.dequant_policy(acc, sc.reshape(1, -1), orc.F32, orc.F32, 1, k_dim=0, group_size=gs)
+    assert (grp.view(np.uint32) == pinned.view(np.uint32)).all()
+    tok = orc.dequant_policy(np.ascontiguousarray(acc.T), sc, orc.F32, orc.F32, 0)
+    assert (tok.T.view(np.uint32) == pinned.view(np.uint32)).all()
+    for dst in (orc.F16, orc.BF16):
+        a = orc.dequant_policy(acc, sc.reshape(1, -1), orc.F32, dst, 1, k_dim=0, group_size=gs)
+        assert (a == orc.dequant(acc, sc, dst, orc.F32)).all()
