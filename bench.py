@@ -8,8 +8,23 @@ int32 accumulation, fused bf16(acc * ch_scale[n] * tok_scale[m]) epilogue), shar
 across ranks with no communication; `value` is the whole-job rate (all ranks' operations divided
 by the slowest rank's device time, CUDA events on the launching stream).
 
-Rank 0 prints ONE JSON line.  At N=1 it also carries, under "others", the same measurement for
-the other baseline configurations (grouped A8W8, MXFP4, SoftMax+AscendQuant, fp16 Matmul).
+Rank 0 prints ONE JSON line.  Under "others" it carries the same measurement for the other baseline
+configurations: at N=1 grouped A8W8, MXFP4, SoftMax+AscendQuant (and its 64 x rows companion), the fp16
+Matmul and the reference's published fp16 8192^3 shape; at N>1 the other two sharded configurations
+(grouped A8W8 by expert group, MXFP4 by N-slab).  `--all` adds the kernels that lie outside the baseline
+configurations.  The last key, "summary", repeats workload / value / fraction of every configuration in
+a few characters each.
+
+Timing: the K steps are captured into one CUDA graph; the graph is replayed R >= 10 times (about 0.4 s
+in total), every replay bracketed by a barrier and a synchronisation on both sides and timed with CUDA
+events on the launching stream, maximum over ranks.  `ms_per_step` and `value` come from the median
+replay, `ms_per_step_range` gives the fastest and slowest one.  SM clocks are sampled only while these
+replays run.  Every rank rotates through enough buffer sets that their total size is at least twice the
+L2 capacity, so no step finds its operands in cache.  Because the timed region is a long back-to-back
+sequence under the board's power cap, `roofline.peak` of the tensor-bound kernels is the SUSTAINED
+measured cuBLAS figure (scaled by the hardware's rate ratio for int8 / fp4); `roofline.frac_of_burst_peak`
+gives the same rate against the burst figure, and `roofline.best_replay` the fastest replay (normally the
+first one, before the cap pulls the clock down) against the burst figure, which is itself a best-of-ten.
 
 `--impl reference` times the CPU restatement of the reference arithmetic (oracle/, OpenMP, all host
 threads) on a bounded row sample of the same workload; the reference's own CPU-debug executable
@@ -30,6 +45,17 @@ for _p in (os.path.join(ROOT, "asc-devkit_clone_b200"), os.path.join(ROOT, "orac
         sys.path.insert(0, _p)
 
 L2_BYTES = 126 * 1024 * 1024
+
+
+def cold_sets(bytes_per_set):
+    """Number of rotating buffer sets whose total size is at least twice the L2 capacity (at least two)."""
+    return max(2, -(-2 * L2_BYTES // max(int(bytes_per_set), 1)))
+
+
+def cache_label(sets, bytes_per_set):
+    total = sets * bytes_per_set
+    rel = ">= 2 x L2" if total >= 2 * L2_BYTES else ("> L2" if total > L2_BYTES else "fits L2: warm")
+    return f"{sets} rotating buffer sets ({total // 2**20} MiB {rel} of {L2_BYTES // 2**20} MiB)"
 
 
 def measured_peaks():
@@ -99,8 +125,8 @@ class Workload:
     scaling = "strong"
     kernels_per_step = 1
     published = None  # (value, note) of a like-for-like number the reference publishes (other hardware)
-    # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, per launch, from the ncu capture summarised in
-    # profiles/ (1 GPU, whole configuration); None where no capture exists
+    # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, per launch, from one ncu capture of the whole
+    # configuration on 1 GPU; None where no capture exists
     traffic_1gpu = None
 
     def units_total(self):       # algorithmic operations (or bytes) of the whole job per step
@@ -123,7 +149,7 @@ class A8W8(Workload):
     name = "a8w8_gemm_4096x4096x11008_dequant_bf16"
     metric, unit, dtype = "quant-GEMM throughput (int8, fused per-token x per-channel dequant)", "TOPS", "s8"
     M, K, N = 4096, 4096, 11008
-    traffic_1gpu = 62.05e6 + 48.92e6   # profiles/gemm_tc_pair_kernel_int8_a8w8_4096x4096x11008.md
+    traffic_1gpu = 62.05e6 + 48.92e6   # ncu: dram__bytes_read.sum + dram__bytes_write.sum of gemm_tc_pair_kernel<int8>
 
     def __init__(self, ab, rank, world, sets):
         self.ab, self.rank, self.world = ab, rank, world
@@ -136,13 +162,13 @@ class A8W8(Workload):
         rng_b = np.random.default_rng(0xA5C00002 + 1000 + rank)   # each rank draws its own B slab
         self.b_h = rng_b.integers(-127, 128, (self.n_loc, self.K)).astype(np.int8)
         self.ch_h = ch[rank * self.n_loc:(rank + 1) * self.n_loc].copy()
-        self.sets = sets
+        self.sets = sets = cold_sets(self.bytes_rank())
         self.a = [ab.to_dev(self.a_h) for _ in range(sets)]
         self.b = [ab.to_dev(self.b_h) for _ in range(sets)]
         self.c = [ab.empty((self.M, self.n_loc), np.uint16) for _ in range(sets)]
         self.tok, self.ch = ab.to_dev(self.tok_h), ab.to_dev(self.ch_h)
         self.config = {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "shard": f"N-slab x{world}",
-                       "cache": f"{sets} rotating buffer sets ({sets * self.bytes_rank() // 2**20} MiB > L2)"}
+                       "cache": cache_label(sets, self.bytes_rank())}
         self.pin = None
 
     def units_total(self):
@@ -192,7 +218,7 @@ class Grouped(Workload):
     metric, unit, dtype = "grouped quant-GEMM throughput (int8, fused dequant)", "TOPS", "s8"
     G, MTOT, K, N = 64, 32768, 7168, 2048
     OUT, ACT = "BF16", 0
-    traffic_1gpu = 1.2107e9 + 0.1229e9   # profiles/gemm_tc_kernel_int8_grouped_64groups_M32768_K7168_N2048.md
+    traffic_1gpu = 1.2542e9 + 0.1257e9   # ncu: dram__bytes_read.sum + dram__bytes_write.sum of gemm_tc_pair_kernel<int8>, grouped
 
     def counts(self):
         return dirichlet_counts(self.G, self.MTOT, 0xA5C00003)
@@ -209,14 +235,15 @@ class Grouped(Workload):
         self.w_h = rng.integers(-127, 128, (self.g_loc, self.N, self.K), dtype=np.int8)
         self.tok_h = rng.uniform(1e-3, 1e-2, max(self.m_loc, 1)).astype(np.float32)
         self.ch_h = rng.uniform(1e-3, 1e-2, (self.g_loc, self.N)).astype(np.float32)
-        self.sets = sets
+        # every pass streams this rank's weights, rows and outputs once: all of them rotate
+        per_set = self.x_h.nbytes + self.w_h.nbytes + 2 * max(self.m_loc, 1) * self.N
+        self.sets = sets = cold_sets(per_set)
         self.x = [ab.to_dev(self.x_h) for _ in range(sets)]
-        self.w = [ab.to_dev(self.w_h) for _ in range(1)]           # 0.94 GB of weights already exceed L2
+        self.w = [ab.to_dev(self.w_h) for _ in range(sets)]
         self.c = [ab.empty((max(self.m_loc, 1), self.N), np.uint16) for _ in range(sets)]
         self.tok, self.ch, self.counts_d = ab.to_dev(self.tok_h), ab.to_dev(self.ch_h), ab.to_dev(self.counts_h)
         self.config = {"workload": self.name, "groups": self.G, "rows": self.MTOT, "K": self.K, "N": self.N,
-                       "shard": f"groups x{world} (greedy by rows)", "rows_this_rank": self.m_loc,
-                       "cache": f"weights of one pass ({self.w_h.nbytes // 2**20} MiB on this rank)" + ("" if self.w_h.nbytes > L2_BYTES else ", may stay in L2")}
+                       "shard": f"groups x{world} (greedy by rows)", "rows_this_rank": self.m_loc, "cache": cache_label(sets, per_set)}
 
     def units_total(self):
         return 2.0 * self.MTOT * self.K * self.N
@@ -227,9 +254,21 @@ class Grouped(Workload):
     def peak(self, peaks):
         return 2.0 * peaks["bf16_tflops"], "TOPS", "2 x measured bf16 cuBLAS burst"
 
+    def extra_roofline(self, ms_per_step, peaks):
+        """The configuration's own bound: every group reads its K x N weights from HBM once whatever its row count, so a group
+        of fewer than about 210 rows (2 x rows op/B below the ridge) is bound by that read, the others by the tensor
+        cores: sum over this rank's groups of max(compute time at the sustained int8 rate, bytes / measured copy bandwidth)."""
+        c = self.counts_h.astype(np.float64)
+        tensor = 2.0 * (peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]) * 1e12
+        comp = 2.0 * c * self.K * self.N / tensor
+        mem = ((c > 0) * float(self.K * self.N) + c * (self.K + 2 * self.N)) / (peaks["hbm_gbs"] * 1e9)
+        bound_ms = float(np.maximum(comp, mem).sum() * 1e3)
+        return {"per_group_bound_ms": round(bound_ms, 4), "frac_of_per_group_bound": round(bound_ms / ms_per_step, 4),
+                "groups_bound_by_weight_read": int((mem > comp).sum())}
+
     def step(self, i, stream=None):
         ab, s = self.ab, i % self.sets
-        ab.check(ab.gemm(ab.KIND_S8, self.m_loc, self.N, self.K, self.x[s], self.w[0], self.c[s], getattr(ab, self.OUT),
+        ab.check(ab.gemm(ab.KIND_S8, self.m_loc, self.N, self.K, self.x[s], self.w[s], self.c[s], getattr(ab, self.OUT),
                          epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, trans_b=True, tok=self.tok, ch=self.ch, group_counts=self.counts_d,
                          groups=self.g_loc, act=self.ACT, stream=stream))
 
@@ -241,7 +280,7 @@ class Grouped(Workload):
 
     def e2e_step(self, i, stream):
         s = i % self.sets
-        self.pin.h2d([self.x[s], self.w[0], self.tok, self.ch, self.counts_d], stream)
+        self.pin.h2d([self.x[s], self.w[s], self.tok, self.ch, self.counts_d], stream)
         self.step(i, stream)
         self.pin.d2h(self.c[s], stream)
 
@@ -271,8 +310,8 @@ class MXFP4(Workload):
     name = "mxfp4_gemm_8192x8192x8192_requant_int8_bf16"
     metric, unit, dtype = "quant-GEMM throughput (MXFP4 e2m1 x ue8m0, int8 requant + bf16 out)", "TFLOPS", "fp4_e2m1"
     M = K = N = 8192
-    kernels_per_step = 3  # two scale re-tiling launches + the GEMM
-    traffic_1gpu = 95.2e6 + 168.0e6    # profiles/gemm_tc_pair_kernel_mxfp4_8192x8192x8192.md
+    kernels_per_step = 2  # re-tiling of A's scales + the GEMM (the weights' scales are prepacked once, outside the timed region)
+    traffic_1gpu = 95.2e6 + 168.0e6    # ncu: dram__bytes_read.sum + dram__bytes_write.sum of gemm_tc_pair_kernel<mxf4>
     published = (1614.0, "Ascend 950PR basic-API MXFP4 8192^3, bf16 out; the reference's published figure")
 
     def __init__(self, ab, rank, world, sets):
@@ -286,14 +325,17 @@ class MXFP4(Workload):
         # accumulators ~ N(0, K * E[a^2] E[b^2]); quantised unit normals keep E[x^2] ~ 1 -> sigma ~ sqrt(K)
         scales = (rng.uniform(0.5, 2.0, self.N) * 40.0 / np.sqrt(self.K)).astype(np.float32)
         self.q_h = quant_params(scales[rank * self.n_loc:(rank + 1) * self.n_loc])
-        self.sets = sets
+        per_set = self.a_h.nbytes + self.b_h.nbytes + 3 * self.M * self.n_loc
+        self.sets = sets = cold_sets(per_set)
         self.a = [ab.to_dev(self.a_h) for _ in range(sets)]
         self.b = [ab.to_dev(self.b_h) for _ in range(sets)]
         self.sa, self.sb, self.q = ab.to_dev(self.sa_h), ab.to_dev(self.sb_h), ab.to_dev(self.q_h)
+        # the weights' scale factors are static: re-tiled once here; a step re-tiles only A's
+        self.sb_packed = ab.mx_scale_prepack(self.sb, self.n_loc, self.K) if self.sb is not None else None
         self.c = [ab.empty((self.M, self.n_loc), np.int8) for _ in range(sets)]
         self.c2 = [ab.empty((self.M, self.n_loc), np.uint16) for _ in range(sets)]
         self.config = {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "shard": f"N-slab x{world}",
-                       "cache": f"{sets} rotating buffer sets"}
+                       "cache": cache_label(sets, per_set), "scales": "B prepacked once (static weights), A re-tiled every step"}
 
     def units_total(self):
         return 2.0 * self.M * self.K * self.N
@@ -307,8 +349,8 @@ class MXFP4(Workload):
     def step(self, i, stream=None):
         ab, s = self.ab, i % self.sets
         ab.check(ab.gemm(ab.KIND_MXFP4, self.M, self.n_loc, self.K, self.a[s], self.b[s], self.c[s], ab.S8,
-                         epilogue=ab.EPI_FIXPIPE_QUANT, trans_b=True, scale_a=self.sa, scale_b=self.sb, quant=self.q,
-                         c2=self.c2[s], c2_dtype=ab.BF16, stream=stream))
+                         epilogue=ab.EPI_FIXPIPE_QUANT, trans_b=True, scale_a=self.sa, scale_b=self.sb_packed, quant=self.q,
+                         c2=self.c2[s], c2_dtype=ab.BF16, scale_flags=ab.SCALE_B_PREPACKED, stream=stream))
 
     def e2e_bytes(self):
         return (self.a_h.nbytes + self.b_h.nbytes + self.sa_h.nbytes + self.sb_h.nbytes + self.q_h.nbytes,
@@ -332,13 +374,20 @@ class MXFP4(Workload):
         return time.perf_counter() - t0, 2.0 * rows * self.K * self.n_loc, f"{rows} of {self.M} rows of A x all {self.n_loc} columns"
 
     def verify(self, orc):
+        """Stage-wise and bit exact: the fp32 accumulators of the same GEMM (same tiles, fp32 output) agree with the oracle within
+        the GEMM tolerance, and both timed outputs equal the oracle's output stage applied to those accumulators."""
+        ab = self.ab
+        d_acc = ab.empty((self.M, self.n_loc), np.float32)
+        ab.check(ab.gemm(ab.KIND_MXFP4, self.M, self.n_loc, self.K, self.a[0], self.b[0], d_acc, ab.F32, trans_b=True, scale_a=self.sa,
+                         scale_b=self.sb_packed, scale_flags=ab.SCALE_B_PREPACKED))
+        ab.sync()
+        acc_gpu = d_acc.download()[:16]
+        d_acc.free()
         acc = orc.gemm_mxf4(self.a_h[:16], self.sa_h[:16], self.b_h, self.sb_h, base_k=256)
-        q = self.c[0].download()[:16]
-        bf = self.c2[0].download()[:16]
-        ref_q = orc.fixpipe_qf322b8(acc, self.q_h)
-        d = np.abs(q.astype(np.int32) - ref_q.astype(np.int32))
-        ok_bf = np.allclose(orc.bf16_bits_to_f32(bf), acc, rtol=1e-2, atol=1e-3)
-        return bool(d.max() <= 1 and (d != 0).mean() < 1e-3 and ok_bf)
+        ok_acc = np.allclose(acc_gpu, acc, rtol=1e-2, atol=1e-3)
+        ok_q = (self.c[0].download()[:16] == orc.fixpipe_qf322b8(acc_gpu, self.q_h)).all()
+        ok_bf = (self.c2[0].download()[:16] == orc.cast_f32(acc_gpu, orc.BF16)).all()
+        return bool(ok_acc and ok_q and ok_bf)
 
 
 class SoftmaxQuant(Workload):
@@ -349,7 +398,7 @@ class SoftmaxQuant(Workload):
     scaling = "weak"  # rows are independent; every rank runs its own replica of the configuration
     M, K = 4096, 2048
     ROW_FACTOR = 1
-    traffic_1gpu = 16.8e6               # profiles/softmax_rows_kernel_fused_quant_4096x2048.md (outputs still in L2 at kernel end)
+    traffic_1gpu = 16.8e6               # ncu: dram bytes of softmax_rows_kernel (the outputs are still in L2 when the kernel ends)
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
@@ -358,14 +407,14 @@ class SoftmaxQuant(Workload):
         rng = np.random.default_rng(0xA5C00001 + rank)
         self.x_h = np.tile(f16_bits(rng.standard_normal((4096, self.K), dtype=np.float32) * 3.0), (self.ROW_FACTOR, 1))
         self.sc_h = f16_bits((127.0 / rng.uniform(0.5, 2.0, self.K)).astype(np.float32))
-        self.sets = sets = max(sets, 8) if self.ROW_FACTOR == 1 else 2  # 42 MB per set: rotate 8 sets so no step finds its input in L2
+        self.sets = sets = cold_sets(self.per_step_bytes())   # 42 MB per set at the baseline shape: 7 sets
         self.x = [ab.to_dev(self.x_h) for _ in range(sets)]
         self.y = [ab.empty((self.M, self.K), np.uint16) for _ in range(sets)]
         self.q = [ab.empty((self.M, self.K), np.int8) for _ in range(sets)]
         self.sm, self.mx = ab.empty((self.M,), np.float32), ab.empty((self.M,), np.float32)
         self.sc = ab.to_dev(self.sc_h)
         self.config = {"workload": self.name, "M": self.M, "K": self.K, "shard": f"replica per rank x{world}",
-                       "cache": f"{sets} rotating buffer sets ({sets * self.per_step_bytes() // 2**20} MiB > L2)"}
+                       "cache": cache_label(sets, self.per_step_bytes())}
 
     def per_step_bytes(self):
         return self.M * self.K * (2 + 2 + 1) + 8 * self.M + 2 * self.K  # X in, Y + Q + sum + max out, scale in
@@ -418,7 +467,7 @@ class SoftmaxQuantLarge(SoftmaxQuant):
     baseline shape lasts only a few microseconds, so launch ramp-up and tail dominate its bandwidth figure."""
     name = "softmax_ascendquant_262144x2048_fp16_int8"
     ROW_FACTOR = 64
-    traffic_1gpu = 1.0738e9 + 1.5580e9  # profiles/softmax_rows_kernel_fused_quant_262144x2048.md
+    traffic_1gpu = 1.0738e9 + 1.5580e9  # ncu: dram__bytes_read.sum + dram__bytes_write.sum of softmax_rows_kernel
 
 
 class FP16(Workload):
@@ -434,13 +483,14 @@ class FP16(Workload):
         self.a_h = f16_bits(rng.uniform(-1, 1, (self.M, self.K)).astype(np.float32))
         self.b_h = f16_bits(rng.uniform(-1, 1, (self.K, self.N)).astype(np.float32))
         self.bias_h = rng.uniform(-1, 1, self.N).astype(np.float32)
-        self.sets = sets = 48  # 3.7 MB per set: 48 sets = 176 MB > L2
+        self.sets = sets = cold_sets(self.a_h.nbytes + self.b_h.nbytes + 4 * self.M * self.N)  # 3.5 MiB per set: 72 sets
         self.a = [ab.to_dev(self.a_h) for _ in range(sets)]
         self.b = [ab.to_dev(self.b_h) for _ in range(sets)]
         self.c = [ab.empty((self.M, self.N), np.float32) for _ in range(sets)]
         self.bias = ab.to_dev(self.bias_h)
         self.config = {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "shard": f"replica per rank x{world}",
-                       "cache": f"{sets} rotating buffer sets (176 MiB > L2)", "note": "0.54 GFLOP: launch-latency bound"}
+                       "cache": cache_label(sets, self.a_h.nbytes + self.b_h.nbytes + 4 * self.M * self.N),
+                       "note": "0.54 GFLOP: launch-latency bound"}
 
     def units_total(self):
         return 2.0 * self.M * self.K * self.N * self.world
@@ -495,11 +545,12 @@ class FP16Large(Workload):
         rng = np.random.default_rng(0xA5C00005)
         self.a_h = f16_bits(rng.uniform(1, 10, (self.M, self.K)).astype(np.float32))      # the example draws U[1,10)
         self.b_h = f16_bits(np.random.default_rng(0xA5C00005 + 1000 + rank).uniform(1, 10, (self.n_loc, self.K)).astype(np.float32))
-        self.sets = sets
+        per_set = self.a_h.nbytes + self.b_h.nbytes + 2 * self.M * self.n_loc
+        self.sets = sets = cold_sets(per_set)
         self.a = [ab.to_dev(self.a_h) for _ in range(sets)]
         self.b = [ab.to_dev(self.b_h) for _ in range(sets)]
         self.c = [ab.empty((self.M, self.n_loc), np.uint16) for _ in range(sets)]
-        self.config = {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "shard": f"N-slab x{world}", "cache": f"{sets} rotating buffer sets"}
+        self.config = {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "shard": f"N-slab x{world}", "cache": cache_label(sets, per_set)}
 
     def units_total(self):
         return 2.0 * self.M * self.K * self.N
@@ -584,7 +635,7 @@ class QuantPerGroupFp4(RowOp):
     name = "ascendquant_per_group32_fp16_to_fp4_32768x8192"
     metric, dtype = "AscendQuant PER_GROUP (fp16 -> packed fp4 e2m1, fp32 scale per 32 columns) bandwidth", "f16"
     M, N, G = 32768, 8192, 32
-    traffic_1gpu = 570.5e6 + 120.6e6   # profiles/quant_policy_vec_kernel_per_group32_fp16_fp4_32768x8192.md
+    traffic_1gpu = 570.5e6 + 120.6e6   # ncu: dram__bytes_read.sum + dram__bytes_write.sum of the kernel
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
@@ -631,7 +682,7 @@ class SoftmaxFlashStep(RowOp):
     name = "softmaxflashv2_update_262144x2048_fp16"
     metric, dtype = "SoftmaxFlashV2 update step (fp16 data, fp32 statistics) bandwidth", "f16"
     M, K = 262144, 2048
-    traffic_1gpu = 1.0906e9 + 1.0412e9   # profiles/softmax_flash_rows_kernel_update_262144x2048_fp16.md
+    traffic_1gpu = 1.0906e9 + 1.0412e9   # ncu: dram__bytes_read.sum + dram__bytes_write.sum of the kernel
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
@@ -684,7 +735,7 @@ class SoftmaxGradStep(RowOp):
     name = "softmaxgrad_131072x2048_fp16"
     metric, dtype = "SoftmaxGrad (fp16 grad and softmax output in, fp16 out) bandwidth", "f16"
     M, K = 131072, 2048
-    traffic_1gpu = 1.0738e9 + 0.4822e9   # profiles/softmax_grad_rows_kernel_131072x2048_fp16.md
+    traffic_1gpu = 1.0738e9 + 0.4822e9   # ncu: dram__bytes_read.sum + dram__bytes_write.sum of the kernel
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
@@ -733,7 +784,7 @@ class AntiQuantPerChannel(RowOp):
     name = "ascendantiquant_per_channel_int8_to_fp16_131072x2048"
     metric, dtype = "AscendAntiQuant per channel (int8 -> fp16, fp16 scale and offset per column) bandwidth", "f16"
     M, N = 131072, 2048
-    traffic_1gpu = 268.9e6 + 477.8e6   # profiles/antiquant_i8_columns_kernel_int8_fp16_131072x2048.md
+    traffic_1gpu = 268.9e6 + 477.8e6   # ncu: dram__bytes_read.sum + dram__bytes_write.sum of the kernel
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
@@ -780,7 +831,7 @@ class NzUnpack(RowOp):
     name = "nz_weight_unpack_int8_16x7168x2048"
     metric, dtype = "fractal NZ -> K-major weight unpack bandwidth", "u8"
     G, K, N = 16, 7168, 2048
-    traffic_1gpu = 234.9e6 + 181.7e6   # profiles/nz_unpack_kernel_int8_16x7168x2048.md
+    traffic_1gpu = 234.9e6 + 181.7e6   # ncu: dram__bytes_read.sum + dram__bytes_write.sum of the kernel
 
     def __init__(self, ab, rank, world, sets):
         self.ab, self.rank, self.world = ab, rank, world
@@ -910,60 +961,82 @@ class Comm:
             self.dist.destroy_process_group()
 
 
-def time_steps(ab, wl, comm, steps, warmup, stream, e2e=False, stream2=None):
-    """Times exactly `steps` steps between a barrier + synchronize on both sides; returns the max over ranks (ms).
-    The device-resident measurement replays the steps from one CUDA graph, so that the host's launch
-    cost (a Python ctypes call per step) does not sit between kernels that last a few microseconds.
-    The end-to-end measurement alternates two streams (and two buffer sets), so that the copy-out of one
-    step overlaps the copy-in of the next on the full-duplex host link; it is timed on the first stream,
-    which waits for the second before the closing event."""
+def time_e2e(ab, wl, comm, steps, warmup, stream, stream2):
+    """End to end: every step copies its inputs from pinned host memory, runs the call and copies the outputs back.  Two
+    streams (and two pinned landing buffers) alternate, so that the copy-out of one step overlaps the copy-in of the next on
+    the full-duplex host link; timed on the first stream, which waits for the second before the closing event.  Returns the
+    maximum over ranks (ms) for exactly `steps` steps."""
     import ctypes as C
-    streams = [stream, stream2 if (e2e and stream2) else stream]
+    streams = [stream, stream2]
 
     def fn(i):
-        if e2e:
-            wl.pin.slot = i % 2
-            wl.e2e_step(i, streams[i % 2])
-        else:
-            wl.step(i, stream)
+        wl.pin.slot = i % 2
+        wl.e2e_step(i, streams[i % 2])
 
     for i in range(warmup):
         fn(i)
     ab.sync(stream)
-    if streams[1] is not stream:
-        ab.sync(streams[1])
-    graph = None
-    if not e2e:
-        graph = ab.Graph(stream, lambda: [fn(warmup + i) for i in range(steps)])
-        graph.launch()          # one untimed replay: graph upload
-        ab.sync(stream)
+    ab.sync(stream2)
     comm.barrier()
     timer = ab.Timer(stream)
     timer.start()
-    if graph:
-        graph.launch()
-    else:
-        if streams[1] is not stream:   # the second stream starts after the opening event
-            ab.check(ab.lib().ascb200_stream_wait_event(streams[1], timer.e0))
-        for i in range(steps):
-            fn(warmup + i)
-        if streams[1] is not stream:
-            ev = C.c_void_p()
-            ab.check(ab.lib().ascb200_event_create(C.byref(ev)))
-            ab.check(ab.lib().ascb200_event_record(ev, streams[1]))
-            ab.check(ab.lib().ascb200_stream_wait_event(stream, ev))
+    ab.check(ab.lib().ascb200_stream_wait_event(stream2, timer.e0))   # the second stream starts after the opening event
+    for i in range(steps):
+        fn(warmup + i)
+    ev = C.c_void_p()
+    ab.check(ab.lib().ascb200_event_create(C.byref(ev)))
+    ab.check(ab.lib().ascb200_event_record(ev, stream2))
+    ab.check(ab.lib().ascb200_stream_wait_event(stream, ev))
     ms = timer.stop_ms()
     ab.sync(stream)
-    if streams[1] is not stream:
-        ab.sync(streams[1])
+    ab.sync(stream2)
     comm.barrier()
-    if graph:
-        graph.destroy()
     return comm.max(ms)
+
+
+def time_resident(ab, wl, comm, steps, warmup, stream, clock_index, budget_s=0.4):
+    """Device-resident timing.  The `steps` steps are captured into one CUDA graph (so that the host's per-call cost does not
+    sit between kernels that last microseconds); after the warm-up steps and one untimed replay the graph is replayed R >= 10
+    times (R chosen so that the replays last about `budget_s` in total), each replay bracketed by barrier + synchronise and
+    timed with CUDA events on the launching stream, maximum over ranks.  Clocks are sampled only while the replays run.
+    Returns (per-replay times in ms, clock summary)."""
+    for i in range(warmup):
+        wl.step(i, stream)
+    ab.sync(stream)
+    graph = ab.Graph(stream, lambda: [wl.step(warmup + i, stream) for i in range(steps)])
+    timer = ab.Timer(stream)
+    timer.start()
+    graph.launch()                       # untimed: graph upload, and an estimate of one replay
+    est_ms = max(timer.stop_ms(), 1e-3)
+    ab.sync(stream)
+    local_r = int(min(200, max(10, -(-budget_s * 1e3 // est_ms))))
+    repeats = int(comm.max(float(local_r)))   # the same count on every rank
+    sampler = ClockSampler(clock_index)
+    sampler.start()
+    times = []
+    for _ in range(repeats):
+        comm.barrier()
+        timer.start()
+        graph.launch()
+        ms = timer.stop_ms()             # synchronises on the closing event
+        ab.sync(stream)
+        times.append(comm.max(ms))
+    clocks = sampler.stop()
+    comm.barrier()
+    graph.destroy()
+    return times, clocks
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 def cpu_baseline(wl, target_s):
     import oracle as orc
+    orc.set_num_threads(host_threads())   # a launcher may have exported OMP_NUM_THREADS=1
     rows = 2
     t, units, what = wl.cpu_sample(orc, rows)
     # grow the sample until it takes target_s (bounded), keeping the last measurement
@@ -977,8 +1050,9 @@ def cpu_baseline(wl, target_s):
 
 
 def measure(ab, cls, comm, rank, world, args, peaks, with_cpu, clock_index):
-    stream_p = __import__("ctypes").c_void_p()
-    ab.check(ab.lib().ascb200_stream_create(__import__("ctypes").byref(stream_p)))
+    import ctypes as C
+    stream_p = C.c_void_p()
+    ab.check(ab.lib().ascb200_stream_create(C.byref(stream_p)))
     stream = stream_p.value
     wl = cls(ab, rank, world, sets=2)
     # untimed check that the configuration computes the right thing
@@ -987,18 +1061,9 @@ def measure(ab, cls, comm, rank, world, args, peaks, with_cpu, clock_index):
     import oracle as orc
     verified = wl.verify(orc)
 
-    sampler = ClockSampler(clock_index)
-    # keep the GPU busy for a moment so the clock samples describe the loaded state
-    t_end = time.time() + 0.3
-    sampler.start()
-    i = 0
-    while time.time() < t_end:
-        wl.step(i, stream)
-        i += 1
-        if i % 16 == 0:
-            ab.sync(stream)
-    ms = time_steps(ab, wl, comm, args.steps, max(args.warmup, 3), stream)
-    clocks = sampler.stop()
+    warmup = max(args.warmup, 3)
+    times, clocks = time_resident(ab, wl, comm, args.steps, warmup, stream, clock_index)
+    ms = float(np.median(times))
 
     e2e_steps = max(3, min(args.steps, 20))
     bi, bo = wl.e2e_bytes()
@@ -1006,28 +1071,40 @@ def measure(ab, cls, comm, rank, world, args, peaks, with_cpu, clock_index):
         ms_e2e, with_cpu = float("nan"), False
     else:
         wl.e2e_setup()
-        stream2_p = __import__("ctypes").c_void_p()
-        ab.check(ab.lib().ascb200_stream_create(__import__("ctypes").byref(stream2_p)))
-        ms_e2e = time_steps(ab, wl, comm, e2e_steps, 4, stream, e2e=True, stream2=stream2_p.value)
+        stream2_p = C.c_void_p()
+        ab.check(ab.lib().ascb200_stream_create(C.byref(stream2_p)))
+        ms_e2e = time_e2e(ab, wl, comm, e2e_steps, 4, stream, stream2_p.value)
         ab.lib().ascb200_stream_destroy(stream2_p.value)
 
     per_step_s = ms / 1e3 / args.steps
     value = wl.units_total() / per_step_s / wl.unit_scale
     achieved = wl.units_rank() / per_step_s / wl.unit_scale
-    peak, punit, pnote = wl.peak(peaks)
-    # The timed region is a long back-to-back replay under the power cap: for tensor-bound kernels the same fraction against the
-    # SUSTAINED cuBLAS figure (seconds-long loop, same cap) is reported beside the one against the burst figure.
-    frac_sustained = None
-    if wl.bound == "tensor" and peaks.get("bf16_tflops_sustained"):
-        frac_sustained = round(achieved / (peak * peaks["bf16_tflops_sustained"] / peaks["bf16_tflops"]), 4)
+    peak, punit, pnote = wl.peak(peaks)              # the burst figure
+    roof = {"bound": wl.bound, "achieved": round(achieved, 3), "unit": punit, "traffic": (wl.traffic_1gpu if world == 1 else None),
+            "algorithmic": wl.units_rank() if wl.bound == "hbm" else getattr(wl, "algorithmic_bytes", None)}
+    sustained = peaks.get("bf16_tflops_sustained")
+    if wl.bound == "tensor" and sustained:
+        # the replays are a long back-to-back sequence under the power cap: the sustained cuBLAS figure is the denominator
+        peak_s = peak * sustained / peaks["bf16_tflops"]
+        roof.update(peak=round(peak_s, 1), frac=round(achieved / peak_s, 4), frac_of_burst_peak=round(achieved / peak, 4),
+                    peak_source=f"{peaks['source']}, sustained: {pnote.replace('burst', 'sustained loop')}")
+    else:
+        roof.update(peak=round(peak, 1), frac=round(achieved / peak, 4), peak_source=f"{peaks['source']}: {pnote}")
+    # the fastest replay (normally the first, before the power cap pulls the clock down) against the burst figure, which is
+    # itself a best-of-ten
+    best_rate = wl.units_rank() / (min(times) / 1e3 / args.steps) / wl.unit_scale
+    roof["best_replay"] = {"ms_per_step": round(min(times) / args.steps, 6), "achieved": round(best_rate, 3), "frac_of_burst_peak": round(best_rate / peak, 4)}
+    extra = wl.extra_roofline(ms / args.steps, peaks) if hasattr(wl, "extra_roofline") else None
+    if extra:
+        roof.update(extra)
+    med_mhz = clocks.get("sm_mhz")
     line = {
         "metric": wl.metric, "value": round(value, 3), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 6), "higher_is_better": True, "scaling": wl.scaling,
+        "warmup": warmup, "ms_per_step": round(ms / args.steps, 6), "higher_is_better": True, "scaling": wl.scaling,
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
-        "roofline": {"bound": wl.bound, "achieved": round(achieved, 3), "peak": round(peak, 1), "unit": punit,
-                     "frac": round(achieved / peak, 4), "traffic": (wl.traffic_1gpu if world == 1 else None),
-                     "algorithmic": wl.units_rank() if wl.bound == "hbm" else getattr(wl, "algorithmic_bytes", None),
-                     "peak_source": f"{peaks['source']}: {pnote}", "frac_of_sustained_peak": frac_sustained},
+        "repeats": len(times), "ms_per_step_range": [round(min(times) / args.steps, 6), round(max(times) / args.steps, 6)],
+        "ms_x_sm_mhz": round(ms / args.steps * med_mhz, 3) if med_mhz else None,
+        "roofline": roof,
         "e2e": {"value": round(wl.units_total() / (ms_e2e / 1e3 / e2e_steps) / wl.unit_scale, 4), "unit": wl.unit, "h2d_bytes_per_step": int(bi),
                 "d2h_bytes_per_step": int(bo), "steps": e2e_steps},
         "gpu_launches": args.steps * wl.kernels_per_step, "clocks": clocks, "parity_spot_check": verified,
@@ -1046,13 +1123,16 @@ def measure(ab, cls, comm, rank, world, args, peaks, with_cpu, clock_index):
 
 
 def run_reference_arm(args, rank, world, out):
-    """CPU restatement of the reference arithmetic, all host threads, bounded sample per step."""
+    """CPU restatement of the reference arithmetic, all host threads, bounded sample per step.  Rank 0 alone runs it; the
+    workload object is built for rank 0 of `world` ranks, so its configuration labels equal the ones of the GPU arm."""
     if rank != 0:
         return
     import oracle as orc
+    orc.set_num_threads(host_threads())   # torchrun exports OMP_NUM_THREADS=1
 
     class HostOnly:
         """Stands in for the device binding: the reference arm allocates nothing on a GPU."""
+        SCALE_B_PREPACKED = 2
 
         @staticmethod
         def to_dev(a):
@@ -1062,7 +1142,11 @@ def run_reference_arm(args, rank, world, out):
         def empty(shape, dtype):
             return None
 
-    wl = WORKLOADS[args.workload](HostOnly, 0, 1, sets=1)
+        @staticmethod
+        def mx_scale_prepack(*a, **k):
+            return None
+
+    wl = WORKLOADS[args.workload](HostOnly, 0, world, sets=1)
     rows = 2
     t, units, what = wl.cpu_sample(orc, rows)
     while t < 0.7 and rows < 4096 and "whole problem" not in what:   # ~2 s per step
@@ -1078,7 +1162,7 @@ def run_reference_arm(args, rank, world, out):
     value = tot_u / tot_t / wl.unit_scale
     line = {
         "impl": "reference", "metric": wl.metric, "value": round(value, 6), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(tot_t / args.steps * 1e3, 3), "higher_is_better": True, "scaling": wl.scaling,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(tot_t / args.steps * 1e3, 3), "higher_is_better": True, "scaling": wl.scaling,
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config,
         "cpu_baseline": {"value": round(value, 6), "unit": wl.unit, "cores": orc.num_threads(), "kind": "port", "sample": what + " per step"},
         "e2e": {"value": round(value, 6), "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -1101,6 +1185,16 @@ class OneLineStdout:
         os.write(self.real, (text + "\n").encode())
 
 
+BASELINE_OTHERS_1GPU = ["grouped", "mxfp4", "softmax_quant", "softmax_quant_x64", "fp16", "fp16_8192", "grouped_ref_shape"]
+SHARDED = ["a8w8", "grouped", "mxfp4"]
+
+
+def summary_entry(o):
+    return {"workload": o["config"]["workload"], "value": o["value"], "unit": o["unit"], "ms_per_step": o["ms_per_step"],
+            "frac": o["roofline"]["frac"], "best_replay_frac_of_burst": o["roofline"]["best_replay"]["frac_of_burst_peak"], "e2e": o["e2e"]["value"],
+            "parity": o["parity_spot_check"]}
+
+
 def main():
     out = OneLineStdout()
     ap = argparse.ArgumentParser()
@@ -1109,7 +1203,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="a8w8", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ascb200", choices=["ascb200", "reference"])
-    ap.add_argument("--no-others", action="store_true", help="skip the other baseline configurations at N=1")
+    ap.add_argument("--no-others", action="store_true", help="skip the other baseline configurations")
+    ap.add_argument("--all", action="store_true", help="N=1: also measure the kernels outside the baseline configurations")
     ap.add_argument("--allgather", action="store_true",
                     help="N>1, N-slab workloads: also time the NCCL all-gather that gives every rank all C slabs ([rank][M][N/ranks])")
     ap.add_argument("--kernel-only", action="store_true", help="time the device-resident step only (no e2e, no CPU baseline): profiling runs")
@@ -1125,17 +1220,23 @@ def main():
     peaks = measured_peaks()
     line = measure(ab, WORKLOADS[args.workload], comm, rank, world, args, peaks, with_cpu=(world == 1 and rank == 0),
                    clock_index=local_rank)
-    if world == 1 and not args.no_others and not args.kernel_only:
+    if not args.no_others and not args.kernel_only:
+        if world == 1:
+            names = list(WORKLOADS) if args.all else BASELINE_OTHERS_1GPU
+        else:
+            names = SHARDED   # the sharded configurations: the scaling record then carries all three at every N
         others = []
-        for name, cls in WORKLOADS.items():
+        for name in names:
             if name == args.workload:
                 continue
             sub = argparse.Namespace(**vars(args))
             sub.steps = min(args.steps, 50)
-            o = measure(ab, cls, comm, rank, world, sub, peaks, with_cpu=True, clock_index=local_rank)
-            others.append({k: o[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "config", "roofline", "e2e", "cpu_baseline",
-                                             "clocks", "parity_spot_check", "gpu_launches", "vs_published_other_hw") if k in o})
+            o = measure(ab, WORKLOADS[name], comm, rank, world, sub, peaks, with_cpu=(world == 1), clock_index=local_rank)
+            others.append({k: o[k] for k in ("metric", "value", "unit", "n_gpus", "ms_per_step", "ms_per_step_range", "repeats", "ms_x_sm_mhz", "steps",
+                                             "config", "roofline", "e2e", "cpu_baseline", "clocks", "parity_spot_check", "gpu_launches",
+                                             "vs_published_other_hw") if k in o})
         line["others"] = others
+        line["summary"] = [summary_entry(line)] + [summary_entry(o) for o in others]
     comm.close()
     if rank == 0:
         out.emit(json.dumps(line))

@@ -634,6 +634,17 @@ ORC_API void orc_dequant(const int32_t* src, void* dst, int m, int n, int cal_co
         }
 }
 
+/* Sets the number of OpenMP threads of every later call (launchers such as torchrun export OMP_NUM_THREADS=1,
+ * which would silently turn the timed CPU baseline into a single-core run). */
+ORC_API void orc_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads(void)
 {
 #ifdef _OPENMP

@@ -248,6 +248,11 @@ def num_threads():
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n):
+    """OpenMP threads of every later call (overrides an OMP_NUM_THREADS the launcher exported)."""
+    lib().orc_set_num_threads(int(n))
+
+
 def f16_bits_to_f32(bits):
     return np.asarray(bits, np.uint16).view(np.float16).astype(np.float32)
 

@@ -311,6 +311,64 @@ def test_gemm_mxfp4_fp32(m, n, k):
     assert err.max() <= 1e-3 * np.abs(ref).max()  # every product is exact in fp32; only the summation differs
 
 
+@pytest.mark.parametrize("m,n,k", [(384, 512, 1024), (2048, 2560, 512), (100, 200, 192)])
+def test_gemm_mxfp4_prepacked_scales(m, n, k):
+    """Scale tensors re-tiled once with ascb200_mx_scale_prepack (the weights' scales do not change between calls) give the
+    same bytes as scales re-tiled inside the call, for either operand and for both."""
+    ab = dev()
+    rng, a, sa, b, sb = _mx_case(m, n, k, 5 * m + n)
+    d_a, d_b, d_sa, d_sb = ab.to_dev(a), ab.to_dev(b), ab.to_dev(sa), ab.to_dev(sb)
+    pa, pb = ab.mx_scale_prepack(d_sa, m, k), ab.mx_scale_prepack(d_sb, n, k)
+    assert pa.nbytes == ab.lib().ascb200_mx_scale_prepacked_bytes(m, k) == ((m + 127) // 128 + 2) * 2 * ((k + 255) // 256) * 512
+    outs = []
+    for flags, s_a, s_b in ((0, d_sa, d_sb), (ab.SCALE_B_PREPACKED, d_sa, pb), (ab.SCALE_A_PREPACKED, pa, d_sb),
+                            (ab.SCALE_A_PREPACKED | ab.SCALE_B_PREPACKED, pa, pb)):
+        d_c = ab.empty((m, n), np.float32)
+        d_c.fill(0xFF)
+        ab.check(ab.gemm(ab.KIND_MXFP4, m, n, k, d_a, d_b, d_c, ab.F32, trans_b=True, scale_a=s_a, scale_b=s_b, scale_flags=flags))
+        ab.sync()
+        outs.append(d_c.download().view(np.uint32))
+    for o in outs[1:]:
+        assert (o == outs[0]).all()
+    ref = orc.gemm_mxf4(a, sa, b, sb, base_k=256)
+    assert np.allclose(outs[0].view(np.float32), ref, rtol=RTOL, atol=ATOL)
+    assert ab.gemm(ab.KIND_MXFP4, m, n, k, d_a, d_b, d_c, ab.F32, trans_b=True, scale_a=d_sa, scale_b=d_sb, scale_flags=4) == ab.EINVAL
+
+
+def test_gemm_mxfp4_two_streams_with_different_scales():
+    """Two MXFP4 calls with different scale tensors, issued on two streams without any ordering between them, many times
+    over: the re-tiled scales of one call must never be read by the other (each stream has its own scratch)."""
+    import ctypes as C
+    ab = dev()
+    m, n, k = 1024, 1024, 2048
+    rng, a, sa, b, sb = _mx_case(m, n, k, 99)
+    sa2 = (sa.astype(np.int32) + rng.integers(-3, 4, sa.shape)).clip(1, 250).astype(np.uint8)
+    sb2 = (sb.astype(np.int32) + rng.integers(-3, 4, sb.shape)).clip(1, 250).astype(np.uint8)
+    d_a, d_b = ab.to_dev(a), ab.to_dev(b)
+    sets = [(ab.to_dev(sa), ab.to_dev(sb), ab.empty((m, n), np.float32)), (ab.to_dev(sa2), ab.to_dev(sb2), ab.empty((m, n), np.float32))]
+    streams = []
+    for _ in range(2):
+        p = C.c_void_p()
+        ab.check(ab.lib().ascb200_stream_create(C.byref(p)))
+        streams.append(p.value)
+    refs = []
+    for (s_a, s_b, d_c) in sets:   # one call at a time gives the expected bytes of each
+        ab.check(ab.gemm(ab.KIND_MXFP4, m, n, k, d_a, d_b, d_c, ab.F32, trans_b=True, scale_a=s_a, scale_b=s_b))
+        ab.sync()
+        refs.append(d_c.download().view(np.uint32).copy())
+    assert (refs[0] != refs[1]).any()
+    for rep in range(20):
+        for i, (s_a, s_b, d_c) in enumerate(sets):
+            d_c.fill(0, streams[i])
+            ab.check(ab.gemm(ab.KIND_MXFP4, m, n, k, d_a, d_b, d_c, ab.F32, trans_b=True, scale_a=s_a, scale_b=s_b, stream=streams[i]))
+    for i in range(2):
+        ab.sync(streams[i])
+    for i, (_, _, d_c) in enumerate(sets):
+        assert (d_c.download().view(np.uint32) == refs[i]).all(), f"stream {i} read the other call's scales"
+    for sp in streams:
+        ab.lib().ascb200_stream_destroy(sp)
+
+
 def test_gemm_mxfp4_requant_and_bf16():
     """MXFP4 baseline epilogue: int8 via per-channel VQF322B8_PRE plus the bf16 cast of the same accumulators."""
     ab = dev()
