@@ -21,7 +21,7 @@ EXPORTS = [
     "ascb200_malloc", "ascb200_free", "ascb200_malloc_host", "ascb200_free_host", "ascb200_memcpy_h2d", "ascb200_memcpy_d2h",
     "ascb200_memset", "ascb200_stream_create", "ascb200_stream_destroy", "ascb200_stream_sync", "ascb200_event_create",
     "ascb200_event_destroy", "ascb200_event_record", "ascb200_stream_wait_event", "ascb200_event_elapsed_ms", "ascb200_gemm", "ascb200_grouped_gemm",
-    "ascb200_gemm_mxfp4_noalloc", "ascb200_noalloc_status", "ascb200_mx_scale_prepacked_bytes", "ascb200_mx_scale_prepack", "ascb200_graph_begin", "ascb200_graph_end", "ascb200_graph_launch", "ascb200_graph_destroy",
+    "ascb200_gemm_mxfp4_noalloc", "ascb200_noalloc_status", "ascb200_mx_scale_prepacked_bytes", "ascb200_mx_scale_prepack", "ascb200_shard_nslab", "ascb200_shard_groups_lpt", "ascb200_comm_unique_id", "ascb200_comm_init", "ascb200_comm_init_all", "ascb200_comm_destroy", "ascb200_group_start", "ascb200_group_end", "ascb200_allgather_slabs", "ascb200_interleave_slabs", "ascb200_graph_begin", "ascb200_graph_end", "ascb200_graph_launch", "ascb200_graph_destroy",
     "ascb200_nz_unpack", "ascb200_quant_policy", "ascb200_dequant_policy", "ascb200_softmax_flash_v2", "ascb200_softmax", "ascb200_log_softmax", "ascb200_antiquant", "ascb200_softmax_flash", "ascb200_softmax_grad", "ascb200_simple_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
 ]
 
@@ -86,6 +86,17 @@ def lib():
         _lib.ascb200_mx_scale_prepacked_bytes.argtypes = [C.c_int32, C.c_int32]
         _lib.ascb200_mx_scale_prepacked_bytes.restype = C.c_size_t
         _lib.ascb200_mx_scale_prepack.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p]
+        _lib.ascb200_shard_nslab.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+        _lib.ascb200_shard_groups_lpt.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
+        _lib.ascb200_comm_unique_id.argtypes = [C.c_void_p]
+        _lib.ascb200_comm_init.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p]
+        _lib.ascb200_comm_init_all.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_void_p]
+        _lib.ascb200_comm_destroy.argtypes = [C.c_void_p]
+        _lib.ascb200_group_start.argtypes = []
+        _lib.ascb200_group_end.argtypes = []
+        _lib.ascb200_allgather_slabs.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p,
+                                                 C.c_int64, C.c_void_p]
+        _lib.ascb200_interleave_slabs.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]
         _lib.ascb200_graph_begin.argtypes = [C.c_void_p]
         _lib.ascb200_graph_end.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
         _lib.ascb200_graph_launch.argtypes = [C.c_void_p, C.c_void_p]
@@ -211,6 +222,20 @@ def mx_scale_prepack(scale, rows, k, stream=None):
     out = DevBuf(n, (n,), np.uint8)
     check(lib().ascb200_mx_scale_prepack(_ptr(scale), rows, k, out.ptr, n, stream), "mx_scale_prepack")
     return out
+
+
+def shard_nslab(n, rank, world, align=16):
+    lo, hi = C.c_int64(), C.c_int64()
+    check(lib().ascb200_shard_nslab(n, rank, world, align, C.byref(lo), C.byref(hi)), "shard_nslab")
+    return lo.value, hi.value
+
+
+def shard_groups_lpt(counts, world):
+    """Owner rank of every group (greedy by rows)."""
+    counts = np.ascontiguousarray(counts, np.int64)
+    owner = np.empty(len(counts), np.int32)
+    check(lib().ascb200_shard_groups_lpt(counts.ctypes.data, len(counts), world, owner.ctypes.data), "shard_groups_lpt")
+    return owner
 
 
 def nz_unpack(src_nz, dst, groups, k, n, elem_bytes, to_nk=True, stream=None):

@@ -5,7 +5,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-SOURCES = ["capi.cu", "row_ops.cu", "prepack.cu", "quant_policy.cu", "gemm_tc.cu"]
+SOURCES = ["capi.cu", "row_ops.cu", "prepack.cu", "quant_policy.cu", "gemm_tc.cu", "multi_gpu.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(HERE, "csrc")]
 
@@ -31,7 +31,7 @@ def build(force=False, verbose=False):
     for cmd, p in procs:
         if p.wait() != 0:
             raise RuntimeError("nvcc failed: " + " ".join(cmd))
-    subprocess.check_call(["nvcc", "-shared", "-o", out, *objs, "-gencode", "arch=compute_100a,code=sm_100a"])
+    subprocess.check_call(["nvcc", "-shared", "-o", out, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-ldl"])
     return out
 
 

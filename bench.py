@@ -52,6 +52,14 @@ def cold_sets(bytes_per_set):
     return max(2, -(-2 * L2_BYTES // max(int(bytes_per_set), 1)))
 
 
+def plan_nslab(n, rank, world):
+    """Column range of this rank's N-slab from the C ABI's planner (a host function: the CPU arm calls it too)."""
+    import ascb200
+    lo, hi = ascb200.shard_nslab(n, rank, world, 16)
+    assert (hi - lo) * world == n, "the baseline shapes split into equal slabs"
+    return lo, hi
+
+
 def cache_label(sets, bytes_per_set):
     total = sets * bytes_per_set
     rel = ">= 2 x L2" if total >= 2 * L2_BYTES else ("> L2" if total > L2_BYTES else "fits L2: warm")
@@ -114,7 +122,7 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # workloads
 # ------------------------------------------------------------------------------------------------
-from sharding import dirichlet_counts, lpt_partition  # noqa: E402
+from sharding import dirichlet_counts  # noqa: E402  (the seeded group sizes of the baseline; the shard plans come from the C ABI)
 
 
 class Workload:
@@ -153,15 +161,15 @@ class A8W8(Workload):
 
     def __init__(self, ab, rank, world, sets):
         self.ab, self.rank, self.world = ab, rank, world
-        assert self.N % world == 0
-        self.n_loc = self.N // world
+        self.n_lo, n_hi = plan_nslab(self.N, rank, world)
+        self.n_loc = n_hi - self.n_lo
         rng = np.random.default_rng(0xA5C00002)
         self.a_h = rng.integers(-127, 128, (self.M, self.K)).astype(np.int8)
         self.tok_h = rng.uniform(1e-3, 1e-2, self.M).astype(np.float32)
         ch = rng.uniform(1e-3, 1e-2, self.N).astype(np.float32)
         rng_b = np.random.default_rng(0xA5C00002 + 1000 + rank)   # each rank draws its own B slab
         self.b_h = rng_b.integers(-127, 128, (self.n_loc, self.K)).astype(np.int8)
-        self.ch_h = ch[rank * self.n_loc:(rank + 1) * self.n_loc].copy()
+        self.ch_h = ch[self.n_lo:self.n_lo + self.n_loc].copy()
         self.sets = sets = cold_sets(self.bytes_rank())
         self.a = [ab.to_dev(self.a_h) for _ in range(sets)]
         self.b = [ab.to_dev(self.b_h) for _ in range(sets)]
@@ -223,10 +231,15 @@ class Grouped(Workload):
     def counts(self):
         return dirichlet_counts(self.G, self.MTOT, 0xA5C00003)
 
+    @staticmethod
+    def plan_owner(counts, world):
+        import ascb200
+        return ascb200.shard_groups_lpt(counts, world)   # ascb200_shard_groups_lpt: a host function, also used by the CPU arm
+
     def __init__(self, ab, rank, world, sets):
         self.ab, self.rank, self.world = ab, rank, world
         counts = self.counts()
-        mine = lpt_partition(counts, world)[rank]
+        mine = np.flatnonzero(self.plan_owner(counts, world) == rank)
         self.counts_h = counts[mine].astype(np.int64)
         self.m_loc = int(self.counts_h.sum())
         self.g_loc = len(mine)
@@ -317,14 +330,15 @@ class MXFP4(Workload):
     def __init__(self, ab, rank, world, sets):
         from gpu_util import mx_quantize, quant_params
         self.ab, self.rank, self.world = ab, rank, world
-        self.n_loc = self.N // world
+        self.n_lo, n_hi = plan_nslab(self.N, rank, world)
+        self.n_loc = n_hi - self.n_lo
         rng = np.random.default_rng(0xA5C00004)
         self.a_h, self.sa_h = mx_quantize(rng.standard_normal((self.M, self.K), dtype=np.float32))
         rng_b = np.random.default_rng(0xA5C00004 + 1000 + rank)
         self.b_h, self.sb_h = mx_quantize(rng_b.standard_normal((self.n_loc, self.K), dtype=np.float32))
         # accumulators ~ N(0, K * E[a^2] E[b^2]); quantised unit normals keep E[x^2] ~ 1 -> sigma ~ sqrt(K)
         scales = (rng.uniform(0.5, 2.0, self.N) * 40.0 / np.sqrt(self.K)).astype(np.float32)
-        self.q_h = quant_params(scales[rank * self.n_loc:(rank + 1) * self.n_loc])
+        self.q_h = quant_params(scales[self.n_lo:self.n_lo + self.n_loc])
         per_set = self.a_h.nbytes + self.b_h.nbytes + 3 * self.M * self.n_loc
         self.sets = sets = cold_sets(per_set)
         self.a = [ab.to_dev(self.a_h) for _ in range(sets)]
@@ -541,7 +555,8 @@ class FP16Large(Workload):
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
         self.ab, self.rank, self.world = ab, rank, world
-        self.n_loc = self.N // world
+        self.n_lo, n_hi = plan_nslab(self.N, rank, world)
+        self.n_loc = n_hi - self.n_lo
         rng = np.random.default_rng(0xA5C00005)
         self.a_h = f16_bits(rng.uniform(1, 10, (self.M, self.K)).astype(np.float32))      # the example draws U[1,10)
         self.b_h = f16_bits(np.random.default_rng(0xA5C00005 + 1000 + rank).uniform(1, 10, (self.n_loc, self.K)).astype(np.float32))
@@ -934,29 +949,55 @@ class Comm:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t.item())
 
-    def allgather_ms(self, ab, dev_buf, nbytes, reps=5):
-        """Times all_gather_into_tensor of one rank's output slab (copied into a torch buffer once, outside the timing)."""
+    def slab_comm(self, ab):
+        """An NCCL communicator made through the C ABI (ascb200_comm_init); the 128-byte id travels over the rendezvous group."""
+        import ctypes as C
+        if getattr(self, "_slab_comm", None) is None:
+            torch, dist = self.torch, self.dist
+            ident = (C.c_uint8 * 128)()
+            if dist.get_rank() == 0:
+                ab.check(ab.lib().ascb200_comm_unique_id(ident), "comm_unique_id")
+            t = torch.tensor(list(ident), dtype=torch.uint8, device="cuda")
+            dist.broadcast(t, 0)
+            ident = (C.c_uint8 * 128)(*t.cpu().tolist())
+            comm = C.c_void_p()
+            ab.check(ab.lib().ascb200_comm_init(C.byref(comm), self.world, dist.get_rank(), ident), "comm_init")
+            self._slab_comm = comm
+        return self._slab_comm
+
+    def allgather_ms(self, ab, slab, m, n_loc, elem_bytes, stream, reps=5):
+        """Times ascb200_allgather_slabs (NCCL all-gather + local re-layout into row-major [m][ranks * n_loc]) of one rank's output
+        slab and checks the result: every rank's columns of the gathered C carry that rank's checksum."""
         torch, dist = self.torch, self.dist
-        send = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
-        recv = torch.empty(nbytes * self.world, dtype=torch.uint8, device="cuda")
-        ab.sync()
-        host = dev_buf.download(shape=(nbytes,), dtype=np.uint8)
-        send.copy_(torch.from_numpy(host))
+        comm = self.slab_comm(ab)
+        gathered = ab.empty((self.world, m, n_loc * elem_bytes), np.uint8)
+        full = ab.empty((m, self.world * n_loc * elem_bytes), np.uint8)
+        call = lambda: ab.check(ab.lib().ascb200_allgather_slabs(comm, self.world, slab.ptr, m, n_loc, elem_bytes, gathered.ptr, full.ptr, 0, stream),
+                                "allgather_slabs")
         for _ in range(2):
-            dist.all_gather_into_tensor(recv, send)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        dist.barrier()
-        e0.record()
+            call()
+        ab.sync(stream)
+        self.barrier()
+        timer = ab.Timer(stream)
+        timer.start()
         for _ in range(reps):
-            dist.all_gather_into_tensor(recv, send)
-        e1.record()
-        torch.cuda.synchronize()
-        ms = self.max(e0.elapsed_time(e1) / reps)
-        ok = bool((recv[self.dist.get_rank() * nbytes:(self.dist.get_rank() + 1) * nbytes] == send).all().item())
+            call()
+        ms = self.max(timer.stop_ms() / reps)
+        ab.sync(stream)
+        mine = slab.download(shape=(m, n_loc * elem_bytes), dtype=np.uint8)
+        sums = torch.zeros(self.world, dtype=torch.int64, device="cuda")
+        sums[dist.get_rank()] = int(mine.astype(np.int64).sum())
+        dist.all_reduce(sums)
+        got = full.download().reshape(m, self.world, n_loc * elem_bytes)
+        ok = bool((got[:, dist.get_rank()] == mine).all() and (got.astype(np.int64).sum(axis=(0, 2)) == sums.cpu().numpy()).all())
+        gathered.free()
+        full.free()
         return ms, ok
 
     def close(self):
+        if getattr(self, "_slab_comm", None) is not None:
+            import ascb200 as ab
+            ab.lib().ascb200_comm_destroy(self._slab_comm)
         if self.torch:
             self.dist.destroy_process_group()
 
@@ -1109,10 +1150,13 @@ def measure(ab, cls, comm, rank, world, args, peaks, with_cpu, clock_index):
                 "d2h_bytes_per_step": int(bo), "steps": e2e_steps},
         "gpu_launches": args.steps * wl.kernels_per_step, "clocks": clocks, "parity_spot_check": verified,
     }
-    if getattr(args, "allgather", False) and world > 1 and hasattr(wl, "n_loc"):
+    if world > 1 and hasattr(wl, "n_loc") and not args.no_allgather:
+        # outside the timed region: the optional collective that gives every rank the whole row-major C
+        esz = wl.c[0].nbytes // (wl.M * wl.n_loc)
+        ms_ag, ok_ag = comm.allgather_ms(ab, wl.c[0], wl.M, wl.n_loc, esz, stream)
         slab_bytes = wl.c[0].nbytes
-        ms_ag, ok_ag = comm.allgather_ms(ab, wl.c[0], slab_bytes)
-        line["allgather"] = {"ms": round(ms_ag, 4), "bytes_per_rank": slab_bytes, "layout": "[rank][M][N/ranks]", "ok": ok_ag,
+        line["allgather"] = {"ms": round(ms_ag, 4), "bytes_per_rank": slab_bytes, "layout": "row-major [M][N] on every rank", "ok": ok_ag,
+                             "what": "ascb200_allgather_slabs: NCCL all-gather + local re-layout kernel",
                              "busbw_gbs": round(slab_bytes * (world - 1) / (ms_ag / 1e3) / 1e9, 1)}
     if wl.published:
         line["vs_published_other_hw"] = {"ratio": round(value / wl.published[0], 3), "what": wl.published[1]}
@@ -1205,8 +1249,8 @@ def main():
     ap.add_argument("--impl", default="ascb200", choices=["ascb200", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the other baseline configurations")
     ap.add_argument("--all", action="store_true", help="N=1: also measure the kernels outside the baseline configurations")
-    ap.add_argument("--allgather", action="store_true",
-                    help="N>1, N-slab workloads: also time the NCCL all-gather that gives every rank all C slabs ([rank][M][N/ranks])")
+    ap.add_argument("--no-allgather", action="store_true",
+                    help="N>1, N-slab workloads: skip the (untimed-region) measurement of the all-gather that gives every rank the whole C")
     ap.add_argument("--kernel-only", action="store_true", help="time the device-resident step only (no e2e, no CPU baseline): profiling runs")
     args = ap.parse_args()
     rank, local_rank, world = dist_env()
@@ -1234,7 +1278,7 @@ def main():
             o = measure(ab, WORKLOADS[name], comm, rank, world, sub, peaks, with_cpu=(world == 1), clock_index=local_rank)
             others.append({k: o[k] for k in ("metric", "value", "unit", "n_gpus", "ms_per_step", "ms_per_step_range", "repeats", "ms_x_sm_mhz", "steps",
                                              "config", "roofline", "e2e", "cpu_baseline", "clocks", "parity_spot_check", "gpu_launches",
-                                             "vs_published_other_hw") if k in o})
+                                             "vs_published_other_hw", "allgather") if k in o})
         line["others"] = others
         line["summary"] = [summary_entry(line)] + [summary_entry(o) for o in others]
     comm.close()

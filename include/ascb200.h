@@ -206,6 +206,44 @@ ASCB200_API int ascb200_grouped_gemm(const ascb200_gemm_desc* desc, const int64_
 ASCB200_API int ascb200_gemm_mxfp4_noalloc(const ascb200_gemm_desc* desc, void* stream);
 ASCB200_API int ascb200_noalloc_status(void* stream, uint32_t* status_host);
 
+/* ---- several GPUs of one box ---------------------------------------------------------------------- */
+
+/* The reference spreads a Matmul over AI cores with the multi-core tiling (MultiCoreMatmulTiling::SetDim / SetSingleShape,
+ * include/adv_api/matmul/matmul_tiling.h:30-62; block offsets in examples/.../00_matmul/matmul/matmul.asc:114-141) and the grouped
+ * matmul by handing group blocks to cores in turn (quant_group_matmul_custom.asc:254-286).  Across GPUs the same two splits
+ * are used, both without communication; these are plain host functions (no device needed).
+ *
+ * N-slab: rank `rank` of `world` owns columns [*lo, *hi) of B / the per-channel parameters / C; slabs are equal multiples of
+ * `align` columns, the last ranks get what is left (possibly nothing). */
+ASCB200_API int ascb200_shard_nslab(int64_t n, int32_t rank, int32_t world, int32_t align, int64_t* lo, int64_t* hi);
+/* Expert groups: greedy longest-processing-time assignment by row count (largest group first, each to the rank with the
+ * fewest rows so far; ties go to the lower group / rank index).  counts_host[g] <= 0 counts as no rows.  owner_host[g] = rank. */
+ASCB200_API int ascb200_shard_groups_lpt(const int64_t* counts_host, int32_t groups, int32_t world, int32_t* owner_host);
+
+/* The optional collective of the path: every rank ends with the whole C.  Takes the role of the reference's kernel-side
+ * Hccl<>::AllGather(sendBuf, recvBuf, sendCount, dataType, strideCount, repeat) (include/adv_api/hccl/hccl.h:103-105), whose
+ * strideCount places each rank's piece at a stride in recvBuf.  Here: NCCL all-gather of the contiguous slabs into
+ * gathered_dev ([ranks][m][n_loc]) followed by a local re-layout kernel into full_dev (row-major [m][ranks * n_loc], leading
+ * dimension ld_full elements, 0 = packed); full_dev == NULL skips the re-layout.  All ranks call it with the same m, n_loc,
+ * elem_bytes; both buffers are the caller's.  NCCL is loaded at run time (libnccl.so.2); without it these calls return
+ * ASCB200_EUNSUPPORTED.  Communicators: ascb200_comm_unique_id on one rank (128 bytes, handed to the others by whatever means
+ * the host has), then ascb200_comm_init on every rank with its device current; ascb200_comm_init_all creates the
+ * communicators of `ndev` devices in one process (devices == NULL: 0 .. ndev-1), whose collective calls must then be
+ * bracketed by ascb200_group_start / ascb200_group_end.  Inside such a group NCCL only records the all-gather and issues it
+ * when the group is closed: pass full_dev == NULL there and call ascb200_interleave_slabs on every device afterwards. */
+ASCB200_API int ascb200_comm_unique_id(void* id_out_128_bytes);
+ASCB200_API int ascb200_comm_init(void** comm, int32_t world, int32_t rank, const void* unique_id_128_bytes);
+ASCB200_API int ascb200_comm_init_all(void** comms, int32_t ndev, const int32_t* devices);
+ASCB200_API int ascb200_comm_destroy(void* comm);
+ASCB200_API int ascb200_group_start(void);
+ASCB200_API int ascb200_group_end(void);
+ASCB200_API int ascb200_allgather_slabs(void* comm, int32_t ranks, const void* slab_dev, int64_t m, int64_t n_loc, int32_t elem_bytes,
+                                        void* gathered_dev, void* full_dev, int64_t ld_full, void* stream);
+/* The re-layout by itself: [ranks][m][n_loc] -> [m][ld_full] with slab r in columns [r * n_loc, (r + 1) * n_loc).  HBM bound:
+ * 2 * ranks * m * n_loc * elem_bytes bytes per launch. */
+ASCB200_API int ascb200_interleave_slabs(const void* gathered_dev, void* full_dev, int32_t ranks, int64_t m, int64_t n_loc, int64_t ld_full,
+                                         int32_t elem_bytes, void* stream);
+
 /* ---- SoftMax ------------------------------------------------------------------------------------ */
 
 /* Unpacks a fractal ("NZ") matrix [groups][n/C0][k/16][16][C0], C0 = 32 / elem_bytes columns per block (the format

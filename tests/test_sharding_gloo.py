@@ -1,5 +1,6 @@
-"""Multi-rank host logic on CPU: two gloo ranks each compute their shard with the CPU oracle standing in
-for the GPU kernel; the union must equal the unsharded result, and the timing reduction is a max over ranks."""
+"""Multi-rank host logic on CPU: two gloo ranks each take their shard from the C ABI's planners (ascb200_shard_nslab,
+ascb200_shard_groups_lpt: host functions, no device) and compute it with the CPU oracle standing in for the GPU kernel; the
+union must equal the unsharded result, and the timing reduction is a max over ranks."""
 import os
 import sys
 
@@ -15,6 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _worker(rank, world, port, ret):
     for p in (os.path.join(ROOT, "asc-devkit_clone_b200"), os.path.join(ROOT, "oracle")):
         sys.path.insert(0, p)
+    import ascb200 as ab
     import oracle as orc
     import sharding
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
@@ -27,7 +29,7 @@ def _worker(rank, world, port, ret):
         b = rng.integers(-127, 128, (N, K)).astype(np.int8)
         tok = rng.uniform(1e-3, 1e-2, M).astype(np.float32)
         ch = rng.uniform(1e-3, 1e-2, N).astype(np.float32)
-        lo, hi = sharding.n_slab(N, rank, world)
+        lo, hi = ab.shard_nslab(N, rank, world, 16)
         slab = orc.dequant_tok_ch(orc.gemm_i8(a, b[lo:hi], trans_b=True), tok, ch[lo:hi], orc.BF16)
         parts = [torch.zeros((M, hi - lo), dtype=torch.int32) for _ in range(world)]
         dist.all_gather(parts, torch.from_numpy(slab.astype(np.int32)))   # the optional gather of output slabs
@@ -37,7 +39,7 @@ def _worker(rank, world, port, ret):
         # --- grouped matmul sharded by group ---
         G, Kg, Ng = 8, 32, 48
         counts = sharding.dirichlet_counts(G, 200, 5)
-        mine = sharding.lpt_partition(counts, world)[rank]
+        mine = np.flatnonzero(ab.shard_groups_lpt(counts, world) == rank).tolist()
         starts = sharding.group_rows(counts)
         x = rng.integers(-127, 128, (200, Kg)).astype(np.int8)
         w = rng.integers(-127, 128, (G, Ng, Kg)).astype(np.int8)
