@@ -17,11 +17,11 @@ EPI_CAST, EPI_FIXPIPE_QUANT, EPI_DEQUANT_TOKEN_CHANNEL = 0, 1, 2
 EINVAL, EALIGN, EUNSUPPORTED, ENODEV, ECUDA, ETIMEOUT, ETOOBIG = -1, -2, -3, -4, -5, -6, -7
 
 EXPORTS = [
-    "ascb200_init", "ascb200_strerror", "ascb200_last_cuda_error", "ascb200_device_status", "ascb200_sm_count",
+    "ascb200_init", "ascb200_strerror", "ascb200_last_cuda_error", "ascb200_device_status", "ascb200_sm_count", "ascb200_selftest_bounded_wait",
     "ascb200_malloc", "ascb200_free", "ascb200_malloc_host", "ascb200_free_host", "ascb200_memcpy_h2d", "ascb200_memcpy_d2h",
     "ascb200_memset", "ascb200_stream_create", "ascb200_stream_destroy", "ascb200_stream_sync", "ascb200_event_create",
     "ascb200_event_destroy", "ascb200_event_record", "ascb200_stream_wait_event", "ascb200_event_elapsed_ms", "ascb200_gemm", "ascb200_grouped_gemm",
-    "ascb200_gemm_mxfp4_noalloc", "ascb200_noalloc_status", "ascb200_mx_scale_prepacked_bytes", "ascb200_mx_scale_prepack", "ascb200_shard_nslab", "ascb200_shard_groups_lpt", "ascb200_comm_unique_id", "ascb200_comm_init", "ascb200_comm_init_all", "ascb200_comm_destroy", "ascb200_group_start", "ascb200_group_end", "ascb200_allgather_slabs", "ascb200_interleave_slabs", "ascb200_graph_begin", "ascb200_graph_end", "ascb200_graph_launch", "ascb200_graph_destroy",
+    "ascb200_gemm_mxfp4_noalloc", "ascb200_noalloc_status", "ascb200_mx_scale_prepacked_bytes", "ascb200_mx_scale_prepack", "ascb200_fp4_transpose", "ascb200_shard_nslab", "ascb200_shard_groups_lpt", "ascb200_comm_unique_id", "ascb200_comm_init", "ascb200_comm_init_all", "ascb200_comm_destroy", "ascb200_group_start", "ascb200_group_end", "ascb200_allgather_slabs", "ascb200_interleave_slabs", "ascb200_graph_begin", "ascb200_graph_end", "ascb200_graph_launch", "ascb200_graph_destroy",
     "ascb200_nz_unpack", "ascb200_quant_policy", "ascb200_dequant_policy", "ascb200_softmax_flash_v2", "ascb200_softmax", "ascb200_log_softmax", "ascb200_antiquant", "ascb200_softmax_flash", "ascb200_softmax_grad", "ascb200_simple_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
 ]
 
@@ -36,7 +36,7 @@ class GemmDesc(C.Structure):
         ("c2_dev", C.c_void_p), ("ldc2", C.c_int64), ("c2_dtype", C.c_int32),
         ("epilogue", C.c_int32), ("quant_dev", C.c_void_p), ("quant_scalar", C.c_uint64),
         ("tok_scale_dev", C.c_void_p), ("ch_scale_dev", C.c_void_p),
-        ("relu", C.c_int32), ("act", C.c_int32), ("atomic", C.c_int32), ("scale_flags", C.c_int32), ("reserved", C.c_int32 * 2),
+        ("relu", C.c_int32), ("act", C.c_int32), ("atomic", C.c_int32), ("scale_flags", C.c_int32), ("c_layout", C.c_int32), ("reserved", C.c_int32 * 1),
     ]
 
 
@@ -79,13 +79,15 @@ def lib():
         _lib.ascb200_stream_wait_event.argtypes = [C.c_void_p, C.c_void_p]
         _lib.ascb200_event_elapsed_ms.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]
         _lib.ascb200_device_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
+        _lib.ascb200_selftest_bounded_wait.argtypes = [C.POINTER(C.c_uint32), C.c_void_p]
         _lib.ascb200_gemm.argtypes = [C.POINTER(GemmDesc), C.c_void_p]
         _lib.ascb200_grouped_gemm.argtypes = [C.POINTER(GemmDesc), C.c_void_p, C.c_int32, C.c_void_p]
         _lib.ascb200_gemm_mxfp4_noalloc.argtypes = [C.POINTER(GemmDesc), C.c_void_p]
         _lib.ascb200_noalloc_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
         _lib.ascb200_mx_scale_prepacked_bytes.argtypes = [C.c_int32, C.c_int32]
         _lib.ascb200_mx_scale_prepacked_bytes.restype = C.c_size_t
-        _lib.ascb200_mx_scale_prepack.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p]
+        _lib.ascb200_mx_scale_prepack.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p]
+        _lib.ascb200_fp4_transpose.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
         _lib.ascb200_shard_nslab.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         _lib.ascb200_shard_groups_lpt.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
         _lib.ascb200_comm_unique_id.argtypes = [C.c_void_p]
@@ -194,7 +196,7 @@ def _ptr(b):
 
 def gemm(kind, m, n, k, a, b, c, c_dtype, epilogue=EPI_CAST, trans_a=False, trans_b=False, lda=0, ldb=0, ldc=0, bias=None,
          scale_a=None, scale_b=None, c2=None, c2_dtype=0, ldc2=0, quant=None, quant_scalar=0, tok=None, ch=None, relu=False, act=0,
-         group_counts=None, groups=0, stream=None, noalloc=False, atomic=0, scale_flags=0):
+         group_counts=None, groups=0, stream=None, noalloc=False, atomic=0, scale_flags=0, c_layout=0):
     d = GemmDesc()
     d.kind, d.m, d.n, d.k = kind, m, n, k
     d.a_dev, d.b_dev, d.lda, d.ldb = _ptr(a), _ptr(b), lda, ldb
@@ -206,6 +208,7 @@ def gemm(kind, m, n, k, a, b, c, c_dtype, epilogue=EPI_CAST, trans_a=False, tran
     d.tok_scale_dev, d.ch_scale_dev, d.relu, d.act = _ptr(tok), _ptr(ch), int(relu), act
     d.atomic = int(atomic)
     d.scale_flags = int(scale_flags)
+    d.c_layout = int(c_layout)
     if noalloc:
         return lib().ascb200_gemm_mxfp4_noalloc(C.byref(d), stream)
     if groups:
@@ -214,13 +217,17 @@ def gemm(kind, m, n, k, a, b, c, c_dtype, epilogue=EPI_CAST, trans_a=False, tran
 
 
 SCALE_A_PREPACKED, SCALE_B_PREPACKED = 1, 2
+C_ROW_MAJOR, C_COLUMN_MAJOR, C_NZ = 0, 1, 2
 
 
-def mx_scale_prepack(scale, rows, k, stream=None):
+SCALE_A_PAIRED, SCALE_B_PAIRED = 4, 8
+
+
+def mx_scale_prepack(scale, rows, k, stream=None, paired=False):
     """Re-tiles an MX scale tensor [rows, k/32] once; returns the device buffer to pass with the matching SCALE_*_PREPACKED flag."""
     n = lib().ascb200_mx_scale_prepacked_bytes(rows, k)
     out = DevBuf(n, (n,), np.uint8)
-    check(lib().ascb200_mx_scale_prepack(_ptr(scale), rows, k, out.ptr, n, stream), "mx_scale_prepack")
+    check(lib().ascb200_mx_scale_prepack(_ptr(scale), rows, k, int(paired), out.ptr, n, stream), "mx_scale_prepack")
     return out
 
 

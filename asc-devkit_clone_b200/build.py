@@ -5,7 +5,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-SOURCES = ["capi.cu", "row_ops.cu", "prepack.cu", "quant_policy.cu", "gemm_tc.cu", "multi_gpu.cu"]
+SOURCES = ["capi.cu", "row_ops.cu", "prepack.cu", "quant_policy.cu", "gemm_tc.cu", "multi_gpu.cu", "selftest.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(HERE, "csrc")]
 

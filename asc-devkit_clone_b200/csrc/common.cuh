@@ -32,6 +32,8 @@ DeviceState* current_state();           // nullptr (and ASCB200_ENODEV recorded)
 // Scratch of at least `bytes` that belongs to `stream` (see the note on MXFP4 scratch at ascb200_gemm).  Thread-safe.
 int stream_scratch(DeviceState* st, size_t bytes, cudaStream_t stream, void** out);
 int cuda_fail(cudaError_t e);           // records e, returns ASCB200_ECUDA
+// packed fp4 [rows][cols / 2] -> [cols][rows / 2] (csrc/prepack.cu)
+int fp4_transpose(const void* src, void* dst, int rows, int cols, cudaStream_t stream);
 #define ASCB200_CUDA(call)                                   \
     do {                                                     \
         cudaError_t e__ = (call);                            \

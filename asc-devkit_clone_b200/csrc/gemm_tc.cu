@@ -47,6 +47,7 @@ struct EpiParams {
     int vec_c, vec_c2;       // rows of c / c2 are 16-byte aligned at every 32-column boundary
     int tma_c, tma_c2;       // c / c2 (1- or 2-byte elements) may be written with bulk tensor stores
     int atomic;              // 1 add / 2 max / 3 min into c instead of overwriting it (fp32 / int32 / fp16 / bf16 outputs)
+    int layout;              // ASCB200_C_*: row-major, column-major or fractal NZ (the last two are stored from registers)
     const void* bias;        // float (fp32 accumulators) or int32 (int32 accumulators)
     const float* tok;
     const float* ch;
@@ -375,6 +376,72 @@ __device__ __forceinline__ void store_row32(void* base, long long ld, int vec, i
     }
 }
 
+// 32 consecutive outputs of one row into a column-major or fractal (NZ) C.  Column-major: element (row, n) at n * ld + row,
+// so for every column the 32 lanes of a warp (32 consecutive rows) write one contiguous run.  NZ: blocks of C0 columns
+// (16, or 32 for 1-byte types), row-major inside a block: element at ((n / C0) * ld + row) * C0 + n % C0; a lane writes
+// whole C0-element pieces of its row with 16-byte stores when the chunk is complete and the base is aligned.
+template <int DT>
+__device__ __forceinline__ void store_row32_layout(void* base, long long ld, int layout, int row, int col0, int ncols, const float (&f)[32],
+                                                   const int (&qi)[32])
+{
+    constexpr int ESZ = (DT == OUT_F32 || DT == OUT_S32) ? 4 : (DT == OUT_F16 || DT == OUT_BF16) ? 2 : 1;
+    uint32_t v[32];   // one element per entry, already in the output type's bit pattern
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        if constexpr (DT == OUT_F32) v[j] = __float_as_uint(f[j]);
+        else if constexpr (DT == OUT_S32) v[j] = static_cast<uint32_t>(qi[j]);
+        else if constexpr (DT == OUT_F16) v[j] = pack_f16x2_sat(f[j], 0.0f) & 0xFFFFu;
+        else if constexpr (DT == OUT_BF16) v[j] = pack_bf16x2(f[j], 0.0f) & 0xFFFFu;
+        else v[j] = static_cast<uint32_t>(qi[j]) & 0xFFu;
+    }
+    if (layout == ASCB200_C_COLUMN_MAJOR) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (j >= ncols) break;
+            const size_t off = static_cast<size_t>(col0 + j) * static_cast<size_t>(ld) + row;
+            if constexpr (ESZ == 4) static_cast<uint32_t*>(base)[off] = v[j];
+            else if constexpr (ESZ == 2) static_cast<uint16_t*>(base)[off] = static_cast<uint16_t>(v[j]);
+            else static_cast<uint8_t*>(base)[off] = static_cast<uint8_t>(v[j]);
+        }
+        return;
+    }
+    constexpr int C0 = ESZ == 1 ? 32 : 16;
+    const bool vec = ncols == 32 && (col0 % C0) == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+    if (vec) {
+#pragma unroll
+        for (int g = 0; g < 32 / C0; ++g) {
+            uint8_t* out = static_cast<uint8_t*>(base) + ((static_cast<size_t>((col0 + g * C0) / C0) * ld + row) * C0) * ESZ;
+            if constexpr (ESZ == 4) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) st_v4(out + 16 * q, v[g * 16 + 4 * q], v[g * 16 + 4 * q + 1], v[g * 16 + 4 * q + 2], v[g * 16 + 4 * q + 3]);
+            } else if constexpr (ESZ == 2) {
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int b = g * 16 + 8 * q;
+                    st_v4(out + 16 * q, v[b] | (v[b + 1] << 16), v[b + 2] | (v[b + 3] << 16), v[b + 4] | (v[b + 5] << 16), v[b + 6] | (v[b + 7] << 16));
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int b = 16 * q;
+                    st_v4(out + 16 * q, v[b] | (v[b + 1] << 8) | (v[b + 2] << 16) | (v[b + 3] << 24), v[b + 4] | (v[b + 5] << 8) | (v[b + 6] << 16) | (v[b + 7] << 24),
+                          v[b + 8] | (v[b + 9] << 8) | (v[b + 10] << 16) | (v[b + 11] << 24), v[b + 12] | (v[b + 13] << 8) | (v[b + 14] << 16) | (v[b + 15] << 24));
+                }
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        if (j >= ncols) break;
+        const int n = col0 + j;
+        const size_t off = (static_cast<size_t>(n / C0) * static_cast<size_t>(ld) + row) * C0 + n % C0;
+        if constexpr (ESZ == 4) static_cast<uint32_t*>(base)[off] = v[j];
+        else if constexpr (ESZ == 2) static_cast<uint16_t*>(base)[off] = static_cast<uint16_t>(v[j]);
+        else static_cast<uint8_t*>(base)[off] = static_cast<uint8_t>(v[j]);
+    }
+}
+
 // Same values as store_row32 for a 1- or 2-byte type, but through shared memory and one bulk tensor
 // store per warp: lane i writes row i of the 32 x 32 chunk (16-byte pieces XOR-swizzled like the tensor
 // map, so the writes do not collide on banks), lane 0 hands the chunk to the TMA unit, which writes
@@ -546,6 +613,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
             qi[j + 1] = pair >> 8;
         }
         if (st.map_c) stage_store32<OUT_S8>(st.map_c, st.smem_c, st.dual, threadIdx.x & 31, st.row_base, col0, f, qi);
+        else if (row_ok && e.layout != ASCB200_C_ROW_MAJOR) store_row32_layout<OUT_S8>(e.c, e.ldc, e.layout, row, col0, ncols, f, qi);
         else if (row_ok) store_row32<OUT_S8>(e.c, e.ldc, e.vec_c, row, col0, ncols, f, qi);
         return;
     } else {
@@ -556,6 +624,10 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
             }
         }
         if (!row_ok) return;
+        if (e.layout != ASCB200_C_ROW_MAJOR) {
+            store_row32_layout<DT>(e.c, e.ldc, e.layout, row, col0, ncols, f, qi);
+            return;
+        }
         if constexpr (DT != OUT_S8) {
             if (e.atomic) {
                 atomic_row32<DT>(e.c, e.ldc, row, col0, ncols, f, qi, e.atomic);
@@ -1343,9 +1415,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // the order tcgen05.cp (32x128b, warpx4) expects.  Missing rows / K-blocks are filled with 127 (1.0).
 // One launch covers both operands: blocks [0, rb_a * kc_tiles) re-tile A, the rest B.  A block moves
 // 128 rows x 8 chunks through shared memory so that rows are read as whole sectors and chunks written as whole lines.
+// `paired` bit 0 / 1: the source of A / B is stored [ks / 2][rows][2] instead (the two scales of a 64-element K step side
+// by side, rows next): the order the reference keeps a transposed scaleA and a non-transposed scaleB in
+// (examples/.../00_matmul/matmul_mx/scripts/gen_data.py: reshape(sk / 2, 2, n).transpose(0, 2, 1)).
 __global__ void __launch_bounds__(256)
 retile_scales_kernel(const uint8_t* __restrict__ src_a, uint32_t* __restrict__ dst_a, int rows_a, int rb_a, const uint8_t* __restrict__ src_b,
-                     uint32_t* __restrict__ dst_b, int rows_b, int ks, int kc_count, int kc_tiles)
+                     uint32_t* __restrict__ dst_b, int rows_b, int ks, int kc_count, int kc_tiles, int paired)
 {
     constexpr int CH = 8;  // chunks per block: 32 bytes of every row, four words per thread, all loads issued before any is used
     __shared__ uint32_t tile[128][CH + 1];  // [position inside a chunk][chunk]
@@ -1357,14 +1432,22 @@ retile_scales_kernel(const uint8_t* __restrict__ src_a, uint32_t* __restrict__ d
     uint32_t* dst = is_a ? dst_a : dst_b;
     const int rows = is_a ? rows_a : rows_b;
     const int rb = blk / kc_tiles, kc0 = (blk % kc_tiles) * CH;
-    const bool words = (ks & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 3) == 0;
+    const bool pair_src = ((paired >> (is_a ? 0 : 1)) & 1) != 0;
+    const bool words = !pair_src && (ks & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 3) == 0;
     uint32_t w[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
         const int idx = threadIdx.x + u * 256;
-        const int rl = idx / CH, j = idx % CH;
+        // plain source: consecutive threads read along a row; paired source: consecutive threads read consecutive rows
+        const int rl = pair_src ? idx % 128 : idx / CH, j = pair_src ? idx / 128 : idx % CH;
         const int r = rb * 128 + rl, k = (kc0 + j) * 4;
-        if (r < rows && k + 3 < ks && words) {
+        if (pair_src) {
+            w[u] = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                w[u] |= ((r < rows && k + b < ks) ? static_cast<uint32_t>(src[(static_cast<size_t>((k + b) >> 1) * rows + r) * 2 + ((k + b) & 1)]) : 127u)
+                        << (8 * b);
+        } else if (r < rows && k + 3 < ks && words) {
             w[u] = __ldg(reinterpret_cast<const uint32_t*>(src + static_cast<size_t>(r) * ks + k));
         } else {
             w[u] = 0;
@@ -1375,7 +1458,7 @@ retile_scales_kernel(const uint8_t* __restrict__ src_a, uint32_t* __restrict__ d
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
         const int idx = threadIdx.x + u * 256;
-        const int rl = idx / CH, j = idx % CH;
+        const int rl = pair_src ? idx % 128 : idx / CH, j = pair_src ? idx / 128 : idx % CH;
         tile[(rl & 31) * 4 + (rl >> 5)][j] = w[u];
     }
     __syncthreads();
@@ -1509,9 +1592,10 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     if (d->m < 0 || d->n < 0 || d->k < 0) return ASCB200_EINVAL;
     if (d->m == 0 || d->n == 0) return ASCB200_OK;
     if (!d->a_dev || !d->b_dev || !d->c_dev || d->k == 0) return ASCB200_EINVAL;
-    for (int i = 0; i < 2; ++i)
-        if (d->reserved[i] != 0) return ASCB200_EINVAL;
-    if (d->scale_flags & ~(ASCB200_SCALE_A_PREPACKED | ASCB200_SCALE_B_PREPACKED)) return ASCB200_EINVAL;
+    if (d->reserved[0] != 0) return ASCB200_EINVAL;
+    if (d->c_layout < ASCB200_C_ROW_MAJOR || d->c_layout > ASCB200_C_NZ) return ASCB200_EINVAL;
+    if (d->c_layout != ASCB200_C_ROW_MAJOR && (d->atomic || d->c2_dev || groups > 0)) return ASCB200_EUNSUPPORTED;
+    if (d->scale_flags & ~(ASCB200_SCALE_A_PREPACKED | ASCB200_SCALE_B_PREPACKED | ASCB200_SCALE_A_PAIRED | ASCB200_SCALE_B_PAIRED)) return ASCB200_EINVAL;
     const int kind = d->kind;
     if (kind < ASCB200_KIND_F16 || kind > ASCB200_KIND_MXFP4) return ASCB200_EINVAL;
     const bool acc_int = kind == ASCB200_KIND_S8;
@@ -1522,7 +1606,8 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     // ---- epilogue validation ----
     EpiParams e = {};
     e.c = d->c_dev;
-    e.ldc = d->ldc ? d->ldc : d->n;
+    e.layout = d->c_layout;
+    e.ldc = d->ldc ? d->ldc : (d->c_layout == ASCB200_C_ROW_MAJOR ? d->n : d->m);
     e.c_dtype = d->c_dtype;
     e.mode = d->epilogue;
     e.relu = d->relu;
@@ -1532,7 +1617,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     e.ch = d->ch_scale_dev;
     e.quant = reinterpret_cast<const unsigned long long*>(d->quant_dev);
     e.quant_scalar = d->quant_scalar;
-    if (e.ldc < d->n) return ASCB200_EINVAL;
+    if (e.ldc < (e.layout == ASCB200_C_ROW_MAJOR ? d->n : d->m)) return ASCB200_EINVAL;
     switch (d->epilogue) {
         case ASCB200_EPI_CAST:
             if (acc_int ? d->c_dtype != OUT_S32 : !(d->c_dtype == OUT_F32 || d->c_dtype == OUT_F16 || d->c_dtype == OUT_BF16)) return ASCB200_EUNSUPPORTED;
@@ -1563,7 +1648,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     OutMaps outs;
     std::memset(&outs, 0, sizeof(outs));
     const bool no_tma_store = getenv("ASCB200_NO_TMA_STORE") && getenv("ASCB200_NO_TMA_STORE")[0] == '1';
-    e.tma_c = !no_tma_store && make_out_map(&outs.c, e.c_dtype, e.c, d->n, d->m, e.ldc);
+    e.tma_c = !no_tma_store && e.layout == ASCB200_C_ROW_MAJOR && make_out_map(&outs.c, e.c_dtype, e.c, d->n, d->m, e.ldc);
     e.tma_c2 = !no_tma_store && e.c2 && make_out_map(&outs.c2, e.c2_dtype, e.c2, d->n, d->m, e.ldc2);
     e.atomic = d->atomic;
     if (d->atomic < 0 || d->atomic > 3) return ASCB200_EUNSUPPORTED;                         // enAtomic: 0 off, 1 add, 2 max, 3 min
@@ -1574,10 +1659,42 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     const int bits = elem_bits(kind);
     const int k = d->k, m = d->m, n = d->n;
     if (kind == ASCB200_KIND_MXFP4) {
-        // K-major operands only; K a multiple of 64 like the reference's MmadMx
-        if (d->trans_a || !d->trans_b) return ASCB200_EUNSUPPORTED;
+        // K a multiple of 64 like the reference's MmadMx
         if (k % 64 != 0) return ASCB200_EINVAL;
         if (!d->scale_a_dev || !d->scale_b_dev) return ASCB200_EINVAL;
+        if (d->trans_a || !d->trans_b) {
+            // The tensor core takes fp4 operands K-major only.  An operand stored the other way round ([K, M] / the reference's
+            // ND [K, N], two M- / N-neighbours per byte) is transposed into this stream's scratch first, then the call
+            // proceeds on the copies; the scale scratch follows them in the same block.
+            if (fixed) return ASCB200_EUNSUPPORTED;   // the allocation-free entry point has no room for operand copies
+            if ((d->trans_a && ((m & 1) || (d->lda && d->lda != m))) || (!d->trans_b && ((n & 1) || (d->ldb && d->ldb != n)))) return ASCB200_EUNSUPPORTED;
+            auto round256 = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+            const size_t bytes_ta = d->trans_a ? round256(static_cast<size_t>(m) * k / 2) : 0;
+            const size_t bytes_tb = !d->trans_b ? round256(static_cast<size_t>(n) * k / 2) : 0;
+            const size_t kc2 = 2 * static_cast<size_t>((k + 255) / 256);
+            const size_t bytes_sf = (static_cast<size_t>((m + 127) / 128) + (n + 127) / 128 + kSfPadBlocks) * kc2 * SF_CHUNK_BYTES;
+            void* ptr = nullptr;
+            int rc0 = stream_scratch(st, bytes_ta + bytes_tb + bytes_sf, stream, &ptr);
+            if (rc0 != ASCB200_OK) return rc0;
+            uint8_t* base = static_cast<uint8_t*>(ptr);
+            ascb200_gemm_desc d2 = *d;
+            if (d->trans_a) {
+                rc0 = fp4_transpose(d->a_dev, base, k, m, stream);
+                if (rc0 != ASCB200_OK) return rc0;
+                d2.a_dev = base;
+                d2.trans_a = 0;
+                d2.lda = 0;
+            }
+            if (!d->trans_b) {
+                rc0 = fp4_transpose(d->b_dev, base + bytes_ta, k, n, stream);
+                if (rc0 != ASCB200_OK) return rc0;
+                d2.b_dev = base + bytes_ta;
+                d2.trans_b = 1;
+                d2.ldb = 0;
+            }
+            FixedResources sub = {st->status_dev, base + bytes_ta + bytes_tb, bytes_sf, st->sm_count};
+            return run_gemm(&d2, nullptr, 0, stream, &sub);
+        }
     }
     const int64_t lda = d->lda ? d->lda : (d->trans_a ? m : k);
     const int64_t ldb = d->ldb ? d->ldb : (d->trans_b ? k : n);
@@ -1706,7 +1823,8 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
             const int blocks_a = pre_a ? 0 : rba * kc_tiles, blocks_b = pre_b ? 0 : rbb * kc_tiles;
             ASCB200_CUDA(launch_pdl(retile_scales_kernel, dim3(blocks_a + blocks_b), dim3(256), 0, stream, static_cast<const uint8_t*>(d->scale_a_dev),
                                     reinterpret_cast<uint32_t*>(scratch), m, pre_a ? 0 : rba, static_cast<const uint8_t*>(d->scale_b_dev),
-                                    reinterpret_cast<uint32_t*>(scratch + bytes_a), n, ks, kc, kc_tiles));
+                                    reinterpret_cast<uint32_t*>(scratch + bytes_a), n, ks, kc, kc_tiles,
+                                    ((d->scale_flags & ASCB200_SCALE_A_PAIRED) ? 1 : 0) | ((d->scale_flags & ASCB200_SCALE_B_PAIRED) ? 2 : 0)));
         }
         p.sfa = sfa;
         p.sfb = sfb;
@@ -1855,7 +1973,7 @@ int noalloc_status(cudaStream_t stream, uint32_t* status_host)
 }
 
 // Re-tiles one scale tensor [rows, k / 32] into the chunk order of the kernels, padding blocks included.
-int mx_scale_prepack(const void* scale_dev, int rows, int k, void* out_dev, size_t out_bytes, cudaStream_t stream)
+int mx_scale_prepack(const void* scale_dev, int rows, int k, int paired, void* out_dev, size_t out_bytes, cudaStream_t stream)
 {
     if (!scale_dev || !out_dev || rows <= 0 || k <= 0 || k % 64 != 0) return ASCB200_EINVAL;
     if (!aligned_to(out_dev, 16)) return ASCB200_EALIGN;
@@ -1866,7 +1984,7 @@ int mx_scale_prepack(const void* scale_dev, int rows, int k, void* out_dev, size
     const int kc_tiles = (kc + 7) / 8;
     ASCB200_CUDA(launch_pdl(retile_scales_kernel, dim3(rb * kc_tiles), dim3(256), 0, stream, static_cast<const uint8_t*>(scale_dev),
                             static_cast<uint32_t*>(out_dev), rows, rb, static_cast<const uint8_t*>(nullptr), static_cast<uint32_t*>(nullptr), 0, k / 32,
-                            kc, kc_tiles));
+                            kc, kc_tiles, paired ? 1 : 0));
     return ASCB200_OK;
 }
 
@@ -1883,10 +2001,10 @@ size_t ascb200_mx_scale_prepacked_bytes(int32_t rows, int32_t k)
     return static_cast<size_t>((rows + 127) / 128 + ascb200::kSfPadBlocks) * (2 * ((k + 255) / 256)) * ascb200::SF_CHUNK_BYTES;
 }
 
-int ascb200_mx_scale_prepack(const void* scale_dev, int32_t rows, int32_t k, void* out_dev, size_t out_bytes, void* stream)
+int ascb200_mx_scale_prepack(const void* scale_dev, int32_t rows, int32_t k, int32_t paired, void* out_dev, size_t out_bytes, void* stream)
 {
     if (!ascb200::current_state()) return ASCB200_ENODEV;
-    return ascb200::mx_scale_prepack(scale_dev, rows, k, out_dev, out_bytes, static_cast<cudaStream_t>(stream));
+    return ascb200::mx_scale_prepack(scale_dev, rows, k, paired, out_dev, out_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int ascb200_gemm_mxfp4_noalloc(const ascb200_gemm_desc* desc, void* stream)

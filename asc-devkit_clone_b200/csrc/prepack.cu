@@ -100,8 +100,88 @@ __global__ void __launch_bounds__(256) nz_unpack_kernel(const uint8_t* __restric
     }
 }
 
+// Transposition of a packed fp4 matrix: src [rows][cols / 2] (column pairs per byte, even column low) -> dst [cols][rows / 2]
+// (row pairs per byte, even row low).  A block moves a tile of 256 rows x 64 columns through shared memory (rows read as 32
+// contiguous bytes; 36-byte row pitch keeps the word writes off each other's banks); a thread then builds, for one column, the 32
+// output bytes of 64 consecutive rows and stores them as two 16-byte vectors when the destination allows.
+constexpr int FP4_T_ROWS = 256, FP4_T_COLS = 64, FP4_T_PITCH = 36;
+
+__global__ void __launch_bounds__(256)
+fp4_transpose_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int rows, int cols, int src_pitch, int dst_pitch)
+{
+    __shared__ __align__(16) uint8_t tile[FP4_T_ROWS * FP4_T_PITCH];
+    grid_dependency_wait();
+    const int r0 = blockIdx.y * FP4_T_ROWS, c0 = blockIdx.x * FP4_T_COLS;
+    {
+        // thread t loads row r0 + t: 32 bytes = columns c0 .. c0 + 63
+        const int r = r0 + threadIdx.x;
+        uint32_t w[8];
+        const uint8_t* p = src + static_cast<size_t>(r) * src_pitch + c0 / 2;
+        const bool full = r < rows && c0 + FP4_T_COLS <= cols && (reinterpret_cast<uintptr_t>(p) & 3) == 0;
+        if (full) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) w[j] = __ldg(reinterpret_cast<const uint32_t*>(p) + j);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                w[j] = 0;
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    if (r < rows && c0 + (4 * j + b) * 2 < cols) w[j] |= static_cast<uint32_t>(p[4 * j + b]) << (8 * b);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) *reinterpret_cast<uint32_t*>(tile + threadIdx.x * FP4_T_PITCH + 4 * j) = w[j];
+    }
+    __syncthreads();
+    // thread (c, q): column c0 + c, rows r0 + 64 q .. + 63 -> 32 output bytes
+    const int c = threadIdx.x & 63, q = threadIdx.x >> 6;
+    if (c0 + c >= cols) return;
+    const int shift = 4 * (c & 1);
+    uint32_t out[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int rp = 64 * q + 2 * (4 * j + b);   // even row of the pair, inside the tile
+            const uint32_t lo = (tile[rp * FP4_T_PITCH + (c >> 1)] >> shift) & 0xFu;
+            const uint32_t hi = (tile[(rp + 1) * FP4_T_PITCH + (c >> 1)] >> shift) & 0xFu;
+            word |= (lo | (hi << 4)) << (8 * b);
+        }
+        out[j] = word;
+    }
+    uint8_t* o = dst + static_cast<size_t>(c0 + c) * dst_pitch + (r0 + 64 * q) / 2;
+    const int valid = min(32, (rows - (r0 + 64 * q) + 1) / 2);   // output bytes that lie inside the matrix
+    if (valid <= 0) return;
+    if (valid == 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+        *reinterpret_cast<uint4*>(o) = make_uint4(out[0], out[1], out[2], out[3]);
+        *reinterpret_cast<uint4*>(o + 16) = make_uint4(out[4], out[5], out[6], out[7]);
+    } else {
+        for (int b = 0; b < valid; ++b) o[b] = static_cast<uint8_t>(out[b >> 2] >> (8 * (b & 3)));
+    }
+}
+
 }  // namespace
+
+int fp4_transpose(const void* src, void* dst, int rows, int cols, cudaStream_t stream)
+{
+    if (!src || !dst || rows < 0 || cols < 0 || (rows & 1) || (cols & 1)) return ASCB200_EINVAL;
+    if (rows == 0 || cols == 0) return ASCB200_OK;
+    dim3 grid((cols + FP4_T_COLS - 1) / FP4_T_COLS, (rows + FP4_T_ROWS - 1) / FP4_T_ROWS);
+    if (grid.y > 65535u) return ASCB200_ETOOBIG;
+    ASCB200_CUDA(launch_pdl(fp4_transpose_kernel, grid, dim3(256), 0, stream, static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), rows, cols,
+                            cols / 2, rows / 2));
+    return ASCB200_OK;
+}
+
 }  // namespace ascb200
+
+extern "C" int ascb200_fp4_transpose(const void* src_dev, void* dst_dev, int32_t rows, int32_t cols, void* stream)
+{
+    if (!ascb200::current_state()) return ASCB200_ENODEV;
+    return ascb200::fp4_transpose(src_dev, dst_dev, rows, cols, static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int ascb200_nz_unpack(const void* src_nz, void* dst, int32_t groups, int32_t k, int32_t n, int32_t elem_bytes, int32_t to_nk, void* stream)
 {

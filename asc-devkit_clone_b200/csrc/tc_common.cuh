@@ -120,10 +120,10 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 // Slow path shared by both wait flavours: called once every few hundred failed polls.
-__device__ __noinline__ bool mbar_wait_expired(long long t0, volatile uint32_t* abort_smem, uint32_t* status)
+static __device__ __noinline__ bool mbar_wait_expired(long long t0, volatile uint32_t* abort_smem, uint32_t* status, long long limit = kWaitLimitCycles)
 {
     if (*abort_smem) return true;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > limit) {
         *abort_smem = 1u;
         atomicOr(status, 1u);
         return true;
@@ -131,14 +131,15 @@ __device__ __noinline__ bool mbar_wait_expired(long long t0, volatile uint32_t* 
     return false;
 }
 // Returns false when the wait was abandoned (abort already set, or the time limit ran out).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_smem, uint32_t* status)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_smem, uint32_t* status,
+                                          long long limit = kWaitLimitCycles)
 {
     if (mbar_test_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t it = 0;
     while (true) {
         if (mbar_test_wait(bar, parity)) return true;
-        if ((++it & 1023u) == 0u && mbar_wait_expired(t0, abort_smem, status)) return false;
+        if ((++it & 1023u) == 0u && mbar_wait_expired(t0, abort_smem, status, limit)) return false;
     }
 }
 

@@ -64,6 +64,12 @@ ASCB200_API int ascb200_last_cuda_error(void);
  * inside a GEMM kernel expired. Non-zero status makes the call return ASCB200_ETIMEOUT and clears it. */
 ASCB200_API int ascb200_device_status(void* stream, uint32_t* status_host);
 ASCB200_API int ascb200_sm_count(void);
+/* Self-test of the bounded waits (the failure-detection path of the GEMM kernels: every mbarrier wait gives up after a time
+ * limit, sets the status bit and lets the kernel return normally).  Launches a one-CTA kernel that waits, with the kernels'
+ * own wait routine and a limit of about 0.1 ms, on a barrier that nothing completes.  Nothing hangs or traps.  On return
+ * result_host3 = {1 if the wait was abandoned, 1 if the CTA-wide abort word was set, cycles waited / 1024}, and the device
+ * status word has bit 0 set: the next ascb200_device_status returns ASCB200_ETIMEOUT and clears it. */
+ASCB200_API int ascb200_selftest_bounded_wait(uint32_t* result_host3, void* stream);
 
 /* Memory and stream shims for aclrtMalloc / aclrtMallocHost / aclrtMemcpy(Async) /
  * aclrtSynchronizeStream as used by the examples (matmul.asc:219-260). */
@@ -137,12 +143,29 @@ typedef struct ascb200_gemm_desc {
     int32_t act;             /* 0 none, 1 FasterGelu (DEQUANT_TOKEN_CHANNEL only) */
     int32_t atomic;          /* enAtomic of IterateAll / GetTensorC: 0 C is overwritten, 1 C += result, 2 C = max(C, result), 3 C = min(C, result); F32, S32, F16, BF16 outputs */
     int32_t scale_flags;     /* MXFP4: ASCB200_SCALE_*_PREPACKED bits; 0 = scale_a_dev / scale_b_dev are plain [rows, k/32] tensors */
-    int32_t reserved[2];     /* must be zero */
+    int32_t c_layout;        /* ASCB200_C_*: how c_dev is laid out (CubeFormat of C_TYPE); ROW_MAJOR = 0 */
+    int32_t reserved[1];     /* must be zero */
 } ascb200_gemm_desc;
+
+/* Layouts of C, the formats the reference's copy-out stage writes (CopyOutNZ2ND / CopyOutNZ2NZ / CopyOutNZ2DN,
+ * impl/adv_api/detail/matmul/stage/copy_cube_out/copy_cube_out_fixpipe.h:109-127; CubeFormat, include/adv_api/matmul/matmul_config.h:26-37):
+ *   ROW_MAJOR     ND: element (i, j) at i * ldc + j;
+ *   COLUMN_MAJOR  element (i, j) at j * ldc + i, ldc >= m (0 = m);
+ *   NZ            fractal: element (i, j) at ((j / C0) * ldc + i) * C0 + j % C0 with C0 = 16 elements (32 for 1-byte outputs) and
+ *                 ldc >= m the row count of the whole matrix (0 = m): blocks of C0 columns, row-major inside a block
+ *                 (dstOffset / stride of CopyOutNZ2NZ, copy_cube_out_fixpipe.h:272-290); the buffer holds ceil(n / C0) blocks.
+ * The other layouts take every epilogue and output type; `atomic` and the second output (c2_dev) go with ROW_MAJOR only. */
+enum { ASCB200_C_ROW_MAJOR = 0, ASCB200_C_COLUMN_MAJOR = 1, ASCB200_C_NZ = 2 };
 
 /* scale_flags: the scale tensor was re-tiled once with ascb200_mx_scale_prepack (static weights); the call then skips its
  * own re-tiling of that tensor and reads the prepacked copy in place. */
-enum { ASCB200_SCALE_A_PREPACKED = 1, ASCB200_SCALE_B_PREPACKED = 2 };
+enum { ASCB200_SCALE_A_PREPACKED = 1, ASCB200_SCALE_B_PREPACKED = 2,
+       /* the (not prepacked) scale tensor is stored [k/64][rows][2] - the two scales of a 64-element K step side by side, rows
+        * next - instead of [rows][k/32]: the order the reference keeps a transposed scaleA ([K/32, M] -> isTransposeScaleA) and a
+        * non-transposed scaleB ([K/32, N]) in, for LoadData2DMx's 32-byte scale fractals
+        * (examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul_mx/scripts/gen_data.py:73-76;
+        *  05_best_practices/01_matrix_compute/matmul_mxfp4_high_performance/scripts/gen_data.py:63) */
+       ASCB200_SCALE_A_PAIRED = 4, ASCB200_SCALE_B_PAIRED = 8 };
 
 /* One whole Matmul: what Matmul<...>::IterateAll produces for the object state set by
  * SetTensorA / SetTensorB / SetBias / SetQuantScalar / SetQuantVector
@@ -161,10 +184,19 @@ ASCB200_API int ascb200_gemm(const ascb200_gemm_desc* desc, void* stream);
  * (LoadData with LoadData2DMxParams: include/basic_api/kernel_struct_mm.h:132-153; examples/.../load_data_2dmx_l12l0), done once
  * for a tensor that does not change between calls (the weights' scales): re-tiles scale_dev, e8m0 bytes [rows, k/32] row-major,
  * into out_dev in the order ascb200_gemm reads (512-byte chunks of 128 rows x 4 K-blocks, two padding blocks of rows at the end).
+ * paired != 0: the source is in the [k/64][rows][2] order described at ASCB200_SCALE_A_PAIRED.
  * out_dev must be 16-byte aligned and hold ascb200_mx_scale_prepacked_bytes(rows, k) bytes; k a multiple of 64.  Pass out_dev as
  * scale_a_dev / scale_b_dev with the matching ASCB200_SCALE_*_PREPACKED flag. */
 ASCB200_API size_t ascb200_mx_scale_prepacked_bytes(int32_t rows, int32_t k);
-ASCB200_API int ascb200_mx_scale_prepack(const void* scale_dev, int32_t rows, int32_t k, void* out_dev, size_t out_bytes, void* stream);
+ASCB200_API int ascb200_mx_scale_prepack(const void* scale_dev, int32_t rows, int32_t k, int32_t paired, void* out_dev, size_t out_bytes,
+                                         void* stream);
+/* Transposes a packed fp4 matrix: src [rows][cols / 2 bytes] (two column-neighbours per byte, even column in the low nibble)
+ * -> dst [cols][rows / 2 bytes] (two row-neighbours per byte, even row in the low nibble).  rows and cols even.  This turns the
+ * reference's ND B of an MX Matmul ([K, N], two N-neighbours per byte:
+ * 05_best_practices/01_matrix_compute/matmul_mxfp4_high_performance/scripts/gen_data.py:25-36,46) into the K-major [N, K] operand
+ * the tensor core needs (and a transposed A, [K, M], into [M, K]).  ascb200_gemm does the same into its stream scratch on
+ * every call when it is given trans_b == 0 (or trans_a == 1) with kind MXFP4; weights are better transposed once. */
+ASCB200_API int ascb200_fp4_transpose(const void* src_dev, void* dst_dev, int32_t rows, int32_t cols, void* stream);
 
 /* Grouped int8 matmul of the reference's QuantGroupMatmul example kernel
  * (examples/01_simd_cpp_api/05_best_practices/03_fusion_compute/quant_group_matmul_high_performance/

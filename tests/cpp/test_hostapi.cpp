@@ -4,6 +4,8 @@
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
+#include <algorithm>
 #include <random>
 #include <vector>
 
@@ -716,6 +718,338 @@ static void TestIterateBatch()
     std::printf("IterateBatch (4 x A, shared B): ok\n");
 }
 
+// Batch layouts BSNGD / SBNGD with the shapes and the loop of the reference's batch_matmul example (batch_matmul.asc:166-193,
+// scripts/gen_data.py:19-66: A [B, S, N, G, D], B [B, S', N, G, D] used transposed, C [B, S, N, G, S']): every (b, n, g) is one
+// [S, D] x [D, S'] product whose rows lie N * G * D elements apart.  int8 data, int32 results compared exactly.
+template <LayoutMode LAYOUT>
+static void TestBatchLayout(const char* name)
+{
+    using namespace AscendC;
+    const int B = 2, SA = 32, SB = 96, N = 1, G = 3, D = 64;
+    std::mt19937 rng(11);
+    std::uniform_int_distribution<int> u(-6, 6);
+    const bool sb = LAYOUT == LayoutMode::SBNGD;
+    // element (b, s, n, g, d) of a tensor with inner extent `in`: BSNGD [B][S][N][G][in], SBNGD [S][B][N][G][in]
+    auto at = [&](int b, int s, int n, int g, int d, int S, int in) -> size_t {
+        return sb ? ((((static_cast<size_t>(s) * B + b) * N + n) * G + g) * in + d) : ((((static_cast<size_t>(b) * S + s) * N + n) * G + g) * in + d);
+    };
+    std::vector<int8_t> a(static_cast<size_t>(B) * SA * N * G * D), b(static_cast<size_t>(B) * SB * N * G * D);
+    for (auto& v : a) v = static_cast<int8_t>(u(rng));
+    for (auto& v : b) v = static_cast<int8_t>(u(rng));
+    DevBuf<int8_t> dA(a), dB(b);
+    DevBuf<int32_t> dC(static_cast<size_t>(B) * SA * N * G * SB);
+    matmul_tiling::BatchMatmulTiling api;
+    api.SetAType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_INT8, false);
+    api.SetBType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_INT8, true);
+    api.SetCType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_INT32);
+    api.SetShape(SA, SB, D);
+    api.SetOrgShape(SA, SB, D);
+    api.SetALayout(B, SA, N, G, D);
+    api.SetBLayout(B, SB, N, G, D);
+    api.SetCLayout(B, SA, N, G, SB);
+    api.SetBatchNum(N * G);
+    TCubeTiling tiling{};
+    CHECK(api.GetTiling(tiling) == 0, "BatchMatmulTiling::GetTiling");
+    {
+        TPipe pipe;
+        using TA = MatmulType<TPosition::GM, CubeFormat::ND, int8_t, false, LAYOUT>;
+        using TB = MatmulType<TPosition::GM, CubeFormat::ND, int8_t, true, LAYOUT>;
+        using TC = MatmulType<TPosition::GM, CubeFormat::ND, int32_t, false, LAYOUT>;
+        Matmul<TA, TB, TC, TC> mm;
+        REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, &tiling);
+        GlobalTensor<int8_t> ga, gb;
+        GlobalTensor<int32_t> gc;
+        ga.SetGlobalBuffer(dA.p, a.size());
+        gb.SetGlobalBuffer(dB.p, b.size());
+        gc.SetGlobalBuffer(dC.p, dC.n);
+        const int batchA = N * G, batchB = N * G;
+        for (int i = 0; i < B; ++i) {   // one call per b: all N * G matrices of that row block
+            const size_t offA = sb ? static_cast<size_t>(i) * N * G * D : static_cast<size_t>(i) * D * SA * batchA;
+            const size_t offB = sb ? static_cast<size_t>(i) * N * G * D : static_cast<size_t>(i) * D * SB * batchB;
+            const size_t offC = sb ? static_cast<size_t>(i) * N * G * SB : static_cast<size_t>(i) * batchA * SB * SA;
+            mm.SetTensorA(ga[offA], false);
+            mm.SetTensorB(gb[offB], true);
+            mm.IterateBatch(gc[offC], batchA, batchB, false);
+        }
+        mm.End();
+    }
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<int32_t> c = dC.Download();
+    int bad = 0;
+    for (int bi = 0; bi < B; ++bi)
+        for (int g = 0; g < G; ++g)
+            for (int s1 = 0; s1 < SA; ++s1)
+                for (int s2 = 0; s2 < SB; ++s2) {
+                    int32_t acc = 0;
+                    for (int d = 0; d < D; ++d) acc += static_cast<int32_t>(a[at(bi, s1, 0, g, d, SA, D)]) * b[at(bi, s2, 0, g, d, SB, D)];
+                    if (c[at(bi, s1, 0, g, s2, SA, SB)] != acc) ++bad;
+                }
+    CHECK(bad == 0, "IterateBatch %s: %d wrong", name, bad);
+    std::printf("IterateBatch %s: ok\n", name);
+}
+
+// IterateNBatch + GetBatchTensorC as in batch_matmul_iterate_n_batch.asc:150-190 (A [1, M, 1, b, K], B [1, N, 1, b, K], C
+// [1, M, 1, b, N], BatchNum = 1 per call): three calls of one matrix each, results in the workspace.
+static void TestIterateNBatch()
+{
+    using namespace AscendC;
+    const int M = 32, N = 64, K = 64, NB = 3;
+    std::mt19937 rng(12);
+    std::uniform_int_distribution<int> u(-6, 6);
+    std::vector<int8_t> a(static_cast<size_t>(M) * NB * K), b(static_cast<size_t>(N) * NB * K);
+    for (auto& v : a) v = static_cast<int8_t>(u(rng));
+    for (auto& v : b) v = static_cast<int8_t>(u(rng));
+    DevBuf<int8_t> dA(a), dB(b);
+    DevBuf<int32_t> dC(static_cast<size_t>(M) * NB * N);
+    matmul_tiling::BatchMatmulTiling api;
+    api.SetAType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_INT8, false);
+    api.SetBType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_INT8, true);
+    api.SetCType(matmul_tiling::TPosition::GM, matmul_tiling::CubeFormat::ND, matmul_tiling::DataType::DT_INT32);
+    api.SetShape(M, N, K);
+    api.SetOrgShape(M, N, K);
+    api.SetALayout(1, M, 1, NB, K);
+    api.SetBLayout(1, N, 1, NB, K);
+    api.SetCLayout(1, M, 1, NB, N);
+    api.SetBatchNum(1);
+    TCubeTiling tiling{};
+    CHECK(api.GetTiling(tiling) == 0, "BatchMatmulTiling::GetTiling");
+    {
+        TPipe pipe;
+        using TA = MatmulType<TPosition::GM, CubeFormat::ND, int8_t, false, LayoutMode::BSNGD>;
+        using TB = MatmulType<TPosition::GM, CubeFormat::ND, int8_t, true, LayoutMode::BSNGD>;
+        using TC = MatmulType<TPosition::GM, CubeFormat::ND, int32_t, false, LayoutMode::BSNGD>;
+        Matmul<TA, TB, TC, TC> mm;
+        REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, &tiling);
+        GlobalTensor<int8_t> ga, gb;
+        GlobalTensor<int32_t> gc;
+        ga.SetGlobalBuffer(dA.p, a.size());
+        gb.SetGlobalBuffer(dB.p, b.size());
+        gc.SetGlobalBuffer(dC.p, dC.n);
+        mm.SetTensorA(ga, false);
+        mm.SetTensorB(gb, true);
+        const int nNum = tiling.ALayoutInfoB * tiling.ALayoutInfoN * tiling.ALayoutInfoG / tiling.BatchNum;
+        CHECK(nNum == NB, "nNum %d", nNum);
+        mm.SetWorkspace(gc);
+        mm.template IterateNBatch<false>(nNum, 1, 1, false);
+        for (int j = 0; j < nNum; ++j) {
+            GlobalTensor<int32_t> t = mm.template GetBatchTensorC<false>(1, 1, false);
+            CHECK(t.GetPhyAddr() == dC.p + static_cast<size_t>(j) * N, "GetBatchTensorC %d", j);
+        }
+        mm.End();
+    }
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<int32_t> c = dC.Download();
+    int bad = 0;
+    for (int g = 0; g < NB; ++g)
+        for (int m = 0; m < M; ++m)
+            for (int n = 0; n < N; ++n) {
+                int32_t acc = 0;
+                for (int k = 0; k < K; ++k) acc += static_cast<int32_t>(a[(static_cast<size_t>(m) * NB + g) * K + k]) * b[(static_cast<size_t>(n) * NB + g) * K + k];
+                if (c[(static_cast<size_t>(m) * NB + g) * N + n] != acc) ++bad;
+            }
+    CHECK(bad == 0, "IterateNBatch: %d wrong", bad);
+    std::printf("IterateNBatch (BSNGD, three calls of one matrix): ok\n");
+}
+
+// Iterate / GetTensorC over base blocks: in place (each block at its position in C) and block-sequential (each block a compact
+// matrix in its own slot, as the grouped example collects them: quant_group_matmul_custom.asc:320-328), both iteration orders;
+// then the column-major and fractal output formats of IterateAll.
+static void TestBaseBlocksAndOutputFormats()
+{
+    using namespace AscendC;
+    const int M = 200, N = 328, K = 128, BM = 96, BN = 128;
+    std::mt19937 rng(13);
+    std::uniform_int_distribution<int> u(-7, 7);
+    std::vector<int8_t> a(static_cast<size_t>(M) * K), b(static_cast<size_t>(N) * K);
+    for (auto& v : a) v = static_cast<int8_t>(u(rng));
+    for (auto& v : b) v = static_cast<int8_t>(u(rng));
+    std::vector<int32_t> ref(static_cast<size_t>(M) * N);
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            int32_t acc = 0;
+            for (int k = 0; k < K; ++k) acc += static_cast<int32_t>(a[static_cast<size_t>(m) * K + k]) * b[static_cast<size_t>(n) * K + k];
+            ref[static_cast<size_t>(m) * N + n] = acc;
+        }
+    DevBuf<int8_t> dA(a), dB(b);
+    TCubeTiling tiling{};
+    tiling.usedCoreNum = 1;
+    tiling.M = tiling.singleCoreM = M;
+    tiling.N = tiling.singleCoreN = N;
+    tiling.Ka = tiling.Kb = tiling.singleCoreK = K;
+    tiling.baseM = BM;
+    tiling.baseN = BN;
+    tiling.baseK = 64;
+    using T8 = MatmulType<TPosition::GM, CubeFormat::ND, int8_t>;
+    using T8T = MatmulType<TPosition::GM, CubeFormat::ND, int8_t, true>;
+    const int mIter = (M + BM - 1) / BM, nIter = (N + BN - 1) / BN;
+    for (int order = 0; order < 2; ++order) {
+        tiling.iterateOrder = order;
+        DevBuf<int32_t> dC(static_cast<size_t>(M) * N), dSlots(static_cast<size_t>(mIter) * nIter * BM * BN);
+        {
+            TPipe pipe;
+            using T32 = MatmulType<TPosition::GM, CubeFormat::ND, int32_t>;
+            Matmul<T8, T8T, T32, T32> mm;
+            REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, &tiling);
+            GlobalTensor<int8_t> ga, gb;
+            GlobalTensor<int32_t> gc, gs;
+            ga.SetGlobalBuffer(dA.p, a.size());
+            gb.SetGlobalBuffer(dB.p, b.size());
+            gc.SetGlobalBuffer(dC.p, dC.n);
+            gs.SetGlobalBuffer(dSlots.p, dSlots.n);
+            mm.SetTensorA(ga, false);
+            mm.SetTensorB(gb, true);
+            int blocks = 0;
+            while (mm.Iterate()) {
+                mm.GetTensorC(gc);                                                      // at its place in [M, N]
+                mm.GetTensorC(gs[static_cast<size_t>(blocks) * BM * BN], 0, true);      // compact, in slot `blocks`
+                ++blocks;
+            }
+            CHECK(blocks == mIter * nIter, "Iterate returned %d blocks", blocks);
+            mm.End();
+        }
+        CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+        const std::vector<int32_t> c = dC.Download(), slots = dSlots.Download();
+        int bad = 0;
+        for (size_t i = 0; i < c.size(); ++i) bad += c[i] != ref[i];
+        for (int blk = 0; blk < mIter * nIter; ++blk) {
+            const int row = order == 1 ? blk / nIter : blk % mIter, col = order == 1 ? blk % nIter : blk / mIter;
+            const int h = std::min(BM, M - row * BM), w = std::min(BN, N - col * BN);
+            for (int i = 0; i < h; ++i)
+                for (int j = 0; j < w; ++j)
+                    bad += slots[static_cast<size_t>(blk) * BM * BN + static_cast<size_t>(i) * w + j] != ref[static_cast<size_t>(row * BM + i) * N + col * BN + j];
+        }
+        CHECK(bad == 0, "base blocks, iterateOrder %d: %d wrong", order, bad);
+    }
+    // output formats
+    {
+        DevBuf<int32_t> dCm(static_cast<size_t>(M) * N), dNz(static_cast<size_t>((N + 15) / 16) * M * 16);
+        TPipe pipe;
+        using TCM = MatmulType<TPosition::GM, CubeFormat::COLUMN_MAJOR, int32_t>;
+        using TNZ = MatmulType<TPosition::GM, CubeFormat::NZ, int32_t>;
+        GlobalTensor<int8_t> ga, gb;
+        ga.SetGlobalBuffer(dA.p, a.size());
+        gb.SetGlobalBuffer(dB.p, b.size());
+        {
+            Matmul<T8, T8T, TCM, TCM> mm;
+            REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, &tiling);
+            GlobalTensor<int32_t> gc;
+            gc.SetGlobalBuffer(dCm.p, dCm.n);
+            mm.SetTensorA(ga, false);
+            mm.SetTensorB(gb, true);
+            mm.IterateAll(gc);
+            mm.End();
+        }
+        {
+            Matmul<T8, T8T, TNZ, TNZ> mm;
+            REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, &tiling);
+            GlobalTensor<int32_t> gc;
+            gc.SetGlobalBuffer(dNz.p, dNz.n);
+            mm.SetTensorA(ga, false);
+            mm.SetTensorB(gb, true);
+            while (mm.Iterate()) mm.GetTensorC(gc);   // block by block into the fractal matrix
+            mm.End();
+        }
+        CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+        const std::vector<int32_t> cm = dCm.Download(), nz = dNz.Download();
+        int bad = 0;
+        for (int m = 0; m < M; ++m)
+            for (int n = 0; n < N; ++n) {
+                bad += cm[static_cast<size_t>(n) * M + m] != ref[static_cast<size_t>(m) * N + n];
+                bad += nz[(static_cast<size_t>(n / 16) * M + m) * 16 + n % 16] != ref[static_cast<size_t>(m) * N + n];
+            }
+        CHECK(bad == 0, "COLUMN_MAJOR / NZ outputs: %d wrong", bad);
+    }
+    std::printf("Iterate / GetTensorC base blocks (in place, sequential), COLUMN_MAJOR and NZ outputs: ok\n");
+}
+
+// MX Matmul through the mirror with the reference's layouts of an untransposed B ([K, N] fp4, scaleB [K/64][N][2]) against the
+// K-major form of the same operands: identical bits.
+static void TestMxLayouts()
+{
+    using namespace AscendC;
+    const int M = 128, N = 192, K = 256, SK = K / 32;
+    std::mt19937 rng(14);
+    std::uniform_int_distribution<int> code(0, 15), sc(124, 130);
+    std::vector<uint8_t> ca(static_cast<size_t>(M) * K), cb(static_cast<size_t>(K) * N);   // fp4 codes, A [M, K], B [K, N]
+    for (auto& v : ca) v = static_cast<uint8_t>(code(rng));
+    for (auto& v : cb) v = static_cast<uint8_t>(code(rng));
+    std::vector<uint8_t> sa(static_cast<size_t>(M) * SK), sbT(static_cast<size_t>(N) * SK);     // scaleA [M, SK], scaleB^T [N, SK]
+    for (auto& v : sa) v = static_cast<uint8_t>(sc(rng));
+    for (auto& v : sbT) v = static_cast<uint8_t>(sc(rng));
+    std::vector<fp4x2_e2m1_t> a(static_cast<size_t>(M) * K / 2), bNd(static_cast<size_t>(K) * N / 2), bKm(static_cast<size_t>(N) * K / 2);
+    for (int m = 0; m < M; ++m)
+        for (int k = 0; k < K; k += 2) a[(static_cast<size_t>(m) * K + k) / 2].bits = static_cast<uint8_t>(ca[static_cast<size_t>(m) * K + k] | (ca[static_cast<size_t>(m) * K + k + 1] << 4));
+    for (int k = 0; k < K; ++k)
+        for (int n = 0; n < N; n += 2) bNd[(static_cast<size_t>(k) * N + n) / 2].bits = static_cast<uint8_t>(cb[static_cast<size_t>(k) * N + n] | (cb[static_cast<size_t>(k) * N + n + 1] << 4));
+    for (int n = 0; n < N; ++n)
+        for (int k = 0; k < K; k += 2) bKm[(static_cast<size_t>(n) * K + k) / 2].bits = static_cast<uint8_t>(cb[static_cast<size_t>(k) * N + n] | (cb[static_cast<size_t>(k + 1) * N + n] << 4));
+    std::vector<fp8_e8m0_t> vsa(sa.size()), vsbT(sbT.size()), vsbP(sbT.size());
+    for (size_t i = 0; i < sa.size(); ++i) vsa[i].bits = sa[i];
+    for (size_t i = 0; i < sbT.size(); ++i) vsbT[i].bits = sbT[i];
+    for (int p = 0; p < SK / 2; ++p)
+        for (int n = 0; n < N; ++n)
+            for (int j = 0; j < 2; ++j) vsbP[(static_cast<size_t>(p) * N + n) * 2 + j].bits = sbT[static_cast<size_t>(n) * SK + 2 * p + j];
+    DevBuf<fp4x2_e2m1_t> dA(a), dBnd(bNd), dBkm(bKm);
+    DevBuf<fp8_e8m0_t> dSa(vsa), dSbT(vsbT), dSbP(vsbP);
+    DevBuf<float> dC1(static_cast<size_t>(M) * N), dC2(static_cast<size_t>(M) * N);
+    TCubeTiling tiling{};
+    tiling.usedCoreNum = 1;
+    tiling.M = tiling.singleCoreM = M;
+    tiling.N = tiling.singleCoreN = N;
+    tiling.Ka = tiling.Kb = tiling.singleCoreK = K;
+    tiling.baseM = 128;
+    tiling.baseN = 256;
+    tiling.baseK = 256;
+    {
+        TPipe pipe;
+        using TA = MatmulTypeWithScale<TPosition::GM, TPosition::GM, CubeFormat::ND, fp4x2_e2m1_t, false>;
+        using TBT = MatmulTypeWithScale<TPosition::GM, TPosition::GM, CubeFormat::ND, fp4x2_e2m1_t, true>;
+        using TBN = MatmulTypeWithScale<TPosition::GM, TPosition::GM, CubeFormat::ND, fp4x2_e2m1_t, false>;
+        using TC = MatmulType<TPosition::GM, CubeFormat::ND, float>;
+        GlobalTensor<fp4x2_e2m1_t> ga, gbn, gbk;
+        GlobalTensor<fp8_e8m0_t> gsa, gsbt, gsbp;
+        GlobalTensor<float> gc1, gc2;
+        ga.SetGlobalBuffer(dA.p, a.size());
+        gbn.SetGlobalBuffer(dBnd.p, bNd.size());
+        gbk.SetGlobalBuffer(dBkm.p, bKm.size());
+        gsa.SetGlobalBuffer(dSa.p, vsa.size());
+        gsbt.SetGlobalBuffer(dSbT.p, vsbT.size());
+        gsbp.SetGlobalBuffer(dSbP.p, vsbP.size());
+        gc1.SetGlobalBuffer(dC1.p, dC1.n);
+        gc2.SetGlobalBuffer(dC2.p, dC2.n);
+        {
+            Matmul<TA, TBT, TC, TC, CFG_MDL, MatmulCallBackFunc<>, MatmulWithScalePolicy> mm;
+            REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, &tiling);
+            mm.SetTensorA(ga, false);
+            mm.SetTensorB(gbk, true);
+            mm.SetTensorScaleA(gsa, false);
+            mm.SetTensorScaleB(gsbt, true);
+            mm.IterateAll(gc1);
+            mm.End();
+        }
+        {
+            Matmul<TA, TBN, TC, TC, CFG_MDL, MatmulCallBackFunc<>, MatmulWithScalePolicy> mm;
+            REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, &tiling);
+            mm.SetTensorA(ga, false);
+            mm.SetTensorB(gbn, false);          // [K, N]
+            mm.SetTensorScaleA(gsa, false);
+            mm.SetTensorScaleB(gsbp, false);    // [K/64][N][2]
+            mm.IterateAll(gc2);
+            mm.IterateAll(gc2);                 // the transposed copy of B is kept between calls
+            mm.End();
+        }
+    }
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<float> c1 = dC1.Download(), c2 = dC2.Download();
+    int bad = 0, nonzero = 0;
+    for (size_t i = 0; i < c1.size(); ++i) {
+        bad += std::memcmp(&c1[i], &c2[i], sizeof(float)) != 0;
+        nonzero += c1[i] != 0.0f;
+    }
+    CHECK(bad == 0 && nonzero > 0, "MX layouts: %d differ, %d non-zero", bad, nonzero);
+    std::printf("MX Matmul, [K, N] B with pair-ordered scaleB == K-major form: ok\n");
+}
+
 static void TestErrorLatch()
 {
     AscendC::ClearLastError();
@@ -745,6 +1079,11 @@ int main()
     TestAntiQuant();
     TestConstantTiling();
     TestIterateBatch();
+    TestBatchLayout<LayoutMode::BSNGD>("BSNGD");
+    TestBatchLayout<LayoutMode::SBNGD>("SBNGD");
+    TestIterateNBatch();
+    TestBaseBlocksAndOutputFormats();
+    TestMxLayouts();
     TestErrorLatch();
     std::printf(g_fail ? "%d checks failed\n" : "hostapi ok\n", g_fail);
     return g_fail ? 1 : 0;

@@ -29,6 +29,10 @@ input+output samples as .npz, so the tests can pin the CPU oracle without the re
   mxfp4.npz          05_best_practices/01_matrix_compute/matmul_mxfp4_high_performance/scripts/gen_data.py:39-69
                      (needs the absent en_dtypes package; its float64 golden formula is applied here to
                      e2m1 operands made with ml_dtypes.float4_e2m1fn, on a reduced shape)
+  mxfp4_nd.npz       the same example's layouts for a B that is not transposed: [K, N] packed by its own pack_two_fp4 (the
+                     function is taken out of the file's syntax tree and executed, since importing the file needs en_dtypes),
+                     scaleB re-ordered to [sK/2, N, 2] as in gen_data.py:63; A transposed ([K, M]) with scaleA in the same pair
+                     order, as 04_advanced_api/00_matmul/matmul_mx/scripts/gen_data.py:71-76 does for is_trans_scalea
   casts.npz          CAST_RINT rule of docs/zh/api/SIMD-API/basic_api/data_structures/precision_conversion.md:19-23
                      with its worked examples (1.5 -> 2, 2.5 -> 2, 2^6+0.5 -> 2^6, 2^7-0.5 -> 2^7-1 saturated)
                      plus IEEE boundary cases worked out by hand from the same rule
@@ -283,6 +287,43 @@ def mxfp4(ref):
                         golden_bf16_bits=golden.astype(ml_dtypes.bfloat16).view(np.uint16))
 
 
+def function_from_file(path, name):
+    """Compiles one top-level function of a Python file without importing the file (whose imports may be unavailable)."""
+    import ast
+    tree = ast.parse(open(path).read())
+    fn = next(node for node in tree.body if isinstance(node, ast.FunctionDef) and node.name == name)
+    ns = {"np": np}
+    exec(compile(ast.Module(body=[fn], type_ignores=[]), path, "exec"), ns)
+    return ns[name]
+
+
+def mxfp4_nd(ref):
+    import ml_dtypes
+    path = os.path.join(ref, EX, "05_best_practices/01_matrix_compute/matmul_mxfp4_high_performance/scripts/gen_data.py")
+    pack_two_fp4 = function_from_file(path, "pack_two_fp4")
+    rng = np.random.default_rng(23)
+    m, n, k = 48, 80, 256
+    sk = int(np.ceil(k / 64) * 2)
+    grid = np.array([0, 0.5, 1, 1.5, 2, 3, 4, 6, -0.0, -0.5, -1, -1.5, -2, -3, -4, -6], np.float32)
+    ca = rng.integers(0, 16, (m, k)).astype(np.uint8)      # A [M, K]
+    cb = rng.integers(0, 16, (k, n)).astype(np.uint8)      # B [K, N]: not transposed, the example's layout
+    x1 = grid[ca].astype(ml_dtypes.float4_e2m1fn)
+    x2 = grid[cb].astype(ml_dtypes.float4_e2m1fn)
+    s1 = rng.integers(120, 134, (m, sk)).astype(np.uint8)  # scaleA [M, sK]
+    s2 = rng.integers(120, 134, (sk, n)).astype(np.uint8)  # scaleB [sK, N]
+    x1f = x1.astype(np.float64) * np.repeat(2.0 ** (s1.astype(np.float64) - 127), 32, axis=1)
+    x2f = x2.astype(np.float64) * np.repeat(2.0 ** (s2.astype(np.float64) - 127), 32, axis=0)
+    golden = np.matmul(x1f, x2f)
+    np.savez_compressed(
+        os.path.join(HERE, "mxfp4_nd.npz"),
+        a=pack_two_fp4(x1), b_nd=pack_two_fp4(x2),                                           # gen_data.py:64-65
+        a_t=pack_two_fp4(np.ascontiguousarray(x1.T)),                                        # A stored [K, M]
+        sa=s1, sb_paired=np.ascontiguousarray(s2.reshape(sk // 2, 2, n).transpose(0, 2, 1)),  # gen_data.py:63
+        sa_paired=np.ascontiguousarray(s1.T.reshape(sk // 2, 2, m).transpose(0, 2, 1)),      # matmul_mx gen_data.py:71-74
+        b_kmajor=pack_two_fp4(np.ascontiguousarray(x2.T)), sb=np.ascontiguousarray(s2.T),    # the transposed-B form of the same operands
+        golden_f64=golden)
+
+
 def casts(ref):
     # precision_conversion.md: the CAST_RINT rule and its worked examples, plus hand-derived boundary cases
     np.savez_compressed(
@@ -303,6 +344,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("ASC_REFERENCE_ROOT", "reference"))
     args = ap.parse_args()
-    for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, logsoftmax, softmaxgrad, softmaxflashv2, quant, antiquant, dequant, grouped, mxfp4, casts):
+    for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, logsoftmax, softmaxgrad, softmaxflashv2, quant, antiquant, dequant, grouped, mxfp4, mxfp4_nd, casts):
         fn(args.ref)
         print("wrote", fn.__name__)

@@ -332,7 +332,7 @@ def test_gemm_mxfp4_prepacked_scales(m, n, k):
         assert (o == outs[0]).all()
     ref = orc.gemm_mxf4(a, sa, b, sb, base_k=256)
     assert np.allclose(outs[0].view(np.float32), ref, rtol=RTOL, atol=ATOL)
-    assert ab.gemm(ab.KIND_MXFP4, m, n, k, d_a, d_b, d_c, ab.F32, trans_b=True, scale_a=d_sa, scale_b=d_sb, scale_flags=4) == ab.EINVAL
+    assert ab.gemm(ab.KIND_MXFP4, m, n, k, d_a, d_b, d_c, ab.F32, trans_b=True, scale_a=d_sa, scale_b=d_sb, scale_flags=16) == ab.EINVAL
 
 
 def test_gemm_mxfp4_two_streams_with_different_scales():
@@ -367,6 +367,108 @@ def test_gemm_mxfp4_two_streams_with_different_scales():
         assert (d_c.download().view(np.uint32) == refs[i]).all(), f"stream {i} read the other call's scales"
     for sp in streams:
         ab.lib().ascb200_stream_destroy(sp)
+
+
+def test_gemm_mxfp4_reference_layouts_of_untransposed_operands(golden_dir):
+    """MX Matmul in the layouts the reference's examples write: B [K, N] (two N-neighbours per byte) with scaleB [sK/2, N, 2],
+    and a transposed A [K, M] with scaleA in the same pair order.  Every combination gives the bytes of the K-major call."""
+    import os
+    ab = dev()
+    g = np.load(os.path.join(golden_dir, "mxfp4_nd.npz"))
+    m, n, k = g["a"].shape[0], g["b_kmajor"].shape[0], g["a"].shape[1] * 2
+    d = {key: ab.to_dev(g[key]) for key in ("a", "a_t", "b_nd", "b_kmajor", "sa", "sa_paired", "sb", "sb_paired")}
+
+    def run(a, ta, sa, fa, b, tb, sb, fb):
+        d_c = ab.empty((m, n), np.float32)
+        d_c.fill(0xFF)
+        ab.check(ab.gemm(ab.KIND_MXFP4, m, n, k, d[a], d[b], d_c, ab.F32, trans_a=ta, trans_b=tb, scale_a=d[sa], scale_b=d[sb], scale_flags=fa | fb))
+        ab.sync()
+        return d_c.download()
+
+    base = run("a", False, "sa", 0, "b_kmajor", True, "sb", 0)
+    assert np.allclose(base, g["golden_f64"], rtol=RTOL, atol=ATOL)
+    for args in (("a", False, "sa", 0, "b_nd", False, "sb_paired", ab.SCALE_B_PAIRED),
+                 ("a_t", True, "sa_paired", ab.SCALE_A_PAIRED, "b_kmajor", True, "sb", 0),
+                 ("a_t", True, "sa_paired", ab.SCALE_A_PAIRED, "b_nd", False, "sb_paired", ab.SCALE_B_PAIRED),
+                 ("a", False, "sa", 0, "b_nd", False, "sb", 0)):   # ND operand with plain scales
+        assert (run(*args).view(np.uint32) == base.view(np.uint32)).all(), args
+    # prepacked from the pair order
+    pb = ab.mx_scale_prepack(d["sb_paired"], n, k, paired=True)
+    d_c = ab.empty((m, n), np.float32)
+    ab.check(ab.gemm(ab.KIND_MXFP4, m, n, k, d["a"], d["b_nd"], d_c, ab.F32, trans_b=False, scale_a=d["sa"], scale_b=pb, scale_flags=ab.SCALE_B_PREPACKED))
+    ab.sync()
+    assert (d_c.download().view(np.uint32) == base.view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("rows,cols", [(256, 64), (512, 192), (300, 70), (64, 2), (2, 130), (1024, 1000)])
+def test_fp4_transpose(rows, cols):
+    ab = dev()
+    rng = np.random.default_rng(rows + cols)
+    codes = rng.integers(0, 16, (rows, cols), dtype=np.uint8)
+    src = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
+    want = (codes.T[:, 0::2] | (codes.T[:, 1::2] << 4)).astype(np.uint8)
+    d_dst = ab.DevBuf(want.size + 64)
+    d_dst.fill(0xEE)
+    ab.check(ab.lib().ascb200_fp4_transpose(ab.to_dev(src).ptr, d_dst.ptr, rows, cols, None))
+    ab.sync()
+    got = d_dst.download(shape=(want.size + 64,), dtype=np.uint8)
+    assert (got[want.size:] == 0xEE).all()
+    assert (got[:want.size].reshape(want.shape) == want).all()
+    assert ab.lib().ascb200_fp4_transpose(ab.to_dev(src).ptr, d_dst.ptr, rows + 1, cols, None) == ab.EINVAL
+
+
+@pytest.mark.parametrize("layout", [1, 2])
+@pytest.mark.parametrize("case", ["f16_f32", "f16_f16", "i8_s32", "i8_bf16_dequant", "i8_s8_req8", "f16_pair"])
+def test_gemm_output_layouts_column_major_and_nz(layout, case):
+    """C written column-major (CubeFormat::COLUMN_MAJOR) or fractal (CubeFormat::NZ: blocks of 16 columns, 32 for 1-byte outputs,
+    row-major inside a block) holds the values of the row-major result, nothing beyond its last element is written."""
+    ab = dev()
+    rng = np.random.default_rng(layout * 10 + len(case))
+    m, n, k = (200, 328, 256) if case != "f16_pair" else (2304, 2560, 128)
+    kw = {}
+    if case.startswith("f16"):
+        a = f16_bits(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+        b = f16_bits(rng.uniform(-1, 1, (n, k)).astype(np.float32))
+        kind, c_dtype = ab.KIND_F16, (ab.F16 if case == "f16_f16" else ab.F32)
+    else:
+        a = rng.integers(-127, 128, (m, k), dtype=np.int8)
+        b = rng.integers(-127, 128, (n, k), dtype=np.int8)
+        kind = ab.KIND_S8
+        if case == "i8_s32":
+            c_dtype = ab.S32
+        elif case == "i8_bf16_dequant":
+            c_dtype = ab.BF16
+            kw = dict(epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, tok=ab.to_dev(rng.uniform(1e-3, 1e-2, m).astype(np.float32)),
+                      ch=ab.to_dev(rng.uniform(1e-3, 1e-2, n).astype(np.float32)))
+        else:
+            c_dtype = ab.S8
+            kw = dict(epilogue=ab.EPI_FIXPIPE_QUANT, quant=ab.to_dev(quant_params(rng.uniform(1e-4, 3e-4, n).astype(np.float32))))
+    np_t = NP_OUT[c_dtype]
+    esz = np.dtype(np_t).itemsize
+    d_a, d_b = ab.to_dev(a), ab.to_dev(b)
+    d_ref = ab.empty((m, n), np_t)
+    ab.check(ab.gemm(kind, m, n, k, d_a, d_b, d_ref, c_dtype, trans_b=True, **kw))
+    ab.sync()
+    ref = d_ref.download()
+    c0 = 32 if esz == 1 else 16
+    blocks = (n + c0 - 1) // c0
+    elems = m * n if layout == 1 else blocks * m * c0
+    d_c = ab.DevBuf(elems * esz + 64)
+    d_c.fill(0x5A)
+    ab.check(ab.gemm(kind, m, n, k, d_a, d_b, d_c, c_dtype, trans_b=True, c_layout=layout, **kw))
+    ab.sync()
+    raw = d_c.download(shape=(elems * esz + 64,), dtype=np.uint8)
+    assert (raw[elems * esz:] == 0x5A).all()
+    got = raw[:elems * esz].view(np_t)
+    if layout == 1:
+        assert np.ascontiguousarray(got.reshape(n, m).T).tobytes() == np.ascontiguousarray(ref).tobytes()
+    else:
+        nz = got.reshape(blocks, m, c0)
+        back = nz.transpose(1, 0, 2).reshape(m, blocks * c0)[:, :n]
+        assert np.ascontiguousarray(back).tobytes() == np.ascontiguousarray(ref).tobytes()
+        if n % c0:   # the padding columns of the last block are left untouched
+            pad = nz[-1][:, n % c0:]
+            assert (np.ascontiguousarray(pad).view(np.uint8) == 0x5A).all()
 
 
 def test_gemm_mxfp4_requant_and_bf16():
@@ -754,3 +856,26 @@ def test_grouped_random_counts_and_shapes():
         ref = orc.grouped_i8(x, w, counts, tok, ch, orc.BF16 if c_dtype == ab.BF16 else orc.F16, trans_b=trans_b)
         got = host[:m * n * 2].view(np.uint16).reshape(m, n)
         assert (got == ref).all(), f"case {case}: counts {counts.tolist()} n {n} k {k}: {(got != ref).sum()} differ"
+
+
+def test_bounded_wait_expires_and_reports():
+    """Failure detection without a fault: a wait that nothing can satisfy runs into its time limit, the kernel returns
+    normally, the status word reports it once (ASCB200_ETIMEOUT), is cleared by the read, and the device keeps working."""
+    import ctypes as C
+    ab = dev()
+    ab.sync()
+    res = (C.c_uint32 * 3)()
+    ab.check(ab.lib().ascb200_selftest_bounded_wait(res, None), "selftest")
+    assert res[0] == 1 and res[1] == 1, list(res)
+    assert 150 <= res[2] <= 5000, f"waited {res[2] * 1024} cycles for a limit of 200000"
+    st = C.c_uint32(0)
+    assert ab.lib().ascb200_device_status(None, C.byref(st)) == ab.ETIMEOUT and st.value & 1
+    assert ab.lib().ascb200_device_status(None, C.byref(st)) == 0 and st.value == 0   # cleared by the read above
+    # the context is intact: a GEMM right after it is exact
+    rng = np.random.default_rng(3)
+    a = rng.integers(-127, 128, (128, 256), dtype=np.int8)
+    b = rng.integers(-127, 128, (128, 256), dtype=np.int8)
+    d_c = ab.empty((128, 128), np.int32)
+    ab.check(ab.gemm(ab.KIND_S8, 128, 128, 256, ab.to_dev(a), ab.to_dev(b), d_c, ab.S32, trans_b=True))
+    ab.sync()
+    assert (d_c.download() == orc.gemm_i8(a, b, trans_b=True)).all()

@@ -290,3 +290,25 @@ def test_quant_policies_reduce_to_the_pinned_forms(golden_dir):
     for dst in (orc.F16, orc.BF16):
         a = orc.dequant_policy(acc, sc.reshape(1, -1), orc.F32, dst, 1, k_dim=0, group_size=gs)
         assert (a == orc.dequant(acc, sc, dst, orc.F32)).all()
+
+
+def _fp4_codes(packed):
+    """packed [R, C/2] (even column in the low nibble) -> codes [R, C]."""
+    out = np.empty((packed.shape[0], packed.shape[1] * 2), np.uint8)
+    out[:, 0::2], out[:, 1::2] = packed & 15, packed >> 4
+    return out
+
+
+def test_mxfp4_layouts_of_the_untransposed_b_recipe(golden_dir):
+    """The reference's layouts for an MX Matmul whose B is not transposed: [K, N] packed two N-neighbours per byte and scaleB
+    [sK/2, N, 2].  They are the K-major operands in another order; the oracle on the re-ordered operands meets the float64 golden."""
+    g = load(golden_dir, "mxfp4_nd.npz")
+    codes_b = _fp4_codes(g["b_nd"])                       # [K, N]
+    assert (_fp4_codes(g["b_kmajor"]) == codes_b.T).all()
+    assert (_fp4_codes(g["a_t"]) == _fp4_codes(g["a"]).T).all()
+    sk2, n, _ = g["sb_paired"].shape
+    assert (g["sb_paired"].transpose(1, 0, 2).reshape(n, 2 * sk2) == g["sb"]).all()
+    m = g["sa"].shape[0]
+    assert (g["sa_paired"].transpose(1, 0, 2).reshape(m, 2 * sk2) == g["sa"]).all()
+    ref = orc.gemm_mxf4(g["a"], g["sa"], g["b_kmajor"], g["sb"], base_k=256)
+    assert np.allclose(ref, g["golden_f64"], rtol=1e-5, atol=1e-2)
