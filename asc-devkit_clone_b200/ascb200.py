@@ -12,7 +12,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
 F32, F16, BF16, S8, S32, FP4, FP8_E4M3, FP8_E5M2 = 0, 1, 2, 3, 4, 5, 6, 7
-KIND_F16, KIND_BF16, KIND_S8, KIND_MXFP4 = 0, 1, 2, 3
+KIND_F16, KIND_BF16, KIND_S8, KIND_MXFP4, KIND_MXFP8_E4M3, KIND_MXFP8_E5M2 = 0, 1, 2, 3, 4, 5
 EPI_CAST, EPI_FIXPIPE_QUANT, EPI_DEQUANT_TOKEN_CHANNEL = 0, 1, 2
 EINVAL, EALIGN, EUNSUPPORTED, ENODEV, ECUDA, ETIMEOUT, ETOOBIG = -1, -2, -3, -4, -5, -6, -7
 

@@ -78,22 +78,24 @@ template <int KIND, int BLOCK_N>
 struct Cfg {
     static constexpr int B_TILE_BYTES = BLOCK_N * ROW_BYTES;
     static constexpr int SF_B_BLOCKS = (BLOCK_N + 127) / 128;  // 128-row scale blocks that one B tile touches
-    static constexpr int SF_BYTES = KIND == KIND_MXF4 ? (2 + 2 * SF_B_BLOCKS) * SF_CHUNK_BYTES : 0;
+    static constexpr bool IS_MX = KIND == KIND_MXF4 || KIND == KIND_MXF8;
+    static constexpr int SF_CHUNKS = KIND == KIND_MXF4 ? 2 : 1;  // 512-byte scale chunks (4 scales per row) per 128 rows and K block
+    static constexpr int SF_BYTES = IS_MX ? (1 + SF_B_BLOCKS) * SF_CHUNKS * SF_CHUNK_BYTES : 0;
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + SF_BYTES;
     // output staging for bulk tensor stores: per epilogue warp 2 KB (2-byte chunk) + 1 KB (1-byte chunk)
-    static constexpr int EPI_BYTES_PER_WARP = (KIND == KIND_MXF4 && BLOCK_N == 256) ? 0 : 3072;
+    static constexpr int EPI_BYTES_PER_WARP = (IS_MX && BLOCK_N == 256) ? 0 : 3072;
     static constexpr int EPI_BYTES = NUM_EPI_WARPS * EPI_BYTES_PER_WARP;
     static constexpr int FIXED_BYTES = 1024 /*alignment slack*/ + 256 /*barriers*/ + 2 * (MAX_GROUPS + 1) * static_cast<int>(sizeof(int)) + EPI_BYTES;
     static constexpr int NUM_STAGES = std::min(8, (227 * 1024 - FIXED_BYTES) / STAGE_BYTES);
-    static constexpr int ACC_STAGES = (KIND == KIND_MXF4 && BLOCK_N == 256) ? 1 : 2;  // 2 x 256 accumulator columns would leave no TMEM for scales
+    static constexpr int ACC_STAGES = (IS_MX && BLOCK_N == 256) ? 1 : 2;  // 2 x 256 accumulator columns would leave no TMEM for scales
     static constexpr int ACC_COLS = ACC_STAGES * BLOCK_N;
     static constexpr int SF_COLS_PER_STAGE = 24;  // 8 for A + 16 for B
     static constexpr int SF_COL0 = ACC_COLS;
-    static constexpr int TMEM_NEED = ACC_COLS + (KIND == KIND_MXF4 ? NUM_STAGES * SF_COLS_PER_STAGE : 0);
+    static constexpr int TMEM_NEED = ACC_COLS + (IS_MX ? NUM_STAGES * SF_COLS_PER_STAGE : 0);
     static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
     static_assert(TMEM_NEED <= 512, "TMEM budget");
     // bytes of one K step of the instruction (32 in every kind) -> elements along K per tile row
-    static constexpr int BLOCK_K = KIND == KIND_F16 ? 64 : KIND == KIND_I8 ? 128 : 256;
+    static constexpr int BLOCK_K = KIND == KIND_F16 ? 64 : KIND == KIND_MXF4 ? 256 : 128;
     static constexpr int UMMA_K = BLOCK_K / 4;
     static constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + FIXED_BYTES;
 };
@@ -816,6 +818,12 @@ __device__ __forceinline__ void issue_sf_copies(const Cursor& c)
             sf_copy_issue<PAIR>(c.sf_tmem + 8 + rb * 4, c.sf_lo + 64 + rb * 64, sf_hi);
             sf_copy_issue<PAIR>(c.sf_tmem + 16 + rb * 4, c.sf_lo + 96 + rb * 64, sf_hi);
         }
+    } else if constexpr (KIND == KIND_MXF8) {
+        // one chunk per 128 rows and K block (128 elements = four scales per row): A, then the blocks of B
+        constexpr uint32_t sf_hi = (128u >> 4) | (1u << 14);
+        sf_copy_issue<PAIR>(c.sf_tmem + 0, c.sf_lo, sf_hi);
+#pragma unroll
+        for (int rb = 0; rb < SF_B_BLOCKS; ++rb) sf_copy_issue<PAIR>(c.sf_tmem + 8 + rb * 4, c.sf_lo + 32 + rb * 32, sf_hi);
     }
 }
 
@@ -830,6 +838,13 @@ __device__ __forceinline__ void issue_mmas(const Cursor& c, uint32_t d_tmem, uin
         mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 2, hi_word, c.b_lo + 2, hi_word, idesc_hi_sf, c.sf_tmem, sfb, 1u);
         mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 4, hi_word, c.b_lo + 4, hi_word, idesc, c.sf_tmem + 4, sfb + 8, 1u);
         mma_issue_mxf4<PAIR>(d_tmem, c.a_lo + 6, hi_word, c.b_lo + 6, hi_word, idesc_hi_sf, c.sf_tmem + 4, sfb + 8, 1u);
+    } else if constexpr (KIND == KIND_MXF8) {
+        // instruction i of the K block takes byte i of the scale columns (selectors in bits 4-5 and 29-30 of the descriptor)
+        const uint32_t sfb = c.sf_tmem + 8 + sfb_col_offset;
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i)
+            mma_issue_mxf8(d_tmem, c.a_lo + i * a_kstep16, hi_word, c.b_lo + i * b_kstep16, hi_word, idesc | (i << 4) | (i << 29), c.sf_tmem, sfb,
+                           (first && i == 0) ? 0u : 1u);
     } else {
         mma_issue<KIND, PAIR>(d_tmem, c.a_lo, hi_word, c.b_lo, hi_word, idesc, first ? 0u : 1u);
         mma_issue<KIND, PAIR>(d_tmem, c.a_lo + a_kstep16, hi_word, c.b_lo + b_kstep16, hi_word, idesc, 1u);
@@ -938,14 +953,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                         for (int j = 0; j < BLOCK_N / MN_PER_BOX; ++j) tma_load_3d(sb + j * BOX_BYTES, &tmap_b, t.n0 + j * MN_PER_BOX, k0, t.group, bar);
                     }
-                    if constexpr (KIND == KIND_MXF4) {
+                    if constexpr (C::IS_MX) {
                         const uint32_t ssf = sb + C::B_TILE_BYTES;
-                        const size_t kc = static_cast<size_t>(kb) * 2;
-                        bulk_load(ssf, p.sfa + (static_cast<size_t>(t.row0 / 128) * p.sf_kc + kc) * SF_CHUNK_BYTES, 2 * SF_CHUNK_BYTES, bar);
+                        constexpr uint32_t SF_LOAD = C::SF_CHUNKS * SF_CHUNK_BYTES;   // the chunks of this K block of one 128-row block
+                        const size_t kc = static_cast<size_t>(kb) * C::SF_CHUNKS;
+                        bulk_load(ssf, p.sfa + (static_cast<size_t>(t.row0 / 128) * p.sf_kc + kc) * SF_CHUNK_BYTES, SF_LOAD, bar);
 #pragma unroll
                         for (int rb = 0; rb < C::SF_B_BLOCKS; ++rb)
-                            bulk_load(ssf + (1 + rb) * 2 * SF_CHUNK_BYTES,
-                                      p.sfb + (static_cast<size_t>(t.n0 / 128 + rb) * p.sf_kc + kc) * SF_CHUNK_BYTES, 2 * SF_CHUNK_BYTES, bar);
+                            bulk_load(ssf + (1 + rb) * SF_LOAD, p.sfb + (static_cast<size_t>(t.n0 / 128 + rb) * p.sf_kc + kc) * SF_CHUNK_BYTES, SF_LOAD, bar);
                     }
                 }
                 __syncwarp();
@@ -1573,7 +1588,9 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     return ASCB200_OK;
 }
 
-int elem_bits(int kind) { return kind == ASCB200_KIND_MXFP4 ? 4 : kind == ASCB200_KIND_S8 ? 8 : 16; }
+bool is_mxfp8(int kind) { return kind == ASCB200_KIND_MXFP8_E4M3 || kind == ASCB200_KIND_MXFP8_E5M2; }
+bool is_mx(int kind) { return kind == ASCB200_KIND_MXFP4 || is_mxfp8(kind); }
+int elem_bits(int kind) { return kind == ASCB200_KIND_MXFP4 ? 4 : (kind == ASCB200_KIND_S8 || is_mxfp8(kind)) ? 8 : 16; }
 
 // Device resources of one call when they do not come from the per-device state of ascb200_init.
 struct FixedResources {
@@ -1597,7 +1614,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     if (d->c_layout != ASCB200_C_ROW_MAJOR && (d->atomic || d->c2_dev || groups > 0)) return ASCB200_EUNSUPPORTED;
     if (d->scale_flags & ~(ASCB200_SCALE_A_PREPACKED | ASCB200_SCALE_B_PREPACKED | ASCB200_SCALE_A_PAIRED | ASCB200_SCALE_B_PAIRED)) return ASCB200_EINVAL;
     const int kind = d->kind;
-    if (kind < ASCB200_KIND_F16 || kind > ASCB200_KIND_MXFP4) return ASCB200_EINVAL;
+    if (kind < ASCB200_KIND_F16 || kind > ASCB200_KIND_MXFP8_E5M2) return ASCB200_EINVAL;
     const bool acc_int = kind == ASCB200_KIND_S8;
     const bool grouped = groups > 0;
     if (grouped && (groups > MAX_GROUPS)) return ASCB200_ETOOBIG;
@@ -1658,10 +1675,12 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     // ---- operands ----
     const int bits = elem_bits(kind);
     const int k = d->k, m = d->m, n = d->n;
-    if (kind == ASCB200_KIND_MXFP4) {
+    if (is_mx(kind)) {
         // K a multiple of 64 like the reference's MmadMx
         if (k % 64 != 0) return ASCB200_EINVAL;
         if (!d->scale_a_dev || !d->scale_b_dev) return ASCB200_EINVAL;
+    }
+    if (kind == ASCB200_KIND_MXFP4) {
         if (d->trans_a || !d->trans_b) {
             // The tensor core takes fp4 operands K-major only.  An operand stored the other way round ([K, M] / the reference's
             // ND [K, N], two M- / N-neighbours per byte) is transposed into this stream's scratch first, then the call
@@ -1718,7 +1737,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     // much time as useful ones (64 groups of 512 rows on average: masked pairs 490 us, single-CTA tiles 406-475 us).
     const bool group_swap_ok = grouped && !(getenv("ASCB200_NO_GROUP_SWAP") && getenv("ASCB200_NO_GROUP_SWAP")[0] == '1');
     const bool pair_allowed = pair_possible && (!grouped || group_swap_ok || m / groups >= 16 * BLOCK_M);
-    const int wide = kind == ASCB200_KIND_MXFP4 ? 192 : 256;   // fp4 at 256 columns cannot double-buffer its accumulators in TMEM
+    const int wide = is_mx(kind) ? 192 : 256;   // block-scaled kinds at 256 columns cannot double-buffer their accumulators in TMEM
     int block_n = 64;
     bool use_pair = false;
     {
@@ -1728,7 +1747,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         Cand cands[20];
         int num_cands = 0;
         cands[num_cands++] = {wide, true, 1.0};
-        if (kind != ASCB200_KIND_MXFP4 && d->trans_b && !(grouped && group_swap_ok)) {
+        if (!is_mx(kind) && d->trans_b && !(grouped && group_swap_ok)) {
             // CTA-pair tiles of any width that is a multiple of 16: a narrower tile re-reads A more often per column
             // (128 columns measured at 0.75 of the full width's rate), but may fill the last wave far better
             for (int bn = 240; bn >= 64; bn -= 16) cands[num_cands++] = {bn, true, 1.0 / (1.0 + 0.33 * (256.0 / bn - 1.0))};
@@ -1739,7 +1758,8 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         for (int ci = 0; ci < num_cands; ++ci) {
             const Cand& c = cands[ci];
             if (c.pair && !pair_allowed) continue;
-            if (c.bn == 64 && kind == ASCB200_KIND_MXFP4) continue;                          // scale blocks span 128 rows
+            if (c.bn == 64 && is_mx(kind)) continue;                                         // scale blocks span 128 rows
+            if (c.pair && is_mxfp8(kind)) continue;                                          // block-scaled fp8 runs on single CTAs
             if (c.bn == 64 && !c.pair && kind == ASCB200_KIND_S8 && !d->trans_b) continue;   // N-contiguous int8 B comes in boxes of 128 columns
             if (c.bn > 64 && n <= c.bn / 2 && (c.pair || c.bn != 128)) continue;             // do not pad N by more than 2x
             const long long n_tiles = (n + c.bn - 1) / c.bn;
@@ -1760,7 +1780,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     if (const char* force = getenv("ASCB200_PAIR_N")) {
         // testing / tuning override: CTA-pair kernel with this tile width where the kernel supports it
         const int bn = atoi(force);
-        if (pair_possible && kind != ASCB200_KIND_MXFP4 && (d->trans_b || bn == 256) && bn >= 16 && bn <= 256 && bn % 16 == 0) {
+        if (pair_possible && !is_mx(kind) && (d->trans_b || bn == 256) && bn >= 16 && bn <= 256 && bn % 16 == 0) {
             block_n = bn;
             use_pair = true;
         }
@@ -1788,18 +1808,18 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     p.b_mn = d->trans_b ? 0 : 1;
     p.groups = grouped ? groups : 0;
     p.pair_n = block_n;
-    p.allow_m64 = kind != ASCB200_KIND_MXFP4 && !(getenv("ASCB200_NO_M64") && getenv("ASCB200_NO_M64")[0] == '1');
+    p.allow_m64 = !is_mx(kind) && !(getenv("ASCB200_NO_M64") && getenv("ASCB200_NO_M64")[0] == '1');
     p.group_swap = (grouped && use_pair && block_n == 256 && group_swap_ok) ? 1 : 0;
     p.group_counts = reinterpret_cast<const long long*>(group_counts);
     p.status = fixed ? fixed->status_dev : st->status_dev;
     p.epi = e;
 
-    if (kind == ASCB200_KIND_MXFP4) {
+    if (is_mx(kind)) {
         // Scale factors in the 512-byte chunk order the kernels copy into TMEM (layout documented at retile_scales_kernel):
         // taken as they are when the caller prepacked them (ascb200_mx_scale_prepack: static weights), else re-tiled here
         // into scratch that belongs to `stream`, so that calls on different streams do not overwrite each other's scales.
         const int ks = k / 32;
-        const int kc = 2 * p.num_k_blocks;
+        const int kc = 2 * ((k + 255) / 256);   // chunks (4 scales each) per 128-row block: the same pitch for every MX kind and for prepacked tensors
         const bool pre_a = (d->scale_flags & ASCB200_SCALE_A_PREPACKED) != 0, pre_b = (d->scale_flags & ASCB200_SCALE_B_PREPACKED) != 0;
         const int rba = (m + 127) / 128, rbb = (n + 127) / 128 + kSfPadBlocks;  // B tiles may read up to two blocks past the last row
         const size_t bytes_a = pre_a ? 0 : static_cast<size_t>(rba) * kc * SF_CHUNK_BYTES, bytes_b = pre_b ? 0 : static_cast<size_t>(rbb) * kc * SF_CHUNK_BYTES;
@@ -1874,6 +1894,13 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         const uint32_t fmt = kind == ASCB200_KIND_BF16 ? 1u : 0u;
         p.idesc = make_idesc(1, fmt, fmt, a_mn, b_mn, 2 * BLOCK_M, block_n);
         return launch_gemm_pair<KIND_F16, 256>(ta, tb, ta, tb, outs, p, clusters, stream);
+    }
+    if (is_mxfp8(kind)) {
+        const uint32_t fmt = kind == ASCB200_KIND_MXFP8_E5M2 ? 1u : 0u;
+        p.idesc = make_idesc_mxf8(fmt, fmt, a_mn, b_mn, BLOCK_M, block_n);
+        if (block_n == 256) return launch_gemm<KIND_MXF8, 256>(ta, tb, outs, p, grid, stream);
+        if (block_n == 192) return launch_gemm<KIND_MXF8, 192>(ta, tb, outs, p, grid, stream);
+        return launch_gemm<KIND_MXF8, 128>(ta, tb, outs, p, grid, stream);
     }
     switch (kind) {
         case ASCB200_KIND_F16:

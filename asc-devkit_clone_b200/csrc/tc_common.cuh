@@ -313,7 +313,7 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar)
                  : "memory");
 }
 
-enum : int { KIND_F16 = 0, KIND_I8 = 1, KIND_MXF4 = 2 };
+enum : int { KIND_F16 = 0, KIND_I8 = 1, KIND_MXF4 = 2, KIND_MXF8 = 3 };
 
 template <int KIND>
 __device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
@@ -424,6 +424,17 @@ __device__ __forceinline__ void mma_issue_mxf4(uint32_t d_tmem, uint32_t a_lo, u
     else ASCB200_MMA_ASM("1");
 #undef ASCB200_MMA_ASM
 }
+// Block-scaled fp8 (e4m3 / e5m2 operands, one ue8m0 scale per 32 K elements = one per 32-deep instruction).
+__device__ __forceinline__ void mma_issue_mxf8(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %8, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], da, db, %5, [%6], [%7], p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+}
 template <bool PAIR>
 __device__ __forceinline__ void sf_copy_issue(uint32_t taddr, uint32_t s_lo, uint32_t s_hi)
 {
@@ -471,6 +482,12 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t c_fmt, uint32_t a_fmt
 __host__ __device__ constexpr uint32_t make_idesc_mxf4(uint32_t m, uint32_t n)
 {
     return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24);
+}
+// Instruction descriptor, kind::mxf8f6f4 block scaled: operand formats e4m3 = 0, e5m2 = 1; ue8m0 scales (bit 23); the
+// scale-factor byte selectors (bits 4-5 for B, 29-30 for A: which of a TMEM column's four bytes) are added per instruction.
+__host__ __device__ constexpr uint32_t make_idesc_mxf8(uint32_t a_fmt, uint32_t b_fmt, uint32_t a_mn, uint32_t b_mn, uint32_t m, uint32_t n)
+{
+    return (a_fmt << 7) | (b_fmt << 10) | (a_mn << 15) | (b_mn << 16) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24);
 }
 
 }  // namespace tc

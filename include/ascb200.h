@@ -116,17 +116,22 @@ enum {
     ASCB200_EPI_DEQUANT_TOKEN_CHANNEL = 2
 };
 
-enum { ASCB200_KIND_F16 = 0, ASCB200_KIND_BF16 = 1, ASCB200_KIND_S8 = 2, ASCB200_KIND_MXFP4 = 3 };
+enum { ASCB200_KIND_F16 = 0, ASCB200_KIND_BF16 = 1, ASCB200_KIND_S8 = 2, ASCB200_KIND_MXFP4 = 3,
+       /* MX Matmul with fp8 operands (one byte per element, e4m3fn or e5m2) and e8m0 block scales, the other operand kinds of
+        * MmadMx (docs/zh/api/SIMD-API/basic_api/cube_compute_ISASI/mmad_compute/MmadMx.md:160-171; example
+        * examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul_mx): tcgen05.mma.kind::mxf8f6f4.block_scale.  Either operand
+        * may be stored K-major or the other way round (trans_a / trans_b as for int8); scales and scale_flags as for MXFP4. */
+       ASCB200_KIND_MXFP8_E4M3 = 4, ASCB200_KIND_MXFP8_E5M2 = 5 };
 
 typedef struct ascb200_gemm_desc {
-    int32_t kind;            /* ASCB200_KIND_*: operand type; accumulator is fp32 (F16/BF16/MXFP4) or int32 (S8) */
+    int32_t kind;            /* ASCB200_KIND_*: operand type; accumulator is fp32 (F16/BF16/MXFP4/MXFP8) or int32 (S8) */
     int32_t m, n, k;         /* C[m,n] = A[m,k] * B[k,n]; k counts elements (fp4 values for MXFP4) */
     const void* a_dev;       /* trans_a == 0: [m,k] row-major (ND); trans_a == 1: [k,m] row-major */
     const void* b_dev;       /* trans_b == 0: [k,n] row-major (ND); trans_b == 1: [n,k] row-major */
     int64_t lda, ldb;        /* leading dimensions in elements (0 = packed) */
     int32_t trans_a, trans_b;
-    const void* scale_a_dev; /* MXFP4: e8m0 bytes [m, k/32] row-major */
-    const void* scale_b_dev; /* MXFP4: e8m0 bytes [n, k/32] row-major */
+    const void* scale_a_dev; /* MXFP4 / MXFP8: e8m0 bytes [m, k/32] row-major (or see scale_flags) */
+    const void* scale_b_dev; /* MXFP4 / MXFP8: e8m0 bytes [n, k/32] row-major (or see scale_flags) */
     const void* bias_dev;    /* NULL or [n]: fp32 for fp32 accumulators, int32 for int32 accumulators */
     void* c_dev;             /* [m,n] row-major, leading dimension ldc (0 = n) */
     int64_t ldc;

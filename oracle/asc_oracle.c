@@ -249,6 +249,55 @@ ORC_API void orc_gemm_mxf4(const uint8_t* A, const uint8_t* sA, const uint8_t* B
     free(Bf);
 }
 
+/* fp8 -> fp32: e4m3fn (bias 7, no infinities, 0x7F / 0xFF are NaN) or e5m2 (bias 15, IEEE-like infinities and NaNs). */
+ORC_API float orc_fp8_to_f32(uint8_t v, int e5m2)
+{
+    const int mbits = e5m2 ? 2 : 3, bias = e5m2 ? 15 : 7;
+    const int sign = v >> 7, exp = (v & 0x7F) >> mbits, man = v & ((1 << mbits) - 1);
+    float f;
+    if (e5m2 && exp == 31) f = man ? NAN : INFINITY;
+    else if (!e5m2 && exp == 15 && man == 7) f = NAN;
+    else if (exp == 0) f = ldexpf((float)man, 1 - bias - mbits);
+    else f = ldexpf((float)(man | (1 << mbits)), exp - bias - mbits);
+    return sign ? -f : f;
+}
+
+/* MX matmul with fp8 operands (e4m3fn or e5m2, one byte per element), one e8m0 scale per 32 K elements, fp32 result
+ * (MmadMx.md:71-75,160-171; golden recipe examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul_mx/scripts/gen_data.py:60-68:
+ * operands times 2^(scale - 127), float64 matmul, cast to fp32).  Both operands K-major: A [M,K], B [N,K], sA [M,K/32], sB [N,K/32].
+ * Products are exact in double; summed in double per baseK chunk, the chunks added in fp32. */
+ORC_API void orc_gemm_mxf8(const uint8_t* A, const uint8_t* sA, const uint8_t* B, const uint8_t* sB, const float* bias, float* C, int M, int N,
+                           int K, int baseK, int e5m2)
+{
+    if (baseK <= 0) baseK = K;
+    const int KS = K / 32;
+    float* Af = (float*)malloc((size_t)M * K * sizeof(float));
+    float* Bf = (float*)malloc((size_t)N * K * sizeof(float));
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int k = 0; k < K; ++k) Af[(size_t)m * K + k] = orc_fp8_to_f32(A[(size_t)m * K + k], e5m2) * orc_e8m0_to_f32(sA[(size_t)m * KS + k / 32]);
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int k = 0; k < K; ++k) Bf[(size_t)n * K + k] = orc_fp8_to_f32(B[(size_t)n * K + k], e5m2) * orc_e8m0_to_f32(sB[(size_t)n * KS + k / 32]);
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m) {
+        const float* a = Af + (size_t)m * K;
+        for (int n = 0; n < N; ++n) {
+            const float* b = Bf + (size_t)n * K;
+            float acc = bias ? bias[n] : 0.0f;
+            for (int k0 = 0; k0 < K; k0 += baseK) {
+                int k1 = k0 + baseK < K ? k0 + baseK : K;
+                double part = 0.0;
+                for (int k = k0; k < k1; ++k) part += (double)a[k] * (double)b[k];
+                acc += (float)part;
+            }
+            C[(size_t)m * N + n] = acc;
+        }
+    }
+    free(Af);
+    free(Bf);
+}
+
 /* ---------------------------------------------------------------------------------------------
  * Fixpipe epilogues (L0C -> GM).
  * ------------------------------------------------------------------------------------------- */

@@ -78,6 +78,15 @@ def gemm_mxf4(a, sa, b, sb, bias=None, base_k=0):
     return c
 
 
+def gemm_mxf8(a, sa, b, sb, e5m2, bias=None, base_k=0):
+    """a [M,K], b [N,K] fp8 bytes (e4m3fn, or e5m2 when e5m2 is true); sa [M,K/32], sb [N,K/32] e8m0 bytes. Returns fp32 [M,N]."""
+    a, sa, b, sb, bias = _c(a, np.uint8), _c(sa, np.uint8), _c(b, np.uint8), _c(sb, np.uint8), _c(bias, np.float32)
+    M, N, K = a.shape[0], b.shape[0], a.shape[1]
+    c = np.empty((M, N), np.float32)
+    lib().orc_gemm_mxf8(_p(a), _p(sa), _p(b), _p(sb), _p(bias), _p(c), M, N, K, int(base_k), int(bool(e5m2)))
+    return c
+
+
 def cast_f32(acc, dtype, relu=False):
     acc = _c(acc, np.float32)
     out = np.empty(acc.shape, _OUT[dtype])

@@ -33,6 +33,9 @@ input+output samples as .npz, so the tests can pin the CPU oracle without the re
                      function is taken out of the file's syntax tree and executed, since importing the file needs en_dtypes),
                      scaleB re-ordered to [sK/2, N, 2] as in gen_data.py:63; A transposed ([K, M]) with scaleA in the same pair
                      order, as 04_advanced_api/00_matmul/matmul_mx/scripts/gen_data.py:71-76 does for is_trans_scalea
+  mxfp8.npz          04_advanced_api/00_matmul/matmul_mx/scripts/gen_data.py run as a script: fp8 e5m2 operands A [32, 128] and
+                     B [128, 128] (not transposed), e8m0 scales A [32, 4] and B in the pair order [2, 128, 2], fp32 golden from its
+                     float64 product
   casts.npz          CAST_RINT rule of docs/zh/api/SIMD-API/basic_api/data_structures/precision_conversion.md:19-23
                      with its worked examples (1.5 -> 2, 2.5 -> 2, 2^6+0.5 -> 2^6, 2^7-0.5 -> 2^7-1 saturated)
                      plus IEEE boundary cases worked out by hand from the same rule
@@ -324,6 +327,17 @@ def mxfp4_nd(ref):
         golden_f64=golden)
 
 
+def mxfp8(ref):
+    files = run_script_in_tmp(os.path.join(ref, EX, "04_advanced_api/00_matmul/matmul_mx/scripts/gen_data.py"), 29)
+    m, n, k = 32, 128, 128
+    np.savez_compressed(os.path.join(HERE, "mxfp8.npz"),
+                        a=np.frombuffer(files["input/x1_gm.bin"], np.uint8).reshape(m, k),
+                        b_kn=np.frombuffer(files["input/x2_gm.bin"], np.uint8).reshape(k, n),
+                        sa=np.frombuffer(files["input/x1_mx_gm.bin"], np.uint8).reshape(m, k // 32),
+                        sb_paired=np.frombuffer(files["input/x2_mx_gm.bin"], np.uint8).reshape(k // 64, n, 2),
+                        golden=np.frombuffer(files["output/golden.bin"], np.float32).reshape(m, n))
+
+
 def casts(ref):
     # precision_conversion.md: the CAST_RINT rule and its worked examples, plus hand-derived boundary cases
     np.savez_compressed(
@@ -344,6 +358,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("ASC_REFERENCE_ROOT", "reference"))
     args = ap.parse_args()
-    for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, logsoftmax, softmaxgrad, softmaxflashv2, quant, antiquant, dequant, grouped, mxfp4, mxfp4_nd, casts):
+    for fn in (fixpipe, matmul_fp16, matmul_quant, softmax, logsoftmax, softmaxgrad, softmaxflashv2, quant, antiquant, dequant, grouped, mxfp4, mxfp4_nd, mxfp8, casts):
         fn(args.ref)
         print("wrote", fn.__name__)

@@ -471,6 +471,58 @@ def test_gemm_output_layouts_column_major_and_nz(layout, case):
             assert (np.ascontiguousarray(pad).view(np.uint8) == 0x5A).all()
 
 
+def _fp8_codes(rng, shape, e5m2):
+    """Random finite fp8 codes of moderate magnitude (|x| <= 8) so that sums of a few thousand products stay well inside fp32."""
+    import ml_dtypes
+    t = ml_dtypes.float8_e5m2 if e5m2 else ml_dtypes.float8_e4m3fn
+    return (rng.standard_normal(shape) * 2).clip(-8, 8).astype(np.float32).astype(t).view(np.uint8)
+
+
+def test_gemm_mxfp8_reference_example(golden_dir):
+    """The reference's matmul_mx example as its generator writes it: e5m2 A [32, 128], B [128, 128] stored [K, N], scaleA [M, K/32],
+    scaleB in the pair order [K/64][N][2]; fp32 output against the generator's golden."""
+    import os
+    ab = dev()
+    g = np.load(os.path.join(golden_dir, "mxfp8.npz"))
+    m, k = g["a"].shape
+    n = g["b_kn"].shape[1]
+    d_c = ab.empty((m, n), np.float32)
+    ab.check(ab.gemm(ab.KIND_MXFP8_E5M2, m, n, k, ab.to_dev(g["a"]), ab.to_dev(g["b_kn"]), d_c, ab.F32, trans_b=False, scale_a=ab.to_dev(g["sa"]),
+                     scale_b=ab.to_dev(g["sb_paired"]), scale_flags=ab.SCALE_B_PAIRED))
+    ab.sync()
+    assert np.allclose(d_c.download(), g["golden"], rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("e5m2", [False, True])
+@pytest.mark.parametrize("m,n,k,trans_a,trans_b", [(128, 128, 128, False, True), (384, 512, 1024, False, True), (100, 200, 192, False, True),
+                                                   (256, 640, 512, False, False), (208, 264, 320, True, True), (1024, 2304, 256, False, True)])
+def test_gemm_mxfp8(m, n, k, trans_a, trans_b, e5m2):
+    """MX Matmul with fp8 operands (e4m3fn / e5m2) and e8m0 scales per 32 K elements against the oracle, K-major and transposed
+    operand layouts, fp32 and bf16 outputs."""
+    ab = dev()
+    rng = np.random.default_rng(m + n + k + int(e5m2))
+    a = _fp8_codes(rng, (m, k), e5m2)
+    b = _fp8_codes(rng, (n, k), e5m2)
+    sa = rng.integers(123, 131, (m, k // 32), dtype=np.uint8)
+    sb = rng.integers(123, 131, (n, k // 32), dtype=np.uint8)
+    ref = orc.gemm_mxf8(a, sa, b, sb, e5m2, base_k=128)
+    a_dev = ab.to_dev(np.ascontiguousarray(a.T) if trans_a else a)
+    b_dev = ab.to_dev(b if trans_b else np.ascontiguousarray(b.T))
+    kind = ab.KIND_MXFP8_E5M2 if e5m2 else ab.KIND_MXFP8_E4M3
+    d_c = ab.empty((m, n), np.float32)
+    d_c.fill(0xFF)
+    ab.check(ab.gemm(kind, m, n, k, a_dev, b_dev, d_c, ab.F32, trans_a=trans_a, trans_b=trans_b, scale_a=ab.to_dev(sa), scale_b=ab.to_dev(sb)))
+    ab.sync()
+    got = d_c.download()
+    err = np.abs(got - ref)
+    assert (err <= ATOL + RTOL * np.abs(ref)).all(), f"max err {err.max()} ref {np.abs(ref).max()}"
+    assert err.max() <= 1e-3 * np.abs(ref).max()   # every product is exact in fp32; only the summation order differs
+    d_bf = ab.empty((m, n), np.uint16)
+    ab.check(ab.gemm(kind, m, n, k, a_dev, b_dev, d_bf, ab.BF16, trans_a=trans_a, trans_b=trans_b, scale_a=ab.to_dev(sa), scale_b=ab.to_dev(sb)))
+    ab.sync()
+    assert (d_bf.download() == orc.cast_f32(got, orc.BF16)).all()   # the cast applied to the GPU's own accumulators: bit exact
+
+
 def test_gemm_mxfp4_requant_and_bf16():
     """MXFP4 baseline epilogue: int8 via per-channel VQF322B8_PRE plus the bf16 cast of the same accumulators."""
     ab = dev()

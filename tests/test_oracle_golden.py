@@ -312,3 +312,23 @@ def test_mxfp4_layouts_of_the_untransposed_b_recipe(golden_dir):
     assert (g["sa_paired"].transpose(1, 0, 2).reshape(m, 2 * sk2) == g["sa"]).all()
     ref = orc.gemm_mxf4(g["a"], g["sa"], g["b_kmajor"], g["sb"], base_k=256)
     assert np.allclose(ref, g["golden_f64"], rtol=1e-5, atol=1e-2)
+
+
+def test_mxfp8_recipe(golden_dir):
+    """MX Matmul with fp8 operands on the files the reference's matmul_mx generator writes (e5m2 A [32, 128], B [128, 128] not
+    transposed, scaleB in the pair order): the oracle's product equals the generator's golden; the fp8 decoder agrees with
+    ml_dtypes on all 256 codes of both formats."""
+    import ctypes as C
+    import ml_dtypes
+    g = load(golden_dir, "mxfp8.npz")
+    n = g["b_kn"].shape[1]
+    sb = g["sb_paired"].transpose(1, 0, 2).reshape(n, -1)
+    got = orc.gemm_mxf8(g["a"], g["sa"], np.ascontiguousarray(g["b_kn"].T), sb, e5m2=True)
+    assert np.allclose(got, g["golden"], rtol=1e-6, atol=1e-6)
+    fn = orc.lib().orc_fp8_to_f32
+    fn.restype = C.c_float
+    codes = np.arange(256, dtype=np.uint8)
+    for e5m2, t in ((0, ml_dtypes.float8_e4m3fn), (1, ml_dtypes.float8_e5m2)):
+        mine = np.array([fn(int(v), e5m2) for v in codes], np.float32)
+        want = codes.view(t).astype(np.float32)
+        assert ((mine == want) | (np.isnan(mine) & np.isnan(want))).all()
