@@ -22,7 +22,7 @@ EXPORTS = [
     "ascb200_memset", "ascb200_stream_create", "ascb200_stream_destroy", "ascb200_stream_sync", "ascb200_event_create",
     "ascb200_event_destroy", "ascb200_event_record", "ascb200_stream_wait_event", "ascb200_event_elapsed_ms", "ascb200_gemm", "ascb200_grouped_gemm",
     "ascb200_gemm_mxfp4_noalloc", "ascb200_noalloc_status", "ascb200_mx_scale_prepacked_bytes", "ascb200_mx_scale_prepack", "ascb200_fp4_transpose", "ascb200_shard_nslab", "ascb200_shard_groups_lpt", "ascb200_comm_unique_id", "ascb200_comm_init", "ascb200_comm_init_all", "ascb200_comm_destroy", "ascb200_group_start", "ascb200_group_end", "ascb200_allgather_slabs", "ascb200_interleave_slabs", "ascb200_graph_begin", "ascb200_graph_end", "ascb200_graph_launch", "ascb200_graph_destroy",
-    "ascb200_nz_unpack", "ascb200_quant_policy", "ascb200_dequant_policy", "ascb200_softmax_flash_v2", "ascb200_softmax", "ascb200_log_softmax", "ascb200_antiquant", "ascb200_softmax_flash", "ascb200_softmax_grad", "ascb200_simple_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
+    "ascb200_nz_unpack", "ascb200_quant_policy", "ascb200_quant_policy_rm", "ascb200_dequant_policy", "ascb200_softmax_flash_v2", "ascb200_softmax", "ascb200_log_softmax", "ascb200_antiquant", "ascb200_softmax_flash", "ascb200_softmax_grad", "ascb200_simple_softmax", "ascb200_quant_per_tensor", "ascb200_quant_per_channel", "ascb200_softmax_quant", "ascb200_dequant",
 ]
 
 
@@ -106,6 +106,8 @@ def lib():
         _lib.ascb200_nz_unpack.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
         _lib.ascb200_quant_policy.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                               C.c_int32, C.c_void_p, C.c_void_p, C.c_float, C.c_int32, C.c_void_p]
+        _lib.ascb200_quant_policy_rm.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                                 C.c_int32, C.c_void_p, C.c_void_p, C.c_float, C.c_int32, C.c_int32, C.c_void_p]
         _lib.ascb200_dequant_policy.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                                 C.c_int32, C.c_void_p, C.c_void_p]
         _lib.ascb200_softmax_flash_v2.argtypes = [C.c_void_p] * 7 + [C.c_int32] * 6 + [C.c_void_p]
@@ -297,7 +299,10 @@ QUANT_PER_TOKEN, QUANT_PER_GROUP = 2, 3
 
 
 def quant_policy(src, dst, m, n, src_dtype, scale_dtype, dst_dtype, policy, scale, k_dim=1, group_size=0, offset=None, offset_scalar=0.0,
-                 has_offset=False, stream=None):
+                 has_offset=False, stream=None, round_mode=None):
+    if round_mode is not None:
+        return lib().ascb200_quant_policy_rm(_ptr(src), _ptr(dst), m, n, src_dtype, scale_dtype, dst_dtype, policy, k_dim, group_size, _ptr(scale),
+                                             _ptr(offset), C.c_float(offset_scalar), int(has_offset), int(round_mode), stream)
     return lib().ascb200_quant_policy(_ptr(src), _ptr(dst), m, n, src_dtype, scale_dtype, dst_dtype, policy, k_dim, group_size, _ptr(scale),
                                       _ptr(offset), C.c_float(offset_scalar), int(has_offset), stream)
 

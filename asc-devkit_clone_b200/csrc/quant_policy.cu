@@ -33,6 +33,7 @@ struct QuantPolicyArgs {
     int m, n;
     int policy, k_dim, group_size;
     int scale_cols;  // columns of the scale tensor for PER_GROUP
+    int round_mode;  // RoundMode of the final conversion (int8 destinations): 1 RINT, 2 FLOOR, 3 CEIL, 4 ROUND (half away from zero), 5 TRUNC
 };
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
@@ -60,11 +61,15 @@ __device__ __forceinline__ float mul_add_in(float x, ST s, ST o, bool has_offset
 }
 
 template <int DST>
-__device__ __forceinline__ uint32_t to_byte(float v)
+__device__ __forceinline__ uint32_t to_byte(float v, int round_mode = 1)
 {
     if constexpr (DST == ASCB200_S8) {
         int r;
-        asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));  // NaN -> 0
+        if (round_mode == 1) asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));  // NaN -> 0
+        else if (round_mode == 2) asm("cvt.rmi.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+        else if (round_mode == 3) asm("cvt.rpi.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+        else if (round_mode == 5) asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+        else asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(roundf(v)));   // CAST_ROUND: halves away from zero, then exact
         return static_cast<uint32_t>(r) & 0xFFu;
     } else {
         uint16_t pair;
@@ -139,12 +144,12 @@ __device__ __forceinline__ void quant_policy_store(const QuantPolicyArgs& a, siz
             uint32_t w0 = 0, w1 = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                w0 |= to_byte<DST>(v[j]) << (8 * j);
-                w1 |= to_byte<DST>(v[4 + j]) << (8 * j);
+                w0 |= to_byte<DST>(v[j], a.round_mode) << (8 * j);
+                w1 |= to_byte<DST>(v[4 + j], a.round_mode) << (8 * j);
             }
             *reinterpret_cast<uint2*>(out) = make_uint2(w0, w1);
         } else {
-            *out = static_cast<uint8_t>(to_byte<DST>(v[0]));
+            *out = static_cast<uint8_t>(to_byte<DST>(v[0], a.round_mode));
         }
     }
 }
@@ -574,7 +579,18 @@ extern "C" int ascb200_quant_policy(const void* src, void* dst, int32_t m, int32
                                     int32_t policy, int32_t k_dim, int32_t group_size, const void* scale, const void* offset_tensor,
                                     float offset_scalar, int32_t has_offset, void* stream)
 {
+    return ascb200_quant_policy_rm(src, dst, m, n, src_dtype, scale_dtype, dst_dtype, policy, k_dim, group_size, scale, offset_tensor, offset_scalar,
+                                   has_offset, /*CAST_RINT*/ 1, stream);
+}
+
+extern "C" int ascb200_quant_policy_rm(const void* src, void* dst, int32_t m, int32_t n, int32_t src_dtype, int32_t scale_dtype, int32_t dst_dtype,
+                                       int32_t policy, int32_t k_dim, int32_t group_size, const void* scale, const void* offset_tensor,
+                                       float offset_scalar, int32_t has_offset, int32_t round_mode, void* stream)
+{
     using namespace ascb200;
+    if (round_mode == 0) round_mode = 1;                                                  // CAST_NONE: the default rounding
+    if (round_mode < 1 || round_mode > 5) return ASCB200_EUNSUPPORTED;                    // CAST_ODD, CAST_HYBRID, ... are not built
+    if (round_mode != 1 && dst_dtype != ASCB200_S8) return ASCB200_EUNSUPPORTED;          // fp8 / fp4 destinations round to nearest even only
     DeviceState* st = current_state();
     if (!st) return ASCB200_ENODEV;
     if (!src || !dst || !scale || m < 0 || n < 0) return ASCB200_EINVAL;
@@ -597,6 +613,7 @@ extern "C" int ascb200_quant_policy(const void* src, void* dst, int32_t m, int32
     a.k_dim = k_dim;
     a.group_size = policy == ASCB200_QUANT_PER_GROUP ? group_size : 1;
     a.scale_cols = policy == ASCB200_QUANT_PER_GROUP ? (n + group_size - 1) / group_size : 1;
+    a.round_mode = round_mode;
     const int esz = src_dtype == ASCB200_F32 ? 4 : 2;
     const bool vec8 = n % 8 == 0 && aligned_to(src, 16) && aligned_to(dst, 8) && (src_dtype == ASCB200_F32 || esz == 2);
     cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -450,15 +450,19 @@ inline void QuantPolicy(const LocalTensor<dstT>& dst, const LocalTensor<srcT>& s
 {
     static_assert(policy == AscendQuantPolicy::PER_TOKEN || policy == AscendQuantPolicy::PER_GROUP,
                   "unsupported policy for AscendQuant in current device!");  // the reference's own restriction
-    static_assert(config.roundMode == RoundMode::CAST_RINT, "only the default rounding (CAST_RINT) is implemented");
+    static_assert(config.roundMode == RoundMode::CAST_NONE || config.roundMode == RoundMode::CAST_RINT || config.roundMode == RoundMode::CAST_FLOOR ||
+                      config.roundMode == RoundMode::CAST_CEIL || config.roundMode == RoundMode::CAST_ROUND || config.roundMode == RoundMode::CAST_TRUNC,
+                  "CAST_ODD and the hybrid rounding modes are not implemented");
+    static_assert(config.roundMode == RoundMode::CAST_NONE || config.roundMode == RoundMode::CAST_RINT || std::is_same<dstT, int8_t>::value,
+                  "fp8 / fp4 destinations round to nearest even only");
     if (para.n == 0 || para.calCount % para.n != 0) {
         Latch(ASCB200_EINVAL, "AscendQuant (calCount must be an integer multiple of n)");
         return;
     }
-    Latch(ascb200_quant_policy(src.GetPhyAddr(), dst.GetPhyAddr(), static_cast<int32_t>(para.calCount / para.n), static_cast<int32_t>(para.n),
-                               DTypeOf<srcT>::value, DTypeOf<scaleT>::value, DTypeOf<dstT>::value, static_cast<int32_t>(policy), config.kDim,
-                               static_cast<int32_t>(para.groupSize), scale.GetPhyAddr(), offsetTensor, offsetScalar, config.hasOffset ? 1 : 0,
-                               CurrentStream()),
+    Latch(ascb200_quant_policy_rm(src.GetPhyAddr(), dst.GetPhyAddr(), static_cast<int32_t>(para.calCount / para.n), static_cast<int32_t>(para.n),
+                                  DTypeOf<srcT>::value, DTypeOf<scaleT>::value, DTypeOf<dstT>::value, static_cast<int32_t>(policy), config.kDim,
+                                  static_cast<int32_t>(para.groupSize), scale.GetPhyAddr(), offsetTensor, offsetScalar, config.hasOffset ? 1 : 0,
+                                  static_cast<int32_t>(config.roundMode), CurrentStream()),
           "AscendQuant (policy)");
 }
 }  // namespace detail

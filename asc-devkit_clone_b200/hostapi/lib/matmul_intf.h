@@ -44,6 +44,8 @@ template <> struct KindOf<half> { static constexpr int value = ASCB200_KIND_F16;
 template <> struct KindOf<bfloat16_t> { static constexpr int value = ASCB200_KIND_BF16; };
 template <> struct KindOf<int8_t> { static constexpr int value = ASCB200_KIND_S8; };
 template <> struct KindOf<fp4x2_e2m1_t> { static constexpr int value = ASCB200_KIND_MXFP4; };
+template <> struct KindOf<fp8_e4m3fn_t> { static constexpr int value = ASCB200_KIND_MXFP8_E4M3; };   // MX Matmul (with scale tensors) only
+template <> struct KindOf<fp8_e5m2_t> { static constexpr int value = ASCB200_KIND_MXFP8_E5M2; };
 // The fifth argument is a MatmulConfig or, for constant tiling, the MatmulApiStaticTiling made from one.
 constexpr const MatmulConfig& ToMatmulConfig(const MatmulConfig& cfg) { return cfg; }
 constexpr const MatmulConfig& ToMatmulConfig(const MatmulApiStaticTiling& tiling) { return tiling.cfg; }
@@ -68,8 +70,9 @@ public:
     static_assert(A_TYPE::layout == B_TYPE::layout || A_TYPE::layout == LayoutMode::NONE || B_TYPE::layout == LayoutMode::NONE,
                   "A and B must have the same batch layout (IterateBatch.md)");
     static_assert(B_TYPE::format != CubeFormat::NZ || sizeof(SrcBT) <= 2, "NZ unpacking covers 1- and 2-byte elements");
-    static constexpr bool isMx = std::is_same<SrcAT, fp4x2_e2m1_t>::value;
-    static constexpr int elemsPerStorage = isMx ? 2 : 1;  // GlobalTensor offsets count storage units (bytes for packed fp4)
+    static constexpr bool isFp4 = std::is_same<SrcAT, fp4x2_e2m1_t>::value;
+    static constexpr bool isMx = isFp4 || std::is_same<SrcAT, fp8_e4m3fn_t>::value || std::is_same<SrcAT, fp8_e5m2_t>::value;
+    static constexpr int elemsPerStorage = isFp4 ? 2 : 1;  // GlobalTensor offsets count storage units (bytes for packed fp4)
 
     Matmul() = default;
     Matmul(const Matmul&) = delete;  // the object may own the unpacked copy of an NZ operand
@@ -432,13 +435,13 @@ private:
             // [K/64][rows][2] (SetTensorScaleA / SetTensorScaleB, impl/adv_api/detail/matmul/mx_matmul_impl.h:136-158).
             const int64_t sk = singleK_ / 32;
             d.scale_flags = (transScaleA_ ? ASCB200_SCALE_A_PAIRED : 0) | (!transScaleB_ ? ASCB200_SCALE_B_PAIRED : 0);
-            if (!whole && (transScaleA_ || !transScaleB_ || (transA_ && (rowOff & 1)) || (!transB_ && (colOff & 1)))) {
+            if (!whole && (transScaleA_ || !transScaleB_ || (isFp4 && ((transA_ && (rowOff & 1)) || (!transB_ && (colOff & 1)))))) {
                 AscendC::detail::Latch(ASCB200_EUNSUPPORTED, "Matmul (MX sub-block with pair-ordered scales or an odd offset)");
                 return;
             }
             d.scale_a_dev = scaleA_ + static_cast<int64_t>(rowOff) * sk;
             d.scale_b_dev = scaleB_ + static_cast<int64_t>(colOff) * sk;
-            if (!transB_ && whole && singleN_ == orgN_ && singleK_ == orgKb_) {
+            if (isFp4 && !transB_ && whole && singleN_ == orgN_ && singleK_ == orgKb_) {
                 // the reference's ND B ([K, N], two N-neighbours per byte): weights, transposed to K-major once per tensor
                 if (unpackedFor_ != b_) {
                     if (!EnsureCopyOfB(static_cast<size_t>(orgN_) * orgKb_ / 2)) return;

@@ -352,6 +352,13 @@ enum { ASCB200_QUANT_PER_TOKEN = 2, ASCB200_QUANT_PER_GROUP = 3 };  /* values of
 ASCB200_API int ascb200_quant_policy(const void* src_dev, void* dst_dev, int32_t m, int32_t n, int32_t src_dtype, int32_t scale_dtype,
                                      int32_t dst_dtype, int32_t policy, int32_t k_dim, int32_t group_size, const void* scale_dev,
                                      const void* offset_tensor_dev, float offset_scalar, int32_t has_offset, void* stream);
+/* The same with config.roundMode (include/adv_api/quantization/ascend_quant_utils.h:55-64): round_mode takes the values of
+ * RoundMode (impl/basic_api/utils/kernel_utils_mode.h:103-120): 0 CAST_NONE and 1 CAST_RINT nearest even, 2 CAST_FLOOR, 3 CAST_CEIL,
+ * 4 CAST_ROUND halves away from zero, 5 CAST_TRUNC towards zero; all saturating.  Modes other than nearest even go with S8
+ * destinations; CAST_ODD and the hybrid modes are not built (ASCB200_EUNSUPPORTED). */
+ASCB200_API int ascb200_quant_policy_rm(const void* src_dev, void* dst_dev, int32_t m, int32_t n, int32_t src_dtype, int32_t scale_dtype,
+                                        int32_t dst_dtype, int32_t policy, int32_t k_dim, int32_t group_size, const void* scale_dev,
+                                        const void* offset_tensor_dev, float offset_scalar, int32_t has_offset, int32_t round_mode, void* stream);
 
 /* AscendDequant with a policy (include/adv_api/quantization/ascend_dequant.h:293-318, AscendDeQuantPolicy / AscendDeQuantParam of
  * include/adv_api/quantization/ascend_dequant_utils.h:32-44): dst[i,j] = cast(float(src[i,j]) * float(scale)), scale per row

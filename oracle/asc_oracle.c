@@ -738,8 +738,36 @@ static float round_to(float v, int dtype)
     if (dtype == ORC_BF16) return orc_bf16_to_f32(orc_f32_to_bf16(v));
     return v;
 }
+ORC_API void orc_quant_policy_rm(const void* src, uint8_t* dst, int m, int n, int src_dtype, int scale_dtype, int dst_dtype, int policy, int k_dim,
+                                 int group_size, const void* scale, const void* offset_t, float offset_scalar, int has_offset, int round_mode);
+
+/* fp32 -> int8 under a RoundMode of the reference (impl/basic_api/utils/kernel_utils_mode.h:103-120; the rules and worked examples of
+ * docs/zh/api/SIMD-API/basic_api/data_structures/precision_conversion.md): 1 RINT nearest even, 2 FLOOR, 3 CEIL, 4 ROUND halves away
+ * from zero, 5 TRUNC; saturating, NaN -> 0. */
+ORC_API int8_t orc_f32_to_s8_mode(float f, int round_mode)
+{
+    if (f != f) return 0;
+    float r;
+    switch (round_mode) {
+        case 2: r = floorf(f); break;
+        case 3: r = ceilf(f); break;
+        case 4: r = roundf(f); break;
+        case 5: r = truncf(f); break;
+        default: return f32_to_s8_rint_sat(f);
+    }
+    return (int8_t)(r < -128.0f ? -128.0f : r > 127.0f ? 127.0f : r);
+}
+
 ORC_API void orc_quant_policy(const void* src, uint8_t* dst, int m, int n, int src_dtype, int scale_dtype, int dst_dtype, int policy, int k_dim,
                               int group_size, const void* scale, const void* offset_t, float offset_scalar, int has_offset)
+{
+    orc_quant_policy_rm(src, dst, m, n, src_dtype, scale_dtype, dst_dtype, policy, k_dim, group_size, scale, offset_t, offset_scalar, has_offset, 1);
+}
+
+/* AscendQuant PER_TOKEN / PER_GROUP with config.roundMode applied to the final conversion of int8 destinations
+ * (include/adv_api/quantization/ascend_quant_utils.h:55-64). */
+ORC_API void orc_quant_policy_rm(const void* src, uint8_t* dst, int m, int n, int src_dtype, int scale_dtype, int dst_dtype, int policy, int k_dim,
+                                 int group_size, const void* scale, const void* offset_t, float offset_scalar, int has_offset, int round_mode)
 {
     const int scale_cols = policy == 3 ? (n + group_size - 1) / group_size : 1;
 #pragma omp parallel for schedule(static)
@@ -760,7 +788,7 @@ ORC_API void orc_quant_policy(const void* src, uint8_t* dst, int m, int n, int s
             v = round_to(x * s, scale_dtype);
             if (has_offset && dst_dtype != ORC_FP4_E2M1) v = round_to(v + o, scale_dtype);
             if (dst_dtype == ORC_S8) {
-                dst[(size_t)i * n + j] = (uint8_t)orc_f32_to_s8(v);
+                dst[(size_t)i * n + j] = (uint8_t)orc_f32_to_s8_mode(v, round_mode);
             } else {
                 const uint8_t c = orc_f32_to_e2m1(orc_bf16_to_f32(orc_f32_to_bf16(v)));
                 uint8_t* b = dst + ((size_t)i * n + j) / 2;

@@ -270,7 +270,8 @@ def bf16_bits_to_f32(bits):
     return (np.asarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 
-def quant_policy(src, scale, src_dtype, scale_dtype, dst_dtype, policy, k_dim=1, group_size=0, offset=None, offset_scalar=0.0, has_offset=False):
+def quant_policy(src, scale, src_dtype, scale_dtype, dst_dtype, policy, k_dim=1, group_size=0, offset=None, offset_scalar=0.0, has_offset=False,
+                 round_mode=1):
     """AscendQuant PER_TOKEN (policy 2) / PER_GROUP (policy 3). src [m, n] as stored (uint16 bits for F16 / BF16, float32 for F32);
     returns uint8 [m, n] (int8 / fp8 bytes) or [m, n/2] packed e2m1."""
     src = np.ascontiguousarray(src)
@@ -278,8 +279,8 @@ def quant_policy(src, scale, src_dtype, scale_dtype, dst_dtype, policy, k_dim=1,
     m, n = src.shape
     out = np.zeros((m, n // 2) if dst_dtype == FP4_E2M1 else (m, n), np.uint8)
     off = None if offset is None else np.ascontiguousarray(offset)
-    lib().orc_quant_policy(_p(src), _p(out), m, n, src_dtype, scale_dtype, dst_dtype, policy, k_dim, group_size, _p(scale),
-                           _p(off) if off is not None else None, C.c_float(offset_scalar), int(has_offset))
+    lib().orc_quant_policy_rm(_p(src), _p(out), m, n, src_dtype, scale_dtype, dst_dtype, policy, k_dim, group_size, _p(scale),
+                              _p(off) if off is not None else None, C.c_float(offset_scalar), int(has_offset), int(round_mode))
     return out
 
 

@@ -1050,6 +1050,77 @@ static void TestMxLayouts()
     std::printf("MX Matmul, [K, N] B with pair-ordered scaleB == K-major form: ok\n");
 }
 
+// MX Matmul with fp8 e5m2 operands as in the reference's matmul_mx example (A [M, K], B [K, N] not transposed, scaleB in the pair
+// order): small integers and power-of-two scales, so the expected fp32 result is exact.
+static void TestMxFp8()
+{
+    using namespace AscendC;
+    const int M = 64, N = 128, K = 128, SK = K / 32;
+    static const uint8_t kCode[5] = {0x00, 0x3C, 0x40, 0x42, 0x44};   // e5m2 encodings of 0, 1, 2, 3, 4
+    std::mt19937 rng(15);
+    std::uniform_int_distribution<int> u(-4, 4), sc(126, 129);
+    std::vector<int> va(static_cast<size_t>(M) * K), vb(static_cast<size_t>(K) * N);
+    for (auto& v : va) v = u(rng);
+    for (auto& v : vb) v = u(rng);
+    std::vector<fp8_e5m2_t> a(va.size()), b(vb.size());
+    for (size_t i = 0; i < va.size(); ++i) a[i].bits = static_cast<uint8_t>(kCode[std::abs(va[i])] | (va[i] < 0 ? 0x80 : 0));
+    for (size_t i = 0; i < vb.size(); ++i) b[i].bits = static_cast<uint8_t>(kCode[std::abs(vb[i])] | (vb[i] < 0 ? 0x80 : 0));
+    std::vector<uint8_t> sa(static_cast<size_t>(M) * SK), sb(static_cast<size_t>(SK) * N);   // scaleA [M, SK], scaleB [SK, N]
+    for (auto& v : sa) v = static_cast<uint8_t>(sc(rng));
+    for (auto& v : sb) v = static_cast<uint8_t>(sc(rng));
+    std::vector<fp8_e8m0_t> vsa(sa.size()), vsbP(sb.size());
+    for (size_t i = 0; i < sa.size(); ++i) vsa[i].bits = sa[i];
+    for (int p = 0; p < SK / 2; ++p)
+        for (int n = 0; n < N; ++n)
+            for (int j = 0; j < 2; ++j) vsbP[(static_cast<size_t>(p) * N + n) * 2 + j].bits = sb[static_cast<size_t>(2 * p + j) * N + n];
+    DevBuf<fp8_e5m2_t> dA(a), dB(b);
+    DevBuf<fp8_e8m0_t> dSa(vsa), dSb(vsbP);
+    DevBuf<float> dC(static_cast<size_t>(M) * N);
+    TCubeTiling tiling{};
+    tiling.usedCoreNum = 1;
+    tiling.M = tiling.singleCoreM = M;
+    tiling.N = tiling.singleCoreN = N;
+    tiling.Ka = tiling.Kb = tiling.singleCoreK = K;
+    tiling.baseM = 64;
+    tiling.baseN = 128;
+    tiling.baseK = 128;
+    {
+        TPipe pipe;
+        using TA = MatmulTypeWithScale<TPosition::GM, TPosition::GM, CubeFormat::ND, fp8_e5m2_t, false>;
+        using TB = MatmulTypeWithScale<TPosition::GM, TPosition::GM, CubeFormat::ND, fp8_e5m2_t, false>;
+        using TC = MatmulType<TPosition::GM, CubeFormat::ND, float>;
+        Matmul<TA, TB, TC, TC, CFG_MDL, MatmulCallBackFunc<>, MatmulWithScalePolicy> mm;
+        REGIST_MATMUL_OBJ(&pipe, GetSysWorkSpacePtr(), mm, &tiling);
+        GlobalTensor<fp8_e5m2_t> ga, gb;
+        GlobalTensor<fp8_e8m0_t> gsa, gsb;
+        GlobalTensor<float> gc;
+        ga.SetGlobalBuffer(dA.p, a.size());
+        gb.SetGlobalBuffer(dB.p, b.size());
+        gsa.SetGlobalBuffer(dSa.p, vsa.size());
+        gsb.SetGlobalBuffer(dSb.p, vsbP.size());
+        gc.SetGlobalBuffer(dC.p, dC.n);
+        mm.SetTensorA(ga, false);
+        mm.SetTensorB(gb, false);
+        mm.SetTensorScaleA(gsa, false);
+        mm.SetTensorScaleB(gsb, false);
+        mm.IterateAll(gc);
+        mm.End();
+    }
+    CHECK(GetLastError() == 0, "operator error %d", GetLastError());
+    const std::vector<float> c = dC.Download();
+    int bad = 0;
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            double acc = 0.0;
+            for (int k = 0; k < K; ++k)
+                acc += std::ldexp(static_cast<double>(va[static_cast<size_t>(m) * K + k]), sa[static_cast<size_t>(m) * SK + k / 32] - 127) *
+                       std::ldexp(static_cast<double>(vb[static_cast<size_t>(k) * N + n]), sb[static_cast<size_t>(k / 32) * N + n] - 127);
+            bad += c[static_cast<size_t>(m) * N + n] != static_cast<float>(acc);
+        }
+    CHECK(bad == 0, "MX fp8 Matmul: %d wrong", bad);
+    std::printf("MX Matmul fp8 e5m2, [K, N] B, pair-ordered scaleB: ok\n");
+}
+
 static void TestErrorLatch()
 {
     AscendC::ClearLastError();
@@ -1084,6 +1155,7 @@ int main()
     TestIterateNBatch();
     TestBaseBlocksAndOutputFormats();
     TestMxLayouts();
+    TestMxFp8();
     TestErrorLatch();
     std::printf(g_fail ? "%d checks failed\n" : "hostapi ok\n", g_fail);
     return g_fail ? 1 : 0;

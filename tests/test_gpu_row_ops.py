@@ -193,6 +193,35 @@ def test_quant_per_token_policy(m, n, has_offset, src_dtype, scale_dtype, dst_dt
     assert (got == ref).all(), f"{(got != ref).sum()} of {ref.size} differ; first {np.argwhere(got != ref)[:4].tolist()}"
 
 
+@pytest.mark.parametrize("round_mode", [0, 1, 2, 3, 4, 5])   # RoundMode: NONE, RINT, FLOOR, CEIL, ROUND, TRUNC
+@pytest.mark.parametrize("policy,src_dtype,scale_dtype", [(2, 1, 0), (3, 0, 0), (2, 2, 2)])
+def test_quant_policy_round_modes(round_mode, policy, src_dtype, scale_dtype):
+    """config.roundMode of the policy AscendQuant on int8 destinations: values that land on and next to halves (also negative and
+    saturating ones), bit exact against the oracle; fp8 destinations take nearest-even only."""
+    ab = dev()
+    m, n, group = 24, 256, 64
+    rng = np.random.default_rng(round_mode * 10 + policy)
+    base = rng.integers(-140, 141, (m, n)).astype(np.float32)
+    frac = rng.choice(np.array([0.0, 0.25, 0.5, 0.75], np.float32), (m, n))
+    x = _as_stored((base + frac) / 4.0, src_dtype)          # scale 4 puts the products on quarters
+    shape = (m,) if policy == 2 else (m, n // group)
+    scale = _as_stored(np.full(shape, 4.0, np.float32), scale_dtype)
+    d_q = ab.empty((m, n), np.uint8)
+    ab.check(ab.quant_policy(ab.to_dev(x), d_q, m, n, src_dtype, scale_dtype, ab.S8, policy, ab.to_dev(scale), k_dim=1, group_size=group if policy == 3 else 0,
+                             round_mode=round_mode))
+    ab.sync()
+    ref = orc.quant_policy(x, scale, src_dtype, scale_dtype, orc.S8, policy, k_dim=1, group_size=group if policy == 3 else 0, round_mode=round_mode or 1)
+    got = d_q.download().reshape(m, n)
+    assert (got == ref).all(), f"{(got != ref).sum()} differ; first {np.argwhere(got != ref)[:4].tolist()}"
+    if round_mode in (2, 3, 4, 5):
+        rint = orc.quant_policy(x, scale, src_dtype, scale_dtype, orc.S8, policy, k_dim=1, group_size=group if policy == 3 else 0)
+        assert (rint != ref).any()   # the mode really changes results on this data
+        assert ab.quant_policy(ab.to_dev(x), d_q, m, n, src_dtype, scale_dtype, ab.FP8_E4M3, policy, ab.to_dev(scale), k_dim=1,
+                               group_size=group if policy == 3 else 0, round_mode=round_mode) == ab.EUNSUPPORTED
+    assert ab.quant_policy(ab.to_dev(x), d_q, m, n, src_dtype, scale_dtype, ab.S8, policy, ab.to_dev(scale), k_dim=1,
+                           group_size=group if policy == 3 else 0, round_mode=6) == ab.EUNSUPPORTED
+
+
 @pytest.mark.parametrize("dst_dtype", [3, 6, 5])          # int8, fp8 e4m3, packed fp4 e2m1
 @pytest.mark.parametrize("src_dtype,scale_dtype", [(1, 0), (2, 0), (0, 0), (1, 1)])
 @pytest.mark.parametrize("m,n,group,k_dim", [(48, 256, 32, 1), (40, 320, 64, 1), (70, 96, 32, 0), (9, 250, 128, 1)])

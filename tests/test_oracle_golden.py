@@ -332,3 +332,21 @@ def test_mxfp8_recipe(golden_dir):
         mine = np.array([fn(int(v), e5m2) for v in codes], np.float32)
         want = codes.view(t).astype(np.float32)
         assert ((mine == want) | (np.isnan(mine) & np.isnan(want))).all()
+
+
+def test_round_modes_follow_the_conversion_rules():
+    """float -> int8 under the reference's RoundMode values, on the worked examples of precision_conversion.md and the cases around
+    them: 1.5 / 2.5 / -0.5 / -1.5 under nearest-even, floor, ceil, halves-away-from-zero and truncation, with saturation."""
+    import ctypes as C
+    fn = orc.lib().orc_f32_to_s8_mode
+    fn.restype = C.c_int8
+    fn.argtypes = [C.c_float, C.c_int]
+    x = [0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 2.4, -2.6, 127.5, 300.0, -128.5, -1e9]
+    want = {1: [0, 2, 2, 0, -2, -2, 2, -3, 127, 127, -128, -128],      # CAST_RINT
+            2: [0, 1, 2, -1, -2, -3, 2, -3, 127, 127, -128, -128],     # CAST_FLOOR
+            3: [1, 2, 3, 0, -1, -2, 3, -2, 127, 127, -128, -128],      # CAST_CEIL
+            4: [1, 2, 3, -1, -2, -3, 2, -3, 127, 127, -128, -128],     # CAST_ROUND
+            5: [0, 1, 2, 0, -1, -2, 2, -2, 127, 127, -128, -128]}      # CAST_TRUNC
+    for mode, w in want.items():
+        assert [fn(v, mode) for v in x] == w, mode
+    assert fn(float("nan"), 4) == 0
