@@ -82,11 +82,17 @@ struct Cfg {
     static constexpr int SF_CHUNKS = KIND == KIND_MXF4 ? 2 : 1;  // 512-byte scale chunks (4 scales per row) per 128 rows and K block
     static constexpr int SF_BYTES = IS_MX ? (1 + SF_B_BLOCKS) * SF_CHUNKS * SF_CHUNK_BYTES : 0;
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + SF_BYTES;
-    // output staging for bulk tensor stores: per epilogue warp 2 KB (2-byte chunk) + 1 KB (1-byte chunk)
-    static constexpr int EPI_BYTES_PER_WARP = (IS_MX && BLOCK_N == 256) ? 0 : 3072;
+    // output staging for bulk tensor stores, per epilogue warp: 3 KB hold a 2-byte chunk (2 KB) beside a 1-byte chunk (1 KB),
+    // or two 1-byte chunks in turn; 4 KB, taken where they cost no pipeline stage, also hold two 2-byte chunks in turn
+    static constexpr int stages_with(int epi_per_warp)
+    {
+        return std::min(8, (227 * 1024 - 1024 /*alignment slack*/ - 256 /*barriers*/ - 2 * (MAX_GROUPS + 1) * static_cast<int>(sizeof(int)) -
+                            NUM_EPI_WARPS * epi_per_warp) / STAGE_BYTES);
+    }
+    static constexpr int EPI_BYTES_PER_WARP = (IS_MX && BLOCK_N == 256) ? 0 : stages_with(4096) == stages_with(3072) ? 4096 : 3072;
     static constexpr int EPI_BYTES = NUM_EPI_WARPS * EPI_BYTES_PER_WARP;
     static constexpr int FIXED_BYTES = 1024 /*alignment slack*/ + 256 /*barriers*/ + 2 * (MAX_GROUPS + 1) * static_cast<int>(sizeof(int)) + EPI_BYTES;
-    static constexpr int NUM_STAGES = std::min(8, (227 * 1024 - FIXED_BYTES) / STAGE_BYTES);
+    static constexpr int NUM_STAGES = stages_with(EPI_BYTES_PER_WARP);
     static constexpr int ACC_STAGES = (IS_MX && BLOCK_N == 256) ? 1 : 2;  // 2 x 256 accumulator columns would leave no TMEM for scales
     static constexpr int ACC_COLS = ACC_STAGES * BLOCK_N;
     static constexpr int SF_COLS_PER_STAGE = 24;  // 8 for A + 16 for B
@@ -119,7 +125,8 @@ struct EpiStage {
     const CUtensorMap* map_c2;
     uint32_t smem_c, smem_c2;
     int row_base;  // first output row of the warp
-    bool dual;     // both outputs staged: two bulk groups are in flight per chunk
+    bool dual;     // the newest bulk group of this warp reads another buffer than the one written next: both outputs staged, or one
+                   // output staged into two buffers in turn
 };
 
 // Grouped mode: prefix sums of rows and of tiles per group, built once per CTA by warp 0.
@@ -507,9 +514,11 @@ __device__ __forceinline__ void load_params32(const float* p, int ncols, float (
 // The fixpipe stage for 32 accumulators r[] of output row `row`, columns col0 .. col0+ncols.
 // MODE / DT are compile-time so that each combination is a short straight-line sequence.
 // chan0: index of column col0 in bias / quant; ch_off: index in the per-channel scale array.
+// ch_lane: per-token x per-channel dequant only: the per-channel scale of column col0 + lane (0 beyond the chunk), loaded
+// one chunk ahead by the caller; the 32 lanes exchange them with shuffles.
 template <bool ACC_INT, int MODE, int DT>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const EpiParams& e, const EpiStage& st, int row, bool row_ok, int col0, int ncols,
-                                               size_t chan0, size_t ch_off, float tok)
+                                               size_t chan0, float ch_lane, float tok)
 {
     // Runs on all 32 lanes (the quantising path exchanges per-column parameters with shuffles); lanes whose
     // row lies outside the matrix compute on whatever their TMEM lane holds and store nothing.
@@ -585,21 +594,18 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
             }
         }
     } else if (e.act == 0) {  // ASCB200_EPI_DEQUANT_TOKEN_CHANNEL without activation: two packed multiplies per column pair
-        float s[32];
-        load_params32(e.ch + ch_off, ncols, s);
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
             // (acc * ch[n]) * tok[m], each product rounded to nearest like the separate Mul steps of the reference
-            float2 v = mul_f32x2(mul_f32x2(make_float2(f[j], f[j + 1]), make_float2(s[j], s[j + 1])), make_float2(tok, tok));
+            const float2 s = make_float2(__shfl_sync(0xFFFFFFFFu, ch_lane, j), __shfl_sync(0xFFFFFFFFu, ch_lane, j + 1));
+            float2 v = mul_f32x2(mul_f32x2(make_float2(f[j], f[j + 1]), s), make_float2(tok, tok));
             f[j] = v.x;
             f[j + 1] = v.y;
         }
     } else {  // ASCB200_EPI_DEQUANT_TOKEN_CHANNEL with FasterGelu
-        float s[32];
-        load_params32(e.ch + ch_off, ncols, s);
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-            float v = __fmul_rn(__fmul_rn(f[j], s[j]), tok);
+            float v = __fmul_rn(__fmul_rn(f[j], __shfl_sync(0xFFFFFFFFu, ch_lane, j)), tok);
             if (e.act == 1) v = faster_gelu(v);
             f[j] = v;
         }
@@ -641,14 +647,37 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
 }
 
 // Drains this warp's share of one accumulator tile: TMEM lanes of `quad`, chunks [chunk0, chunk1).
+// What an epilogue warp loads for its next tile before it waits for that tile's accumulators (per-token x per-channel dequant):
+// the per-token scale of the lane's row and the per-channel scale of the lane's column in the warp's first chunk.  Their
+// latency then falls into the wait instead of in front of the first chunk, which matters for a CTA's last tile, whose epilogue
+// nothing overlaps.
+struct EpiPre {
+    float tok, ch0;
+};
+__device__ __forceinline__ float load_ch_lane(const GemmParams& p, const TileInfo& t, int c, int lane)
+{
+    const int col = t.n0 + c * 32 + lane;
+    return (col < p.n && col < t.n_end) ? __ldg(p.epi.ch + static_cast<size_t>(t.group) * p.n + col) : 0.0f;
+}
+__device__ __forceinline__ EpiPre epilogue_preload(const GemmParams& p, const TileInfo& t, int quad, int lane, int chunk0)
+{
+    EpiPre r = {1.0f, 0.0f};
+    if (p.epi.mode != ASCB200_EPI_DEQUANT_TOKEN_CHANNEL) return r;
+    const int row = t.m64 ? t.row0 + quad * 16 + lane : t.row0 + quad * 32 + lane;
+    if (row < t.row_end && !(t.m64 && lane >= 16) && p.epi.tok) r.tok = __ldg(p.epi.tok + row);
+    r.ch0 = load_ch_lane(p, t, chunk0, lane);
+    return r;
+}
+
 template <bool ACC_INT, int MODE, int DT, int BLOCK_N>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInfo& t, const OutMaps& outs, uint32_t stage_smem, int stage_bytes,
-                                              uint32_t t_addr, int quad, int lane, int chunk0, int chunk1)
+                                              uint32_t t_addr, int quad, int lane, int chunk0, int chunk1, const EpiPre& pre)
 {
     // 128-row tiles: lane l of quadrant q holds row 32 q + l; 64-row tiles: lanes 0-15 hold rows 16 q + l
     const int row = t.m64 ? t.row0 + quad * 16 + lane : t.row0 + quad * 32 + lane;
     const bool row_ok = row < t.row_end && !(t.m64 && lane >= 16);
-    const float tok = (MODE == ASCB200_EPI_DEQUANT_TOKEN_CHANNEL && row_ok && p.epi.tok) ? __ldg(p.epi.tok + row) : 1.0f;
+    const float tok = MODE == ASCB200_EPI_DEQUANT_TOKEN_CHANNEL ? pre.tok : 1.0f;
+    float ch_cur = pre.ch0;
     EpiStage st;
     st.row_base = t.row0 + quad * 32;
     // bulk stores clip at the matrix edge only: a group that ends inside this warp's rows is stored from registers
@@ -663,31 +692,44 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
     st.smem_c = stage_smem;
     st.smem_c2 = stage_smem + c_used;
     st.dual = stage_c && stage_c2;
+    // one staged output and room for two of its chunks: chunks alternate between two buffers, so that a chunk is converted and
+    // written to shared memory while the TMA unit still reads the chunk before it.  The tile's first chunk waits for every
+    // earlier store of the warp (the previous tile may have ended on either buffer).
+    const bool alternate = stage_c && !stage_c2 && 2 * C_BYTES <= stage_bytes;
     const EpiStage direct = {nullptr, nullptr, 0u, 0u, st.row_base, false};
+    int staged = 0;  // chunks of this tile handed to the TMA unit so far
 #pragma unroll 1
     for (int c = chunk0; c < chunk1; ++c) {
         const int col0 = t.n0 + c * 32;
         if (col0 >= p.n || col0 >= t.n_end) break;  // uniform across the warp
         uint32_t r[32];
         tmem_ld_32x32(t_addr + c * 32, r);
+        // the next chunk's per-channel scales are requested now and arrive while this chunk is converted and stored
+        const float ch_next = (MODE == ASCB200_EPI_DEQUANT_TOKEN_CHANNEL && c + 1 < chunk1) ? load_ch_lane(p, t, c + 1, lane) : 0.0f;
         tmem_ld_wait();
         // a chunk that the tile only half owns (tile widths are multiples of 16) is stored from registers: the
         // bulk store's 32-column box would reach into the neighbouring tile.  So is a chunk that crosses the right edge of
         // the matrix: the TMA unit clips columns in 16-byte pieces, not per element (an int8 matrix of 328 columns got 8
         // bytes past its edge written), so only whole rows are left to its clipping.
         const bool whole = col0 + 32 <= t.n_end && col0 + 32 <= p.n;
+        if (alternate && whole) {
+            st.smem_c = stage_smem + ((staged & 1) ? C_BYTES : 0);
+            st.dual = staged > 0;
+            ++staged;
+        }
         epilogue_chunk<ACC_INT, MODE, DT>(r, p.epi, whole ? st : direct, row, row_ok, col0, min(whole ? 32 : t.n_end - col0, p.n - col0),
-                                          static_cast<size_t>(col0), static_cast<size_t>(t.group) * p.n + col0, tok);
+                                          static_cast<size_t>(col0), ch_cur, tok);
+        ch_cur = ch_next;
     }
 }
 
 template <bool ACC_INT, int BLOCK_N>
 __device__ __forceinline__ void epilogue_dispatch(const GemmParams& p, const TileInfo& t, const OutMaps& outs, uint32_t stage_smem, int stage_bytes,
-                                                  uint32_t t_addr, int quad, int lane, int chunk0, int chunk1)
+                                                  uint32_t t_addr, int quad, int lane, int chunk0, int chunk1, const EpiPre& pre)
 {
 #define ASCB200_EPI_CASE(MODE, DT)                                                                          \
     if (p.epi.mode == MODE && p.epi.c_dtype == DT) {                                                          \
-        epilogue_tile<ACC_INT, MODE, DT, BLOCK_N>(p, t, outs, stage_smem, stage_bytes, t_addr, quad, lane, chunk0, chunk1); \
+        epilogue_tile<ACC_INT, MODE, DT, BLOCK_N>(p, t, outs, stage_smem, stage_bytes, t_addr, quad, lane, chunk0, chunk1, pre); \
         return;                                                                                               \
     }
     if constexpr (ACC_INT) {
@@ -1023,12 +1065,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int tile = blockIdx.x; ok && locate_tile<BLOCK_N>(p, tile, num_m, total_tiles, row_start, tile_start, cursor, t); tile += gridDim.x, ++acc_iter) {
             const int acc_stage = acc_iter % C::ACC_STAGES;
             const uint32_t acc_phase = (acc_iter / C::ACC_STAGES) & 1u;
+            const EpiPre pre = epilogue_preload(p, t, quad, lane, chunk0);
             ok = mbar_wait_relaxed(smem_u32(&acc_full_bar[acc_stage]), acc_phase, abort_word, p.status);
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc_stage * BLOCK_N;
             epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, outs, smem_u32(epi_stage) + (warp - 4) * C::EPI_BYTES_PER_WARP, C::EPI_BYTES_PER_WARP, t_addr,
-                                                        quad, lane, chunk0, chunk1);
+                                                        quad, lane, chunk0, chunk1, pre);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[acc_stage]));
@@ -1118,10 +1161,14 @@ struct Cfg2 {
     static constexpr int SF_COLS_PER_STAGE = 24;
     static constexpr int SF_COL0 = ACC_STAGES * BLOCK_N;
     static constexpr int MAX_SF_STAGES = KIND == KIND_MXF4 ? (512 - SF_COL0) / SF_COLS_PER_STAGE : 8;
-    static constexpr int EPI_BYTES_PER_WARP = 3072;  // staged output chunks (see Cfg)
-    static constexpr int EPI_BYTES = NUM_EPI_WARPS * EPI_BYTES_PER_WARP;
     static constexpr int TABLE_BYTES = 2 * (MAX_GROUPS + 1) * static_cast<int>(sizeof(int));  // grouped mode: row and tile prefix sums
-    static constexpr int NUM_STAGES = std::min(8, (227 * 1024 - 1024 - 256 - EPI_BYTES - TABLE_BYTES) / STAGE_BYTES);
+    static constexpr int stages_with(int epi_per_warp)
+    {
+        return std::min(8, (227 * 1024 - 1024 - 256 - NUM_EPI_WARPS * epi_per_warp - TABLE_BYTES) / STAGE_BYTES);
+    }
+    static constexpr int EPI_BYTES_PER_WARP = stages_with(4096) == stages_with(3072) ? 4096 : 3072;  // staged output chunks (see Cfg)
+    static constexpr int EPI_BYTES = NUM_EPI_WARPS * EPI_BYTES_PER_WARP;
+    static constexpr int NUM_STAGES = stages_with(EPI_BYTES_PER_WARP);
     static constexpr int SF_SLOTS = std::min(NUM_STAGES, MAX_SF_STAGES);  // scale-factor slots in TMEM
     static constexpr int TMEM_COLS = 512;
     static_assert(ACC_STAGES * BLOCK_N + (KIND == KIND_MXF4 ? SF_SLOTS * SF_COLS_PER_STAGE : 0) <= 512, "TMEM budget");
@@ -1386,6 +1433,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int tile; ok && feed.take(total_tiles, tile, ok, abort_word, p.status) && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t); ++acc_iter) {
             const int acc_stage = acc_iter & 1;
             const uint32_t acc_phase = (acc_iter >> 1) & 1u;
+            if (!t.swap_n) t.row0 += static_cast<int>(rank) * BLOCK_M;  // this CTA's half of the pair tile
+            const EpiPre pre = t.swap_n ? EpiPre{1.0f, 0.0f} : epilogue_preload(p, t, quad, lane, chunk0);
             ok = mbar_wait_relaxed(smem_u32(&acc_full_bar[acc_stage]), acc_phase, abort_word, p.status);
             if (!ok) break;
             tc_fence_after();
@@ -1399,9 +1448,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 else if (p.epi.c_dtype == OUT_F16) epilogue_tile_swapped<OUT_F16>(p, t, t_addr, n_lane, lane, c0, c1);
                 else epilogue_tile_swapped<OUT_F32>(p, t, t_addr, n_lane, lane, c0, c1);
             } else {
-                t.row0 += static_cast<int>(rank) * BLOCK_M;  // this CTA's half of the pair tile
                 epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, outs, smem_u32(epi_stage) + (warp - 4) * C::EPI_BYTES_PER_WARP, C::EPI_BYTES_PER_WARP,
-                                                            t_addr, quad, lane, chunk0, chunk1);
+                                                            t_addr, quad, lane, chunk0, chunk1, pre);
             }
             tc_fence_before();
             __syncwarp();
