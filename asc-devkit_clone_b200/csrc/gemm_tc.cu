@@ -82,17 +82,12 @@ struct Cfg {
     static constexpr int SF_CHUNKS = KIND == KIND_MXF4 ? 2 : 1;  // 512-byte scale chunks (4 scales per row) per 128 rows and K block
     static constexpr int SF_BYTES = IS_MX ? (1 + SF_B_BLOCKS) * SF_CHUNKS * SF_CHUNK_BYTES : 0;
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + SF_BYTES;
-    // output staging for bulk tensor stores, per epilogue warp: 3 KB hold a 2-byte chunk (2 KB) beside a 1-byte chunk (1 KB),
-    // or two 1-byte chunks in turn; 4 KB, taken where they cost no pipeline stage, also hold two 2-byte chunks in turn
-    static constexpr int stages_with(int epi_per_warp)
-    {
-        return std::min(8, (227 * 1024 - 1024 /*alignment slack*/ - 256 /*barriers*/ - 2 * (MAX_GROUPS + 1) * static_cast<int>(sizeof(int)) -
-                            NUM_EPI_WARPS * epi_per_warp) / STAGE_BYTES);
-    }
-    static constexpr int EPI_BYTES_PER_WARP = (IS_MX && BLOCK_N == 256) ? 0 : stages_with(4096) == stages_with(3072) ? 4096 : 3072;
+    // per epilogue warp: 2 KB stage a 2-byte output chunk for its bulk tensor store; the third KB stages a 1-byte chunk beside it
+    // (two outputs) or, for the per-token x per-channel dequant, holds the per-channel scales of the warp's columns
+    static constexpr int EPI_BYTES_PER_WARP = (IS_MX && BLOCK_N == 256) ? 0 : 3072;
     static constexpr int EPI_BYTES = NUM_EPI_WARPS * EPI_BYTES_PER_WARP;
     static constexpr int FIXED_BYTES = 1024 /*alignment slack*/ + 256 /*barriers*/ + 2 * (MAX_GROUPS + 1) * static_cast<int>(sizeof(int)) + EPI_BYTES;
-    static constexpr int NUM_STAGES = stages_with(EPI_BYTES_PER_WARP);
+    static constexpr int NUM_STAGES = std::min(8, (227 * 1024 - FIXED_BYTES) / STAGE_BYTES);
     static constexpr int ACC_STAGES = (IS_MX && BLOCK_N == 256) ? 1 : 2;  // 2 x 256 accumulator columns would leave no TMEM for scales
     static constexpr int ACC_COLS = ACC_STAGES * BLOCK_N;
     static constexpr int SF_COLS_PER_STAGE = 24;  // 8 for A + 16 for B
@@ -125,8 +120,7 @@ struct EpiStage {
     const CUtensorMap* map_c2;
     uint32_t smem_c, smem_c2;
     int row_base;  // first output row of the warp
-    bool dual;     // the newest bulk group of this warp reads another buffer than the one written next: both outputs staged, or one
-                   // output staged into two buffers in turn
+    bool dual;     // both outputs staged: two bulk groups are in flight per chunk
 };
 
 // Grouped mode: prefix sums of rows and of tiles per group, built once per CTA by warp 0.
@@ -223,9 +217,14 @@ __device__ __forceinline__ bool locate_pair_tile(const GemmParams& p, int tile, 
 // (quant_group_matmul_high_performance/scripts/gen_data.py:19-23), which is x / (1 + e^(-1.702 x)) written
 // so that no exponential overflows.  Evaluated in the short form with one ex2 and one fast division:
 // for x << 0 the exponential overflows to +inf and the quotient is -0, the limit of the long form.
+// Five instructions per value: the flush-to-zero forms of ex2 and rcp need none of the range handling that the compiler
+// wraps around __expf and __fdividef (about forty instructions per value, which made the epilogue issue bound).
 __device__ __forceinline__ float faster_gelu(float x)
 {
-    return __fdividef(x, 1.0f + __expf(-1.702f * x));
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -2.4554669595930156f));  // e^(-1.702 x) = 2^(-1.702 log2(e) x)
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return x * r;
 }
 
 // fp32 -> int8 value, round to nearest even, saturating, NaN -> 0 (one conversion instruction).
@@ -257,11 +256,10 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
 }
 __device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi)
 {
-    // round to nearest even; overflow saturates to +-65504 (NaN is kept)
-    lo = (lo != lo) ? lo : fminf(fmaxf(lo, -65504.0f), 65504.0f);
-    hi = (hi != hi) ? hi : fminf(fmaxf(hi, -65504.0f), 65504.0f);
-    __half2 v = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
+    // round to nearest even; overflow and infinities saturate to +-65504, NaN is kept: one instruction for both values
+    uint32_t v;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(v) : "f"(hi), "f"(lo));
+    return v;
 }
 
 // Stores 32 consecutive outputs of one row; DT is the element type of the destination.
@@ -514,11 +512,11 @@ __device__ __forceinline__ void load_params32(const float* p, int ncols, float (
 // The fixpipe stage for 32 accumulators r[] of output row `row`, columns col0 .. col0+ncols.
 // MODE / DT are compile-time so that each combination is a short straight-line sequence.
 // chan0: index of column col0 in bias / quant; ch_off: index in the per-channel scale array.
-// ch_lane: per-token x per-channel dequant only: the per-channel scale of column col0 + lane (0 beyond the chunk), loaded
-// one chunk ahead by the caller; the 32 lanes exchange them with shuffles.
+// ch_smem: per-token x per-channel dequant only: shared-memory address of the chunk's 32 per-channel scales (0 beyond the
+// tile or the matrix), which the caller put there before the tile's first chunk.
 template <bool ACC_INT, int MODE, int DT>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const EpiParams& e, const EpiStage& st, int row, bool row_ok, int col0, int ncols,
-                                               size_t chan0, float ch_lane, float tok)
+                                               size_t chan0, uint32_t ch_smem, float tok)
 {
     // Runs on all 32 lanes (the quantising path exchanges per-column parameters with shuffles); lanes whose
     // row lies outside the matrix compute on whatever their TMEM lane holds and store nothing.
@@ -593,21 +591,21 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
                 f[j] = v;
             }
         }
-    } else if (e.act == 0) {  // ASCB200_EPI_DEQUANT_TOKEN_CHANNEL without activation: two packed multiplies per column pair
+    } else {  // ASCB200_EPI_DEQUANT_TOKEN_CHANNEL
+        float s[32];  // every lane reads the same 16 bytes: one broadcast per load
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-            // (acc * ch[n]) * tok[m], each product rounded to nearest like the separate Mul steps of the reference
-            const float2 s = make_float2(__shfl_sync(0xFFFFFFFFu, ch_lane, j), __shfl_sync(0xFFFFFFFFu, ch_lane, j + 1));
-            float2 v = mul_f32x2(mul_f32x2(make_float2(f[j], f[j + 1]), s), make_float2(tok, tok));
-            f[j] = v.x;
-            f[j + 1] = v.y;
-        }
-    } else {  // ASCB200_EPI_DEQUANT_TOKEN_CHANNEL with FasterGelu
+        for (int j = 0; j < 32; j += 4) ld_shared_v4(ch_smem + 4 * j, s[j], s[j + 1], s[j + 2], s[j + 3]);
+        if (e.act == 0) {  // without activation: two packed multiplies per column pair
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            float v = __fmul_rn(__fmul_rn(f[j], __shfl_sync(0xFFFFFFFFu, ch_lane, j)), tok);
-            if (e.act == 1) v = faster_gelu(v);
-            f[j] = v;
+            for (int j = 0; j < 32; j += 2) {
+                // (acc * ch[n]) * tok[m], each product rounded to nearest like the separate Mul steps of the reference
+                float2 v = mul_f32x2(mul_f32x2(make_float2(f[j], f[j + 1]), make_float2(s[j], s[j + 1])), make_float2(tok, tok));
+                f[j] = v.x;
+                f[j + 1] = v.y;
+            }
+        } else {  // FasterGelu
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = faster_gelu(__fmul_rn(__fmul_rn(f[j], s[j]), tok));
         }
     }
     if constexpr (DT == OUT_E4M3 || DT == OUT_E5M2) {
@@ -648,24 +646,30 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const Ep
 
 // Drains this warp's share of one accumulator tile: TMEM lanes of `quad`, chunks [chunk0, chunk1).
 // What an epilogue warp loads for its next tile before it waits for that tile's accumulators (per-token x per-channel dequant):
-// the per-token scale of the lane's row and the per-channel scale of the lane's column in the warp's first chunk.  Their
-// latency then falls into the wait instead of in front of the first chunk, which matters for a CTA's last tile, whose epilogue
-// nothing overlaps.
+// the per-token scale of the lane's row and four of the per-channel scales of the warp's columns (the warp owns at most four
+// chunks = 128 columns; lane l loads columns 4 l .. 4 l + 3 of them).  Their latency then falls into the wait instead of in
+// front of the first chunk, which matters for a CTA's last tile, whose epilogue nothing overlaps.
 struct EpiPre {
-    float tok, ch0;
+    float tok;
+    float4 ch;
 };
-__device__ __forceinline__ float load_ch_lane(const GemmParams& p, const TileInfo& t, int c, int lane)
-{
-    const int col = t.n0 + c * 32 + lane;
-    return (col < p.n && col < t.n_end) ? __ldg(p.epi.ch + static_cast<size_t>(t.group) * p.n + col) : 0.0f;
-}
+constexpr int kEpiChOffset = 2048;  // where in a warp's staging area the per-channel scales live (behind the 2-byte output chunk)
 __device__ __forceinline__ EpiPre epilogue_preload(const GemmParams& p, const TileInfo& t, int quad, int lane, int chunk0)
 {
-    EpiPre r = {1.0f, 0.0f};
+    EpiPre r = {1.0f, make_float4(0.0f, 0.0f, 0.0f, 0.0f)};
     if (p.epi.mode != ASCB200_EPI_DEQUANT_TOKEN_CHANNEL) return r;
     const int row = t.m64 ? t.row0 + quad * 16 + lane : t.row0 + quad * 32 + lane;
     if (row < t.row_end && !(t.m64 && lane >= 16) && p.epi.tok) r.tok = __ldg(p.epi.tok + row);
-    r.ch0 = load_ch_lane(p, t, chunk0, lane);
+    const int col = t.n0 + chunk0 * 32 + lane * 4, end = min(p.n, t.n_end);
+    const float* src = p.epi.ch + static_cast<size_t>(t.group) * p.n + col;
+    if (col + 4 <= end && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        r.ch = __ldg(reinterpret_cast<const float4*>(src));
+    } else {
+        if (col < end) r.ch.x = __ldg(src);
+        if (col + 1 < end) r.ch.y = __ldg(src + 1);
+        if (col + 2 < end) r.ch.z = __ldg(src + 2);
+        if (col + 3 < end) r.ch.w = __ldg(src + 3);
+    }
     return r;
 }
 
@@ -677,7 +681,12 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
     const int row = t.m64 ? t.row0 + quad * 16 + lane : t.row0 + quad * 32 + lane;
     const bool row_ok = row < t.row_end && !(t.m64 && lane >= 16);
     const float tok = MODE == ASCB200_EPI_DEQUANT_TOKEN_CHANNEL ? pre.tok : 1.0f;
-    float ch_cur = pre.ch0;
+    if constexpr (MODE == ASCB200_EPI_DEQUANT_TOKEN_CHANNEL) {
+        __syncwarp();  // every lane has finished reading the previous tile's scales
+        st_shared_v4(stage_smem + kEpiChOffset + lane * 16, __float_as_uint(pre.ch.x), __float_as_uint(pre.ch.y), __float_as_uint(pre.ch.z),
+                     __float_as_uint(pre.ch.w));
+        __syncwarp();
+    }
     EpiStage st;
     st.row_base = t.row0 + quad * 32;
     // bulk stores clip at the matrix edge only: a group that ends inside this warp's rows is stored from registers
@@ -692,34 +701,21 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
     st.smem_c = stage_smem;
     st.smem_c2 = stage_smem + c_used;
     st.dual = stage_c && stage_c2;
-    // one staged output and room for two of its chunks: chunks alternate between two buffers, so that a chunk is converted and
-    // written to shared memory while the TMA unit still reads the chunk before it.  The tile's first chunk waits for every
-    // earlier store of the warp (the previous tile may have ended on either buffer).
-    const bool alternate = stage_c && !stage_c2 && 2 * C_BYTES <= stage_bytes;
     const EpiStage direct = {nullptr, nullptr, 0u, 0u, st.row_base, false};
-    int staged = 0;  // chunks of this tile handed to the TMA unit so far
 #pragma unroll 1
     for (int c = chunk0; c < chunk1; ++c) {
         const int col0 = t.n0 + c * 32;
         if (col0 >= p.n || col0 >= t.n_end) break;  // uniform across the warp
         uint32_t r[32];
         tmem_ld_32x32(t_addr + c * 32, r);
-        // the next chunk's per-channel scales are requested now and arrive while this chunk is converted and stored
-        const float ch_next = (MODE == ASCB200_EPI_DEQUANT_TOKEN_CHANNEL && c + 1 < chunk1) ? load_ch_lane(p, t, c + 1, lane) : 0.0f;
         tmem_ld_wait();
         // a chunk that the tile only half owns (tile widths are multiples of 16) is stored from registers: the
         // bulk store's 32-column box would reach into the neighbouring tile.  So is a chunk that crosses the right edge of
         // the matrix: the TMA unit clips columns in 16-byte pieces, not per element (an int8 matrix of 328 columns got 8
         // bytes past its edge written), so only whole rows are left to its clipping.
         const bool whole = col0 + 32 <= t.n_end && col0 + 32 <= p.n;
-        if (alternate && whole) {
-            st.smem_c = stage_smem + ((staged & 1) ? C_BYTES : 0);
-            st.dual = staged > 0;
-            ++staged;
-        }
         epilogue_chunk<ACC_INT, MODE, DT>(r, p.epi, whole ? st : direct, row, row_ok, col0, min(whole ? 32 : t.n_end - col0, p.n - col0),
-                                          static_cast<size_t>(col0), ch_cur, tok);
-        ch_cur = ch_next;
+                                          static_cast<size_t>(col0), stage_smem + kEpiChOffset + (c - chunk0) * 128, tok);
     }
 }
 
@@ -917,6 +913,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // 128-byte swizzled tiles need 1024-byte aligned bases
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* tiles = smem;
+    static_assert(KIND != KIND_I8 || C::EPI_BYTES_PER_WARP >= kEpiChOffset + 512, "room for the per-channel scales of four chunks");
     uint8_t* epi_stage = smem + C::NUM_STAGES * C::STAGE_BYTES;  // [NUM_EPI_WARPS][EPI_BYTES_PER_WARP], 1024-byte aligned
     uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + C::EPI_BYTES);
     uint64_t* full_bar = bars;                         // [NUM_STAGES]
@@ -1161,14 +1158,10 @@ struct Cfg2 {
     static constexpr int SF_COLS_PER_STAGE = 24;
     static constexpr int SF_COL0 = ACC_STAGES * BLOCK_N;
     static constexpr int MAX_SF_STAGES = KIND == KIND_MXF4 ? (512 - SF_COL0) / SF_COLS_PER_STAGE : 8;
-    static constexpr int TABLE_BYTES = 2 * (MAX_GROUPS + 1) * static_cast<int>(sizeof(int));  // grouped mode: row and tile prefix sums
-    static constexpr int stages_with(int epi_per_warp)
-    {
-        return std::min(8, (227 * 1024 - 1024 - 256 - NUM_EPI_WARPS * epi_per_warp - TABLE_BYTES) / STAGE_BYTES);
-    }
-    static constexpr int EPI_BYTES_PER_WARP = stages_with(4096) == stages_with(3072) ? 4096 : 3072;  // staged output chunks (see Cfg)
+    static constexpr int EPI_BYTES_PER_WARP = 3072;  // staged output chunks and per-channel scales (see Cfg)
     static constexpr int EPI_BYTES = NUM_EPI_WARPS * EPI_BYTES_PER_WARP;
-    static constexpr int NUM_STAGES = stages_with(EPI_BYTES_PER_WARP);
+    static constexpr int TABLE_BYTES = 2 * (MAX_GROUPS + 1) * static_cast<int>(sizeof(int));  // grouped mode: row and tile prefix sums
+    static constexpr int NUM_STAGES = std::min(8, (227 * 1024 - 1024 - 256 - EPI_BYTES - TABLE_BYTES) / STAGE_BYTES);
     static constexpr int SF_SLOTS = std::min(NUM_STAGES, MAX_SF_STAGES);  // scale-factor slots in TMEM
     static constexpr int TMEM_COLS = 512;
     static_assert(ACC_STAGES * BLOCK_N + (KIND == KIND_MXF4 ? SF_SLOTS * SF_COLS_PER_STAGE : 0) <= 512, "TMEM budget");
@@ -1189,6 +1182,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // both CTAs must use identical offsets: the dynamic shared memory window starts at the same offset in each
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* tiles = smem;
+    static_assert(KIND != KIND_I8 || C::EPI_BYTES_PER_WARP >= kEpiChOffset + 512, "room for the per-channel scales of four chunks");
     uint8_t* epi_stage = smem + C::NUM_STAGES * C::STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + C::EPI_BYTES);
     uint64_t* full_bar = bars;
@@ -1453,7 +1447,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(smem_u32(&acc_empty_bar[acc_stage]) & kPeerBitMask);
+            if (lane == 0) mbar_arrive_cluster_tmem(smem_u32(&acc_empty_bar[acc_stage]) & kPeerBitMask);
         }
         if (lane == 0) bulk_wait_group_read<0>();
     }

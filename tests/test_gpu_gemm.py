@@ -190,6 +190,29 @@ def test_gemm_a8w8_token_channel_dequant(m, n, k, c_dtype):
     assert (d_c.download() == ref).all()
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 512, 256), (200, 328, 128)])   # staged bulk stores / stores from registers at the ragged edge
+def test_gemm_a8w8_dequant_to_half_saturates_and_keeps_nan(m, n, k):
+    """fp16 output of the dequant epilogue: products beyond the half range (and infinite ones) become +-65504 like the
+    reference's saturating cast, a NaN scale stays NaN; everything else bit exact."""
+    ab = dev()
+    rng, a, b = _i8_inputs(m, n, k, False, True, 77)
+    tok = rng.uniform(0.5, 2.0, m).astype(np.float32)
+    ch = rng.uniform(0.5, 2.0, n).astype(np.float32)   # |acc| reaches 1e5 and more: many products overflow half
+    ch[3] = np.inf
+    ch[n - 2] = np.nan
+    tok[5] = 3.0e38                                   # overflows fp32 in the second product
+    d_c = ab.empty((m, n), np.uint16)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.F16, epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL,
+                     trans_b=True, tok=ab.to_dev(tok), ch=ab.to_dev(ch)))
+    ab.sync()
+    got = d_c.download()
+    ref = orc.dequant_tok_ch(orc.gemm_i8(a, b, trans_b=True), tok, ch, ab.F16)
+    nan = (ref & 0x7FFF) > 0x7C00
+    assert nan.any() and ((ref & 0x7FFF) == 0x7BFF).any() and not ((ref & 0x7FFF) == 0x7C00).any()
+    assert (((got & 0x7FFF) > 0x7C00) == nan).all()
+    assert (got[~nan] == ref[~nan]).all()
+
+
 @pytest.mark.parametrize("trans_b", [True, False])
 @pytest.mark.parametrize("counts", [[40, 0, 7, 300], [128, 128], [1, 1, 1, 1, 1, 500, 0, 0, 3]])
 def test_grouped_a8w8(counts, trans_b):
