@@ -93,6 +93,7 @@ int ascb200_init(int device)
     if (prop.major != 10) return ASCB200_ENODEV;
     st->device = device;
     st->sm_count = prop.multiProcessorCount;
+    st->l2_bytes = prop.l2CacheSize;
     ASCB200_CUDA(cudaMalloc(&st->status_dev, 256));
     ASCB200_CUDA(cudaMemset(st->status_dev, 0, 256));
     st->ready = true;

@@ -14,6 +14,7 @@ struct DeviceState {
     bool ready = false;
     int device = -1;
     int sm_count = 0;
+    long long l2_bytes = 0;
     uint32_t* status_dev = nullptr;  // bit 0: bounded wait expired inside a GEMM kernel
     // scratch for re-tiled MX scale factors, one block per stream that asked for one (grows on demand)
     struct StreamScratch {

@@ -92,6 +92,25 @@ def test_gemm_i8_cta_pair_exact(m, n, k, trans_a, trans_b):
     assert (got == ref).all(), f"{(got != ref).sum()} of {ref.size} differ; first {np.argwhere(got != ref)[:5].tolist()}"
 
 
+@pytest.mark.parametrize("band", [1, 2, 4, 7])
+@pytest.mark.parametrize("m,n,k,no_pair", [(2200, 2568, 272, False), (1100, 712, 144, True)])
+def test_gemm_i8_banded_tile_order_exact(m, n, k, no_pair, band, monkeypatch):
+    """The banded tile order (bands of `band` row blocks, the last band narrower) that large A operands take by themselves,
+    forced here on small shapes: every tile is still computed exactly once, on CTA pairs and on single CTAs."""
+    monkeypatch.setenv("ASCB200_BAND_M", str(band))
+    if no_pair:
+        monkeypatch.setenv("ASCB200_NO_PAIR", "1")
+    ab = dev()
+    rng, a, b = _i8_inputs(m, n, k, False, True, m + band)
+    d_c = ab.empty((m, n), np.int32)
+    d_c.fill(0x5A)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.S32, trans_b=True))
+    ab.sync()
+    ref = orc.gemm_i8(a, b, None, trans_b=True)
+    got = d_c.download()
+    assert (got == ref).all(), f"{(got != ref).sum()} of {ref.size} differ; first {np.argwhere(got != ref)[:5].tolist()}"
+
+
 @pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, False)])
 def test_gemm_f16_cta_pair(trans_a, trans_b):
     run_f16(2304, 2560, 192, trans_a, trans_b, bias=True, c_dtype=0, seed=31)
