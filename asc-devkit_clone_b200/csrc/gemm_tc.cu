@@ -1166,7 +1166,10 @@ struct TileFeed {
         }
         tile = slots[s];
         __syncwarp();
-        if ((threadIdx.x & 31) == 0) mbar_arrive_cluster(empty0 + 8 * s);
+        // The slot may be rewritten once every reader has arrived.  The arrival's address is made to depend on the value read
+        // (tile numbers are below 2^30, so the added term is zero), so it cannot leave before the read has returned; it then
+        // needs no cluster-scope release, which would first wait for all of the warp's stores in flight.
+        if ((threadIdx.x & 31) == 0) mbar_arrive_cluster_tmem(empty0 + 8 * s + (static_cast<uint32_t>(tile + 1) >> 30));
         return tile >= 0;
     }
 };
