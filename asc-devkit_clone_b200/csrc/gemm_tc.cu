@@ -67,6 +67,8 @@ struct GemmParams {
     int pair_n;              // CTA-pair kernels for fp16 / bf16 / int8: columns per tile (multiple of 16, at most 256)
     int allow_m64;           // fp16 / bf16 / int8, single-CTA kernel: tiles of at most 64 rows use the 64-row instruction
     int band_m;              // not grouped: tiles are walked in bands of band_m row blocks (all columns of a band before the next band)
+    int ring_stages;         // CTA-pair kernels, fp16 / bf16 / int8 with K-major B: the shared-memory ring is cut for the call's tile width,
+    int ring_stage_bytes;    // so that narrower tiles get more stages in flight (0: the kernel's compile-time geometry)
     int group_swap;          // grouped int8 on CTA pairs: a group's last, partial 256-row block is multiplied with the operand roles swapped
     uint32_t idesc;
     uint32_t idesc_swap;     // instruction descriptor of such a block without its N field (the weights are then the 256-row operand)
@@ -821,8 +823,13 @@ struct IssueCursor {
     uint32_t a_lo0, b_lo0, sf_lo0, full_bar0, empty_bar0, sf_tmem0;
     int stage, sf_slot;  // the TMEM columns of the scales rotate on their own (fewer slots than shared-memory stages fit TMEM)
     uint32_t phase;
-    __device__ __forceinline__ void init(uint32_t tiles_addr, uint32_t a_lbo_enc, uint32_t b_lbo_enc, uint32_t full0, uint32_t empty0, uint32_t sf_tmem_base)
+    uint32_t step16;     // bytes between stages / 16 and the number of stages: the template's, unless the ring was cut at run time
+    int nstages;
+    __device__ __forceinline__ void init(uint32_t tiles_addr, uint32_t a_lbo_enc, uint32_t b_lbo_enc, uint32_t full0, uint32_t empty0, uint32_t sf_tmem_base,
+                                         int stages = NUM_STAGES, int stage_bytes = STAGE_BYTES)
     {
+        nstages = stages;
+        step16 = static_cast<uint32_t>(stage_bytes) >> 4;
         a_lo0 = (a_lbo_enc << 16) | (tiles_addr >> 4);
         b_lo0 = (b_lbo_enc << 16) | ((tiles_addr + B_OFFSET) >> 4);
         sf_lo0 = (1u << 16) | ((tiles_addr + SF_OFFSET) >> 4);   // no-swizzle descriptor, leading offset 16 bytes
@@ -845,13 +852,13 @@ struct IssueCursor {
     }
     __device__ __forceinline__ void advance()
     {
-        if (++stage == NUM_STAGES) {
+        if (++stage == nstages) {
             rewind();
             phase ^= 1u;
         } else {
-            a_lo += STAGE_BYTES >> 4;
-            b_lo += STAGE_BYTES >> 4;
-            sf_lo += STAGE_BYTES >> 4;
+            a_lo += step16;
+            b_lo += step16;
+            sf_lo += step16;
             full_bar += 8;
             empty_bar += 8;
         }
@@ -1130,6 +1137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // barrier.  A negative number ends the kernel.  The ring lets the producer run one tile ahead of the epilogue and no more,
 // so that at the end of the kernel no cluster sits on tiles that an idle one could take.
 constexpr int kSchedSlots = 2;
+constexpr int kMaxRingStages = 8;  // barrier storage of the CTA-pair kernel's operand ring
 constexpr int kSchedConsumersLeader = 1 + 1 + NUM_EPI_WARPS, kSchedConsumersPeer = 1 + NUM_EPI_WARPS;
 struct TileFeed {
     int next, stride;            // static
@@ -1212,16 +1220,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     static_assert(KIND != KIND_I8 || C::EPI_BYTES_PER_WARP >= kEpiChOffset + 512, "room for the per-channel scales of four chunks");
     uint8_t* epi_stage = smem + C::NUM_STAGES * C::STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + C::EPI_BYTES);
-    uint64_t* full_bar = bars;
-    uint64_t* empty_bar = bars + C::NUM_STAGES;
-    uint64_t* acc_full_bar = bars + 2 * C::NUM_STAGES;
+    uint64_t* full_bar = bars;                 // [kMaxRingStages]
+    uint64_t* empty_bar = bars + kMaxRingStages;
+    uint64_t* acc_full_bar = bars + 2 * kMaxRingStages;
     uint64_t* acc_empty_bar = acc_full_bar + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
     uint64_t* sched_full = reinterpret_cast<uint64_t*>(tmem_slot + 2);   // [kSchedSlots] in each CTA
     uint64_t* sched_empty = sched_full + kSchedSlots;                   // [kSchedSlots], the leader's are used
     volatile int* sched_tile = reinterpret_cast<volatile int*>(sched_empty + kSchedSlots);  // [kSchedSlots] in each CTA
-    static_assert((2 * 8 + 4 + 2 * kSchedSlots) * 8 + 8 + kSchedSlots * 4 <= 256, "barrier area");
+    static_assert((2 * kMaxRingStages + 4 + 2 * kSchedSlots) * 8 + 8 + kSchedSlots * 4 <= 256, "barrier area");
+    static_assert(C::NUM_STAGES <= kMaxRingStages, "barrier area");
+    // The ring of operand stages: the compile-time geometry, or (narrower tiles of a call) more and smaller stages in the same bytes.
+    const bool cut_ring = KIND != KIND_MXF4 && p.ring_stages > 0;
+    const int num_stages = cut_ring ? p.ring_stages : C::NUM_STAGES;
+    const int stage_bytes = cut_ring ? p.ring_stage_bytes : C::STAGE_BYTES;
     int* row_start = reinterpret_cast<int*>(epi_stage + C::EPI_BYTES + 256);  // both CTAs build identical tables
     int* tile_start = row_start + (MAX_GROUPS + 1);
 
@@ -1237,7 +1250,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int num_m = (p.m + PAIR_M - 1) / PAIR_M;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::NUM_STAGES; ++s) {
+        for (int s = 0; s < num_stages; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
@@ -1292,7 +1305,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (elect_one()) {
                     const uint32_t own_bar = smem_u32(&full_bar[stage]);
                     const uint32_t bar = own_bar & kPeerBitMask;  // the leader's barrier counts both CTAs' bytes
-                    const uint32_t sa = smem_u32(tiles + stage * C::STAGE_BYTES);
+                    const uint32_t sa = smem_u32(tiles) + stage * stage_bytes;
                     const uint32_t sb = sa + A_TILE_BYTES;
                     if (rank == 0) mbar_expect_tx(own_bar, 2 * (a_bytes + (bn / 2) * ROW_BYTES + C::SF_BYTES));
                     const int k0 = kb * C::BLOCK_K;
@@ -1325,7 +1338,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                 }
                 __syncwarp();
-                if (++stage == C::NUM_STAGES) {
+                if (++stage == num_stages) {
                     stage = 0;
                     phase ^= 1u;
                 }
@@ -1333,9 +1346,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         // drain: every stage's last release (a multicast commit from the leader) must have landed in
         // this CTA's shared memory before the CTA may exit
-        for (int i = 0; ok && i < C::NUM_STAGES; ++i) {
+        for (int i = 0; ok && i < num_stages; ++i) {
             ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_word, p.status);
-            if (++stage == C::NUM_STAGES) {
+            if (++stage == num_stages) {
                 stage = 0;
                 phase ^= 1u;
             }
@@ -1349,7 +1362,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t a_k16 = (p.a_mn ? C::UMMA_K * ROW_BYTES : 32) >> 4, b_k16 = (p.b_mn ? C::UMMA_K * ROW_BYTES : 32) >> 4;
         const uint32_t idesc_hi_sf = p.idesc | (2u << 4) | (2u << 29);
         IssueCursor<C::STAGE_BYTES, C::NUM_STAGES, A_TILE_BYTES, A_TILE_BYTES + C::B_TILE_BYTES, C::SF_COLS_PER_STAGE, C::SF_SLOTS> cur;
-        cur.init(smem_u32(tiles), a_lbo, b_lbo, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]), tmem_base + C::SF_COL0);
+        cur.init(smem_u32(tiles), a_lbo, b_lbo, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]), tmem_base + C::SF_COL0, num_stages, stage_bytes);
         int cursor = 0;
         TileInfo t;
         TileFeed feed;
@@ -1653,7 +1666,15 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
         ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured[dev & 15] = true;
     }
-    ASCB200_CUDA(launch_pdl(gemm_tc_pair_kernel<KIND, BLOCK_N>, 2 * clusters, NUM_THREADS, C::SMEM_BYTES, stream, ta, tb, tsfa, tsfb, outs, p));
+    GemmParams q = p;
+    if (KIND != KIND_MXF4 && !p.b_mn && !(getenv("ASCB200_NO_RING_CUT") && getenv("ASCB200_NO_RING_CUT")[0] == '1')) {
+        // K-major B: a stage holds 128 rows of A and pair_n / 2 rows of B.  The operand round trip (stage released -> producer
+        // -> L2 -> shared memory -> MMA) takes about 3000 cycles, so with six stages a K block cannot take less than about 510
+        // cycles whatever the tile width; narrower tiles get the same bytes as more stages.
+        q.ring_stage_bytes = A_TILE_BYTES + (p.pair_n / 2) * ROW_BYTES;
+        q.ring_stages = std::min(kMaxRingStages, C::NUM_STAGES * C::STAGE_BYTES / q.ring_stage_bytes);
+    }
+    ASCB200_CUDA(launch_pdl(gemm_tc_pair_kernel<KIND, BLOCK_N>, 2 * clusters, NUM_THREADS, C::SMEM_BYTES, stream, ta, tb, tsfa, tsfb, outs, q));
     return ASCB200_OK;
 }
 
