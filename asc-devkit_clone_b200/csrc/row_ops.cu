@@ -242,6 +242,12 @@ __device__ __forceinline__ void softmax_one_row(const uint4 (&raw)[NCHUNK], int 
 }
 
 constexpr int kSoftmaxWarpBlock = 224;  // 7 warps; two such blocks per SM
+#ifndef ASCB200_SOFTMAX_PREFETCH_ROWS
+#define ASCB200_SOFTMAX_PREFETCH_ROWS 1
+#endif
+// Rows per warp requested from L2 before the dependency wait.  Measured on 4096 x 2048 halves with the fused quantisation,
+// cold inputs, consecutive launches of one stream: 8.93 us without, 8.06 us with one row, 8.96 us with two or four.
+constexpr int kSoftmaxPrefetchRows = ASCB200_SOFTMAX_PREFETCH_ROWS;
 
 // PERSIST (warp rows only): few rows per warp -> machine-sized grid with next-row prefetch; many rows ->
 // one row per warp and small blocks, where 20 resident warps per SM keep more requests in flight.
@@ -254,6 +260,16 @@ softmax_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, float* __res
     constexpr int VEC = 16 / sizeof(T);
     __shared__ float red[32];
     const int nchunks = k / VEC;
+    if constexpr (TPR <= 32) {
+        // While the kernel before this one in the stream drains, ask L2 for the warp's first row (a hint: nothing is read into
+        // the program before the dependency wait, and L2 stays coherent if that kernel still writes the row).
+        const int first = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+        const int line = (threadIdx.x & 31) * 128;
+        const int ahead_rows = PERSIST ? kSoftmaxPrefetchRows : 1;
+        for (int i = 0, row = first; i < ahead_rows && row < m; ++i, row += gridDim.x * (blockDim.x >> 5))
+            if (line < k * static_cast<int>(sizeof(T)))
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(src + static_cast<size_t>(row) * k) + line));
+    }
     grid_dependency_wait();
     if constexpr (TPR > 32) {
         const int row = blockIdx.x;
