@@ -495,37 +495,31 @@ inline void SoftMaxTilingFunc(const TensorShape& srcShape, const uint32_t dataTy
 {
     using namespace tiling_detail;
     if (!SoftmaxArgsOk(srcShape, dataTypeSize)) return;
-    uint32_t srcM, srcK;
-    LastAxis(srcShape, srcM, srcK);
-    const uint32_t perBlk = kBlk / dataTypeSize;
-    const uint32_t work = localWorkSpaceSize / kFloat;
-    uint32_t baseM = std::min(work / (perBlk + srcK + kBasicUnit), srcM);
-    if (baseM < srcM && baseM > kBasicTileNum) baseM = baseM / kBasicTileNum * kBasicTileNum;
-    if (baseM > kBasicTileNum && srcM % kBasicTileNum == 0 && srcK % kBasicUnit == 0) {  // "basic block" adjustment
-        baseM = baseM / kBasicTileNum * kBasicTileNum;
-        while (srcM % baseM != 0) baseM -= kBasicTileNum;
-        while (baseM * srcK >= kBasicUnit * kBasicMin) baseM /= 2;
+    uint32_t rows, cols;
+    LastAxis(srcShape, rows, cols);
+    const uint32_t statCols = kBlk / dataTypeSize;  // one 32-byte block of max / sum values per row
+
+    // Rows per pass: what the scratch holds (a row needs its cols values, its statistics block and one basic unit, all fp32),
+    // in whole basic tiles when the matrix is split at all; shapes made of basic blocks get a divisor of the row count that
+    // also keeps a pass under the basic-block size.
+    uint32_t pass = std::min((localWorkSpaceSize / kFloat) / (statCols + cols + kBasicUnit), rows);
+    const auto wholeTiles = [](uint32_t r) { return r - r % kBasicTileNum; };
+    if (pass < rows && pass > kBasicTileNum) pass = wholeTiles(pass);
+    const bool basicBlocks = rows % kBasicTileNum == 0 && cols % kBasicUnit == 0;
+    if (basicBlocks && pass > kBasicTileNum) {
+        for (pass = wholeTiles(pass); rows % pass != 0;) pass -= kBasicTileNum;
+        while (pass * cols >= kBasicUnit * kBasicMin) pass >>= 1;
     }
-    tiling.set_srcM(srcM);
-    tiling.set_srcK(srcK);
-    tiling.set_srcSize(srcM * srcK);
-    tiling.set_outMaxM(srcM);
-    tiling.set_outMaxK(perBlk);
-    tiling.set_outMaxSize(srcM * perBlk);
-    tiling.set_splitM(baseM);
-    tiling.set_splitK(srcK);
-    tiling.set_splitSize(baseM * srcK);
-    tiling.set_reduceM(baseM);
-    tiling.set_reduceK(perBlk);
-    tiling.set_reduceSize(baseM * perBlk);
-    uint32_t tail = 0;
-    if (baseM != 0) {
-        tail = srcM % baseM;
-        tiling.set_rangeM(srcM / baseM);
-    }
-    tiling.set_tailM(tail);
-    tiling.set_tailSplitSize(tail * srcK);
-    tiling.set_tailReduceSize(tail * perBlk);
+    const uint32_t passes = pass ? rows / pass : 0, left = pass ? rows % pass : 0;
+
+    // The structure describes three row ranges (whole source, one pass, the last partial pass), each as the data rectangle
+    // rows x cols and the statistics rectangle rows x statCols.
+    tiling.set_srcM(rows), tiling.set_srcK(cols), tiling.set_srcSize(rows * cols);
+    tiling.set_outMaxM(rows), tiling.set_outMaxK(statCols), tiling.set_outMaxSize(rows * statCols);
+    tiling.set_splitM(pass), tiling.set_splitK(cols), tiling.set_splitSize(pass * cols);
+    tiling.set_reduceM(pass), tiling.set_reduceK(statCols), tiling.set_reduceSize(pass * statCols);
+    if (pass) tiling.set_rangeM(passes);
+    tiling.set_tailM(left), tiling.set_tailSplitSize(left * cols), tiling.set_tailReduceSize(left * statCols);
 }
 inline void SoftMaxTilingFunc(const TensorShape& srcShape, const uint32_t dataTypeSize, const uint32_t localWorkSpaceSize, ::SoftMaxTiling& tiling)
 {
