@@ -157,7 +157,7 @@ class A8W8(Workload):
     name = "a8w8_gemm_4096x4096x11008_dequant_bf16"
     metric, unit, dtype = "quant-GEMM throughput (int8, fused per-token x per-channel dequant)", "TOPS", "s8"
     M, K, N = 4096, 4096, 11008
-    traffic_1gpu = 62.05e6 + 48.92e6   # ncu: dram__bytes_read.sum + dram__bytes_write.sum of gemm_tc_pair_kernel<int8>
+    traffic_1gpu = 62.05e6 + 49.67e6   # ncu: dram__bytes_read.sum + dram__bytes_write.sum of gemm_tc_pair_kernel<int8>
 
     def __init__(self, ab, rank, world, sets):
         self.ab, self.rank, self.world = ab, rank, world
@@ -226,7 +226,7 @@ class Grouped(Workload):
     metric, unit, dtype = "grouped quant-GEMM throughput (int8, fused dequant)", "TOPS", "s8"
     G, MTOT, K, N = 64, 32768, 7168, 2048
     OUT, ACT = "BF16", 0
-    traffic_1gpu = 1.2542e9 + 0.1257e9   # ncu: dram__bytes_read.sum + dram__bytes_write.sum of gemm_tc_pair_kernel<int8>, grouped
+    traffic_1gpu = 1.2680e9 + 0.1266e9   # ncu: dram__bytes_read.sum + dram__bytes_write.sum of gemm_tc_pair_kernel<int8>, grouped
 
     def counts(self):
         return dirichlet_counts(self.G, self.MTOT, 0xA5C00003)
@@ -324,7 +324,7 @@ class MXFP4(Workload):
     metric, unit, dtype = "quant-GEMM throughput (MXFP4 e2m1 x ue8m0, int8 requant + bf16 out)", "TFLOPS", "fp4_e2m1"
     M = K = N = 8192
     kernels_per_step = 2  # re-tiling of A's scales + the GEMM (the weights' scales are prepacked once, outside the timed region)
-    traffic_1gpu = 95.2e6 + 168.0e6    # ncu: dram__bytes_read.sum + dram__bytes_write.sum of gemm_tc_pair_kernel<mxf4>
+    traffic_1gpu = 87.1e6 + 167.9e6    # ncu: dram__bytes_read.sum + dram__bytes_write.sum of gemm_tc_pair_kernel<mxf4>
     published = (1614.0, "Ascend 950PR basic-API MXFP4 8192^3, bf16 out; the reference's published figure")
 
     def __init__(self, ab, rank, world, sets):
@@ -551,6 +551,7 @@ class FP16Large(Workload):
     metric, unit, dtype = "adv_api Matmul fp16 -> fp16, 8192^3 (the reference's published shape)", "TFLOPS", "f16"
     M = K = N = 8192
     published = (427.0, "Ascend 950PR basic-API fp16 8192^3, 2572 us (the reference's published figure); Atlas A2 adv_api: 269")
+    traffic_1gpu = 1.0571e9 + 0.1269e9   # ncu: dram__bytes_read.sum + dram__bytes_write.sum of gemm_tc_pair_kernel<f16>, banded tile order
 
     def __init__(self, ab, rank, world, sets):
         from gpu_util import f16_bits
