@@ -485,7 +485,10 @@ __device__ __forceinline__ void stage_store32(const CUtensorMap* map, uint32_t s
                                               const float (&f)[32], const int (&qi)[32], int atomic = 0)
 {
     static_assert(DT == OUT_F16 || DT == OUT_BF16 || DT == OUT_S8, "staged stores carry 1- and 2-byte outputs");
-    if (lane == 0) {
+    // (bulk groups belong to the thread that committed them: the wait, the store and the final wait before the CTA exits all
+    // run on the lane that elect.sync picks, which is the same one every time for a full warp; the compiler then keeps the
+    // tensor map address and the coordinates in uniform registers, which shortens the issue of the store)
+    if (elect_one()) {
         if (dual) bulk_wait_group_read<1>();
         else bulk_wait_group_read<0>();
     }
@@ -508,7 +511,7 @@ __device__ __forceinline__ void stage_store32(const CUtensorMap* map, uint32_t s
     }
     fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0) {
+    if (elect_one()) {
         if (atomic == 0) tma_store_2d(map, smem, col0, row_base);
         else if (atomic == kAtomicAdd) tma_reduce_add_2d(map, smem, col0, row_base);  // the tensor map then carries the real element type
         else if (atomic == kAtomicMax) tma_reduce_max_2d(map, smem, col0, row_base);
@@ -1104,7 +1107,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[acc_stage]));
         }
-        if (lane == 0) bulk_wait_group_read<0>();  // staged chunks have left shared memory before the CTA may exit
+        if (elect_one()) bulk_wait_group_read<0>();  // staged chunks have left shared memory before the CTA may exit
     }
 
     // ===== teardown =====
@@ -1489,7 +1492,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster_tmem(smem_u32(&acc_empty_bar[acc_stage]) & kPeerBitMask);
         }
-        if (lane == 0) bulk_wait_group_read<0>();
+        if (elect_one()) bulk_wait_group_read<0>();
     }
 
     // ===== teardown =====
