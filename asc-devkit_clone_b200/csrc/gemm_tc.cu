@@ -67,6 +67,8 @@ struct GemmParams {
     int pair_n;              // CTA-pair kernels for fp16 / bf16 / int8: columns per tile (multiple of 16, at most 256)
     int allow_m64;           // fp16 / bf16 / int8, single-CTA kernel: tiles of at most 64 rows use the 64-row instruction
     int band_m;              // not grouped: tiles are walked in bands of band_m row blocks (all columns of a band before the next band)
+    int split_k;             // single-CTA kernel: > 1 = that many CTAs of a cluster share every tile, each multiplying its own range of K
+                             // blocks; the leader adds the others' accumulators, which they write into its shared memory (one tile per cluster)
     int ring_stages;         // CTA-pair kernels, fp16 / bf16 / int8 with K-major B: the shared-memory ring is cut for the call's tile width,
     int ring_stage_bytes;    // so that narrower tiles get more stages in flight (0: the kernel's compile-time geometry)
     int group_swap;          // grouped int8 on CTA pairs: a group's last, partial 256-row block is multiplied with the operand roles swapped
@@ -704,7 +706,8 @@ __device__ __forceinline__ EpiPre epilogue_preload(const GemmParams& p, const Ti
 
 template <bool ACC_INT, int MODE, int DT, int BLOCK_N>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInfo& t, const OutMaps& outs, uint32_t stage_smem, int stage_bytes,
-                                              uint32_t t_addr, int quad, int lane, int chunk0, int chunk1, const EpiPre& pre)
+                                              uint32_t t_addr, int quad, int lane, int chunk0, int chunk1, const EpiPre& pre, uint32_t sk_base,
+                                              int sk_parts)
 {
     // 128-row tiles: lane l of quadrant q holds row 32 q + l; 64-row tiles: lanes 0-15 hold rows 16 q + l
     const int row = t.m64 ? t.row0 + quad * 16 + lane : t.row0 + quad * 32 + lane;
@@ -738,6 +741,21 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
         uint32_t r[32];
         tmem_ld_32x32(t_addr + c * 32, r);
         tmem_ld_wait();
+        // split K: add what the other CTAs of the cluster accumulated over their K ranges, in rank order (see splitk_send_tile)
+        for (int s = 0; s < sk_parts; ++s) {
+            const uint32_t part = sk_base + static_cast<uint32_t>(s) * (BLOCK_N * 512) + ((c * 8) * 128 + quad * 32 + lane) * 16;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                float x0, x1, x2, x3;
+                ld_shared_v4(part + (j / 4) * 2048, x0, x1, x2, x3);
+                if constexpr (ACC_INT) {
+                    r[j] += __float_as_uint(x0), r[j + 1] += __float_as_uint(x1), r[j + 2] += __float_as_uint(x2), r[j + 3] += __float_as_uint(x3);
+                } else {
+                    r[j] = __float_as_uint(__uint_as_float(r[j]) + x0), r[j + 1] = __float_as_uint(__uint_as_float(r[j + 1]) + x1);
+                    r[j + 2] = __float_as_uint(__uint_as_float(r[j + 2]) + x2), r[j + 3] = __float_as_uint(__uint_as_float(r[j + 3]) + x3);
+                }
+            }
+        }
         // a chunk that the tile only half owns (tile widths are multiples of 16) is stored from registers: the
         // bulk store's 32-column box would reach into the neighbouring tile.  So is a chunk that crosses the right edge of
         // the matrix: the TMA unit clips columns in 16-byte pieces, not per element (an int8 matrix of 328 columns got 8
@@ -750,11 +768,12 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
 
 template <bool ACC_INT, int BLOCK_N>
 __device__ __forceinline__ void epilogue_dispatch(const GemmParams& p, const TileInfo& t, const OutMaps& outs, uint32_t stage_smem, int stage_bytes,
-                                                  uint32_t t_addr, int quad, int lane, int chunk0, int chunk1, const EpiPre& pre)
+                                                  uint32_t t_addr, int quad, int lane, int chunk0, int chunk1, const EpiPre& pre, uint32_t sk_base = 0,
+                                                  int sk_parts = 0)
 {
 #define ASCB200_EPI_CASE(MODE, DT)                                                                          \
     if (p.epi.mode == MODE && p.epi.c_dtype == DT) {                                                          \
-        epilogue_tile<ACC_INT, MODE, DT, BLOCK_N>(p, t, outs, stage_smem, stage_bytes, t_addr, quad, lane, chunk0, chunk1, pre); \
+        epilogue_tile<ACC_INT, MODE, DT, BLOCK_N>(p, t, outs, stage_smem, stage_bytes, t_addr, quad, lane, chunk0, chunk1, pre, sk_base, sk_parts); \
         return;                                                                                               \
     }
     if constexpr (ACC_INT) {
@@ -833,6 +852,10 @@ struct IssueCursor {
     {
         nstages = stages;
         step16 = static_cast<uint32_t>(stage_bytes) >> 4;
+        // A shared-memory descriptor holds the offset inside the issuing CTA's own shared memory (14 bits of address / 16).  In a
+        // cluster the shared-window address of every CTA but the first carries its rank above those bits, which would spill
+        // into the descriptor's leading-offset field (seen as MN-major boxes read 256 bytes off in the second CTA of a cluster).
+        tiles_addr &= 0x3FFFFu;
         a_lo0 = (a_lbo_enc << 16) | (tiles_addr >> 4);
         b_lo0 = (b_lbo_enc << 16) | ((tiles_addr + B_OFFSET) >> 4);
         sf_lo0 = (1u << 16) | ((tiles_addr + SF_OFFSET) >> 4);   // no-swizzle descriptor, leading offset 16 bytes
@@ -936,6 +959,26 @@ __device__ __forceinline__ void issue_k_block(const Cursor& c, uint32_t d_tmem, 
     issue_mmas<KIND, PAIR>(c, d_tmem, hi_word, a_kstep16, b_kstep16, idesc, idesc_hi_sf, sfb_col_offset, first);
 }
 
+// Split K over a cluster (single-CTA kernel): a CTA that is not the leader hands its accumulator to the leader.  Each epilogue
+// thread writes the 32 values of its row and chunk into the leader's shared memory (the leader's operand ring, idle by then) as
+// eight 16-byte pieces laid out [chunk][piece][row], so that the 32 lanes of a warp write and later read consecutive
+// addresses, and then arrives on the leader's barrier with release at cluster scope.  The values travel as raw accumulator
+// bits: int32 sums stay exact, fp32 sums are added in rank order (one more rounding per rank than a single chain).
+template <int BLOCK_N>
+__device__ __forceinline__ void splitk_send_tile(uint32_t leader_part, uint32_t leader_bar, uint32_t t_addr, int quad, int lane, int chunk0, int chunk1)
+{
+#pragma unroll 1
+    for (int c = chunk0; c < chunk1; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const uint32_t dst = leader_part + ((c * 8) * 128 + quad * 32 + lane) * 16;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) st_cluster_v4(dst + (j / 4) * 2048, r[j], r[j + 1], r[j + 2], r[j + 3]);
+    }
+    mbar_arrive_cluster(leader_bar);
+}
+
 // ---- the kernel --------------------------------------------------------------------------------
 template <int KIND, int BLOCK_N>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -956,6 +999,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint64_t* acc_empty_bar = acc_full_bar + 2;        // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
+    uint64_t* parts_full_bar = reinterpret_cast<uint64_t*>(tmem_slot + 2);  // split K, leader: every other CTA's accumulator has arrived
+    uint64_t* ring_free_bar = parts_full_bar + 1;                          // split K, others: the leader's ring may be overwritten
+    static_assert((2 * 8 + 4 + 2) * 8 + 8 <= 256, "barrier area");
     int* row_start = reinterpret_cast<int*>(epi_stage + C::EPI_BYTES + 256);
     int* tile_start = row_start + (MAX_GROUPS + 1);
 
@@ -963,6 +1009,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int lane = threadIdx.x & 31;
     const int num_n = (p.n + BLOCK_N - 1) / BLOCK_N;
     const int num_m = (p.m + BLOCK_M - 1) / BLOCK_M;
+    // Split K: the sk CTAs of a cluster take the same tile (one per cluster, the host sees to that) and consecutive ranges of
+    // its K blocks, none of them empty.
+    const int sk = p.split_k > 1 ? p.split_k : 1;
+    const int sk_rank = sk > 1 ? static_cast<int>(cluster_ctarank()) : 0;
+    const int kb_per = (p.num_k_blocks + sk - 1) / sk;
+    const int kb0 = sk_rank * kb_per, kb1 = min(p.num_k_blocks, kb0 + kb_per);
+    const int first_tile = static_cast<int>(blockIdx.x) / sk, tile_stride = static_cast<int>(gridDim.x) / sk;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::NUM_STAGES; ++s) {
@@ -973,6 +1026,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mbar_init(smem_u32(&acc_full_bar[s]), 1);
             mbar_init(smem_u32(&acc_empty_bar[s]), NUM_EPI_WARPS);
         }
+        mbar_init(smem_u32(parts_full_bar), (sk - 1) * NUM_EPI_WARPS * 32 + (sk == 1));  // every epilogue thread of every other CTA
+        mbar_init(smem_u32(ring_free_bar), 1);
         *abort_word = 0u;
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
@@ -988,6 +1043,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     tc_fence_before();
     __syncthreads();
+    if (sk > 1) cluster_sync_all();  // the other CTAs' barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = p.groups > 0 ? tile_start[p.groups] : num_m * num_n;
@@ -998,8 +1054,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         uint32_t phase = 0;
         TileInfo t;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && locate_tile<BLOCK_N>(p, tile, num_m, total_tiles, row_start, tile_start, cursor, t); tile += gridDim.x) {
-            for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+        for (int tile = first_tile; ok && locate_tile<BLOCK_N>(p, tile, num_m, total_tiles, row_start, tile_start, cursor, t); tile += tile_stride) {
+            for (int kb = kb0; kb < kb1; ++kb) {
                 ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_word, p.status);
                 if (!ok) break;
                 if (elect_one()) {
@@ -1058,7 +1114,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t idesc_hi_sf = p.idesc | (2u << 4) | (2u << 29);  // MXFP4: scale bytes 2..3 of the TMEM column
         IssueCursor<C::STAGE_BYTES, C::NUM_STAGES, A_TILE_BYTES, A_TILE_BYTES + C::B_TILE_BYTES, C::SF_COLS_PER_STAGE> cur;
         cur.init(smem_u32(tiles), a_lbo, b_lbo, smem_u32(&full_bar[0]), smem_u32(&empty_bar[0]), tmem_base + C::SF_COL0);
-        for (int tile = blockIdx.x; ok && locate_tile<BLOCK_N>(p, tile, num_m, total_tiles, row_start, tile_start, cursor, t); tile += gridDim.x, ++acc_iter) {
+        for (int tile = first_tile; ok && locate_tile<BLOCK_N>(p, tile, num_m, total_tiles, row_start, tile_start, cursor, t); tile += tile_stride, ++acc_iter) {
             const int acc_stage = acc_iter % C::ACC_STAGES;
             const uint32_t acc_phase = (acc_iter / C::ACC_STAGES) & 1u;
             ok = mbar_wait(smem_u32(&acc_empty_bar[acc_stage]), acc_phase ^ 1u, abort_word, p.status);
@@ -1071,13 +1127,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // bits 24-28 of the descriptor): half the multiplications, and under the power cap half the energy, of rows
             // that would be thrown away.  Its accumulator rows 16 q .. 16 q + 15 land in lanes 0-15 of TMEM quadrant q.
             const uint32_t idesc = t.m64 ? ((p.idesc & ~(0x1Fu << 24)) | (4u << 24)) : p.idesc;
-            const int last = p.num_k_blocks - 1;
-            for (int kb = 0; kb <= last; ++kb) {
+            const int last = kb1 - 1;
+            for (int kb = kb0; kb <= last; ++kb) {
                 ok = mbar_wait(cur.full_bar, cur.phase, abort_word, p.status);
                 if (!ok) break;
                 tc_fence_after();
                 if (elect_one()) {
-                    issue_k_block<KIND, false, C::SF_B_BLOCKS>(cur, d_tmem, hi_word, a_k16, b_k16, idesc, idesc_hi_sf, sfb_off, kb == 0);
+                    issue_k_block<KIND, false, C::SF_B_BLOCKS>(cur, d_tmem, hi_word, a_k16, b_k16, idesc, idesc_hi_sf, sfb_off, kb == kb0);
                     if (kb == last) tc_commit(acc_full);
                 }
                 __syncwarp();
@@ -1093,7 +1149,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         int cursor = 0, acc_iter = 0;
         TileInfo t;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && locate_tile<BLOCK_N>(p, tile, num_m, total_tiles, row_start, tile_start, cursor, t); tile += gridDim.x, ++acc_iter) {
+        for (int tile = first_tile; ok && locate_tile<BLOCK_N>(p, tile, num_m, total_tiles, row_start, tile_start, cursor, t); tile += tile_stride, ++acc_iter) {
             const int acc_stage = acc_iter % C::ACC_STAGES;
             const uint32_t acc_phase = (acc_iter / C::ACC_STAGES) & 1u;
             const EpiPre pre = epilogue_preload(p, t, quad, lane, chunk0);
@@ -1101,8 +1157,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc_stage * BLOCK_N;
+            if (sk > 1 && sk_rank != 0) {
+                // wait until the leader's MMAs have read the last of its ring, then write this CTA's accumulator over it
+                ok = mbar_wait_cluster(smem_u32(ring_free_bar), 0u, true, abort_word, p.status);
+                if (!ok) break;
+                splitk_send_tile<BLOCK_N>(map_to_cta(smem_u32(tiles), 0) + static_cast<uint32_t>(sk_rank - 1) * (BLOCK_N * 512),
+                                          map_to_cta(smem_u32(parts_full_bar), 0), t_addr, quad, lane, chunk0, chunk1);
+                continue;  // one tile per cluster: nothing follows
+            }
+            if (sk > 1) {
+                // this CTA's MMAs are done (the accumulator is complete), so its ring is free: tell the others, then wait for them
+                if (warp == 4 && elect_one())
+                    for (int r = 1; r < sk; ++r) mbar_arrive_cluster_tmem(map_to_cta(smem_u32(ring_free_bar), static_cast<uint32_t>(r)));
+                ok = mbar_wait_cluster(smem_u32(parts_full_bar), 0u, true, abort_word, p.status);
+                if (!ok) break;
+            }
             epilogue_dispatch<KIND == KIND_I8, BLOCK_N>(p, t, outs, smem_u32(epi_stage) + (warp - 4) * C::EPI_BYTES_PER_WARP, C::EPI_BYTES_PER_WARP, t_addr,
-                                                        quad, lane, chunk0, chunk1, pre);
+                                                        quad, lane, chunk0, chunk1, pre, smem_u32(tiles), sk - 1);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[acc_stage]));
@@ -1653,7 +1724,18 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& out
         ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured[dev & 15] = true;
     }
-    ASCB200_CUDA(launch_pdl(gemm_tc_kernel<KIND, BLOCK_N>, grid, NUM_THREADS, C::SMEM_BYTES, stream, ta, tb, outs, p));
+    // Split K over a cluster: only while every cluster gets at most one tile, every CTA at least one K block, and the other
+    // CTAs' accumulators (BLOCK_N x 512 bytes each) fit the leader's operand ring.
+    GemmParams q = p;
+    int sk = p.split_k;
+    while (sk > 1 && ((sk - 1) * BLOCK_N * 512 > C::NUM_STAGES * C::STAGE_BYTES || p.num_k_blocks <= (sk - 1) * ((p.num_k_blocks + sk - 1) / sk))) sk >>= 1;
+    q.split_k = sk > 1 ? sk : 0;
+    if (q.split_k > 1) {
+        ASCB200_CUDA(launch_pdl_cluster(gemm_tc_kernel<KIND, BLOCK_N>, grid * q.split_k, NUM_THREADS, C::SMEM_BYTES, stream, static_cast<unsigned>(q.split_k), ta, tb,
+                                        outs, q));
+        return ASCB200_OK;
+    }
+    ASCB200_CUDA(launch_pdl(gemm_tc_kernel<KIND, BLOCK_N>, grid, NUM_THREADS, C::SMEM_BYTES, stream, ta, tb, outs, q));
     return ASCB200_OK;
 }
 
@@ -1954,6 +2036,18 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     const long long max_tiles = grouped ? (static_cast<long long>((m + BLOCK_M - 1) / BLOCK_M) + groups) * ((n + block_n - 1) / block_n)
                                         : static_cast<long long>((m + BLOCK_M - 1) / BLOCK_M) * ((n + block_n - 1) / block_n);
     const int grid = static_cast<int>(std::min<long long>(max_tiles, sm_count));
+    // Few tiles and a long K: clusters of 2 or 4 CTAs share each tile and split its K blocks (a K block cannot take less than
+    // about 370 cycles whatever the tile's width, so a small problem's time is its number of K blocks); the leader adds the
+    // others' accumulators in rank order.  Never for grouped calls or calls that bring their own device resources.
+    if (!use_pair && !grouped && !fixed) {
+        int sk = 0;
+        if (max_tiles * 2 <= sm_count && p.num_k_blocks >= 8) sk = (max_tiles * 4 <= sm_count && p.num_k_blocks >= 16) ? 4 : 2;
+        if (const char* force = getenv("ASCB200_SPLIT_K")) {
+            const int v = atoi(force);
+            sk = (v == 2 || v == 4 || v == 8) && max_tiles * v <= sm_count ? v : 0;
+        }
+        p.split_k = sk;
+    }
 
     const uint32_t a_mn = p.a_mn, b_mn = p.b_mn;
     if (use_pair) {

@@ -111,6 +111,59 @@ def test_gemm_i8_banded_tile_order_exact(m, n, k, no_pair, band, monkeypatch):
     assert (got == ref).all(), f"{(got != ref).sum()} of {ref.size} differ; first {np.argwhere(got != ref)[:5].tolist()}"
 
 
+@pytest.mark.parametrize("split", [2, 4])
+@pytest.mark.parametrize("m,n,k,trans_b", [(128, 64, 2048, True), (300, 200, 1664, True), (100, 336, 1152, False), (512, 512, 4096, True)])
+def test_gemm_i8_split_k_over_a_cluster_exact(m, n, k, trans_b, split, monkeypatch):
+    """Few tiles, long K: the CTAs of a cluster split the K blocks of each tile and the leader adds their accumulators
+    (through its shared memory).  Integer sums: bit exact, also with a ragged last K block and with bias."""
+    monkeypatch.setenv("ASCB200_SPLIT_K", str(split))
+    monkeypatch.setenv("ASCB200_NO_PAIR", "1")
+    ab = dev()
+    rng, a, b = _i8_inputs(m, n, k, False, trans_b, m + split)
+    bias = rng.integers(-1000, 1000, n).astype(np.int32)
+    d_c = ab.empty((m, n), np.int32)
+    d_c.fill(0x5A)
+    ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.S32, trans_b=trans_b, bias=ab.to_dev(bias)))
+    ab.sync()
+    ref = orc.gemm_i8(a, b, bias, trans_b=trans_b)
+    got = d_c.download()
+    assert (got == ref).all(), f"{(got != ref).sum()} of {ref.size} differ; first {np.argwhere(got != ref)[:5].tolist()}"
+
+
+@pytest.mark.parametrize("split", [0, 2, 4])
+def test_gemm_f16_split_k_over_a_cluster(split, monkeypatch):
+    """The fp16 baseline configuration (512 x 512 x 1024 + bias -> fp32) with the K blocks split over clusters of 2 and 4
+    CTAs, and as one chain: fp32 sums are added in rank order, inside the tolerance of the configuration."""
+    monkeypatch.setenv("ASCB200_SPLIT_K", str(split))
+    run_f16(512, 512, 1024, False, True, bias=True, c_dtype=0, seed=11)
+
+
+@pytest.mark.parametrize("trans_a,trans_b", [(True, False), (True, True), (False, False)])
+@pytest.mark.parametrize("c_dtype", [0, 1])
+def test_gemm_f16_split_k_with_untransposed_operands(trans_a, trans_b, c_dtype, monkeypatch):
+    """M- / N-contiguous operands arrive as several 64-wide boxes per tile whose distance is part of the shared-memory
+    descriptor; every CTA of the cluster builds its descriptors from its own shared-memory offset."""
+    monkeypatch.setenv("ASCB200_SPLIT_K", "2")
+    run_f16(256, 192, 1024, trans_a, trans_b, bias=True, c_dtype=c_dtype, seed=13)
+    monkeypatch.setenv("ASCB200_SPLIT_K", "4")
+    run_f16(128, 256, 2048, trans_a, trans_b, bf16=True, bias=False, c_dtype=c_dtype, seed=14)
+
+
+def test_gemm_mxfp4_split_k_over_a_cluster(monkeypatch):
+    """Block-scaled fp4 with the K blocks (and their scale chunks) split over a cluster of two CTAs."""
+    monkeypatch.setenv("ASCB200_SPLIT_K", "2")
+    monkeypatch.setenv("ASCB200_NO_PAIR", "1")
+    ab = dev()
+    m, n, k = 256, 384, 4096
+    rng, a, sa, b, sb = _mx_case(m, n, k, 21)
+    d_c = ab.empty((m, n), np.float32)
+    ab.check(ab.gemm(ab.KIND_MXFP4, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.F32, trans_b=True, scale_a=ab.to_dev(sa), scale_b=ab.to_dev(sb)))
+    ab.sync()
+    ref = orc.gemm_mxf4(a, sa, b, sb, base_k=256)
+    err = np.abs(d_c.download() - ref)
+    assert (err <= ATOL + RTOL * np.abs(ref)).all() and err.max() <= 1e-3 * np.abs(ref).max()
+
+
 @pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, False)])
 def test_gemm_f16_cta_pair(trans_a, trans_b):
     run_f16(2304, 2560, 192, trans_a, trans_b, bias=True, c_dtype=0, seed=31)
