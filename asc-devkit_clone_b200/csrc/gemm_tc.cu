@@ -1763,6 +1763,30 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     return ASCB200_OK;
 }
 
+// Split K over a cluster (single-CTA kernel): 4 or 2 CTAs per tile, or 0.  Time of a small problem ~ 5 us fixed + 0.21 us per K
+// block of the longest CTA + 1.5 / 2.8 us for the exchange with 2 / 4 CTAs (fitted to fp16 512 x 512 x K: K = 1024, 16 blocks,
+// 8.3 -> 8.6 / 9.1 us with 2 / 4 CTAs; K = 2048: 11.9 -> 10.4 / 10.2; K = 4096: 19.5 -> 14.5 / 12.5; and 128 x 1024 x 8192: 33.8 ->
+// 21.7 / 15.7).  Every cluster needs a tile of its own, every CTA a K block, and the other CTAs' accumulators (block_n x 512 bytes
+// each) must fit the leader's operand ring (about 192 KB).  `gain`: estimated time relative to no split.
+int pick_split_k(long long tiles, int num_k_blocks, int block_n, int sm_count, double* gain = nullptr)
+{
+    const double fixed = 5.0, per_block = 0.21, exchange[5] = {0.0, 0.0, 1.5, 0.0, 2.8};
+    const double base = fixed + per_block * num_k_blocks;
+    int best = 0;
+    double best_t = base;
+    for (int sk = 2; sk <= 4; sk <<= 1) {
+        if (tiles * sk > sm_count || num_k_blocks < 2 * sk) continue;
+        if (static_cast<long long>(sk - 1) * block_n * 512 > 192 * 1024) continue;
+        const double t = fixed + per_block * ((num_k_blocks + sk - 1) / sk) + exchange[sk];
+        if (t < 0.97 * best_t) {
+            best_t = t;
+            best = sk;
+        }
+    }
+    if (gain) *gain = best_t / base;
+    return best;
+}
+
 bool is_mxfp8(int kind) { return kind == ASCB200_KIND_MXFP8_E4M3 || kind == ASCB200_KIND_MXFP8_E5M2; }
 bool is_mx(int kind) { return kind == ASCB200_KIND_MXFP4 || is_mxfp8(kind); }
 int elem_bits(int kind) { return kind == ASCB200_KIND_MXFP4 ? 4 : (kind == ASCB200_KIND_S8 || is_mxfp8(kind)) ? 8 : 16; }
@@ -1945,7 +1969,12 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
             const long long tiles = c.pair ? pair_m_tiles * n_tiles : m_tiles * n_tiles;
             const long long slots = c.pair ? pair_clusters : sm_count;
             const long long waves = (tiles + slots - 1) / slots;
-            const double cost = static_cast<double>(waves) * (c.pair ? 2 : 1) * BLOCK_M * c.bn / c.eff / (c.pair ? 2 : 1);
+            double cost = static_cast<double>(waves) * (c.pair ? 2 : 1) * BLOCK_M * c.bn / c.eff / (c.pair ? 2 : 1);
+            if (!c.pair && !grouped && !fixed) {  // single-CTA tiles may split K over a cluster (measured speed-ups, see pick_split_k)
+                double gain = 1.0;
+                pick_split_k(tiles, (k + block_k - 1) / block_k, c.bn, sm_count, &gain);
+                cost *= gain;
+            }
             if (best < 0 || cost < best) {
                 best = cost;
                 block_n = c.bn;
@@ -2040,8 +2069,7 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
     // about 370 cycles whatever the tile's width, so a small problem's time is its number of K blocks); the leader adds the
     // others' accumulators in rank order.  Never for grouped calls or calls that bring their own device resources.
     if (!use_pair && !grouped && !fixed) {
-        int sk = 0;
-        if (max_tiles * 2 <= sm_count && p.num_k_blocks >= 8) sk = (max_tiles * 4 <= sm_count && p.num_k_blocks >= 16) ? 4 : 2;
+        int sk = pick_split_k(max_tiles, p.num_k_blocks, block_n, sm_count);
         if (const char* force = getenv("ASCB200_SPLIT_K")) {
             const int v = atoi(force);
             sk = (v == 2 || v == 4 || v == 8) && max_tiles * v <= sm_count ? v : 0;
