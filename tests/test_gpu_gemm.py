@@ -112,7 +112,7 @@ def test_gemm_i8_banded_tile_order_exact(m, n, k, no_pair, band, monkeypatch):
 
 
 @pytest.mark.parametrize("split", [2, 4])
-@pytest.mark.parametrize("m,n,k,trans_b", [(128, 64, 2048, True), (300, 200, 1664, True), (100, 336, 1152, False), (512, 512, 4096, True)])
+@pytest.mark.parametrize("m,n,k,trans_b", [(128, 64, 2048, True), (300, 200, 1664, True), (100, 336, 1152, False), (512, 512, 4096, True), (40, 320, 8192, True)])
 def test_gemm_i8_split_k_over_a_cluster_exact(m, n, k, trans_b, split, monkeypatch):
     """Few tiles, long K: the CTAs of a cluster split the K blocks of each tile and the leader adds their accumulators
     (through its shared memory).  Integer sums: bit exact, also with a ragged last K block and with bias."""
@@ -147,6 +147,34 @@ def test_gemm_f16_split_k_with_untransposed_operands(trans_a, trans_b, c_dtype, 
     run_f16(256, 192, 1024, trans_a, trans_b, bias=True, c_dtype=c_dtype, seed=13)
     monkeypatch.setenv("ASCB200_SPLIT_K", "4")
     run_f16(128, 256, 2048, trans_a, trans_b, bf16=True, bias=False, c_dtype=c_dtype, seed=14)
+
+
+@pytest.mark.parametrize("mode", ["dequant_bf16", "req8", "s32_atomic_add"])
+def test_gemm_i8_split_k_chosen_by_itself_with_fused_epilogues(mode):
+    """A long K and few tiles: the library splits K by itself (no switch set); the fused stages after the sum are unchanged."""
+    ab = dev()
+    m, n, k = 128, 512, 8192
+    rng, a, b = _i8_inputs(m, n, k, False, True, 31)
+    acc = orc.gemm_i8(a, b, None, trans_b=True)
+    if mode == "dequant_bf16":
+        tok = rng.uniform(1e-3, 1e-2, m).astype(np.float32); ch = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+        d_c = ab.empty((m, n), np.uint16)
+        ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.BF16, epilogue=ab.EPI_DEQUANT_TOKEN_CHANNEL, trans_b=True,
+                         tok=ab.to_dev(tok), ch=ab.to_dev(ch)))
+        ref = orc.dequant_tok_ch(acc, tok, ch, ab.BF16)
+    elif mode == "req8":
+        scales = rng.uniform(2e-5, 6e-5, n).astype(np.float32)
+        q = quant_params(scales)
+        d_c = ab.empty((m, n), np.int8)
+        ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.S8, epilogue=ab.EPI_FIXPIPE_QUANT, trans_b=True, quant=ab.to_dev(q)))
+        ref = orc.fixpipe_req8(acc, q)
+    else:
+        start = rng.integers(-1000, 1000, (m, n)).astype(np.int32)
+        d_c = ab.to_dev(start)
+        ab.check(ab.gemm(ab.KIND_S8, m, n, k, ab.to_dev(a), ab.to_dev(b), d_c, ab.S32, trans_b=True, atomic=1))
+        ref = start + acc
+    ab.sync()
+    assert (d_c.download() == ref).all()
 
 
 def test_gemm_mxfp4_split_k_over_a_cluster(monkeypatch):
