@@ -297,7 +297,7 @@ __device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi)
 // through the half / bfloat16 atomics (rounded to the destination type); max / min of floats through the integer order of
 // their bit patterns (ascending for positive, descending for negative values), of 16-bit types through a
 // compare-and-swap on the element.
-constexpr int kAtomicAdd = 1, kAtomicMax = 2, kAtomicMin = 3;
+constexpr int kAtomicAdd = 1, kAtomicMax = 2;  // 3: minimum (the remaining value of enAtomic)
 
 __device__ __forceinline__ void atomic_maxmin_f32(float* p, float v, bool is_max)
 {

@@ -524,7 +524,7 @@ template <typename ST> __device__ __forceinline__ void stat_store(ST* p, size_t 
 template <> __device__ __forceinline__ void stat_store<float>(float* p, size_t i, float v) { p[i] = v; }
 template <> __device__ __forceinline__ void stat_store<__half>(__half* p, size_t i, float v) { p[i] = __float2half_rn(clamp_half_range(v)); }
 
-constexpr int kFlashNormalise = 1, kFlashSimple = 2;  // values of the kernel's `normalise` argument (0: SoftmaxFlashV2)
+constexpr int kFlashSimple = 2;  // the kernel's `normalise` argument: 0 SoftmaxFlashV2, 1 SoftmaxFlash (normalised y), 2 SimpleSoftMax
 
 template <typename T, typename ST, int TPR, int NCHUNK, bool UPDATE>
 __global__ void __launch_bounds__(TPR > 32 ? TPR : 128, TPR > 32 ? 1 : 5)
