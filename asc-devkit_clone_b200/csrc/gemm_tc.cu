@@ -74,7 +74,6 @@ struct GemmParams {
     int group_swap;          // grouped int8 on CTA pairs: a group's last, partial 256-row block is multiplied with the operand roles swapped
     uint32_t idesc;
     uint32_t idesc_swap;     // instruction descriptor of such a block without its N field (the weights are then the 256-row operand)
-    int* tile_counter;       // CTA-pair kernel: not null = tiles are handed out at run time from this counter (zero at launch)
     uint32_t* status;
     EpiParams epi;
 };
@@ -1204,55 +1203,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // CTAs with multicast commits; epilogue warps of both CTAs release the accumulator stage on the
 // leader's barrier.  Plain (non-grouped) problems only.
 
-// Where a role of the CTA-pair kernel gets its next tile from.  Static: cluster c takes tiles c, c + clusters, ...  Dynamic
-// (grouped problems, whose tiles differ in cost by more than a factor of ten): warp 3 of the leader CTA draws tile numbers
-// from a counter in global memory and publishes each one in a two-slot ring that exists in both CTAs' shared memory; every
-// role (producer and epilogue warps of both CTAs, the leader's MMA warp) reads the slot and releases it on the leader's
-// barrier.  A negative number ends the kernel.  The ring lets the producer run one tile ahead of the epilogue and no more,
-// so that at the end of the kernel no cluster sits on tiles that an idle one could take.
-constexpr int kSchedSlots = 2;
 constexpr int kMaxRingStages = 8;  // barrier storage of the CTA-pair kernel's operand ring
-constexpr int kSchedConsumersLeader = 1 + 1 + NUM_EPI_WARPS, kSchedConsumersPeer = 1 + NUM_EPI_WARPS;
+// Tiles of a CTA pair: cluster c takes tiles c, c + clusters, ...  (Handing tiles out at run time from a counter was measured on
+// the grouped configuration, whose tiles differ widely in cost: 554 k against 557 k cycles, and is not kept.)
 struct TileFeed {
-    int next, stride;            // static
-    uint32_t full0, empty0;      // dynamic: own full barriers, the leader's empty barriers (cluster address)
-    const volatile int* slots;
-    int it;
-    bool dynamic, relaxed;
-    __device__ __forceinline__ void init(bool dyn, int cluster_id, int num_clusters, uint64_t* sched_full, uint64_t* sched_empty, const volatile int* sl,
-                                         bool relaxed_wait)
+    int next, stride;
+    __device__ __forceinline__ void init(int cluster_id, int num_clusters)
     {
-        dynamic = dyn;
         next = cluster_id;
         stride = num_clusters;
-        full0 = smem_u32(sched_full);
-        empty0 = smem_u32(sched_empty) & kPeerBitMask;
-        slots = sl;
-        it = 0;
-        relaxed = relaxed_wait;
     }
-    // Called by all lanes of a warp.  False: no more tiles (or the wait was abandoned: `ok` is cleared).
-    __device__ __forceinline__ bool take(int total_tiles, int& tile, bool& ok, volatile uint32_t* abort_smem, uint32_t* status)
+    __device__ __forceinline__ bool take(int total_tiles, int& tile)
     {
-        if (!dynamic) {
-            tile = next;
-            next += stride;
-            return tile < total_tiles;
-        }
-        const int s = it % kSchedSlots;
-        const uint32_t ph = static_cast<uint32_t>(it / kSchedSlots) & 1u;
-        ++it;
-        if (!mbar_wait_cluster(full0 + 8 * s, ph, relaxed, abort_smem, status)) {
-            ok = false;
-            return false;
-        }
-        tile = slots[s];
-        __syncwarp();
-        // The slot may be rewritten once every reader has arrived.  The arrival's address is made to depend on the value read
-        // (tile numbers are below 2^30, so the added term is zero), so it cannot leave before the read has returned; it then
-        // needs no cluster-scope release, which would first wait for all of the warp's stores in flight.
-        if ((threadIdx.x & 31) == 0) mbar_arrive_cluster_tmem(empty0 + 8 * s + (static_cast<uint32_t>(tile + 1) >> 30));
-        return tile >= 0;
+        tile = next;
+        next += stride;
+        return tile < total_tiles;
     }
 };
 
@@ -1300,10 +1265,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint64_t* acc_empty_bar = acc_full_bar + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
-    uint64_t* sched_full = reinterpret_cast<uint64_t*>(tmem_slot + 2);   // [kSchedSlots] in each CTA
-    uint64_t* sched_empty = sched_full + kSchedSlots;                   // [kSchedSlots], the leader's are used
-    volatile int* sched_tile = reinterpret_cast<volatile int*>(sched_empty + kSchedSlots);  // [kSchedSlots] in each CTA
-    static_assert((2 * kMaxRingStages + 4 + 2 * kSchedSlots) * 8 + 8 + kSchedSlots * 4 <= 256, "barrier area");
+    static_assert((2 * kMaxRingStages + 4) * 8 + 8 <= 256, "barrier area");
     static_assert(C::NUM_STAGES <= kMaxRingStages, "barrier area");
     // The ring of operand stages: the compile-time geometry, or (narrower tiles of a call) more and smaller stages in the same bytes.
     const bool cut_ring = KIND != KIND_MXF4 && p.ring_stages > 0;
@@ -1332,10 +1294,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             mbar_init(smem_u32(&acc_full_bar[s]), 1);
             mbar_init(smem_u32(&acc_empty_bar[s]), 2 * NUM_EPI_WARPS);  // epilogue warps of both CTAs
         }
-        for (int s = 0; s < kSchedSlots; ++s) {
-            mbar_init(smem_u32(&sched_full[s]), 1);
-            mbar_init(smem_u32(&sched_empty[s]), kSchedConsumersLeader + kSchedConsumersPeer);
-        }
         *abort_word = 0u;
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
@@ -1353,7 +1311,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_tiles = p.groups > 0 ? tile_start[p.groups] : num_m * num_n;
-    const bool dynamic_tiles = p.tile_counter != nullptr;
 
     if (warp == 0) {
         // ===== TMA producer (both CTAs) =====
@@ -1362,8 +1319,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         bool ok = true;
         TileInfo t;
         TileFeed feed;
-        feed.init(dynamic_tiles, cluster_id, num_clusters, sched_full, sched_empty, sched_tile, false);
-        for (int tile; ok && feed.take(total_tiles, tile, ok, abort_word, p.status) && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t);) {
+        feed.init(cluster_id, num_clusters);
+        for (int tile; ok && feed.take(total_tiles, tile) && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t);) {
             // rows past the end of a group belong to the next group (or lie outside the matrix and read as zero): they are
             // multiplied like the others and never stored
             // A swapped block (see GemmParams::group_swap) takes its swap_n rows as the narrow operand: each CTA loads half of
@@ -1440,8 +1397,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         int cursor = 0;
         TileInfo t;
         TileFeed feed;
-        feed.init(dynamic_tiles, cluster_id, num_clusters, sched_full, sched_empty, sched_tile, false);
-        for (int tile; ok && feed.take(total_tiles, tile, ok, abort_word, p.status) && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t); ++acc_iter) {
+        feed.init(cluster_id, num_clusters);
+        for (int tile; ok && feed.take(total_tiles, tile) && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t); ++acc_iter) {
             const int acc_stage = acc_iter & 1;
             const uint32_t acc_phase = (acc_iter >> 1) & 1u;
             ok = mbar_wait(smem_u32(&acc_empty_bar[acc_stage]), acc_phase ^ 1u, abort_word, p.status);
@@ -1506,27 +1463,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 cur.advance();
             }
         }
-    } else if (warp == 3 && rank == 0 && dynamic_tiles) {
-        // ===== tile scheduler (leader CTA only) =====
-        const uint32_t peer_tile0 = map_to_cta(smem_u32(const_cast<int*>(sched_tile)), 1), peer_full0 = map_to_cta(smem_u32(sched_full), 1);
-        bool ok = true;
-        for (int it = 0; ok; ++it) {
-            const int s = it % kSchedSlots;
-            const uint32_t ph = static_cast<uint32_t>(it / kSchedSlots) & 1u;
-            ok = mbar_wait_cluster(smem_u32(&sched_empty[s]), ph ^ 1u, true, abort_word, p.status);
-            if (!ok) break;
-            int tile = 0;
-            if (lane == 0) {
-                tile = atomicAdd(p.tile_counter, 1);
-                if (tile >= total_tiles) tile = -1;
-                sched_tile[s] = tile;
-                st_cluster_u32(peer_tile0 + 4 * s, static_cast<uint32_t>(tile));
-                mbar_arrive_cluster(smem_u32(&sched_full[s]));   // release at cluster scope: the slot is written before the arrival is seen
-                mbar_arrive_cluster(peer_full0 + 8 * s);
-            }
-            tile = __shfl_sync(0xFFFFFFFFu, tile, 0);
-            if (tile < 0) break;
-        }
     } else if (warp >= 4) {
         // ===== epilogue (both CTAs, each for its own 128 rows) =====
         const int quad = warp & 3;
@@ -1537,8 +1473,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         bool ok = true;
         TileInfo t;
         TileFeed feed;
-        feed.init(dynamic_tiles, cluster_id, num_clusters, sched_full, sched_empty, sched_tile, true);
-        for (int tile; ok && feed.take(total_tiles, tile, ok, abort_word, p.status) && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t); ++acc_iter) {
+        feed.init(cluster_id, num_clusters);
+        for (int tile; ok && feed.take(total_tiles, tile) && locate_pair_tile(p, tile, num_m, total_tiles, bn, row_start, tile_start, cursor, t); ++acc_iter) {
             const int acc_stage = acc_iter & 1;
             const uint32_t acc_phase = (acc_iter >> 1) & 1u;
             if (!t.swap_n) t.row0 += static_cast<int>(rank) * BLOCK_M;  // this CTA's half of the pair tile
@@ -2092,18 +2028,6 @@ int run_gemm(const ascb200_gemm_desc* d, const int64_t* group_counts, int groups
         if (kind == ASCB200_KIND_S8) {
             p.idesc = make_idesc(2, 1, 1, a_mn, b_mn, 2 * BLOCK_M, block_n);
             CUtensorMap tx32 = ta;
-            if (grouped && !fixed && getenv("ASCB200_DYNAMIC_TILES") && getenv("ASCB200_DYNAMIC_TILES")[0] == '1') {
-                // Opt-in: tiles are handed out at run time from a counter in this stream's scratch, cleared on the stream
-                // before the launch.  Tiles of a grouped problem differ widely in cost (a swapped block of 16 rows against a
-                // full one), and with the static assignment the busiest SM of the 64-group configuration spends 90 % of
-                // the kernel in MMAs, the idlest 52 %; yet the kernel did not get shorter with run-time hand-out (576 k against 551 k
-                // cycles): its small groups are bound by the one read of their weights from HBM, not by the tile order.
-                void* ptr = nullptr;
-                rc = stream_scratch(st, 256, stream, &ptr);
-                if (rc != ASCB200_OK) return rc;
-                ASCB200_CUDA(cudaMemsetAsync(ptr, 0, sizeof(int), stream));
-                p.tile_counter = static_cast<int*>(ptr);
-            }
             if (p.group_swap) {
                 // the weights as the 256-row operand, rows of A as the narrow one (its N field is filled in per block);
                 // A once more with boxes of 32 rows, for blocks that hold fewer than 97 rows per CTA

@@ -276,10 +276,6 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a,
 {
     asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v)
-{
-    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
-}
 // Tile load issued by either CTA of a pair: data lands in the issuing CTA, the bytes are counted on
 // the leader's barrier.  No multicast: every CTA fetches exactly the rows it owns.
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, int x, int y, int z, uint32_t leader_bar)

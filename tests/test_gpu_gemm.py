@@ -366,8 +366,6 @@ def test_grouped_a8w8_swapped_tail_blocks(trans_b, c_dtype, monkeypatch):
     block's rows, rounded up to 16, on the N side).  Group sizes cover every box count of the narrow operand, tails that end on
     and next to multiples of 16 and 32, whole blocks before a tail, and a column count that is no multiple of the tile width."""
     monkeypatch.setenv("ASCB200_PAIR_N", "256")
-    if c_dtype == 2 and trans_b:
-        monkeypatch.setenv("ASCB200_DYNAMIC_TILES", "1")   # tiles handed out at run time from a counter instead of by cluster number
     ab = dev()
     counts = np.array([1, 15, 16, 17, 0, 63, 64, 65, 96, 97, 128, 129, 191, 193, 240, 241, 255, 256, 257, 512 + 33, 768], np.int64)
     G, k, n = len(counts), 384, 608
