@@ -979,11 +979,15 @@ __device__ __forceinline__ void splitk_send_tile(uint32_t leader_part, uint32_t 
 }
 
 // ---- the kernel --------------------------------------------------------------------------------
-template <int KIND, int BLOCK_N>
+// GROUPED = false compiles the group tables, the per-group tile search and the swapped blocks out of the kernel: a plain
+// launch through the grouped build took 0.3 to 0.8 us longer (one rank's slab of the 8-GPU A8W8 split: 21.0 against 20.2 us).
+template <int KIND, int BLOCK_N, bool GROUPED>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ OutMaps outs,
-               const GemmParams p)
+               const GemmParams p_in)
 {
+    GemmParams p = p_in;
+    if constexpr (!GROUPED) p.groups = 0, p.group_swap = 0;
     using C = Cfg<KIND, BLOCK_N>;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzled tiles need 1024-byte aligned bases
@@ -1244,12 +1248,14 @@ struct Cfg2 {
     static constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256 + TABLE_BYTES;
 };
 
-template <int KIND, int BLOCK_N>
+template <int KIND, int BLOCK_N, bool GROUPED>   // GROUPED: see gemm_tc_kernel
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const __grid_constant__ OutMaps outs,
-                    const GemmParams p)
+                    const GemmParams p_in)
 {
+    GemmParams p = p_in;
+    if constexpr (!GROUPED) p.groups = 0, p.group_swap = 0;
     using C = Cfg2<KIND, BLOCK_N>;
     constexpr int PAIR_M = 2 * BLOCK_M;
     extern __shared__ uint8_t smem_raw[];
@@ -1649,15 +1655,15 @@ bool make_out_map(CUtensorMap* map, int dtype, const void* base, uint64_t cols, 
     return r == CUDA_SUCCESS;
 }
 
-template <int KIND, int BLOCK_N>
-int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& outs, const GemmParams& p, int grid, cudaStream_t stream)
+template <int KIND, int BLOCK_N, bool GROUPED>
+int launch_gemm_as(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& outs, const GemmParams& p, int grid, cudaStream_t stream)
 {
     using C = Cfg<KIND, BLOCK_N>;
     static bool configured[16] = {};
     int dev = 0;
     ASCB200_CUDA(cudaGetDevice(&dev));
     if (!configured[dev & 15]) {
-        ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<KIND, BLOCK_N, GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured[dev & 15] = true;
     }
     // Split K over a cluster: only while every cluster gets at most one tile, every CTA at least one K block, and the other
@@ -1667,16 +1673,25 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& out
     while (sk > 1 && ((sk - 1) * BLOCK_N * 512 > C::NUM_STAGES * C::STAGE_BYTES || p.num_k_blocks <= (sk - 1) * ((p.num_k_blocks + sk - 1) / sk))) sk >>= 1;
     q.split_k = sk > 1 ? sk : 0;
     if (q.split_k > 1) {
-        ASCB200_CUDA(launch_pdl_cluster(gemm_tc_kernel<KIND, BLOCK_N>, grid * q.split_k, NUM_THREADS, C::SMEM_BYTES, stream, static_cast<unsigned>(q.split_k), ta, tb,
+        ASCB200_CUDA(launch_pdl_cluster(gemm_tc_kernel<KIND, BLOCK_N, GROUPED>, grid * q.split_k, NUM_THREADS, C::SMEM_BYTES, stream, static_cast<unsigned>(q.split_k), ta, tb,
                                         outs, q));
         return ASCB200_OK;
     }
-    ASCB200_CUDA(launch_pdl(gemm_tc_kernel<KIND, BLOCK_N>, grid, NUM_THREADS, C::SMEM_BYTES, stream, ta, tb, outs, q));
+    ASCB200_CUDA(launch_pdl(gemm_tc_kernel<KIND, BLOCK_N, GROUPED>, grid, NUM_THREADS, C::SMEM_BYTES, stream, ta, tb, outs, q));
     return ASCB200_OK;
 }
 
+// Grouped calls exist for int8 only; every other call takes the build without the group code.
 template <int KIND, int BLOCK_N>
-int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsfa, const CUtensorMap& tsfb, const OutMaps& outs,
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& outs, const GemmParams& p, int grid, cudaStream_t stream)
+{
+    if constexpr (KIND == KIND_I8)
+        if (p.groups > 0) return launch_gemm_as<KIND, BLOCK_N, true>(ta, tb, outs, p, grid, stream);
+    return launch_gemm_as<KIND, BLOCK_N, false>(ta, tb, outs, p, grid, stream);
+}
+
+template <int KIND, int BLOCK_N, bool GROUPED>
+int launch_gemm_pair_as(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsfa, const CUtensorMap& tsfb, const OutMaps& outs,
                      const GemmParams& p, int clusters, cudaStream_t stream)
 {
     using C = Cfg2<KIND, BLOCK_N>;
@@ -1684,19 +1699,26 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     int dev = 0;
     ASCB200_CUDA(cudaGetDevice(&dev));
     if (!configured[dev & 15]) {
-        ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        ASCB200_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<KIND, BLOCK_N, GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured[dev & 15] = true;
     }
     GemmParams q = p;
     if (KIND != KIND_MXF4 && !p.b_mn && !(getenv("ASCB200_NO_RING_CUT") && getenv("ASCB200_NO_RING_CUT")[0] == '1')) {
-        // K-major B: a stage holds 128 rows of A and pair_n / 2 rows of B.  The operand round trip (stage released -> producer
-        // -> L2 -> shared memory -> MMA) takes about 3000 cycles, so with six stages a K block cannot take less than about 510
-        // cycles whatever the tile width; narrower tiles get the same bytes as more stages.
+        // K-major B: a stage holds 128 rows of A and pair_n / 2 rows of B, so narrower tiles get the ring's bytes as more
+        // stages (worth 1 to 2 % on a 160-column slab tile; what limits those tiles is the duration of a narrow MMA).
         q.ring_stage_bytes = A_TILE_BYTES + (p.pair_n / 2) * ROW_BYTES;
         q.ring_stages = std::min(kMaxRingStages, C::NUM_STAGES * C::STAGE_BYTES / q.ring_stage_bytes);
     }
-    ASCB200_CUDA(launch_pdl(gemm_tc_pair_kernel<KIND, BLOCK_N>, 2 * clusters, NUM_THREADS, C::SMEM_BYTES, stream, ta, tb, tsfa, tsfb, outs, q));
+    ASCB200_CUDA(launch_pdl(gemm_tc_pair_kernel<KIND, BLOCK_N, GROUPED>, 2 * clusters, NUM_THREADS, C::SMEM_BYTES, stream, ta, tb, tsfa, tsfb, outs, q));
     return ASCB200_OK;
+}
+template <int KIND, int BLOCK_N>
+int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsfa, const CUtensorMap& tsfb, const OutMaps& outs,
+                     const GemmParams& p, int clusters, cudaStream_t stream)
+{
+    if constexpr (KIND == KIND_I8)
+        if (p.groups > 0) return launch_gemm_pair_as<KIND, BLOCK_N, true>(ta, tb, tsfa, tsfb, outs, p, clusters, stream);
+    return launch_gemm_pair_as<KIND, BLOCK_N, false>(ta, tb, tsfa, tsfb, outs, p, clusters, stream);
 }
 
 // Split K over a cluster (single-CTA kernel): 4 or 2 CTAs per tile, or 0.  Time of a small problem ~ 5 us fixed + 0.21 us per K
