@@ -175,7 +175,12 @@ enum { ASCB200_SCALE_A_PREPACKED = 1, ASCB200_SCALE_B_PREPACKED = 2,
 /* One whole Matmul: what Matmul<...>::IterateAll produces for the object state set by
  * SetTensorA / SetTensorB / SetBias / SetQuantScalar / SetQuantVector
  * (include/adv_api/matmul/matmul.h:79-399; impl/adv_api/detail/matmul/matmul_impl.h:119-139),
- * MX variant with SetTensorScaleA/B (impl/adv_api/detail/matmul/mx_matmul_impl.h:136-173). */
+ * MX variant with SetTensorScaleA/B (impl/adv_api/detail/matmul/mx_matmul_impl.h:136-173).
+ *
+ * Integer results do not depend on how the library tiles the problem.  fp32 accumulation follows the tile plan (a tile's K blocks
+ * in ascending order; with few tiles and a long K, two or four CTAs of a cluster each sum a consecutive range of K blocks and
+ * the ranges are added in ascending order), so a floating-point result is reproducible for a given shape and device, and equal to
+ * any other plan's within the rounding of fp32 sums. */
 ASCB200_API int ascb200_gemm(const ascb200_gemm_desc* desc, void* stream);
 /* MXFP4 and scratch memory.  The tensor core reads MX scale factors in tiles of 128 rows x 4 K-blocks, so ascb200_gemm re-tiles
  * every scale tensor that is not prepacked into device scratch before the GEMM (one extra, small launch).  The scratch belongs
